@@ -1,0 +1,307 @@
+/*
+ * rns_b200.h - C ABI of the B200 (sm_100a) RNS linear library, librns_b200.so.
+ *
+ * Every entry point takes plain pointers and sizes, enqueues its work on the
+ * stream it is given and returns a status code at once; none of them
+ * allocates, frees or synchronises (the one set-up exception is documented at
+ * its declaration).  Pointers named "d_*" are device pointers on the current
+ * device; "moduli" is always a host array.  All matrices are row-major.
+ *
+ * Vocabulary: a *channel* is one modulus m_c of the residue number system; a
+ * *plane* is the int8 matrix of centred residues of one channel; P is the
+ * product of the active moduli.
+ *
+ * Each declaration cites the interface of the reference implementation
+ * (Nek1tt/rns-llm v0.5) that it stands in for, as path:line inside that
+ * project.
+ */
+#ifndef RNS_B200_H_
+#define RNS_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(_WIN32)
+#define RNS_API
+#else
+#define RNS_API __attribute__((visibility("default")))
+#endif
+
+/* Opaque stand-in for cudaStream_t so that C callers need no CUDA headers. */
+typedef void* rns_stream_t;
+
+#define RNS_MAX_CHANNELS 10   /* reference: csrc/rns_cuda.cu:963-975 accepts 2..10 */
+#define RNS_TC_MAX_CHANNELS 8 /* channel count the tcgen05 kernel is instantiated for */
+
+typedef enum rns_status {
+    RNS_OK = 0,
+    RNS_ERR_INVALID_ARGUMENT = 1, /* bad pointer, size, stride, enum value         */
+    RNS_ERR_BAD_MODULI = 2,       /* not in [2,255] or not pairwise coprime        */
+    RNS_ERR_UNSUPPORTED = 3,      /* valid request outside what the kernels cover  */
+    RNS_ERR_OVERFLOW = 4,         /* P or a dot-product bound exceeds its type     */
+    RNS_ERR_CUDA = 5,             /* a CUDA runtime/driver call failed             */
+    RNS_ERR_DEVICE_TIMEOUT = 6    /* a bounded device-side wait expired            */
+} rns_status;
+
+/* Element type of the source integers handed to the encoders. */
+typedef enum rns_int_type { RNS_INT8 = 0, RNS_INT16 = 1, RNS_INT32 = 2 } rns_int_type;
+
+/* What the fused GEMM epilogue stores. */
+typedef enum rns_out_type {
+    RNS_OUT_INT64 = 0, /* exact integer, as the reference's workspace.output     */
+    RNS_OUT_INT32 = 1, /* exact integer; requires P/2 < 2^31                     */
+    RNS_OUT_F16 = 2,   /* dequantised: f16( f32(x)*row_scale*col_scale + bias )  */
+    RNS_OUT_BF16 = 3,
+    RNS_OUT_F32 = 4
+} rns_out_type;
+
+/* Floating type of an activation tensor given to the quantiser. */
+typedef enum rns_float_type { RNS_F16 = 0, RNS_BF16 = 1, RNS_F32 = 2 } rns_float_type;
+
+/* Text of the last error raised on the calling thread ("" if none). */
+RNS_API const char* rns_last_error(void);
+
+/* Library/ABI version: major*10000 + minor*100 + patch. */
+RNS_API int rns_version(void);
+
+/* ------------------------------------------------------------------------
+ * Host-side constants
+ * --------------------------------------------------------------------- */
+
+/*
+ * Validates moduli (each in [2,255], pairwise coprime: reference
+ * src/rns_llm/reference.py:11-23) and writes the constants the reference keeps
+ * per (device, moduli) in _DeviceConstants (backends/cuda_backend.py:48-66,
+ * 137-166): reciprocals floor(2^32/m) [channels], pairwise inverses
+ * inv[j*channels+i] = m_j^-1 mod m_i for j<i [channels*channels], and P.
+ * Any output pointer may be NULL.  RNS_ERR_OVERFLOW when P > INT64_MAX.
+ */
+RNS_API int rns_host_constants(const int32_t* moduli, int channels,
+                               int64_t* reciprocals, int32_t* pairwise_inverses,
+                               int64_t* modulus_product);
+
+/*
+ * Smallest prefix length c >= min_channels with 2*bound < m_0*...*m_{c-1}
+ * (reference src/rns_llm/adaptive.py:15-41).  Returns c, or a negative
+ * rns_status: -RNS_ERR_OVERFLOW when even the full set is too small.
+ */
+RNS_API int rns_minimal_prefix_channels(const int32_t* moduli, int channels,
+                                        int64_t absolute_bound, int min_channels);
+
+/*
+ * Host evaluation of the exact expressions the device epilogue and the
+ * in-kernel encoder use (same source, compiled for the CPU).  For tests and
+ * for callers that want to check a modulus set without a GPU; no counterpart
+ * in the reference, whose device arithmetic cannot run on the host.
+ *   rns_host_reconstruct: sums int32 [channels, count] (per-channel dot
+ *     products, any representative) -> signed value, as csrc/rns_cuda.cu:
+ *     442-476 would produce from the same accumulators, using the first
+ *     `active` channels.
+ *   rns_host_encode_centered_i8: int8 [count] -> centred planes int8
+ *     [channels, count] through the packed single-fold encoder (count % 4 == 0,
+ *     every modulus >= 86).
+ */
+RNS_API int rns_host_reconstruct(const int32_t* sums, int64_t count, const int32_t* moduli,
+                                 int channels, int active, int64_t* out);
+RNS_API int rns_host_encode_centered_i8(const int8_t* values, int64_t count,
+                                        const int32_t* moduli, int channels, int8_t* out);
+
+/* ------------------------------------------------------------------------
+ * Plane-level entry points: the six functions of the reference's FFI module
+ * rns_llm._C (csrc/bindings.cpp:45-75), with raw pointers in place of tensors.
+ * --------------------------------------------------------------------- */
+
+/*
+ * encode_int8 (csrc/bindings.cpp:46-49; kernel csrc/rns_cuda.cu:126-148):
+ * canonical residues in [0, m).  d_out is uint8 [channels, elements].
+ */
+RNS_API int rns_encode_canonical_i8(const int8_t* d_values, int64_t elements,
+                                    const int32_t* moduli, int channels,
+                                    uint8_t* d_out, rns_stream_t stream);
+
+/*
+ * encode_centered (csrc/bindings.cpp:51-54; kernel csrc/rns_cuda.cu:98-124):
+ * centred residues; C remainder then fold into [-floor(m/2), floor(m/2)], so
+ * for an even modulus -m/2 stays negative.  d_out is int8 [channels, elements].
+ */
+RNS_API int rns_encode_centered(const void* d_values, rns_int_type type, int64_t elements,
+                                const int32_t* moduli, int channels,
+                                int8_t* d_out, rns_stream_t stream);
+
+/*
+ * matmul_residues (csrc/bindings.cpp:56-59; csrc/rns_cuda.cu:628-709):
+ * canonical uint8 planes a [channels,M,K] x b [channels,K,N] -> canonical
+ * uint8 [channels,M,N].  The reference's kernel_id (0..2) selects between
+ * kernels with identical results; it is validated and otherwise ignored.
+ */
+RNS_API int rns_matmul_canonical_planes(const uint8_t* d_a, const uint8_t* d_b,
+                                        const int32_t* moduli, int channels,
+                                        int m, int k, int n, int kernel_id,
+                                        uint8_t* d_out, rns_stream_t stream);
+
+/*
+ * matmul_centered_residues (csrc/bindings.cpp:61-64; csrc/rns_cuda.cu:711-816):
+ * centred int8 planes -> centred int8 planes [channels,M,N].  kernel_id 0..3
+ * (scalar, dp4a, dp4a_safe, cublas) is validated; every value runs the same
+ * exact kernel.  kernel_id 3 keeps the reference's K%4==0 && N%4==0 check.
+ */
+RNS_API int rns_matmul_centered_planes(const int8_t* d_a, const int8_t* d_b,
+                                       const int32_t* moduli, int channels,
+                                       int m, int k, int n, int kernel_id,
+                                       int8_t* d_out, rns_stream_t stream);
+
+/*
+ * decode_garner (csrc/bindings.cpp:66-69; csrc/rns_cuda.cu:416-440, 818-885):
+ * centred int8 planes [channels, elements] -> signed int64 in (-P/2, P/2].
+ */
+RNS_API int rns_decode_garner(const int8_t* d_residues, int64_t elements,
+                              const int32_t* moduli, int channels,
+                              int64_t* d_out, rns_stream_t stream);
+
+/*
+ * matmul_centered_fused_out (csrc/bindings.cpp:71-74; csrc/rns_cuda.cu:887-980):
+ * centred planes a [channels,M,K], b [channels,K,N] -> d_out int64 [M,N].
+ * d_accumulators (int32 [channels,M,N]) is the caller's workspace as in the
+ * reference and receives the raw per-channel sums.  lut_channels (0..2) is
+ * validated and otherwise ignored: reduction happens in registers.  Keeps the
+ * reference's K%4==0 && N%4==0 && 2<=channels<=10 checks.
+ */
+RNS_API int rns_matmul_centered_fused_out(const int8_t* d_a, const int8_t* d_b,
+                                          const int32_t* moduli, int channels,
+                                          int m, int k, int n, int lut_channels,
+                                          int32_t* d_accumulators, int64_t* d_out,
+                                          rns_stream_t stream);
+
+/* ------------------------------------------------------------------------
+ * The fused sm_100a path
+ * --------------------------------------------------------------------- */
+
+/*
+ * Arguments of rns_linear_fused.  Replaces, in one launch, the chain
+ * encode_centered(a) -> cublasGemmStridedBatchedEx -> fused_reduce_garner_kernel
+ * -> eager dequantisation of the reference (backends/cuda_backend.py:514-539,
+ * 398-459; csrc/rns_cuda.cu:478-523, 442-476; layers/rns_linear.py:264, 272-275).
+ *
+ * Activations come either as source integers d_a int8 [M,K] (row stride lda,
+ * residues formed inside the kernel) or as planes d_a_planes int8
+ * [channels,M,K] produced by rns_quantize_activations / rns_encode_centered
+ * (row stride lda, plane stride a_plane_stride); exactly one is non-NULL.
+ * Weights are ALWAYS source integers d_w int8 [N,K] (the nn.Linear layout, row
+ * stride ldw): one byte per value whatever the channel count; their residues
+ * are formed inside the kernel.
+ *
+ * d_active_channels, when non-NULL, points to a device int c (2..channels):
+ * only the first c moduli are used (adaptive prefix, backends/cuda_backend.py:
+ * 573-622, decided on the device by rns_select_channels).
+ *
+ * Integer output types store x = sum_k a[m,k]*w[n,k] reconstructed and
+ * recentred exactly as csrc/rns_cuda.cu:380-414.  Floating output types store
+ * type( f32(x) * row_scale[m*row_scale_stride] * col_scale[n] (+ bias[n]) )
+ * with every product and the sum rounded to f32 in that order, which is the
+ * arithmetic of layers/rns_linear.py:272-275; row_scale_stride is 0 for a
+ * per-tensor activation scale and 1 for per-row scales.
+ *
+ * d_status, when non-NULL, is a device int the kernel sets to a non-zero
+ * rns_status (RNS_ERR_DEVICE_TIMEOUT) if a bounded wait expires.
+ *
+ * Requirements of the tensor-core kernel: K % 16 == 0, lda/ldw/a_plane_stride
+ * multiples of 16, 16-byte aligned bases, 2 <= channels <= 8, every modulus
+ * >= 86 (one fold maps any int8 value to its centred residue).  Anything else
+ * returns RNS_ERR_UNSUPPORTED; callers then use the plane-level functions.
+ */
+typedef struct rns_linear_args {
+    int32_t m, n, k;
+    int32_t channels;
+    int32_t moduli[RNS_MAX_CHANNELS];
+    const int8_t* d_a;
+    const int8_t* d_a_planes;
+    int64_t lda;
+    int64_t a_plane_stride;
+    const int8_t* d_w;
+    int64_t ldw;
+    const int32_t* d_active_channels;
+    void* d_out;
+    int64_t ldo;              /* in elements of the output type */
+    int32_t out_type;         /* rns_out_type */
+    const float* d_row_scale; /* floating outputs only */
+    int32_t row_scale_stride; /* 0 or 1 */
+    const float* d_col_scale; /* [N], floating outputs only */
+    const float* d_bias;      /* [N] or NULL */
+    int32_t* d_status;
+    int32_t tile_n;           /* 0 = choose; else 16..128, multiple of 16 */
+    int32_t tile_k;           /* 0 = choose; else 64 or 128 */
+} rns_linear_args;
+
+RNS_API int rns_linear_fused(const rns_linear_args* args, rns_stream_t stream);
+
+/* 1 when rns_linear_fused accepts this problem, 0 when it would return
+ * RNS_ERR_UNSUPPORTED (the role of CudaRNSBackend.cublas_compatible,
+ * backends/cuda_backend.py:224-239). */
+RNS_API int rns_linear_fused_supported(const int32_t* moduli, int channels, int k,
+                                       int64_t lda, int64_t ldw);
+
+/*
+ * Activation quantiser: RNSLinear._symmetric_scale + _quantize
+ * (layers/rns_linear.py:154-166, 239-241) and, optionally, the activation
+ * encode of backends/cuda_backend.py:532, in at most two launches and without
+ * a host round trip.
+ *
+ *   scale = max(absmax / quant_max, FLT_EPSILON)   (per tensor, or per row when
+ *                                                   per_row != 0)
+ *   q     = clamp(rint(x / scale), -quant_max, quant_max)      (ties to even)
+ *
+ * d_x is [M,K] with row stride ldx (elements).  Outputs: d_q int8 [M,K]
+ * (may be NULL when only planes are wanted), d_planes int8 [channels,M,K]
+ * (NULL to skip), d_scale float [1] or [M], d_row_l1_max int32 [1] = max_m
+ * sum_k |q[m,k]| (NULL to skip; input of rns_select_channels).
+ * d_scratch: 16 bytes of device scratch owned by the caller's stream.
+ * quant_max must be 127 (8-bit sources).
+ */
+RNS_API int rns_quantize_activations(const void* d_x, rns_float_type type,
+                                     int m, int k, int64_t ldx, int per_row,
+                                     int quant_max,
+                                     const int32_t* moduli, int channels,
+                                     int8_t* d_q, int8_t* d_planes, float* d_scale,
+                                     int32_t* d_row_l1_max, void* d_scratch,
+                                     rns_stream_t stream);
+
+/*
+ * Row-L1 maximum of already-quantised activations: max_m sum_k |a[m,k]|, the
+ * quantity select_adaptive_variant reads back with .item()
+ * (backends/cuda_backend.py:591), left on the device instead.
+ */
+RNS_API int rns_row_l1_max_i8(const int8_t* d_a, int m, int k, int64_t lda,
+                              int32_t* d_row_l1_max, rns_stream_t stream);
+
+/*
+ * On-device adaptive prefix selection (backends/cuda_backend.py:573-601 +
+ * src/rns_llm/adaptive.py:15-52): bound = *d_row_l1_max * max_abs_weight;
+ * *d_active_channels = smallest c >= min_channels with 2*bound < prod(m[:c]).
+ * When even the full set is too small the reference raises OverflowError; here
+ * *d_active_channels = channels and *d_status = RNS_ERR_OVERFLOW (if given).
+ * d_meta, when non-NULL, receives int64 {channels, bound, capacity} for
+ * last_adaptive_metadata, to be read lazily.
+ */
+RNS_API int rns_select_channels(const int32_t* d_row_l1_max, int32_t max_abs_weight,
+                                const int32_t* moduli, int channels, int min_channels,
+                                int32_t* d_active_channels, int64_t* d_meta,
+                                int32_t* d_status, rns_stream_t stream);
+
+/*
+ * Weight quantiser: per-output-channel symmetric int8 of layers/rns_linear.py:
+ * 183-184 kept in the nn.Linear layout [N,K] (no transpose, no planes).
+ * d_w is [N,K] (row stride ldw elements); d_wq int8 [N,K]; d_scale float [N];
+ * d_max_abs int32 [1] = max |wq| (NULL to skip; feeds rns_select_channels).
+ */
+RNS_API int rns_quantize_weight(const void* d_w, rns_float_type type, int n, int k,
+                                int64_t ldw, int quant_max, int8_t* d_wq, float* d_scale,
+                                int32_t* d_max_abs, rns_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RNS_B200_H_ */

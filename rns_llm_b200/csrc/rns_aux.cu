@@ -1,0 +1,609 @@
+// Plane-level kernels (the surface of the reference's FFI module) and the
+// quantisation / channel-selection prologues of the fused path.  These are
+// HBM-bound or tiny; the tensor-core GEMM lives in rns_gemm_sm100.cu.
+#include "rns_common.cuh"
+
+#include <cfloat>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+namespace rns {
+
+static inline cudaStream_t as_stream(rns_stream_t s) { return reinterpret_cast<cudaStream_t>(s); }
+
+static int grid_for(int64_t work, int threads, int cap = 148 * 16) {
+    int64_t blocks = (work + threads - 1) / threads;
+    if (blocks < 1) blocks = 1;
+    if (blocks > cap) blocks = cap;
+    return (int)blocks;
+}
+
+struct ModList {
+    int32_t channels;
+    int32_t mod[kMaxCh];
+};
+
+static ModList modlist(const Plan& p) {
+    ModList l;
+    l.channels = p.channels;
+    for (int i = 0; i < kMaxCh; ++i) l.mod[i] = p.mod[i];
+    return l;
+}
+
+// ---------------------------------------------------------------------------
+// Encoders.  One thread per source element, all channels: the source is read
+// once (the reference reads it once per channel, csrc/rns_cuda.cu:98-124).
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void encode_centered_kernel(const T* __restrict__ values, int8_t* __restrict__ out,
+                                       ModList ml, int64_t elements) {
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < elements;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        const int v = (int)values[i];
+#pragma unroll 1
+        for (int c = 0; c < ml.channels; ++c) {
+            const int m = ml.mod[c];
+            int r = v % m;  // C remainder: sign of the dividend
+            const int half = m / 2;
+            if (r > half) r -= m;
+            else if (r < -half) r += m;
+            out[(int64_t)c * elements + i] = (int8_t)r;
+        }
+    }
+}
+
+__global__ void encode_canonical_kernel(const int8_t* __restrict__ values, uint8_t* __restrict__ out,
+                                        ModList ml, int64_t elements) {
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < elements;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        const int v = (int)values[i];
+#pragma unroll 1
+        for (int c = 0; c < ml.channels; ++c) {
+            const int m = ml.mod[c];
+            int r = v % m;
+            if (r < 0) r += m;
+            out[(int64_t)c * elements + i] = (uint8_t)r;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Plane GEMM: exact per-channel product of byte planes with int64 sums, tiled
+// through shared memory.  Serves the plane-level entry points only (arbitrary
+// shapes, B stored [K,N]); the product path is the tcgen05 kernel.
+//   MODE 0: canonical uint8 in, canonical uint8 out
+//   MODE 1: centred int8 in, centred int8 out
+//   MODE 2: centred int8 in, raw int32 sums out
+// ---------------------------------------------------------------------------
+constexpr int kPT = 32;  // output tile edge
+constexpr int kPK = 32;  // k slab
+
+template <int MODE>
+__global__ void __launch_bounds__(256)
+plane_gemm_kernel(const void* __restrict__ a_, const void* __restrict__ b_, void* __restrict__ out_,
+                  ModList ml, int m, int k, int n) {
+    using In = typename std::conditional<MODE == 0, uint8_t, int8_t>::type;
+    const In* a = static_cast<const In*>(a_) + (int64_t)blockIdx.z * m * k;
+    const In* b = static_cast<const In*>(b_) + (int64_t)blockIdx.z * k * n;
+    __shared__ int sa[kPT][kPK + 1];
+    __shared__ int sb[kPK][kPT + 1];
+    const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;  // each thread: 2x2 outputs
+    const int row0 = blockIdx.y * kPT, col0 = blockIdx.x * kPT;
+    long long acc[2][2] = {{0, 0}, {0, 0}};
+    for (int k0 = 0; k0 < k; k0 += kPK) {
+        for (int idx = threadIdx.x; idx < kPT * kPK; idx += 256) {
+            const int r = idx / kPK, c = idx % kPK;
+            const int gr = row0 + r, gc = k0 + c;
+            sa[r][c] = (gr < m && gc < k) ? (int)a[(int64_t)gr * k + gc] : 0;
+            const int br = idx / kPT, bc = idx % kPT;
+            const int gbr = k0 + br, gbc = col0 + bc;
+            sb[br][bc] = (gbr < k && gbc < n) ? (int)b[(int64_t)gbr * n + gbc] : 0;
+        }
+        __syncthreads();
+#pragma unroll 8
+        for (int kk = 0; kk < kPK; ++kk) {
+            const int a0 = sa[ty * 2][kk], a1 = sa[ty * 2 + 1][kk];
+            const int b0 = sb[kk][tx * 2], b1 = sb[kk][tx * 2 + 1];
+            acc[0][0] += a0 * b0; acc[0][1] += a0 * b1;
+            acc[1][0] += a1 * b0; acc[1][1] += a1 * b1;
+        }
+        __syncthreads();
+    }
+    const int mod = ml.mod[blockIdx.z];
+    for (int i = 0; i < 2; ++i)
+        for (int j = 0; j < 2; ++j) {
+            const int gr = row0 + ty * 2 + i, gc = col0 + tx * 2 + j;
+            if (gr >= m || gc >= n) continue;
+            const int64_t o = ((int64_t)blockIdx.z * m + gr) * n + gc;
+            if (MODE == 2) {
+                static_cast<int32_t*>(out_)[o] = (int32_t)acc[i][j];
+            } else {
+                long long r = acc[i][j] % mod;
+                if (MODE == 0) {
+                    if (r < 0) r += mod;
+                    static_cast<uint8_t*>(out_)[o] = (uint8_t)r;
+                } else {
+                    const int half = mod / 2;
+                    if (r > half) r -= mod;
+                    else if (r < -half) r += mod;
+                    static_cast<int8_t*>(out_)[o] = (int8_t)r;
+                }
+            }
+        }
+}
+
+// ---------------------------------------------------------------------------
+// Reconstruction from planes: SRC = int8 centred residues or int32 raw sums.
+// ---------------------------------------------------------------------------
+template <int R, typename SRC>
+__global__ void __launch_bounds__(256)
+garner_planes_kernel(const SRC* __restrict__ src, int64_t* __restrict__ out,
+                     const __grid_constant__ Plan pl, int64_t elements) {
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < elements;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        int acc[R];
+#pragma unroll
+        for (int c = 0; c < R; ++c) acc[c] = (int)src[(int64_t)c * elements + i];
+        out[i] = reconstruct<R>(acc, pl, R);
+    }
+}
+
+template <typename SRC>
+static int launch_garner(const SRC* src, int64_t* out, const Plan& pl, int64_t elements,
+                         cudaStream_t st) {
+    const int blocks = grid_for(elements, 256);
+#define RNS_CASE(RR) \
+    case RR: garner_planes_kernel<RR, SRC><<<blocks, 256, 0, st>>>(src, out, pl, elements); break;
+    switch (pl.channels) {
+        RNS_CASE(2) RNS_CASE(3) RNS_CASE(4) RNS_CASE(5) RNS_CASE(6)
+        RNS_CASE(7) RNS_CASE(8) RNS_CASE(9) RNS_CASE(10)
+        default:
+            return fail(RNS_ERR_UNSUPPORTED, "Garner reconstruction supports 2..10 channels");
+    }
+#undef RNS_CASE
+    RNS_CUDA_OK(cudaGetLastError());
+    return RNS_OK;
+}
+
+// ---------------------------------------------------------------------------
+// Activation quantiser
+// ---------------------------------------------------------------------------
+template <typename T> __device__ __forceinline__ float load_f(const T* p, int64_t i);
+template <> __device__ __forceinline__ float load_f<__half>(const __half* p, int64_t i) { return __half2float(p[i]); }
+template <> __device__ __forceinline__ float load_f<__nv_bfloat16>(const __nv_bfloat16* p, int64_t i) { return __bfloat162float(p[i]); }
+template <> __device__ __forceinline__ float load_f<float>(const float* p, int64_t i) { return p[i]; }
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+__device__ __forceinline__ int warp_sum(int v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// Scratch layout (16 bytes): [0] absmax bits (uint), [1] row-L1 max (int).
+// Pass 1: tensor-wide absmax by atomicMax on the float's bit pattern (order
+// preserving for non-negative floats).  The scratch word is zeroed by a
+// memset node enqueued before it.
+template <typename T>
+__global__ void __launch_bounds__(256)
+absmax_kernel(const T* __restrict__ x, int m, int k, int64_t ldx, unsigned* __restrict__ scratch) {
+    float best = 0.0f;
+    const int64_t total = (int64_t)m * k;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = i / k, c = i - r * k;
+        best = fmaxf(best, fabsf(load_f<T>(x, r * ldx + c)));
+    }
+    best = warp_max(best);
+    __shared__ float part[8];
+    if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = best;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        float v = threadIdx.x < 8 ? part[threadIdx.x] : 0.0f;
+        v = warp_max(v);
+        if (threadIdx.x == 0) atomicMax(scratch, __float_as_uint(v));
+    }
+}
+
+__device__ __forceinline__ int quantize_one(float v, float scale, int qmax) {
+    // torch: clamp(round(v / scale), -qmax, qmax); round = ties to even.
+    float q = rintf(__fdiv_rn(v, scale));
+    q = fminf(fmaxf(q, (float)-qmax), (float)qmax);
+    return (int)q;
+}
+
+__device__ __forceinline__ int centred_residue(int v, int m) {
+    int r = v % m;
+    const int half = m / 2;
+    if (r > half) r -= m;
+    else if (r < -half) r += m;
+    return r;
+}
+
+// Pass 2 (one block per row): scale, int8 values, optional planes, row L1.
+// PER_ROW: the block first reduces its own row's absmax.
+template <typename T, bool PER_ROW>
+__global__ void __launch_bounds__(256)
+quantize_rows_kernel(const T* __restrict__ x, int m, int k, int64_t ldx, int qmax, ModList ml,
+                     int8_t* __restrict__ q_out, int8_t* __restrict__ planes,
+                     float* __restrict__ scale_out, int* __restrict__ row_l1_max,
+                     const unsigned* __restrict__ scratch) {
+    __shared__ float part[8];
+    __shared__ int ipart[8];
+    __shared__ float s_scale;
+    for (int row = blockIdx.x; row < m; row += gridDim.x) {
+        const T* xr = x + (int64_t)row * ldx;
+        float absmax;
+        if (PER_ROW) {
+            float best = 0.0f;
+            for (int c = threadIdx.x; c < k; c += blockDim.x) best = fmaxf(best, fabsf(load_f<T>(xr, c)));
+            best = warp_max(best);
+            if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = best;
+            __syncthreads();
+            if (threadIdx.x < 32) {
+                float v = threadIdx.x < 8 ? part[threadIdx.x] : 0.0f;
+                v = warp_max(v);
+                if (threadIdx.x == 0) s_scale = v;
+            }
+            __syncthreads();
+            absmax = s_scale;
+            __syncthreads();
+        } else {
+            absmax = __uint_as_float(*scratch);
+        }
+        const float scale = fmaxf(__fdiv_rn(absmax, (float)qmax), FLT_EPSILON);
+        if (threadIdx.x == 0) {
+            if (PER_ROW) scale_out[row] = scale;
+            else if (row == 0) scale_out[0] = scale;
+        }
+        int l1 = 0;
+        for (int c = threadIdx.x; c < k; c += blockDim.x) {
+            const int q = quantize_one(load_f<T>(xr, c), scale, qmax);
+            l1 += q < 0 ? -q : q;
+            const int64_t o = (int64_t)row * k + c;
+            if (q_out) q_out[o] = (int8_t)q;
+            if (planes) {
+#pragma unroll 1
+                for (int ch = 0; ch < ml.channels; ++ch)
+                    planes[(int64_t)ch * m * k + o] = (int8_t)centred_residue(q, ml.mod[ch]);
+            }
+        }
+        if (row_l1_max) {
+            l1 = warp_sum(l1);
+            if ((threadIdx.x & 31) == 0) ipart[threadIdx.x >> 5] = l1;
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                int total = 0;
+                for (int w = 0; w < 8; ++w) total += ipart[w];
+                atomicMax(row_l1_max, total);
+            }
+            __syncthreads();
+        }
+    }
+}
+
+__global__ void __launch_bounds__(256)
+row_l1_max_kernel(const int8_t* __restrict__ a, int m, int k, int64_t lda, int* __restrict__ out) {
+    __shared__ int ipart[8];
+    for (int row = blockIdx.x; row < m; row += gridDim.x) {
+        int l1 = 0;
+        for (int c = threadIdx.x; c < k; c += blockDim.x) {
+            const int v = a[(int64_t)row * lda + c];
+            l1 += v < 0 ? -v : v;
+        }
+        l1 = warp_sum(l1);
+        if ((threadIdx.x & 31) == 0) ipart[threadIdx.x >> 5] = l1;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            int total = 0;
+            for (int w = 0; w < 8; ++w) total += ipart[w];
+            atomicMax(out, total);
+        }
+        __syncthreads();
+    }
+}
+
+struct SelectArgs {
+    int32_t channels, min_channels, max_abs_weight;
+    int64_t product[kMaxCh + 1];
+};
+
+__global__ void select_channels_kernel(const int* __restrict__ row_l1_max, SelectArgs sa,
+                                       int* __restrict__ active, long long* __restrict__ meta,
+                                       int* __restrict__ status) {
+    if (threadIdx.x != 0 || blockIdx.x != 0) return;
+    const long long bound = (long long)(*row_l1_max) * sa.max_abs_weight;
+    int chosen = 0;
+    for (int c = sa.min_channels; c <= sa.channels; ++c)
+        if (2 * bound < sa.product[c]) { chosen = c; break; }
+    if (chosen == 0) {
+        chosen = sa.channels;
+        if (status) atomicExch(status, (int)RNS_ERR_OVERFLOW);
+    }
+    *active = chosen;
+    if (meta) {
+        meta[0] = chosen;
+        meta[1] = bound;
+        meta[2] = (sa.product[chosen] - 1) / 2;
+    }
+}
+
+// Weight quantiser: one block per output channel (row of W).
+template <typename T>
+__global__ void __launch_bounds__(256)
+quantize_weight_kernel(const T* __restrict__ w, int n, int k, int64_t ldw, int qmax,
+                       int8_t* __restrict__ wq, float* __restrict__ scale_out,
+                       int* __restrict__ max_abs) {
+    __shared__ float part[8];
+    __shared__ float s_scale;
+    for (int row = blockIdx.x; row < n; row += gridDim.x) {
+        const T* wr = w + (int64_t)row * ldw;
+        float best = 0.0f;
+        for (int c = threadIdx.x; c < k; c += blockDim.x) best = fmaxf(best, fabsf(load_f<T>(wr, c)));
+        best = warp_max(best);
+        if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = best;
+        __syncthreads();
+        if (threadIdx.x < 32) {
+            float v = threadIdx.x < 8 ? part[threadIdx.x] : 0.0f;
+            v = warp_max(v);
+            if (threadIdx.x == 0) s_scale = fmaxf(__fdiv_rn(v, (float)qmax), FLT_EPSILON);
+        }
+        __syncthreads();
+        const float scale = s_scale;
+        if (threadIdx.x == 0) scale_out[row] = scale;
+        int biggest = 0;
+        for (int c = threadIdx.x; c < k; c += blockDim.x) {
+            const int q = quantize_one(load_f<T>(wr, c), scale, qmax);
+            wq[(int64_t)row * k + c] = (int8_t)q;
+            biggest = max(biggest, q < 0 ? -q : q);
+        }
+        if (max_abs) {
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) biggest = max(biggest, __shfl_xor_sync(0xffffffffu, biggest, o));
+            if ((threadIdx.x & 31) == 0) atomicMax(max_abs, biggest);
+        }
+        __syncthreads();
+    }
+}
+
+static int check_gemm_dims(const void* a, const void* b, const void* out, int m, int k, int n) {
+    if (!a || !b || !out) return fail(RNS_ERR_INVALID_ARGUMENT, "plane GEMM: NULL pointer");
+    if (m <= 0 || k <= 0 || n <= 0)
+        return fail(RNS_ERR_INVALID_ARGUMENT, "matrix dimensions must be positive");
+    return RNS_OK;
+}
+
+template <int MODE>
+static int launch_plane_gemm(const void* a, const void* b, void* out, const Plan& pl, int m, int k,
+                             int n, cudaStream_t st) {
+    if (pl.channels > 65535) return fail(RNS_ERR_INVALID_ARGUMENT, "too many residue channels");
+    dim3 grid((n + kPT - 1) / kPT, (m + kPT - 1) / kPT, pl.channels);
+    plane_gemm_kernel<MODE><<<grid, 256, 0, st>>>(a, b, out, modlist(pl), m, k, n);
+    RNS_CUDA_OK(cudaGetLastError());
+    return RNS_OK;
+}
+
+}  // namespace rns
+
+// ===========================================================================
+// C ABI
+// ===========================================================================
+using namespace rns;
+
+extern "C" {
+
+int rns_encode_canonical_i8(const int8_t* d_values, int64_t elements, const int32_t* moduli,
+                            int channels, uint8_t* d_out, rns_stream_t stream) {
+    Plan pl;
+    if (int rc = build_plan(moduli, channels, &pl)) return rc;
+    if (elements < 0 || (elements > 0 && (!d_values || !d_out)))
+        return fail(RNS_ERR_INVALID_ARGUMENT, "encode: NULL pointer or negative size");
+    if (elements == 0) return RNS_OK;
+    encode_canonical_kernel<<<grid_for(elements, 256), 256, 0, as_stream(stream)>>>(
+        d_values, d_out, modlist(pl), elements);
+    RNS_CUDA_OK(cudaGetLastError());
+    return RNS_OK;
+}
+
+int rns_encode_centered(const void* d_values, rns_int_type type, int64_t elements,
+                        const int32_t* moduli, int channels, int8_t* d_out, rns_stream_t stream) {
+    Plan pl;
+    if (int rc = build_plan(moduli, channels, &pl)) return rc;
+    if (elements < 0 || (elements > 0 && (!d_values || !d_out)))
+        return fail(RNS_ERR_INVALID_ARGUMENT, "encode: NULL pointer or negative size");
+    if (elements == 0) return RNS_OK;
+    const int blocks = grid_for(elements, 256);
+    cudaStream_t st = as_stream(stream);
+    const ModList ml = modlist(pl);
+    switch (type) {
+        case RNS_INT8:
+            encode_centered_kernel<int8_t><<<blocks, 256, 0, st>>>(
+                static_cast<const int8_t*>(d_values), d_out, ml, elements);
+            break;
+        case RNS_INT16:
+            encode_centered_kernel<int16_t><<<blocks, 256, 0, st>>>(
+                static_cast<const int16_t*>(d_values), d_out, ml, elements);
+            break;
+        case RNS_INT32:
+            encode_centered_kernel<int32_t><<<blocks, 256, 0, st>>>(
+                static_cast<const int32_t*>(d_values), d_out, ml, elements);
+            break;
+        default:
+            return fail(RNS_ERR_INVALID_ARGUMENT, "centered encoder supports int8, int16 and int32");
+    }
+    RNS_CUDA_OK(cudaGetLastError());
+    return RNS_OK;
+}
+
+int rns_matmul_canonical_planes(const uint8_t* d_a, const uint8_t* d_b, const int32_t* moduli,
+                                int channels, int m, int k, int n, int kernel_id, uint8_t* d_out,
+                                rns_stream_t stream) {
+    Plan pl;
+    if (int rc = build_plan(moduli, channels, &pl)) return rc;
+    if (int rc = check_gemm_dims(d_a, d_b, d_out, m, k, n)) return rc;
+    if (kernel_id < 0 || kernel_id > 2)
+        return fail(RNS_ERR_INVALID_ARGUMENT, "kernel_id must be 0, 1 or 2");
+    return launch_plane_gemm<0>(d_a, d_b, d_out, pl, m, k, n, as_stream(stream));
+}
+
+int rns_matmul_centered_planes(const int8_t* d_a, const int8_t* d_b, const int32_t* moduli,
+                               int channels, int m, int k, int n, int kernel_id, int8_t* d_out,
+                               rns_stream_t stream) {
+    Plan pl;
+    if (int rc = build_plan(moduli, channels, &pl)) return rc;
+    if (int rc = check_gemm_dims(d_a, d_b, d_out, m, k, n)) return rc;
+    if (kernel_id < 0 || kernel_id > 3)
+        return fail(RNS_ERR_INVALID_ARGUMENT,
+                    "centered kernel_id must be scalar=0, dp4a=1, dp4a_safe=2 or cublas=3");
+    if (kernel_id == 3 && (k % 4 != 0 || n % 4 != 0))
+        return fail(RNS_ERR_INVALID_ARGUMENT,
+                    "cuBLAS int8 path requires K and N to be multiples of 4");
+    return launch_plane_gemm<1>(d_a, d_b, d_out, pl, m, k, n, as_stream(stream));
+}
+
+int rns_decode_garner(const int8_t* d_residues, int64_t elements, const int32_t* moduli,
+                      int channels, int64_t* d_out, rns_stream_t stream) {
+    Plan pl;
+    if (int rc = build_plan(moduli, channels, &pl)) return rc;
+    if (elements < 0 || (elements > 0 && (!d_residues || !d_out)))
+        return fail(RNS_ERR_INVALID_ARGUMENT, "decode: NULL pointer or negative size");
+    if (elements == 0) return RNS_OK;
+    return launch_garner<int8_t>(d_residues, d_out, pl, elements, as_stream(stream));
+}
+
+int rns_matmul_centered_fused_out(const int8_t* d_a, const int8_t* d_b, const int32_t* moduli,
+                                  int channels, int m, int k, int n, int lut_channels,
+                                  int32_t* d_accumulators, int64_t* d_out, rns_stream_t stream) {
+    Plan pl;
+    if (int rc = build_plan(moduli, channels, &pl)) return rc;
+    if (int rc = check_gemm_dims(d_a, d_b, d_out, m, k, n)) return rc;
+    if (!d_accumulators) return fail(RNS_ERR_INVALID_ARGUMENT, "accumulator workspace is NULL");
+    if (k % 4 != 0 || n % 4 != 0)
+        return fail(RNS_ERR_INVALID_ARGUMENT, "fused path requires K and N multiples of 4");
+    if (channels < 2 || channels > 10)
+        return fail(RNS_ERR_UNSUPPORTED, "fused Garner path supports 2..10 channels");
+    if (lut_channels < 0 || lut_channels > 2 || lut_channels > channels)
+        return fail(RNS_ERR_INVALID_ARGUMENT,
+                    "lut_channels must be 0, 1 or 2 and <= channel count");
+    cudaStream_t st = as_stream(stream);
+    if (int rc = launch_plane_gemm<2>(d_a, d_b, d_accumulators, pl, m, k, n, st)) return rc;
+    return launch_garner<int32_t>(d_accumulators, d_out, pl, (int64_t)m * n, st);
+}
+
+int rns_quantize_activations(const void* d_x, rns_float_type type, int m, int k, int64_t ldx,
+                             int per_row, int quant_max, const int32_t* moduli, int channels,
+                             int8_t* d_q, int8_t* d_planes, float* d_scale,
+                             int32_t* d_row_l1_max, void* d_scratch, rns_stream_t stream) {
+    if (!d_x || !d_scale || (!d_q && !d_planes))
+        return fail(RNS_ERR_INVALID_ARGUMENT, "quantize: NULL pointer");
+    if (m <= 0 || k <= 0 || ldx < k)
+        return fail(RNS_ERR_INVALID_ARGUMENT, "quantize: bad shape or stride");
+    if (quant_max != 127)
+        return fail(RNS_ERR_UNSUPPORTED, "the fused quantiser produces 8-bit values (quant_max 127)");
+    if (!per_row && !d_scratch)
+        return fail(RNS_ERR_INVALID_ARGUMENT, "quantize: per-tensor scale needs d_scratch");
+    ModList ml{};
+    if (d_planes) {
+        Plan pl;
+        if (int rc = build_plan(moduli, channels, &pl)) return rc;
+        ml = modlist(pl);
+    }
+    cudaStream_t st = as_stream(stream);
+    unsigned* scratch = static_cast<unsigned*>(d_scratch);
+    if (!per_row) RNS_CUDA_OK(cudaMemsetAsync(scratch, 0, 16, st));
+    if (d_row_l1_max) RNS_CUDA_OK(cudaMemsetAsync(d_row_l1_max, 0, sizeof(int32_t), st));
+    const int rows_grid = m < 148 * 8 ? m : 148 * 8;
+#define RNS_QUANT(T)                                                                           \
+    do {                                                                                       \
+        const T* x = static_cast<const T*>(d_x);                                               \
+        if (per_row) {                                                                         \
+            quantize_rows_kernel<T, true><<<rows_grid, 256, 0, st>>>(                          \
+                x, m, k, ldx, quant_max, ml, d_q, d_planes, d_scale, d_row_l1_max, scratch);   \
+        } else {                                                                               \
+            absmax_kernel<T><<<grid_for((int64_t)m * k, 256 * 8, 148 * 4), 256, 0, st>>>(      \
+                x, m, k, ldx, scratch);                                                        \
+            quantize_rows_kernel<T, false><<<rows_grid, 256, 0, st>>>(                         \
+                x, m, k, ldx, quant_max, ml, d_q, d_planes, d_scale, d_row_l1_max, scratch);   \
+        }                                                                                      \
+    } while (0)
+    switch (type) {
+        case RNS_F16: RNS_QUANT(__half); break;
+        case RNS_BF16: RNS_QUANT(__nv_bfloat16); break;
+        case RNS_F32: RNS_QUANT(float); break;
+        default: return fail(RNS_ERR_INVALID_ARGUMENT, "quantize: unknown float type");
+    }
+#undef RNS_QUANT
+    RNS_CUDA_OK(cudaGetLastError());
+    return RNS_OK;
+}
+
+int rns_row_l1_max_i8(const int8_t* d_a, int m, int k, int64_t lda, int32_t* d_row_l1_max,
+                      rns_stream_t stream) {
+    if (!d_a || !d_row_l1_max) return fail(RNS_ERR_INVALID_ARGUMENT, "row_l1_max: NULL pointer");
+    if (m <= 0 || k <= 0 || lda < k)
+        return fail(RNS_ERR_INVALID_ARGUMENT, "row_l1_max: bad shape or stride");
+    cudaStream_t st = as_stream(stream);
+    RNS_CUDA_OK(cudaMemsetAsync(d_row_l1_max, 0, sizeof(int32_t), st));
+    row_l1_max_kernel<<<m < 148 * 8 ? m : 148 * 8, 256, 0, st>>>(d_a, m, k, lda, d_row_l1_max);
+    RNS_CUDA_OK(cudaGetLastError());
+    return RNS_OK;
+}
+
+int rns_select_channels(const int32_t* d_row_l1_max, int32_t max_abs_weight, const int32_t* moduli,
+                        int channels, int min_channels, int32_t* d_active_channels,
+                        int64_t* d_meta, int32_t* d_status, rns_stream_t stream) {
+    Plan pl;
+    if (int rc = build_plan(moduli, channels, &pl)) return rc;
+    if (!d_row_l1_max || !d_active_channels)
+        return fail(RNS_ERR_INVALID_ARGUMENT, "select_channels: NULL pointer");
+    if (min_channels < 2 || min_channels > channels)
+        return fail(RNS_ERR_INVALID_ARGUMENT, "min_channels must be between 2 and len(moduli)");
+    if (max_abs_weight < 0)
+        return fail(RNS_ERR_INVALID_ARGUMENT, "bounds must be non-negative");
+    SelectArgs sa;
+    sa.channels = channels;
+    sa.min_channels = min_channels;
+    sa.max_abs_weight = max_abs_weight;
+    for (int i = 0; i <= kMaxCh; ++i) sa.product[i] = pl.product[i];
+    select_channels_kernel<<<1, 32, 0, as_stream(stream)>>>(
+        d_row_l1_max, sa, d_active_channels, reinterpret_cast<long long*>(d_meta), d_status);
+    RNS_CUDA_OK(cudaGetLastError());
+    return RNS_OK;
+}
+
+int rns_quantize_weight(const void* d_w, rns_float_type type, int n, int k, int64_t ldw,
+                        int quant_max, int8_t* d_wq, float* d_scale, int32_t* d_max_abs,
+                        rns_stream_t stream) {
+    if (!d_w || !d_wq || !d_scale) return fail(RNS_ERR_INVALID_ARGUMENT, "quantize_weight: NULL pointer");
+    if (n <= 0 || k <= 0 || ldw < k)
+        return fail(RNS_ERR_INVALID_ARGUMENT, "quantize_weight: bad shape or stride");
+    if (quant_max < 1 || quant_max > 127)
+        return fail(RNS_ERR_UNSUPPORTED, "weights are quantised to at most 8 bits");
+    cudaStream_t st = as_stream(stream);
+    if (d_max_abs) RNS_CUDA_OK(cudaMemsetAsync(d_max_abs, 0, sizeof(int32_t), st));
+    const int grid = n < 148 * 8 ? n : 148 * 8;
+    switch (type) {
+        case RNS_F16:
+            quantize_weight_kernel<__half><<<grid, 256, 0, st>>>(
+                static_cast<const __half*>(d_w), n, k, ldw, quant_max, d_wq, d_scale, d_max_abs);
+            break;
+        case RNS_BF16:
+            quantize_weight_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(
+                static_cast<const __nv_bfloat16*>(d_w), n, k, ldw, quant_max, d_wq, d_scale, d_max_abs);
+            break;
+        case RNS_F32:
+            quantize_weight_kernel<float><<<grid, 256, 0, st>>>(
+                static_cast<const float*>(d_w), n, k, ldw, quant_max, d_wq, d_scale, d_max_abs);
+            break;
+        default:
+            return fail(RNS_ERR_INVALID_ARGUMENT, "quantize_weight: unknown float type");
+    }
+    RNS_CUDA_OK(cudaGetLastError());
+    return RNS_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,216 @@
+// Shared host/device definitions of librns_b200: error plumbing, the host-side
+// number theory that turns a modulus list into kernel constants, and the
+// per-element reconstruction arithmetic used by every epilogue.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cstdint>
+#include <cstdio>
+#include <cstdarg>
+#include <cstring>
+
+#include "../../include/rns_b200.h"
+
+namespace rns {
+
+// ---------------------------------------------------------------------------
+// Errors
+// ---------------------------------------------------------------------------
+void set_error(const char* fmt, ...);
+int fail(int code, const char* fmt, ...);
+
+#define RNS_CUDA_OK(expr)                                                        \
+    do {                                                                         \
+        cudaError_t err__ = (expr);                                              \
+        if (err__ != cudaSuccess)                                                \
+            return ::rns::fail(RNS_ERR_CUDA, "%s failed: %s", #expr,             \
+                               cudaGetErrorString(err__));                       \
+    } while (0)
+
+// ---------------------------------------------------------------------------
+// Constants of one modulus set, as kernels consume them (passed by value in
+// kernel parameters, so every access with a compile-time index is a constant
+// bank operand).
+// ---------------------------------------------------------------------------
+constexpr int kMaxCh = RNS_MAX_CHANNELS;
+
+struct Plan {
+    int32_t channels;
+    int32_t mod[kMaxCh];
+    // floor(2^32/m) clipped to INT32_MAX: q = mulhi(v, recip) is within one of
+    // floor(v/m) for any int32 v, so v - q*m lies in [-m, 2m).
+    int32_t recip[kMaxCh];
+    float modf[kMaxCh];
+    float rcpf[kMaxCh];            // 1.0f / m
+    // Flattened Garner: digit_i = centred( r_i*gscale[i] + sum_{j<i} gneg[i][j]*digit_j  mod m_i )
+    // with gscale[i] = (m_0..m_{i-1})^-1 mod m_i and gneg[i][j] = -(m_0..m_{j-1}) * gscale[i]
+    // mod m_i, both stored as centred representatives.  Every partial sum stays
+    // below 2^24 in magnitude (|r| < 2m, |digit| <= m/2, m <= 255, <= 10 terms),
+    // so fp32 evaluates it exactly.
+    float gscale[kMaxCh];
+    float gneg[kMaxCh][kMaxCh];
+    // Place values prod_{t<i} m_t.  The first four always fit 32 bits together
+    // with the centred partial sum they build (255^4/2 < 2^31).
+    uint32_t place32[4];
+    int64_t place64[kMaxCh];
+    int64_t product[kMaxCh + 1];   // product[c] = m_0*...*m_{c-1}; product[0] = 1
+    // SWAR encoder constants (valid when encode_single_fold): bytes of
+    // enc_hi = 127 - floor(m/2), enc_lo = floor(m/2), replicated four times.
+    uint32_t enc_hi[kMaxCh];
+    uint32_t enc_lo[kMaxCh];
+    int32_t encode_single_fold;    // every modulus >= 86
+};
+
+// Builds the plan; returns an rns_status.  Pure host arithmetic.
+int build_plan(const int32_t* moduli, int channels, Plan* out);
+
+// ---------------------------------------------------------------------------
+// Device arithmetic shared by the epilogues
+// ---------------------------------------------------------------------------
+#ifdef __CUDACC__
+#define RNS_HD __host__ __device__ __forceinline__
+#else
+#define RNS_HD inline
+#endif
+
+// The arithmetic below compiles for the host as well, so that CPU tests can run
+// the exact expressions the kernels evaluate.
+constexpr float kMagic = 12582912.0f;          // 1.5 * 2^23
+constexpr int kMagicBits = 0x4B400000;
+
+RNS_HD float bits_to_float(int v) {
+#ifdef __CUDA_ARCH__
+    return __int_as_float(v);
+#else
+    float f; memcpy(&f, &v, 4); return f;
+#endif
+}
+RNS_HD int float_to_bits(float f) {
+#ifdef __CUDA_ARCH__
+    return __float_as_int(f);
+#else
+    int v; memcpy(&v, &f, 4); return v;
+#endif
+}
+RNS_HD float fma_rn(float a, float b, float c) {
+#ifdef __CUDA_ARCH__
+    return __fmaf_rn(a, b, c);
+#else
+    return __builtin_fmaf(a, b, c);
+#endif
+}
+RNS_HD float mul_rn(float a, float b) {
+#ifdef __CUDA_ARCH__
+    return __fmul_rn(a, b);
+#else
+    volatile float r = a * b; return r;
+#endif
+}
+RNS_HD float add_rn(float a, float b) {
+#ifdef __CUDA_ARCH__
+    return __fadd_rn(a, b);
+#else
+    volatile float r = a + b; return r;
+#endif
+}
+RNS_HD int mul_hi(int a, int b) {
+#ifdef __CUDA_ARCH__
+    return __mulhi(a, b);
+#else
+    return (int)(((long long)a * (long long)b) >> 32);
+#endif
+}
+
+// Exact int -> float for |v| < 2^22 without the conversion unit.
+RNS_HD float small_int_to_float(int v) { return add_rn(bits_to_float(v + kMagicBits), -kMagic); }
+// Exact float (integral, |v| < 2^22) -> int.
+RNS_HD int small_float_to_int(float v) { return float_to_bits(add_rn(v, kMagic)) - kMagicBits; }
+
+// Loose residue of an int32 accumulator: congruent to v mod m, in [-m, 2m).
+RNS_HD int loose_residue(int v, int m, int recip) { return v - mul_hi(v, recip) * m; }
+
+// t -> representative of t mod m with |result| <= m/2 (t integral, |t| < 2^22).
+RNS_HD float centre_mod(float t, float m, float rcp) {
+    const float q = add_rn(fma_rn(t, rcp, kMagic), -kMagic);
+    return fma_rn(-q, m, t);
+}
+
+// Centred digits of the mixed-radix form of the value whose channel sums are acc[].
+template <int R>
+RNS_HD void garner_digits(const int (&acc)[R], const Plan& pl, int active, float (&digit)[R]) {
+#pragma unroll
+    for (int i = 0; i < R; ++i) {
+        digit[i] = 0.0f;
+        if (i < active) {
+            const float r = small_int_to_float(loose_residue(acc[i], pl.mod[i], pl.recip[i]));
+            float t = (i == 0) ? r : mul_rn(r, pl.gscale[i]);
+#pragma unroll
+            for (int j = 0; j < i; ++j) t = fma_rn(pl.gneg[i][j], digit[j], t);
+            digit[i] = centre_mod(t, pl.modf[i], pl.rcpf[i]);
+        }
+    }
+}
+
+// Mixed-radix reconstruction of one output element from R int32 channel sums.
+// Follows csrc/rns_cuda.cu:380-414 of the reference (digits, place-value sum,
+// "if x > P/2: x -= P") but with centred digits, so the sum is already signed;
+// the final range fix-up reproduces the reference's representative (-P/2, P/2]
+// in every case, including even P and inputs beyond the capacity.
+// Returns the value as int64; `active` (<= R) is the number of channels in use.
+template <int R>
+RNS_HD long long reconstruct(const int (&acc)[R], const Plan& pl, int active) {
+    float digit[R];
+    garner_digits<R>(acc, pl, active, digit);
+    int lo = 0;
+#pragma unroll
+    for (int i = 0; i < (R < 4 ? R : 4); ++i)
+        if (i < active) lo += (int)pl.place32[i] * small_float_to_int(digit[i]);
+    long long x = lo;
+    if (R > 4) {
+#pragma unroll
+        for (int i = 4; i < R; ++i)
+            if (i < active) x += pl.place64[i] * (long long)small_float_to_int(digit[i]);
+    }
+    const long long prod = pl.product[active];
+    const long long half = prod >> 1;
+    if (x > half) x -= prod;
+    else if (x < half - prod + 1) x += prod;
+    return x;
+}
+
+// Same, for R <= 4 where everything fits 32 bits (P < 2^32, |x| <= P/2 < 2^31).
+template <int R>
+RNS_HD int reconstruct32(const int (&acc)[R], const Plan& pl, int active) {
+    static_assert(R <= 4, "32-bit reconstruction covers at most four channels");
+    float digit[R];
+    garner_digits<R>(acc, pl, active, digit);
+    unsigned x = 0;
+#pragma unroll
+    for (int i = 0; i < R; ++i)
+        if (i < active) x += pl.place32[i] * (unsigned)small_float_to_int(digit[i]);
+    const unsigned prod = (unsigned)pl.product[active];
+    const int half = (int)(prod >> 1);
+    const int low = (int)((unsigned)half - prod + 1u);
+    int sx = (int)x;
+    if (sx > half) sx = (int)(x - prod);
+    else if (sx < low) sx = (int)(x + prod);
+    return sx;
+}
+
+// Centred residues of four packed int8 values for one modulus (single fold;
+// requires m >= 86).  u = bytes biased by 128, ul = u with the top bit of each
+// byte cleared, hi/lo = Plan::enc_hi/enc_lo.  Bit 7 of (ul + hi) & u is set
+// where x > floor(m/2); bit 7 of ~((ul + lo) | u) where x < -floor(m/2).  The
+// biased result never leaves [0,255] per byte, so one 32-bit multiply-add
+// applies all four folds.  -m/2 of an even modulus is kept negative, as the
+// reference's device encoder does (csrc/rns_cuda.cu:116-122).
+RNS_HD uint32_t encode_word(uint32_t u, uint32_t ul, uint32_t hi, uint32_t lo, uint32_t m) {
+    const uint32_t down = (ul + hi) & u & 0x80808080u;
+    const uint32_t up = ~((ul + lo) | u) & 0x80808080u;
+    const uint32_t delta = (up >> 7) - (down >> 7);
+    return (u + delta * m) ^ 0x80808080u;
+}
+
+
+
+}  // namespace rns

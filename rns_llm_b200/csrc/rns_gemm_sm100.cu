@@ -1,0 +1,662 @@
+// Fused RNS linear for sm_100a: TMA -> in-kernel residue encoding -> one
+// tcgen05.mma.kind::i8 per residue channel (int32 accumulators in TMEM) ->
+// epilogue with modular reduction, mixed-radix reconstruction, recentring and
+// dequantisation.  One CTA computes one 128 x tile_n output tile.
+//
+// Warp roles (320 threads):
+//   warp 0      TMA producer (one elected lane)
+//   warp 1      TMEM owner + MMA issuer (one elected lane)
+//   warps 2..9  encoders during the K loop, epilogue afterwards
+//
+// Per pipeline stage the shared memory holds
+//   raw  : source bytes as TMA delivers them (W tile, and the A tile when the
+//          activations come as source integers), hardware-swizzled;
+//   enc  : `channels` operand tiles for A and for W in the canonical K-major
+//          swizzled layout the MMA reads.
+// Residue encoding is elementwise, so an encoder thread reads 16 bytes at some
+// offset of a raw tile and writes 16 bytes at the SAME offset of each channel's
+// operand tile: the swizzle TMA applied is exactly the one the MMA expects.
+//
+// Every wait on an mbarrier is bounded in time; when one expires the CTA
+// records RNS_ERR_DEVICE_TIMEOUT in the caller's status word, skips the
+// remaining work, frees its tensor memory and returns.
+#include "rns_common.cuh"
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include <atomic>
+#include <mutex>
+#include <type_traits>
+
+namespace rns {
+
+constexpr int kTileM = 128;
+constexpr int kThreads = 320;
+constexpr int kWorkerWarps = 8;
+constexpr int kWorkerThreads = kWorkerWarps * 32;
+constexpr int kMaxStages = 6;
+constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s
+
+struct GemmParams {
+    Plan plan;
+    int32_t m, n, k;
+    int32_t tile_n, tile_k;      // tile_k in {64,128}
+    int32_t stages;
+    int32_t a_is_planes;
+    int32_t tmem_cols;
+    const int32_t* active_ptr;
+    void* out;
+    int64_t ldo;
+    int32_t out_type;
+    const float* row_scale;
+    int32_t row_scale_stride;
+    const float* col_scale;
+    const float* bias;
+    int32_t* status;
+    // shared-memory map (byte offsets from the 1024-aligned base)
+    uint32_t stage_bytes, off_raw_a, off_raw_w, off_enc_a, off_enc_w;
+    uint32_t tile_a_bytes, tile_w_bytes;
+};
+
+// ---------------------------------------------------------------------------
+// PTX wrappers
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_addr(const void* p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ uint64_t global_timer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ void fence_proxy_async_smem() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
+                                            int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
+        : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
+                                            int x, int y, int z) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "r"(z)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t holder_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(holder_smem),
+                 "r"(cols)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols)
+                 : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void umma_i8(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc,
+                                        uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, int (&v)[8]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
+          "=r"(v[7])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() {
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// K-major operand tile with 64- or 128-byte swizzle: rows of tile_k bytes,
+// groups of 8 rows 8*tile_k bytes apart.  Fields as in the sm_100 matrix
+// descriptor: start>>4 [0,14), leading offset [16,30) (unused for swizzled
+// K-major, set to 1), stride offset>>4 [32,46), version=1 [46,48), swizzle
+// mode [61,64) (2 = 128B, 4 = 64B).
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, uint32_t tile_k) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)((8u * tile_k) >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)(tile_k == 128 ? 2 : 4) << 61;
+    return d;
+}
+// Instruction descriptor: S32 accumulate [4,6)=2, signed 8-bit A [7,10)=1 and
+// B [10,13)=1, both K-major, N>>3 at [17,23), M>>4 at [24,29).
+__device__ __forceinline__ uint32_t make_idesc(uint32_t n) {
+    return (2u << 4) | (1u << 7) | (1u << 10) | ((n >> 3) << 17) | ((uint32_t)(kTileM >> 4) << 24);
+}
+
+// Waits for `parity` of `bar`; false (and *abort set) when the time limit passes
+// or another thread of the CTA already gave up.
+__device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity, volatile int* abort) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = global_timer_ns();
+    for (uint32_t spin = 1;; ++spin) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((spin & 255u) == 0) {
+            if (*abort) return false;
+            if (global_timer_ns() - t0 > kWaitLimitNs) {
+                *abort = 1;
+                return false;
+            }
+        }
+    }
+}
+
+struct __align__(8) SharedCtl {
+    uint64_t full_raw[kMaxStages];
+    uint64_t empty_raw[kMaxStages];
+    uint64_t full_enc[kMaxStages];
+    uint64_t empty_enc[kMaxStages];
+    uint64_t acc_full;
+    uint32_t tmem_base;
+    int abort;
+};
+
+template <int R>
+__global__ void __launch_bounds__(kThreads, 1)
+rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                const __grid_constant__ GemmParams p) {
+    extern __shared__ uint8_t smem_dyn[];
+    __shared__ SharedCtl ctl;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t tiles_base = (smem_addr(smem_dyn) + 1023u) & ~1023u;
+    uint8_t* tiles_ptr = smem_dyn + (tiles_base - smem_addr(smem_dyn));
+
+    const int n0 = blockIdx.x * p.tile_n;
+    const int m0 = blockIdx.y * kTileM;
+    const int kblocks = (p.k + p.tile_k - 1) / p.tile_k;
+    const int stages = p.stages;
+    const bool a_planes = p.a_is_planes != 0;
+
+    int active = R;
+    if (p.active_ptr != nullptr) {
+        active = *p.active_ptr;
+        active = active < 1 ? 1 : (active > R ? R : active);
+    }
+
+    if (threadIdx.x == 0) {
+        ctl.abort = 0;
+        for (int s = 0; s < stages; ++s) {
+            mbar_init(smem_addr(&ctl.full_raw[s]), 1);
+            mbar_init(smem_addr(&ctl.empty_raw[s]), kWorkerThreads);
+            mbar_init(smem_addr(&ctl.full_enc[s]), kWorkerThreads + (a_planes ? 1 : 0));
+            mbar_init(smem_addr(&ctl.empty_enc[s]), 1);
+        }
+        mbar_init(smem_addr(&ctl.acc_full), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_addr(&ctl.tmem_base), (uint32_t)p.tmem_cols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = ctl.tmem_base;
+    volatile int* abort = &ctl.abort;
+
+    if (warp == 0) {
+        // ------------------------------ TMA producer ------------------------------
+        if (lane == 0) {
+            const uint32_t raw_bytes = p.tile_w_bytes + (a_planes ? 0u : p.tile_a_bytes);
+            for (int kb = 0; kb < kblocks; ++kb) {
+                const int s = kb % stages;
+                const uint32_t round = (uint32_t)(kb / stages);
+                const uint32_t stage = tiles_base + (uint32_t)s * p.stage_bytes;
+                // A slot is free once its previous round has been consumed;
+                // the first round needs no wait.
+                if (round > 0 && !wait_bounded(smem_addr(&ctl.empty_raw[s]), (round - 1) & 1, abort)) break;
+                const uint32_t fr = smem_addr(&ctl.full_raw[s]);
+                mbar_arrive_expect_tx(fr, raw_bytes);
+                tma_load_2d(stage + p.off_raw_w, &map_w, fr, kb * p.tile_k, n0);
+                if (!a_planes) {
+                    tma_load_2d(stage + p.off_raw_a, &map_a, fr, kb * p.tile_k, m0);
+                } else {
+                    if (round > 0 && !wait_bounded(smem_addr(&ctl.empty_enc[s]), (round - 1) & 1, abort)) break;
+                    const uint32_t fe = smem_addr(&ctl.full_enc[s]);
+                    mbar_arrive_expect_tx(fe, (uint32_t)active * p.tile_a_bytes);
+                    for (int c = 0; c < active; ++c)
+                        tma_load_3d(stage + p.off_enc_a + (uint32_t)c * p.tile_a_bytes, &map_a, fe,
+                                    kb * p.tile_k, m0, c);
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ------------------------------ MMA issuer --------------------------------
+        if (lane == 0) {
+            const uint32_t idesc = make_idesc((uint32_t)p.tile_n);
+            bool ok = true;
+            for (int kb = 0; kb < kblocks && ok; ++kb) {
+                const int s = kb % stages;
+                const uint32_t round = (uint32_t)(kb / stages);
+                const uint32_t stage = tiles_base + (uint32_t)s * p.stage_bytes;
+                ok = wait_bounded(smem_addr(&ctl.full_enc[s]), round & 1, abort);
+                if (!ok) break;
+                tc_fence_after();
+                for (int c = 0; c < active; ++c) {
+                    const uint32_t a_tile = stage + p.off_enc_a + (uint32_t)c * p.tile_a_bytes;
+                    const uint32_t w_tile = stage + p.off_enc_w + (uint32_t)c * p.tile_w_bytes;
+                    const uint32_t d = tmem_base + (uint32_t)(c * p.tile_n);
+                    for (int ks = 0; ks < p.tile_k / 32; ++ks) {
+                        umma_i8(d, make_smem_desc(a_tile + ks * 32, p.tile_k),
+                                make_smem_desc(w_tile + ks * 32, p.tile_k), idesc,
+                                (kb > 0 || ks > 0) ? 1u : 0u);
+                    }
+                }
+                umma_commit(smem_addr(&ctl.empty_enc[s]));
+            }
+            if (ok) umma_commit(smem_addr(&ctl.acc_full));
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------ encoders ----------------------------------
+        const int wt = threadIdx.x - 64;  // 0..255
+        const int rows_a = min(kTileM, p.m - m0);
+        const int rows_w = min(p.tile_n, p.n - n0);
+        // 16-byte chunks that hold valid rows (row r occupies bytes [r*tile_k, (r+1)*tile_k)
+        // of a tile in every swizzle mode).
+        const int chunks_a = a_planes ? 0 : rows_a * (p.tile_k / 16);
+        const int chunks_w = rows_w * (p.tile_k / 16);
+        bool ok = true;
+        for (int kb = 0; kb < kblocks && ok; ++kb) {
+            const int s = kb % stages;
+            const uint32_t round = (uint32_t)(kb / stages);
+            uint8_t* stage = tiles_ptr + (size_t)s * p.stage_bytes;
+            ok = wait_bounded(smem_addr(&ctl.full_raw[s]), round & 1, abort);
+            if (ok && round > 0) ok = wait_bounded(smem_addr(&ctl.empty_enc[s]), (round - 1) & 1, abort);
+            if (!ok) break;
+            for (int part = 0; part < 2; ++part) {
+                const int chunks = part == 0 ? chunks_w : chunks_a;
+                const uint8_t* raw = stage + (part == 0 ? p.off_raw_w : p.off_raw_a);
+                uint8_t* enc = stage + (part == 0 ? p.off_enc_w : p.off_enc_a);
+                const uint32_t tile_bytes = part == 0 ? p.tile_w_bytes : p.tile_a_bytes;
+                for (int ch = wt; ch < chunks; ch += kWorkerThreads) {
+                    const uint4 x = *reinterpret_cast<const uint4*>(raw + ch * 16);
+                    const uint32_t u0 = x.x ^ 0x80808080u, u1 = x.y ^ 0x80808080u;
+                    const uint32_t u2 = x.z ^ 0x80808080u, u3 = x.w ^ 0x80808080u;
+                    const uint32_t l0 = u0 & 0x7f7f7f7fu, l1 = u1 & 0x7f7f7f7fu;
+                    const uint32_t l2 = u2 & 0x7f7f7f7fu, l3 = u3 & 0x7f7f7f7fu;
+#pragma unroll
+                    for (int c = 0; c < R; ++c) {
+                        if (c < active) {
+                            const uint32_t hi = p.plan.enc_hi[c], lo = p.plan.enc_lo[c];
+                            const uint32_t m = (uint32_t)p.plan.mod[c];
+                            uint4 y;
+                            y.x = encode_word(u0, l0, hi, lo, m);
+                            y.y = encode_word(u1, l1, hi, lo, m);
+                            y.z = encode_word(u2, l2, hi, lo, m);
+                            y.w = encode_word(u3, l3, hi, lo, m);
+                            *reinterpret_cast<uint4*>(enc + (size_t)c * tile_bytes + ch * 16) = y;
+                        }
+                    }
+                }
+            }
+            fence_proxy_async_smem();
+            mbar_arrive(smem_addr(&ctl.full_enc[s]));
+            mbar_arrive(smem_addr(&ctl.empty_raw[s]));
+        }
+
+        // ------------------------------ epilogue ----------------------------------
+        if (ok) ok = wait_bounded(smem_addr(&ctl.acc_full), 0, abort);
+        if (ok) {
+            tc_fence_after();
+            const int quarter = warp & 3;             // TMEM lanes 32*quarter .. +31
+            const int half_id = (warp - 2) >> 2;      // which half of the tile's columns
+            const int row = m0 + quarter * 32 + lane;
+            const int cols_per_half = p.tile_n / 2;   // tile_n is a multiple of 16
+            const int col_begin = half_id * cols_per_half;
+            const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
+            float rs = 0.0f;
+            const bool is_float = p.out_type >= RNS_OUT_F16;
+            if (is_float && row < p.m) rs = p.row_scale[(int64_t)row * p.row_scale_stride];
+            using XInt = typename std::conditional<(R <= 4), int, long long>::type;
+            for (int cc = 0; cc < cols_per_half; cc += 8) {
+                __syncwarp();  // the tensor-memory loads below are warp-collective
+                const int col = col_begin + cc;
+                int acc[R][8];
+#pragma unroll
+                for (int c = 0; c < R; ++c) {
+                    if (c < active) {
+                        tmem_ld8(lane_base + (uint32_t)(c * p.tile_n + col), acc[c]);
+                    } else {
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) acc[c][e] = 0;
+                    }
+                }
+                tmem_ld_wait();
+                const int gcol = n0 + col;
+                if (row >= p.m || gcol >= p.n) continue;
+                XInt xs[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    int one[R];
+#pragma unroll
+                    for (int c = 0; c < R; ++c) one[c] = acc[c][e];
+                    if constexpr (R <= 4) xs[e] = reconstruct32<R>(one, p.plan, active);
+                    else xs[e] = reconstruct<R>(one, p.plan, active);
+                }
+                const int valid = min(8, p.n - gcol);
+                const int64_t o = (int64_t)row * p.ldo + gcol;
+                if (p.out_type == RNS_OUT_INT64) {
+                    long long* out = static_cast<long long*>(p.out) + o;
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) if (e < valid) out[e] = xs[e];
+                } else if (p.out_type == RNS_OUT_INT32) {
+                    int* out = static_cast<int*>(p.out) + o;
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) if (e < valid) out[e] = (int)xs[e];
+                } else {
+                    float y[8];
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) {
+                        if (e < valid) {
+                            float xf;
+                            if constexpr (R <= 4) xf = __int2float_rn(xs[e]);
+                            else xf = __ll2float_rn(xs[e]);
+                            float v = __fmul_rn(__fmul_rn(xf, rs), p.col_scale[gcol + e]);
+                            if (p.bias != nullptr) v = __fadd_rn(v, p.bias[gcol + e]);
+                            y[e] = v;
+                        } else {
+                            y[e] = 0.0f;
+                        }
+                    }
+                    if (p.out_type == RNS_OUT_F32) {
+                        float* out = static_cast<float*>(p.out) + o;
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) if (e < valid) out[e] = y[e];
+                    } else if (p.out_type == RNS_OUT_F16) {
+                        __half* out = static_cast<__half*>(p.out) + o;
+                        if (valid == 8 && ((reinterpret_cast<uintptr_t>(out) & 15) == 0)) {
+                            __half2 h[4];
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) h[e] = __floats2half2_rn(y[2 * e], y[2 * e + 1]);
+                            *reinterpret_cast<uint4*>(out) = *reinterpret_cast<const uint4*>(h);
+                        } else {
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) if (e < valid) out[e] = __float2half_rn(y[e]);
+                        }
+                    } else {
+                        __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.out) + o;
+                        if (valid == 8 && ((reinterpret_cast<uintptr_t>(out) & 15) == 0)) {
+                            __nv_bfloat162 h[4];
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) h[e] = __floats2bfloat162_rn(y[2 * e], y[2 * e + 1]);
+                            *reinterpret_cast<uint4*>(out) = *reinterpret_cast<const uint4*>(h);
+                        } else {
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) if (e < valid) out[e] = __float2bfloat16_rn(y[e]);
+                        }
+                    }
+                }
+            }
+        }
+    }
+
+    // ------------------------------ teardown ---------------------------------------
+    tc_fence_before();
+    __syncthreads();
+    if (threadIdx.x == 0 && ctl.abort && p.status != nullptr)
+        atomicExch(p.status, (int)RNS_ERR_DEVICE_TIMEOUT);
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, (uint32_t)p.tmem_cols);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(sym);
+    });
+    return fn;
+}
+
+static int make_map(CUtensorMap* map, const void* base, int rank, const uint64_t* dims,
+                    const uint64_t* strides_bytes, const uint32_t* box, int tile_k) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return fail(RNS_ERR_CUDA, "cuTensorMapEncodeTiled is unavailable in this driver");
+    cuuint64_t gdim[3];
+    cuuint64_t gstr[2];
+    cuuint32_t bx[3];
+    cuuint32_t es[3] = {1, 1, 1};
+    for (int i = 0; i < rank; ++i) { gdim[i] = dims[i]; bx[i] = box[i]; }
+    for (int i = 0; i + 1 < rank; ++i) gstr[i] = strides_bytes[i];
+    const CUresult rc = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, (cuuint32_t)rank,
+                           const_cast<void*>(base), gdim, gstr, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                           tile_k == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+                           CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (rc != CUDA_SUCCESS) return fail(RNS_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d)", (int)rc);
+    return RNS_OK;
+}
+
+constexpr int kSmemBudget = 227 * 1024 - 2048;  // dynamic bytes we allow ourselves
+
+static int round_up_pow2(int v) {
+    int r = 32;
+    while (r < v) r <<= 1;
+    return r;
+}
+
+static bool tc_supported(const Plan& pl, int k, int64_t lda, int64_t ldw, const char** why) {
+    if (pl.channels < 2 || pl.channels > RNS_TC_MAX_CHANNELS) { *why = "channel count outside 2..8"; return false; }
+    if (!pl.encode_single_fold) { *why = "a modulus below 86 needs more than one fold"; return false; }
+    if (k <= 0 || k % 16 != 0) { *why = "K must be a positive multiple of 16"; return false; }
+    if (lda % 16 != 0 || ldw % 16 != 0) { *why = "row strides must be multiples of 16 bytes"; return false; }
+    return true;
+}
+
+template <int R>
+static int launch(const CUtensorMap& ma, const CUtensorMap& mw, const GemmParams& gp, dim3 grid,
+                  size_t smem, cudaStream_t st) {
+    // The opt-in shared-memory size is a per-device function attribute: set it on
+    // the first launch of this instantiation on each device.
+    static std::atomic<uint64_t> configured{0};
+    int dev = 0;
+    RNS_CUDA_OK(cudaGetDevice(&dev));
+    const uint64_t bit = 1ull << (dev & 63);
+    if (!(configured.load(std::memory_order_acquire) & bit)) {
+        RNS_CUDA_OK(cudaFuncSetAttribute(rns_gemm_kernel<R>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         227 * 1024 - 1024));
+        configured.fetch_or(bit, std::memory_order_release);
+    }
+    rns_gemm_kernel<R><<<grid, kThreads, smem, st>>>(ma, mw, gp);
+    RNS_CUDA_OK(cudaGetLastError());
+    return RNS_OK;
+}
+
+}  // namespace rns
+
+using namespace rns;
+
+extern "C" {
+
+int rns_linear_fused_supported(const int32_t* moduli, int channels, int k, int64_t lda, int64_t ldw) {
+    Plan pl;
+    if (build_plan(moduli, channels, &pl) != RNS_OK) return 0;
+    const char* why = "";
+    return tc_supported(pl, k, lda, ldw, &why) ? 1 : 0;
+}
+
+int rns_linear_fused(const rns_linear_args* a, rns_stream_t stream) {
+    if (!a) return fail(RNS_ERR_INVALID_ARGUMENT, "args is NULL");
+    GemmParams gp;
+    memset(&gp, 0, sizeof(gp));
+    if (int rc = build_plan(a->moduli, a->channels, &gp.plan)) return rc;
+    if (a->m <= 0 || a->n <= 0 || a->k <= 0)
+        return fail(RNS_ERR_INVALID_ARGUMENT, "matrix dimensions must be positive");
+    if ((a->d_a == nullptr) == (a->d_a_planes == nullptr))
+        return fail(RNS_ERR_INVALID_ARGUMENT, "give exactly one of d_a and d_a_planes");
+    if (!a->d_w || !a->d_out) return fail(RNS_ERR_INVALID_ARGUMENT, "d_w and d_out must be non-NULL");
+    if (a->lda < a->k || a->ldw < a->k || a->ldo < a->n)
+        return fail(RNS_ERR_INVALID_ARGUMENT, "a leading dimension is smaller than its row");
+    const bool planes = a->d_a_planes != nullptr;
+    if (planes && a->a_plane_stride < (int64_t)(a->m - 1) * a->lda + a->k)
+        return fail(RNS_ERR_INVALID_ARGUMENT, "a_plane_stride is smaller than one plane");
+    if (a->out_type < RNS_OUT_INT64 || a->out_type > RNS_OUT_F32)
+        return fail(RNS_ERR_INVALID_ARGUMENT, "unknown out_type");
+    const bool is_float = a->out_type >= RNS_OUT_F16;
+    if (is_float && (!a->d_row_scale || !a->d_col_scale))
+        return fail(RNS_ERR_INVALID_ARGUMENT, "floating outputs need d_row_scale and d_col_scale");
+    if (is_float && a->row_scale_stride != 0 && a->row_scale_stride != 1)
+        return fail(RNS_ERR_INVALID_ARGUMENT, "row_scale_stride must be 0 or 1");
+    const Plan& pl = gp.plan;
+    const int R = pl.channels;
+    if (a->out_type == RNS_OUT_INT32 && (pl.product[R] >> 1) >= (1ll << 31))
+        return fail(RNS_ERR_OVERFLOW, "int32 output needs product(moduli)/2 < 2^31");
+    const char* why = "";
+    if (!tc_supported(pl, a->k, a->lda, a->ldw, &why))
+        return fail(RNS_ERR_UNSUPPORTED, "tensor-core path: %s", why);
+    if (planes && a->a_plane_stride % 16 != 0)
+        return fail(RNS_ERR_UNSUPPORTED, "tensor-core path: a_plane_stride must be a multiple of 16");
+    const void* a_base = planes ? (const void*)a->d_a_planes : (const void*)a->d_a;
+    if ((reinterpret_cast<uintptr_t>(a_base) & 15) || (reinterpret_cast<uintptr_t>(a->d_w) & 15))
+        return fail(RNS_ERR_UNSUPPORTED, "tensor-core path: operand bases must be 16-byte aligned");
+
+    // ---- tile configuration -------------------------------------------------
+    const int max_tile_n = ((512 / R) / 16) * 16 > 128 ? 128 : ((512 / R) / 16) * 16;
+    int tile_k = a->tile_k;
+    if (tile_k == 0) tile_k = 64;
+    if (tile_k != 64 && tile_k != 128) return fail(RNS_ERR_INVALID_ARGUMENT, "tile_k must be 64 or 128");
+    int tile_n = a->tile_n;
+    const int m_tiles = (a->m + kTileM - 1) / kTileM;
+    if (tile_n == 0) {
+        // Largest tile that still gives every SM a CTA; small problems take the
+        // narrowest tile so that more SMs stream the weights.
+        tile_n = 32;
+        const int cands[] = {128, 96, 64, 48, 32};
+        for (int c : cands) {
+            if (c > max_tile_n) continue;
+            if ((int64_t)m_tiles * ((a->n + c - 1) / c) >= 148) { tile_n = c; break; }
+        }
+        if (tile_n > max_tile_n) tile_n = max_tile_n;
+    }
+    if (tile_n < 16 || tile_n > 128 || tile_n % 16 != 0 || tile_n > max_tile_n)
+        return fail(RNS_ERR_INVALID_ARGUMENT, "tile_n must be a multiple of 16 in [16, %d]", max_tile_n);
+
+    gp.tile_a_bytes = kTileM * tile_k;
+    gp.tile_w_bytes = tile_n * tile_k;
+    uint32_t off = 0;
+    gp.off_raw_w = off; off += gp.tile_w_bytes;
+    gp.off_raw_a = off; if (!planes) off += gp.tile_a_bytes;
+    gp.off_enc_a = off; off += R * gp.tile_a_bytes;
+    gp.off_enc_w = off; off += R * gp.tile_w_bytes;
+    gp.stage_bytes = (off + 1023u) & ~1023u;
+    int stages = kSmemBudget / (int)gp.stage_bytes;
+    if (stages > kMaxStages) stages = kMaxStages;
+    const int kblocks = (a->k + tile_k - 1) / tile_k;
+    if (stages > kblocks) stages = kblocks;
+    if (stages < 1)
+        return fail(RNS_ERR_UNSUPPORTED, "tile configuration does not fit shared memory");
+    if (stages < 2 && kblocks > 1 && tile_k == 128)
+        return fail(RNS_ERR_UNSUPPORTED, "tile_k=128 leaves room for one stage only; use tile_k=64");
+    gp.stages = stages;
+    gp.m = a->m; gp.n = a->n; gp.k = a->k;
+    gp.tile_n = tile_n; gp.tile_k = tile_k;
+    gp.a_is_planes = planes ? 1 : 0;
+    gp.tmem_cols = round_up_pow2(R * tile_n);
+    gp.active_ptr = a->d_active_channels;
+    gp.out = a->d_out; gp.ldo = a->ldo; gp.out_type = a->out_type;
+    gp.row_scale = a->d_row_scale; gp.row_scale_stride = a->row_scale_stride;
+    gp.col_scale = a->d_col_scale; gp.bias = a->d_bias; gp.status = a->d_status;
+
+    // ---- tensor maps -------------------------------------------------------
+    CUtensorMap map_a, map_w;
+    {
+        const uint64_t dims[2] = {(uint64_t)a->k, (uint64_t)a->n};
+        const uint64_t strides[1] = {(uint64_t)a->ldw};
+        const uint32_t box[2] = {(uint32_t)tile_k, (uint32_t)tile_n};
+        if (int rc = make_map(&map_w, a->d_w, 2, dims, strides, box, tile_k)) return rc;
+    }
+    if (planes) {
+        const uint64_t dims[3] = {(uint64_t)a->k, (uint64_t)a->m, (uint64_t)R};
+        const uint64_t strides[2] = {(uint64_t)a->lda, (uint64_t)a->a_plane_stride};
+        const uint32_t box[3] = {(uint32_t)tile_k, (uint32_t)kTileM, 1u};
+        if (int rc = make_map(&map_a, a_base, 3, dims, strides, box, tile_k)) return rc;
+    } else {
+        const uint64_t dims[2] = {(uint64_t)a->k, (uint64_t)a->m};
+        const uint64_t strides[1] = {(uint64_t)a->lda};
+        const uint32_t box[2] = {(uint32_t)tile_k, (uint32_t)kTileM};
+        if (int rc = make_map(&map_a, a_base, 2, dims, strides, box, tile_k)) return rc;
+    }
+
+    const dim3 grid((a->n + tile_n - 1) / tile_n, m_tiles, 1);
+    const size_t smem = (size_t)stages * gp.stage_bytes + 1024;
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    switch (R) {
+        case 2: return launch<2>(map_a, map_w, gp, grid, smem, st);
+        case 3: return launch<3>(map_a, map_w, gp, grid, smem, st);
+        case 4: return launch<4>(map_a, map_w, gp, grid, smem, st);
+        case 5: return launch<5>(map_a, map_w, gp, grid, smem, st);
+        case 6: return launch<6>(map_a, map_w, gp, grid, smem, st);
+        case 7: return launch<7>(map_a, map_w, gp, grid, smem, st);
+        case 8: return launch<8>(map_a, map_w, gp, grid, smem, st);
+        default: return fail(RNS_ERR_UNSUPPORTED, "tensor-core path: channel count outside 2..8");
+    }
+}
+
+}  // extern "C"
