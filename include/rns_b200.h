@@ -284,12 +284,15 @@ RNS_API int rns_row_l1_max_i8(const int8_t* d_a, int m, int k, int64_t lda,
  * When even the full set is too small the reference raises OverflowError; here
  * *d_active_channels = channels and *d_status = RNS_ERR_OVERFLOW (if given).
  * d_meta, when non-NULL, receives int64 {channels, bound, capacity} for
- * last_adaptive_metadata, to be read lazily.
+ * last_adaptive_metadata, to be read lazily.  d_histogram, when non-NULL, is
+ * int64 [RNS_MAX_CHANNELS+1]; entry [c] is incremented when c channels are
+ * chosen (the adaptive_channels_{c} counters of backends/cuda_backend.py:599,
+ * kept on the device and read only when statistics are asked for).
  */
 RNS_API int rns_select_channels(const int32_t* d_row_l1_max, int32_t max_abs_weight,
                                 const int32_t* moduli, int channels, int min_channels,
                                 int32_t* d_active_channels, int64_t* d_meta,
-                                int32_t* d_status, rns_stream_t stream);
+                                int64_t* d_histogram, int32_t* d_status, rns_stream_t stream);
 
 /*
  * Weight quantiser: per-output-channel symmetric int8 of layers/rns_linear.py:

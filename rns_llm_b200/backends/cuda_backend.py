@@ -1,0 +1,903 @@
+"""CudaRNSBackend for B200: the reference's backend contract over librns_b200.so.
+
+Same public surface as ``src/rns_llm/backends/cuda_backend.py`` of the reference
+(class, dataclasses, method names, argument meaning, exception classes, stats
+keys), so code written against the reference backend runs unchanged.  What
+differs is underneath:
+
+* a prepared weight is the quantised int8 matrix in the nn.Linear layout
+  [N,K], ONE byte per value; residue planes are formed inside the GEMM kernel
+  (``PreparedRNSWeight.residues`` materialises [R,K,N] planes only when a
+  caller asks for that attribute);
+* ``matmul_prepared_fused`` is one kernel launch (encode, R tensor-core GEMMs,
+  reduction, Garner, recentring) instead of encode + cuBLAS + Garner, with no
+  int32 accumulator round trip through HBM;
+* adaptive prefix selection happens on the device: no ``.item()`` on the hot
+  path, metadata and per-channel-count statistics are read lazily;
+* temporaries come from a per-stream arena.
+
+Every computation goes through the C ABI; there is no PyTorch fallback.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from collections import Counter
+from collections.abc import Mapping
+from dataclasses import dataclass, field
+from math import prod
+from typing import Iterable, Literal, Sequence
+
+import torch
+
+from .. import _native as N
+from ..adaptive import minimal_prefix_channels, safe_l1_dot_bound
+from ..arena import StreamArena
+from ..moduli import (
+    compact_byte_mod_lut,
+    crt_constants,
+    garner_pairwise_inverses,
+    validate_moduli,
+)
+
+CanonicalKernelName = Literal["auto", "naive", "tiled", "tiled_safe"]
+CenteredKernelName = Literal["auto", "scalar", "dp4a", "dp4a_safe", "cublas", "tcgen05", "planes"]
+
+# Activations with at least this many rows are encoded to planes once by a
+# separate kernel; below it every CTA encodes its own A tile inside the GEMM.
+PLANES_MIN_ROWS = 512
+
+_INT_TYPES = {torch.int8: N.INT8, torch.int16: N.INT16, torch.int32: N.INT32}
+_FLOAT_TYPES = {torch.float16: N.F16, torch.bfloat16: N.BF16, torch.float32: N.F32}
+_OUT_TYPES = {torch.int64: N.OUT_INT64, torch.int32: N.OUT_INT32, torch.float16: N.OUT_F16,
+              torch.bfloat16: N.OUT_BF16, torch.float32: N.OUT_F32}
+
+
+def cuda_extension_available() -> bool:
+    """True when librns_b200.so has been built (reference: cuda_backend.py:40-45)."""
+    return N.available()
+
+
+def _load_extension():
+    try:
+        return N.load()
+    except (RuntimeError, OSError, AttributeError) as exc:
+        raise RuntimeError(
+            "CUDA extension is not built. Run: python -m rns_llm_b200.csrc.build"
+        ) from exc
+
+
+class PreparedRNSWeight:
+    """Cached Transformer weight ready for the RNS GEMM.
+
+    Reference: ``PreparedRNSWeight`` (cuda_backend.py:68-76) holds residue
+    planes [R,K,N], R bytes per value.  Here ``weight_nk`` is the int8 matrix
+    [N,K] (kernel ``"tcgen05"``) and planes are never stored; ``residues``
+    builds them on first access for callers that read the attribute.  Sources
+    wider than int8, or moduli the packed encoder cannot fold in one step, use
+    kernel ``"planes"`` and keep real planes as the reference does.
+    """
+
+    def __init__(self, *, backend: "CudaRNSBackend", moduli: tuple[int, ...], k: int, n: int,
+                 kernel: str, weight_nk: torch.Tensor | None = None,
+                 weight_kn: torch.Tensor | None = None, residues: torch.Tensor | None = None) -> None:
+        self._backend = backend
+        self.moduli = moduli
+        self.k = int(k)
+        self.n = int(n)
+        self.kernel = kernel
+        self.weight_nk = weight_nk
+        self._weight_kn = weight_kn
+        self._residues = residues
+
+    @property
+    def residues(self) -> torch.Tensor:
+        if self._residues is None:
+            kn = self._weight_kn if self._weight_kn is not None else self.weight_nk.t().contiguous()
+            self._residues = self._backend._encode_centered_raw(kn, self.moduli)
+        return self._residues
+
+    @property
+    def device(self) -> torch.device:
+        return (self.weight_nk if self.weight_nk is not None else self._residues).device
+
+    def prefix(self, channels: int, kernel: str) -> "PreparedRNSWeight":
+        """The same weight restricted to the first ``channels`` moduli (no copy)."""
+        return PreparedRNSWeight(
+            backend=self._backend, moduli=self.moduli[:channels], k=self.k, n=self.n, kernel=kernel,
+            weight_nk=self.weight_nk, weight_kn=self._weight_kn,
+            residues=None if self._residues is None else self._residues[:channels],
+        )
+
+
+@dataclass
+class RNSWorkspace:
+    """Reusable output memory for one shape/stream/request (cuda_backend.py:79-88).
+
+    ``accumulators`` ([R,M,N] int32) exists only for the plane-level pipeline; the
+    fused kernel keeps its accumulators in tensor memory and needs ``output`` only.
+    """
+
+    accumulators: torch.Tensor | None
+    output: torch.Tensor
+    channels: int
+    m: int
+    n: int
+
+
+@dataclass(frozen=True)
+class PreparedAdaptiveRNSWeight:
+    """One prepared weight with its safe prefix variants (cuda_backend.py:90-97)."""
+
+    variants: dict[int, PreparedRNSWeight]
+    full_moduli: tuple[int, ...]
+    max_abs_weight: int
+    min_channels: int
+
+
+@dataclass
+class RNSRequestBatchWorkspace:
+    """Preallocated merged-activation buffer plus output (cuda_backend.py:100-107)."""
+
+    activations: torch.Tensor
+    fused: RNSWorkspace
+    rows_per_request: tuple[int, ...]
+    k: int
+    _offsets: tuple[int, ...] = field(default=(), repr=False)
+
+
+class AdaptiveMetadata(Mapping):
+    """``{"channels", "bound", "capacity"}`` of one adaptive call.
+
+    The reference returns Python ints, which costs a device-to-host sync per
+    call (cuda_backend.py:591, 617-621).  Here the three numbers stay in a
+    device tensor and are fetched the first time a key is read.
+    """
+
+    _KEYS = ("channels", "bound", "capacity")
+
+    def __init__(self, device_values: torch.Tensor) -> None:
+        self._device_values = device_values
+        self._host: dict[str, int] | None = None
+
+    def _fetch(self) -> dict[str, int]:
+        if self._host is None:
+            values = self._device_values.cpu().tolist()
+            self._host = dict(zip(self._KEYS, (int(v) for v in values)))
+            self._device_values = None
+        return self._host
+
+    def __getitem__(self, key: str) -> int:
+        return self._fetch()[key]
+
+    def __iter__(self):
+        return iter(self._KEYS)
+
+    def __len__(self) -> int:
+        return 3
+
+    def __repr__(self) -> str:
+        return f"AdaptiveMetadata({self._fetch()!r})"
+
+
+@dataclass
+class _DeviceState:
+    status: torch.Tensor          # int32 [1]: device-side error word
+    histogram: torch.Tensor       # int64 [MAX_CHANNELS+1]: adaptive selections per channel count
+
+
+class CudaRNSBackend:
+    """RNS backend over hand-written sm_100a kernels (one process per GPU)."""
+
+    name = "cuda-rns-b200"
+
+    def __init__(self) -> None:
+        if not torch.cuda.is_available():
+            raise RuntimeError("CUDA is not available in this PyTorch installation")
+        self._lib = _load_extension()
+        self._stats: Counter[str] = Counter()
+        self._device_state: dict[int, _DeviceState] = {}
+        self._moduli_arrays: dict[tuple[int, ...], C.Array] = {}
+        self.arena = StreamArena()
+
+    # ------------------------------------------------------------------
+    # plumbing
+    # ------------------------------------------------------------------
+    def _mods(self, moduli: Iterable[int]) -> tuple[tuple[int, ...], C.Array]:
+        mods = validate_moduli(moduli)
+        arr = self._moduli_arrays.get(mods)
+        if arr is None:
+            arr = N.moduli_array(mods)
+            self._moduli_arrays[mods] = arr
+        return mods, arr
+
+    @staticmethod
+    def _stream(device: torch.device) -> int:
+        return int(torch.cuda.current_stream(device).cuda_stream)
+
+    def _state(self, device: torch.device) -> _DeviceState:
+        index = device.index if device.index is not None else torch.cuda.current_device()
+        state = self._device_state.get(index)
+        if state is None:
+            dev = torch.device("cuda", index)
+            state = _DeviceState(
+                status=torch.zeros(1, dtype=torch.int32, device=dev),
+                histogram=torch.zeros(N.MAX_CHANNELS + 1, dtype=torch.int64, device=dev),
+            )
+            self._device_state[index] = state
+        return state
+
+    def reset_stats(self) -> None:
+        self._stats.clear()
+        for state in self._device_state.values():
+            state.histogram.zero_()
+
+    def stats_snapshot(self) -> dict[str, int]:
+        """Counters with the reference's keys (cuda_backend.py:129-135).  The
+        ``adaptive_channels_{c}`` entries live on the device and are read here."""
+        snapshot = dict(self._stats)
+        for state in self._device_state.values():
+            for channels, count in enumerate(state.histogram.cpu().tolist()):
+                if count:
+                    key = f"adaptive_channels_{channels}"
+                    snapshot[key] = snapshot.get(key, 0) + int(count)
+        return snapshot
+
+    def check_status(self) -> None:
+        """Raises if a kernel recorded a device-side failure (bounded wait expired,
+        or an adaptive bound beyond the full set's capacity).  Synchronises."""
+        for state in self._device_state.values():
+            code = int(state.status.item())
+            if code == N.ERR_OVERFLOW:
+                state.status.zero_()
+                raise OverflowError("full moduli set cannot represent the activation bound")
+            if code != N.OK:
+                state.status.zero_()
+                raise RuntimeError(f"RNS kernel reported device status {code}")
+
+    @staticmethod
+    def _validate_matrix(matrix: torch.Tensor, name: str, ndim: int) -> None:
+        if not matrix.is_cuda:
+            raise ValueError(f"{name} must be a CUDA tensor")
+        if matrix.ndim != ndim:
+            raise ValueError(f"{name} must have rank {ndim}")
+        if not matrix.is_contiguous():
+            raise ValueError(f"{name} must be contiguous")
+
+    # ------------------------------------------------------------------
+    # Encoding
+    # ------------------------------------------------------------------
+    def encode(self, values: torch.Tensor, moduli: Iterable[int]) -> torch.Tensor:
+        """Canonical [0,m) uint8 planes (cuda_backend.py:177-184)."""
+        self._validate_matrix(values, "values", values.ndim)
+        if values.dtype != torch.int8:
+            raise ValueError("canonical CUDA encoder currently expects torch.int8")
+        mods, arr = self._mods(moduli)
+        out = torch.empty((len(mods), *values.shape), dtype=torch.uint8, device=values.device)
+        with torch.cuda.device(values.device):
+            N.check(self._lib.rns_encode_canonical_i8(values.data_ptr(), values.numel(), arr, len(mods),
+                                                      out.data_ptr(), self._stream(values.device)))
+        return out
+
+    def _encode_centered_raw(self, values: torch.Tensor, moduli: Iterable[int]) -> torch.Tensor:
+        mods, arr = self._mods(moduli)
+        out = torch.empty((len(mods), *values.shape), dtype=torch.int8, device=values.device)
+        with torch.cuda.device(values.device):
+            N.check(self._lib.rns_encode_centered(values.data_ptr(), _INT_TYPES[values.dtype],
+                                                  values.numel(), arr, len(mods), out.data_ptr(),
+                                                  self._stream(values.device)))
+        return out
+
+    def encode_centered(self, values: torch.Tensor, moduli: Iterable[int]) -> torch.Tensor:
+        """int8/int16/int32 -> centred int8 planes [R,*shape] (cuda_backend.py:186-200)."""
+        self._validate_matrix(values, "values", values.ndim)
+        if values.dtype not in _INT_TYPES:
+            raise ValueError("centered encoder supports int8, int16 and int32")
+        self._stats["encode_centered_calls"] += 1
+        self._stats["encode_centered_values"] += int(values.numel())
+        return self._encode_centered_raw(values, moduli)
+
+    # ------------------------------------------------------------------
+    # Bounds and selection (cuda_backend.py:205-261)
+    # ------------------------------------------------------------------
+    @staticmethod
+    def accumulator_bound(k: int, moduli: Iterable[int]) -> int:
+        return int(k) * (max(validate_moduli(moduli)) - 1) ** 2
+
+    @staticmethod
+    def centered_accumulator_bound(k: int, moduli: Iterable[int]) -> int:
+        return int(k) * max(m // 2 for m in validate_moduli(moduli)) ** 2
+
+    def select_kernel(self, k: int, moduli: Iterable[int], requested: CanonicalKernelName) -> str:
+        if requested != "auto":
+            return requested
+        return "tiled" if self.accumulator_bound(k, moduli) <= 0xFFFFFFFF else "tiled_safe"
+
+    def cublas_compatible(self, *, k: int, n: int, moduli: Iterable[int], device: torch.device) -> bool:
+        """Shape test of the reference's fused path (cuda_backend.py:224-239):
+        K and N multiples of 4, 2..10 channels, int32-safe accumulators.  Kept
+        because plane-level callers rely on it; see ``tensor_core_compatible``
+        for the kernel this backend prefers."""
+        return (
+            k % 4 == 0
+            and n % 4 == 0
+            and 2 <= len(validate_moduli(moduli)) <= 10
+            and self.centered_accumulator_bound(k, moduli) <= 0x7FFFFFFF
+        )
+
+    def tensor_core_compatible(self, *, k: int, moduli: Iterable[int]) -> bool:
+        """True when int8 sources with this K and these moduli run on the
+        tcgen05 kernel: K % 16 == 0, 2..8 channels, every modulus >= 86."""
+        mods, arr = self._mods(moduli)
+        return bool(self._lib.rns_linear_fused_supported(arr, len(mods), int(k), int(k), int(k))) and (
+            int(k) * 127 * 127 <= 0x7FFFFFFF
+        )
+
+    def select_centered_kernel(self, *, k: int, n: int, moduli: Iterable[int],
+                               requested: CenteredKernelName, device: torch.device) -> str:
+        if requested != "auto":
+            return requested
+        if self.cublas_compatible(k=k, n=n, moduli=moduli, device=device):
+            return "cublas"
+        if self.centered_accumulator_bound(k, moduli) <= 0x7FFFFFFF:
+            return "dp4a"
+        return "dp4a_safe"
+
+    # ------------------------------------------------------------------
+    # Plane-level GEMMs (cuda_backend.py:266-459)
+    # ------------------------------------------------------------------
+    def matmul_residues(self, a_residues: torch.Tensor, b_residues: torch.Tensor,
+                        moduli: Iterable[int], *, kernel: CanonicalKernelName = "auto") -> torch.Tensor:
+        self._validate_matrix(a_residues, "a_residues", 3)
+        self._validate_matrix(b_residues, "b_residues", 3)
+        if a_residues.dtype != torch.uint8 or b_residues.dtype != torch.uint8:
+            raise ValueError("canonical residue matrices must use torch.uint8")
+        if a_residues.device != b_residues.device:
+            raise ValueError("a_residues and b_residues must be on the same device")
+        if a_residues.shape[0] != b_residues.shape[0]:
+            raise ValueError("residue channel counts do not match")
+        if a_residues.shape[2] != b_residues.shape[1]:
+            raise ValueError("K dimensions do not match")
+        mods, arr = self._mods(moduli)
+        if a_residues.shape[0] != len(mods):
+            raise ValueError("tensor channel count does not match moduli")
+        selected = self.select_kernel(a_residues.shape[2], mods, kernel)
+        kernel_id = {"naive": 0, "tiled": 1, "tiled_safe": 2}[selected]
+        r, m, k = map(int, a_residues.shape)
+        n = int(b_residues.shape[2])
+        out = torch.empty((r, m, n), dtype=torch.uint8, device=a_residues.device)
+        with torch.cuda.device(a_residues.device):
+            N.check(self._lib.rns_matmul_canonical_planes(
+                a_residues.data_ptr(), b_residues.data_ptr(), arr, r, m, k, n, kernel_id,
+                out.data_ptr(), self._stream(a_residues.device)))
+        return out
+
+    def _check_centered_planes(self, a_residues, b_residues, moduli):
+        self._validate_matrix(a_residues, "a_residues", 3)
+        self._validate_matrix(b_residues, "b_residues", 3)
+        if a_residues.dtype != torch.int8 or b_residues.dtype != torch.int8:
+            raise ValueError("centered residue matrices must use torch.int8")
+        if a_residues.device != b_residues.device:
+            raise ValueError("a_residues and b_residues must share a device")
+        if a_residues.shape[0] != b_residues.shape[0]:
+            raise ValueError("channel counts do not match")
+        if a_residues.shape[2] != b_residues.shape[1]:
+            raise ValueError("K dimensions do not match")
+        mods, arr = self._mods(moduli)
+        if len(mods) != a_residues.shape[0]:
+            raise ValueError("moduli count does not match residue channels")
+        return mods, arr
+
+    def matmul_centered_residues(self, a_residues: torch.Tensor, b_residues: torch.Tensor,
+                                 moduli: Iterable[int], *, kernel: CenteredKernelName = "auto") -> torch.Tensor:
+        mods, arr = self._check_centered_planes(a_residues, b_residues, moduli)
+        r, m, k = map(int, a_residues.shape)
+        n = int(b_residues.shape[2])
+        selected = self.select_centered_kernel(k=k, n=n, moduli=mods, requested=kernel,
+                                               device=a_residues.device)
+        if selected == "cublas" and not self.cublas_compatible(k=k, n=n, moduli=mods,
+                                                               device=a_residues.device):
+            raise ValueError("cuBLAS path constraints are not satisfied")
+        kernel_id = {"scalar": 0, "dp4a": 1, "dp4a_safe": 2, "cublas": 3}.get(selected)
+        if kernel_id is None:
+            raise ValueError(f"unknown centered kernel: {selected}")
+        out = torch.empty((r, m, n), dtype=torch.int8, device=a_residues.device)
+        with torch.cuda.device(a_residues.device):
+            N.check(self._lib.rns_matmul_centered_planes(
+                a_residues.data_ptr(), b_residues.data_ptr(), arr, r, m, k, n, kernel_id,
+                out.data_ptr(), self._stream(a_residues.device)))
+        return out
+
+    def decode_garner(self, residues: torch.Tensor, moduli: Iterable[int]) -> torch.Tensor:
+        self._validate_matrix(residues, "residues", residues.ndim)
+        if residues.dtype != torch.int8:
+            raise ValueError("Garner decoder expects centered int8 residues")
+        if residues.ndim < 2:
+            raise ValueError("residues must have shape [R,...]")
+        mods, arr = self._mods(moduli)
+        if residues.shape[0] != len(mods):
+            raise ValueError("moduli count mismatch")
+        out = torch.empty(residues.shape[1:], dtype=torch.int64, device=residues.device)
+        with torch.cuda.device(residues.device):
+            N.check(self._lib.rns_decode_garner(residues.data_ptr(), out.numel(), arr, len(mods),
+                                                out.data_ptr(), self._stream(residues.device)))
+        return out
+
+    def create_workspace(self, *, device: torch.device, channels: int, m: int, n: int,
+                         with_accumulators: bool = False) -> RNSWorkspace:
+        """Output memory for one shape (cuda_backend.py:366-380).  The int32
+        accumulator planes of the reference are allocated only on request or
+        when a plane-level call first needs them."""
+        return RNSWorkspace(
+            accumulators=torch.empty((channels, m, n), dtype=torch.int32, device=device)
+            if with_accumulators else None,
+            output=torch.empty((m, n), dtype=torch.int64, device=device),
+            channels=int(channels), m=int(m), n=int(n),
+        )
+
+    @staticmethod
+    def _check_workspace(workspace: RNSWorkspace, *, channels: int, m: int, n: int,
+                         device: torch.device) -> None:
+        if (workspace.channels, workspace.m, workspace.n) != (channels, m, n):
+            raise ValueError("workspace shape does not match operation")
+        if workspace.output.device != device:
+            raise ValueError("workspace device does not match operation")
+
+    def matmul_centered_fused(self, a_residues: torch.Tensor, b_residues: torch.Tensor,
+                              moduli: Iterable[int], *, lut_channels: int = 0,
+                              workspace: RNSWorkspace | None = None) -> torch.Tensor:
+        """Plane-level fused call: planes [R,M,K] x [R,K,N] -> int64 [M,N]
+        (cuda_backend.py:398-459).  For callers that already hold planes; the
+        hot path is ``matmul_prepared_fused``."""
+        if a_residues.dtype != torch.int8 or b_residues.dtype != torch.int8:
+            raise ValueError("fused path expects centered int8 residue planes")
+        if a_residues.ndim == 3 and b_residues.ndim == 3 and (
+            a_residues.shape[0] != b_residues.shape[0] or a_residues.shape[2] != b_residues.shape[1]
+        ):
+            raise ValueError("R/K dimensions do not match")
+        if lut_channels not in (0, 1, 2):
+            raise ValueError("lut_channels must be 0, 1 or 2")
+        mods, arr = self._check_centered_planes(a_residues, b_residues, moduli)
+        r, m, k = map(int, a_residues.shape)
+        n = int(b_residues.shape[2])
+        if not self.cublas_compatible(k=k, n=n, moduli=mods, device=a_residues.device):
+            raise ValueError("fused path requires a cuBLAS-compatible shape/device")
+        if workspace is None:
+            workspace = self.create_workspace(device=a_residues.device, channels=r, m=m, n=n,
+                                              with_accumulators=True)
+        self._check_workspace(workspace, channels=r, m=m, n=n, device=a_residues.device)
+        if workspace.accumulators is None:
+            workspace.accumulators = torch.empty((r, m, n), dtype=torch.int32, device=a_residues.device)
+        self._stats["fused_gemm_calls"] += 1
+        self._stats[f"fused_gemm_channels_{r}"] += 1
+        with torch.cuda.device(a_residues.device):
+            N.check(self._lib.rns_matmul_centered_fused_out(
+                a_residues.data_ptr(), b_residues.data_ptr(), arr, r, m, k, n, min(lut_channels, r),
+                workspace.accumulators.data_ptr(), workspace.output.data_ptr(),
+                self._stream(a_residues.device)))
+        return workspace.output
+
+    # ------------------------------------------------------------------
+    # Prepared weights
+    # ------------------------------------------------------------------
+    def prepare_weight(self, b: torch.Tensor, moduli: Iterable[int]) -> PreparedRNSWeight:
+        """``b`` is [K,N] as in the reference (cuda_backend.py:464-487)."""
+        self._validate_matrix(b, "b", 2)
+        if b.dtype not in _INT_TYPES:
+            raise ValueError("prepared weights support int8/int16/int32")
+        mods, _ = self._mods(moduli)
+        k, n = int(b.shape[0]), int(b.shape[1])
+        if b.dtype == torch.int8 and self.tensor_core_compatible(k=k, moduli=mods):
+            return PreparedRNSWeight(backend=self, moduli=mods, k=k, n=n, kernel="tcgen05",
+                                     weight_nk=b.t().contiguous(), weight_kn=None)
+        residues = self.encode_centered(b.contiguous(), mods)
+        kernel = self.select_centered_kernel(k=k, n=n, moduli=mods, requested="auto", device=b.device)
+        return PreparedRNSWeight(backend=self, moduli=mods, k=k, n=n, kernel=kernel, residues=residues)
+
+    def prepare_weight_nk(self, w: torch.Tensor, moduli: Iterable[int]) -> PreparedRNSWeight:
+        """``w`` is int8 [N,K], the nn.Linear layout: no transpose, no copy."""
+        self._validate_matrix(w, "w", 2)
+        if w.dtype != torch.int8:
+            raise ValueError("prepare_weight_nk expects int8")
+        mods, _ = self._mods(moduli)
+        n, k = int(w.shape[0]), int(w.shape[1])
+        if not self.tensor_core_compatible(k=k, moduli=mods):
+            return self.prepare_weight(w.t().contiguous(), mods)
+        return PreparedRNSWeight(backend=self, moduli=mods, k=k, n=n, kernel="tcgen05", weight_nk=w)
+
+    def _check_activation(self, a: torch.Tensor, prepared: PreparedRNSWeight) -> None:
+        self._validate_matrix(a, "a", 2)
+        if a.dtype not in _INT_TYPES:
+            raise ValueError("a must be int8/int16/int32")
+        if int(a.shape[1]) != prepared.k:
+            raise ValueError("K dimension does not match prepared weight")
+        if a.device != prepared.device:
+            raise ValueError("activation and prepared weight must share device")
+
+    def matmul_prepared(self, a: torch.Tensor, prepared_weight: PreparedRNSWeight, *,
+                        decode: bool = True, kernel: CenteredKernelName = "auto") -> torch.Tensor:
+        """Unfused path of the reference (cuda_backend.py:489-512): encode, plane
+        GEMM to centred residues, CRT decode."""
+        self._check_activation(a, prepared_weight)
+        a_residues = self.encode_centered(a.contiguous(), prepared_weight.moduli)
+        if kernel in ("tcgen05", "planes"):
+            kernel = "auto"
+        result = self.matmul_centered_residues(a_residues, prepared_weight.residues,
+                                               prepared_weight.moduli, kernel=kernel)
+        return self.decode(result, prepared_weight.moduli) if decode else result
+
+    def _launch_fused(self, *, prepared: PreparedRNSWeight, m: int, a: torch.Tensor | None,
+                      a_planes: torch.Tensor | None, out: torch.Tensor,
+                      active: torch.Tensor | None = None, row_scale: torch.Tensor | None = None,
+                      row_scale_stride: int = 0, col_scale: torch.Tensor | None = None,
+                      bias: torch.Tensor | None = None, tile_n: int = 0, tile_k: int = 0) -> None:
+        mods = prepared.moduli
+        w = prepared.weight_nk
+        args = N.LinearArgs()
+        args.m, args.n, args.k = m, prepared.n, prepared.k
+        args.channels = len(mods)
+        for i, mod in enumerate(mods):
+            args.moduli[i] = mod
+        if a_planes is not None:
+            args.d_a_planes = a_planes.data_ptr()
+            args.lda = prepared.k
+            args.a_plane_stride = m * prepared.k
+        else:
+            args.d_a = a.data_ptr()
+            args.lda = a.stride(0)
+        args.d_w = w.data_ptr()
+        args.ldw = w.stride(0)
+        args.d_active_channels = None if active is None else active.data_ptr()
+        args.d_out = out.data_ptr()
+        args.ldo = out.stride(0)
+        args.out_type = _OUT_TYPES[out.dtype]
+        if row_scale is not None:
+            args.d_row_scale = row_scale.data_ptr()
+            args.row_scale_stride = row_scale_stride
+            args.d_col_scale = col_scale.data_ptr()
+            args.d_bias = None if bias is None else bias.data_ptr()
+        device = w.device
+        args.d_status = self._state(device).status.data_ptr()
+        args.tile_n, args.tile_k = tile_n, tile_k
+        N.check(self._lib.rns_linear_fused(C.byref(args), self._stream(device)))
+
+    def matmul_prepared_fused(self, a: torch.Tensor, prepared_weight: PreparedRNSWeight, *,
+                              lut_channels: int = 0, workspace: RNSWorkspace | None = None,
+                              _active: torch.Tensor | None = None) -> torch.Tensor:
+        """Quantised activations [M,K] x prepared weight -> exact int64 [M,N]
+        (cuda_backend.py:514-539).  The result aliases ``workspace.output``."""
+        self._check_activation(a, prepared_weight)
+        if lut_channels not in (0, 1, 2):
+            raise ValueError("lut_channels must be 0, 1 or 2")
+        mods = prepared_weight.moduli
+        channels = len(mods)
+        m = int(a.shape[0])
+        if prepared_weight.kernel != "tcgen05" or a.dtype != torch.int8:
+            if prepared_weight.kernel not in ("tcgen05", "cublas"):
+                raise ValueError("fused prepared path currently requires cuBLAS-compatible weight")
+            a_residues = self.encode_centered(a.contiguous(), mods)
+            return self.matmul_centered_fused(a_residues, prepared_weight.residues, mods,
+                                              lut_channels=lut_channels, workspace=workspace)
+        if workspace is None:
+            workspace = self.create_workspace(device=a.device, channels=channels, m=m,
+                                              n=prepared_weight.n)
+        self._check_workspace(workspace, channels=channels, m=m, n=prepared_weight.n, device=a.device)
+        self._stats["encode_centered_calls"] += 1
+        self._stats["encode_centered_values"] += int(a.numel())
+        self._stats["fused_gemm_calls"] += 1
+        self._stats[f"fused_gemm_channels_{channels}"] += 1
+        with torch.cuda.device(a.device):
+            if m >= PLANES_MIN_ROWS:
+                frame = self.arena.frame(a.device)
+                planes = frame.alloc((channels, m, prepared_weight.k), torch.int8)
+                _, arr = self._mods(mods)
+                N.check(self._lib.rns_encode_centered(a.data_ptr(), N.INT8, a.numel(), arr, channels,
+                                                      planes.data_ptr(), self._stream(a.device)))
+                self._launch_fused(prepared=prepared_weight, m=m, a=None, a_planes=planes,
+                                   out=workspace.output, active=_active)
+            else:
+                self._launch_fused(prepared=prepared_weight, m=m, a=a, a_planes=None,
+                                   out=workspace.output, active=_active)
+        return workspace.output
+
+    # ------------------------------------------------------------------
+    # Adaptive channel prefix (cuda_backend.py:541-622)
+    # ------------------------------------------------------------------
+    def prepare_weight_adaptive(self, b: torch.Tensor, moduli: Iterable[int], *,
+                                min_channels: int = 3) -> PreparedAdaptiveRNSWeight:
+        full = self.prepare_weight(b, moduli)
+        return self._adaptive_from_full(full, int(b.to(torch.int32).abs().max().item()), min_channels)
+
+    def _adaptive_from_full(self, full: PreparedRNSWeight, max_abs_weight: int,
+                            min_channels: int) -> PreparedAdaptiveRNSWeight:
+        if not 2 <= min_channels <= len(full.moduli):
+            raise ValueError("min_channels must be between 2 and full channel count")
+        variants: dict[int, PreparedRNSWeight] = {}
+        for channels in range(min_channels, len(full.moduli) + 1):
+            if full.kernel == "tcgen05":
+                kernel = "tcgen05"
+            else:
+                kernel = self.select_centered_kernel(k=full.k, n=full.n, moduli=full.moduli[:channels],
+                                                     requested="auto", device=full.device)
+            variants[channels] = full if channels == len(full.moduli) else full.prefix(channels, kernel)
+        return PreparedAdaptiveRNSWeight(variants=variants, full_moduli=full.moduli,
+                                         max_abs_weight=int(max_abs_weight), min_channels=int(min_channels))
+
+    def select_adaptive_variant(self, a: torch.Tensor, prepared: PreparedAdaptiveRNSWeight
+                                ) -> tuple[PreparedRNSWeight, int]:
+        """Host-side selection with the reference's signature and its
+        device-to-host synchronisation (cuda_backend.py:573-601).  The hot path
+        (``matmul_prepared_adaptive_fused``) does not call this."""
+        self._validate_matrix(a, "a", 2)
+        if a.dtype not in _INT_TYPES:
+            raise ValueError("a must be int8/int16/int32")
+        max_row_l1 = int(a.to(torch.int32).abs().sum(dim=1).max().item())
+        bound = safe_l1_dot_bound(max_row_l1, prepared.max_abs_weight)
+        channels = minimal_prefix_channels(prepared.full_moduli, bound, min_channels=prepared.min_channels)
+        self._stats["adaptive_selections"] += 1
+        self._stats[f"adaptive_channels_{channels}"] += 1
+        return prepared.variants[channels], bound
+
+    def matmul_prepared_adaptive_fused(self, a: torch.Tensor, prepared: PreparedAdaptiveRNSWeight, *,
+                                       lut_channels: int = 2,
+                                       workspace_by_channels: dict[int, RNSWorkspace] | None = None,
+                                       return_metadata: bool = False):
+        """Adaptive prefix, decided on the device: row-L1 maximum, safe bound,
+        smallest sufficient prefix and the GEMM that uses it are all queued
+        without a host round trip.  An activation bound beyond the full set's
+        capacity (``OverflowError`` in the reference, adaptive.py:38-41) sets
+        the device status word; ``check_status()`` raises it."""
+        full = prepared.variants[len(prepared.full_moduli)]
+        self._check_activation(a, full)
+        if full.kernel != "tcgen05" or a.dtype != torch.int8:
+            variant, bound = self.select_adaptive_variant(a, prepared)
+            workspace = None if workspace_by_channels is None else workspace_by_channels.get(len(variant.moduli))
+            output = self.matmul_prepared_fused(a, variant, lut_channels=lut_channels, workspace=workspace)
+            if return_metadata:
+                return output, {"channels": len(variant.moduli), "bound": bound,
+                                "capacity": (prod(variant.moduli) - 1) // 2}
+            return output
+        mods, arr = self._mods(prepared.full_moduli)
+        channels = len(mods)
+        m = int(a.shape[0])
+        device = a.device
+        state = self._state(device)
+        workspace = None
+        if workspace_by_channels is not None:
+            # Any workspace of the right [M,N] serves: the kernel keeps no per-channel memory.
+            workspace = workspace_by_channels.get(channels) or next(iter(workspace_by_channels.values()), None)
+            if workspace is not None and (workspace.m, workspace.n) != (m, full.n):
+                raise ValueError("workspace shape does not match operation")
+        out = workspace.output if workspace is not None else torch.empty(
+            (m, full.n), dtype=torch.int64, device=device)
+        with torch.cuda.device(device):
+            frame = self.arena.frame(device)
+            scratch = frame.alloc(8, torch.int32)          # [0] row-L1 max, [1] active channels
+            meta = torch.empty(3, dtype=torch.int64, device=device) if return_metadata else None
+            stream = self._stream(device)
+            N.check(self._lib.rns_row_l1_max_i8(a.data_ptr(), m, full.k, a.stride(0),
+                                                scratch.data_ptr(), stream))
+            N.check(self._lib.rns_select_channels(
+                scratch.data_ptr(), prepared.max_abs_weight, arr, channels, prepared.min_channels,
+                scratch.data_ptr() + 4, None if meta is None else meta.data_ptr(),
+                state.histogram.data_ptr(), state.status.data_ptr(), stream))
+            active = scratch[1:2]
+            self._stats["adaptive_selections"] += 1
+            self._stats["encode_centered_calls"] += 1
+            self._stats["encode_centered_values"] += int(a.numel())
+            self._stats["fused_gemm_calls"] += 1
+            self._launch_fused(prepared=full, m=m, a=a, a_planes=None, out=out, active=active)
+        if return_metadata:
+            return out, AdaptiveMetadata(meta)
+        return out
+
+    # ------------------------------------------------------------------
+    # Continuous batching (cuda_backend.py:624-703)
+    # ------------------------------------------------------------------
+    def create_request_batch_workspace(self, *, device: torch.device, dtype: torch.dtype,
+                                       rows_per_request: Sequence[int], k: int, channels: int,
+                                       n: int) -> RNSRequestBatchWorkspace:
+        rows = tuple(int(x) for x in rows_per_request)
+        if not rows or any(x <= 0 for x in rows):
+            raise ValueError("rows_per_request must contain positive sizes")
+        total = sum(rows)
+        offsets = [0]
+        for r in rows:
+            offsets.append(offsets[-1] + r)
+        return RNSRequestBatchWorkspace(
+            activations=torch.empty((total, k), dtype=dtype, device=device),
+            fused=self.create_workspace(device=device, channels=channels, m=total, n=n),
+            rows_per_request=rows, k=int(k), _offsets=tuple(offsets),
+        )
+
+    def matmul_prepared_fused_requests(self, requests: Sequence[torch.Tensor],
+                                       prepared_weight: PreparedRNSWeight, *, lut_channels: int = 2,
+                                       workspace: RNSRequestBatchWorkspace | None = None,
+                                       clone_outputs: bool = False) -> tuple[torch.Tensor, ...]:
+        """Concatenate requests along M, one RNS GEMM, split the rows again.
+        The merge is a single gather launch (``torch.cat(..., out=)``) rather
+        than one copy per request (cuda_backend.py:684-688)."""
+        if not requests:
+            raise ValueError("requests must not be empty")
+        first = requests[0]
+        rows = tuple(int(x.shape[0]) for x in requests)
+        for index, tensor in enumerate(requests):
+            self._validate_matrix(tensor, f"requests[{index}]", 2)
+            if tensor.dtype != first.dtype or tensor.device != first.device:
+                raise ValueError("all requests must share dtype/device")
+            if int(tensor.shape[1]) != prepared_weight.k:
+                raise ValueError("request K does not match prepared weight")
+        if workspace is None:
+            workspace = self.create_request_batch_workspace(
+                device=first.device, dtype=first.dtype, rows_per_request=rows, k=prepared_weight.k,
+                channels=len(prepared_weight.moduli), n=prepared_weight.n)
+        if workspace.rows_per_request != rows or workspace.k != prepared_weight.k:
+            raise ValueError("request batch workspace does not match request shapes")
+        if len(requests) == 1:
+            workspace.activations.copy_(first)
+        else:
+            torch.cat(tuple(requests), dim=0, out=workspace.activations)
+        merged = self.matmul_prepared_fused(workspace.activations, prepared_weight,
+                                            lut_channels=lut_channels, workspace=workspace.fused)
+        outputs = []
+        offset = 0
+        for row_count in rows:
+            view = merged[offset:offset + row_count]
+            outputs.append(view.clone() if clone_outputs else view)
+            offset += row_count
+        self._stats["continuous_batch_calls"] += 1
+        self._stats["continuous_batch_requests"] += len(requests)
+        return tuple(outputs)
+
+    # ------------------------------------------------------------------
+    # Floating-point linear: quantise -> fused GEMM with dequantising epilogue
+    # ------------------------------------------------------------------
+    def linear_forward(self, x: torch.Tensor, prepared: PreparedRNSWeight, weight_scale: torch.Tensor,
+                       bias: torch.Tensor | None, *, per_row: bool = False,
+                       adaptive: PreparedAdaptiveRNSWeight | None = None,
+                       return_metadata: bool = False, out: torch.Tensor | None = None):
+        """y[M,N] = dequant( quant(x)[M,K] @ Wq[N,K]^T ) in the dtype of ``x``.
+
+        The whole of ``RNSLinear.forward`` after weight preparation
+        (layers/rns_linear.py:237-275): activation scale and quantisation
+        (per tensor as in the reference, or per row), residue encoding, the
+        per-channel GEMMs, reconstruction and ``x*s_a*s_w + bias`` in fp32, in
+        two or three launches.  ``x`` is [M,K] float16/bfloat16/float32 with
+        unit inner stride; ``weight_scale`` float32 [N]; ``bias`` float32 [N].
+        ``out`` may be a [M,N] view with unit inner stride (e.g. a column block
+        of a wider matrix)."""
+        if prepared.kernel != "tcgen05":
+            raise ValueError("linear_forward needs a tensor-core prepared weight")
+        if x.ndim != 2 or x.stride(1) != 1 or x.dtype not in _FLOAT_TYPES:
+            raise ValueError("x must be a [M,K] float16/bfloat16/float32 matrix with unit inner stride")
+        m, k = int(x.shape[0]), int(x.shape[1])
+        if k != prepared.k:
+            raise ValueError("K dimension does not match prepared weight")
+        device = x.device
+        mods, arr = self._mods(prepared.moduli if adaptive is None else adaptive.full_moduli)
+        channels = len(mods)
+        if out is None:
+            out = torch.empty((m, prepared.n), dtype=x.dtype, device=device)
+        elif out.shape != (m, prepared.n) or out.stride(1) != 1 or out.dtype != x.dtype:
+            raise ValueError("out must be [M,N] of x's dtype with unit inner stride")
+        use_planes = m >= PLANES_MIN_ROWS and adaptive is None
+        meta = None
+        with torch.cuda.device(device):
+            frame = self.arena.frame(device)
+            scale = frame.alloc(m if per_row else 1, torch.float32)
+            scratch = frame.alloc(8, torch.int32)   # [0..3] absmax scratch, [4] row-L1 max, [5] active
+            q = None if use_planes else frame.alloc((m, k), torch.int8)
+            planes = frame.alloc((channels, m, k), torch.int8) if use_planes else None
+            stream = self._stream(device)
+            N.check(self._lib.rns_quantize_activations(
+                x.data_ptr(), _FLOAT_TYPES[x.dtype], m, k, x.stride(0), 1 if per_row else 0, 127,
+                arr, channels, None if q is None else q.data_ptr(),
+                None if planes is None else planes.data_ptr(), scale.data_ptr(),
+                scratch.data_ptr() + 16 if adaptive is not None else None,
+                scratch.data_ptr(), stream))
+            active = None
+            if adaptive is not None:
+                state = self._state(device)
+                if return_metadata:
+                    meta = torch.empty(3, dtype=torch.int64, device=device)
+                N.check(self._lib.rns_select_channels(
+                    scratch.data_ptr() + 16, adaptive.max_abs_weight, arr, channels,
+                    adaptive.min_channels, scratch.data_ptr() + 20,
+                    None if meta is None else meta.data_ptr(), state.histogram.data_ptr(),
+                    state.status.data_ptr(), stream))
+                active = scratch[5:6]
+                self._stats["adaptive_selections"] += 1
+            self._stats["encode_centered_calls"] += 1
+            self._stats["encode_centered_values"] += m * k
+            self._stats["fused_gemm_calls"] += 1
+            if adaptive is None:
+                self._stats[f"fused_gemm_channels_{channels}"] += 1
+            self._launch_fused(prepared=prepared if adaptive is None else adaptive.variants[channels],
+                               m=m, a=q, a_planes=planes, out=out, active=active,
+                               row_scale=scale, row_scale_stride=1 if per_row else 0,
+                               col_scale=weight_scale, bias=bias)
+        if return_metadata:
+            return out, (AdaptiveMetadata(meta) if meta is not None else None)
+        return out
+
+    def quantize_weight(self, weight: torch.Tensor, quant_max: int = 127
+                        ) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+        """Per-output-channel symmetric int8 of an nn.Linear weight [N,K]
+        (layers/rns_linear.py:183-184), kept in that layout.  Returns
+        (int8 [N,K], float32 scale [N], int32 [1] max |q| on the device)."""
+        if weight.ndim != 2 or weight.stride(1) != 1 or weight.dtype not in _FLOAT_TYPES:
+            raise ValueError("weight must be a [N,K] floating matrix with unit inner stride")
+        n, k = int(weight.shape[0]), int(weight.shape[1])
+        wq = torch.empty((n, k), dtype=torch.int8, device=weight.device)
+        scale = torch.empty(n, dtype=torch.float32, device=weight.device)
+        max_abs = torch.empty(1, dtype=torch.int32, device=weight.device)
+        with torch.cuda.device(weight.device):
+            N.check(self._lib.rns_quantize_weight(
+                weight.data_ptr(), _FLOAT_TYPES[weight.dtype], n, k, weight.stride(0), int(quant_max),
+                wq.data_ptr(), scale.data_ptr(), max_abs.data_ptr(), self._stream(weight.device)))
+        return wq, scale, max_abs
+
+    # ------------------------------------------------------------------
+    # CRT decode and wide helpers (cuda_backend.py:705-799)
+    # ------------------------------------------------------------------
+    def decode(self, residues: torch.Tensor, moduli: Iterable[int], *, signed: bool = True) -> torch.Tensor:
+        """Chinese-remainder decode kept as the reference's cross-check of the
+        Garner kernel (cuda_backend.py:706-731); a handful of int64 tensor ops,
+        not on the hot path."""
+        self._validate_matrix(residues, "residues", residues.ndim)
+        if residues.dtype not in (torch.uint8, torch.int8):
+            raise ValueError("decoder expects uint8 canonical or int8 centered residues")
+        product, coefficients = crt_constants(moduli)
+        result = torch.zeros(residues.shape[1:], dtype=torch.int64, device=residues.device)
+        for channel, coefficient in enumerate(coefficients):
+            result = torch.remainder(result + residues[channel].to(torch.int64) * coefficient, product)
+        if signed:
+            result = torch.where(result > product // 2, result - product, result)
+        return result
+
+    def matmul_wide(self, a: torch.Tensor, b: torch.Tensor, moduli: Iterable[int], *,
+                    decode: bool = True, kernel: CenteredKernelName = "auto") -> torch.Tensor:
+        self._validate_matrix(a, "a", 2)
+        self._validate_matrix(b, "b", 2)
+        if a.dtype not in _INT_TYPES:
+            raise ValueError("a must be int8/int16/int32")
+        if b.dtype != a.dtype:
+            raise ValueError("a and b must use the same integer dtype")
+        if a.shape[1] != b.shape[0]:
+            raise ValueError("K dimensions do not match")
+        mods, _ = self._mods(moduli)
+        a_residues = self.encode_centered(a.contiguous(), mods)
+        b_residues = self.encode_centered(b.contiguous(), mods)
+        output = self.matmul_centered_residues(a_residues, b_residues, mods, kernel=kernel)
+        return self.decode(output, mods) if decode else output
+
+    def matmul_wide_fused(self, a: torch.Tensor, b: torch.Tensor, moduli: Iterable[int], *,
+                          lut_channels: int = 0, workspace: RNSWorkspace | None = None) -> torch.Tensor:
+        self._validate_matrix(a, "a", 2)
+        self._validate_matrix(b, "b", 2)
+        if a.dtype not in _INT_TYPES:
+            raise ValueError("a must be int8/int16/int32")
+        if b.dtype != a.dtype or a.shape[1] != b.shape[0]:
+            raise ValueError("dtype/K mismatch")
+        mods, _ = self._mods(moduli)
+        if a.dtype == torch.int8 and self.tensor_core_compatible(k=int(a.shape[1]), moduli=mods):
+            return self.matmul_prepared_fused(a, self.prepare_weight(b, mods), lut_channels=lut_channels,
+                                              workspace=workspace)
+        a_residues = self.encode_centered(a.contiguous(), mods)
+        b_residues = self.encode_centered(b.contiguous(), mods)
+        return self.matmul_centered_fused(a_residues, b_residues, mods, lut_channels=lut_channels,
+                                          workspace=workspace)
+
+    def matmul_int8(self, a: torch.Tensor, b: torch.Tensor, moduli: Iterable[int], *,
+                    decode: bool = True, kernel: CenteredKernelName = "auto") -> torch.Tensor:
+        if a.dtype != torch.int8 or b.dtype != torch.int8:
+            raise ValueError("matmul_int8 expects int8 inputs")
+        return self.matmul_wide(a, b, moduli, decode=decode, kernel=kernel)
+
+    # Host-side constants in the reference's shapes, for callers that want them
+    # (cuda_backend.py:48-66): reciprocals, P, CRT coefficients, pairwise inverses, LUT.
+    @staticmethod
+    def host_constants(moduli: Iterable[int]):
+        mods = validate_moduli(moduli)
+        product, coefficients = crt_constants(mods)
+        return (tuple((1 << 32) // m for m in mods), product, coefficients,
+                garner_pairwise_inverses(mods), compact_byte_mod_lut(mods))

@@ -314,6 +314,7 @@ struct SelectArgs {
 
 __global__ void select_channels_kernel(const int* __restrict__ row_l1_max, SelectArgs sa,
                                        int* __restrict__ active, long long* __restrict__ meta,
+                                       long long* __restrict__ histogram,
                                        int* __restrict__ status) {
     if (threadIdx.x != 0 || blockIdx.x != 0) return;
     const long long bound = (long long)(*row_l1_max) * sa.max_abs_weight;
@@ -330,6 +331,7 @@ __global__ void select_channels_kernel(const int* __restrict__ row_l1_max, Selec
         meta[1] = bound;
         meta[2] = (sa.product[chosen] - 1) / 2;
     }
+    if (histogram) histogram[chosen] += 1;
 }
 
 // Weight quantiser: one block per output channel (row of W).
@@ -555,7 +557,8 @@ int rns_row_l1_max_i8(const int8_t* d_a, int m, int k, int64_t lda, int32_t* d_r
 
 int rns_select_channels(const int32_t* d_row_l1_max, int32_t max_abs_weight, const int32_t* moduli,
                         int channels, int min_channels, int32_t* d_active_channels,
-                        int64_t* d_meta, int32_t* d_status, rns_stream_t stream) {
+                        int64_t* d_meta, int64_t* d_histogram, int32_t* d_status,
+                        rns_stream_t stream) {
     Plan pl;
     if (int rc = build_plan(moduli, channels, &pl)) return rc;
     if (!d_row_l1_max || !d_active_channels)
@@ -570,7 +573,8 @@ int rns_select_channels(const int32_t* d_row_l1_max, int32_t max_abs_weight, con
     sa.max_abs_weight = max_abs_weight;
     for (int i = 0; i <= kMaxCh; ++i) sa.product[i] = pl.product[i];
     select_channels_kernel<<<1, 32, 0, as_stream(stream)>>>(
-        d_row_l1_max, sa, d_active_channels, reinterpret_cast<long long*>(d_meta), d_status);
+        d_row_l1_max, sa, d_active_channels, reinterpret_cast<long long*>(d_meta),
+        reinterpret_cast<long long*>(d_histogram), d_status);
     RNS_CUDA_OK(cudaGetLastError());
     return RNS_OK;
 }

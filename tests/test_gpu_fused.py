@@ -1,0 +1,348 @@
+"""The fused tcgen05 path through the C ABI against the oracle: bit-exact
+integers, bit-exact dequantised fp16 (the oracle follows the reference's fp32
+operation order, so the 1e-3 relative tolerance of the specification is met
+with zero error), quantiser, adaptive prefix, continuous batching, streams."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import rns_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+C0 = (127, 126, 125, 121)
+C4 = (127, 126, 125, 121, 113)
+REL_TOL = 1e-3  # north-star tolerance for dequantised outputs
+
+
+@pytest.fixture(scope="module")
+def backend():
+    from rns_llm_b200.backends import CudaRNSBackend
+    return CudaRNSBackend()
+
+
+def dev(arr):
+    return torch.from_numpy(np.ascontiguousarray(arr)).cuda()
+
+
+def fused_int(backend, a, w_nk, mods, *, planes=False, tile_n=0, tile_k=0, out_dtype=torch.int64, active=None):
+    """Direct call of rns_linear_fused on a [M,K] int8 and w [N,K] int8."""
+    prepared = backend.prepare_weight_nk(dev(w_nk), mods)
+    assert prepared.kernel == "tcgen05"
+    m = a.shape[0]
+    out = torch.full((m, w_nk.shape[0]), -7, dtype=out_dtype, device="cuda")
+    a_dev = dev(a)
+    if planes:
+        a_planes = backend.encode_centered(a_dev, mods)
+        backend._launch_fused(prepared=prepared, m=m, a=None, a_planes=a_planes, out=out,
+                              tile_n=tile_n, tile_k=tile_k, active=active)
+    else:
+        backend._launch_fused(prepared=prepared, m=m, a=a_dev, a_planes=None, out=out,
+                              tile_n=tile_n, tile_k=tile_k, active=active)
+    torch.cuda.synchronize()
+    backend.check_status()
+    return out.cpu().numpy()
+
+
+def rand_i8(rng, shape, lo=-127, hi=127):
+    return rng.integers(lo, hi + 1, size=shape).astype(np.int8)
+
+
+def test_config0_bit_exact(backend, golden):
+    rng = np.random.default_rng(1000)
+    a = rng.integers(-127, 128, size=(128, 768), dtype=np.int64).astype(np.int8)
+    b = rng.integers(-127, 128, size=(768, 768), dtype=np.int64).astype(np.int8)
+    exact = O.exact_matmul(a, b)
+    g = golden("gemm")
+    assert [int(exact.sum()), int(np.abs(exact).sum()), int(exact[0, 0]), int(exact[-1, -1])] == \
+        [int(v) for v in g["c0_checksum"]]
+    w = np.ascontiguousarray(b.T)
+    for planes in (False, True):
+        assert np.array_equal(fused_int(backend, a, w, C0, planes=planes), exact)
+    assert np.array_equal(fused_int(backend, a, w, C0, out_dtype=torch.int32), exact.astype(np.int32))
+    # the backend entry point the reference exposes
+    prepared = backend.prepare_weight(dev(b), C0)
+    got = backend.matmul_prepared_fused(dev(a), prepared, lut_channels=2)
+    assert got.dtype == torch.int64 and np.array_equal(got.cpu().numpy(), exact)
+
+
+@pytest.mark.parametrize("m,k,n", [(1, 64, 16), (17, 64, 20), (5, 128, 33), (128, 768, 96),
+                                   (129, 256, 130), (300, 1024, 260), (256, 4096, 256)])
+@pytest.mark.parametrize("planes", [False, True])
+def test_shapes_ragged_and_deep(backend, m, k, n, planes):
+    rng = np.random.default_rng(m * 7 + k + n)
+    a, w = rand_i8(rng, (m, k), -128, 127), rand_i8(rng, (n, k), -128, 127)
+    assert np.array_equal(fused_int(backend, a, w, C0, planes=planes), O.exact_matmul(a, w.T))
+
+
+@pytest.mark.parametrize("tile_n", [16, 32, 48, 64, 96, 128])
+@pytest.mark.parametrize("tile_k", [64, 128])
+def test_tile_shapes(backend, tile_n, tile_k):
+    rng = np.random.default_rng(tile_n + tile_k)
+    mods = (127, 125)  # two channels leave room for every tile shape
+    a, w = rand_i8(rng, (140, 512)), rand_i8(rng, (200, 512))
+    exact = O.exact_matmul(a, w.T)
+    # two moduli hold +-7937: compare modulo P through the oracle's reconstruction
+    expect = O.decode_garner(np.stack([exact % 127, exact % 125]), mods)
+    assert np.array_equal(fused_int(backend, a, w, mods, tile_n=tile_n, tile_k=tile_k), expect)
+
+
+@pytest.mark.parametrize("mods", [(127, 125), (127, 126, 125), C0, C4, (127, 126, 125, 121, 113, 109),
+                                  (255, 253, 251, 247), (127, 125, 123, 121, 119, 113, 109, 107)])
+def test_channel_counts(backend, mods):
+    rng = np.random.default_rng(len(mods))
+    k = 16384 if mods == C4 else 256
+    a, w = rand_i8(rng, (40, k)), rand_i8(rng, (72, k))
+    exact = O.exact_matmul(a, w.T)
+    cap = O.signed_capacity(mods)
+    if np.abs(exact).max() <= cap:
+        expect = exact
+    else:
+        expect = O.decode_garner(np.stack([exact % m for m in mods]), mods)
+    for planes in (False, True):
+        assert np.array_equal(fused_int(backend, a, w, mods, planes=planes), expect)
+
+
+def test_genuine_residues_reach_the_tensor_core(backend):
+    """With the product of the moduli far below the true dot products the result
+    must be the wrapped value of the residue arithmetic, not the plain integer
+    product: evidence that every channel multiplies residues."""
+    rng = np.random.default_rng(99)
+    mods = (127, 113)
+    a, w = rand_i8(rng, (64, 1024)), rand_i8(rng, (64, 1024))
+    exact = O.exact_matmul(a, w.T)
+    assert np.abs(exact).max() > O.signed_capacity(mods)
+    expect = O.rns_matmul_device_pipeline(a, w.T, mods)
+    got = fused_int(backend, a, w, mods)
+    assert np.array_equal(got, expect) and not np.array_equal(got, exact)
+
+
+@pytest.mark.parametrize("tag", ["qkv16", "odd"])
+def test_linear_forward_matches_reference_golden(backend, golden, tag):
+    g = golden("rns_linear")
+    x = dev(g[f"{tag}_x"])
+    weight = dev(g[f"{tag}_weight"])
+    bias = dev(g[f"{tag}_bias"])
+    w_q, w_scale, max_abs = backend.quantize_weight(weight)
+    assert np.array_equal(w_q.cpu().numpy(), g[f"{tag}_w_q"])
+    assert np.array_equal(w_scale.cpu().numpy(), g[f"{tag}_w_scale"])
+    assert int(max_abs.item()) == int(np.abs(g[f"{tag}_w_q"].astype(np.int32)).max())
+    prepared = backend.prepare_weight_nk(w_q, C0)
+    flat = x.reshape(-1, x.shape[-1])
+    y = backend.linear_forward(flat, prepared, w_scale, bias.float())
+    torch.cuda.synchronize()
+    backend.check_status()
+    expect = g[f"{tag}_y"].reshape(y.shape)
+    got = y.cpu().numpy()
+    assert np.array_equal(got.view(np.uint16), expect.view(np.uint16))
+    denom = np.maximum(np.abs(expect.astype(np.float32)), 1e-3)
+    assert float(np.max(np.abs(got.astype(np.float32) - expect.astype(np.float32)) / denom)) <= REL_TOL
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("per_row", [False, True])
+@pytest.mark.parametrize("m", [3, 700])
+def test_linear_forward_dtypes_and_scales(backend, dtype, per_row, m):
+    torch.manual_seed(5)
+    k, n = 256, 136
+    x = torch.randn(m, k).to(dtype)
+    weight = (torch.randn(n, k) * 0.05).to(dtype)
+    bias = torch.randn(n).to(dtype)
+    np_dtype = {torch.float16: np.float16, torch.float32: np.float32}.get(dtype, np.float32)
+    res = O.rns_linear_forward(x.float().numpy(), weight.float().numpy(), bias.float().numpy(), C0,
+                               per_row=per_row, out_dtype=np_dtype)
+    w_q, w_scale, _ = backend.quantize_weight(weight.cuda())
+    assert np.array_equal(w_q.cpu().numpy(), res["w_q"])
+    prepared = backend.prepare_weight_nk(w_q, C0)
+    y = backend.linear_forward(x.cuda(), prepared, w_scale, bias.float().cuda(), per_row=per_row)
+    torch.cuda.synchronize()
+    backend.check_status()
+    if dtype == torch.bfloat16:
+        expect = torch.from_numpy(res["y"]).to(torch.bfloat16)
+        assert torch.equal(y.cpu(), expect)
+    else:
+        assert np.array_equal(y.cpu().numpy(), res["y"])
+
+
+def test_quantizer_outputs(backend):
+    rng = np.random.default_rng(31)
+    x = (rng.standard_normal((37, 192)) * 3).astype(np.float16)
+    x[5, 7] = 0.0
+    from rns_llm_b200 import _native as N
+    lib = N.load()
+    xd = dev(x)
+    for per_row in (0, 1):
+        q = torch.empty((37, 192), dtype=torch.int8, device="cuda")
+        planes = torch.empty((4, 37, 192), dtype=torch.int8, device="cuda")
+        scale = torch.empty(37 if per_row else 1, dtype=torch.float32, device="cuda")
+        l1 = torch.empty(1, dtype=torch.int32, device="cuda")
+        scratch = torch.empty(4, dtype=torch.int32, device="cuda")
+        N.check(lib.rns_quantize_activations(xd.data_ptr(), N.F16, 37, 192, 192, per_row, 127,
+                                             N.moduli_array(C0), 4, q.data_ptr(), planes.data_ptr(),
+                                             scale.data_ptr(), l1.data_ptr(), scratch.data_ptr(),
+                                             torch.cuda.current_stream().cuda_stream))
+        torch.cuda.synchronize()
+        exp_scale = O.symmetric_scale(x.astype(np.float32), 127, axis=1 if per_row else None)
+        exp_q = O.quantize(x.astype(np.float32), exp_scale, 127)
+        assert np.array_equal(scale.cpu().numpy(), exp_scale.reshape(-1))
+        assert np.array_equal(q.cpu().numpy(), exp_q)
+        assert np.array_equal(planes.cpu().numpy(), O.encode_centered(exp_q, C0, "device"))
+        assert int(l1.item()) == int(np.abs(exp_q.astype(np.int64)).sum(axis=1).max())
+    zeros = torch.zeros((4, 64), dtype=torch.float16, device="cuda")
+    wq, ws, _ = backend.quantize_weight(zeros)
+    assert float(ws[0]) == float(np.finfo(np.float32).eps) and int(wq.abs().max()) == 0
+
+
+def test_adaptive_prefix_selected_on_device(backend):
+    rng = np.random.default_rng(1002)
+    a_low = rand_i8(rng, (128, 768), -15, 15)
+    a_full = rand_i8(rng, (128, 768))
+    w_kn = rand_i8(rng, (768, 768))
+    adaptive = backend.prepare_weight_adaptive(dev(w_kn), C0, min_channels=3)
+    assert adaptive.max_abs_weight == 127 and sorted(adaptive.variants) == [3, 4]
+    backend.reset_stats()
+    out_low, meta_low = backend.matmul_prepared_adaptive_fused(dev(a_low), adaptive, return_metadata=True)
+    out_full, meta_full = backend.matmul_prepared_adaptive_fused(dev(a_full), adaptive, return_metadata=True)
+    assert np.array_equal(out_low.cpu().numpy(), O.exact_matmul(a_low, w_kn))
+    assert np.array_equal(out_full.cpu().numpy(), O.exact_matmul(a_full, w_kn))
+    exp_low = O.adaptive_channels(a_low, w_kn.T, C0, 3)
+    exp_full = O.adaptive_channels(a_full, w_kn.T, C0, 3)
+    assert (meta_low["channels"], meta_low["bound"]) == exp_low and exp_low[0] == 3
+    assert (meta_full["channels"], meta_full["bound"]) == exp_full and exp_full[0] == 4
+    assert meta_low["bound"] <= meta_low["capacity"] == O.signed_capacity(C0[:3])
+    stats = backend.stats_snapshot()
+    assert stats["adaptive_selections"] == 2
+    assert stats["adaptive_channels_3"] == 1 and stats["adaptive_channels_4"] == 1
+    backend.check_status()
+    # host-synchronising selection kept with the reference's signature
+    variant, bound = backend.select_adaptive_variant(dev(a_low), adaptive)
+    assert len(variant.moduli) == 3 and bound == exp_low[1]
+
+
+def test_adaptive_runs_under_graph_capture(backend):
+    """No host synchronisation on the adaptive path: it can be captured."""
+    rng = np.random.default_rng(41)
+    a_low = dev(rand_i8(rng, (16, 256), -8, 8))
+    w_kn = rand_i8(rng, (256, 64), -40, 40)
+    adaptive = backend.prepare_weight_adaptive(dev(w_kn), C0, min_channels=3)
+    ws = {4: backend.create_workspace(device=a_low.device, channels=4, m=16, n=64)}
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        backend.matmul_prepared_adaptive_fused(a_low, adaptive, workspace_by_channels=ws)  # warm the arena
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            out = backend.matmul_prepared_adaptive_fused(a_low, adaptive, workspace_by_channels=ws)
+        out.zero_()
+        graph.replay()
+        stream.synchronize()
+    assert np.array_equal(out.cpu().numpy(), O.exact_matmul(a_low.cpu().numpy(), w_kn))
+
+
+def test_adaptive_overflow_sets_status(backend):
+    rng = np.random.default_rng(43)
+    mods = (127, 113)
+    a = dev(rand_i8(rng, (8, 1024)))
+    w_kn = dev(rand_i8(rng, (1024, 32)))
+    adaptive = backend.prepare_weight_adaptive(w_kn, mods, min_channels=2)
+    backend.matmul_prepared_adaptive_fused(a, adaptive)
+    with pytest.raises(OverflowError):
+        backend.check_status()
+    backend.check_status()  # cleared
+
+
+def test_continuous_batch_matches_independent_requests(backend):
+    rng = np.random.default_rng(1002)
+    weight_kn = rand_i8(rng, (768, 768))
+    prepared = backend.prepare_weight(dev(weight_kn), C0)
+    for rows in ((1,), (1, 1), (1, 1, 1, 1), (1, 3, 5, 2)):
+        requests = [rand_i8(rng, (r, 768)) for r in rows]
+        ws = backend.create_request_batch_workspace(device=torch.device("cuda"), dtype=torch.int8,
+                                                    rows_per_request=rows, k=768, channels=4, n=768)
+        backend.reset_stats()
+        merged = backend.matmul_prepared_fused_requests([dev(r) for r in requests], prepared,
+                                                        workspace=ws, clone_outputs=True)
+        for request, actual in zip(requests, merged):
+            independent = backend.matmul_prepared_fused(dev(request), prepared)
+            assert torch.equal(actual, independent)
+            assert np.array_equal(actual.cpu().numpy(), O.exact_matmul(request, weight_kn))
+        stats = backend.stats_snapshot()
+        assert stats["continuous_batch_calls"] == 1 and stats["continuous_batch_requests"] == len(rows)
+    with pytest.raises(ValueError):
+        backend.matmul_prepared_fused_requests([], prepared)
+    with pytest.raises(ValueError):
+        backend.create_request_batch_workspace(device=torch.device("cuda"), dtype=torch.int8,
+                                               rows_per_request=[1, 0], k=768, channels=4, n=768)
+
+
+def test_streams_have_private_scratch(backend):
+    rng = np.random.default_rng(51)
+    weight = (torch.randn(96, 512) * 0.03).half().cuda()
+    w_q, w_scale, _ = backend.quantize_weight(weight)
+    prepared = backend.prepare_weight_nk(w_q, C0)
+    streams = [torch.cuda.Stream() for _ in range(4)]
+    xs = [torch.randn(24 + 8 * i, 512).half().cuda() for i in range(4)]
+    torch.cuda.synchronize()
+    outs = [None] * 4
+    for _ in range(5):
+        for i, s in enumerate(streams):
+            with torch.cuda.stream(s):
+                outs[i] = backend.linear_forward(xs[i], prepared, w_scale, None)
+    torch.cuda.synchronize()
+    backend.check_status()
+    for i in range(4):
+        expect = O.rns_linear_forward(xs[i].cpu().numpy(), weight.cpu().numpy(), None, C0)["y"]
+        assert np.array_equal(outs[i].cpu().numpy(), expect)
+    assert len(backend.arena.streams()) >= 4
+
+
+def test_fused_argument_errors(backend):
+    from rns_llm_b200 import _native as N
+    a = torch.zeros((8, 64), dtype=torch.int8, device="cuda")
+    w = torch.zeros((16, 64), dtype=torch.int8, device="cuda")
+    prepared = backend.prepare_weight_nk(w, C0)
+    out = torch.zeros((8, 16), dtype=torch.int64, device="cuda")
+    with pytest.raises(ValueError):
+        backend._launch_fused(prepared=prepared, m=8, a=a, a_planes=None, out=out, tile_n=24)
+    with pytest.raises(ValueError):
+        backend._launch_fused(prepared=prepared, m=8, a=a, a_planes=None, out=out, tile_k=32)
+    with pytest.raises(ValueError):
+        backend.matmul_prepared_fused(a[:, :48].contiguous(), prepared)
+    with pytest.raises(ValueError):
+        backend.matmul_prepared_fused(a, prepared, lut_channels=3)
+    # K not a multiple of 16 or small moduli: served by the plane-level pipeline, still exact
+    rng = np.random.default_rng(61)
+    a2, b2 = rand_i8(rng, (9, 20)), rand_i8(rng, (20, 12))
+    prepared2 = backend.prepare_weight(dev(b2), C0)
+    assert prepared2.kernel == "cublas"
+    assert np.array_equal(backend.matmul_prepared_fused(dev(a2), prepared2).cpu().numpy(), O.exact_matmul(a2, b2))
+    small = (3, 5, 7, 11, 13, 17, 19, 23)
+    a3, b3 = rand_i8(rng, (6, 64)), rand_i8(rng, (64, 8))
+    prepared3 = backend.prepare_weight(dev(b3), small)
+    assert prepared3.kernel != "tcgen05"
+    assert np.array_equal(backend.matmul_prepared_fused(dev(a3), prepared3).cpu().numpy(), O.exact_matmul(a3, b3))
+    assert N.load().rns_linear_fused(None, None) == N.ERR_INVALID_ARGUMENT
+
+
+def test_full_size_against_independent_int_gemm(backend, c_oracle):
+    """Configuration-4 layer shapes: too large for the CPU oracle in full, so the
+    whole output is compared with torch._int_mm (cuBLAS int8 -> int32, an
+    independent exact GEMM) and a sample of rows with the C oracle."""
+    torch.manual_seed(1004)
+    for (m, k, n, mods) in ((4096, 4096, 4096, C0), (1024, 16384, 1024, C4)):
+        a = torch.randint(-127, 128, (m, k), dtype=torch.int8, device="cuda")
+        w = torch.randint(-127, 128, (n, k), dtype=torch.int8, device="cuda")
+        prepared = backend.prepare_weight_nk(w, mods)
+        got = backend.matmul_prepared_fused(a, prepared)
+        expect = torch._int_mm(a, w.t())
+        assert torch.equal(got, expect.to(torch.int64))
+        rows = [0, 1, m // 2, m - 1]
+        sample, _ = c_oracle.linear(a[rows].cpu().numpy(), w.cpu().numpy(), mods)
+        assert np.array_equal(got[rows].cpu().numpy(), sample)
+        # linearity: (a + a2) W = a W + a2 W for operands that stay inside int8
+        a_half = torch.div(a, 2, rounding_mode="trunc").to(torch.int8)
+        rest = (a - a_half).to(torch.int8)
+        both = backend.matmul_prepared_fused(a_half, prepared).clone() + \
+            backend.matmul_prepared_fused(rest, prepared)
+        assert torch.equal(both, got)
+    backend.check_status()
