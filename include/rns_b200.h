@@ -254,16 +254,24 @@ RNS_API int rns_linear_fused_supported(const int32_t* moduli, int channels, int 
  *                                                   per_row != 0)
  *   q     = clamp(rint(x / scale), -quant_max, quant_max)      (ties to even)
  *
- * d_x is [M,K] with row stride ldx (elements).  Outputs: d_q int8 [M,K]
+ * d_x is the logical [M,K] matrix.  Element (r,c) is read at
+ *   d_x[(c / col_block) * col_block_stride + r * ldx + (c % col_block)]
+ * (all in elements): col_block <= 0 means a plain matrix with row stride ldx;
+ * col_block = K/G, col_block_stride = M*K/G, ldx = K/G reads the layout an
+ * all-gather of G column shards [M,K/G] leaves behind, so the gathered output
+ * of a column-sharded layer feeds the next layer without a transposing copy.
+ * Outputs: d_q int8 [M,K]
  * (may be NULL when only planes are wanted), d_planes int8 [channels,M,K]
  * (NULL to skip), d_scale float [1] or [M], d_row_l1_max int32 [1] = max_m
  * sum_k |q[m,k]| (NULL to skip; input of rns_select_channels).
- * d_scratch: 16 bytes of device scratch owned by the caller's stream.
+ * d_scratch: 16 bytes of device scratch owned by the caller's stream (used
+ * only by the two-launch per-tensor path, M*K > 128 Ki elements).
  * quant_max must be 127 (8-bit sources).
  */
 RNS_API int rns_quantize_activations(const void* d_x, rns_float_type type,
-                                     int m, int k, int64_t ldx, int per_row,
-                                     int quant_max,
+                                     int m, int k, int64_t ldx,
+                                     int col_block, int64_t col_block_stride,
+                                     int per_row, int quant_max,
                                      const int32_t* moduli, int channels,
                                      int8_t* d_q, int8_t* d_planes, float* d_scale,
                                      int32_t* d_row_l1_max, void* d_scratch,

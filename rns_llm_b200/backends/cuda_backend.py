@@ -762,14 +762,25 @@ class CudaRNSBackend:
         (per tensor as in the reference, or per row), residue encoding, the
         per-channel GEMMs, reconstruction and ``x*s_a*s_w + bias`` in fp32, in
         two or three launches.  ``x`` is [M,K] float16/bfloat16/float32 with
-        unit inner stride; ``weight_scale`` float32 [N]; ``bias`` float32 [N].
+        unit inner stride, or the [G,M,K/G] result of an all-gather of column
+        shards; ``weight_scale`` float32 [N]; ``bias`` float32 [N].
         ``out`` may be a [M,N] view with unit inner stride (e.g. a column block
         of a wider matrix)."""
         if prepared.kernel != "tcgen05":
             raise ValueError("linear_forward needs a tensor-core prepared weight")
-        if x.ndim != 2 or x.stride(1) != 1 or x.dtype not in _FLOAT_TYPES:
-            raise ValueError("x must be a [M,K] float16/bfloat16/float32 matrix with unit inner stride")
-        m, k = int(x.shape[0]), int(x.shape[1])
+        if x.dtype not in _FLOAT_TYPES:
+            raise ValueError("x must be float16, bfloat16 or float32")
+        if x.ndim == 3:
+            # [G, M, K/G] contiguous: what an all-gather of G column shards produces.
+            if not x.is_contiguous():
+                raise ValueError("a gathered activation [G,M,K/G] must be contiguous")
+            blocks, m, col_block = (int(v) for v in x.shape)
+            k, ldx, col_block_stride = blocks * col_block, col_block, m * col_block
+        elif x.ndim == 2 and x.stride(1) == 1:
+            m, k = int(x.shape[0]), int(x.shape[1])
+            ldx, col_block, col_block_stride = int(x.stride(0)), 0, 0
+        else:
+            raise ValueError("x must be [M,K] with unit inner stride, or a gathered [G,M,K/G]")
         if k != prepared.k:
             raise ValueError("K dimension does not match prepared weight")
         device = x.device
@@ -789,7 +800,8 @@ class CudaRNSBackend:
             planes = frame.alloc((channels, m, k), torch.int8) if use_planes else None
             stream = self._stream(device)
             N.check(self._lib.rns_quantize_activations(
-                x.data_ptr(), _FLOAT_TYPES[x.dtype], m, k, x.stride(0), 1 if per_row else 0, 127,
+                x.data_ptr(), _FLOAT_TYPES[x.dtype], m, k, ldx, col_block, col_block_stride,
+                1 if per_row else 0, 127,
                 arr, channels, None if q is None else q.data_ptr(),
                 None if planes is None else planes.data_ptr(), scale.data_ptr(),
                 scratch.data_ptr() + 16 if adaptive is not None else None,

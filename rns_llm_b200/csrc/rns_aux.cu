@@ -184,28 +184,47 @@ __device__ __forceinline__ int warp_sum(int v) {
     return v;
 }
 
-// Scratch layout (16 bytes): [0] absmax bits (uint), [1] row-L1 max (int).
-// Pass 1: tensor-wide absmax by atomicMax on the float's bit pattern (order
-// preserving for non-negative floats).  The scratch word is zeroed by a
-// memset node enqueued before it.
+// ---------------------------------------------------------------------------
+// Activation source view.  Element (r, c) of the logical [M,K] matrix lives at
+//   x[(c / col_block) * col_block_stride + r * ldx + (c % col_block)]
+// which covers a plain strided matrix (col_block = K) and the layout an
+// all-gather of column shards leaves behind: G blocks [M, K/G] one after the
+// other (col_block = K/G, col_block_stride = M*K/G, ldx = K/G).
+// ---------------------------------------------------------------------------
+struct SrcView {
+    const void* x;
+    int32_t m, k;
+    int64_t ldx;
+    int32_t col_block;
+    int64_t col_block_stride;
+    int32_t vec8;  // 1: every group of 8 columns is contiguous and 16-byte aligned
+};
+
+__device__ __forceinline__ int64_t src_offset(const SrcView& s, int r, int c) {
+    const int b = c / s.col_block;
+    return (int64_t)b * s.col_block_stride + (int64_t)r * s.ldx + (c - b * s.col_block);
+}
+
+// Eight consecutive columns starting at column c (a multiple of 8) of row r.
 template <typename T>
-__global__ void __launch_bounds__(256)
-absmax_kernel(const T* __restrict__ x, int m, int k, int64_t ldx, unsigned* __restrict__ scratch) {
-    float best = 0.0f;
-    const int64_t total = (int64_t)m * k;
-    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
-         i += (int64_t)gridDim.x * blockDim.x) {
-        const int64_t r = i / k, c = i - r * k;
-        best = fmaxf(best, fabsf(load_f<T>(x, r * ldx + c)));
-    }
-    best = warp_max(best);
-    __shared__ float part[8];
-    if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = best;
-    __syncthreads();
-    if (threadIdx.x < 32) {
-        float v = threadIdx.x < 8 ? part[threadIdx.x] : 0.0f;
-        v = warp_max(v);
-        if (threadIdx.x == 0) atomicMax(scratch, __float_as_uint(v));
+__device__ __forceinline__ void load8(const SrcView& s, int r, int c, float (&v)[8]) {
+    const T* base = static_cast<const T*>(s.x) + src_offset(s, r, c);
+    if (s.vec8) {
+        if constexpr (sizeof(T) == 2) {
+            const uint4 raw = *reinterpret_cast<const uint4*>(base);
+            const T* h = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] = load_f<T>(h, i);
+        } else {
+            const float4 lo = *reinterpret_cast<const float4*>(base);
+            const float4 hi = *reinterpret_cast<const float4*>(base + 4);
+            v[0] = lo.x; v[1] = lo.y; v[2] = lo.z; v[3] = lo.w;
+            v[4] = hi.x; v[5] = hi.y; v[6] = hi.z; v[7] = hi.w;
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            v[i] = (c + i < s.k) ? load_f<T>(static_cast<const T*>(s.x), src_offset(s, r, c + i)) : 0.0f;
     }
 }
 
@@ -224,66 +243,176 @@ __device__ __forceinline__ int centred_residue(int v, int m) {
     return r;
 }
 
-// Pass 2 (one block per row): scale, int8 values, optional planes, row L1.
-// PER_ROW: the block first reduces its own row's absmax.
+struct QuantOut {
+    int8_t* q;        // [M,K] or NULL
+    int8_t* planes;   // [channels,M,K] or NULL
+    float* scale;     // [1] or [M]
+    int* row_l1_max;  // [1] or NULL
+    int32_t channels;
+    int32_t mod[kMaxCh];
+    uint32_t enc_hi[kMaxCh], enc_lo[kMaxCh];
+    int32_t single_fold;
+};
+
+// Quantises columns [c, c+8) of row r, stores values and planes, returns sum |q|.
+template <typename T>
+__device__ __forceinline__ int quantize_group(const SrcView& s, const QuantOut& o, int r, int c,
+                                              float scale, int qmax) {
+    float v[8];
+    load8<T>(s, r, c, v);
+    int q[8];
+    int l1 = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        q[i] = quantize_one(v[i], scale, qmax);
+        l1 += q[i] < 0 ? -q[i] : q[i];
+    }
+    const int64_t off = (int64_t)r * s.k + c;
+    const bool full = c + 8 <= s.k;
+    uint32_t w0 = 0, w1 = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        w0 |= (uint32_t)(q[i] & 0xff) << (8 * i);
+        w1 |= (uint32_t)(q[4 + i] & 0xff) << (8 * i);
+    }
+    if (full && (off & 7) == 0) {
+        if (o.q) *reinterpret_cast<uint2*>(o.q + off) = make_uint2(w0, w1);
+        if (o.planes) {
+            const int64_t plane = (int64_t)s.m * s.k;
+            if (o.single_fold) {
+                const uint32_t u0 = w0 ^ 0x80808080u, u1 = w1 ^ 0x80808080u;
+                const uint32_t l0 = u0 & 0x7f7f7f7fu, l1w = u1 & 0x7f7f7f7fu;
+#pragma unroll 1
+                for (int ch = 0; ch < o.channels; ++ch) {
+                    const uint32_t m = (uint32_t)o.mod[ch];
+                    *reinterpret_cast<uint2*>(o.planes + ch * plane + off) =
+                        make_uint2(encode_word(u0, l0, o.enc_hi[ch], o.enc_lo[ch], m),
+                                   encode_word(u1, l1w, o.enc_hi[ch], o.enc_lo[ch], m));
+                }
+            } else {
+#pragma unroll 1
+                for (int ch = 0; ch < o.channels; ++ch) {
+                    uint32_t e0 = 0, e1 = 0;
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        e0 |= (uint32_t)(centred_residue(q[i], o.mod[ch]) & 0xff) << (8 * i);
+                        e1 |= (uint32_t)(centred_residue(q[4 + i], o.mod[ch]) & 0xff) << (8 * i);
+                    }
+                    *reinterpret_cast<uint2*>(o.planes + ch * plane + off) = make_uint2(e0, e1);
+                }
+            }
+        }
+    } else {
+        for (int i = 0; i < 8 && c + i < s.k; ++i) {
+            if (o.q) o.q[off + i] = (int8_t)q[i];
+            if (o.planes)
+                for (int ch = 0; ch < o.channels; ++ch)
+                    o.planes[(int64_t)ch * s.m * s.k + off + i] = (int8_t)centred_residue(q[i], o.mod[ch]);
+        }
+    }
+    return l1;
+}
+
+template <typename T>
+__device__ __forceinline__ float group_absmax(const SrcView& s, int r, int c) {
+    float v[8];
+    load8<T>(s, r, c, v);
+    float best = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) best = fmaxf(best, fabsf(v[i]));
+    return best;
+}
+
+// Pass 1 of the per-tensor quantiser: tensor-wide absmax by atomicMax on the
+// float's bit pattern (order preserving for non-negative floats).  The scratch
+// word is zeroed by a memset enqueued before the kernel.
+template <typename T>
+__global__ void __launch_bounds__(256)
+absmax_kernel(const __grid_constant__ SrcView s, unsigned* __restrict__ scratch) {
+    float best = 0.0f;
+    const int groups_per_row = (s.k + 7) / 8;
+    const int64_t total = (int64_t)s.m * groups_per_row;
+    for (int64_t g = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; g < total;
+         g += (int64_t)gridDim.x * blockDim.x) {
+        const int r = (int)(g / groups_per_row);
+        const int c = (int)(g - (int64_t)r * groups_per_row) * 8;
+        best = fmaxf(best, group_absmax<T>(s, r, c));
+    }
+    best = warp_max(best);
+    __shared__ float part[8];
+    if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = best;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        float v = threadIdx.x < 8 ? part[threadIdx.x] : 0.0f;
+        v = warp_max(v);
+        if (threadIdx.x == 0) atomicMax(scratch, __float_as_uint(v));
+    }
+}
+
+// Pass 2 (one warp per row, eight rows per block): scale, int8 values, optional
+// planes, row L1.  PER_ROW: the warp first reduces its own row's absmax.
 template <typename T, bool PER_ROW>
 __global__ void __launch_bounds__(256)
-quantize_rows_kernel(const T* __restrict__ x, int m, int k, int64_t ldx, int qmax, ModList ml,
-                     int8_t* __restrict__ q_out, int8_t* __restrict__ planes,
-                     float* __restrict__ scale_out, int* __restrict__ row_l1_max,
-                     const unsigned* __restrict__ scratch) {
-    __shared__ float part[8];
-    __shared__ int ipart[8];
-    __shared__ float s_scale;
-    for (int row = blockIdx.x; row < m; row += gridDim.x) {
-        const T* xr = x + (int64_t)row * ldx;
+quantize_rows_kernel(const __grid_constant__ SrcView s, const __grid_constant__ QuantOut o,
+                     int qmax, const unsigned* __restrict__ scratch) {
+    const int lane = threadIdx.x & 31;
+    const int warps = (gridDim.x * blockDim.x) >> 5;
+    const int groups_per_row = (s.k + 7) / 8;
+    int worst_l1 = 0;
+    for (int row = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; row < s.m; row += warps) {
         float absmax;
         if (PER_ROW) {
             float best = 0.0f;
-            for (int c = threadIdx.x; c < k; c += blockDim.x) best = fmaxf(best, fabsf(load_f<T>(xr, c)));
-            best = warp_max(best);
-            if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = best;
-            __syncthreads();
-            if (threadIdx.x < 32) {
-                float v = threadIdx.x < 8 ? part[threadIdx.x] : 0.0f;
-                v = warp_max(v);
-                if (threadIdx.x == 0) s_scale = v;
-            }
-            __syncthreads();
-            absmax = s_scale;
-            __syncthreads();
+            for (int g = lane; g < groups_per_row; g += 32) best = fmaxf(best, group_absmax<T>(s, row, g * 8));
+            absmax = warp_max(best);
         } else {
             absmax = __uint_as_float(*scratch);
         }
         const float scale = fmaxf(__fdiv_rn(absmax, (float)qmax), FLT_EPSILON);
-        if (threadIdx.x == 0) {
-            if (PER_ROW) scale_out[row] = scale;
-            else if (row == 0) scale_out[0] = scale;
+        if (lane == 0) {
+            if (PER_ROW) o.scale[row] = scale;
+            else if (row == 0) o.scale[0] = scale;
         }
         int l1 = 0;
-        for (int c = threadIdx.x; c < k; c += blockDim.x) {
-            const int q = quantize_one(load_f<T>(xr, c), scale, qmax);
-            l1 += q < 0 ? -q : q;
-            const int64_t o = (int64_t)row * k + c;
-            if (q_out) q_out[o] = (int8_t)q;
-            if (planes) {
-#pragma unroll 1
-                for (int ch = 0; ch < ml.channels; ++ch)
-                    planes[(int64_t)ch * m * k + o] = (int8_t)centred_residue(q, ml.mod[ch]);
-            }
-        }
-        if (row_l1_max) {
-            l1 = warp_sum(l1);
-            if ((threadIdx.x & 31) == 0) ipart[threadIdx.x >> 5] = l1;
-            __syncthreads();
-            if (threadIdx.x == 0) {
-                int total = 0;
-                for (int w = 0; w < 8; ++w) total += ipart[w];
-                atomicMax(row_l1_max, total);
-            }
-            __syncthreads();
-        }
+        for (int g = lane; g < groups_per_row; g += 32) l1 += quantize_group<T>(s, o, row, g * 8, scale, qmax);
+        if (o.row_l1_max) worst_l1 = max(worst_l1, warp_sum(l1));
     }
+    if (o.row_l1_max && lane == 0 && worst_l1 > 0) atomicMax(o.row_l1_max, worst_l1);
+}
+
+// Per-tensor quantiser for small activations in ONE launch of one CTA: absmax
+// through shared memory, then the same per-row work.  No scratch, no memset.
+template <typename T>
+__global__ void __launch_bounds__(1024)
+quantize_small_kernel(const __grid_constant__ SrcView s, const __grid_constant__ QuantOut o, int qmax) {
+    __shared__ float part[32];
+    __shared__ float s_absmax;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int groups_per_row = (s.k + 7) / 8;
+    const int total = s.m * groups_per_row;
+    float best = 0.0f;
+    for (int g = threadIdx.x; g < total; g += blockDim.x) {
+        const int r = g / groups_per_row;
+        best = fmaxf(best, group_absmax<T>(s, r, (g - r * groups_per_row) * 8));
+    }
+    best = warp_max(best);
+    if (lane == 0) part[warp] = best;
+    if (threadIdx.x == 0 && o.row_l1_max) *o.row_l1_max = 0;
+    __syncthreads();
+    if (warp == 0) {
+        float v = warp_max(part[lane]);
+        if (lane == 0) s_absmax = v;
+    }
+    __syncthreads();
+    const float scale = fmaxf(__fdiv_rn(s_absmax, (float)qmax), FLT_EPSILON);
+    if (threadIdx.x == 0) o.scale[0] = scale;
+    int worst_l1 = 0;
+    for (int row = warp; row < s.m; row += (int)(blockDim.x >> 5)) {
+        int l1 = 0;
+        for (int g = lane; g < groups_per_row; g += 32) l1 += quantize_group<T>(s, o, row, g * 8, scale, qmax);
+        if (o.row_l1_max) worst_l1 = max(worst_l1, warp_sum(l1));
+    }
+    if (o.row_l1_max && lane == 0 && worst_l1 > 0) atomicMax(o.row_l1_max, worst_l1);
 }
 
 __global__ void __launch_bounds__(256)
@@ -497,46 +626,64 @@ int rns_matmul_centered_fused_out(const int8_t* d_a, const int8_t* d_b, const in
 }
 
 int rns_quantize_activations(const void* d_x, rns_float_type type, int m, int k, int64_t ldx,
+                             int col_block, int64_t col_block_stride,
                              int per_row, int quant_max, const int32_t* moduli, int channels,
                              int8_t* d_q, int8_t* d_planes, float* d_scale,
                              int32_t* d_row_l1_max, void* d_scratch, rns_stream_t stream) {
     if (!d_x || !d_scale || (!d_q && !d_planes))
         return fail(RNS_ERR_INVALID_ARGUMENT, "quantize: NULL pointer");
-    if (m <= 0 || k <= 0 || ldx < k)
-        return fail(RNS_ERR_INVALID_ARGUMENT, "quantize: bad shape or stride");
+    if (col_block <= 0) { col_block = k; col_block_stride = 0; }
+    if (m <= 0 || k <= 0 || ldx < col_block || k % col_block != 0)
+        return fail(RNS_ERR_INVALID_ARGUMENT, "quantize: bad shape, stride or column block");
     if (quant_max != 127)
         return fail(RNS_ERR_UNSUPPORTED, "the fused quantiser produces 8-bit values (quant_max 127)");
-    if (!per_row && !d_scratch)
+    const bool small = !per_row && (int64_t)m * k <= 128 * 1024;
+    if (!per_row && !small && !d_scratch)
         return fail(RNS_ERR_INVALID_ARGUMENT, "quantize: per-tensor scale needs d_scratch");
-    ModList ml{};
+    QuantOut qo{};
+    qo.q = d_q; qo.planes = d_planes; qo.scale = d_scale; qo.row_l1_max = d_row_l1_max;
     if (d_planes) {
         Plan pl;
         if (int rc = build_plan(moduli, channels, &pl)) return rc;
-        ml = modlist(pl);
+        qo.channels = pl.channels;
+        qo.single_fold = pl.encode_single_fold;
+        for (int i = 0; i < kMaxCh; ++i) {
+            qo.mod[i] = pl.mod[i]; qo.enc_hi[i] = pl.enc_hi[i]; qo.enc_lo[i] = pl.enc_lo[i];
+        }
     }
+    size_t esize = 2;
+    if (type == RNS_F32) esize = 4;
+    else if (type != RNS_F16 && type != RNS_BF16)
+        return fail(RNS_ERR_INVALID_ARGUMENT, "quantize: unknown float type");
+    SrcView sv{};
+    sv.x = d_x; sv.m = m; sv.k = k; sv.ldx = ldx;
+    sv.col_block = col_block; sv.col_block_stride = col_block_stride;
+    const size_t vec_bytes = 8 * esize;  // bytes of one group; alignment needed: 16
+    sv.vec8 = (k % 8 == 0 && col_block % 8 == 0 && (ldx * esize) % 16 == 0 &&
+               (col_block_stride * esize) % 16 == 0 &&
+               (reinterpret_cast<uintptr_t>(d_x) % 16) == 0) ? 1 : 0;
+    (void)vec_bytes;
     cudaStream_t st = as_stream(stream);
     unsigned* scratch = static_cast<unsigned*>(d_scratch);
-    if (!per_row) RNS_CUDA_OK(cudaMemsetAsync(scratch, 0, 16, st));
-    if (d_row_l1_max) RNS_CUDA_OK(cudaMemsetAsync(d_row_l1_max, 0, sizeof(int32_t), st));
-    const int rows_grid = m < 148 * 8 ? m : 148 * 8;
+    if (!per_row && !small) RNS_CUDA_OK(cudaMemsetAsync(scratch, 0, 16, st));
+    if (d_row_l1_max && !small) RNS_CUDA_OK(cudaMemsetAsync(d_row_l1_max, 0, sizeof(int32_t), st));
+    const int row_blocks = grid_for(m, 8, 148 * 8);  // eight rows (warps) per block
+    const int64_t groups = (int64_t)m * ((k + 7) / 8);
 #define RNS_QUANT(T)                                                                           \
     do {                                                                                       \
-        const T* x = static_cast<const T*>(d_x);                                               \
         if (per_row) {                                                                         \
-            quantize_rows_kernel<T, true><<<rows_grid, 256, 0, st>>>(                          \
-                x, m, k, ldx, quant_max, ml, d_q, d_planes, d_scale, d_row_l1_max, scratch);   \
+            quantize_rows_kernel<T, true><<<row_blocks, 256, 0, st>>>(sv, qo, quant_max, scratch); \
+        } else if (small) {                                                                    \
+            quantize_small_kernel<T><<<1, 1024, 0, st>>>(sv, qo, quant_max);                   \
         } else {                                                                               \
-            absmax_kernel<T><<<grid_for((int64_t)m * k, 256 * 8, 148 * 4), 256, 0, st>>>(      \
-                x, m, k, ldx, scratch);                                                        \
-            quantize_rows_kernel<T, false><<<rows_grid, 256, 0, st>>>(                         \
-                x, m, k, ldx, quant_max, ml, d_q, d_planes, d_scale, d_row_l1_max, scratch);   \
+            absmax_kernel<T><<<grid_for(groups, 256 * 4, 148 * 8), 256, 0, st>>>(sv, scratch); \
+            quantize_rows_kernel<T, false><<<row_blocks, 256, 0, st>>>(sv, qo, quant_max, scratch); \
         }                                                                                      \
     } while (0)
     switch (type) {
         case RNS_F16: RNS_QUANT(__half); break;
         case RNS_BF16: RNS_QUANT(__nv_bfloat16); break;
-        case RNS_F32: RNS_QUANT(float); break;
-        default: return fail(RNS_ERR_INVALID_ARGUMENT, "quantize: unknown float type");
+        default: RNS_QUANT(float); break;
     }
 #undef RNS_QUANT
     RNS_CUDA_OK(cudaGetLastError());

@@ -177,7 +177,7 @@ def test_quantizer_outputs(backend):
         scale = torch.empty(37 if per_row else 1, dtype=torch.float32, device="cuda")
         l1 = torch.empty(1, dtype=torch.int32, device="cuda")
         scratch = torch.empty(4, dtype=torch.int32, device="cuda")
-        N.check(lib.rns_quantize_activations(xd.data_ptr(), N.F16, 37, 192, 192, per_row, 127,
+        N.check(lib.rns_quantize_activations(xd.data_ptr(), N.F16, 37, 192, 192, 0, 0, per_row, 127,
                                              N.moduli_array(C0), 4, q.data_ptr(), planes.data_ptr(),
                                              scale.data_ptr(), l1.data_ptr(), scratch.data_ptr(),
                                              torch.cuda.current_stream().cuda_stream))

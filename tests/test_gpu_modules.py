@@ -54,7 +54,7 @@ def test_fused_qkv_bit_equals_three_layers(backend, tokens, activation_scale):
                                    per_row=activation_scale == "row")
         assert np.array_equal(expect.cpu().numpy(), res["y"])
         # and it is a faithful int8 approximation of the fp16 layer
-        ref = orig(x).float()
+        ref = orig(x).detach().float()
         assert float((expect.float() - ref).abs().max()) < 0.05
     backend.check_status()
 
@@ -84,7 +84,7 @@ def test_installed_fusion_in_attention_like_module(backend):
     # default moduli of the reference installer: dense_coprime -> (255,253,251,247)
     attention2 = Attention().eval()
     c2 = install_opt_qkv_fusion(attention2, backend=backend)
-    assert c2.projection.combined.moduli == (255, 253, 251, 247)
+    assert c2.projection.combined.moduli == (255, 253, 251)   # hidden 256: three moduli cover 2*256*127^2
     for g, e in zip(attention2(h), expected):
         assert float((g.float() - e).abs().max()) < 0.05
 
