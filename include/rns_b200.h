@@ -194,6 +194,19 @@ RNS_API int rns_matmul_centered_fused_out(const int8_t* d_a, const int8_t* d_b,
  * stride ldw): one byte per value whatever the channel count; their residues
  * are formed inside the kernel.
  *
+ * Packed tile layouts.  TMA moves a [rows x 64 B] box of a row-major matrix as
+ * one request per 64-byte row, which bounds the load rate far below what the
+ * tensor cores consume.  The packed layouts store every 64-byte-deep tile row
+ * block contiguously and already in the shared-memory (64-byte swizzled) image,
+ * so that one bulk copy fills a pipeline stage:
+ *   weights      [K_pad/64][N_pad][64]        N_pad = N rounded up to 384,
+ *   activations  [M_pad/128][K_pad/64][128][64]             (source integers)
+ *   planes       [M_pad/128][K_pad/64][channels][128][64]   M_pad = M up to 128,
+ * K_pad = K rounded up to 64 (the weight side is zero there).  Inside a 64-byte
+ * row the 16-byte chunk j of row r is stored at chunk j ^ ((r >> 1) & 3).
+ * rns_pack_weight / rns_quantize_activations / rns_encode_planes_packed write
+ * these layouts; lda, ldw and a_plane_stride are ignored for packed operands.
+ *
  * d_active_channels, when non-NULL, points to a device int c (2..channels):
  * only the first c moduli are used (adaptive prefix, backends/cuda_backend.py:
  * 573-622, decided on the device by rns_select_channels).
@@ -233,10 +246,38 @@ typedef struct rns_linear_args {
     const float* d_bias;      /* [N] or NULL */
     int32_t* d_status;
     int32_t tile_n;           /* 0 = choose; else 16..128, multiple of 16 */
-    int32_t tile_k;           /* 0 = choose; else 64 or 128 */
+    int32_t tile_k;           /* 0 = choose; else 64 or 128 (128: plain layouts only) */
+    int32_t a_packed;         /* 1: d_a / d_a_planes is in the packed tile layout */
+    int32_t w_packed;         /* 1: d_w is in the packed tile layout (rns_pack_weight) */
 } rns_linear_args;
 
 RNS_API int rns_linear_fused(const rns_linear_args* args, rns_stream_t stream);
+
+/* Bytes of the packed layouts (see rns_linear_args). */
+RNS_API int64_t rns_packed_weight_bytes(int n, int k);
+RNS_API int64_t rns_packed_activation_bytes(int m, int k, int channels /* 1 = source integers */);
+
+/*
+ * Repacks quantised weights d_w int8 [N,K] (row stride ldw) into the packed
+ * layout (zero padded), once per weight: the packed matrix replaces the plain
+ * one, so a cached weight still costs one byte per value.  No reference
+ * counterpart (the reference caches `channels` planes, backends/cuda_backend.py:
+ * 464-487).  rns_unpack_weight is the inverse, for callers that ask for the
+ * plain matrix or its planes again.
+ */
+RNS_API int rns_pack_weight(const int8_t* d_w, int n, int k, int64_t ldw, int8_t* d_packed,
+                            rns_stream_t stream);
+RNS_API int rns_unpack_weight(const int8_t* d_packed, int n, int k, int8_t* d_w, int64_t ldw,
+                              rns_stream_t stream);
+
+/*
+ * Centred planes of already-quantised activations d_a int8 [M,K] (row stride
+ * lda) in the packed planes layout: the activation encode of
+ * backends/cuda_backend.py:532 for the large-M path.
+ */
+RNS_API int rns_encode_planes_packed(const int8_t* d_a, int m, int k, int64_t lda,
+                                     const int32_t* moduli, int channels, int8_t* d_planes_packed,
+                                     rns_stream_t stream);
 
 /* 1 when rns_linear_fused accepts this problem, 0 when it would return
  * RNS_ERR_UNSUPPORTED (the role of CudaRNSBackend.cublas_compatible,
@@ -262,7 +303,8 @@ RNS_API int rns_linear_fused_supported(const int32_t* moduli, int channels, int 
  * of a column-sharded layer feeds the next layer without a transposing copy.
  * Outputs: d_q int8 [M,K]
  * (may be NULL when only planes are wanted), d_planes int8 [channels,M,K]
- * (NULL to skip), d_scale float [1] or [M], d_row_l1_max int32 [1] = max_m
+ * (NULL to skip) - both in the packed tile layouts of rns_linear_args when
+ * packed_out != 0 (sizes: rns_packed_activation_bytes) -, d_scale float [1] or [M], d_row_l1_max int32 [1] = max_m
  * sum_k |q[m,k]| (NULL to skip; input of rns_select_channels).
  * d_scratch: 16 bytes of device scratch owned by the caller's stream (used
  * only by the two-launch per-tensor path, M*K > 128 Ki elements).
@@ -273,7 +315,8 @@ RNS_API int rns_quantize_activations(const void* d_x, rns_float_type type,
                                      int col_block, int64_t col_block_stride,
                                      int per_row, int quant_max,
                                      const int32_t* moduli, int channels,
-                                     int8_t* d_q, int8_t* d_planes, float* d_scale,
+                                     int8_t* d_q, int8_t* d_planes, int packed_out,
+                                     float* d_scale,
                                      int32_t* d_row_l1_max, void* d_scratch,
                                      rns_stream_t stream);
 

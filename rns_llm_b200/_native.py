@@ -49,6 +49,8 @@ class LinearArgs(C.Structure):
         ("d_status", C.c_void_p),
         ("tile_n", C.c_int32),
         ("tile_k", C.c_int32),
+        ("a_packed", C.c_int32),
+        ("w_packed", C.c_int32),
     ]
 
 
@@ -72,7 +74,12 @@ SIGNATURES: dict[str, tuple] = {
     "rns_matmul_centered_fused_out": (C.c_int, [_VP, _VP, _I32P, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _VP, _VP, _VP]),
     "rns_linear_fused": (C.c_int, [C.POINTER(LinearArgs), _VP]),
     "rns_linear_fused_supported": (C.c_int, [_I32P, C.c_int, C.c_int, C.c_int64, C.c_int64]),
-    "rns_quantize_activations": (C.c_int, [_VP, C.c_int, C.c_int, C.c_int, C.c_int64, C.c_int, C.c_int64, C.c_int, C.c_int, _I32P, C.c_int, _VP, _VP, _VP, _VP, _VP, _VP]),
+    "rns_quantize_activations": (C.c_int, [_VP, C.c_int, C.c_int, C.c_int, C.c_int64, C.c_int, C.c_int64, C.c_int, C.c_int, _I32P, C.c_int, _VP, _VP, C.c_int, _VP, _VP, _VP, _VP]),
+    "rns_packed_weight_bytes": (C.c_int64, [C.c_int, C.c_int]),
+    "rns_packed_activation_bytes": (C.c_int64, [C.c_int, C.c_int, C.c_int]),
+    "rns_pack_weight": (C.c_int, [_VP, C.c_int, C.c_int, C.c_int64, _VP, _VP]),
+    "rns_unpack_weight": (C.c_int, [_VP, C.c_int, C.c_int, _VP, C.c_int64, _VP]),
+    "rns_encode_planes_packed": (C.c_int, [_VP, C.c_int, C.c_int, C.c_int64, _I32P, C.c_int, _VP, _VP]),
     "rns_row_l1_max_i8": (C.c_int, [_VP, C.c_int, C.c_int, C.c_int64, _VP, _VP]),
     "rns_select_channels": (C.c_int, [_VP, C.c_int32, _I32P, C.c_int, C.c_int, _VP, _VP, _VP, _VP, _VP]),
     "rns_quantize_weight": (C.c_int, [_VP, C.c_int, C.c_int, C.c_int, C.c_int64, C.c_int, _VP, _VP, _VP, _VP]),

@@ -70,41 +70,50 @@ class PreparedRNSWeight:
     """Cached Transformer weight ready for the RNS GEMM.
 
     Reference: ``PreparedRNSWeight`` (cuda_backend.py:68-76) holds residue
-    planes [R,K,N], R bytes per value.  Here ``weight_nk`` is the int8 matrix
-    [N,K] (kernel ``"tcgen05"``) and planes are never stored; ``residues``
-    builds them on first access for callers that read the attribute.  Sources
-    wider than int8, or moduli the packed encoder cannot fold in one step, use
-    kernel ``"planes"`` and keep real planes as the reference does.
+    planes [R,K,N], R bytes per value.  Here (kernel ``"tcgen05"``) the weight
+    is kept ONCE, as the quantised int8 matrix in the packed tile layout the
+    kernel's bulk copies read (``weight_packed``, one byte per value plus
+    padding of N to 384 and K to 64); planes are never stored.  ``weight_nk``
+    and ``residues`` rebuild the plain [N,K] matrix / the [R,K,N] planes on
+    access for callers that read those attributes.  Sources wider than int8, or
+    moduli the packed encoder cannot fold in one step, use the plane-level
+    kernels and keep real planes as the reference does.
     """
 
     def __init__(self, *, backend: "CudaRNSBackend", moduli: tuple[int, ...], k: int, n: int,
-                 kernel: str, weight_nk: torch.Tensor | None = None,
-                 weight_kn: torch.Tensor | None = None, residues: torch.Tensor | None = None) -> None:
+                 kernel: str, weight_packed: torch.Tensor | None = None,
+                 residues: torch.Tensor | None = None) -> None:
         self._backend = backend
         self.moduli = moduli
         self.k = int(k)
         self.n = int(n)
         self.kernel = kernel
-        self.weight_nk = weight_nk
-        self._weight_kn = weight_kn
+        self.weight_packed = weight_packed
         self._residues = residues
+
+    @property
+    def weight_nk(self) -> torch.Tensor | None:
+        """Plain int8 [N,K] copy of the packed weight (rebuilt on every access)."""
+        if self.weight_packed is None:
+            return None
+        return self._backend._unpack_weight(self.weight_packed, self.n, self.k)
 
     @property
     def residues(self) -> torch.Tensor:
         if self._residues is None:
-            kn = self._weight_kn if self._weight_kn is not None else self.weight_nk.t().contiguous()
-            self._residues = self._backend._encode_centered_raw(kn, self.moduli)
+            kn = self.weight_nk.t().contiguous()
+            return self._backend._encode_centered_raw(kn, self.moduli)
         return self._residues
 
     @property
     def device(self) -> torch.device:
-        return (self.weight_nk if self.weight_nk is not None else self._residues).device
+        return (self.weight_packed if self.weight_packed is not None else self._residues).device
 
     def prefix(self, channels: int, kernel: str) -> "PreparedRNSWeight":
         """The same weight restricted to the first ``channels`` moduli (no copy)."""
         return PreparedRNSWeight(
             backend=self._backend, moduli=self.moduli[:channels], k=self.k, n=self.n, kernel=kernel,
-            weight_nk=self.weight_nk, weight_kn=self._weight_kn,
+            weight_packed=self.weight_packed,
             residues=None if self._residues is None else self._residues[:channels],
         )
 
@@ -487,22 +496,43 @@ class CudaRNSBackend:
         mods, _ = self._mods(moduli)
         k, n = int(b.shape[0]), int(b.shape[1])
         if b.dtype == torch.int8 and self.tensor_core_compatible(k=k, moduli=mods):
-            return PreparedRNSWeight(backend=self, moduli=mods, k=k, n=n, kernel="tcgen05",
-                                     weight_nk=b.t().contiguous(), weight_kn=None)
+            return self.prepare_weight_nk(b.t(), mods)
         residues = self.encode_centered(b.contiguous(), mods)
         kernel = self.select_centered_kernel(k=k, n=n, moduli=mods, requested="auto", device=b.device)
         return PreparedRNSWeight(backend=self, moduli=mods, k=k, n=n, kernel=kernel, residues=residues)
 
+    def _pack_weight(self, w: torch.Tensor) -> torch.Tensor:
+        n, k = int(w.shape[0]), int(w.shape[1])
+        if w.stride(1) != 1 or (w.stride(0) % 16) or (w.data_ptr() % 16):
+            w = w.contiguous()
+        packed = torch.empty(int(self._lib.rns_packed_weight_bytes(n, k)), dtype=torch.int8, device=w.device)
+        with torch.cuda.device(w.device):
+            N.check(self._lib.rns_pack_weight(w.data_ptr(), n, k, w.stride(0), packed.data_ptr(),
+                                              self._stream(w.device)))
+        return packed
+
+    def _unpack_weight(self, packed: torch.Tensor, n: int, k: int) -> torch.Tensor:
+        w = torch.empty((n, k), dtype=torch.int8, device=packed.device)
+        with torch.cuda.device(packed.device):
+            N.check(self._lib.rns_unpack_weight(packed.data_ptr(), n, k, w.data_ptr(), k,
+                                                self._stream(packed.device)))
+        return w
+
     def prepare_weight_nk(self, w: torch.Tensor, moduli: Iterable[int]) -> PreparedRNSWeight:
-        """``w`` is int8 [N,K], the nn.Linear layout: no transpose, no copy."""
-        self._validate_matrix(w, "w", 2)
+        """``w`` is int8 [N,K] (the nn.Linear layout; any row stride).  The
+        prepared weight is its packed copy; ``w`` itself is not kept."""
+        if not w.is_cuda:
+            raise ValueError("w must be a CUDA tensor")
+        if w.ndim != 2:
+            raise ValueError("w must have rank 2")
         if w.dtype != torch.int8:
             raise ValueError("prepare_weight_nk expects int8")
         mods, _ = self._mods(moduli)
         n, k = int(w.shape[0]), int(w.shape[1])
         if not self.tensor_core_compatible(k=k, moduli=mods):
             return self.prepare_weight(w.t().contiguous(), mods)
-        return PreparedRNSWeight(backend=self, moduli=mods, k=k, n=n, kernel="tcgen05", weight_nk=w)
+        return PreparedRNSWeight(backend=self, moduli=mods, k=k, n=n, kernel="tcgen05",
+                                 weight_packed=self._pack_weight(w))
 
     def _check_activation(self, a: torch.Tensor, prepared: PreparedRNSWeight) -> None:
         self._validate_matrix(a, "a", 2)
@@ -526,12 +556,15 @@ class CudaRNSBackend:
         return self.decode(result, prepared_weight.moduli) if decode else result
 
     def _launch_fused(self, *, prepared: PreparedRNSWeight, m: int, a: torch.Tensor | None,
-                      a_planes: torch.Tensor | None, out: torch.Tensor,
+                      a_planes: torch.Tensor | None, out: torch.Tensor, a_packed: bool = False,
                       active: torch.Tensor | None = None, row_scale: torch.Tensor | None = None,
                       row_scale_stride: int = 0, col_scale: torch.Tensor | None = None,
-                      bias: torch.Tensor | None = None, tile_n: int = 0, tile_k: int = 0) -> None:
+                      bias: torch.Tensor | None = None, tile_n: int = 0, tile_k: int = 0,
+                      plain_weight: torch.Tensor | None = None) -> None:
+        """Fills ``rns_linear_args`` and launches.  ``a`` / ``a_planes`` are plain
+        ([M,K] / [R,M,K]) unless ``a_packed``; the weight is the prepared packed
+        copy unless ``plain_weight`` ([N,K] int8) is given."""
         mods = prepared.moduli
-        w = prepared.weight_nk
         args = N.LinearArgs()
         args.m, args.n, args.k = m, prepared.n, prepared.k
         args.channels = len(mods)
@@ -543,9 +576,17 @@ class CudaRNSBackend:
             args.a_plane_stride = m * prepared.k
         else:
             args.d_a = a.data_ptr()
-            args.lda = a.stride(0)
-        args.d_w = w.data_ptr()
-        args.ldw = w.stride(0)
+            args.lda = prepared.k if a_packed else a.stride(0)
+        args.a_packed = 1 if a_packed else 0
+        if plain_weight is not None:
+            args.d_w = plain_weight.data_ptr()
+            args.ldw = plain_weight.stride(0)
+            device = plain_weight.device
+        else:
+            args.d_w = prepared.weight_packed.data_ptr()
+            args.ldw = prepared.k
+            args.w_packed = 1
+            device = prepared.weight_packed.device
         args.d_active_channels = None if active is None else active.data_ptr()
         args.d_out = out.data_ptr()
         args.ldo = out.stride(0)
@@ -555,7 +596,6 @@ class CudaRNSBackend:
             args.row_scale_stride = row_scale_stride
             args.d_col_scale = col_scale.data_ptr()
             args.d_bias = None if bias is None else bias.data_ptr()
-        device = w.device
         args.d_status = self._state(device).status.data_ptr()
         args.tile_n, args.tile_k = tile_n, tile_k
         N.check(self._lib.rns_linear_fused(C.byref(args), self._stream(device)))
@@ -588,11 +628,13 @@ class CudaRNSBackend:
         with torch.cuda.device(a.device):
             if m >= PLANES_MIN_ROWS:
                 frame = self.arena.frame(a.device)
-                planes = frame.alloc((channels, m, prepared_weight.k), torch.int8)
+                planes = frame.alloc(int(self._lib.rns_packed_activation_bytes(m, prepared_weight.k, channels)),
+                                     torch.int8)
                 _, arr = self._mods(mods)
-                N.check(self._lib.rns_encode_centered(a.data_ptr(), N.INT8, a.numel(), arr, channels,
-                                                      planes.data_ptr(), self._stream(a.device)))
-                self._launch_fused(prepared=prepared_weight, m=m, a=None, a_planes=planes,
+                N.check(self._lib.rns_encode_planes_packed(a.data_ptr(), m, prepared_weight.k, a.stride(0),
+                                                           arr, channels, planes.data_ptr(),
+                                                           self._stream(a.device)))
+                self._launch_fused(prepared=prepared_weight, m=m, a=None, a_planes=planes, a_packed=True,
                                    out=workspace.output, active=_active)
             else:
                 self._launch_fused(prepared=prepared_weight, m=m, a=a, a_planes=None,
@@ -771,11 +813,12 @@ class CudaRNSBackend:
         if x.dtype not in _FLOAT_TYPES:
             raise ValueError("x must be float16, bfloat16 or float32")
         if x.ndim == 3:
-            # [G, M, K/G] contiguous: what an all-gather of G column shards produces.
-            if not x.is_contiguous():
-                raise ValueError("a gathered activation [G,M,K/G] must be contiguous")
+            # [G, M, K/G]: what an all-gather of G column shards produces (or a
+            # column-block view of it); only the innermost stride must be 1.
+            if x.stride(2) != 1:
+                raise ValueError("a gathered activation [G,M,K/G] needs unit inner stride")
             blocks, m, col_block = (int(v) for v in x.shape)
-            k, ldx, col_block_stride = blocks * col_block, col_block, m * col_block
+            k, ldx, col_block_stride = blocks * col_block, int(x.stride(1)), int(x.stride(0))
         elif x.ndim == 2 and x.stride(1) == 1:
             m, k = int(x.shape[0]), int(x.shape[1])
             ldx, col_block, col_block_stride = int(x.stride(0)), 0, 0
@@ -796,14 +839,16 @@ class CudaRNSBackend:
             frame = self.arena.frame(device)
             scale = frame.alloc(m if per_row else 1, torch.float32)
             scratch = frame.alloc(8, torch.int32)   # [0..3] absmax scratch, [4] row-L1 max, [5] active
-            q = None if use_planes else frame.alloc((m, k), torch.int8)
-            planes = frame.alloc((channels, m, k), torch.int8) if use_planes else None
+            q = None if use_planes else frame.alloc(
+                int(self._lib.rns_packed_activation_bytes(m, k, 1)), torch.int8)
+            planes = frame.alloc(int(self._lib.rns_packed_activation_bytes(m, k, channels)),
+                                 torch.int8) if use_planes else None
             stream = self._stream(device)
             N.check(self._lib.rns_quantize_activations(
                 x.data_ptr(), _FLOAT_TYPES[x.dtype], m, k, ldx, col_block, col_block_stride,
                 1 if per_row else 0, 127,
                 arr, channels, None if q is None else q.data_ptr(),
-                None if planes is None else planes.data_ptr(), scale.data_ptr(),
+                None if planes is None else planes.data_ptr(), 1, scale.data_ptr(),
                 scratch.data_ptr() + 16 if adaptive is not None else None,
                 scratch.data_ptr(), stream))
             active = None
@@ -824,7 +869,7 @@ class CudaRNSBackend:
             if adaptive is None:
                 self._stats[f"fused_gemm_channels_{channels}"] += 1
             self._launch_fused(prepared=prepared if adaptive is None else adaptive.variants[channels],
-                               m=m, a=q, a_planes=planes, out=out, active=active,
+                               m=m, a=q, a_planes=planes, a_packed=True, out=out, active=active,
                                row_scale=scale, row_scale_stride=1 if per_row else 0,
                                col_scale=weight_scale, bias=bias)
         if return_metadata:

@@ -250,8 +250,11 @@ struct QuantOut {
     int* row_l1_max;  // [1] or NULL
     int32_t channels;
     int32_t mod[kMaxCh];
-    uint32_t enc_hi[kMaxCh], enc_lo[kMaxCh];
+    uint32_t enc_hi[kMaxCh], enc_lo[kMaxCh], enc_mk[kMaxCh];
     int32_t single_fold;
+    int32_t fast;
+    int32_t packed;     // outputs in the packed tile layouts
+    int32_t kblocks;    // K_pad / 64 (packed only)
 };
 
 // Quantises columns [c, c+8) of row r, stores values and planes, returns sum |q|.
@@ -267,7 +270,6 @@ __device__ __forceinline__ int quantize_group(const SrcView& s, const QuantOut& 
         q[i] = quantize_one(v[i], scale, qmax);
         l1 += q[i] < 0 ? -q[i] : q[i];
     }
-    const int64_t off = (int64_t)r * s.k + c;
     const bool full = c + 8 <= s.k;
     uint32_t w0 = 0, w1 = 0;
 #pragma unroll
@@ -275,34 +277,39 @@ __device__ __forceinline__ int quantize_group(const SrcView& s, const QuantOut& 
         w0 |= (uint32_t)(q[i] & 0xff) << (8 * i);
         w1 |= (uint32_t)(q[4 + i] & 0xff) << (8 * i);
     }
+    // Plain: byte offset r*K + c, planes M*K apart.  Packed: tile layouts, where a
+    // group of 8 columns (c % 8 == 0) is half of one 16-byte chunk.
+    const int64_t off = o.packed ? packed_act_offset(r, c, 0, 1, o.kblocks) : (int64_t)r * s.k + c;
     if (full && (off & 7) == 0) {
         if (o.q) *reinterpret_cast<uint2*>(o.q + off) = make_uint2(w0, w1);
         if (o.planes) {
-            const int64_t plane = (int64_t)s.m * s.k;
-            if (o.single_fold) {
-                const uint32_t u0 = w0 ^ 0x80808080u, u1 = w1 ^ 0x80808080u;
-                const uint32_t l0 = u0 & 0x7f7f7f7fu, l1w = u1 & 0x7f7f7f7fu;
+            const int64_t plane = o.packed ? (int64_t)kPackM * kPackK : (int64_t)s.m * s.k;
+            const int64_t base = o.packed ? packed_act_offset(r, c, 0, o.channels, o.kblocks) : off;
+            const uint32_t u0 = w0 ^ 0x80808080u, u1 = w1 ^ 0x80808080u;
+            const uint32_t l0 = u0 & 0x7f7f7f7fu, l1w = u1 & 0x7f7f7f7fu;
 #pragma unroll 1
-                for (int ch = 0; ch < o.channels; ++ch) {
-                    const uint32_t m = (uint32_t)o.mod[ch];
-                    *reinterpret_cast<uint2*>(o.planes + ch * plane + off) =
-                        make_uint2(encode_word(u0, l0, o.enc_hi[ch], o.enc_lo[ch], m),
-                                   encode_word(u1, l1w, o.enc_hi[ch], o.enc_lo[ch], m));
-                }
-            } else {
-#pragma unroll 1
-                for (int ch = 0; ch < o.channels; ++ch) {
+            for (int ch = 0; ch < o.channels; ++ch) {
+                uint2 e;
+                if (o.single_fold && o.fast) {
+                    e = make_uint2(encode_word<true>(u0, l0, o.enc_hi[ch], o.enc_lo[ch], o.enc_mk[ch]),
+                                   encode_word<true>(u1, l1w, o.enc_hi[ch], o.enc_lo[ch], o.enc_mk[ch]));
+                } else if (o.single_fold) {
+                    e = make_uint2(encode_word<false>(u0, l0, o.enc_hi[ch], o.enc_lo[ch], o.enc_mk[ch]),
+                                   encode_word<false>(u1, l1w, o.enc_hi[ch], o.enc_lo[ch], o.enc_mk[ch]));
+                } else {
                     uint32_t e0 = 0, e1 = 0;
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
                         e0 |= (uint32_t)(centred_residue(q[i], o.mod[ch]) & 0xff) << (8 * i);
                         e1 |= (uint32_t)(centred_residue(q[4 + i], o.mod[ch]) & 0xff) << (8 * i);
                     }
-                    *reinterpret_cast<uint2*>(o.planes + ch * plane + off) = make_uint2(e0, e1);
+                    e = make_uint2(e0, e1);
                 }
+                *reinterpret_cast<uint2*>(o.planes + base + ch * plane) = e;
             }
         }
     } else {
+        // ragged tail or unaligned output: plain layout only (the packed layout needs K % 8 == 0)
         for (int i = 0; i < 8 && c + i < s.k; ++i) {
             if (o.q) o.q[off + i] = (int8_t)q[i];
             if (o.planes)
@@ -501,6 +508,97 @@ quantize_weight_kernel(const T* __restrict__ w, int n, int k, int64_t ldw, int q
     }
 }
 
+
+// ---------------------------------------------------------------------------
+// Packed tile layouts
+// ---------------------------------------------------------------------------
+// One thread per 16-byte chunk of the packed weight [K_pad/64][N_pad][64].
+template <bool UNPACK>
+__global__ void __launch_bounds__(256)
+pack_weight_kernel(int8_t* __restrict__ plain, int8_t* __restrict__ packed, int n, int k, int64_t ldw,
+                   int64_t n_pad, int kblocks) {
+    const int64_t chunks = (int64_t)kblocks * n_pad * 4;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < chunks;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        const int chunk = (int)(i & 3);
+        const int64_t row_id = i >> 2;
+        const int row = (int)(row_id % n_pad);
+        const int kb = (int)(row_id / n_pad);
+        const int col = kb * kPackK + chunk * 16;
+        int8_t* pk = packed + packed_weight_offset(row, col, n_pad);
+        if (UNPACK) {
+            if (row < n)
+                for (int j = 0; j < 16 && col + j < k; ++j) plain[(int64_t)row * ldw + col + j] = pk[j];
+        } else {
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (row < n && col < k) {
+                const int8_t* src = plain + (int64_t)row * ldw + col;
+                if (col + 16 <= k && (reinterpret_cast<uintptr_t>(src) & 15) == 0) {
+                    v = *reinterpret_cast<const uint4*>(src);
+                } else {
+                    int8_t tmp[16] = {0};
+                    for (int j = 0; j < 16 && col + j < k; ++j) tmp[j] = src[j];
+                    v = *reinterpret_cast<const uint4*>(tmp);
+                }
+            }
+            *reinterpret_cast<uint4*>(pk) = v;
+        }
+    }
+}
+
+// One thread per 16-byte chunk of the source activations; writes every channel.
+__global__ void __launch_bounds__(256)
+encode_planes_packed_kernel(const int8_t* __restrict__ a, int m, int k, int64_t lda, QuantOut o) {
+    const int chunks_per_row = (k + 15) / 16;
+    const int64_t chunks = (int64_t)m * chunks_per_row;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < chunks;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        const int row = (int)(i / chunks_per_row);
+        const int col = (int)(i - (int64_t)row * chunks_per_row) * 16;
+        const int8_t* src = a + (int64_t)row * lda + col;
+        uint4 x;
+        if (col + 16 <= k && (reinterpret_cast<uintptr_t>(src) & 15) == 0) {
+            x = *reinterpret_cast<const uint4*>(src);
+        } else {
+            int8_t tmp[16] = {0};
+            for (int j = 0; j < 16 && col + j < k; ++j) tmp[j] = src[j];
+            x = *reinterpret_cast<const uint4*>(tmp);
+        }
+        const uint32_t w[4] = {x.x, x.y, x.z, x.w};
+        const int64_t base = packed_act_offset(row, col, 0, o.channels, o.kblocks);
+#pragma unroll 1
+        for (int ch = 0; ch < o.channels; ++ch) {
+            uint32_t e[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const uint32_t u = w[j] ^ 0x80808080u, ul = w[j] & 0x7f7f7f7fu;
+                if (o.single_fold && o.fast) e[j] = encode_word<true>(u, ul, o.enc_hi[ch], o.enc_lo[ch], o.enc_mk[ch]);
+                else if (o.single_fold) e[j] = encode_word<false>(u, ul, o.enc_hi[ch], o.enc_lo[ch], o.enc_mk[ch]);
+                else {
+                    e[j] = 0;
+                    for (int b = 0; b < 4; ++b)
+                        e[j] |= (uint32_t)(centred_residue((int)(int8_t)(w[j] >> (8 * b)), o.mod[ch]) & 0xff) << (8 * b);
+                }
+            }
+            *reinterpret_cast<uint4*>(o.planes + base + (int64_t)ch * kPackM * kPackK) =
+                make_uint4(e[0], e[1], e[2], e[3]);
+        }
+    }
+}
+
+static int fill_encoder(QuantOut& qo, const int32_t* moduli, int channels) {
+    Plan pl;
+    if (int rc = build_plan(moduli, channels, &pl)) return rc;
+    qo.channels = pl.channels;
+    qo.single_fold = pl.encode_single_fold;
+    qo.fast = pl.encode_fast;
+    for (int i = 0; i < kMaxCh; ++i) {
+        qo.mod[i] = pl.mod[i]; qo.enc_hi[i] = pl.enc_hi[i]; qo.enc_lo[i] = pl.enc_lo[i];
+        qo.enc_mk[i] = pl.enc_mk[i];
+    }
+    return RNS_OK;
+}
+
 static int check_gemm_dims(const void* a, const void* b, const void* out, int m, int k, int n) {
     if (!a || !b || !out) return fail(RNS_ERR_INVALID_ARGUMENT, "plane GEMM: NULL pointer");
     if (m <= 0 || k <= 0 || n <= 0)
@@ -628,7 +726,7 @@ int rns_matmul_centered_fused_out(const int8_t* d_a, const int8_t* d_b, const in
 int rns_quantize_activations(const void* d_x, rns_float_type type, int m, int k, int64_t ldx,
                              int col_block, int64_t col_block_stride,
                              int per_row, int quant_max, const int32_t* moduli, int channels,
-                             int8_t* d_q, int8_t* d_planes, float* d_scale,
+                             int8_t* d_q, int8_t* d_planes, int packed_out, float* d_scale,
                              int32_t* d_row_l1_max, void* d_scratch, rns_stream_t stream) {
     if (!d_x || !d_scale || (!d_q && !d_planes))
         return fail(RNS_ERR_INVALID_ARGUMENT, "quantize: NULL pointer");
@@ -640,17 +738,14 @@ int rns_quantize_activations(const void* d_x, rns_float_type type, int m, int k,
     const bool small = !per_row && (int64_t)m * k <= 128 * 1024;
     if (!per_row && !small && !d_scratch)
         return fail(RNS_ERR_INVALID_ARGUMENT, "quantize: per-tensor scale needs d_scratch");
+    if (packed_out && k % 8 != 0)
+        return fail(RNS_ERR_INVALID_ARGUMENT, "quantize: the packed layout needs K % 8 == 0");
     QuantOut qo{};
     qo.q = d_q; qo.planes = d_planes; qo.scale = d_scale; qo.row_l1_max = d_row_l1_max;
-    if (d_planes) {
-        Plan pl;
-        if (int rc = build_plan(moduli, channels, &pl)) return rc;
-        qo.channels = pl.channels;
-        qo.single_fold = pl.encode_single_fold;
-        for (int i = 0; i < kMaxCh; ++i) {
-            qo.mod[i] = pl.mod[i]; qo.enc_hi[i] = pl.enc_hi[i]; qo.enc_lo[i] = pl.enc_lo[i];
-        }
-    }
+    qo.packed = packed_out ? 1 : 0;
+    qo.kblocks = (k + kPackK - 1) / kPackK;
+    if (d_planes)
+        if (int rc = fill_encoder(qo, moduli, channels)) return rc;
     size_t esize = 2;
     if (type == RNS_F32) esize = 4;
     else if (type != RNS_F16 && type != RNS_BF16)
@@ -686,6 +781,54 @@ int rns_quantize_activations(const void* d_x, rns_float_type type, int m, int k,
         default: RNS_QUANT(float); break;
     }
 #undef RNS_QUANT
+    RNS_CUDA_OK(cudaGetLastError());
+    return RNS_OK;
+}
+
+int64_t rns_packed_weight_bytes(int n, int k) {
+    if (n <= 0 || k <= 0) return 0;
+    return round_up_i64(k, kPackK) * round_up_i64(n, kPackNPad);
+}
+
+int64_t rns_packed_activation_bytes(int m, int k, int channels) {
+    if (m <= 0 || k <= 0 || channels <= 0) return 0;
+    return round_up_i64(m, kPackM) * round_up_i64(k, kPackK) * channels;
+}
+
+int rns_pack_weight(const int8_t* d_w, int n, int k, int64_t ldw, int8_t* d_packed, rns_stream_t stream) {
+    if (!d_w || !d_packed) return fail(RNS_ERR_INVALID_ARGUMENT, "pack_weight: NULL pointer");
+    if (n <= 0 || k <= 0 || ldw < k) return fail(RNS_ERR_INVALID_ARGUMENT, "pack_weight: bad shape or stride");
+    const int64_t n_pad = round_up_i64(n, kPackNPad);
+    const int kblocks = (k + kPackK - 1) / kPackK;
+    pack_weight_kernel<false><<<grid_for(n_pad * kblocks * 4, 256), 256, 0, as_stream(stream)>>>(
+        const_cast<int8_t*>(d_w), d_packed, n, k, ldw, n_pad, kblocks);
+    RNS_CUDA_OK(cudaGetLastError());
+    return RNS_OK;
+}
+
+int rns_unpack_weight(const int8_t* d_packed, int n, int k, int8_t* d_w, int64_t ldw, rns_stream_t stream) {
+    if (!d_w || !d_packed) return fail(RNS_ERR_INVALID_ARGUMENT, "unpack_weight: NULL pointer");
+    if (n <= 0 || k <= 0 || ldw < k) return fail(RNS_ERR_INVALID_ARGUMENT, "unpack_weight: bad shape or stride");
+    const int64_t n_pad = round_up_i64(n, kPackNPad);
+    const int kblocks = (k + kPackK - 1) / kPackK;
+    pack_weight_kernel<true><<<grid_for(n_pad * kblocks * 4, 256), 256, 0, as_stream(stream)>>>(
+        d_w, const_cast<int8_t*>(d_packed), n, k, ldw, n_pad, kblocks);
+    RNS_CUDA_OK(cudaGetLastError());
+    return RNS_OK;
+}
+
+int rns_encode_planes_packed(const int8_t* d_a, int m, int k, int64_t lda, const int32_t* moduli,
+                             int channels, int8_t* d_planes_packed, rns_stream_t stream) {
+    if (!d_a || !d_planes_packed) return fail(RNS_ERR_INVALID_ARGUMENT, "encode_planes_packed: NULL pointer");
+    if (m <= 0 || k <= 0 || lda < k)
+        return fail(RNS_ERR_INVALID_ARGUMENT, "encode_planes_packed: bad shape or stride");
+    QuantOut qo{};
+    if (int rc = fill_encoder(qo, moduli, channels)) return rc;
+    qo.planes = d_planes_packed;
+    qo.packed = 1;
+    qo.kblocks = (k + kPackK - 1) / kPackK;
+    encode_planes_packed_kernel<<<grid_for((int64_t)m * ((k + 15) / 16), 256), 256, 0, as_stream(stream)>>>(
+        d_a, m, k, lda, qo);
     RNS_CUDA_OK(cudaGetLastError());
     return RNS_OK;
 }

@@ -58,8 +58,35 @@ struct Plan {
     // enc_hi = 127 - floor(m/2), enc_lo = floor(m/2), replicated four times.
     uint32_t enc_hi[kMaxCh];
     uint32_t enc_lo[kMaxCh];
+    uint32_t enc_mk[kMaxCh];       // m << 25 when encode_fast, else m
+    int32_t encode_fast;           // every modulus < 128
     int32_t encode_single_fold;    // every modulus >= 86
 };
+
+// Packed tile layouts (see rns_linear_args in the public header).
+constexpr int kPackK = 64;     // bytes of K per packed row
+constexpr int kPackM = 128;    // activation rows per packed tile
+constexpr int kPackNPad = 384; // weight rows are padded to a multiple of this
+
+#ifdef __CUDACC__
+#define RNS_HD_INLINE __host__ __device__ __forceinline__
+#else
+#define RNS_HD_INLINE inline
+#endif
+RNS_HD_INLINE int64_t round_up_i64(int64_t v, int64_t q) { return (v + q - 1) / q * q; }
+// Offset inside one [rows][64] packed block of byte `col` (0..63) of row `row`.
+RNS_HD_INLINE int packed_row_offset(int row, int col) {
+    return row * kPackK + ((((col >> 4) ^ ((row >> 1) & 3)) << 4) | (col & 15));
+}
+// Weight byte (n, k) -> offset in [K_pad/64][N_pad][64].
+RNS_HD_INLINE int64_t packed_weight_offset(int n, int k, int64_t n_pad) {
+    return ((int64_t)(k >> 6) * n_pad) * kPackK + packed_row_offset(n, k & 63);
+}
+// Activation byte (m, k) of channel c -> offset in [M_pad/128][K_pad/64][channels][128][64].
+RNS_HD_INLINE int64_t packed_act_offset(int m, int k, int c, int channels, int64_t kblocks) {
+    const int64_t tile = ((int64_t)(m >> 7) * kblocks + (k >> 6)) * channels + c;
+    return tile * (kPackM * kPackK) + packed_row_offset(m & 127, k & 63);
+}
 
 // Builds the plan; returns an rns_status.  Pure host arithmetic.
 int build_plan(const int32_t* moduli, int channels, Plan* out);
@@ -197,20 +224,35 @@ RNS_HD int reconstruct32(const int (&acc)[R], const Plan& pl, int active) {
     return sx;
 }
 
+RNS_HD uint32_t mul_hi_u32(uint32_t a, uint32_t b) {
+#ifdef __CUDA_ARCH__
+    return __umulhi(a, b);
+#else
+    return (uint32_t)(((unsigned long long)a * (unsigned long long)b) >> 32);
+#endif
+}
+
 // Centred residues of four packed int8 values for one modulus (single fold;
 // requires m >= 86).  u = bytes biased by 128, ul = u with the top bit of each
 // byte cleared, hi/lo = Plan::enc_hi/enc_lo.  Bit 7 of (ul + hi) & u is set
 // where x > floor(m/2); bit 7 of ~((ul + lo) | u) where x < -floor(m/2).  The
-// biased result never leaves [0,255] per byte, so one 32-bit multiply-add
-// applies all four folds.  -m/2 of an even modulus is kept negative, as the
-// reference's device encoder does (csrc/rns_cuda.cu:116-122).
-RNS_HD uint32_t encode_word(uint32_t u, uint32_t ul, uint32_t hi, uint32_t lo, uint32_t m) {
+// biased result never leaves [0,255] per byte, so 32-bit arithmetic applies all
+// four folds without carries between bytes.  -m/2 of an even modulus is kept
+// negative, as the reference's device encoder does (csrc/rns_cuda.cu:116-122).
+//
+// Two forms of the last step.  FAST (every modulus < 128, mk = m << 25):
+// mulhi(mask, mk) turns each set bit 8i+7 into m << 8i; the multiplies run on
+// the FMA pipe and leave the integer ALU (half rate on this architecture) the
+// two logic operations.  Otherwise the masks are shifted down and multiplied by
+// m (mk = m).
+template <bool FAST>
+RNS_HD uint32_t encode_word(uint32_t u, uint32_t ul, uint32_t hi, uint32_t lo, uint32_t mk) {
     const uint32_t down = (ul + hi) & u & 0x80808080u;
     const uint32_t up = ~((ul + lo) | u) & 0x80808080u;
-    const uint32_t delta = (up >> 7) - (down >> 7);
-    return (u + delta * m) ^ 0x80808080u;
+    uint32_t v;
+    if (FAST) v = mul_hi_u32(up, mk) + u - mul_hi_u32(down, mk);
+    else v = u + ((up >> 7) - (down >> 7)) * mk;
+    return v ^ 0x80808080u;
 }
-
-
 
 }  // namespace rns

@@ -3,10 +3,10 @@
 // epilogue with modular reduction, mixed-radix reconstruction, recentring and
 // dequantisation.  One CTA computes one 128 x tile_n output tile.
 //
-// Warp roles (320 threads):
+// Warp roles (576 threads):
 //   warp 0      TMA producer (one elected lane)
 //   warp 1      TMEM owner + MMA issuer (one elected lane)
-//   warps 2..9  encoders during the K loop, epilogue afterwards
+//   warps 2..17 encoders during the K loop, epilogue afterwards
 //
 // Per pipeline stage the shared memory holds
 //   raw  : source bytes as TMA delivers them (W tile, and the A tile when the
@@ -33,8 +33,8 @@
 namespace rns {
 
 constexpr int kTileM = 128;
-constexpr int kThreads = 320;
-constexpr int kWorkerWarps = 8;
+constexpr int kWorkerWarps = 16;
+constexpr int kThreads = 64 + kWorkerWarps * 32;
 constexpr int kWorkerThreads = kWorkerWarps * 32;
 constexpr int kMaxStages = 6;
 constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s
@@ -45,6 +45,10 @@ struct GemmParams {
     int32_t tile_n, tile_k;      // tile_k in {64,128}
     int32_t stages;
     int32_t a_is_planes;
+    int32_t a_packed, w_packed;   // operands in the packed tile layouts (bulk copies)
+    const int8_t* a_ptr;          // packed activations / planes
+    const int8_t* w_ptr;          // packed weights
+    int64_t w_npad;               // padded weight rows of the packed layout
     int32_t tmem_cols;
     const int32_t* active_ptr;
     void* out;
@@ -109,6 +113,12 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
         "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes"
         " [%0], [%1, {%3, %4, %5}], [%2];"
         ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "r"(z)
+        : "memory");
+}
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+        ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
         : "memory");
 }
 __device__ __forceinline__ void tmem_alloc(uint32_t holder_smem, uint32_t cols) {
@@ -191,6 +201,34 @@ __device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity, vola
     }
 }
 
+// Encodes the 16-byte chunks [wt, wt+kWorkerThreads, ...) of one raw tile into
+// the R operand tiles.  ALL: every channel is active (no per-channel branch).
+template <int R, bool FAST, bool ALL>
+__device__ __forceinline__ void encode_chunks(const uint8_t* raw, uint8_t* enc, uint32_t tile_bytes,
+                                              int chunks, int wt, int active,
+                                              const uint32_t (&enc_hi)[R], const uint32_t (&enc_lo)[R],
+                                              const uint32_t (&enc_mk)[R]) {
+    for (int ch = wt; ch < chunks; ch += kWorkerThreads) {
+        const uint4 x = *reinterpret_cast<const uint4*>(raw + ch * 16);
+        const uint32_t u0 = x.x ^ 0x80808080u, u1 = x.y ^ 0x80808080u;
+        const uint32_t u2 = x.z ^ 0x80808080u, u3 = x.w ^ 0x80808080u;
+        const uint32_t l0 = x.x & 0x7f7f7f7fu, l1 = x.y & 0x7f7f7f7fu;
+        const uint32_t l2 = x.z & 0x7f7f7f7fu, l3 = x.w & 0x7f7f7f7fu;
+        uint8_t* dst = enc + ch * 16;
+#pragma unroll
+        for (int c = 0; c < R; ++c) {
+            if (ALL || c < active) {
+                uint4 y;
+                y.x = encode_word<FAST>(u0, l0, enc_hi[c], enc_lo[c], enc_mk[c]);
+                y.y = encode_word<FAST>(u1, l1, enc_hi[c], enc_lo[c], enc_mk[c]);
+                y.z = encode_word<FAST>(u2, l2, enc_hi[c], enc_lo[c], enc_mk[c]);
+                y.w = encode_word<FAST>(u3, l3, enc_hi[c], enc_lo[c], enc_mk[c]);
+                *reinterpret_cast<uint4*>(dst + (size_t)c * tile_bytes) = y;
+            }
+        }
+    }
+}
+
 struct __align__(8) SharedCtl {
     uint64_t full_raw[kMaxStages];
     uint64_t empty_raw[kMaxStages];
@@ -259,16 +297,29 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 if (round > 0 && !wait_bounded(smem_addr(&ctl.empty_raw[s]), (round - 1) & 1, abort)) break;
                 const uint32_t fr = smem_addr(&ctl.full_raw[s]);
                 mbar_arrive_expect_tx(fr, raw_bytes);
-                tma_load_2d(stage + p.off_raw_w, &map_w, fr, kb * p.tile_k, n0);
+                if (p.w_packed)
+                    bulk_load(stage + p.off_raw_w,
+                              p.w_ptr + ((int64_t)kb * p.w_npad + n0) * kPackK, p.tile_w_bytes, fr);
+                else
+                    tma_load_2d(stage + p.off_raw_w, &map_w, fr, kb * p.tile_k, n0);
+                const int64_t a_tile = (int64_t)blockIdx.y * kblocks + kb;   // packed tile index
                 if (!a_planes) {
-                    tma_load_2d(stage + p.off_raw_a, &map_a, fr, kb * p.tile_k, m0);
+                    if (p.a_packed)
+                        bulk_load(stage + p.off_raw_a, p.a_ptr + a_tile * (kPackM * kPackK), p.tile_a_bytes, fr);
+                    else
+                        tma_load_2d(stage + p.off_raw_a, &map_a, fr, kb * p.tile_k, m0);
                 } else {
                     if (round > 0 && !wait_bounded(smem_addr(&ctl.empty_enc[s]), (round - 1) & 1, abort)) break;
                     const uint32_t fe = smem_addr(&ctl.full_enc[s]);
                     mbar_arrive_expect_tx(fe, (uint32_t)active * p.tile_a_bytes);
-                    for (int c = 0; c < active; ++c)
-                        tma_load_3d(stage + p.off_enc_a + (uint32_t)c * p.tile_a_bytes, &map_a, fe,
-                                    kb * p.tile_k, m0, c);
+                    if (p.a_packed) {
+                        bulk_load(stage + p.off_enc_a, p.a_ptr + a_tile * ((int64_t)R * kPackM * kPackK),
+                                  (uint32_t)active * p.tile_a_bytes, fe);
+                    } else {
+                        for (int c = 0; c < active; ++c)
+                            tma_load_3d(stage + p.off_enc_a + (uint32_t)c * p.tile_a_bytes, &map_a, fe,
+                                        kb * p.tile_k, m0, c);
+                    }
                 }
             }
         }
@@ -309,6 +360,12 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         // of a tile in every swizzle mode).
         const int chunks_a = a_planes ? 0 : rows_a * (p.tile_k / 16);
         const int chunks_w = rows_w * (p.tile_k / 16);
+        uint32_t enc_hi[R], enc_lo[R], enc_mk[R];
+#pragma unroll
+        for (int c = 0; c < R; ++c) {
+            enc_hi[c] = p.plan.enc_hi[c]; enc_lo[c] = p.plan.enc_lo[c]; enc_mk[c] = p.plan.enc_mk[c];
+        }
+        const bool fast = p.plan.encode_fast != 0;
         bool ok = true;
         for (int kb = 0; kb < kblocks && ok; ++kb) {
             const int s = kb % stages;
@@ -322,26 +379,12 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 const uint8_t* raw = stage + (part == 0 ? p.off_raw_w : p.off_raw_a);
                 uint8_t* enc = stage + (part == 0 ? p.off_enc_w : p.off_enc_a);
                 const uint32_t tile_bytes = part == 0 ? p.tile_w_bytes : p.tile_a_bytes;
-                for (int ch = wt; ch < chunks; ch += kWorkerThreads) {
-                    const uint4 x = *reinterpret_cast<const uint4*>(raw + ch * 16);
-                    const uint32_t u0 = x.x ^ 0x80808080u, u1 = x.y ^ 0x80808080u;
-                    const uint32_t u2 = x.z ^ 0x80808080u, u3 = x.w ^ 0x80808080u;
-                    const uint32_t l0 = u0 & 0x7f7f7f7fu, l1 = u1 & 0x7f7f7f7fu;
-                    const uint32_t l2 = u2 & 0x7f7f7f7fu, l3 = u3 & 0x7f7f7f7fu;
-#pragma unroll
-                    for (int c = 0; c < R; ++c) {
-                        if (c < active) {
-                            const uint32_t hi = p.plan.enc_hi[c], lo = p.plan.enc_lo[c];
-                            const uint32_t m = (uint32_t)p.plan.mod[c];
-                            uint4 y;
-                            y.x = encode_word(u0, l0, hi, lo, m);
-                            y.y = encode_word(u1, l1, hi, lo, m);
-                            y.z = encode_word(u2, l2, hi, lo, m);
-                            y.w = encode_word(u3, l3, hi, lo, m);
-                            *reinterpret_cast<uint4*>(enc + (size_t)c * tile_bytes + ch * 16) = y;
-                        }
-                    }
-                }
+                if (fast && active == R)
+                    encode_chunks<R, true, true>(raw, enc, tile_bytes, chunks, wt, active, enc_hi, enc_lo, enc_mk);
+                else if (fast)
+                    encode_chunks<R, true, false>(raw, enc, tile_bytes, chunks, wt, active, enc_hi, enc_lo, enc_mk);
+                else
+                    encode_chunks<R, false, false>(raw, enc, tile_bytes, chunks, wt, active, enc_hi, enc_lo, enc_mk);
             }
             fence_proxy_async_smem();
             mbar_arrive(smem_addr(&ctl.full_enc[s]));
@@ -353,18 +396,15 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         if (ok) {
             tc_fence_after();
             const int quarter = warp & 3;             // TMEM lanes 32*quarter .. +31
-            const int half_id = (warp - 2) >> 2;      // which half of the tile's columns
+            const int part = (warp - 2) >> 2;         // 8-column chunks are dealt round-robin
             const int row = m0 + quarter * 32 + lane;
-            const int cols_per_half = p.tile_n / 2;   // tile_n is a multiple of 16
-            const int col_begin = half_id * cols_per_half;
             const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
             float rs = 0.0f;
             const bool is_float = p.out_type >= RNS_OUT_F16;
             if (is_float && row < p.m) rs = p.row_scale[(int64_t)row * p.row_scale_stride];
             using XInt = typename std::conditional<(R <= 4), int, long long>::type;
-            for (int cc = 0; cc < cols_per_half; cc += 8) {
+            for (int col = part * 8; col < p.tile_n; col += (kWorkerWarps / 4) * 8) {
                 __syncwarp();  // the tensor-memory loads below are warp-collective
-                const int col = col_begin + cc;
                 int acc[R][8];
 #pragma unroll
                 for (int c = 0; c < R; ++c) {
@@ -552,10 +592,11 @@ int rns_linear_fused(const rns_linear_args* a, rns_stream_t stream) {
     if ((a->d_a == nullptr) == (a->d_a_planes == nullptr))
         return fail(RNS_ERR_INVALID_ARGUMENT, "give exactly one of d_a and d_a_planes");
     if (!a->d_w || !a->d_out) return fail(RNS_ERR_INVALID_ARGUMENT, "d_w and d_out must be non-NULL");
-    if (a->lda < a->k || a->ldw < a->k || a->ldo < a->n)
-        return fail(RNS_ERR_INVALID_ARGUMENT, "a leading dimension is smaller than its row");
     const bool planes = a->d_a_planes != nullptr;
-    if (planes && a->a_plane_stride < (int64_t)(a->m - 1) * a->lda + a->k)
+    const bool a_packed = a->a_packed != 0, w_packed = a->w_packed != 0;
+    if ((!a_packed && a->lda < a->k) || (!w_packed && a->ldw < a->k) || a->ldo < a->n)
+        return fail(RNS_ERR_INVALID_ARGUMENT, "a leading dimension is smaller than its row");
+    if (planes && !a_packed && a->a_plane_stride < (int64_t)(a->m - 1) * a->lda + a->k)
         return fail(RNS_ERR_INVALID_ARGUMENT, "a_plane_stride is smaller than one plane");
     if (a->out_type < RNS_OUT_INT64 || a->out_type > RNS_OUT_F32)
         return fail(RNS_ERR_INVALID_ARGUMENT, "unknown out_type");
@@ -569,9 +610,11 @@ int rns_linear_fused(const rns_linear_args* a, rns_stream_t stream) {
     if (a->out_type == RNS_OUT_INT32 && (pl.product[R] >> 1) >= (1ll << 31))
         return fail(RNS_ERR_OVERFLOW, "int32 output needs product(moduli)/2 < 2^31");
     const char* why = "";
-    if (!tc_supported(pl, a->k, a->lda, a->ldw, &why))
+    if (!tc_supported(pl, a->k, a_packed ? 16 : a->lda, w_packed ? 16 : a->ldw, &why))
         return fail(RNS_ERR_UNSUPPORTED, "tensor-core path: %s", why);
-    if (planes && a->a_plane_stride % 16 != 0)
+    if ((a_packed || w_packed) && a->tile_k == 128)
+        return fail(RNS_ERR_INVALID_ARGUMENT, "packed operands use tile_k = 64");
+    if (planes && !a_packed && a->a_plane_stride % 16 != 0)
         return fail(RNS_ERR_UNSUPPORTED, "tensor-core path: a_plane_stride must be a multiple of 16");
     const void* a_base = planes ? (const void*)a->d_a_planes : (const void*)a->d_a;
     if ((reinterpret_cast<uintptr_t>(a_base) & 15) || (reinterpret_cast<uintptr_t>(a->d_w) & 15))
@@ -597,6 +640,8 @@ int rns_linear_fused(const rns_linear_args* a, rns_stream_t stream) {
     }
     if (tile_n < 16 || tile_n > 128 || tile_n % 16 != 0 || tile_n > max_tile_n)
         return fail(RNS_ERR_INVALID_ARGUMENT, "tile_n must be a multiple of 16 in [16, %d]", max_tile_n);
+    if (w_packed && kPackNPad % tile_n != 0)
+        return fail(RNS_ERR_INVALID_ARGUMENT, "packed weights need a tile_n that divides %d", kPackNPad);
 
     gp.tile_a_bytes = kTileM * tile_k;
     gp.tile_w_bytes = tile_n * tile_k;
@@ -618,6 +663,11 @@ int rns_linear_fused(const rns_linear_args* a, rns_stream_t stream) {
     gp.m = a->m; gp.n = a->n; gp.k = a->k;
     gp.tile_n = tile_n; gp.tile_k = tile_k;
     gp.a_is_planes = planes ? 1 : 0;
+    gp.a_packed = a_packed ? 1 : 0;
+    gp.w_packed = w_packed ? 1 : 0;
+    gp.a_ptr = planes ? a->d_a_planes : a->d_a;
+    gp.w_ptr = a->d_w;
+    gp.w_npad = round_up_i64(a->n, kPackNPad);
     gp.tmem_cols = round_up_pow2(R * tile_n);
     gp.active_ptr = a->d_active_channels;
     gp.out = a->d_out; gp.ldo = a->ldo; gp.out_type = a->out_type;
@@ -626,13 +676,17 @@ int rns_linear_fused(const rns_linear_args* a, rns_stream_t stream) {
 
     // ---- tensor maps -------------------------------------------------------
     CUtensorMap map_a, map_w;
-    {
+    memset(&map_a, 0, sizeof(map_a));
+    memset(&map_w, 0, sizeof(map_w));
+    if (!w_packed) {
         const uint64_t dims[2] = {(uint64_t)a->k, (uint64_t)a->n};
         const uint64_t strides[1] = {(uint64_t)a->ldw};
         const uint32_t box[2] = {(uint32_t)tile_k, (uint32_t)tile_n};
         if (int rc = make_map(&map_w, a->d_w, 2, dims, strides, box, tile_k)) return rc;
     }
-    if (planes) {
+    if (a_packed) {
+        // bulk copies: no tensor map
+    } else if (planes) {
         const uint64_t dims[3] = {(uint64_t)a->k, (uint64_t)a->m, (uint64_t)R};
         const uint64_t strides[2] = {(uint64_t)a->lda, (uint64_t)a->a_plane_stride};
         const uint32_t box[3] = {(uint32_t)tile_k, (uint32_t)kTileM, 1u};

@@ -80,6 +80,11 @@ int build_plan(const int32_t* moduli, int channels, Plan* out) {
             return fail(RNS_ERR_OVERFLOW, "product(moduli) must fit signed int64");
         p.product[i + 1] = (int64_t)prod;
     }
+    p.encode_fast = 1;
+    for (int i = 0; i < channels; ++i)
+        if (p.mod[i] >= 128) p.encode_fast = 0;
+    for (int i = 0; i < channels; ++i)
+        p.enc_mk[i] = p.encode_fast ? (uint32_t)p.mod[i] << 25 : (uint32_t)p.mod[i];
     for (int i = 0; i < channels; ++i) {
         const int m = p.mod[i];
         const int64_t place_mod = (int64_t)(p.product[i] % m);
@@ -171,8 +176,9 @@ int rns_host_encode_centered_i8(const int8_t* values, int64_t count, const int32
         memcpy(&x, values + i, 4);
         const uint32_t u = x ^ 0x80808080u, ul = u & 0x7f7f7f7fu;
         for (int c = 0; c < channels; ++c) {
-            const uint32_t y = rns::encode_word(u, ul, plan.enc_hi[c], plan.enc_lo[c],
-                                                (uint32_t)plan.mod[c]);
+            const uint32_t y = plan.encode_fast
+                ? rns::encode_word<true>(u, ul, plan.enc_hi[c], plan.enc_lo[c], plan.enc_mk[c])
+                : rns::encode_word<false>(u, ul, plan.enc_hi[c], plan.enc_lo[c], plan.enc_mk[c]);
             memcpy(out + (int64_t)c * count + i, &y, 4);
         }
     }

@@ -178,7 +178,8 @@ class RNSLinear(nn.Module):
         self._weight_scale = scale.to(self.weight.device)
         # The reference exposes the cached planes here; this build caches the
         # quantised matrix itself when the tensor-core kernel serves the layer.
-        self._weight_residues = prepared.weight_nk if prepared.weight_nk is not None else prepared.residues
+        self._weight_residues = (prepared.weight_packed if prepared.weight_packed is not None
+                                 else prepared.residues)
         self._prepared_weight = prepared
         self._adaptive_prepared_weight = adaptive
         self._prepared_weight_version = version

@@ -1,0 +1,143 @@
+"""Column-sharded RNS linears: one process per GPU, weights split along the
+output features, outputs exchanged with one NCCL all-gather per layer.
+
+Every output column n of an RNS linear depends only on W[n,:], its scale and
+bias, and on the (replicated) activation, so the layer splits along N with no
+other communication: rank g quantises the full activation (cheap, and the
+per-tensor scale needs all of it anyway), runs the fused GEMM on its
+``N / world`` rows of the weight, and the fp16 shards are gathered.
+
+``all_gather_into_tensor`` concatenates along dim 0, so G shards [M, N/G] arrive
+as a [G, M, N/G] tensor.  The next sharded layer reads that layout directly
+(the activation quantiser addresses element (m, c) as block c // (N/G), row m,
+column c % (N/G)), so a layer stack never pays a transposing copy; ``unshard``
+produces the ordinary [M, N] matrix when a caller needs it.
+
+Fused QKV is sharded inside each of q, k and v (rank g owns rows
+[q_g; k_g; v_g]), so that the three projections of the gathered result are
+again plain column blocks.
+
+The reference has no multi-GPU path; the layer arithmetic is that of
+``RNSLinear`` (src/rns_llm/layers/rns_linear.py:225-275 of the reference).
+"""
+from __future__ import annotations
+
+from typing import Iterable, Sequence
+
+import torch
+import torch.distributed as dist
+from torch import nn
+
+
+def shard_rows(out_features: int, world: int, rank: int, groups: int = 1) -> list[slice]:
+    """Row ranges of the full weight [N,K] owned by ``rank``: one contiguous
+    range per group (``groups=3`` for a q|k|v-concatenated weight).  N must be
+    divisible by ``groups * world``."""
+    if out_features % (groups * world) != 0:
+        raise ValueError(f"out_features={out_features} is not divisible by groups*world={groups * world}")
+    if not 0 <= rank < world:
+        raise ValueError("rank out of range")
+    per_group = out_features // groups
+    per_rank = per_group // world
+    return [slice(g * per_group + rank * per_rank, g * per_group + (rank + 1) * per_rank) for g in range(groups)]
+
+
+def shard_tensor(full: torch.Tensor, world: int, rank: int, groups: int = 1) -> torch.Tensor:
+    """Rows of ``full`` ([N,...]) owned by ``rank``, groups concatenated."""
+    return torch.cat([full[s] for s in shard_rows(full.shape[0], world, rank, groups)], dim=0)
+
+
+def unshard(gathered: torch.Tensor, groups: int = 1) -> torch.Tensor:
+    """[G, M, N/G] (result of the all-gather) -> [M, N] in the column order of
+    the unsharded layer."""
+    world, m, local = gathered.shape
+    per = local // groups
+    # gathered[g, m, j*per + c] is column  j*(world*per) + g*per + c  of the full output
+    return gathered.view(world, m, groups, per).permute(1, 2, 0, 3).reshape(m, groups * world * per)
+
+
+def group_view(gathered: torch.Tensor, groups: int, index: int) -> torch.Tensor:
+    """Group ``index`` (e.g. q, k or v) of a gathered [G, M, N/G] output as a
+    [G, M, N/(G*groups)] view: itself a gathered activation of that group."""
+    per = gathered.shape[2] // groups
+    return gathered[:, :, index * per:(index + 1) * per]
+
+
+class ColumnShardedRNSLinear(nn.Module):
+    """The shard of an RNS linear that one rank owns.
+
+    ``forward(x)`` takes the replicated activation, either [.., K] or a gathered
+    [G, M, K/G] tensor from a previous sharded layer, and returns the gathered
+    output [G, M, N/G] (``gather=True``) or the local shard [M, N/G].
+    """
+
+    def __init__(self, weight_shard: torch.Tensor, bias_shard: torch.Tensor | None, *, backend,
+                 moduli: Iterable[int], rank: int, world: int, group=None, groups: int = 1,
+                 activation_scale: str = "tensor") -> None:
+        super().__init__()
+        if weight_shard.ndim != 2:
+            raise ValueError("weight_shard must be [N/world, K]")
+        if activation_scale not in ("tensor", "row"):
+            raise ValueError("activation_scale must be 'tensor' or 'row'")
+        self.backend = backend
+        self.moduli = tuple(int(m) for m in moduli)
+        self.rank, self.world, self.group, self.groups = int(rank), int(world), group, int(groups)
+        self.local_features = int(weight_shard.shape[0])
+        self.in_features = int(weight_shard.shape[1])
+        self.out_features = self.local_features * self.world
+        self.per_row = activation_scale == "row"
+        w_q, scale, _ = backend.quantize_weight(weight_shard.contiguous())
+        self.prepared = backend.prepare_weight_nk(w_q, self.moduli)
+        if self.prepared.kernel != "tcgen05":
+            raise ValueError("sharded layers need the tensor-core kernel (int8, K % 16 == 0, moduli >= 86)")
+        self.weight_scale = scale
+        self.bias = None if bias_shard is None else bias_shard.detach().float().contiguous()
+        self._gather_buffers: dict[tuple[int, torch.dtype, int], torch.Tensor] = {}
+
+    @classmethod
+    def from_linear(cls, layer: nn.Linear, *, backend, moduli, rank: int, world: int, group=None,
+                    groups: int = 1, activation_scale: str = "tensor") -> "ColumnShardedRNSLinear":
+        weight = shard_tensor(layer.weight.detach(), world, rank, groups)
+        bias = None if layer.bias is None else shard_tensor(layer.bias.detach(), world, rank, groups)
+        return cls(weight, bias, backend=backend, moduli=moduli, rank=rank, world=world, group=group,
+                   groups=groups, activation_scale=activation_scale)
+
+    def _buffer(self, m: int, dtype: torch.dtype, device: torch.device) -> torch.Tensor:
+        stream = int(torch.cuda.current_stream(device).cuda_stream)
+        key = (m, dtype, stream)
+        buf = self._gather_buffers.get(key)
+        if buf is None:
+            buf = torch.empty((self.world, m, self.local_features), dtype=dtype, device=device)
+            self._gather_buffers[key] = buf
+        return buf
+
+    def forward(self, x: torch.Tensor, *, gather: bool = True, out: torch.Tensor | None = None) -> torch.Tensor:
+        if x.ndim == 3 and x.shape[0] * x.shape[2] == self.in_features and x.shape[2] != self.in_features:
+            flat, m = x, int(x.shape[1])          # gathered activation [G, M, K/G]
+        else:
+            flat = x.reshape(-1, self.in_features)
+            m = int(flat.shape[0])
+        gathered = out if out is not None else self._buffer(m, flat.dtype, flat.device)
+        local = gathered[self.rank]
+        self.backend.linear_forward(flat, self.prepared, self.weight_scale, self.bias,
+                                    per_row=self.per_row, out=local)
+        if not gather:
+            return local
+        if self.world > 1:
+            # In place: this rank's shard already sits at its slot of the output.
+            dist.all_gather_into_tensor(gathered.view(self.world * m, self.local_features), local,
+                                        group=self.group)
+        return gathered
+
+
+def sharded_qkv_from_linears(q_proj: nn.Linear, k_proj: nn.Linear, v_proj: nn.Linear, *, backend, moduli,
+                             rank: int, world: int, group=None,
+                             activation_scale: str = "tensor") -> ColumnShardedRNSLinear:
+    """Rank-local shard of the fused q|k|v projection (rows [q_g; k_g; v_g])."""
+    layers: Sequence[nn.Linear] = (q_proj, k_proj, v_proj)
+    weight = torch.cat([shard_tensor(l.weight.detach(), world, rank) for l in layers], dim=0)
+    bias = None
+    if q_proj.bias is not None:
+        bias = torch.cat([shard_tensor(l.bias.detach(), world, rank) for l in layers], dim=0)
+    return ColumnShardedRNSLinear(weight, bias, backend=backend, moduli=moduli, rank=rank, world=world,
+                                  group=group, groups=3, activation_scale=activation_scale)

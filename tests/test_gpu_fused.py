@@ -25,23 +25,54 @@ def dev(arr):
     return torch.from_numpy(np.ascontiguousarray(arr)).cuda()
 
 
-def fused_int(backend, a, w_nk, mods, *, planes=False, tile_n=0, tile_k=0, out_dtype=torch.int64, active=None):
-    """Direct call of rns_linear_fused on a [M,K] int8 and w [N,K] int8."""
-    prepared = backend.prepare_weight_nk(dev(w_nk), mods)
+def packed_act_offsets(m, k, channels):
+    """Byte offsets of element (row, col, channel) in the packed activation layout
+    (include/rns_b200.h): [M/128][K/64][channels][128][64] with 16-byte chunks of a
+    row XORed by (row >> 1) & 3."""
+    rows = np.arange(m)[:, None, None]
+    cols = np.arange(k)[None, :, None]
+    ch = np.arange(channels)[None, None, :]
+    kblocks = (k + 63) // 64
+    tile = ((rows >> 7) * kblocks + (cols >> 6)) * channels + ch
+    r, c = rows & 127, cols & 63
+    inner = r * 64 + ((((c >> 4) ^ ((r >> 1) & 3)) << 4) | (c & 15))
+    return tile * 8192 + inner
+
+
+def fused_int(backend, a, w_nk, mods, *, planes=False, packed=False, plain_weight=False, tile_n=0, tile_k=0,
+              out_dtype=torch.int64, active=None):
+    """Direct call of rns_linear_fused on a [M,K] int8 and w [N,K] int8.
+    planes: activations as centred planes; packed: activations in the packed tile
+    layout; plain_weight: weight through the tensor map instead of the packed copy."""
+    w_dev = dev(w_nk)
+    prepared = backend.prepare_weight_nk(w_dev, mods)
     assert prepared.kernel == "tcgen05"
-    m = a.shape[0]
+    m, k = a.shape
     out = torch.full((m, w_nk.shape[0]), -7, dtype=out_dtype, device="cuda")
     a_dev = dev(a)
-    if planes:
-        a_planes = backend.encode_centered(a_dev, mods)
-        backend._launch_fused(prepared=prepared, m=m, a=None, a_planes=a_planes, out=out,
-                              tile_n=tile_n, tile_k=tile_k, active=active)
+    kwargs = dict(prepared=prepared, m=m, out=out, tile_n=tile_n, tile_k=tile_k, active=active,
+                  plain_weight=w_dev if plain_weight else None)
+    if planes and packed:
+        from rns_llm_b200 import _native as N
+        buf = torch.empty(int(N.load().rns_packed_activation_bytes(m, k, len(mods))), dtype=torch.int8, device="cuda")
+        N.check(N.load().rns_encode_planes_packed(a_dev.data_ptr(), m, k, k, N.moduli_array(mods), len(mods),
+                                                  buf.data_ptr(), torch.cuda.current_stream().cuda_stream))
+        backend._launch_fused(a=None, a_planes=buf, a_packed=True, **kwargs)
+    elif planes:
+        backend._launch_fused(a=None, a_planes=backend.encode_centered(a_dev, mods), **kwargs)
+    elif packed:
+        host = np.zeros(((m + 127) // 128) * 128 * ((k + 63) // 64) * 64, dtype=np.int8)
+        host[packed_act_offsets(m, k, 1)[:, :, 0]] = a
+        backend._launch_fused(a=dev(host), a_planes=None, a_packed=True, **kwargs)
     else:
-        backend._launch_fused(prepared=prepared, m=m, a=a_dev, a_planes=None, out=out,
-                              tile_n=tile_n, tile_k=tile_k, active=active)
+        backend._launch_fused(a=a_dev, a_planes=None, **kwargs)
     torch.cuda.synchronize()
     backend.check_status()
     return out.cpu().numpy()
+
+
+MODES = [dict(), dict(planes=True), dict(packed=True), dict(planes=True, packed=True),
+         dict(plain_weight=True), dict(planes=True, plain_weight=True)]
 
 
 def rand_i8(rng, shape, lo=-127, hi=127):
@@ -57,8 +88,8 @@ def test_config0_bit_exact(backend, golden):
     assert [int(exact.sum()), int(np.abs(exact).sum()), int(exact[0, 0]), int(exact[-1, -1])] == \
         [int(v) for v in g["c0_checksum"]]
     w = np.ascontiguousarray(b.T)
-    for planes in (False, True):
-        assert np.array_equal(fused_int(backend, a, w, C0, planes=planes), exact)
+    for mode in MODES:
+        assert np.array_equal(fused_int(backend, a, w, C0, **mode), exact), mode
     assert np.array_equal(fused_int(backend, a, w, C0, out_dtype=torch.int32), exact.astype(np.int32))
     # the backend entry point the reference exposes
     prepared = backend.prepare_weight(dev(b), C0)
@@ -68,11 +99,11 @@ def test_config0_bit_exact(backend, golden):
 
 @pytest.mark.parametrize("m,k,n", [(1, 64, 16), (17, 64, 20), (5, 128, 33), (128, 768, 96),
                                    (129, 256, 130), (300, 1024, 260), (256, 4096, 256)])
-@pytest.mark.parametrize("planes", [False, True])
-def test_shapes_ragged_and_deep(backend, m, k, n, planes):
+@pytest.mark.parametrize("mode", range(len(MODES)))
+def test_shapes_ragged_and_deep(backend, m, k, n, mode):
     rng = np.random.default_rng(m * 7 + k + n)
     a, w = rand_i8(rng, (m, k), -128, 127), rand_i8(rng, (n, k), -128, 127)
-    assert np.array_equal(fused_int(backend, a, w, C0, planes=planes), O.exact_matmul(a, w.T))
+    assert np.array_equal(fused_int(backend, a, w, C0, **MODES[mode]), O.exact_matmul(a, w.T))
 
 
 @pytest.mark.parametrize("tile_n", [16, 32, 48, 64, 96, 128])
@@ -84,7 +115,11 @@ def test_tile_shapes(backend, tile_n, tile_k):
     exact = O.exact_matmul(a, w.T)
     # two moduli hold +-7937: compare modulo P through the oracle's reconstruction
     expect = O.decode_garner(np.stack([exact % 127, exact % 125]), mods)
-    assert np.array_equal(fused_int(backend, a, w, mods, tile_n=tile_n, tile_k=tile_k), expect)
+    # tile_k = 128 exists for plain (tensor-map) operands only
+    assert np.array_equal(fused_int(backend, a, w, mods, tile_n=tile_n, tile_k=tile_k, plain_weight=True), expect)
+    if tile_k == 64:
+        for mode in MODES[:4]:
+            assert np.array_equal(fused_int(backend, a, w, mods, tile_n=tile_n, **mode), expect), mode
 
 
 @pytest.mark.parametrize("mods", [(127, 125), (127, 126, 125), C0, C4, (127, 126, 125, 121, 113, 109),
@@ -99,8 +134,8 @@ def test_channel_counts(backend, mods):
         expect = exact
     else:
         expect = O.decode_garner(np.stack([exact % m for m in mods]), mods)
-    for planes in (False, True):
-        assert np.array_equal(fused_int(backend, a, w, mods, planes=planes), expect)
+    for mode in MODES:
+        assert np.array_equal(fused_int(backend, a, w, mods, **mode), expect), mode
 
 
 def test_genuine_residues_reach_the_tensor_core(backend):
@@ -171,6 +206,7 @@ def test_quantizer_outputs(backend):
     from rns_llm_b200 import _native as N
     lib = N.load()
     xd = dev(x)
+    exp = {}
     for per_row in (0, 1):
         q = torch.empty((37, 192), dtype=torch.int8, device="cuda")
         planes = torch.empty((4, 37, 192), dtype=torch.int8, device="cuda")
@@ -178,7 +214,7 @@ def test_quantizer_outputs(backend):
         l1 = torch.empty(1, dtype=torch.int32, device="cuda")
         scratch = torch.empty(4, dtype=torch.int32, device="cuda")
         N.check(lib.rns_quantize_activations(xd.data_ptr(), N.F16, 37, 192, 192, 0, 0, per_row, 127,
-                                             N.moduli_array(C0), 4, q.data_ptr(), planes.data_ptr(),
+                                             N.moduli_array(C0), 4, q.data_ptr(), planes.data_ptr(), 0,
                                              scale.data_ptr(), l1.data_ptr(), scratch.data_ptr(),
                                              torch.cuda.current_stream().cuda_stream))
         torch.cuda.synchronize()
@@ -188,6 +224,27 @@ def test_quantizer_outputs(backend):
         assert np.array_equal(q.cpu().numpy(), exp_q)
         assert np.array_equal(planes.cpu().numpy(), O.encode_centered(exp_q, C0, "device"))
         assert int(l1.item()) == int(np.abs(exp_q.astype(np.int64)).sum(axis=1).max())
+        exp[per_row] = exp_q
+    # packed tile layouts, and the two-launch per-tensor path (M*K > 128 Ki elements)
+    big = (rng.standard_normal((300, 512)) * 2).astype(np.float16)
+    for values, per_row in ((x, 0), (big, 0), (big, 1)):
+        m, k = values.shape
+        vd = dev(values)
+        qp = torch.zeros(int(lib.rns_packed_activation_bytes(m, k, 1)), dtype=torch.int8, device="cuda")
+        pp = torch.zeros(int(lib.rns_packed_activation_bytes(m, k, 4)), dtype=torch.int8, device="cuda")
+        scale = torch.empty(m if per_row else 1, dtype=torch.float32, device="cuda")
+        scratch = torch.empty(4, dtype=torch.int32, device="cuda")
+        N.check(lib.rns_quantize_activations(vd.data_ptr(), N.F16, m, k, k, 0, 0, per_row, 127,
+                                             N.moduli_array(C0), 4, qp.data_ptr(), pp.data_ptr(), 1,
+                                             scale.data_ptr(), None, scratch.data_ptr(),
+                                             torch.cuda.current_stream().cuda_stream))
+        torch.cuda.synchronize()
+        exp_scale = O.symmetric_scale(values.astype(np.float32), 127, axis=1 if per_row else None)
+        exp_q = O.quantize(values.astype(np.float32), exp_scale, 127)
+        assert np.array_equal(scale.cpu().numpy(), exp_scale.reshape(-1))
+        assert np.array_equal(qp.cpu().numpy()[packed_act_offsets(m, k, 1)[:, :, 0]], exp_q)
+        got_planes = pp.cpu().numpy()[packed_act_offsets(m, k, 4)]            # [M,K,4]
+        assert np.array_equal(got_planes.transpose(2, 0, 1), O.encode_centered(exp_q, C0, "device"))
     zeros = torch.zeros((4, 64), dtype=torch.float16, device="cuda")
     wq, ws, _ = backend.quantize_weight(zeros)
     assert float(ws[0]) == float(np.finfo(np.float32).eps) and int(wq.abs().max()) == 0
@@ -346,3 +403,16 @@ def test_full_size_against_independent_int_gemm(backend, c_oracle):
             backend.matmul_prepared_fused(rest, prepared)
         assert torch.equal(both, got)
     backend.check_status()
+
+
+def test_weight_pack_roundtrip_and_residues(backend):
+    rng = np.random.default_rng(71)
+    for n, k in ((20, 64), (384, 128), (500, 208)):
+        w = rand_i8(rng, (n, k), -128, 127)
+        prepared = backend.prepare_weight_nk(dev(w), C0)
+        from rns_llm_b200 import _native as N
+        assert prepared.weight_packed.numel() == N.load().rns_packed_weight_bytes(n, k) == \
+            ((n + 383) // 384) * 384 * ((k + 63) // 64) * 64
+        assert np.array_equal(prepared.weight_nk.cpu().numpy(), w)
+        # planes are derived on request, in the reference's [R,K,N] shape
+        assert np.array_equal(prepared.residues.cpu().numpy(), O.encode_centered(w.T, C0, "device"))

@@ -96,7 +96,9 @@ def test_weight_cache_follows_in_place_updates(backend):
     y1 = layer(x)
     cached = layer._prepared_weight
     assert layer(x).data_ptr() != 0 and layer._prepared_weight is cached
-    assert layer._weight_residues.dtype == torch.int8 and layer._weight_residues.shape == (48, 128)
+    # the cached weight is the packed int8 matrix: N padded to 384, K to 64, one byte per value
+    assert layer._weight_residues.dtype == torch.int8 and layer._weight_residues.numel() == 384 * 128
+    assert torch.equal(cached.weight_nk, backend.quantize_weight(layer.weight.detach())[0])
     with torch.no_grad():
         layer.weight.mul_(2.0)
     y2 = layer(x)
