@@ -1,0 +1,415 @@
+#!/usr/bin/env python
+"""Benchmark of the RNS linear hot path on B200.
+
+Workload (``config.workload``): configuration 4 of BASELINE.json, the
+OPT-6.7B-shaped layer stack - 32 layers x {QKV 4096->12288, out_proj 4096->4096,
+fc1 4096->16384, fc2 16384->4096}, every linear an RNS linear, M = 4096 tokens,
+moduli (127,126,125,121) for K = 4096 and (127,126,125,121,113) for K = 16384,
+random-init weights and seeded synthetic activations.  It is the largest
+configuration that fits one GPU and the one the headline metric (RNS-GEMM int8
+channel-TOPS at M >= 1024) is defined on.  One *step* is one pass of the 128
+linears over one 4096-token batch: quantise activations -> fused RNS GEMM
+(residue encode, one int8 tensor-core GEMM per channel, Garner, dequantise).
+
+``python bench.py --gpus N --steps K --warmup W`` prints ONE JSON line on rank 0.
+With N > 1 (launched by torchrun, one rank per GPU) every linear is column
+sharded along its output features and the fp16 shards are all-gathered with
+NCCL; the total work is fixed, so scaling is "strong".
+
+``--impl reference`` times the CPU restatement of the reference's own path
+(oracle/) on the host cores instead; that is the only place this file executes
+anything from oracle/, besides the ``cpu_baseline`` block of the normal run.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+MODULI_4 = (127, 126, 125, 121)
+MODULI_5 = (127, 126, 125, 121, 113)
+HIDDEN, FFN = 4096, 16384
+# (name, K, N, moduli, groups)   groups=3: q|k|v concatenated along N
+LINEARS = (
+    ("qkv", HIDDEN, 3 * HIDDEN, MODULI_4, 3),
+    ("out_proj", HIDDEN, HIDDEN, MODULI_4, 1),
+    ("fc1", HIDDEN, FFN, MODULI_4, 1),
+    ("fc2", FFN, HIDDEN, MODULI_5, 1),
+)
+METRIC = "rns_gemm_int8_channel_tops"
+UNIT = "TOPS"
+
+
+def channel_ops_per_step(tokens: int, layers: int) -> float:
+    """2 * R * M * K * N summed over the stack (benchmarks/benchmark_cuda.py:256-261
+    of the reference defines rns_channel_tops this way)."""
+    return float(sum(2.0 * len(mods) * tokens * k * n for _, k, n, mods, _ in LINEARS) * layers)
+
+
+def useful_ops_per_step(tokens: int, layers: int) -> float:
+    return float(sum(2.0 * tokens * k * n for _, k, n, _, _ in LINEARS) * layers)
+
+
+def load_peaks() -> dict:
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        data = json.loads(path.read_text())
+        data["source"] = "measured"
+        return data
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+# --------------------------------------------------------------------------
+# clocks
+# --------------------------------------------------------------------------
+class ClockSampler:
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int) -> None:
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.file = None
+
+    def start(self) -> None:
+        try:
+            self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-i", str(self.gpu_index), "-lms", "100"],
+                stdout=self.file, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        self.file.flush()
+        self.file.seek(0)
+        sm, sm_max, power, reasons = [], [], [], set()
+        for line in self.file.read().splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1])); sm_max.append(float(parts[2])); power.append(float(parts[3]))
+            except ValueError:
+                continue
+            for name, value in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"),
+                                   parts[5:9]):
+                if value.lower().startswith("active"):
+                    reasons.add(name)
+        name = self.file.name
+        self.file.close()
+        os.unlink(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(sm_max), "power_w_max": max(power),
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# --------------------------------------------------------------------------
+# CPU arm (oracle port)
+# --------------------------------------------------------------------------
+def cpu_port_sample(target_seconds: float = 12.0) -> dict:
+    """Times the C restatement of the reference path (oracle/rns_oracle.c, all
+    host threads) on rows of the workload's QKV linear; the sample grows until
+    it takes about ``target_seconds``."""
+    import numpy as np
+    from oracle import c_oracle
+
+    c_oracle.build()
+    threads = c_oracle.threads()
+    name, k, n, mods, _ = LINEARS[0]
+    rng = np.random.default_rng(1004)
+    w = rng.integers(-127, 128, size=(n, k), dtype=np.int64).astype(np.int8)
+    rows = max(threads, 8)
+    elapsed = 0.0
+    while True:
+        a = rng.integers(-127, 128, size=(rows, k), dtype=np.int64).astype(np.int8)
+        scale = np.ones(1, dtype=np.float32)
+        col = np.ones(n, dtype=np.float32)
+        t0 = time.perf_counter()
+        c_oracle.linear(a, w, mods, scale, col, None, want_float=True)
+        elapsed = time.perf_counter() - t0
+        if elapsed >= target_seconds / 3 or rows >= 4096:
+            break
+        rows = min(4096, int(rows * max(2.0, target_seconds / max(elapsed, 1e-3) / 1.5)))
+    ops = 2.0 * len(mods) * rows * k * n
+    return {"value": ops / elapsed / 1e12, "unit": UNIT, "cores": threads, "kind": "port",
+            "sample": f"{rows} rows of the {name} linear (K={k}, N={n}, R={len(mods)}), "
+                      f"C restatement of the reference path incl. weight encode, {elapsed:.1f} s",
+            "seconds": elapsed}
+
+
+def numpy_reference_sample() -> dict:
+    """The reference's own NumPy algorithm (rns_matmul_numpy) restated in
+    oracle/rns_oracle.py, on configuration 0 (M=128, K=N=768)."""
+    import numpy as np
+    from oracle import rns_oracle as O
+
+    rng = np.random.default_rng(1000)
+    a = rng.integers(-127, 128, size=(128, 768), dtype=np.int64).astype(np.int8)
+    b = rng.integers(-127, 128, size=(768, 768), dtype=np.int64).astype(np.int8)
+    best = min(_timed(lambda: O.rns_matmul(a, b, MODULI_4)) for _ in range(3))
+    return {"seconds": best, "channel_tops": 2.0 * 4 * 128 * 768 * 768 / best / 1e12,
+            "what": "NumPy restatement of rns_matmul_numpy on configuration 0, 1 effective core"}
+
+
+def _timed(fn) -> float:
+    t0 = time.perf_counter()
+    fn()
+    return time.perf_counter() - t0
+
+
+def run_reference_arm(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    samples = []
+    for _ in range(max(1, args.warmup // 3)):
+        cpu_port_sample(target_seconds=3.0)
+    for _ in range(args.steps):
+        samples.append(cpu_port_sample(target_seconds=10.0))
+    value = statistics.median(s["value"] for s in samples)
+    seconds = statistics.median(s["seconds"] for s in samples)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": seconds * 1e3,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int8",
+        "data": "synthetic",
+        "config": workload_config(args, sharded=False),
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": samples[0]["cores"], "kind": "port",
+                         "sample": samples[0]["sample"]},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(args, sharded: bool) -> dict:
+    return {
+        "workload": "opt6.7b_layer_stack_prefill (BASELINE.json configs[4])",
+        "layers": args.layers, "tokens": args.tokens, "hidden": HIDDEN, "ffn": FFN,
+        "linears_per_layer": [f"{name}:{k}->{n}:R{len(mods)}" for name, k, n, mods, _ in LINEARS],
+        "moduli_k4096": list(MODULI_4), "moduli_k16384": list(MODULI_5),
+        "activation_scale": "per-tensor", "out_dtype": "float16",
+        "parallelism": f"column-sharded N x{args.gpus} + NCCL all-gather" if sharded else "single GPU",
+        "l2_policy": "inputs larger than L2 (about 6.4 GB of int8 weights streamed per step)",
+    }
+
+
+# --------------------------------------------------------------------------
+# GPU arm
+# --------------------------------------------------------------------------
+def build_stack(backend, args, rank: int, world: int, device):
+    """Random-init weights, quantised and prepared layer by layer (the fp16
+    weights are not kept).  Returns a list of layers, each a list of sharded
+    linears in LINEARS order."""
+    import torch
+    from rns_llm_b200.parallel import ColumnShardedRNSLinear, shard_tensor
+
+    gen = torch.Generator(device=device)
+    gen.manual_seed(1004)
+    stack = []
+    for _ in range(args.layers):
+        layer = []
+        for name, k, n, mods, groups in LINEARS:
+            weight = torch.randn((n, k), generator=gen, device=device, dtype=torch.float16) * (1.0 / k ** 0.5)
+            bias = torch.randn((n,), generator=gen, device=device, dtype=torch.float16) * 0.01
+            shard_w = shard_tensor(weight, world, rank, groups)
+            shard_b = shard_tensor(bias, world, rank, groups)
+            layer.append(ColumnShardedRNSLinear(shard_w, shard_b, backend=backend, moduli=mods, rank=rank,
+                                                world=world, groups=groups))
+            del weight, bias, shard_w, shard_b
+        stack.append(layer)
+    return stack
+
+
+def run_stack(stack, x):
+    """One step: the 4*layers linears in data-flow order.  The q block of the
+    fused QKV output stands in for the attention output that feeds out_proj."""
+    from rns_llm_b200.parallel import group_view
+
+    h = x
+    for qkv, out_proj, fc1, fc2 in stack:
+        t = qkv(h)                                   # [G, M, 3*H/G]
+        t = out_proj(group_view(t, 3, 0))            # q block, gathered layout
+        t = fc1(t)
+        h = fc2(t)
+    return h
+
+
+def main() -> None:
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=5)
+    parser.add_argument("--warmup", type=int, default=3)
+    parser.add_argument("--impl", default="rns_b200", choices=["rns_b200", "reference"])
+    parser.add_argument("--layers", type=int, default=32)
+    parser.add_argument("--tokens", type=int, default=4096)
+    parser.add_argument("--no-cpu-baseline", action="store_true")
+    args = parser.parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torchrun --nproc-per-node {args.gpus}")
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; the RNS path has no CPU implementation")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+
+    from rns_llm_b200.backends import CudaRNSBackend
+
+    backend = CudaRNSBackend()
+    warmup = max(args.warmup, 3)
+    stack = build_stack(backend, args, rank, world, device)
+    torch.manual_seed(4321)
+    host_x = torch.randn((args.tokens, HIDDEN), dtype=torch.float16).pin_memory()
+    host_y = torch.empty((args.tokens, HIDDEN), dtype=torch.float16).pin_memory()
+    dev_x = host_x.to(device)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- GEMM-kernel timing hooks (roofline.achieved) ----------------------
+    gemm_events: list = []
+    original_launch = backend._launch_fused
+
+    def timed_launch(**kw):
+        start = torch.cuda.Event(enable_timing=True)
+        stop = torch.cuda.Event(enable_timing=True)
+        start.record()
+        original_launch(**kw)
+        stop.record()
+        gemm_events.append((start, stop))
+
+    def step_device():
+        return run_stack(stack, dev_x)
+
+    def step_e2e():
+        x = host_x.to(device, non_blocking=True)
+        y = run_stack(stack, x)
+        from rns_llm_b200.parallel import unshard
+        host_y.copy_(unshard(y, 1), non_blocking=True)
+        return y
+
+    for _ in range(warmup):
+        step_device()
+    barrier()
+    y_check = step_device()
+    if not bool(torch.isfinite(y_check).all()):
+        raise SystemExit("non-finite activations in the layer stack")
+    backend.check_status()
+
+    # ---- timed region: device-resident inputs -------------------------------
+    backend._launch_fused = timed_launch
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    barrier()
+    start = torch.cuda.Event(enable_timing=True)
+    stop = torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(args.steps):
+        step_device()
+    stop.record()
+    barrier()
+    clocks = sampler.stop()
+    backend._launch_fused = original_launch
+    elapsed_ms = start.elapsed_time(stop)
+    gemm_ms = sum(a.elapsed_time(b) for a, b in gemm_events)
+    gemm_launches = len(gemm_events)
+
+    # ---- timed region: end to end from host buffers -------------------------
+    for _ in range(2):
+        step_e2e()
+    barrier()
+    e_start = torch.cuda.Event(enable_timing=True)
+    e_stop = torch.cuda.Event(enable_timing=True)
+    e_start.record()
+    for _ in range(args.steps):
+        step_e2e()
+    e_stop.record()
+    barrier()
+    e2e_ms = e_start.elapsed_time(e_stop)
+    backend.check_status()
+
+    times = torch.tensor([elapsed_ms, e2e_ms, gemm_ms], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    elapsed_ms, e2e_ms, gemm_ms = (float(v) for v in times.tolist())
+
+    if rank == 0:
+        ops = channel_ops_per_step(args.tokens, args.layers)
+        ms_per_step = elapsed_ms / args.steps
+        value = ops / (ms_per_step * 1e-3) / 1e12
+        e2e_value = ops / (e2e_ms / args.steps * 1e-3) / 1e12
+        peaks = load_peaks()
+        # Dominant kernel: rns_gemm_kernel.  Per launch it performs 2*R*M*K*(N/world)
+        # int8 tensor-core operations (algorithmic, = SURVEY 8(d) "ops" per call).
+        gemm_ops_per_rank = ops / world * args.steps
+        achieved = gemm_ops_per_rank / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else None
+        int8_peak = 2.0 * float(peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"]))
+        launches_per_linear = 3          # absmax + quantise/encode + fused GEMM
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+            "config": workload_config(args, sharded=world > 1),
+            "useful_tops": useful_ops_per_step(args.tokens, args.layers) / (ms_per_step * 1e-3) / 1e12,
+            "tokens_per_s": args.tokens / (ms_per_step * 1e-3),
+            "roofline": {
+                "bound": "tensor", "kernel": "rns_gemm_kernel", "achieved": achieved, "peak": int8_peak,
+                "unit": "TOPS", "frac": None if achieved is None else achieved / int8_peak,
+                "peak_source": f"2 x bf16_tflops_sustained of MEASURED_PEAKS.json ({peaks['source']}); "
+                               "the file records no int8 figure",
+                "launches": gemm_launches, "avg_launch_ms": gemm_ms / max(gemm_launches, 1),
+                "traffic": None,
+            },
+            "clocks": clocks,
+            "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms / args.steps,
+                    "h2d_bytes_per_step": int(host_x.numel() * 2), "d2h_bytes_per_step": int(host_y.numel() * 2)},
+            "gpu_launches": int(len(LINEARS) * args.layers * launches_per_linear * args.steps),
+        }
+        if not args.no_cpu_baseline:
+            try:
+                line["cpu_baseline"] = {k: v for k, v in cpu_port_sample().items() if k != "seconds"}
+                line["cpu_baseline"]["numpy_reference_config0"] = numpy_reference_sample()
+            except Exception as exc:  # the CPU baseline must not lose the GPU measurement
+                line["cpu_baseline"] = {"value": None, "unit": UNIT, "cores": os.cpu_count(), "kind": "port",
+                                        "sample": f"failed: {exc}"}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

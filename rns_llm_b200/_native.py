@@ -6,11 +6,15 @@ this module raises, and nothing in the package computes the path another way.
 from __future__ import annotations
 
 import ctypes as C
+import os
 import threading
 from pathlib import Path
 from typing import Sequence
 
-_LIB_PATH = Path(__file__).resolve().parent / "csrc" / "librns_b200.so"
+# RNS_B200_LIBRARY points at another build of the same library (e.g. one with
+# extra instrumentation); by default the in-tree build is loaded.
+_LIB_PATH = Path(os.environ.get("RNS_B200_LIBRARY") or
+                 Path(__file__).resolve().parent / "csrc" / "librns_b200.so")
 _lock = threading.Lock()
 _lib: C.CDLL | None = None
 

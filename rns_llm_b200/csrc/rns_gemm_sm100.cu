@@ -32,6 +32,13 @@
 
 namespace rns {
 
+#ifdef RNS_ABLATION
+#define RNS_ABLATED(bit) ((p.ablate >> (bit)) & 1)
+static int g_ablate = 0;
+#else
+#define RNS_ABLATED(bit) false
+#endif
+
 constexpr int kTileM = 128;
 constexpr int kWorkerWarps = 16;
 constexpr int kThreads = 64 + kWorkerWarps * 32;
@@ -41,6 +48,8 @@ constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s
 
 struct GemmParams {
     Plan plan;
+    int32_t ablate;               // timing experiments only; always 0 unless built with RNS_ABLATION
+
     int32_t m, n, k;
     int32_t tile_n, tile_k;      // tile_k in {64,128}
     int32_t stages;
@@ -267,8 +276,8 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         ctl.abort = 0;
         for (int s = 0; s < stages; ++s) {
             mbar_init(smem_addr(&ctl.full_raw[s]), 1);
-            mbar_init(smem_addr(&ctl.empty_raw[s]), kWorkerThreads);
-            mbar_init(smem_addr(&ctl.full_enc[s]), kWorkerThreads + (a_planes ? 1 : 0));
+            mbar_init(smem_addr(&ctl.empty_raw[s]), kWorkerWarps);
+            mbar_init(smem_addr(&ctl.full_enc[s]), kWorkerWarps + (a_planes ? 1 : 0));
             mbar_init(smem_addr(&ctl.empty_enc[s]), 1);
         }
         mbar_init(smem_addr(&ctl.acc_full), 1);
@@ -296,8 +305,9 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 // the first round needs no wait.
                 if (round > 0 && !wait_bounded(smem_addr(&ctl.empty_raw[s]), (round - 1) & 1, abort)) break;
                 const uint32_t fr = smem_addr(&ctl.full_raw[s]);
-                mbar_arrive_expect_tx(fr, raw_bytes);
-                if (p.w_packed)
+                mbar_arrive_expect_tx(fr, RNS_ABLATED(3) ? (a_planes ? 0u : p.tile_a_bytes) : raw_bytes);
+                if (RNS_ABLATED(3)) {
+                } else if (p.w_packed)
                     bulk_load(stage + p.off_raw_w,
                               p.w_ptr + ((int64_t)kb * p.w_npad + n0) * kPackK, p.tile_w_bytes, fr);
                 else
@@ -311,8 +321,9 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 } else {
                     if (round > 0 && !wait_bounded(smem_addr(&ctl.empty_enc[s]), (round - 1) & 1, abort)) break;
                     const uint32_t fe = smem_addr(&ctl.full_enc[s]);
-                    mbar_arrive_expect_tx(fe, (uint32_t)active * p.tile_a_bytes);
-                    if (p.a_packed) {
+                    mbar_arrive_expect_tx(fe, RNS_ABLATED(2) ? 0u : (uint32_t)active * p.tile_a_bytes);
+                    if (RNS_ABLATED(2)) {
+                    } else if (p.a_packed) {
                         bulk_load(stage + p.off_enc_a, p.a_ptr + a_tile * ((int64_t)R * kPackM * kPackK),
                                   (uint32_t)active * p.tile_a_bytes, fe);
                     } else {
@@ -336,7 +347,7 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 ok = wait_bounded(smem_addr(&ctl.full_enc[s]), round & 1, abort);
                 if (!ok) break;
                 tc_fence_after();
-                for (int c = 0; c < active; ++c) {
+                for (int c = 0; c < (RNS_ABLATED(1) ? 0 : active); ++c) {
                     const uint32_t a_tile = stage + p.off_enc_a + (uint32_t)c * p.tile_a_bytes;
                     const uint32_t w_tile = stage + p.off_enc_w + (uint32_t)c * p.tile_w_bytes;
                     const uint32_t d = tmem_base + (uint32_t)(c * p.tile_n);
@@ -374,7 +385,7 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             ok = wait_bounded(smem_addr(&ctl.full_raw[s]), round & 1, abort);
             if (ok && round > 0) ok = wait_bounded(smem_addr(&ctl.empty_enc[s]), (round - 1) & 1, abort);
             if (!ok) break;
-            for (int part = 0; part < 2; ++part) {
+            for (int part = 0; part < (RNS_ABLATED(0) ? 0 : 2); ++part) {
                 const int chunks = part == 0 ? chunks_w : chunks_a;
                 const uint8_t* raw = stage + (part == 0 ? p.off_raw_w : p.off_raw_a);
                 uint8_t* enc = stage + (part == 0 ? p.off_enc_w : p.off_enc_a);
@@ -386,14 +397,20 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 else
                     encode_chunks<R, false, false>(raw, enc, tile_bytes, chunks, wt, active, enc_hi, enc_lo, enc_mk);
             }
+            // Every writer makes its stores visible to the async proxy, the warp
+            // converges, and one lane signals for the warp: 16 arrivals per stage
+            // instead of 512 (arrivals on one mbarrier serialise).
             fence_proxy_async_smem();
-            mbar_arrive(smem_addr(&ctl.full_enc[s]));
-            mbar_arrive(smem_addr(&ctl.empty_raw[s]));
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(smem_addr(&ctl.full_enc[s]));
+                mbar_arrive(smem_addr(&ctl.empty_raw[s]));
+            }
         }
 
         // ------------------------------ epilogue ----------------------------------
         if (ok) ok = wait_bounded(smem_addr(&ctl.acc_full), 0, abort);
-        if (ok) {
+        if (ok && !RNS_ABLATED(4)) {
             tc_fence_after();
             const int quarter = warp & 3;             // TMEM lanes 32*quarter .. +31
             const int part = (warp - 2) >> 2;         // 8-column chunks are dealt round-robin
@@ -575,6 +592,10 @@ using namespace rns;
 
 extern "C" {
 
+#ifdef RNS_ABLATION
+__attribute__((visibility("default"))) void rns_debug_set_ablation(int bits) { rns::g_ablate = bits; }
+#endif
+
 int rns_linear_fused_supported(const int32_t* moduli, int channels, int k, int64_t lda, int64_t ldw) {
     Plan pl;
     if (build_plan(moduli, channels, &pl) != RNS_OK) return 0;
@@ -662,6 +683,9 @@ int rns_linear_fused(const rns_linear_args* a, rns_stream_t stream) {
     gp.stages = stages;
     gp.m = a->m; gp.n = a->n; gp.k = a->k;
     gp.tile_n = tile_n; gp.tile_k = tile_k;
+#ifdef RNS_ABLATION
+    gp.ablate = g_ablate;
+#endif
     gp.a_is_planes = planes ? 1 : 0;
     gp.a_packed = a_packed ? 1 : 0;
     gp.w_packed = w_packed ? 1 : 0;
