@@ -201,7 +201,7 @@ RNS_API int rns_matmul_centered_fused_out(const int8_t* d_a, const int8_t* d_b,
  * so that one bulk copy fills a pipeline stage:
  *   weights      [K_pad/64][N_pad][64]        N_pad = N rounded up to 384,
  *   activations  [M_pad/128][K_pad/64][128][64]             (source integers)
- *   planes       [M_pad/128][K_pad/64][channels][128][64]   M_pad = M up to 128,
+ *   planes       [M_pad/128][K_pad/64][channels][128][64]   M_pad = M up to 256,
  * K_pad = K rounded up to 64 (the weight side is zero there).  Inside a 64-byte
  * row the 16-byte chunk j of row r is stored at chunk j ^ ((r >> 1) & 3).
  * rns_pack_weight / rns_quantize_activations / rns_encode_planes_packed write
@@ -249,6 +249,7 @@ typedef struct rns_linear_args {
     int32_t tile_k;           /* 0 = choose; else 64 or 128 (128: plain layouts only) */
     int32_t a_packed;         /* 1: d_a / d_a_planes is in the packed tile layout */
     int32_t w_packed;         /* 1: d_w is in the packed tile layout (rns_pack_weight) */
+    int32_t pair_mode;        /* 1: two-CTA tiles (256 x tile_n), 0: one CTA per tile, 2: choose */
 } rns_linear_args;
 
 RNS_API int rns_linear_fused(const rns_linear_args* args, rns_stream_t stream);

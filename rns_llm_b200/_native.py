@@ -55,6 +55,7 @@ class LinearArgs(C.Structure):
         ("tile_k", C.c_int32),
         ("a_packed", C.c_int32),
         ("w_packed", C.c_int32),
+        ("pair_mode", C.c_int32),
     ]
 
 

@@ -560,7 +560,7 @@ class CudaRNSBackend:
                       active: torch.Tensor | None = None, row_scale: torch.Tensor | None = None,
                       row_scale_stride: int = 0, col_scale: torch.Tensor | None = None,
                       bias: torch.Tensor | None = None, tile_n: int = 0, tile_k: int = 0,
-                      plain_weight: torch.Tensor | None = None) -> None:
+                      plain_weight: torch.Tensor | None = None, pair_mode: int = 2) -> None:
         """Fills ``rns_linear_args`` and launches.  ``a`` / ``a_planes`` are plain
         ([M,K] / [R,M,K]) unless ``a_packed``; the weight is the prepared packed
         copy unless ``plain_weight`` ([N,K] int8) is given."""
@@ -598,6 +598,7 @@ class CudaRNSBackend:
             args.d_bias = None if bias is None else bias.data_ptr()
         args.d_status = self._state(device).status.data_ptr()
         args.tile_n, args.tile_k = tile_n, tile_k
+        args.pair_mode = pair_mode
         N.check(self._lib.rns_linear_fused(C.byref(args), self._stream(device)))
 
     def matmul_prepared_fused(self, a: torch.Tensor, prepared_weight: PreparedRNSWeight, *,

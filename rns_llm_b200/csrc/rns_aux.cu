@@ -792,7 +792,8 @@ int64_t rns_packed_weight_bytes(int n, int k) {
 
 int64_t rns_packed_activation_bytes(int m, int k, int channels) {
     if (m <= 0 || k <= 0 || channels <= 0) return 0;
-    return round_up_i64(m, kPackM) * round_up_i64(k, kPackK) * channels;
+    // two row tiles at a time: a CTA pair always loads both, even past M
+    return round_up_i64(m, 2 * kPackM) * round_up_i64(k, kPackK) * channels;
 }
 
 int rns_pack_weight(const int8_t* d_w, int n, int k, int64_t ldw, int8_t* d_packed, rns_stream_t stream) {

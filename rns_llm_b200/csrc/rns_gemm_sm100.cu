@@ -1,7 +1,11 @@
 // Fused RNS linear for sm_100a: TMA -> in-kernel residue encoding -> one
 // tcgen05.mma.kind::i8 per residue channel (int32 accumulators in TMEM) ->
 // epilogue with modular reduction, mixed-radix reconstruction, recentring and
-// dequantisation.  One CTA computes one 128 x tile_n output tile.
+// dequantisation.  One CTA computes one 128 x tile_n output tile; in PAIR mode two
+// CTAs of a cluster (tcgen05 cta_group::2) compute a 256 x tile_n tile together:
+// each holds its own 128 rows of A and HALF of the W tile, the leader CTA issues
+// the MMAs, and each CTA's tensor memory receives its own 128 rows.  Pairing
+// halves the W bytes every SM has to load, encode and feed to the tensor core.
 //
 // Warp roles (576 threads):
 //   warp 0      TMA producer (one elected lane)
@@ -161,6 +165,63 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
                  : "memory");
 }
+__device__ __forceinline__ void tmem_alloc2(uint32_t holder_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(holder_smem),
+                 "r"(cols)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish2() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc2(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols)
+                 : "memory");
+}
+__device__ __forceinline__ void umma_i8_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc,
+                                             uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// Arrives on the barrier at this shared-memory offset in BOTH CTAs of the pair
+// once the MMAs issued so far have completed.
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+    asm volatile(
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+        ::"r"(bar), "h"((uint16_t)3)
+        : "memory");
+}
+// Arrive on the barrier at the same offset in another CTA of the cluster.
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t bar, uint32_t cta_rank) {
+    asm volatile(
+        "{\n\t.reg .b32 remote;\n\t"
+        "mapa.shared::cluster.u32 remote, %0, %1;\n\t"
+        "mbarrier.arrive.release.cluster.shared::cluster.b64 _, [remote];\n\t}"
+        ::"r"(bar), "r"(cta_rank)
+        : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ uint32_t cluster_cta_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
 __device__ __forceinline__ void tmem_ld8(uint32_t taddr, int (&v)[8]) {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
@@ -189,17 +250,19 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, uint32_t tile_
 }
 // Instruction descriptor: S32 accumulate [4,6)=2, signed 8-bit A [7,10)=1 and
 // B [10,13)=1, both K-major, N>>3 at [17,23), M>>4 at [24,29).
-__device__ __forceinline__ uint32_t make_idesc(uint32_t n) {
-    return (2u << 4) | (1u << 7) | (1u << 10) | ((n >> 3) << 17) | ((uint32_t)(kTileM >> 4) << 24);
+__device__ __forceinline__ uint32_t make_idesc(uint32_t m, uint32_t n) {
+    return (2u << 4) | (1u << 7) | (1u << 10) | ((n >> 3) << 17) | ((m >> 4) << 24);
 }
 
 // Waits for `parity` of `bar`; false (and *abort set) when the time limit passes
 // or another thread of the CTA already gave up.
+template <bool CLUSTER = false>
 __device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity, volatile int* abort) {
-    if (mbar_try_wait(bar, parity)) return true;
+    auto poll = [&]() { return CLUSTER ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity); };
+    if (poll()) return true;
     const uint64_t t0 = global_timer_ns();
     for (uint32_t spin = 1;; ++spin) {
-        if (mbar_try_wait(bar, parity)) return true;
+        if (poll()) return true;
         if ((spin & 255u) == 0) {
             if (*abort) return false;
             if (global_timer_ns() - t0 > kWaitLimitNs) {
@@ -244,11 +307,12 @@ struct __align__(8) SharedCtl {
     uint64_t full_enc[kMaxStages];
     uint64_t empty_enc[kMaxStages];
     uint64_t acc_full;
+    uint64_t peer_ready[kMaxStages];  // PAIR, leader only: the peer CTA's stage is complete
     uint32_t tmem_base;
     int abort;
 };
 
-template <int R>
+template <int R, bool PAIR>
 __global__ void __launch_bounds__(kThreads, 1)
 rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                 const __grid_constant__ GemmParams p) {
@@ -260,8 +324,15 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     const uint32_t tiles_base = (smem_addr(smem_dyn) + 1023u) & ~1023u;
     uint8_t* tiles_ptr = smem_dyn + (tiles_base - smem_addr(smem_dyn));
 
-    const int n0 = blockIdx.x * p.tile_n;
-    const int m0 = blockIdx.y * kTileM;
+    // PAIR: the grid is (row tiles, column tiles) and CTAs (2j, y), (2j+1, y) form a
+    // cluster along x; rank 0 leads.  Each loads and encodes tile_n/2 rows of W
+    // starting at w_row0.  Otherwise the grid is (column tiles, row tiles).
+    const uint32_t pair_rank = PAIR ? cluster_cta_rank() : 0u;
+    const int m_tile = PAIR ? blockIdx.x : blockIdx.y;
+    const int n0 = (PAIR ? blockIdx.y : blockIdx.x) * p.tile_n;
+    const int w_rows = PAIR ? p.tile_n / 2 : p.tile_n;
+    const int w_row0 = n0 + (int)pair_rank * w_rows;
+    const int m0 = m_tile * kTileM;
     const int kblocks = (p.k + p.tile_k - 1) / p.tile_k;
     const int stages = p.stages;
     const bool a_planes = p.a_is_planes != 0;
@@ -279,16 +350,23 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             mbar_init(smem_addr(&ctl.empty_raw[s]), kWorkerWarps);
             mbar_init(smem_addr(&ctl.full_enc[s]), kWorkerWarps + (a_planes ? 1 : 0));
             mbar_init(smem_addr(&ctl.empty_enc[s]), 1);
+            mbar_init(smem_addr(&ctl.peer_ready[s]), 1);
         }
         mbar_init(smem_addr(&ctl.acc_full), 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
-        tmem_alloc(smem_addr(&ctl.tmem_base), (uint32_t)p.tmem_cols);
-        tmem_relinquish();
+        if (PAIR) {
+            tmem_alloc2(smem_addr(&ctl.tmem_base), (uint32_t)p.tmem_cols);
+            tmem_relinquish2();
+        } else {
+            tmem_alloc(smem_addr(&ctl.tmem_base), (uint32_t)p.tmem_cols);
+            tmem_relinquish();
+        }
     }
     tc_fence_before();
-    __syncthreads();
+    // Barriers of both CTAs must exist before the partner signals them.
+    if (PAIR) cluster_sync_all(); else __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = ctl.tmem_base;
     volatile int* abort = &ctl.abort;
@@ -309,10 +387,10 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 if (RNS_ABLATED(3)) {
                 } else if (p.w_packed)
                     bulk_load(stage + p.off_raw_w,
-                              p.w_ptr + ((int64_t)kb * p.w_npad + n0) * kPackK, p.tile_w_bytes, fr);
+                              p.w_ptr + ((int64_t)kb * p.w_npad + w_row0) * kPackK, p.tile_w_bytes, fr);
                 else
-                    tma_load_2d(stage + p.off_raw_w, &map_w, fr, kb * p.tile_k, n0);
-                const int64_t a_tile = (int64_t)blockIdx.y * kblocks + kb;   // packed tile index
+                    tma_load_2d(stage + p.off_raw_w, &map_w, fr, kb * p.tile_k, w_row0);
+                const int64_t a_tile = (int64_t)m_tile * kblocks + kb;   // packed tile index
                 if (!a_planes) {
                     if (p.a_packed)
                         bulk_load(stage + p.off_raw_a, p.a_ptr + a_tile * (kPackM * kPackK), p.tile_a_bytes, fr);
@@ -337,14 +415,25 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         __syncwarp();
     } else if (warp == 1) {
         // ------------------------------ MMA issuer --------------------------------
-        if (lane == 0) {
-            const uint32_t idesc = make_idesc((uint32_t)p.tile_n);
+        // PAIR: only the leader issues MMAs; the peer's lane relays "my stage is
+        // complete" to the leader's peer_ready barrier.  Completion of the MMAs is
+        // signalled to the empty_enc / acc_full barriers of both CTAs.
+        if (lane == 0 && PAIR && pair_rank != 0) {
+            for (int kb = 0; kb < kblocks; ++kb) {
+                const int s = kb % stages;
+                const uint32_t round = (uint32_t)(kb / stages);
+                if (!wait_bounded(smem_addr(&ctl.full_enc[s]), round & 1, abort)) break;
+                mbar_arrive_remote(smem_addr(&ctl.peer_ready[s]), 0);
+            }
+        } else if (lane == 0) {
+            const uint32_t idesc = make_idesc(PAIR ? 256u : 128u, (uint32_t)p.tile_n);
             bool ok = true;
             for (int kb = 0; kb < kblocks && ok; ++kb) {
                 const int s = kb % stages;
                 const uint32_t round = (uint32_t)(kb / stages);
                 const uint32_t stage = tiles_base + (uint32_t)s * p.stage_bytes;
                 ok = wait_bounded(smem_addr(&ctl.full_enc[s]), round & 1, abort);
+                if (ok && PAIR) ok = wait_bounded<true>(smem_addr(&ctl.peer_ready[s]), round & 1, abort);
                 if (!ok) break;
                 tc_fence_after();
                 for (int c = 0; c < (RNS_ABLATED(1) ? 0 : active); ++c) {
@@ -352,21 +441,27 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     const uint32_t w_tile = stage + p.off_enc_w + (uint32_t)c * p.tile_w_bytes;
                     const uint32_t d = tmem_base + (uint32_t)(c * p.tile_n);
                     for (int ks = 0; ks < p.tile_k / 32; ++ks) {
-                        umma_i8(d, make_smem_desc(a_tile + ks * 32, p.tile_k),
-                                make_smem_desc(w_tile + ks * 32, p.tile_k), idesc,
-                                (kb > 0 || ks > 0) ? 1u : 0u);
+                        const uint64_t da = make_smem_desc(a_tile + ks * 32, p.tile_k);
+                        const uint64_t db = make_smem_desc(w_tile + ks * 32, p.tile_k);
+                        const uint32_t acc = (kb > 0 || ks > 0) ? 1u : 0u;
+                        if (PAIR) umma_i8_pair(d, da, db, idesc, acc);
+                        else umma_i8(d, da, db, idesc, acc);
                     }
                 }
-                umma_commit(smem_addr(&ctl.empty_enc[s]));
+                if (PAIR) umma_commit_pair(smem_addr(&ctl.empty_enc[s]));
+                else umma_commit(smem_addr(&ctl.empty_enc[s]));
             }
-            if (ok) umma_commit(smem_addr(&ctl.acc_full));
+            if (ok) {
+                if (PAIR) umma_commit_pair(smem_addr(&ctl.acc_full));
+                else umma_commit(smem_addr(&ctl.acc_full));
+            }
         }
         __syncwarp();
     } else {
         // ------------------------------ encoders ----------------------------------
         const int wt = threadIdx.x - 64;  // 0..255
         const int rows_a = min(kTileM, p.m - m0);
-        const int rows_w = min(p.tile_n, p.n - n0);
+        const int rows_w = max(0, min(w_rows, p.n - w_row0));
         // 16-byte chunks that hold valid rows (row r occupies bytes [r*tile_k, (r+1)*tile_k)
         // of a tile in every swizzle mode).
         const int chunks_a = a_planes ? 0 : rows_a * (p.tile_k / 16);
@@ -503,12 +598,15 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 
     // ------------------------------ teardown ---------------------------------------
     tc_fence_before();
-    __syncthreads();
+    // PAIR: neither CTA may free tensor memory or leave (its shared memory feeds the
+    // partner's MMAs) before both have finished.
+    if (PAIR) cluster_sync_all(); else __syncthreads();
     if (threadIdx.x == 0 && ctl.abort && p.status != nullptr)
         atomicExch(p.status, (int)RNS_ERR_DEVICE_TIMEOUT);
     if (warp == 1) {
         tc_fence_after();
-        tmem_dealloc(tmem_base, (uint32_t)p.tmem_cols);
+        if (PAIR) tmem_dealloc2(tmem_base, (uint32_t)p.tmem_cols);
+        else tmem_dealloc(tmem_base, (uint32_t)p.tmem_cols);
     }
 }
 
@@ -567,7 +665,7 @@ static bool tc_supported(const Plan& pl, int k, int64_t lda, int64_t ldw, const 
     return true;
 }
 
-template <int R>
+template <int R, bool PAIR>
 static int launch(const CUtensorMap& ma, const CUtensorMap& mw, const GemmParams& gp, dim3 grid,
                   size_t smem, cudaStream_t st) {
     // The opt-in shared-memory size is a per-device function attribute: set it on
@@ -577,13 +675,40 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& mw, const GemmParams
     RNS_CUDA_OK(cudaGetDevice(&dev));
     const uint64_t bit = 1ull << (dev & 63);
     if (!(configured.load(std::memory_order_acquire) & bit)) {
-        RNS_CUDA_OK(cudaFuncSetAttribute(rns_gemm_kernel<R>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        RNS_CUDA_OK(cudaFuncSetAttribute(rns_gemm_kernel<R, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          227 * 1024 - 1024));
         configured.fetch_or(bit, std::memory_order_release);
     }
-    rns_gemm_kernel<R><<<grid, kThreads, smem, st>>>(ma, mw, gp);
-    RNS_CUDA_OK(cudaGetLastError());
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    if (PAIR) {
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+    }
+    const cudaError_t rc = cudaLaunchKernelEx(&cfg, rns_gemm_kernel<R, PAIR>, ma, mw, gp);
+    if (rc != cudaSuccess) {
+        int clusters = -1;
+        if (PAIR) cudaOccupancyMaxActiveClusters(&clusters, rns_gemm_kernel<R, PAIR>, &cfg);
+        cudaGetLastError();
+        return fail(RNS_ERR_CUDA, "launch of the RNS GEMM failed: %s (grid %u x %u, smem %zu, pair %d, "
+                    "max active clusters %d)", cudaGetErrorString(rc), grid.x, grid.y, smem, (int)PAIR, clusters);
+    }
     return RNS_OK;
+}
+
+template <int R>
+static int launch_either(bool pair, const CUtensorMap& ma, const CUtensorMap& mw, const GemmParams& gp,
+                         dim3 grid, size_t smem, cudaStream_t st) {
+    return pair ? launch<R, true>(ma, mw, gp, grid, smem, st) : launch<R, false>(ma, mw, gp, grid, smem, st);
 }
 
 }  // namespace rns
@@ -647,7 +772,13 @@ int rns_linear_fused(const rns_linear_args* a, rns_stream_t stream) {
     if (tile_k == 0) tile_k = 64;
     if (tile_k != 64 && tile_k != 128) return fail(RNS_ERR_INVALID_ARGUMENT, "tile_k must be 64 or 128");
     int tile_n = a->tile_n;
-    const int m_tiles = (a->m + kTileM - 1) / kTileM;
+    int m_tiles = (a->m + kTileM - 1) / kTileM;
+    // Pair mode (two CTAs per 256 x tile_n tile): 1 = on, 0 = off, anything else = choose.
+    // It pays when there are enough tiles to fill the GPU twice over.
+    bool pair = a->pair_mode == 1;
+    if (a->pair_mode != 0 && a->pair_mode != 1)
+        pair = m_tiles >= 2 && (int64_t)m_tiles * ((a->n + 127) / 128) >= 2 * 148;
+    if (pair && tile_k == 128) return fail(RNS_ERR_INVALID_ARGUMENT, "pair mode uses tile_k = 64");
     if (tile_n == 0) {
         // Largest tile that still gives every SM a CTA; small problems take the
         // narrowest tile so that more SMs stream the weights.
@@ -658,14 +789,18 @@ int rns_linear_fused(const rns_linear_args* a, rns_stream_t stream) {
             if ((int64_t)m_tiles * ((a->n + c - 1) / c) >= 148) { tile_n = c; break; }
         }
         if (tile_n > max_tile_n) tile_n = max_tile_n;
+        if (pair && tile_n % 32 != 0) tile_n = tile_n + 16 <= max_tile_n ? tile_n + 16 : tile_n - 16;
     }
     if (tile_n < 16 || tile_n > 128 || tile_n % 16 != 0 || tile_n > max_tile_n)
         return fail(RNS_ERR_INVALID_ARGUMENT, "tile_n must be a multiple of 16 in [16, %d]", max_tile_n);
     if (w_packed && kPackNPad % tile_n != 0)
         return fail(RNS_ERR_INVALID_ARGUMENT, "packed weights need a tile_n that divides %d", kPackNPad);
 
+    if (pair && tile_n % 32 != 0)
+        return fail(RNS_ERR_INVALID_ARGUMENT, "pair mode needs tile_n to be a multiple of 32");
+    if (pair) m_tiles = (m_tiles + 1) / 2 * 2;
     gp.tile_a_bytes = kTileM * tile_k;
-    gp.tile_w_bytes = tile_n * tile_k;
+    gp.tile_w_bytes = (pair ? tile_n / 2 : tile_n) * tile_k;
     uint32_t off = 0;
     gp.off_raw_w = off; off += gp.tile_w_bytes;
     gp.off_raw_a = off; if (!planes) off += gp.tile_a_bytes;
@@ -705,7 +840,7 @@ int rns_linear_fused(const rns_linear_args* a, rns_stream_t stream) {
     if (!w_packed) {
         const uint64_t dims[2] = {(uint64_t)a->k, (uint64_t)a->n};
         const uint64_t strides[1] = {(uint64_t)a->ldw};
-        const uint32_t box[2] = {(uint32_t)tile_k, (uint32_t)tile_n};
+        const uint32_t box[2] = {(uint32_t)tile_k, (uint32_t)(pair ? tile_n / 2 : tile_n)};
         if (int rc = make_map(&map_w, a->d_w, 2, dims, strides, box, tile_k)) return rc;
     }
     if (a_packed) {
@@ -722,17 +857,19 @@ int rns_linear_fused(const rns_linear_args* a, rns_stream_t stream) {
         if (int rc = make_map(&map_a, a_base, 2, dims, strides, box, tile_k)) return rc;
     }
 
-    const dim3 grid((a->n + tile_n - 1) / tile_n, m_tiles, 1);
+    const int n_tiles = (a->n + tile_n - 1) / tile_n;
+    if (pair && n_tiles > 65535) return fail(RNS_ERR_UNSUPPORTED, "too many column tiles for pair mode");
+    const dim3 grid = pair ? dim3(m_tiles, n_tiles, 1) : dim3(n_tiles, m_tiles, 1);
     const size_t smem = (size_t)stages * gp.stage_bytes + 1024;
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     switch (R) {
-        case 2: return launch<2>(map_a, map_w, gp, grid, smem, st);
-        case 3: return launch<3>(map_a, map_w, gp, grid, smem, st);
-        case 4: return launch<4>(map_a, map_w, gp, grid, smem, st);
-        case 5: return launch<5>(map_a, map_w, gp, grid, smem, st);
-        case 6: return launch<6>(map_a, map_w, gp, grid, smem, st);
-        case 7: return launch<7>(map_a, map_w, gp, grid, smem, st);
-        case 8: return launch<8>(map_a, map_w, gp, grid, smem, st);
+        case 2: return launch_either<2>(pair, map_a, map_w, gp, grid, smem, st);
+        case 3: return launch_either<3>(pair, map_a, map_w, gp, grid, smem, st);
+        case 4: return launch_either<4>(pair, map_a, map_w, gp, grid, smem, st);
+        case 5: return launch_either<5>(pair, map_a, map_w, gp, grid, smem, st);
+        case 6: return launch_either<6>(pair, map_a, map_w, gp, grid, smem, st);
+        case 7: return launch_either<7>(pair, map_a, map_w, gp, grid, smem, st);
+        case 8: return launch_either<8>(pair, map_a, map_w, gp, grid, smem, st);
         default: return fail(RNS_ERR_UNSUPPORTED, "tensor-core path: channel count outside 2..8");
     }
 }

@@ -40,7 +40,7 @@ def packed_act_offsets(m, k, channels):
 
 
 def fused_int(backend, a, w_nk, mods, *, planes=False, packed=False, plain_weight=False, tile_n=0, tile_k=0,
-              out_dtype=torch.int64, active=None):
+              out_dtype=torch.int64, active=None, pair_mode=2):
     """Direct call of rns_linear_fused on a [M,K] int8 and w [N,K] int8.
     planes: activations as centred planes; packed: activations in the packed tile
     layout; plain_weight: weight through the tensor map instead of the packed copy."""
@@ -51,7 +51,7 @@ def fused_int(backend, a, w_nk, mods, *, planes=False, packed=False, plain_weigh
     out = torch.full((m, w_nk.shape[0]), -7, dtype=out_dtype, device="cuda")
     a_dev = dev(a)
     kwargs = dict(prepared=prepared, m=m, out=out, tile_n=tile_n, tile_k=tile_k, active=active,
-                  plain_weight=w_dev if plain_weight else None)
+                  plain_weight=w_dev if plain_weight else None, pair_mode=pair_mode)
     if planes and packed:
         from rns_llm_b200 import _native as N
         buf = torch.empty(int(N.load().rns_packed_activation_bytes(m, k, len(mods))), dtype=torch.int8, device="cuda")
@@ -61,7 +61,7 @@ def fused_int(backend, a, w_nk, mods, *, planes=False, packed=False, plain_weigh
     elif planes:
         backend._launch_fused(a=None, a_planes=backend.encode_centered(a_dev, mods), **kwargs)
     elif packed:
-        host = np.zeros(((m + 127) // 128) * 128 * ((k + 63) // 64) * 64, dtype=np.int8)
+        host = np.zeros(((m + 255) // 256) * 256 * ((k + 63) // 64) * 64, dtype=np.int8)
         host[packed_act_offsets(m, k, 1)[:, :, 0]] = a
         backend._launch_fused(a=dev(host), a_planes=None, a_packed=True, **kwargs)
     else:
@@ -71,8 +71,12 @@ def fused_int(backend, a, w_nk, mods, *, planes=False, packed=False, plain_weigh
     return out.cpu().numpy()
 
 
-MODES = [dict(), dict(planes=True), dict(packed=True), dict(planes=True, packed=True),
-         dict(plain_weight=True), dict(planes=True, plain_weight=True)]
+# pair_mode=1: two CTAs per 256-row tile (tcgen05 cta_group::2); 0: one CTA per tile
+MODES = [dict(pair_mode=0), dict(planes=True, pair_mode=0), dict(packed=True, pair_mode=0),
+         dict(planes=True, packed=True, pair_mode=0), dict(plain_weight=True, pair_mode=0),
+         dict(planes=True, plain_weight=True, pair_mode=0),
+         dict(pair_mode=1), dict(planes=True, packed=True, pair_mode=1), dict(packed=True, pair_mode=1),
+         dict(planes=True, plain_weight=True, pair_mode=1)]
 
 
 def rand_i8(rng, shape, lo=-127, hi=127):
@@ -116,9 +120,10 @@ def test_tile_shapes(backend, tile_n, tile_k):
     # two moduli hold +-7937: compare modulo P through the oracle's reconstruction
     expect = O.decode_garner(np.stack([exact % 127, exact % 125]), mods)
     # tile_k = 128 exists for plain (tensor-map) operands only
-    assert np.array_equal(fused_int(backend, a, w, mods, tile_n=tile_n, tile_k=tile_k, plain_weight=True), expect)
+    assert np.array_equal(fused_int(backend, a, w, mods, tile_n=tile_n, tile_k=tile_k, plain_weight=True,
+                                    pair_mode=0), expect)
     if tile_k == 64:
-        for mode in MODES[:4]:
+        for mode in MODES[:4] + (MODES[6:] if tile_n % 32 == 0 else []):
             assert np.array_equal(fused_int(backend, a, w, mods, tile_n=tile_n, **mode), expect), mode
 
 
