@@ -109,6 +109,11 @@ RNS_API int rns_host_reconstruct(const int32_t* sums, int64_t count, const int32
                                  int channels, int active, int64_t* out);
 RNS_API int rns_host_encode_centered_i8(const int8_t* values, int64_t count,
                                         const int32_t* moduli, int channels, int8_t* out);
+/*   rns_host_encode_reduced_i8: the fused kernel's default in-kernel encoder:
+ *     one-step reduced residues (x - m for x >= 64, x + m for x < -64, moduli
+ *     above 191 pass through): congruent to x, inside int8, any moduli. */
+RNS_API int rns_host_encode_reduced_i8(const int8_t* values, int64_t count,
+                                       const int32_t* moduli, int channels, int8_t* out);
 
 /* ------------------------------------------------------------------------
  * Plane-level entry points: the six functions of the reference's FFI module
@@ -222,8 +227,8 @@ RNS_API int rns_matmul_centered_fused_out(const int8_t* d_a, const int8_t* d_b,
  * rns_status (RNS_ERR_DEVICE_TIMEOUT) if a bounded wait expires.
  *
  * Requirements of the tensor-core kernel: K % 16 == 0, lda/ldw/a_plane_stride
- * multiples of 16, 16-byte aligned bases, 2 <= channels <= 8, every modulus
- * >= 86 (one fold maps any int8 value to its centred residue).  Anything else
+ * multiples of 16, 16-byte aligned bases, 2 <= channels <= 8 (and every modulus
+ * >= 86 when exact_residues is set).  Anything else
  * returns RNS_ERR_UNSUPPORTED; callers then use the plane-level functions.
  */
 typedef struct rns_linear_args {
@@ -250,6 +255,9 @@ typedef struct rns_linear_args {
     int32_t a_packed;         /* 1: d_a / d_a_planes is in the packed tile layout */
     int32_t w_packed;         /* 1: d_w is in the packed tile layout (rns_pack_weight) */
     int32_t pair_mode;        /* 1: two-CTA tiles (256 x tile_n), 0: one CTA per tile, 2: choose */
+    int32_t enc_groups;       /* 0 = choose; else 1, 2 or 4 groups of encoder warps */
+    int32_t exact_residues;   /* 1: in-kernel residues exactly centred (|r| <= m/2; needs every
+                                 modulus >= 86); 0: one-step reduced residues (any moduli) */
 } rns_linear_args;
 
 RNS_API int rns_linear_fused(const rns_linear_args* args, rns_stream_t stream);

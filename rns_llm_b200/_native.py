@@ -56,6 +56,8 @@ class LinearArgs(C.Structure):
         ("a_packed", C.c_int32),
         ("w_packed", C.c_int32),
         ("pair_mode", C.c_int32),
+        ("enc_groups", C.c_int32),
+        ("exact_residues", C.c_int32),
     ]
 
 
@@ -71,6 +73,7 @@ SIGNATURES: dict[str, tuple] = {
     "rns_minimal_prefix_channels": (C.c_int, [_I32P, C.c_int, C.c_int64, C.c_int]),
     "rns_host_reconstruct": (C.c_int, [_VP, C.c_int64, _I32P, C.c_int, C.c_int, _VP]),
     "rns_host_encode_centered_i8": (C.c_int, [_VP, C.c_int64, _I32P, C.c_int, _VP]),
+    "rns_host_encode_reduced_i8": (C.c_int, [_VP, C.c_int64, _I32P, C.c_int, _VP]),
     "rns_encode_canonical_i8": (C.c_int, [_VP, C.c_int64, _I32P, C.c_int, _VP, _VP]),
     "rns_encode_centered": (C.c_int, [_VP, C.c_int, C.c_int64, _I32P, C.c_int, _VP, _VP]),
     "rns_matmul_canonical_planes": (C.c_int, [_VP, _VP, _I32P, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _VP, _VP]),

@@ -335,7 +335,7 @@ class CudaRNSBackend:
 
     def tensor_core_compatible(self, *, k: int, moduli: Iterable[int]) -> bool:
         """True when int8 sources with this K and these moduli run on the
-        tcgen05 kernel: K % 16 == 0, 2..8 channels, every modulus >= 86."""
+        tcgen05 kernel: K % 16 == 0, 2..8 channels, int32-safe channel sums."""
         mods, arr = self._mods(moduli)
         return bool(self._lib.rns_linear_fused_supported(arr, len(mods), int(k), int(k), int(k))) and (
             int(k) * 127 * 127 <= 0x7FFFFFFF
@@ -560,7 +560,8 @@ class CudaRNSBackend:
                       active: torch.Tensor | None = None, row_scale: torch.Tensor | None = None,
                       row_scale_stride: int = 0, col_scale: torch.Tensor | None = None,
                       bias: torch.Tensor | None = None, tile_n: int = 0, tile_k: int = 0,
-                      plain_weight: torch.Tensor | None = None, pair_mode: int = 2) -> None:
+                      plain_weight: torch.Tensor | None = None, pair_mode: int = 2,
+                      enc_groups: int = 0, exact_residues: bool = False) -> None:
         """Fills ``rns_linear_args`` and launches.  ``a`` / ``a_planes`` are plain
         ([M,K] / [R,M,K]) unless ``a_packed``; the weight is the prepared packed
         copy unless ``plain_weight`` ([N,K] int8) is given."""
@@ -599,6 +600,8 @@ class CudaRNSBackend:
         args.d_status = self._state(device).status.data_ptr()
         args.tile_n, args.tile_k = tile_n, tile_k
         args.pair_mode = pair_mode
+        args.enc_groups = enc_groups
+        args.exact_residues = 1 if exact_residues else 0
         N.check(self._lib.rns_linear_fused(C.byref(args), self._stream(device)))
 
     def matmul_prepared_fused(self, a: torch.Tensor, prepared_weight: PreparedRNSWeight, *,

@@ -60,6 +60,7 @@ struct Plan {
     uint32_t enc_lo[kMaxCh];
     uint32_t enc_mk[kMaxCh];       // m << 25 when encode_fast, else m
     int32_t encode_fast;           // every modulus < 128
+    uint32_t enc_mfold[kMaxCh];    // reduced encoder: m if m <= 191 else 0
     int32_t encode_single_fold;    // every modulus >= 86
 };
 
@@ -253,6 +254,27 @@ RNS_HD uint32_t encode_word(uint32_t u, uint32_t ul, uint32_t hi, uint32_t lo, u
     if (FAST) v = mul_hi_u32(up, mk) + u - mul_hi_u32(down, mk);
     else v = u + ((up >> 7) - (down >> 7)) * mk;
     return v ^ 0x80808080u;
+}
+
+// One-step reduced residues of four packed int8 values, the default encoder of
+// the fused kernel.  A value is folded once, towards zero, when its two top bits
+// differ (x >= 64 or x < -64):  r = x - m for x >= 64,  r = x + m for x < -64,
+// r = x otherwise, for every modulus m <= 191 (larger moduli, whose residues of
+// int8 values need no fold below 96, pass through: mfold = 0).  r is congruent to
+// x and fits a signed byte for every modulus in [2,255]; for the moduli just
+// below 128 it is the centred residue except within a few units of +-64
+// (|r| <= 64 instead of <= m/2), which is all the int32 accumulation and the
+// reconstruction need.  The fold pattern does not depend on the modulus, so it
+// is computed once per word (fold_pattern) and each channel costs one
+// multiply-add and one xor.
+//   u = x ^ 0x80808080 (bytes biased by 128);  d = per-byte +1 / -1 / 0 pattern
+RNS_HD uint32_t fold_pattern(uint32_t x) {
+    const uint32_t f = (x ^ (x << 1)) & 0x80808080u;   // bit 7: top two bits differ
+    const uint32_t up = f & x;                          // negative: add m
+    return (up >> 6) - (f >> 7);                        // 2*up7 - f7 = up7 - down7
+}
+RNS_HD uint32_t encode_word_reduced(uint32_t u, uint32_t d, uint32_t mfold) {
+    return (u + d * mfold) ^ 0x80808080u;
 }
 
 }  // namespace rns

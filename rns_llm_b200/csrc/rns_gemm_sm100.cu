@@ -7,8 +7,8 @@
 // the MMAs, and each CTA's tensor memory receives its own 128 rows.  Pairing
 // halves the W bytes every SM has to load, encode and feed to the tensor core.
 //
-// Warp roles (576 threads):
-//   warp 0      TMA producer (one elected lane)
+// Warp roles (608 threads):
+//   warp 0, 18  load producers (one elected lane each; even / odd K blocks)
 //   warp 1      TMEM owner + MMA issuer (one elected lane)
 //   warps 2..17 encoders during the K loop, epilogue afterwards
 //
@@ -44,11 +44,15 @@ static int g_ablate = 0;
 #endif
 
 constexpr int kTileM = 128;
-constexpr int kWorkerWarps = 16;
-constexpr int kThreads = 64 + kWorkerWarps * 32;
+#ifndef RNS_WORKER_WARPS
+#define RNS_WORKER_WARPS 16
+#endif
+constexpr int kWorkerWarps = RNS_WORKER_WARPS;
+constexpr int kProducerWarpB = 2 + kWorkerWarps;          // second load producer
+constexpr int kThreads = (3 + kWorkerWarps) * 32;
 constexpr int kWorkerThreads = kWorkerWarps * 32;
 constexpr int kMaxStages = 6;
-constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s
+constexpr long long kWaitLimitCycles = 4000000000ll;  // about 2 s of SM clock
 
 struct GemmParams {
     Plan plan;
@@ -63,6 +67,10 @@ struct GemmParams {
     const int8_t* w_ptr;          // packed weights
     int64_t w_npad;               // padded weight rows of the packed layout
     int32_t tmem_cols;
+    int32_t exact_residues;       // in-kernel encoder: exactly centred (1) or one-step reduced (0)
+    int32_t enc_groups;           // worker warps are split into this many groups; group g encodes
+                                  // the K blocks kb = g (mod groups), so that the fixed cost of a
+                                  // stage hand-over overlaps with another group's encoding
     const int32_t* active_ptr;
     void* out;
     int64_t ldo;
@@ -98,6 +106,18 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
         "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Non-blocking test of a phase (never suspends the thread).
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
         : "r"(bar), "r"(parity)
@@ -256,16 +276,24 @@ __device__ __forceinline__ uint32_t make_idesc(uint32_t m, uint32_t n) {
 
 // Waits for `parity` of `bar`; false (and *abort set) when the time limit passes
 // or another thread of the CTA already gave up.
-template <bool CLUSTER = false>
+// SPIN: poll with test_wait instead of the suspending try_wait; for the single
+// threads whose wake-up latency is on the critical path of every K block.
+template <bool CLUSTER = false, bool SPIN = false>
 __device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity, volatile int* abort) {
-    auto poll = [&]() { return CLUSTER ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity); };
-    if (poll()) return true;
-    const uint64_t t0 = global_timer_ns();
+    auto poll = [&]() {
+        return CLUSTER ? mbar_try_wait_cluster(bar, parity)
+                       : (SPIN ? mbar_test_wait(bar, parity) : mbar_try_wait(bar, parity));
+    };
+    // Fast path: no clock is read unless the wait keeps failing (reading the global
+    // timer costs hundreds of cycles, which every blocked wait would otherwise pay).
+    for (int i = 0; i < 64; ++i)
+        if (poll()) return true;
+    long long t0 = clock64();
     for (uint32_t spin = 1;; ++spin) {
         if (poll()) return true;
         if ((spin & 255u) == 0) {
             if (*abort) return false;
-            if (global_timer_ns() - t0 > kWaitLimitNs) {
+            if (clock64() - t0 > kWaitLimitCycles) {
                 *abort = 1;
                 return false;
             }
@@ -277,10 +305,10 @@ __device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity, vola
 // the R operand tiles.  ALL: every channel is active (no per-channel branch).
 template <int R, bool FAST, bool ALL>
 __device__ __forceinline__ void encode_chunks(const uint8_t* raw, uint8_t* enc, uint32_t tile_bytes,
-                                              int chunks, int wt, int active,
+                                              int chunks, int wt, int stride, int active,
                                               const uint32_t (&enc_hi)[R], const uint32_t (&enc_lo)[R],
                                               const uint32_t (&enc_mk)[R]) {
-    for (int ch = wt; ch < chunks; ch += kWorkerThreads) {
+    for (int ch = wt; ch < chunks; ch += stride) {
         const uint4 x = *reinterpret_cast<const uint4*>(raw + ch * 16);
         const uint32_t u0 = x.x ^ 0x80808080u, u1 = x.y ^ 0x80808080u;
         const uint32_t u2 = x.z ^ 0x80808080u, u3 = x.w ^ 0x80808080u;
@@ -301,9 +329,34 @@ __device__ __forceinline__ void encode_chunks(const uint8_t* raw, uint8_t* enc, 
     }
 }
 
+// Same, with the one-step reduced encoder (fold pattern shared by all channels).
+template <int R, bool ALL>
+__device__ __forceinline__ void encode_chunks_reduced(const uint8_t* raw, uint8_t* enc, uint32_t tile_bytes,
+                                                      int chunks, int wt, int stride, int active,
+                                                      const uint32_t (&mfold)[R]) {
+    for (int ch = wt; ch < chunks; ch += stride) {
+        const uint4 x = *reinterpret_cast<const uint4*>(raw + ch * 16);
+        const uint32_t u0 = x.x ^ 0x80808080u, u1 = x.y ^ 0x80808080u;
+        const uint32_t u2 = x.z ^ 0x80808080u, u3 = x.w ^ 0x80808080u;
+        const uint32_t d0 = fold_pattern(x.x), d1 = fold_pattern(x.y);
+        const uint32_t d2 = fold_pattern(x.z), d3 = fold_pattern(x.w);
+        uint8_t* dst = enc + ch * 16;
+#pragma unroll
+        for (int c = 0; c < R; ++c) {
+            if (ALL || c < active) {
+                uint4 y;
+                y.x = encode_word_reduced(u0, d0, mfold[c]);
+                y.y = encode_word_reduced(u1, d1, mfold[c]);
+                y.z = encode_word_reduced(u2, d2, mfold[c]);
+                y.w = encode_word_reduced(u3, d3, mfold[c]);
+                *reinterpret_cast<uint4*>(dst + (size_t)c * tile_bytes) = y;
+            }
+        }
+    }
+}
+
 struct __align__(8) SharedCtl {
-    uint64_t full_raw[kMaxStages];
-    uint64_t empty_raw[kMaxStages];
+    uint64_t full_raw[kMaxStages];    // all loads of the stage have landed
     uint64_t full_enc[kMaxStages];
     uint64_t empty_enc[kMaxStages];
     uint64_t acc_full;
@@ -324,12 +377,13 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     const uint32_t tiles_base = (smem_addr(smem_dyn) + 1023u) & ~1023u;
     uint8_t* tiles_ptr = smem_dyn + (tiles_base - smem_addr(smem_dyn));
 
-    // PAIR: the grid is (row tiles, column tiles) and CTAs (2j, y), (2j+1, y) form a
-    // cluster along x; rank 0 leads.  Each loads and encodes tile_n/2 rows of W
-    // starting at w_row0.  Otherwise the grid is (column tiles, row tiles).
+    // Grid: x walks the column tiles fastest, so that CTAs resident at the same time
+    // share their A tiles in L2.  PAIR: x = 2 * column tile + rank (the two CTAs of a
+    // cluster are neighbours in x), y = pair of row tiles; rank 0 leads.  Each CTA of
+    // a pair loads and encodes tile_n/2 rows of W starting at w_row0.
     const uint32_t pair_rank = PAIR ? cluster_cta_rank() : 0u;
-    const int m_tile = PAIR ? blockIdx.x : blockIdx.y;
-    const int n0 = (PAIR ? blockIdx.y : blockIdx.x) * p.tile_n;
+    const int m_tile = PAIR ? 2 * (int)blockIdx.y + (int)pair_rank : (int)blockIdx.y;
+    const int n0 = (PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x) * p.tile_n;
     const int w_rows = PAIR ? p.tile_n / 2 : p.tile_n;
     const int w_row0 = n0 + (int)pair_rank * w_rows;
     const int m0 = m_tile * kTileM;
@@ -347,8 +401,7 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         ctl.abort = 0;
         for (int s = 0; s < stages; ++s) {
             mbar_init(smem_addr(&ctl.full_raw[s]), 1);
-            mbar_init(smem_addr(&ctl.empty_raw[s]), kWorkerWarps);
-            mbar_init(smem_addr(&ctl.full_enc[s]), kWorkerWarps + (a_planes ? 1 : 0));
+            mbar_init(smem_addr(&ctl.full_enc[s]), kWorkerWarps / p.enc_groups);
             mbar_init(smem_addr(&ctl.empty_enc[s]), 1);
             mbar_init(smem_addr(&ctl.peer_ready[s]), 1);
         }
@@ -371,19 +424,23 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     const uint32_t tmem_base = ctl.tmem_base;
     volatile int* abort = &ctl.abort;
 
-    if (warp == 0) {
-        // ------------------------------ TMA producer ------------------------------
+    if (warp == 0 || warp == kProducerWarpB) {
+        // ------------------------------ load producers ----------------------------
+        // Two producer threads (one lane of warp 0 and one of the last warp) take the
+        // even and the odd K blocks: a stage hand-over is a chain of dependent
+        // shared-memory barrier operations, several hundred cycles for one thread.
+        // A stage (raw tiles and operand tiles alike) is free once the MMAs of its
+        // previous round have completed; all bytes of a stage land on full_raw.
         if (lane == 0) {
-            const uint32_t raw_bytes = p.tile_w_bytes + (a_planes ? 0u : p.tile_a_bytes);
-            for (int kb = 0; kb < kblocks; ++kb) {
+            const uint32_t a_bytes = a_planes ? (uint32_t)active * p.tile_a_bytes : p.tile_a_bytes;
+            const uint32_t stage_tx = (RNS_ABLATED(3) ? 0u : p.tile_w_bytes) + (RNS_ABLATED(2) ? 0u : a_bytes);
+            for (int kb = (warp == 0 ? 0 : 1); kb < kblocks; kb += 2) {
                 const int s = kb % stages;
                 const uint32_t round = (uint32_t)(kb / stages);
                 const uint32_t stage = tiles_base + (uint32_t)s * p.stage_bytes;
-                // A slot is free once its previous round has been consumed;
-                // the first round needs no wait.
-                if (round > 0 && !wait_bounded(smem_addr(&ctl.empty_raw[s]), (round - 1) & 1, abort)) break;
+                if (round > 0 && !wait_bounded<false, true>(smem_addr(&ctl.empty_enc[s]), (round - 1) & 1, abort)) break;
                 const uint32_t fr = smem_addr(&ctl.full_raw[s]);
-                mbar_arrive_expect_tx(fr, RNS_ABLATED(3) ? (a_planes ? 0u : p.tile_a_bytes) : raw_bytes);
+                mbar_arrive_expect_tx(fr, stage_tx);
                 if (RNS_ABLATED(3)) {
                 } else if (p.w_packed)
                     bulk_load(stage + p.off_raw_w,
@@ -391,24 +448,18 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 else
                     tma_load_2d(stage + p.off_raw_w, &map_w, fr, kb * p.tile_k, w_row0);
                 const int64_t a_tile = (int64_t)m_tile * kblocks + kb;   // packed tile index
-                if (!a_planes) {
+                if (RNS_ABLATED(2)) {
+                } else if (!a_planes) {
                     if (p.a_packed)
                         bulk_load(stage + p.off_raw_a, p.a_ptr + a_tile * (kPackM * kPackK), p.tile_a_bytes, fr);
                     else
                         tma_load_2d(stage + p.off_raw_a, &map_a, fr, kb * p.tile_k, m0);
+                } else if (p.a_packed) {
+                    bulk_load(stage + p.off_enc_a, p.a_ptr + a_tile * ((int64_t)R * kPackM * kPackK), a_bytes, fr);
                 } else {
-                    if (round > 0 && !wait_bounded(smem_addr(&ctl.empty_enc[s]), (round - 1) & 1, abort)) break;
-                    const uint32_t fe = smem_addr(&ctl.full_enc[s]);
-                    mbar_arrive_expect_tx(fe, RNS_ABLATED(2) ? 0u : (uint32_t)active * p.tile_a_bytes);
-                    if (RNS_ABLATED(2)) {
-                    } else if (p.a_packed) {
-                        bulk_load(stage + p.off_enc_a, p.a_ptr + a_tile * ((int64_t)R * kPackM * kPackK),
-                                  (uint32_t)active * p.tile_a_bytes, fe);
-                    } else {
-                        for (int c = 0; c < active; ++c)
-                            tma_load_3d(stage + p.off_enc_a + (uint32_t)c * p.tile_a_bytes, &map_a, fe,
-                                        kb * p.tile_k, m0, c);
-                    }
+                    for (int c = 0; c < active; ++c)
+                        tma_load_3d(stage + p.off_enc_a + (uint32_t)c * p.tile_a_bytes, &map_a, fr,
+                                    kb * p.tile_k, m0, c);
                 }
             }
         }
@@ -422,7 +473,7 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             for (int kb = 0; kb < kblocks; ++kb) {
                 const int s = kb % stages;
                 const uint32_t round = (uint32_t)(kb / stages);
-                if (!wait_bounded(smem_addr(&ctl.full_enc[s]), round & 1, abort)) break;
+                if (!wait_bounded<false, true>(smem_addr(&ctl.full_enc[s]), round & 1, abort)) break;
                 mbar_arrive_remote(smem_addr(&ctl.peer_ready[s]), 0);
             }
         } else if (lane == 0) {
@@ -432,10 +483,10 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 const int s = kb % stages;
                 const uint32_t round = (uint32_t)(kb / stages);
                 const uint32_t stage = tiles_base + (uint32_t)s * p.stage_bytes;
-                ok = wait_bounded(smem_addr(&ctl.full_enc[s]), round & 1, abort);
+                ok = wait_bounded<false, true>(smem_addr(&ctl.full_enc[s]), round & 1, abort);
                 if (ok && PAIR) ok = wait_bounded<true>(smem_addr(&ctl.peer_ready[s]), round & 1, abort);
                 if (!ok) break;
-                tc_fence_after();
+                if (!RNS_ABLATED(6)) tc_fence_after();
                 for (int c = 0; c < (RNS_ABLATED(1) ? 0 : active); ++c) {
                     const uint32_t a_tile = stage + p.off_enc_a + (uint32_t)c * p.tile_a_bytes;
                     const uint32_t w_tile = stage + p.off_enc_w + (uint32_t)c * p.tile_w_bytes;
@@ -448,7 +499,8 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                         else umma_i8(d, da, db, idesc, acc);
                     }
                 }
-                if (PAIR) umma_commit_pair(smem_addr(&ctl.empty_enc[s]));
+                if (RNS_ABLATED(5) && !PAIR) mbar_arrive(smem_addr(&ctl.empty_enc[s]));
+                else if (PAIR) umma_commit_pair(smem_addr(&ctl.empty_enc[s]));
                 else umma_commit(smem_addr(&ctl.empty_enc[s]));
             }
             if (ok) {
@@ -459,48 +511,58 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         __syncwarp();
     } else {
         // ------------------------------ encoders ----------------------------------
-        const int wt = threadIdx.x - 64;  // 0..255
+        const int groups = p.enc_groups;
+        const int group = (warp - 2) % groups;
+        const int group_threads = kWorkerThreads / groups;
+        const int wt = ((warp - 2) / groups) * 32 + lane;   // index inside the group
         const int rows_a = min(kTileM, p.m - m0);
         const int rows_w = max(0, min(w_rows, p.n - w_row0));
         // 16-byte chunks that hold valid rows (row r occupies bytes [r*tile_k, (r+1)*tile_k)
         // of a tile in every swizzle mode).
         const int chunks_a = a_planes ? 0 : rows_a * (p.tile_k / 16);
         const int chunks_w = rows_w * (p.tile_k / 16);
-        uint32_t enc_hi[R], enc_lo[R], enc_mk[R];
+        uint32_t enc_hi[R], enc_lo[R], enc_mk[R], enc_mfold[R];
 #pragma unroll
         for (int c = 0; c < R; ++c) {
             enc_hi[c] = p.plan.enc_hi[c]; enc_lo[c] = p.plan.enc_lo[c]; enc_mk[c] = p.plan.enc_mk[c];
+            enc_mfold[c] = p.plan.enc_mfold[c];
         }
+        const bool reduced = p.exact_residues == 0;
         const bool fast = p.plan.encode_fast != 0;
         bool ok = true;
-        for (int kb = 0; kb < kblocks && ok; ++kb) {
+        for (int kb = group; kb < kblocks && ok; kb += groups) {
             const int s = kb % stages;
             const uint32_t round = (uint32_t)(kb / stages);
             uint8_t* stage = tiles_ptr + (size_t)s * p.stage_bytes;
-            ok = wait_bounded(smem_addr(&ctl.full_raw[s]), round & 1, abort);
-            if (ok && round > 0) ok = wait_bounded(smem_addr(&ctl.empty_enc[s]), (round - 1) & 1, abort);
+            // Order matters once several groups run ahead of each other: the stage must
+            // first be released by the MMAs of its previous round (which also proves
+            // that full_raw has completed that round), only then is the parity of the
+            // full_raw wait unambiguous.
+            if (round > 0) ok = wait_bounded(smem_addr(&ctl.empty_enc[s]), (round - 1) & 1, abort);
+            if (ok) ok = wait_bounded(smem_addr(&ctl.full_raw[s]), round & 1, abort);
             if (!ok) break;
             for (int part = 0; part < (RNS_ABLATED(0) ? 0 : 2); ++part) {
                 const int chunks = part == 0 ? chunks_w : chunks_a;
                 const uint8_t* raw = stage + (part == 0 ? p.off_raw_w : p.off_raw_a);
                 uint8_t* enc = stage + (part == 0 ? p.off_enc_w : p.off_enc_a);
                 const uint32_t tile_bytes = part == 0 ? p.tile_w_bytes : p.tile_a_bytes;
-                if (fast && active == R)
-                    encode_chunks<R, true, true>(raw, enc, tile_bytes, chunks, wt, active, enc_hi, enc_lo, enc_mk);
+                if (reduced && active == R)
+                    encode_chunks_reduced<R, true>(raw, enc, tile_bytes, chunks, wt, group_threads, active, enc_mfold);
+                else if (reduced)
+                    encode_chunks_reduced<R, false>(raw, enc, tile_bytes, chunks, wt, group_threads, active, enc_mfold);
+                else if (fast && active == R)
+                    encode_chunks<R, true, true>(raw, enc, tile_bytes, chunks, wt, group_threads, active, enc_hi, enc_lo, enc_mk);
                 else if (fast)
-                    encode_chunks<R, true, false>(raw, enc, tile_bytes, chunks, wt, active, enc_hi, enc_lo, enc_mk);
+                    encode_chunks<R, true, false>(raw, enc, tile_bytes, chunks, wt, group_threads, active, enc_hi, enc_lo, enc_mk);
                 else
-                    encode_chunks<R, false, false>(raw, enc, tile_bytes, chunks, wt, active, enc_hi, enc_lo, enc_mk);
+                    encode_chunks<R, false, false>(raw, enc, tile_bytes, chunks, wt, group_threads, active, enc_hi, enc_lo, enc_mk);
             }
             // Every writer makes its stores visible to the async proxy, the warp
             // converges, and one lane signals for the warp: 16 arrivals per stage
             // instead of 512 (arrivals on one mbarrier serialise).
-            fence_proxy_async_smem();
+            if (!RNS_ABLATED(7)) fence_proxy_async_smem();
             __syncwarp();
-            if (lane == 0) {
-                mbar_arrive(smem_addr(&ctl.full_enc[s]));
-                mbar_arrive(smem_addr(&ctl.empty_raw[s]));
-            }
+            if (lane == 0) mbar_arrive(smem_addr(&ctl.full_enc[s]));
         }
 
         // ------------------------------ epilogue ----------------------------------
@@ -657,9 +719,9 @@ static int round_up_pow2(int v) {
     return r;
 }
 
-static bool tc_supported(const Plan& pl, int k, int64_t lda, int64_t ldw, const char** why) {
+static bool tc_supported(const Plan& pl, int k, int64_t lda, int64_t ldw, bool exact, const char** why) {
     if (pl.channels < 2 || pl.channels > RNS_TC_MAX_CHANNELS) { *why = "channel count outside 2..8"; return false; }
-    if (!pl.encode_single_fold) { *why = "a modulus below 86 needs more than one fold"; return false; }
+    if (exact && !pl.encode_single_fold) { *why = "exactly centred residues need every modulus >= 86"; return false; }
     if (k <= 0 || k % 16 != 0) { *why = "K must be a positive multiple of 16"; return false; }
     if (lda % 16 != 0 || ldw % 16 != 0) { *why = "row strides must be multiples of 16 bytes"; return false; }
     return true;
@@ -725,7 +787,7 @@ int rns_linear_fused_supported(const int32_t* moduli, int channels, int k, int64
     Plan pl;
     if (build_plan(moduli, channels, &pl) != RNS_OK) return 0;
     const char* why = "";
-    return tc_supported(pl, k, lda, ldw, &why) ? 1 : 0;
+    return tc_supported(pl, k, lda, ldw, false, &why) ? 1 : 0;
 }
 
 int rns_linear_fused(const rns_linear_args* a, rns_stream_t stream) {
@@ -756,7 +818,7 @@ int rns_linear_fused(const rns_linear_args* a, rns_stream_t stream) {
     if (a->out_type == RNS_OUT_INT32 && (pl.product[R] >> 1) >= (1ll << 31))
         return fail(RNS_ERR_OVERFLOW, "int32 output needs product(moduli)/2 < 2^31");
     const char* why = "";
-    if (!tc_supported(pl, a->k, a_packed ? 16 : a->lda, w_packed ? 16 : a->ldw, &why))
+    if (!tc_supported(pl, a->k, a_packed ? 16 : a->lda, w_packed ? 16 : a->ldw, a->exact_residues != 0, &why))
         return fail(RNS_ERR_UNSUPPORTED, "tensor-core path: %s", why);
     if ((a_packed || w_packed) && a->tile_k == 128)
         return fail(RNS_ERR_INVALID_ARGUMENT, "packed operands use tile_k = 64");
@@ -816,11 +878,17 @@ int rns_linear_fused(const rns_linear_args* a, rns_stream_t stream) {
     if (stages < 2 && kblocks > 1 && tile_k == 128)
         return fail(RNS_ERR_UNSUPPORTED, "tile_k=128 leaves room for one stage only; use tile_k=64");
     gp.stages = stages;
+    gp.enc_groups = a->enc_groups > 0 ? a->enc_groups : (stages >= 5 ? 4 : (stages >= 3 ? 2 : 1));
+    if (gp.enc_groups != 1 && gp.enc_groups != 2 && gp.enc_groups != 4)
+        return fail(RNS_ERR_INVALID_ARGUMENT, "enc_groups must be 1, 2 or 4");
+    // A group works one ring revolution ahead of the next at most: never more groups than stages.
+    while (gp.enc_groups > stages) gp.enc_groups /= 2;
     gp.m = a->m; gp.n = a->n; gp.k = a->k;
     gp.tile_n = tile_n; gp.tile_k = tile_k;
 #ifdef RNS_ABLATION
     gp.ablate = g_ablate;
 #endif
+    gp.exact_residues = a->exact_residues ? 1 : 0;
     gp.a_is_planes = planes ? 1 : 0;
     gp.a_packed = a_packed ? 1 : 0;
     gp.w_packed = w_packed ? 1 : 0;
@@ -858,8 +926,7 @@ int rns_linear_fused(const rns_linear_args* a, rns_stream_t stream) {
     }
 
     const int n_tiles = (a->n + tile_n - 1) / tile_n;
-    if (pair && n_tiles > 65535) return fail(RNS_ERR_UNSUPPORTED, "too many column tiles for pair mode");
-    const dim3 grid = pair ? dim3(m_tiles, n_tiles, 1) : dim3(n_tiles, m_tiles, 1);
+    const dim3 grid = pair ? dim3(2 * n_tiles, m_tiles / 2, 1) : dim3(n_tiles, m_tiles, 1);
     const size_t smem = (size_t)stages * gp.stage_bytes + 1024;
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     switch (R) {

@@ -83,6 +83,7 @@ int build_plan(const int32_t* moduli, int channels, Plan* out) {
     p.encode_fast = 1;
     for (int i = 0; i < channels; ++i)
         if (p.mod[i] >= 128) p.encode_fast = 0;
+    for (int i = 0; i < channels; ++i) p.enc_mfold[i] = p.mod[i] <= 191 ? (uint32_t)p.mod[i] : 0u;
     for (int i = 0; i < channels; ++i)
         p.enc_mk[i] = p.encode_fast ? (uint32_t)p.mod[i] << 25 : (uint32_t)p.mod[i];
     for (int i = 0; i < channels; ++i) {
@@ -179,6 +180,24 @@ int rns_host_encode_centered_i8(const int8_t* values, int64_t count, const int32
             const uint32_t y = plan.encode_fast
                 ? rns::encode_word<true>(u, ul, plan.enc_hi[c], plan.enc_lo[c], plan.enc_mk[c])
                 : rns::encode_word<false>(u, ul, plan.enc_hi[c], plan.enc_lo[c], plan.enc_mk[c]);
+            memcpy(out + (int64_t)c * count + i, &y, 4);
+        }
+    }
+    return RNS_OK;
+}
+
+int rns_host_encode_reduced_i8(const int8_t* values, int64_t count, const int32_t* moduli,
+                               int channels, int8_t* out) {
+    rns::Plan plan;
+    if (int rc = rns::build_plan(moduli, channels, &plan)) return rc;
+    if (!values || !out || count < 0 || count % 4 != 0)
+        return rns::fail(RNS_ERR_INVALID_ARGUMENT, "host_encode: count must be a multiple of 4");
+    for (int64_t i = 0; i < count; i += 4) {
+        uint32_t x;
+        memcpy(&x, values + i, 4);
+        const uint32_t u = x ^ 0x80808080u, d = rns::fold_pattern(x);
+        for (int c = 0; c < channels; ++c) {
+            const uint32_t y = rns::encode_word_reduced(u, d, plan.enc_mfold[c]);
             memcpy(out + (int64_t)c * count + i, &y, 4);
         }
     }

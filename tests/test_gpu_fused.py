@@ -40,7 +40,7 @@ def packed_act_offsets(m, k, channels):
 
 
 def fused_int(backend, a, w_nk, mods, *, planes=False, packed=False, plain_weight=False, tile_n=0, tile_k=0,
-              out_dtype=torch.int64, active=None, pair_mode=2):
+              out_dtype=torch.int64, active=None, pair_mode=2, exact_residues=False):
     """Direct call of rns_linear_fused on a [M,K] int8 and w [N,K] int8.
     planes: activations as centred planes; packed: activations in the packed tile
     layout; plain_weight: weight through the tensor map instead of the packed copy."""
@@ -51,7 +51,8 @@ def fused_int(backend, a, w_nk, mods, *, planes=False, packed=False, plain_weigh
     out = torch.full((m, w_nk.shape[0]), -7, dtype=out_dtype, device="cuda")
     a_dev = dev(a)
     kwargs = dict(prepared=prepared, m=m, out=out, tile_n=tile_n, tile_k=tile_k, active=active,
-                  plain_weight=w_dev if plain_weight else None, pair_mode=pair_mode)
+                  plain_weight=w_dev if plain_weight else None, pair_mode=pair_mode,
+                  exact_residues=exact_residues)
     if planes and packed:
         from rns_llm_b200 import _native as N
         buf = torch.empty(int(N.load().rns_packed_activation_bytes(m, k, len(mods))), dtype=torch.int8, device="cuda")
@@ -76,7 +77,8 @@ MODES = [dict(pair_mode=0), dict(planes=True, pair_mode=0), dict(packed=True, pa
          dict(planes=True, packed=True, pair_mode=0), dict(plain_weight=True, pair_mode=0),
          dict(planes=True, plain_weight=True, pair_mode=0),
          dict(pair_mode=1), dict(planes=True, packed=True, pair_mode=1), dict(packed=True, pair_mode=1),
-         dict(planes=True, plain_weight=True, pair_mode=1)]
+         dict(planes=True, plain_weight=True, pair_mode=1),
+         dict(pair_mode=0, exact_residues=True), dict(packed=True, pair_mode=1, exact_residues=True)]
 
 
 def rand_i8(rng, shape, lo=-127, hi=127):
@@ -128,7 +130,8 @@ def test_tile_shapes(backend, tile_n, tile_k):
 
 
 @pytest.mark.parametrize("mods", [(127, 125), (127, 126, 125), C0, C4, (127, 126, 125, 121, 113, 109),
-                                  (255, 253, 251, 247), (127, 125, 123, 121, 119, 113, 109, 107)])
+                                  (255, 253, 251, 247), (127, 125, 123, 121, 119, 113, 109, 107),
+                                  (3, 5, 7, 11, 13, 17, 19, 23), (191, 193, 85, 64)])
 def test_channel_counts(backend, mods):
     rng = np.random.default_rng(len(mods))
     k = 16384 if mods == C4 else 256
@@ -139,7 +142,10 @@ def test_channel_counts(backend, mods):
         expect = exact
     else:
         expect = O.decode_garner(np.stack([exact % m for m in mods]), mods)
+    single_fold = min(mods) >= 86
     for mode in MODES:
+        if mode.get("exact_residues") and not single_fold:
+            continue
         assert np.array_equal(fused_int(backend, a, w, mods, **mode), expect), mode
 
 
@@ -378,11 +384,17 @@ def test_fused_argument_errors(backend):
     prepared2 = backend.prepare_weight(dev(b2), C0)
     assert prepared2.kernel == "cublas"
     assert np.array_equal(backend.matmul_prepared_fused(dev(a2), prepared2).cpu().numpy(), O.exact_matmul(a2, b2))
-    small = (3, 5, 7, 11, 13, 17, 19, 23)
+    # more than eight channels: plane-level pipeline as well
+    many = (3, 5, 7, 11, 13, 17, 19, 23, 29)
     a3, b3 = rand_i8(rng, (6, 64)), rand_i8(rng, (64, 8))
-    prepared3 = backend.prepare_weight(dev(b3), small)
+    prepared3 = backend.prepare_weight(dev(b3), many)
     assert prepared3.kernel != "tcgen05"
     assert np.array_equal(backend.matmul_prepared_fused(dev(a3), prepared3).cpu().numpy(), O.exact_matmul(a3, b3))
+    # exactly centred in-kernel residues need every modulus >= 86
+    small = backend.prepare_weight_nk(dev(np.ascontiguousarray(b3.T)), (3, 5, 7, 11, 13, 17, 19, 23))
+    with pytest.raises(ValueError):
+        backend._launch_fused(prepared=small, m=6, a=dev(a3), a_planes=None,
+                              out=torch.zeros((6, 8), dtype=torch.int64, device="cuda"), exact_residues=True)
     assert N.load().rns_linear_fused(None, None) == N.ERR_INVALID_ARGUMENT
 
 

@@ -172,12 +172,41 @@ def test_packed_encoder_exhaustive(native, mods):
     assert np.array_equal(out, O.encode_centered(values, mods, "device"))
 
 
+def test_reduced_encoder_every_modulus(native):
+    """The fused kernel's default encoder: congruent, inside int8, for any moduli;
+    within 64 of zero for the moduli just below 128."""
+    values = np.arange(-128, 128, dtype=np.int8)
+    lib = native.load()
+    for start in range(2, 256, 6):
+        mods = [m for m in range(start, min(start + 6, 256))]
+        # coprimality is not needed by the encoder, but the plan builder checks it: one modulus at a time
+        for m in mods:
+            pair = (m, m + 1) if m < 255 else (254, 255)
+            out = np.empty((2, 256), dtype=np.int8)
+            native.check(lib.rns_host_encode_reduced_i8(values.ctypes.data, 256, native.moduli_array(pair), 2,
+                                                        out.ctypes.data))
+            for c, mod in enumerate(pair):
+                assert np.all((out[c].astype(int) - values.astype(int)) % mod == 0), mod
+                changed = out[c] != values
+                if mod <= 191:
+                    assert np.array_equal(changed, (values >= 64) | (values < -64)), mod
+                else:
+                    assert not changed.any()
+    out = np.empty((5, 256), dtype=np.int8)
+    native.check(lib.rns_host_encode_reduced_i8(values.ctypes.data, 256, native.moduli_array(C4), 5, out.ctypes.data))
+    assert int(np.abs(out.astype(int)).max()) == 64
+    exact = O.encode_centered(values, C4, "device").astype(int)
+    near = np.abs(np.abs(values.astype(int)) - 64) <= 8
+    assert np.array_equal(out.astype(int)[:, ~near], exact[:, ~near])
+
+
 def test_packed_encoder_rejects_small_moduli(native):
     values = np.zeros(4, dtype=np.int8)
     out = np.empty((2, 4), dtype=np.int8)
     with pytest.raises(ValueError):
         native.check(native.load().rns_host_encode_centered_i8(
             values.ctypes.data, 4, native.moduli_array((85, 127)), 2, out.ctypes.data))
-    assert native.load().rns_linear_fused_supported(native.moduli_array((85, 127)), 2, 64, 64, 64) == 0
+    # the fused kernel's default (one-step reduced) encoder takes any moduli
+    assert native.load().rns_linear_fused_supported(native.moduli_array((85, 127)), 2, 64, 64, 64) == 1
     assert native.load().rns_linear_fused_supported(native.moduli_array(C0), 4, 768, 768, 768) == 1
     assert native.load().rns_linear_fused_supported(native.moduli_array(C0), 4, 100, 100, 100) == 0
