@@ -364,6 +364,41 @@ RNS_API int rns_quantize_weight(const void* d_w, rns_float_type type, int n, int
                                 int64_t ldw, int quant_max, int8_t* d_wq, float* d_scale,
                                 int32_t* d_max_abs, rns_stream_t stream);
 
+/*
+ * The floating-point linear for hosts that cannot allocate device memory.  It
+ * has no counterpart in the reference, whose workspaces are torch tensors.
+ *
+ * Who needs it: a C or C++ serving loop that binds this library through the C
+ * ABI, is handed its input and output buffers by its own framework, and must
+ * not call cudaMalloc on the request path (it may own no allocator at all).
+ * The two-step path above asks such a caller for scratch it does not have - the
+ * quantised activations, their scale and a reduction word.  Here that scratch
+ * is a fixed array inside the library, RNS_STATIC_SCRATCH_BYTES of packed
+ * activations plus a 256-byte control block, present on every GPU that loads
+ * the library until the process exits.
+ *
+ *   y[M,N] = type( f32(q(x) . Wq^T) * s_a * col_scale[n] + bias[n] ),
+ *   q, s_a = per-tensor symmetric 8-bit quantisation of x, as RNSLinear.forward.
+ *
+ * d_x is [M,K] of `type` (row stride ldx elements); d_w_packed comes from
+ * rns_pack_weight; d_out is [M,N] of out_type (F16/BF16/F32, row stride ldo).
+ * Problems whose packed activations (rns_packed_activation_bytes(m, k, 1)) do
+ * not fit the array are refused with RNS_ERR_UNSUPPORTED.
+ *
+ * The first call on each device looks up the array's device address, with that
+ * device current; make that first call before starting any stream capture.  No
+ * call allocates or frees.  Every call uses the same array: the quantiser clears
+ * the one word that must start at zero, everything else is overwritten before it
+ * is read, and two calls whose work overlaps on the GPU (different streams)
+ * would race - serialise them.
+ */
+#define RNS_STATIC_SCRATCH_BYTES (8u << 20)
+RNS_API int64_t rns_static_scratch_bytes(void);
+RNS_API int rns_linear_static(const void* d_x, rns_float_type type, int m, int k, int64_t ldx,
+                              const int8_t* d_w_packed, int n, const int32_t* moduli, int channels,
+                              const float* d_col_scale, const float* d_bias, void* d_out, int64_t ldo,
+                              int32_t out_type, int32_t* d_status, rns_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif
