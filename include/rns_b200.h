@@ -256,6 +256,7 @@ typedef struct rns_linear_args {
     int32_t w_packed;         /* 1: d_w is in the packed tile layout (rns_pack_weight) */
     int32_t pair_mode;        /* 1: two-CTA tiles (256 x tile_n), 0: one CTA per tile, 2: choose */
     int32_t enc_groups;       /* 0 = choose; else 1, 2 or 4 groups of encoder warps */
+    int32_t enc_stages;       /* 0 = choose; else depth of the operand ring (1..8) */
     int32_t exact_residues;   /* 1: in-kernel residues exactly centred (|r| <= m/2; needs every
                                  modulus >= 86); 0: one-step reduced residues (any moduli) */
 } rns_linear_args;

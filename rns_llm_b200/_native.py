@@ -57,6 +57,7 @@ class LinearArgs(C.Structure):
         ("w_packed", C.c_int32),
         ("pair_mode", C.c_int32),
         ("enc_groups", C.c_int32),
+        ("enc_stages", C.c_int32),
         ("exact_residues", C.c_int32),
     ]
 

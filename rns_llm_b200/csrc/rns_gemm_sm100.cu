@@ -39,8 +39,13 @@ namespace rns {
 #ifdef RNS_ABLATION
 #define RNS_ABLATED(bit) ((p.ablate >> (bit)) & 1)
 static int g_ablate = 0;
+static long long* g_timing = nullptr;   // device buffer of per-role cycle sums (CTA 0)
+#define RNS_TIC(var) long long var = clock64()
+#define RNS_TOC(slot, var) do { long long now__ = clock64(); if (p.timing && blockIdx.x == 0 && blockIdx.y == 0) p.timing[slot] += now__ - var; var = now__; } while (0)
 #else
 #define RNS_ABLATED(bit) false
+#define RNS_TIC(var)
+#define RNS_TOC(slot, var)
 #endif
 
 constexpr int kTileM = 128;
@@ -51,16 +56,22 @@ constexpr int kWorkerWarps = RNS_WORKER_WARPS;
 constexpr int kProducerWarpB = 2 + kWorkerWarps;          // second load producer
 constexpr int kThreads = (3 + kWorkerWarps) * 32;
 constexpr int kWorkerThreads = kWorkerWarps * 32;
-constexpr int kMaxStages = 6;
+constexpr int kMaxStages = 8;
+#ifndef RNS_SPIN_WORKERS
+#define RNS_SPIN_WORKERS 0
+#endif
+constexpr bool kSpinWorkers = RNS_SPIN_WORKERS != 0;   // worker warps poll without suspending
 constexpr long long kWaitLimitCycles = 4000000000ll;  // about 2 s of SM clock
 
 struct GemmParams {
     Plan plan;
     int32_t ablate;               // timing experiments only; always 0 unless built with RNS_ABLATION
+    long long* timing;            // likewise
 
     int32_t m, n, k;
     int32_t tile_n, tile_k;      // tile_k in {64,128}
-    int32_t stages;
+    int32_t raw_stages;           // ring of raw (source byte) tiles: deep, covers the load latency
+    int32_t enc_stages;           // ring of operand tiles: encode + MMA + release
     int32_t a_is_planes;
     int32_t a_packed, w_packed;   // operands in the packed tile layouts (bulk copies)
     const int8_t* a_ptr;          // packed activations / planes
@@ -81,7 +92,8 @@ struct GemmParams {
     const float* bias;
     int32_t* status;
     // shared-memory map (byte offsets from the 1024-aligned base)
-    uint32_t stage_bytes, off_raw_a, off_raw_w, off_enc_a, off_enc_w;
+    uint32_t raw_stage_bytes, enc_stage_bytes, enc_ring_offset;   // raw ring first, operand ring after
+    uint32_t off_raw_a, off_raw_w, off_enc_a, off_enc_w;          // inside a raw / an operand stage
     uint32_t tile_a_bytes, tile_w_bytes;
 };
 
@@ -356,7 +368,8 @@ __device__ __forceinline__ void encode_chunks_reduced(const uint8_t* raw, uint8_
 }
 
 struct __align__(8) SharedCtl {
-    uint64_t full_raw[kMaxStages];    // all loads of the stage have landed
+    uint64_t full_raw[kMaxStages];    // raw tiles of the stage have landed
+    uint64_t empty_raw[kMaxStages];   // encoders have read the raw tiles
     uint64_t full_enc[kMaxStages];
     uint64_t empty_enc[kMaxStages];
     uint64_t acc_full;
@@ -388,8 +401,9 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     const int w_row0 = n0 + (int)pair_rank * w_rows;
     const int m0 = m_tile * kTileM;
     const int kblocks = (p.k + p.tile_k - 1) / p.tile_k;
-    const int stages = p.stages;
+    const int raw_stages = p.raw_stages, enc_stages = p.enc_stages;
     const bool a_planes = p.a_is_planes != 0;
+    const int groups = p.enc_groups;
 
     int active = R;
     if (p.active_ptr != nullptr) {
@@ -399,9 +413,10 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 
     if (threadIdx.x == 0) {
         ctl.abort = 0;
-        for (int s = 0; s < stages; ++s) {
+        for (int s = 0; s < kMaxStages; ++s) {
             mbar_init(smem_addr(&ctl.full_raw[s]), 1);
-            mbar_init(smem_addr(&ctl.full_enc[s]), kWorkerWarps / p.enc_groups);
+            mbar_init(smem_addr(&ctl.empty_raw[s]), kWorkerWarps / groups);
+            mbar_init(smem_addr(&ctl.full_enc[s]), kWorkerWarps / groups + (a_planes ? 1 : 0));
             mbar_init(smem_addr(&ctl.empty_enc[s]), 1);
             mbar_init(smem_addr(&ctl.peer_ready[s]), 1);
         }
@@ -423,42 +438,61 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     tc_fence_after();
     const uint32_t tmem_base = ctl.tmem_base;
     volatile int* abort = &ctl.abort;
+    const uint32_t enc_base = tiles_base + p.enc_ring_offset;
 
-    if (warp == 0 || warp == kProducerWarpB) {
-        // ------------------------------ load producers ----------------------------
-        // Two producer threads (one lane of warp 0 and one of the last warp) take the
-        // even and the odd K blocks: a stage hand-over is a chain of dependent
-        // shared-memory barrier operations, several hundred cycles for one thread.
-        // A stage (raw tiles and operand tiles alike) is free once the MMAs of its
-        // previous round have completed; all bytes of a stage land on full_raw.
+    if (warp == 0) {
+        // ------------------------------ raw-tile producer -------------------------
+        // Source bytes (the W tile, and the A tile when activations are not planes)
+        // go to the deep raw ring; a slot is free as soon as the encoders have read it.
         if (lane == 0) {
-            const uint32_t a_bytes = a_planes ? (uint32_t)active * p.tile_a_bytes : p.tile_a_bytes;
-            const uint32_t stage_tx = (RNS_ABLATED(3) ? 0u : p.tile_w_bytes) + (RNS_ABLATED(2) ? 0u : a_bytes);
-            for (int kb = (warp == 0 ? 0 : 1); kb < kblocks; kb += 2) {
-                const int s = kb % stages;
-                const uint32_t round = (uint32_t)(kb / stages);
-                const uint32_t stage = tiles_base + (uint32_t)s * p.stage_bytes;
-                if (round > 0 && !wait_bounded<false, true>(smem_addr(&ctl.empty_enc[s]), (round - 1) & 1, abort)) break;
+            const uint32_t tx = (RNS_ABLATED(3) ? 0u : p.tile_w_bytes) +
+                                ((a_planes || RNS_ABLATED(2)) ? 0u : p.tile_a_bytes);
+            for (int kb = 0; kb < kblocks; ++kb) {
+                const int s = kb % raw_stages;
+                const uint32_t round = (uint32_t)(kb / raw_stages);
+                const uint32_t stage = tiles_base + (uint32_t)s * p.raw_stage_bytes;
+                RNS_TIC(t_p);
+                if (round > 0 && !wait_bounded<false, true>(smem_addr(&ctl.empty_raw[s]), (round - 1) & 1, abort)) break;
+                RNS_TOC(0, t_p);
                 const uint32_t fr = smem_addr(&ctl.full_raw[s]);
-                mbar_arrive_expect_tx(fr, stage_tx);
+                mbar_arrive_expect_tx(fr, tx);
                 if (RNS_ABLATED(3)) {
                 } else if (p.w_packed)
                     bulk_load(stage + p.off_raw_w,
                               p.w_ptr + ((int64_t)kb * p.w_npad + w_row0) * kPackK, p.tile_w_bytes, fr);
                 else
                     tma_load_2d(stage + p.off_raw_w, &map_w, fr, kb * p.tile_k, w_row0);
-                const int64_t a_tile = (int64_t)m_tile * kblocks + kb;   // packed tile index
-                if (RNS_ABLATED(2)) {
-                } else if (!a_planes) {
+                if (!a_planes && !RNS_ABLATED(2)) {
+                    const int64_t a_tile = (int64_t)m_tile * kblocks + kb;   // packed tile index
                     if (p.a_packed)
                         bulk_load(stage + p.off_raw_a, p.a_ptr + a_tile * (kPackM * kPackK), p.tile_a_bytes, fr);
                     else
                         tma_load_2d(stage + p.off_raw_a, &map_a, fr, kb * p.tile_k, m0);
+                }
+                RNS_TOC(1, t_p);
+            }
+        }
+        __syncwarp();
+    } else if (warp == kProducerWarpB) {
+        // ------------------------------ plane producer ----------------------------
+        // Activation planes are MMA operands as they arrive: they go straight into
+        // the operand ring, whose slots are released by the MMAs.
+        if (lane == 0 && a_planes) {
+            const uint32_t a_bytes = (uint32_t)active * p.tile_a_bytes;
+            for (int kb = 0; kb < kblocks; ++kb) {
+                const int s = kb % enc_stages;
+                const uint32_t round = (uint32_t)(kb / enc_stages);
+                const uint32_t stage = enc_base + (uint32_t)s * p.enc_stage_bytes;
+                if (round > 0 && !wait_bounded<false, true>(smem_addr(&ctl.empty_enc[s]), (round - 1) & 1, abort)) break;
+                const uint32_t fe = smem_addr(&ctl.full_enc[s]);
+                mbar_arrive_expect_tx(fe, RNS_ABLATED(2) ? 0u : a_bytes);
+                const int64_t a_tile = (int64_t)m_tile * kblocks + kb;
+                if (RNS_ABLATED(2)) {
                 } else if (p.a_packed) {
-                    bulk_load(stage + p.off_enc_a, p.a_ptr + a_tile * ((int64_t)R * kPackM * kPackK), a_bytes, fr);
+                    bulk_load(stage + p.off_enc_a, p.a_ptr + a_tile * ((int64_t)R * kPackM * kPackK), a_bytes, fe);
                 } else {
                     for (int c = 0; c < active; ++c)
-                        tma_load_3d(stage + p.off_enc_a + (uint32_t)c * p.tile_a_bytes, &map_a, fr,
+                        tma_load_3d(stage + p.off_enc_a + (uint32_t)c * p.tile_a_bytes, &map_a, fe,
                                     kb * p.tile_k, m0, c);
                 }
             }
@@ -471,8 +505,8 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         // signalled to the empty_enc / acc_full barriers of both CTAs.
         if (lane == 0 && PAIR && pair_rank != 0) {
             for (int kb = 0; kb < kblocks; ++kb) {
-                const int s = kb % stages;
-                const uint32_t round = (uint32_t)(kb / stages);
+                const int s = kb % enc_stages;
+                const uint32_t round = (uint32_t)(kb / enc_stages);
                 if (!wait_bounded<false, true>(smem_addr(&ctl.full_enc[s]), round & 1, abort)) break;
                 mbar_arrive_remote(smem_addr(&ctl.peer_ready[s]), 0);
             }
@@ -480,13 +514,15 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             const uint32_t idesc = make_idesc(PAIR ? 256u : 128u, (uint32_t)p.tile_n);
             bool ok = true;
             for (int kb = 0; kb < kblocks && ok; ++kb) {
-                const int s = kb % stages;
-                const uint32_t round = (uint32_t)(kb / stages);
-                const uint32_t stage = tiles_base + (uint32_t)s * p.stage_bytes;
+                const int s = kb % enc_stages;
+                const uint32_t round = (uint32_t)(kb / enc_stages);
+                const uint32_t stage = enc_base + (uint32_t)s * p.enc_stage_bytes;
+                RNS_TIC(t_m);
                 ok = wait_bounded<false, true>(smem_addr(&ctl.full_enc[s]), round & 1, abort);
                 if (ok && PAIR) ok = wait_bounded<true>(smem_addr(&ctl.peer_ready[s]), round & 1, abort);
                 if (!ok) break;
                 if (!RNS_ABLATED(6)) tc_fence_after();
+                RNS_TOC(2, t_m);
                 for (int c = 0; c < (RNS_ABLATED(1) ? 0 : active); ++c) {
                     const uint32_t a_tile = stage + p.off_enc_a + (uint32_t)c * p.tile_a_bytes;
                     const uint32_t w_tile = stage + p.off_enc_w + (uint32_t)c * p.tile_w_bytes;
@@ -499,9 +535,11 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                         else umma_i8(d, da, db, idesc, acc);
                     }
                 }
+                RNS_TOC(3, t_m);
                 if (RNS_ABLATED(5) && !PAIR) mbar_arrive(smem_addr(&ctl.empty_enc[s]));
                 else if (PAIR) umma_commit_pair(smem_addr(&ctl.empty_enc[s]));
                 else umma_commit(smem_addr(&ctl.empty_enc[s]));
+                RNS_TOC(4, t_m);
             }
             if (ok) {
                 if (PAIR) umma_commit_pair(smem_addr(&ctl.acc_full));
@@ -511,7 +549,6 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         __syncwarp();
     } else {
         // ------------------------------ encoders ----------------------------------
-        const int groups = p.enc_groups;
         const int group = (warp - 2) % groups;
         const int group_threads = kWorkerThreads / groups;
         const int wt = ((warp - 2) / groups) * 32 + lane;   // index inside the group
@@ -531,20 +568,25 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         const bool fast = p.plan.encode_fast != 0;
         bool ok = true;
         for (int kb = group; kb < kblocks && ok; kb += groups) {
-            const int s = kb % stages;
-            const uint32_t round = (uint32_t)(kb / stages);
-            uint8_t* stage = tiles_ptr + (size_t)s * p.stage_bytes;
-            // Order matters once several groups run ahead of each other: the stage must
-            // first be released by the MMAs of its previous round (which also proves
-            // that full_raw has completed that round), only then is the parity of the
-            // full_raw wait unambiguous.
-            if (round > 0) ok = wait_bounded(smem_addr(&ctl.empty_enc[s]), (round - 1) & 1, abort);
-            if (ok) ok = wait_bounded(smem_addr(&ctl.full_raw[s]), round & 1, abort);
+            const int sr = kb % raw_stages, se = kb % enc_stages;
+            const uint32_t round_r = (uint32_t)(kb / raw_stages), round_e = (uint32_t)(kb / enc_stages);
+            const uint8_t* raw_stage = tiles_ptr + (size_t)sr * p.raw_stage_bytes;
+            uint8_t* enc_stage = tiles_ptr + p.enc_ring_offset + (size_t)se * p.enc_stage_bytes;
+            // Order matters once several groups run ahead of each other: the operand
+            // slot must first be released by the MMAs of its previous round.  Because
+            // the raw ring is at least as deep as the operand ring, that also proves
+            // that the raw slot's previous round has completed, which makes the parity
+            // of the full_raw wait unambiguous.
+            RNS_TIC(t_e);
+            if (round_e > 0) ok = wait_bounded<false, kSpinWorkers>(smem_addr(&ctl.empty_enc[se]), (round_e - 1) & 1, abort);
+            if (threadIdx.x == 64) RNS_TOC(5, t_e);
+            if (ok) ok = wait_bounded<false, kSpinWorkers>(smem_addr(&ctl.full_raw[sr]), round_r & 1, abort);
+            if (threadIdx.x == 64) RNS_TOC(6, t_e);
             if (!ok) break;
             for (int part = 0; part < (RNS_ABLATED(0) ? 0 : 2); ++part) {
                 const int chunks = part == 0 ? chunks_w : chunks_a;
-                const uint8_t* raw = stage + (part == 0 ? p.off_raw_w : p.off_raw_a);
-                uint8_t* enc = stage + (part == 0 ? p.off_enc_w : p.off_enc_a);
+                const uint8_t* raw = raw_stage + (part == 0 ? p.off_raw_w : p.off_raw_a);
+                uint8_t* enc = enc_stage + (part == 0 ? p.off_enc_w : p.off_enc_a);
                 const uint32_t tile_bytes = part == 0 ? p.tile_w_bytes : p.tile_a_bytes;
                 if (reduced && active == R)
                     encode_chunks_reduced<R, true>(raw, enc, tile_bytes, chunks, wt, group_threads, active, enc_mfold);
@@ -558,11 +600,16 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     encode_chunks<R, false, false>(raw, enc, tile_bytes, chunks, wt, group_threads, active, enc_hi, enc_lo, enc_mk);
             }
             // Every writer makes its stores visible to the async proxy, the warp
-            // converges, and one lane signals for the warp: 16 arrivals per stage
-            // instead of 512 (arrivals on one mbarrier serialise).
+            // converges, and one lane signals for the warp (arrivals on one mbarrier
+            // serialise): the operand tiles are ready, the raw slot may be refilled.
+            if (threadIdx.x == 64) RNS_TOC(7, t_e);
             if (!RNS_ABLATED(7)) fence_proxy_async_smem();
             __syncwarp();
-            if (lane == 0) mbar_arrive(smem_addr(&ctl.full_enc[s]));
+            if (lane == 0) {
+                mbar_arrive(smem_addr(&ctl.full_enc[se]));
+                mbar_arrive(smem_addr(&ctl.empty_raw[sr]));
+            }
+            if (threadIdx.x == 64) RNS_TOC(8, t_e);
         }
 
         // ------------------------------ epilogue ----------------------------------
@@ -781,6 +828,7 @@ extern "C" {
 
 #ifdef RNS_ABLATION
 __attribute__((visibility("default"))) void rns_debug_set_ablation(int bits) { rns::g_ablate = bits; }
+__attribute__((visibility("default"))) void rns_debug_set_timing(long long* d) { rns::g_timing = d; }
 #endif
 
 int rns_linear_fused_supported(const int32_t* moduli, int channels, int k, int64_t lda, int64_t ldw) {
@@ -863,30 +911,42 @@ int rns_linear_fused(const rns_linear_args* a, rns_stream_t stream) {
     if (pair) m_tiles = (m_tiles + 1) / 2 * 2;
     gp.tile_a_bytes = kTileM * tile_k;
     gp.tile_w_bytes = (pair ? tile_n / 2 : tile_n) * tile_k;
-    uint32_t off = 0;
-    gp.off_raw_w = off; off += gp.tile_w_bytes;
-    gp.off_raw_a = off; if (!planes) off += gp.tile_a_bytes;
-    gp.off_enc_a = off; off += R * gp.tile_a_bytes;
-    gp.off_enc_w = off; off += R * gp.tile_w_bytes;
-    gp.stage_bytes = (off + 1023u) & ~1023u;
-    int stages = kSmemBudget / (int)gp.stage_bytes;
-    if (stages > kMaxStages) stages = kMaxStages;
+    // Two rings in shared memory.  Raw ring: source bytes as loaded (W tile, and the
+    // A tile when activations are not planes).  Operand ring: R tiles for A and for W.
+    gp.off_raw_w = 0;
+    gp.off_raw_a = gp.tile_w_bytes;
+    gp.raw_stage_bytes = (gp.tile_w_bytes + (planes ? 0u : gp.tile_a_bytes) + 1023u) & ~1023u;
+    gp.off_enc_a = 0;
+    gp.off_enc_w = R * gp.tile_a_bytes;
+    gp.enc_stage_bytes = (R * (gp.tile_a_bytes + gp.tile_w_bytes) + 1023u) & ~1023u;
     const int kblocks = (a->k + tile_k - 1) / tile_k;
-    if (stages > kblocks) stages = kblocks;
-    if (stages < 1)
+    // Operand ring: as deep as fits next to a raw ring of at least the same depth;
+    // the rest of the memory deepens the raw ring (it hides the load latency).
+    if (a->enc_stages < 0 || a->enc_stages > kMaxStages)
+        return fail(RNS_ERR_INVALID_ARGUMENT, "enc_stages must be in [0, %d]", kMaxStages);
+    int enc_stages = a->enc_stages > 0 ? a->enc_stages : 4;
+    while (enc_stages > 1 &&
+           (int64_t)enc_stages * (gp.enc_stage_bytes + gp.raw_stage_bytes) > kSmemBudget) --enc_stages;
+    if ((int64_t)enc_stages * (gp.enc_stage_bytes + gp.raw_stage_bytes) > kSmemBudget)
         return fail(RNS_ERR_UNSUPPORTED, "tile configuration does not fit shared memory");
-    if (stages < 2 && kblocks > 1 && tile_k == 128)
-        return fail(RNS_ERR_UNSUPPORTED, "tile_k=128 leaves room for one stage only; use tile_k=64");
-    gp.stages = stages;
-    gp.enc_groups = a->enc_groups > 0 ? a->enc_groups : (stages >= 5 ? 4 : (stages >= 3 ? 2 : 1));
+    if (enc_stages > kblocks) enc_stages = kblocks;
+    int raw_stages = (int)((kSmemBudget - (int64_t)enc_stages * gp.enc_stage_bytes) / gp.raw_stage_bytes);
+    if (raw_stages > kMaxStages) raw_stages = kMaxStages;
+    if (raw_stages > kblocks) raw_stages = kblocks;
+    if (raw_stages < enc_stages) raw_stages = enc_stages;
+    gp.raw_stages = raw_stages;
+    gp.enc_stages = enc_stages;
+    gp.enc_ring_offset = (uint32_t)raw_stages * gp.raw_stage_bytes;
+    gp.enc_groups = a->enc_groups > 0 ? a->enc_groups : (enc_stages >= 3 ? 2 : 1);
     if (gp.enc_groups != 1 && gp.enc_groups != 2 && gp.enc_groups != 4)
         return fail(RNS_ERR_INVALID_ARGUMENT, "enc_groups must be 1, 2 or 4");
-    // A group works one ring revolution ahead of the next at most: never more groups than stages.
-    while (gp.enc_groups > stages) gp.enc_groups /= 2;
+    // A group runs at most one operand slot per member ahead: never more groups than slots.
+    while (gp.enc_groups > enc_stages) gp.enc_groups /= 2;
     gp.m = a->m; gp.n = a->n; gp.k = a->k;
     gp.tile_n = tile_n; gp.tile_k = tile_k;
 #ifdef RNS_ABLATION
     gp.ablate = g_ablate;
+    gp.timing = g_timing;
 #endif
     gp.exact_residues = a->exact_residues ? 1 : 0;
     gp.a_is_planes = planes ? 1 : 0;
@@ -927,7 +987,7 @@ int rns_linear_fused(const rns_linear_args* a, rns_stream_t stream) {
 
     const int n_tiles = (a->n + tile_n - 1) / tile_n;
     const dim3 grid = pair ? dim3(2 * n_tiles, m_tiles / 2, 1) : dim3(n_tiles, m_tiles, 1);
-    const size_t smem = (size_t)stages * gp.stage_bytes + 1024;
+    const size_t smem = (size_t)raw_stages * gp.raw_stage_bytes + (size_t)enc_stages * gp.enc_stage_bytes + 1024;
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     switch (R) {
         case 2: return launch_either<2>(pair, map_a, map_w, gp, grid, smem, st);
