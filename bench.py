@@ -399,7 +399,7 @@ def main() -> None:
                     "h2d_bytes_per_step": int(host_x.numel() * 2), "d2h_bytes_per_step": int(host_y.numel() * 2)},
             "gpu_launches": int(len(LINEARS) * args.layers * launches_per_linear * args.steps),
         }
-        if not args.no_cpu_baseline:
+        if not args.no_cpu_baseline and world == 1:
             try:
                 line["cpu_baseline"] = {k: v for k, v in cpu_port_sample().items() if k != "seconds"}
                 line["cpu_baseline"]["numpy_reference_config0"] = numpy_reference_sample()

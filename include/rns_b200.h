@@ -257,6 +257,10 @@ typedef struct rns_linear_args {
     int32_t pair_mode;        /* 1: two-CTA tiles (256 x tile_n), 0: one CTA per tile, 2: choose */
     int32_t enc_groups;       /* 0 = choose; else 1, 2 or 4 groups of encoder warps */
     int32_t enc_stages;       /* 0 = choose; else depth of the operand ring (1..8) */
+    int32_t sub_blocks;       /* 0 = choose; else K blocks of tile_k bytes per pipeline stage (1..4) */
+    int32_t variant;          /* 0 = choose; 1: operands staged in shared memory; 2: weights as
+                                 tensor-memory operands (packed planes + packed weights, 2..5
+                                 channels; tile_n then means tokens per tile: 32, 64 or 128) */
     int32_t exact_residues;   /* 1: in-kernel residues exactly centred (|r| <= m/2; needs every
                                  modulus >= 86); 0: one-step reduced residues (any moduli) */
 } rns_linear_args;

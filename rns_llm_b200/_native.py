@@ -58,6 +58,8 @@ class LinearArgs(C.Structure):
         ("pair_mode", C.c_int32),
         ("enc_groups", C.c_int32),
         ("enc_stages", C.c_int32),
+        ("sub_blocks", C.c_int32),
+        ("variant", C.c_int32),
         ("exact_residues", C.c_int32),
     ]
 

@@ -562,7 +562,7 @@ class CudaRNSBackend:
                       bias: torch.Tensor | None = None, tile_n: int = 0, tile_k: int = 0,
                       plain_weight: torch.Tensor | None = None, pair_mode: int = 2,
                       enc_groups: int = 0, exact_residues: bool = False,
-                      enc_stages: int = 0) -> None:
+                      enc_stages: int = 0, sub_blocks: int = 0, variant: int = 0) -> None:
         """Fills ``rns_linear_args`` and launches.  ``a`` / ``a_planes`` are plain
         ([M,K] / [R,M,K]) unless ``a_packed``; the weight is the prepared packed
         copy unless ``plain_weight`` ([N,K] int8) is given."""
@@ -604,6 +604,8 @@ class CudaRNSBackend:
         args.enc_groups = enc_groups
         args.exact_residues = 1 if exact_residues else 0
         args.enc_stages = enc_stages
+        args.sub_blocks = sub_blocks
+        args.variant = variant
         N.check(self._lib.rns_linear_fused(C.byref(args), self._stream(device)))
 
     def matmul_prepared_fused(self, a: torch.Tensor, prepared_weight: PreparedRNSWeight, *,

@@ -15,8 +15,9 @@ from pathlib import Path
 
 HERE = Path(__file__).resolve().parent
 REPO = HERE.parent.parent
-SOURCES = ("rns_host.cu", "rns_aux.cu", "rns_gemm_sm100.cu", "rns_static_scratch.cu")
-HEADERS = (HERE / "rns_common.cuh", REPO / "include" / "rns_b200.h")
+SOURCES = ("rns_host.cu", "rns_aux.cu", "rns_gemm_sm100.cu", "rns_gemm_tmem_sm100.cu",
+           "rns_static_scratch.cu")
+HEADERS = (HERE / "rns_common.cuh", HERE / "rns_ptx.cuh", REPO / "include" / "rns_b200.h")
 LIBRARY = HERE / "librns_b200.so"
 
 NVCC_FLAGS = [

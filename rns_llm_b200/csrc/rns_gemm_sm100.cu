@@ -25,6 +25,7 @@
 // records RNS_ERR_DEVICE_TIMEOUT in the caller's status word, skips the
 // remaining work, frees its tensor memory and returns.
 #include "rns_common.cuh"
+#include "rns_ptx.cuh"
 
 #include <cuda.h>
 #include <cuda_bf16.h>
@@ -61,7 +62,6 @@ constexpr int kMaxStages = 8;
 #define RNS_SPIN_WORKERS 0
 #endif
 constexpr bool kSpinWorkers = RNS_SPIN_WORKERS != 0;   // worker warps poll without suspending
-constexpr long long kWaitLimitCycles = 4000000000ll;  // about 2 s of SM clock
 
 struct GemmParams {
     Plan plan;
@@ -72,6 +72,10 @@ struct GemmParams {
     int32_t tile_n, tile_k;      // tile_k in {64,128}
     int32_t raw_stages;           // ring of raw (source byte) tiles: deep, covers the load latency
     int32_t enc_stages;           // ring of operand tiles: encode + MMA + release
+    int32_t sub_blocks;           // K blocks of tile_k bytes per stage (one hand-over per stage:
+                                  // a hand-over costs each role several hundred cycles of
+                                  // dependent barrier operations, whatever the ring depth)
+    uint32_t raw_sub_bytes, enc_sub_bytes;   // one K block inside a raw / an operand stage
     int32_t a_is_planes;
     int32_t a_packed, w_packed;   // operands in the packed tile layouts (bulk copies)
     const int8_t* a_ptr;          // packed activations / planes
@@ -96,222 +100,6 @@ struct GemmParams {
     uint32_t off_raw_a, off_raw_w, off_enc_a, off_enc_w;          // inside a raw / an operand stage
     uint32_t tile_a_bytes, tile_w_bytes;
 };
-
-// ---------------------------------------------------------------------------
-// PTX wrappers
-// ---------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_addr(const void* p) {
-    return (uint32_t)__cvta_generic_to_shared(p);
-}
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
-                 : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-// Non-blocking test of a phase (never suspends the thread).
-__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-__device__ __forceinline__ uint64_t global_timer_ns() {
-    uint64_t t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-__device__ __forceinline__ void fence_proxy_async_smem() {
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
-                                            int x, int y) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
-        " [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
-        : "memory");
-}
-__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
-                                            int x, int y, int z) {
-    asm volatile(
-        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes"
-        " [%0], [%1, {%3, %4, %5}], [%2];"
-        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "r"(z)
-        : "memory");
-}
-__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
-    asm volatile(
-        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-        ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
-        : "memory");
-}
-__device__ __forceinline__ void tmem_alloc(uint32_t holder_smem, uint32_t cols) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(holder_smem),
-                 "r"(cols)
-                 : "memory");
-}
-__device__ __forceinline__ void tmem_relinquish() {
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols)
-                 : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() {
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-}
-__device__ __forceinline__ void tc_fence_after() {
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-}
-__device__ __forceinline__ void umma_i8(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc,
-                                        uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
-                 : "memory");
-}
-__device__ __forceinline__ void tmem_alloc2(uint32_t holder_smem, uint32_t cols) {
-    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(holder_smem),
-                 "r"(cols)
-                 : "memory");
-}
-__device__ __forceinline__ void tmem_relinquish2() {
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc2(uint32_t taddr, uint32_t cols) {
-    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols)
-                 : "memory");
-}
-__device__ __forceinline__ void umma_i8_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc,
-                                             uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-// Arrives on the barrier at this shared-memory offset in BOTH CTAs of the pair
-// once the MMAs issued so far have completed.
-__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
-    asm volatile(
-        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
-        ::"r"(bar), "h"((uint16_t)3)
-        : "memory");
-}
-// Arrive on the barrier at the same offset in another CTA of the cluster.
-__device__ __forceinline__ void mbar_arrive_remote(uint32_t bar, uint32_t cta_rank) {
-    asm volatile(
-        "{\n\t.reg .b32 remote;\n\t"
-        "mapa.shared::cluster.u32 remote, %0, %1;\n\t"
-        "mbarrier.arrive.release.cluster.shared::cluster.b64 _, [remote];\n\t}"
-        ::"r"(bar), "r"(cta_rank)
-        : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-__device__ __forceinline__ uint32_t cluster_cta_rank() {
-    uint32_t r;
-    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-    return r;
-}
-__device__ __forceinline__ void cluster_sync_all() {
-    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_ld8(uint32_t taddr, int (&v)[8]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
-        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
-          "=r"(v[7])
-        : "r"(taddr)
-        : "memory");
-}
-__device__ __forceinline__ void tmem_ld_wait() {
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-
-// K-major operand tile with 64- or 128-byte swizzle: rows of tile_k bytes,
-// groups of 8 rows 8*tile_k bytes apart.  Fields as in the sm_100 matrix
-// descriptor: start>>4 [0,14), leading offset [16,30) (unused for swizzled
-// K-major, set to 1), stride offset>>4 [32,46), version=1 [46,48), swizzle
-// mode [61,64) (2 = 128B, 4 = 64B).
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, uint32_t tile_k) {
-    uint64_t d = 0;
-    d |= (uint64_t)((addr & 0x3FFFFu) >> 4);
-    d |= (uint64_t)1 << 16;
-    d |= (uint64_t)((8u * tile_k) >> 4) << 32;
-    d |= (uint64_t)1 << 46;
-    d |= (uint64_t)(tile_k == 128 ? 2 : 4) << 61;
-    return d;
-}
-// Instruction descriptor: S32 accumulate [4,6)=2, signed 8-bit A [7,10)=1 and
-// B [10,13)=1, both K-major, N>>3 at [17,23), M>>4 at [24,29).
-__device__ __forceinline__ uint32_t make_idesc(uint32_t m, uint32_t n) {
-    return (2u << 4) | (1u << 7) | (1u << 10) | ((n >> 3) << 17) | ((m >> 4) << 24);
-}
-
-// Waits for `parity` of `bar`; false (and *abort set) when the time limit passes
-// or another thread of the CTA already gave up.
-// SPIN: poll with test_wait instead of the suspending try_wait; for the single
-// threads whose wake-up latency is on the critical path of every K block.
-template <bool CLUSTER = false, bool SPIN = false>
-__device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity, volatile int* abort) {
-    auto poll = [&]() {
-        return CLUSTER ? mbar_try_wait_cluster(bar, parity)
-                       : (SPIN ? mbar_test_wait(bar, parity) : mbar_try_wait(bar, parity));
-    };
-    // Fast path: no clock is read unless the wait keeps failing (reading the global
-    // timer costs hundreds of cycles, which every blocked wait would otherwise pay).
-    for (int i = 0; i < 64; ++i)
-        if (poll()) return true;
-    long long t0 = clock64();
-    for (uint32_t spin = 1;; ++spin) {
-        if (poll()) return true;
-        if ((spin & 255u) == 0) {
-            if (*abort) return false;
-            if (clock64() - t0 > kWaitLimitCycles) {
-                *abort = 1;
-                return false;
-            }
-        }
-    }
-}
 
 // Encodes the 16-byte chunks [wt, wt+kWorkerThreads, ...) of one raw tile into
 // the R operand tiles.  ALL: every channel is active (no per-channel branch).
@@ -402,6 +190,8 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     const int m0 = m_tile * kTileM;
     const int kblocks = (p.k + p.tile_k - 1) / p.tile_k;
     const int raw_stages = p.raw_stages, enc_stages = p.enc_stages;
+    const int J = p.sub_blocks;                       // K blocks per stage
+    const int nstages = (kblocks + J - 1) / J;       // stage hand-overs in the K loop
     const bool a_planes = p.a_is_planes != 0;
     const int groups = p.enc_groups;
 
@@ -447,27 +237,32 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         if (lane == 0) {
             const uint32_t tx = (RNS_ABLATED(3) ? 0u : p.tile_w_bytes) +
                                 ((a_planes || RNS_ABLATED(2)) ? 0u : p.tile_a_bytes);
-            for (int kb = 0; kb < kblocks; ++kb) {
-                const int s = kb % raw_stages;
-                const uint32_t round = (uint32_t)(kb / raw_stages);
+            for (int st = 0; st < nstages; ++st) {
+                const int s = st % raw_stages;
+                const uint32_t round = (uint32_t)(st / raw_stages);
                 const uint32_t stage = tiles_base + (uint32_t)s * p.raw_stage_bytes;
+                const int jn = min(J, kblocks - st * J);
                 RNS_TIC(t_p);
                 if (round > 0 && !wait_bounded<false, true>(smem_addr(&ctl.empty_raw[s]), (round - 1) & 1, abort)) break;
                 RNS_TOC(0, t_p);
                 const uint32_t fr = smem_addr(&ctl.full_raw[s]);
-                mbar_arrive_expect_tx(fr, tx);
-                if (RNS_ABLATED(3)) {
-                } else if (p.w_packed)
-                    bulk_load(stage + p.off_raw_w,
-                              p.w_ptr + ((int64_t)kb * p.w_npad + w_row0) * kPackK, p.tile_w_bytes, fr);
-                else
-                    tma_load_2d(stage + p.off_raw_w, &map_w, fr, kb * p.tile_k, w_row0);
-                if (!a_planes && !RNS_ABLATED(2)) {
-                    const int64_t a_tile = (int64_t)m_tile * kblocks + kb;   // packed tile index
-                    if (p.a_packed)
-                        bulk_load(stage + p.off_raw_a, p.a_ptr + a_tile * (kPackM * kPackK), p.tile_a_bytes, fr);
+                mbar_arrive_expect_tx(fr, tx * (uint32_t)jn);
+                for (int j = 0; j < jn; ++j) {
+                    const int kb = st * J + j;
+                    const uint32_t sub = stage + (uint32_t)j * p.raw_sub_bytes;
+                    if (RNS_ABLATED(3)) {
+                    } else if (p.w_packed)
+                        bulk_load(sub + p.off_raw_w,
+                                  p.w_ptr + ((int64_t)kb * p.w_npad + w_row0) * kPackK, p.tile_w_bytes, fr);
                     else
-                        tma_load_2d(stage + p.off_raw_a, &map_a, fr, kb * p.tile_k, m0);
+                        tma_load_2d(sub + p.off_raw_w, &map_w, fr, kb * p.tile_k, w_row0);
+                    if (!a_planes && !RNS_ABLATED(2)) {
+                        const int64_t a_tile = (int64_t)m_tile * kblocks + kb;   // packed tile index
+                        if (p.a_packed)
+                            bulk_load(sub + p.off_raw_a, p.a_ptr + a_tile * (kPackM * kPackK), p.tile_a_bytes, fr);
+                        else
+                            tma_load_2d(sub + p.off_raw_a, &map_a, fr, kb * p.tile_k, m0);
+                    }
                 }
                 RNS_TOC(1, t_p);
             }
@@ -479,21 +274,25 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         // the operand ring, whose slots are released by the MMAs.
         if (lane == 0 && a_planes) {
             const uint32_t a_bytes = (uint32_t)active * p.tile_a_bytes;
-            for (int kb = 0; kb < kblocks; ++kb) {
-                const int s = kb % enc_stages;
-                const uint32_t round = (uint32_t)(kb / enc_stages);
+            for (int st = 0; st < nstages; ++st) {
+                const int s = st % enc_stages;
+                const uint32_t round = (uint32_t)(st / enc_stages);
                 const uint32_t stage = enc_base + (uint32_t)s * p.enc_stage_bytes;
+                const int jn = min(J, kblocks - st * J);
                 if (round > 0 && !wait_bounded<false, true>(smem_addr(&ctl.empty_enc[s]), (round - 1) & 1, abort)) break;
                 const uint32_t fe = smem_addr(&ctl.full_enc[s]);
-                mbar_arrive_expect_tx(fe, RNS_ABLATED(2) ? 0u : a_bytes);
-                const int64_t a_tile = (int64_t)m_tile * kblocks + kb;
-                if (RNS_ABLATED(2)) {
-                } else if (p.a_packed) {
-                    bulk_load(stage + p.off_enc_a, p.a_ptr + a_tile * ((int64_t)R * kPackM * kPackK), a_bytes, fe);
-                } else {
-                    for (int c = 0; c < active; ++c)
-                        tma_load_3d(stage + p.off_enc_a + (uint32_t)c * p.tile_a_bytes, &map_a, fe,
-                                    kb * p.tile_k, m0, c);
+                mbar_arrive_expect_tx(fe, RNS_ABLATED(2) ? 0u : a_bytes * (uint32_t)jn);
+                for (int j = 0; j < jn && !RNS_ABLATED(2); ++j) {
+                    const int kb = st * J + j;
+                    const uint32_t sub = stage + (uint32_t)j * p.enc_sub_bytes;
+                    const int64_t a_tile = (int64_t)m_tile * kblocks + kb;
+                    if (p.a_packed) {
+                        bulk_load(sub + p.off_enc_a, p.a_ptr + a_tile * ((int64_t)R * kPackM * kPackK), a_bytes, fe);
+                    } else {
+                        for (int c = 0; c < active; ++c)
+                            tma_load_3d(sub + p.off_enc_a + (uint32_t)c * p.tile_a_bytes, &map_a, fe,
+                                        kb * p.tile_k, m0, c);
+                    }
                 }
             }
         }
@@ -504,35 +303,39 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         // complete" to the leader's peer_ready barrier.  Completion of the MMAs is
         // signalled to the empty_enc / acc_full barriers of both CTAs.
         if (lane == 0 && PAIR && pair_rank != 0) {
-            for (int kb = 0; kb < kblocks; ++kb) {
-                const int s = kb % enc_stages;
-                const uint32_t round = (uint32_t)(kb / enc_stages);
+            for (int st = 0; st < nstages; ++st) {
+                const int s = st % enc_stages;
+                const uint32_t round = (uint32_t)(st / enc_stages);
                 if (!wait_bounded<false, true>(smem_addr(&ctl.full_enc[s]), round & 1, abort)) break;
                 mbar_arrive_remote(smem_addr(&ctl.peer_ready[s]), 0);
             }
         } else if (lane == 0) {
             const uint32_t idesc = make_idesc(PAIR ? 256u : 128u, (uint32_t)p.tile_n);
             bool ok = true;
-            for (int kb = 0; kb < kblocks && ok; ++kb) {
-                const int s = kb % enc_stages;
-                const uint32_t round = (uint32_t)(kb / enc_stages);
+            for (int st = 0; st < nstages && ok; ++st) {
+                const int s = st % enc_stages;
+                const uint32_t round = (uint32_t)(st / enc_stages);
                 const uint32_t stage = enc_base + (uint32_t)s * p.enc_stage_bytes;
+                const int jn = min(J, kblocks - st * J);
                 RNS_TIC(t_m);
                 ok = wait_bounded<false, true>(smem_addr(&ctl.full_enc[s]), round & 1, abort);
                 if (ok && PAIR) ok = wait_bounded<true>(smem_addr(&ctl.peer_ready[s]), round & 1, abort);
                 if (!ok) break;
                 if (!RNS_ABLATED(6)) tc_fence_after();
                 RNS_TOC(2, t_m);
-                for (int c = 0; c < (RNS_ABLATED(1) ? 0 : active); ++c) {
-                    const uint32_t a_tile = stage + p.off_enc_a + (uint32_t)c * p.tile_a_bytes;
-                    const uint32_t w_tile = stage + p.off_enc_w + (uint32_t)c * p.tile_w_bytes;
-                    const uint32_t d = tmem_base + (uint32_t)(c * p.tile_n);
-                    for (int ks = 0; ks < p.tile_k / 32; ++ks) {
-                        const uint64_t da = make_smem_desc(a_tile + ks * 32, p.tile_k);
-                        const uint64_t db = make_smem_desc(w_tile + ks * 32, p.tile_k);
-                        const uint32_t acc = (kb > 0 || ks > 0) ? 1u : 0u;
-                        if (PAIR) umma_i8_pair(d, da, db, idesc, acc);
-                        else umma_i8(d, da, db, idesc, acc);
+                for (int j = 0; j < jn; ++j) {
+                    const uint32_t sub = stage + (uint32_t)j * p.enc_sub_bytes;
+                    for (int c = 0; c < (RNS_ABLATED(1) ? 0 : active); ++c) {
+                        const uint32_t a_tile = sub + p.off_enc_a + (uint32_t)c * p.tile_a_bytes;
+                        const uint32_t w_tile = sub + p.off_enc_w + (uint32_t)c * p.tile_w_bytes;
+                        const uint32_t d = tmem_base + (uint32_t)(c * p.tile_n);
+                        for (int ks = 0; ks < p.tile_k / 32; ++ks) {
+                            const uint64_t da = make_smem_desc(a_tile + ks * 32, p.tile_k);
+                            const uint64_t db = make_smem_desc(w_tile + ks * 32, p.tile_k);
+                            const uint32_t acc = (st > 0 || j > 0 || ks > 0) ? 1u : 0u;
+                            if (PAIR) umma_i8_pair(d, da, db, idesc, acc);
+                            else umma_i8(d, da, db, idesc, acc);
+                        }
                     }
                 }
                 RNS_TOC(3, t_m);
@@ -567,11 +370,12 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         const bool reduced = p.exact_residues == 0;
         const bool fast = p.plan.encode_fast != 0;
         bool ok = true;
-        for (int kb = group; kb < kblocks && ok; kb += groups) {
-            const int sr = kb % raw_stages, se = kb % enc_stages;
-            const uint32_t round_r = (uint32_t)(kb / raw_stages), round_e = (uint32_t)(kb / enc_stages);
+        for (int st = group; st < nstages && ok; st += groups) {
+            const int sr = st % raw_stages, se = st % enc_stages;
+            const uint32_t round_r = (uint32_t)(st / raw_stages), round_e = (uint32_t)(st / enc_stages);
             const uint8_t* raw_stage = tiles_ptr + (size_t)sr * p.raw_stage_bytes;
             uint8_t* enc_stage = tiles_ptr + p.enc_ring_offset + (size_t)se * p.enc_stage_bytes;
+            const int jn = min(J, kblocks - st * J);
             // Order matters once several groups run ahead of each other: the operand
             // slot must first be released by the MMAs of its previous round.  Because
             // the raw ring is at least as deep as the operand ring, that also proves
@@ -583,10 +387,11 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             if (ok) ok = wait_bounded<false, kSpinWorkers>(smem_addr(&ctl.full_raw[sr]), round_r & 1, abort);
             if (threadIdx.x == 64) RNS_TOC(6, t_e);
             if (!ok) break;
-            for (int part = 0; part < (RNS_ABLATED(0) ? 0 : 2); ++part) {
+            for (int jp = 0; jp < (RNS_ABLATED(0) ? 0 : 2 * jn); ++jp) {
+                const int j = jp >> 1, part = jp & 1;
                 const int chunks = part == 0 ? chunks_w : chunks_a;
-                const uint8_t* raw = raw_stage + (part == 0 ? p.off_raw_w : p.off_raw_a);
-                uint8_t* enc = enc_stage + (part == 0 ? p.off_enc_w : p.off_enc_a);
+                const uint8_t* raw = raw_stage + (size_t)j * p.raw_sub_bytes + (part == 0 ? p.off_raw_w : p.off_raw_a);
+                uint8_t* enc = enc_stage + (size_t)j * p.enc_sub_bytes + (part == 0 ? p.off_enc_w : p.off_enc_a);
                 const uint32_t tile_bytes = part == 0 ? p.tile_w_bytes : p.tile_a_bytes;
                 if (reduced && active == R)
                     encode_chunks_reduced<R, true>(raw, enc, tile_bytes, chunks, wt, group_threads, active, enc_mfold);
@@ -820,6 +625,10 @@ static int launch_either(bool pair, const CUtensorMap& ma, const CUtensorMap& mw
     return pair ? launch<R, true>(ma, mw, gp, grid, smem, st) : launch<R, false>(ma, mw, gp, grid, smem, st);
 }
 
+// rns_gemm_tmem_sm100.cu
+bool tmem_gemm_supported(const rns_linear_args* a);
+int launch_tmem_gemm(const rns_linear_args* a, const Plan& plan, cudaStream_t st);
+
 }  // namespace rns
 
 using namespace rns;
@@ -876,6 +685,17 @@ int rns_linear_fused(const rns_linear_args* a, rns_stream_t stream) {
     if ((reinterpret_cast<uintptr_t>(a_base) & 15) || (reinterpret_cast<uintptr_t>(a->d_w) & 15))
         return fail(RNS_ERR_UNSUPPORTED, "tensor-core path: operand bases must be 16-byte aligned");
 
+    // ---- kernel variant -----------------------------------------------------
+    // 1: both operands staged in shared memory; 2: weights as tensor-memory operands
+    // (packed planes + packed weights only).  Variant 2 is limited to 64-token tiles by
+    // the 512 tensor-memory columns and measured slower (775 vs 1050 channel-TOPS at
+    // 4096^3, four channels), so 0 always resolves to 1; 2 stays selectable.
+    if (a->variant < 0 || a->variant > 2) return fail(RNS_ERR_INVALID_ARGUMENT, "variant must be 0, 1 or 2");
+    if (a->variant == 2 && !tmem_gemm_supported(a))
+        return fail(RNS_ERR_UNSUPPORTED, "variant 2 needs packed planes, packed weights and 2..5 channels");
+    if (a->variant == 2)
+        return launch_tmem_gemm(a, pl, reinterpret_cast<cudaStream_t>(stream));
+
     // ---- tile configuration -------------------------------------------------
     const int max_tile_n = ((512 / R) / 16) * 16 > 128 ? 128 : ((512 / R) / 16) * 16;
     int tile_k = a->tile_k;
@@ -915,24 +735,36 @@ int rns_linear_fused(const rns_linear_args* a, rns_stream_t stream) {
     // A tile when activations are not planes).  Operand ring: R tiles for A and for W.
     gp.off_raw_w = 0;
     gp.off_raw_a = gp.tile_w_bytes;
-    gp.raw_stage_bytes = (gp.tile_w_bytes + (planes ? 0u : gp.tile_a_bytes) + 1023u) & ~1023u;
+    gp.raw_sub_bytes = (gp.tile_w_bytes + (planes ? 0u : gp.tile_a_bytes) + 1023u) & ~1023u;
     gp.off_enc_a = 0;
     gp.off_enc_w = R * gp.tile_a_bytes;
-    gp.enc_stage_bytes = (R * (gp.tile_a_bytes + gp.tile_w_bytes) + 1023u) & ~1023u;
+    gp.enc_sub_bytes = (R * (gp.tile_a_bytes + gp.tile_w_bytes) + 1023u) & ~1023u;
     const int kblocks = (a->k + tile_k - 1) / tile_k;
-    // Operand ring: as deep as fits next to a raw ring of at least the same depth;
-    // the rest of the memory deepens the raw ring (it hides the load latency).
     if (a->enc_stages < 0 || a->enc_stages > kMaxStages)
         return fail(RNS_ERR_INVALID_ARGUMENT, "enc_stages must be in [0, %d]", kMaxStages);
+    if (a->sub_blocks < 0 || a->sub_blocks > 4)
+        return fail(RNS_ERR_INVALID_ARGUMENT, "sub_blocks must be in [0, 4]");
+    // K blocks per stage: as many as still leave two operand stages and two raw
+    // stages (one hand-over per stage; fewer, larger stages amortise its cost).
+    int sub_blocks = a->sub_blocks > 0 ? a->sub_blocks : 2;
+    while (sub_blocks > 1 &&
+           2 * (int64_t)sub_blocks * (gp.enc_sub_bytes + gp.raw_sub_bytes) > kSmemBudget) --sub_blocks;
+    if (sub_blocks > kblocks) sub_blocks = kblocks;
+    gp.sub_blocks = sub_blocks;
+    gp.raw_stage_bytes = (uint32_t)sub_blocks * gp.raw_sub_bytes;
+    gp.enc_stage_bytes = (uint32_t)sub_blocks * gp.enc_sub_bytes;
+    const int nstages = (kblocks + sub_blocks - 1) / sub_blocks;
+    // Operand ring: as deep as fits next to a raw ring of at least the same depth;
+    // the rest of the memory deepens the raw ring (it hides the load latency).
     int enc_stages = a->enc_stages > 0 ? a->enc_stages : 4;
     while (enc_stages > 1 &&
            (int64_t)enc_stages * (gp.enc_stage_bytes + gp.raw_stage_bytes) > kSmemBudget) --enc_stages;
     if ((int64_t)enc_stages * (gp.enc_stage_bytes + gp.raw_stage_bytes) > kSmemBudget)
         return fail(RNS_ERR_UNSUPPORTED, "tile configuration does not fit shared memory");
-    if (enc_stages > kblocks) enc_stages = kblocks;
+    if (enc_stages > nstages) enc_stages = nstages;
     int raw_stages = (int)((kSmemBudget - (int64_t)enc_stages * gp.enc_stage_bytes) / gp.raw_stage_bytes);
     if (raw_stages > kMaxStages) raw_stages = kMaxStages;
-    if (raw_stages > kblocks) raw_stages = kblocks;
+    if (raw_stages > nstages) raw_stages = nstages;
     if (raw_stages < enc_stages) raw_stages = enc_stages;
     gp.raw_stages = raw_stages;
     gp.enc_stages = enc_stages;

@@ -40,7 +40,7 @@ def packed_act_offsets(m, k, channels):
 
 
 def fused_int(backend, a, w_nk, mods, *, planes=False, packed=False, plain_weight=False, tile_n=0, tile_k=0,
-              out_dtype=torch.int64, active=None, pair_mode=2, exact_residues=False):
+              out_dtype=torch.int64, active=None, pair_mode=2, exact_residues=False, **tuning):
     """Direct call of rns_linear_fused on a [M,K] int8 and w [N,K] int8.
     planes: activations as centred planes; packed: activations in the packed tile
     layout; plain_weight: weight through the tensor map instead of the packed copy."""
@@ -52,7 +52,7 @@ def fused_int(backend, a, w_nk, mods, *, planes=False, packed=False, plain_weigh
     a_dev = dev(a)
     kwargs = dict(prepared=prepared, m=m, out=out, tile_n=tile_n, tile_k=tile_k, active=active,
                   plain_weight=w_dev if plain_weight else None, pair_mode=pair_mode,
-                  exact_residues=exact_residues)
+                  exact_residues=exact_residues, **tuning)
     if planes and packed:
         from rns_llm_b200 import _native as N
         buf = torch.empty(int(N.load().rns_packed_activation_bytes(m, k, len(mods))), dtype=torch.int8, device="cuda")
@@ -110,6 +110,40 @@ def test_shapes_ragged_and_deep(backend, m, k, n, mode):
     rng = np.random.default_rng(m * 7 + k + n)
     a, w = rand_i8(rng, (m, k), -128, 127), rand_i8(rng, (n, k), -128, 127)
     assert np.array_equal(fused_int(backend, a, w, C0, **MODES[mode]), O.exact_matmul(a, w.T))
+
+
+@pytest.mark.parametrize("mods", [(127, 125), (127, 126, 125), C0, C4])
+def test_tensor_memory_operand_variant(backend, mods):
+    """variant=2: the weight tile is the MMA's tensor-memory operand, encoded by the
+    worker warps with tcgen05.st; activations are packed planes.  Odd and even numbers
+    of K blocks, ragged M and N, every token-tile width the channel count allows."""
+    rng = np.random.default_rng(len(mods) + 77)
+    cap = O.signed_capacity(mods)
+    for m, k, n in [(64, 64, 128), (100, 192, 200), (300, 1024, 260), (256, 320, 256), (513, 2048, 130)]:
+        a, w = rand_i8(rng, (m, k), -128, 127), rand_i8(rng, (n, k), -128, 127)
+        exact = O.exact_matmul(a, w.T)
+        expect = exact if np.abs(exact).max() <= cap else \
+            O.decode_garner(np.stack([exact % q for q in mods]), mods)
+        widths = [0, 32] + ([64] if len(mods) <= 4 else []) + ([128] if len(mods) <= 2 else [])
+        for tile_t in widths:
+            got = fused_int(backend, a, w, mods, planes=True, packed=True, variant=2, tile_n=tile_t)
+            assert np.array_equal(got, expect), (m, k, n, tile_t)
+    with pytest.raises(Exception):   # plain (unpacked) activations are not a variant-2 input
+        fused_int(backend, a, w, mods, variant=2)
+
+
+@pytest.mark.parametrize("tuning", [dict(sub_blocks=1), dict(sub_blocks=2), dict(sub_blocks=4),
+                                    dict(sub_blocks=2, enc_stages=2), dict(enc_groups=1, enc_stages=1),
+                                    dict(enc_groups=2, enc_stages=3), dict(enc_groups=4, enc_stages=4),
+                                    dict(enc_groups=4, enc_stages=2, sub_blocks=3)])
+@pytest.mark.parametrize("mode", [0, 2, 3, 6, 7, 8])
+def test_pipeline_tuning_knobs(backend, tuning, mode):
+    """K blocks per stage, operand-ring depth and encoder groups only change the
+    schedule: odd K-block counts (tail stages) and ragged edges stay bit-exact."""
+    rng = np.random.default_rng(sum(tuning.values()) + mode)
+    for m, k, n in [(130, 64 * 7, 72), (257, 64 * 18, 260)]:
+        a, w = rand_i8(rng, (m, k), -128, 127), rand_i8(rng, (n, k), -128, 127)
+        assert np.array_equal(fused_int(backend, a, w, C0, **MODES[mode], **tuning), O.exact_matmul(a, w.T)), (m, k, n)
 
 
 @pytest.mark.parametrize("tile_n", [16, 32, 48, 64, 96, 128])
