@@ -42,11 +42,13 @@ namespace rns {
 static int g_ablate = 0;
 static long long* g_timing = nullptr;   // device buffer of per-role cycle sums (CTA 0)
 #define RNS_TIC(var) long long var = clock64()
-#define RNS_TOC(slot, var) do { long long now__ = clock64(); if (p.timing && blockIdx.x == 0 && blockIdx.y == 0) p.timing[slot] += now__ - var; var = now__; } while (0)
+#define RNS_TRACE(slot, st) do { if (p.timing && (p.ablate >> 30) && blockIdx.x == 0 && blockIdx.y == 0 && (threadIdx.x & 31) == 0 && (st) < 64) p.timing[16 + (st) * 12 + (slot)] = clock64(); } while (0)
+#define RNS_TOC(slot, var) do { long long now__ = clock64(); if (p.timing && !(p.ablate >> 30) && blockIdx.x == 0 && blockIdx.y == 0 && (threadIdx.x & 31) == 0) p.timing[slot] += now__ - var; var = now__; } while (0)
 #else
 #define RNS_ABLATED(bit) false
 #define RNS_TIC(var)
 #define RNS_TOC(slot, var)
+#define RNS_TRACE(slot, st)
 #endif
 
 constexpr int kTileM = 128;
@@ -71,7 +73,8 @@ struct GemmParams {
     int32_t m, n, k;
     int32_t tile_n, tile_k;      // tile_k in {64,128}
     int32_t raw_stages;           // ring of raw (source byte) tiles: deep, covers the load latency
-    int32_t enc_stages;           // ring of operand tiles: encode + MMA + release
+    int32_t enc_stages;           // ring of operand tiles written by the encoders: encode + MMA + release
+    int32_t pl_stages;            // ring of activation planes (operands as loaded): load + MMA + release
     int32_t sub_blocks;           // K blocks of tile_k bytes per stage (one hand-over per stage:
                                   // a hand-over costs each role several hundred cycles of
                                   // dependent barrier operations, whatever the ring depth)
@@ -97,33 +100,54 @@ struct GemmParams {
     int32_t* status;
     // shared-memory map (byte offsets from the 1024-aligned base)
     uint32_t raw_stage_bytes, enc_stage_bytes, enc_ring_offset;   // raw ring first, operand ring after
+    uint32_t pl_stage_bytes, pl_sub_bytes, pl_ring_offset;        // plane ring last (planes only)
     uint32_t off_raw_a, off_raw_w, off_enc_a, off_enc_w;          // inside a raw / an operand stage
     uint32_t tile_a_bytes, tile_w_bytes;
 };
 
-// Encodes the 16-byte chunks [wt, wt+kWorkerThreads, ...) of one raw tile into
-// the R operand tiles.  ALL: every channel is active (no per-channel branch).
+// Encodes the 16-byte chunks wt, wt+stride, ... of one raw tile into the R operand
+// tiles.  ALL: every channel is active (no per-channel branch).  Up to four chunks
+// are loaded before any is encoded, so that the shared-memory latency is paid once
+// and the independent words give the scheduler something to overlap: a warp that
+// works through one chunk at a time needs ~700 cycles per chunk, almost all of it
+// dependent-issue latency.
+#ifndef RNS_ENC_BATCH
+#define RNS_ENC_BATCH 1
+#endif
+constexpr int kEncBatch = RNS_ENC_BATCH;
+
 template <int R, bool FAST, bool ALL>
-__device__ __forceinline__ void encode_chunks(const uint8_t* raw, uint8_t* enc, uint32_t tile_bytes,
-                                              int chunks, int wt, int stride, int active,
+__device__ __forceinline__ void encode_chunks(const uint8_t* __restrict__ raw, uint8_t* __restrict__ enc,
+                                              uint32_t tile_bytes, int chunks, int wt, int stride, int active,
                                               const uint32_t (&enc_hi)[R], const uint32_t (&enc_lo)[R],
                                               const uint32_t (&enc_mk)[R]) {
-    for (int ch = wt; ch < chunks; ch += stride) {
-        const uint4 x = *reinterpret_cast<const uint4*>(raw + ch * 16);
-        const uint32_t u0 = x.x ^ 0x80808080u, u1 = x.y ^ 0x80808080u;
-        const uint32_t u2 = x.z ^ 0x80808080u, u3 = x.w ^ 0x80808080u;
-        const uint32_t l0 = x.x & 0x7f7f7f7fu, l1 = x.y & 0x7f7f7f7fu;
-        const uint32_t l2 = x.z & 0x7f7f7f7fu, l3 = x.w & 0x7f7f7f7fu;
-        uint8_t* dst = enc + ch * 16;
+    for (int first = wt; first < chunks; first += kEncBatch * stride) {
+        uint4 x[kEncBatch];
 #pragma unroll
-        for (int c = 0; c < R; ++c) {
-            if (ALL || c < active) {
-                uint4 y;
-                y.x = encode_word<FAST>(u0, l0, enc_hi[c], enc_lo[c], enc_mk[c]);
-                y.y = encode_word<FAST>(u1, l1, enc_hi[c], enc_lo[c], enc_mk[c]);
-                y.z = encode_word<FAST>(u2, l2, enc_hi[c], enc_lo[c], enc_mk[c]);
-                y.w = encode_word<FAST>(u3, l3, enc_hi[c], enc_lo[c], enc_mk[c]);
-                *reinterpret_cast<uint4*>(dst + (size_t)c * tile_bytes) = y;
+        for (int i = 0; i < kEncBatch; ++i) {
+            const int ch = first + i * stride;
+            if (ch < chunks) x[i] = *reinterpret_cast<const uint4*>(raw + ch * 16);
+        }
+#pragma unroll
+        for (int i = 0; i < kEncBatch; ++i) {
+            const int ch = first + i * stride;
+            if (ch < chunks) {
+                const uint32_t u0 = x[i].x ^ 0x80808080u, u1 = x[i].y ^ 0x80808080u;
+                const uint32_t u2 = x[i].z ^ 0x80808080u, u3 = x[i].w ^ 0x80808080u;
+                const uint32_t l0 = x[i].x & 0x7f7f7f7fu, l1 = x[i].y & 0x7f7f7f7fu;
+                const uint32_t l2 = x[i].z & 0x7f7f7f7fu, l3 = x[i].w & 0x7f7f7f7fu;
+                uint8_t* dst = enc + ch * 16;
+#pragma unroll
+                for (int c = 0; c < R; ++c) {
+                    if (ALL || c < active) {
+                        uint4 y;
+                        y.x = encode_word<FAST>(u0, l0, enc_hi[c], enc_lo[c], enc_mk[c]);
+                        y.y = encode_word<FAST>(u1, l1, enc_hi[c], enc_lo[c], enc_mk[c]);
+                        y.z = encode_word<FAST>(u2, l2, enc_hi[c], enc_lo[c], enc_mk[c]);
+                        y.w = encode_word<FAST>(u3, l3, enc_hi[c], enc_lo[c], enc_mk[c]);
+                        *reinterpret_cast<uint4*>(dst + (size_t)c * tile_bytes) = y;
+                    }
+                }
             }
         }
     }
@@ -131,25 +155,36 @@ __device__ __forceinline__ void encode_chunks(const uint8_t* raw, uint8_t* enc, 
 
 // Same, with the one-step reduced encoder (fold pattern shared by all channels).
 template <int R, bool ALL>
-__device__ __forceinline__ void encode_chunks_reduced(const uint8_t* raw, uint8_t* enc, uint32_t tile_bytes,
-                                                      int chunks, int wt, int stride, int active,
-                                                      const uint32_t (&mfold)[R]) {
-    for (int ch = wt; ch < chunks; ch += stride) {
-        const uint4 x = *reinterpret_cast<const uint4*>(raw + ch * 16);
-        const uint32_t u0 = x.x ^ 0x80808080u, u1 = x.y ^ 0x80808080u;
-        const uint32_t u2 = x.z ^ 0x80808080u, u3 = x.w ^ 0x80808080u;
-        const uint32_t d0 = fold_pattern(x.x), d1 = fold_pattern(x.y);
-        const uint32_t d2 = fold_pattern(x.z), d3 = fold_pattern(x.w);
-        uint8_t* dst = enc + ch * 16;
+__device__ __forceinline__ void encode_chunks_reduced(const uint8_t* __restrict__ raw, uint8_t* __restrict__ enc,
+                                                      uint32_t tile_bytes, int chunks, int wt, int stride,
+                                                      int active, const uint32_t (&mfold)[R]) {
+    for (int first = wt; first < chunks; first += kEncBatch * stride) {
+        uint4 x[kEncBatch];
 #pragma unroll
-        for (int c = 0; c < R; ++c) {
-            if (ALL || c < active) {
-                uint4 y;
-                y.x = encode_word_reduced(u0, d0, mfold[c]);
-                y.y = encode_word_reduced(u1, d1, mfold[c]);
-                y.z = encode_word_reduced(u2, d2, mfold[c]);
-                y.w = encode_word_reduced(u3, d3, mfold[c]);
-                *reinterpret_cast<uint4*>(dst + (size_t)c * tile_bytes) = y;
+        for (int i = 0; i < kEncBatch; ++i) {
+            const int ch = first + i * stride;
+            if (ch < chunks) x[i] = *reinterpret_cast<const uint4*>(raw + ch * 16);
+        }
+#pragma unroll
+        for (int i = 0; i < kEncBatch; ++i) {
+            const int ch = first + i * stride;
+            if (ch < chunks) {
+                const uint32_t u0 = x[i].x ^ 0x80808080u, u1 = x[i].y ^ 0x80808080u;
+                const uint32_t u2 = x[i].z ^ 0x80808080u, u3 = x[i].w ^ 0x80808080u;
+                const uint32_t d0 = fold_pattern(x[i].x), d1 = fold_pattern(x[i].y);
+                const uint32_t d2 = fold_pattern(x[i].z), d3 = fold_pattern(x[i].w);
+                uint8_t* dst = enc + ch * 16;
+#pragma unroll
+                for (int c = 0; c < R; ++c) {
+                    if (ALL || c < active) {
+                        uint4 y;
+                        y.x = encode_word_reduced(u0, d0, mfold[c]);
+                        y.y = encode_word_reduced(u1, d1, mfold[c]);
+                        y.z = encode_word_reduced(u2, d2, mfold[c]);
+                        y.w = encode_word_reduced(u3, d3, mfold[c]);
+                        *reinterpret_cast<uint4*>(dst + (size_t)c * tile_bytes) = y;
+                    }
+                }
             }
         }
     }
@@ -160,6 +195,8 @@ struct __align__(8) SharedCtl {
     uint64_t empty_raw[kMaxStages];   // encoders have read the raw tiles
     uint64_t full_enc[kMaxStages];
     uint64_t empty_enc[kMaxStages];
+    uint64_t full_pl[kMaxStages];     // activation planes of the stage have landed
+    uint64_t empty_pl[kMaxStages];    // ... and the MMAs that read them are done
     uint64_t acc_full;
     uint64_t peer_ready[kMaxStages];  // PAIR, leader only: the peer CTA's stage is complete
     uint32_t tmem_base;
@@ -206,8 +243,10 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         for (int s = 0; s < kMaxStages; ++s) {
             mbar_init(smem_addr(&ctl.full_raw[s]), 1);
             mbar_init(smem_addr(&ctl.empty_raw[s]), kWorkerWarps / groups);
-            mbar_init(smem_addr(&ctl.full_enc[s]), kWorkerWarps / groups + (a_planes ? 1 : 0));
+            mbar_init(smem_addr(&ctl.full_enc[s]), kWorkerWarps / groups);
             mbar_init(smem_addr(&ctl.empty_enc[s]), 1);
+            mbar_init(smem_addr(&ctl.full_pl[s]), 1);
+            mbar_init(smem_addr(&ctl.empty_pl[s]), 1);
             mbar_init(smem_addr(&ctl.peer_ready[s]), 1);
         }
         mbar_init(smem_addr(&ctl.acc_full), 1);
@@ -229,6 +268,8 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     const uint32_t tmem_base = ctl.tmem_base;
     volatile int* abort = &ctl.abort;
     const uint32_t enc_base = tiles_base + p.enc_ring_offset;
+    const uint32_t pl_base = tiles_base + p.pl_ring_offset;
+    const int pl_stages = p.pl_stages;
 
     if (warp == 0) {
         // ------------------------------ raw-tile producer -------------------------
@@ -270,30 +311,31 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         __syncwarp();
     } else if (warp == kProducerWarpB) {
         // ------------------------------ plane producer ----------------------------
-        // Activation planes are MMA operands as they arrive: they go straight into
-        // the operand ring, whose slots are released by the MMAs.
+        // Activation planes are MMA operands as they arrive: they go to a ring of
+        // their own, deep enough to cover the load latency, whose slots the MMAs release.
         if (lane == 0 && a_planes) {
             const uint32_t a_bytes = (uint32_t)active * p.tile_a_bytes;
             for (int st = 0; st < nstages; ++st) {
-                const int s = st % enc_stages;
-                const uint32_t round = (uint32_t)(st / enc_stages);
-                const uint32_t stage = enc_base + (uint32_t)s * p.enc_stage_bytes;
+                const int s = st % pl_stages;
+                const uint32_t round = (uint32_t)(st / pl_stages);
+                const uint32_t stage = pl_base + (uint32_t)s * p.pl_stage_bytes;
                 const int jn = min(J, kblocks - st * J);
-                if (round > 0 && !wait_bounded<false, true>(smem_addr(&ctl.empty_enc[s]), (round - 1) & 1, abort)) break;
-                const uint32_t fe = smem_addr(&ctl.full_enc[s]);
-                mbar_arrive_expect_tx(fe, RNS_ABLATED(2) ? 0u : a_bytes * (uint32_t)jn);
+                if (round > 0 && !wait_bounded<false, true>(smem_addr(&ctl.empty_pl[s]), (round - 1) & 1, abort)) break;
+                RNS_TRACE(0, st);
+                const uint32_t fp = smem_addr(&ctl.full_pl[s]);
+                mbar_arrive_expect_tx(fp, RNS_ABLATED(2) ? 0u : a_bytes * (uint32_t)jn);
                 for (int j = 0; j < jn && !RNS_ABLATED(2); ++j) {
                     const int kb = st * J + j;
-                    const uint32_t sub = stage + (uint32_t)j * p.enc_sub_bytes;
+                    const uint32_t sub = stage + (uint32_t)j * p.pl_sub_bytes;
                     const int64_t a_tile = (int64_t)m_tile * kblocks + kb;
                     if (p.a_packed) {
-                        bulk_load(sub + p.off_enc_a, p.a_ptr + a_tile * ((int64_t)R * kPackM * kPackK), a_bytes, fe);
+                        bulk_load(sub, p.a_ptr + a_tile * ((int64_t)R * kPackM * kPackK), a_bytes, fp);
                     } else {
                         for (int c = 0; c < active; ++c)
-                            tma_load_3d(sub + p.off_enc_a + (uint32_t)c * p.tile_a_bytes, &map_a, fe,
-                                        kb * p.tile_k, m0, c);
+                            tma_load_3d(sub + (uint32_t)c * p.tile_a_bytes, &map_a, fp, kb * p.tile_k, m0, c);
                     }
                 }
+                RNS_TRACE(1, st);
             }
         }
         __syncwarp();
@@ -307,44 +349,87 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 const int s = st % enc_stages;
                 const uint32_t round = (uint32_t)(st / enc_stages);
                 if (!wait_bounded<false, true>(smem_addr(&ctl.full_enc[s]), round & 1, abort)) break;
+                if (a_planes && !wait_bounded<false, true>(smem_addr(&ctl.full_pl[st % pl_stages]),
+                                                           (uint32_t)(st / pl_stages) & 1, abort)) break;
                 mbar_arrive_remote(smem_addr(&ctl.peer_ready[s]), 0);
             }
-        } else if (lane == 0) {
+        } else if (!PAIR || pair_rank == 0) {
+            // The whole warp runs this loop, so that the addresses and descriptors
+            // below are warp-uniform values (computed once, in the uniform datapath);
+            // one elected lane issues the MMAs and the commits.  Issued from inside a
+            // single-lane branch the same arithmetic costs ~190 cycles per MMA, three
+            // times the MMA's own duration.
             const uint32_t idesc = make_idesc(PAIR ? 256u : 128u, (uint32_t)p.tile_n);
+            const uint64_t desc0 = make_smem_desc(0, p.tile_k);        // everything but the address
+            const uint32_t a_lo0 = (a_planes ? pl_base : enc_base + p.off_enc_a) >> 4, w_lo0 = (enc_base + p.off_enc_w) >> 4;
+            const uint32_t stage_step = p.enc_stage_bytes >> 4, sub_step = p.enc_sub_bytes >> 4;
+            const uint32_t a_stage_step = (a_planes ? p.pl_stage_bytes : p.enc_stage_bytes) >> 4;
+            const uint32_t a_sub_step = (a_planes ? p.pl_sub_bytes : p.enc_sub_bytes) >> 4;
+            const uint32_t a_step = p.tile_a_bytes >> 4, w_step = p.tile_w_bytes >> 4;
+            const int nks = p.tile_k / 32;
+            const int mma_channels = RNS_ABLATED(1) ? 0 : active;
+            uint32_t a_off[R], w_off[R];
+#pragma unroll
+            for (int c = 0; c < R; ++c) { a_off[c] = (uint32_t)c * a_step; w_off[c] = (uint32_t)c * w_step; }
             bool ok = true;
             for (int st = 0; st < nstages && ok; ++st) {
                 const int s = st % enc_stages;
                 const uint32_t round = (uint32_t)(st / enc_stages);
-                const uint32_t stage = enc_base + (uint32_t)s * p.enc_stage_bytes;
                 const int jn = min(J, kblocks - st * J);
                 RNS_TIC(t_m);
+                const int sa = a_planes ? st % pl_stages : s;       // slot of the A operands
                 ok = wait_bounded<false, true>(smem_addr(&ctl.full_enc[s]), round & 1, abort);
+                RNS_TRACE(8, st);
+                if (ok && a_planes)
+                    ok = wait_bounded<false, true>(smem_addr(&ctl.full_pl[sa]), (uint32_t)(st / pl_stages) & 1, abort);
+                RNS_TRACE(9, st);
                 if (ok && PAIR) ok = wait_bounded<true>(smem_addr(&ctl.peer_ready[s]), round & 1, abort);
+                ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 if (!RNS_ABLATED(6)) tc_fence_after();
                 RNS_TOC(2, t_m);
+                RNS_TRACE(2, st);
+                const uint32_t a_st = a_lo0 + (uint32_t)sa * a_stage_step, w_st = w_lo0 + (uint32_t)s * stage_step;
+                const uint32_t empty_bar = smem_addr(&ctl.empty_enc[s]);
+                const uint32_t empty_pl_bar = smem_addr(&ctl.empty_pl[sa]);
                 for (int j = 0; j < jn; ++j) {
-                    const uint32_t sub = stage + (uint32_t)j * p.enc_sub_bytes;
-                    for (int c = 0; c < (RNS_ABLATED(1) ? 0 : active); ++c) {
-                        const uint32_t a_tile = sub + p.off_enc_a + (uint32_t)c * p.tile_a_bytes;
-                        const uint32_t w_tile = sub + p.off_enc_w + (uint32_t)c * p.tile_w_bytes;
-                        const uint32_t d = tmem_base + (uint32_t)(c * p.tile_n);
-                        for (int ks = 0; ks < p.tile_k / 32; ++ks) {
-                            const uint64_t da = make_smem_desc(a_tile + ks * 32, p.tile_k);
-                            const uint64_t db = make_smem_desc(w_tile + ks * 32, p.tile_k);
-                            const uint32_t acc = (st > 0 || j > 0 || ks > 0) ? 1u : 0u;
-                            if (PAIR) umma_i8_pair(d, da, db, idesc, acc);
-                            else umma_i8(d, da, db, idesc, acc);
+                    const uint32_t a_j = a_st + (uint32_t)j * a_sub_step, w_j = w_st + (uint32_t)j * sub_step;
+                    const uint32_t first = (st > 0 || j > 0) ? 1u : 0u;
+                    if (elect_one()) {
+#pragma unroll
+                        for (int c = 0; c < R; ++c) {
+                            if (c < mma_channels) {
+                                const uint32_t d = tmem_base + (uint32_t)(c * p.tile_n);
+#pragma unroll
+                                for (int ks = 0; ks < 4; ++ks) {
+                                    if (ks < nks) {
+                                        const uint64_t da = desc0 | (uint64_t)(a_j + a_off[c] + (uint32_t)ks * 2u);
+                                        const uint64_t db = desc0 | (uint64_t)(w_j + w_off[c] + (uint32_t)ks * 2u);
+                                        const uint32_t acc = ks > 0 ? 1u : first;
+                                        if (PAIR) umma_i8_pair(d, da, db, idesc, acc);
+                                        else umma_i8(d, da, db, idesc, acc);
+                                    }
+                                }
+                            }
                         }
                     }
+                    __syncwarp();
                 }
                 RNS_TOC(3, t_m);
-                if (RNS_ABLATED(5) && !PAIR) mbar_arrive(smem_addr(&ctl.empty_enc[s]));
-                else if (PAIR) umma_commit_pair(smem_addr(&ctl.empty_enc[s]));
-                else umma_commit(smem_addr(&ctl.empty_enc[s]));
+                RNS_TRACE(3, st);
+                if (elect_one()) {
+                    if (RNS_ABLATED(5) && !PAIR) mbar_arrive(empty_bar);
+                    else if (PAIR) umma_commit_pair(empty_bar);
+                    else umma_commit(empty_bar);
+                    if (a_planes) {
+                        if (PAIR) umma_commit_pair(empty_pl_bar);
+                        else umma_commit(empty_pl_bar);
+                    }
+                }
+                __syncwarp();
                 RNS_TOC(4, t_m);
             }
-            if (ok) {
+            if (ok && elect_one()) {
                 if (PAIR) umma_commit_pair(smem_addr(&ctl.acc_full));
                 else umma_commit(smem_addr(&ctl.acc_full));
             }
@@ -383,9 +468,9 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             // of the full_raw wait unambiguous.
             RNS_TIC(t_e);
             if (round_e > 0) ok = wait_bounded<false, kSpinWorkers>(smem_addr(&ctl.empty_enc[se]), (round_e - 1) & 1, abort);
-            if (threadIdx.x == 64) RNS_TOC(5, t_e);
+            if (threadIdx.x == 64) { RNS_TOC(5, t_e); RNS_TRACE(4, st); }
             if (ok) ok = wait_bounded<false, kSpinWorkers>(smem_addr(&ctl.full_raw[sr]), round_r & 1, abort);
-            if (threadIdx.x == 64) RNS_TOC(6, t_e);
+            if (threadIdx.x == 64) { RNS_TOC(6, t_e); RNS_TRACE(5, st); }
             if (!ok) break;
             for (int jp = 0; jp < (RNS_ABLATED(0) ? 0 : 2 * jn); ++jp) {
                 const int j = jp >> 1, part = jp & 1;
@@ -407,14 +492,14 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             // Every writer makes its stores visible to the async proxy, the warp
             // converges, and one lane signals for the warp (arrivals on one mbarrier
             // serialise): the operand tiles are ready, the raw slot may be refilled.
-            if (threadIdx.x == 64) RNS_TOC(7, t_e);
+            if (threadIdx.x == 64) { RNS_TOC(7, t_e); RNS_TRACE(6, st); }
             if (!RNS_ABLATED(7)) fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) {
                 mbar_arrive(smem_addr(&ctl.full_enc[se]));
                 mbar_arrive(smem_addr(&ctl.empty_raw[sr]));
             }
-            if (threadIdx.x == 64) RNS_TOC(8, t_e);
+            if (threadIdx.x == 64) { RNS_TOC(8, t_e); RNS_TRACE(7, st); }
         }
 
         // ------------------------------ epilogue ----------------------------------
@@ -704,10 +789,12 @@ int rns_linear_fused(const rns_linear_args* a, rns_stream_t stream) {
     int tile_n = a->tile_n;
     int m_tiles = (a->m + kTileM - 1) / kTileM;
     // Pair mode (two CTAs per 256 x tile_n tile): 1 = on, 0 = off, anything else = choose.
-    // It pays when there are enough tiles to fill the GPU twice over.
+    // It pays when there are enough tiles to fill the GPU twice over and the W half
+    // tile stays at 64 rows (up to four channels; with five the tile is 96 wide and
+    // single-CTA tiles measured faster).
     bool pair = a->pair_mode == 1;
     if (a->pair_mode != 0 && a->pair_mode != 1)
-        pair = m_tiles >= 2 && (int64_t)m_tiles * ((a->n + 127) / 128) >= 2 * 148;
+        pair = R <= 4 && m_tiles >= 2 && (int64_t)m_tiles * ((a->n + 127) / 128) >= 2 * 148;
     if (pair && tile_k == 128) return fail(RNS_ERR_INVALID_ARGUMENT, "pair mode uses tile_k = 64");
     if (tile_n == 0) {
         // Largest tile that still gives every SM a CTA; small problems take the
@@ -736,40 +823,51 @@ int rns_linear_fused(const rns_linear_args* a, rns_stream_t stream) {
     gp.off_raw_w = 0;
     gp.off_raw_a = gp.tile_w_bytes;
     gp.raw_sub_bytes = (gp.tile_w_bytes + (planes ? 0u : gp.tile_a_bytes) + 1023u) & ~1023u;
+    // Operand ring: what the encoders write (W tiles; A tiles too unless activations
+    // arrive as planes).  Plane ring: activation planes, operands as loaded.
     gp.off_enc_a = 0;
-    gp.off_enc_w = R * gp.tile_a_bytes;
-    gp.enc_sub_bytes = (R * (gp.tile_a_bytes + gp.tile_w_bytes) + 1023u) & ~1023u;
+    gp.off_enc_w = planes ? 0u : R * gp.tile_a_bytes;
+    gp.enc_sub_bytes = (R * ((planes ? 0u : gp.tile_a_bytes) + gp.tile_w_bytes) + 1023u) & ~1023u;
+    gp.pl_sub_bytes = planes ? R * gp.tile_a_bytes : 0u;
     const int kblocks = (a->k + tile_k - 1) / tile_k;
     if (a->enc_stages < 0 || a->enc_stages > kMaxStages)
         return fail(RNS_ERR_INVALID_ARGUMENT, "enc_stages must be in [0, %d]", kMaxStages);
     if (a->sub_blocks < 0 || a->sub_blocks > 4)
         return fail(RNS_ERR_INVALID_ARGUMENT, "sub_blocks must be in [0, 4]");
-    // K blocks per stage: as many as still leave two operand stages and two raw
-    // stages (one hand-over per stage; fewer, larger stages amortise its cost).
+    // K blocks per stage (one hand-over per stage; measured: two K blocks per stage and
+    // two stages beat four stages of one); never more than leave two stages of every ring.
+    const int64_t per_kb = (int64_t)gp.enc_sub_bytes + gp.raw_sub_bytes + gp.pl_sub_bytes;
     int sub_blocks = a->sub_blocks > 0 ? a->sub_blocks : 2;
-    while (sub_blocks > 1 &&
-           2 * (int64_t)sub_blocks * (gp.enc_sub_bytes + gp.raw_sub_bytes) > kSmemBudget) --sub_blocks;
+    while (sub_blocks > 1 && 2 * sub_blocks * per_kb > kSmemBudget) --sub_blocks;
     if (sub_blocks > kblocks) sub_blocks = kblocks;
     gp.sub_blocks = sub_blocks;
     gp.raw_stage_bytes = (uint32_t)sub_blocks * gp.raw_sub_bytes;
     gp.enc_stage_bytes = (uint32_t)sub_blocks * gp.enc_sub_bytes;
+    gp.pl_stage_bytes = (uint32_t)sub_blocks * gp.pl_sub_bytes;
     const int nstages = (kblocks + sub_blocks - 1) / sub_blocks;
-    // Operand ring: as deep as fits next to a raw ring of at least the same depth;
-    // the rest of the memory deepens the raw ring (it hides the load latency).
+    // Depths: the operand ring as asked (default 4), the plane ring as deep as the
+    // operand ring, and a raw ring at least as deep as the operand ring (the encoders'
+    // parity argument needs that); whatever memory is left deepens first the plane
+    // ring, then the raw ring (both only hide load latency).
     int enc_stages = a->enc_stages > 0 ? a->enc_stages : 4;
-    while (enc_stages > 1 &&
-           (int64_t)enc_stages * (gp.enc_stage_bytes + gp.raw_stage_bytes) > kSmemBudget) --enc_stages;
-    if ((int64_t)enc_stages * (gp.enc_stage_bytes + gp.raw_stage_bytes) > kSmemBudget)
-        return fail(RNS_ERR_UNSUPPORTED, "tile configuration does not fit shared memory");
     if (enc_stages > nstages) enc_stages = nstages;
-    int raw_stages = (int)((kSmemBudget - (int64_t)enc_stages * gp.enc_stage_bytes) / gp.raw_stage_bytes);
-    if (raw_stages > kMaxStages) raw_stages = kMaxStages;
-    if (raw_stages > nstages) raw_stages = nstages;
-    if (raw_stages < enc_stages) raw_stages = enc_stages;
+    auto ring_bytes = [&](int e, int pl, int rw) {
+        return (int64_t)e * gp.enc_stage_bytes + (int64_t)pl * gp.pl_stage_bytes + (int64_t)rw * gp.raw_stage_bytes;
+    };
+    while (enc_stages > 1 && ring_bytes(enc_stages, planes ? enc_stages : 0, enc_stages) > kSmemBudget) --enc_stages;
+    if (ring_bytes(enc_stages, planes ? enc_stages : 0, enc_stages) > kSmemBudget)
+        return fail(RNS_ERR_UNSUPPORTED, "tile configuration does not fit shared memory");
+    int pl_stages = planes ? enc_stages : 0, raw_stages = enc_stages;
+    const int pl_cap = nstages < kMaxStages ? nstages : kMaxStages;
+    while (planes && pl_stages < pl_cap && pl_stages < 6 && ring_bytes(enc_stages, pl_stages + 1, raw_stages) <= kSmemBudget)
+        ++pl_stages;
+    while (raw_stages < pl_cap && ring_bytes(enc_stages, pl_stages, raw_stages + 1) <= kSmemBudget) ++raw_stages;
     gp.raw_stages = raw_stages;
     gp.enc_stages = enc_stages;
+    gp.pl_stages = pl_stages > 0 ? pl_stages : 1;
     gp.enc_ring_offset = (uint32_t)raw_stages * gp.raw_stage_bytes;
-    gp.enc_groups = a->enc_groups > 0 ? a->enc_groups : (enc_stages >= 3 ? 2 : 1);
+    gp.pl_ring_offset = gp.enc_ring_offset + (uint32_t)enc_stages * gp.enc_stage_bytes;
+    gp.enc_groups = a->enc_groups > 0 ? a->enc_groups : (enc_stages >= 2 ? 2 : 1);
     if (gp.enc_groups != 1 && gp.enc_groups != 2 && gp.enc_groups != 4)
         return fail(RNS_ERR_INVALID_ARGUMENT, "enc_groups must be 1, 2 or 4");
     // A group runs at most one operand slot per member ahead: never more groups than slots.
@@ -819,7 +917,7 @@ int rns_linear_fused(const rns_linear_args* a, rns_stream_t stream) {
 
     const int n_tiles = (a->n + tile_n - 1) / tile_n;
     const dim3 grid = pair ? dim3(2 * n_tiles, m_tiles / 2, 1) : dim3(n_tiles, m_tiles, 1);
-    const size_t smem = (size_t)raw_stages * gp.raw_stage_bytes + (size_t)enc_stages * gp.enc_stage_bytes + 1024;
+    const size_t smem = (size_t)ring_bytes(enc_stages, pl_stages, raw_stages) + 1024;
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     switch (R) {
         case 2: return launch_either<2>(pair, map_a, map_w, gp, grid, smem, st);

@@ -90,6 +90,12 @@ __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols)
                  : "memory");
 }
+// True in exactly one lane of a fully active warp (the same lane every time).
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+    return pred != 0;
+}
 __device__ __forceinline__ void tc_fence_before() {
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
 }
@@ -224,7 +230,6 @@ __device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity, vola
         }
     }
 }
-
 
 // Registers -> tensor memory: 16 consecutive 32-bit columns of this warp's 32 lanes.
 __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&v)[16]) {
