@@ -56,6 +56,19 @@ def channel_ops_per_step(tokens: int, layers: int) -> float:
     return float(sum(2.0 * len(mods) * tokens * k * n for _, k, n, mods, _ in LINEARS) * layers)
 
 
+# Mean DRAM traffic of one rns_gemm_kernel launch of this workload on one GPU
+# (dram__bytes_read.sum + dram__bytes_write.sum over the four linears of a layer:
+# 277 + 98 + 483 + 1116 MB), from an ncu capture of `bench.py --layers 2`.
+NCU_DRAM_BYTES_PER_LAUNCH = 493.2e6
+
+
+def algorithmic_bytes_per_launch(tokens: int) -> float:
+    """M*K (int8 activations) + K*N (1 B/value weights) + 4*(1+N) scales + 4*N
+    bias + 2*M*N (fp16 out), mean over the four linears of a layer."""
+    total = sum(tokens * k + k * n + 4 * (1 + n) + 4 * n + 2 * tokens * n for _, k, n, _, _ in LINEARS)
+    return total / len(LINEARS)
+
+
 def useful_ops_per_step(tokens: int, layers: int) -> float:
     return float(sum(2.0 * tokens * k * n for _, k, n, _, _ in LINEARS) * layers)
 
@@ -374,7 +387,7 @@ def main() -> None:
         e2e_value = ops / (e2e_ms / args.steps * 1e-3) / 1e12
         peaks = load_peaks()
         # Dominant kernel: rns_gemm_kernel.  Per launch it performs 2*R*M*K*(N/world)
-        # int8 tensor-core operations (algorithmic, = SURVEY 8(d) "ops" per call).
+        # int8 tensor-core operations (the algorithmic work of one RNS linear).
         gemm_ops_per_rank = ops / world * args.steps
         achieved = gemm_ops_per_rank / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else None
         int8_peak = 2.0 * float(peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"]))
@@ -392,7 +405,10 @@ def main() -> None:
                 "peak_source": f"2 x bf16_tflops_sustained of MEASURED_PEAKS.json ({peaks['source']}); "
                                "the file records no int8 figure",
                 "launches": gemm_launches, "avg_launch_ms": gemm_ms / max(gemm_launches, 1),
-                "traffic": None,
+                "traffic": NCU_DRAM_BYTES_PER_LAUNCH if (world == 1 and args.tokens == 4096) else None,
+                "traffic_unit": "bytes per launch (dram read + write, mean over the four linears)",
+                "traffic_source": "ncu capture of this command with --layers 2, profiles/rns_gemm_kernel_opt6.7b_stack.md",
+                "algorithmic_bytes": algorithmic_bytes_per_launch(args.tokens),
             },
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms / args.steps,
