@@ -41,9 +41,15 @@ namespace rns {
 #define RNS_ABLATED(bit) ((p.ablate >> (bit)) & 1)
 static int g_ablate = 0;
 static long long* g_timing = nullptr;   // device buffer of per-role cycle sums (CTA 0)
+#ifdef RNS_TIMING   // clock reads cost ~100 cycles each: only in builds that want the counters
 #define RNS_TIC(var) long long var = clock64()
 #define RNS_TRACE(slot, st) do { if (p.timing && (p.ablate >> 30) && blockIdx.x == 0 && blockIdx.y == 0 && (threadIdx.x & 31) == 0 && (st) < 64) p.timing[16 + (st) * 12 + (slot)] = clock64(); } while (0)
 #define RNS_TOC(slot, var) do { long long now__ = clock64(); if (p.timing && !(p.ablate >> 30) && blockIdx.x == 0 && blockIdx.y == 0 && (threadIdx.x & 31) == 0) p.timing[slot] += now__ - var; var = now__; } while (0)
+#else
+#define RNS_TIC(var)
+#define RNS_TOC(slot, var)
+#define RNS_TRACE(slot, st)
+#endif
 #else
 #define RNS_ABLATED(bit) false
 #define RNS_TIC(var)
@@ -190,6 +196,20 @@ __device__ __forceinline__ void encode_chunks_reduced(const uint8_t* __restrict_
     }
 }
 
+// Slot and round of consecutive stages in a ring, kept incrementally: a division by a
+// run-time ring depth costs a role ~150 cycles of dependent latency, several times per
+// stage and on every role's critical path.
+struct RingPos {
+    int slot;
+    uint32_t round;
+    int depth;
+    __device__ RingPos(int depth_, int start) : slot(start % depth_), round((uint32_t)(start / depth_)), depth(depth_) {}
+    __device__ void advance(int by) {
+        slot += by;
+        while (slot >= depth) { slot -= depth; ++round; }
+    }
+};
+
 struct __align__(8) SharedCtl {
     uint64_t full_raw[kMaxStages];    // raw tiles of the stage have landed
     uint64_t empty_raw[kMaxStages];   // encoders have read the raw tiles
@@ -278,9 +298,10 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         if (lane == 0) {
             const uint32_t tx = (RNS_ABLATED(3) ? 0u : p.tile_w_bytes) +
                                 ((a_planes || RNS_ABLATED(2)) ? 0u : p.tile_a_bytes);
-            for (int st = 0; st < nstages; ++st) {
-                const int s = st % raw_stages;
-                const uint32_t round = (uint32_t)(st / raw_stages);
+            RingPos ring(raw_stages, 0);
+            for (int st = 0; st < nstages; ++st, ring.advance(1)) {
+                const int s = ring.slot;
+                const uint32_t round = ring.round;
                 const uint32_t stage = tiles_base + (uint32_t)s * p.raw_stage_bytes;
                 const int jn = min(J, kblocks - st * J);
                 RNS_TIC(t_p);
@@ -315,9 +336,10 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         // their own, deep enough to cover the load latency, whose slots the MMAs release.
         if (lane == 0 && a_planes) {
             const uint32_t a_bytes = (uint32_t)active * p.tile_a_bytes;
-            for (int st = 0; st < nstages; ++st) {
-                const int s = st % pl_stages;
-                const uint32_t round = (uint32_t)(st / pl_stages);
+            RingPos ring(pl_stages, 0);
+            for (int st = 0; st < nstages; ++st, ring.advance(1)) {
+                const int s = ring.slot;
+                const uint32_t round = ring.round;
                 const uint32_t stage = pl_base + (uint32_t)s * p.pl_stage_bytes;
                 const int jn = min(J, kblocks - st * J);
                 if (round > 0 && !wait_bounded<false, true>(smem_addr(&ctl.empty_pl[s]), (round - 1) & 1, abort)) break;
@@ -345,12 +367,13 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         // complete" to the leader's peer_ready barrier.  Completion of the MMAs is
         // signalled to the empty_enc / acc_full barriers of both CTAs.
         if (lane == 0 && PAIR && pair_rank != 0) {
-            for (int st = 0; st < nstages; ++st) {
-                const int s = st % enc_stages;
-                const uint32_t round = (uint32_t)(st / enc_stages);
+            RingPos ring(enc_stages, 0), ring_pl(pl_stages, 0);
+            for (int st = 0; st < nstages; ++st, ring.advance(1), ring_pl.advance(1)) {
+                const int s = ring.slot;
+                const uint32_t round = ring.round;
                 if (!wait_bounded<false, true>(smem_addr(&ctl.full_enc[s]), round & 1, abort)) break;
-                if (a_planes && !wait_bounded<false, true>(smem_addr(&ctl.full_pl[st % pl_stages]),
-                                                           (uint32_t)(st / pl_stages) & 1, abort)) break;
+                if (a_planes && !wait_bounded<false, true>(smem_addr(&ctl.full_pl[ring_pl.slot]),
+                                                           ring_pl.round & 1, abort)) break;
                 mbar_arrive_remote(smem_addr(&ctl.peer_ready[s]), 0);
             }
         } else if (!PAIR || pair_rank == 0) {
@@ -372,19 +395,19 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 #pragma unroll
             for (int c = 0; c < R; ++c) { a_off[c] = (uint32_t)c * a_step; w_off[c] = (uint32_t)c * w_step; }
             bool ok = true;
-            for (int st = 0; st < nstages && ok; ++st) {
-                const int s = st % enc_stages;
-                const uint32_t round = (uint32_t)(st / enc_stages);
+            RingPos ring(enc_stages, 0), ring_pl(pl_stages, 0);
+            for (int st = 0; st < nstages && ok; ++st, ring.advance(1), ring_pl.advance(1)) {
+                const int s = ring.slot;
+                const uint32_t round = ring.round;
                 const int jn = min(J, kblocks - st * J);
                 RNS_TIC(t_m);
-                const int sa = a_planes ? st % pl_stages : s;       // slot of the A operands
-                ok = wait_bounded<false, true>(smem_addr(&ctl.full_enc[s]), round & 1, abort);
+                const int sa = a_planes ? ring_pl.slot : s;       // slot of the A operands
+                ok = warp_wait_bounded<false, true>(smem_addr(&ctl.full_enc[s]), round & 1, abort);
                 RNS_TRACE(8, st);
                 if (ok && a_planes)
-                    ok = wait_bounded<false, true>(smem_addr(&ctl.full_pl[sa]), (uint32_t)(st / pl_stages) & 1, abort);
+                    ok = warp_wait_bounded<false, true>(smem_addr(&ctl.full_pl[sa]), ring_pl.round & 1, abort);
                 RNS_TRACE(9, st);
-                if (ok && PAIR) ok = wait_bounded<true>(smem_addr(&ctl.peer_ready[s]), round & 1, abort);
-                ok = __all_sync(0xffffffffu, ok);
+                if (ok && PAIR) ok = warp_wait_bounded<true>(smem_addr(&ctl.peer_ready[s]), round & 1, abort);
                 if (!ok) break;
                 if (!RNS_ABLATED(6)) tc_fence_after();
                 RNS_TOC(2, t_m);
@@ -455,9 +478,10 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         const bool reduced = p.exact_residues == 0;
         const bool fast = p.plan.encode_fast != 0;
         bool ok = true;
-        for (int st = group; st < nstages && ok; st += groups) {
-            const int sr = st % raw_stages, se = st % enc_stages;
-            const uint32_t round_r = (uint32_t)(st / raw_stages), round_e = (uint32_t)(st / enc_stages);
+        RingPos ring_r(raw_stages, group), ring_e(enc_stages, group);
+        for (int st = group; st < nstages && ok; st += groups, ring_r.advance(groups), ring_e.advance(groups)) {
+            const int sr = ring_r.slot, se = ring_e.slot;
+            const uint32_t round_r = ring_r.round, round_e = ring_e.round;
             const uint8_t* raw_stage = tiles_ptr + (size_t)sr * p.raw_stage_bytes;
             uint8_t* enc_stage = tiles_ptr + p.enc_ring_offset + (size_t)se * p.enc_stage_bytes;
             const int jn = min(J, kblocks - st * J);
@@ -467,9 +491,9 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             // that the raw slot's previous round has completed, which makes the parity
             // of the full_raw wait unambiguous.
             RNS_TIC(t_e);
-            if (round_e > 0) ok = wait_bounded<false, kSpinWorkers>(smem_addr(&ctl.empty_enc[se]), (round_e - 1) & 1, abort);
+            if (round_e > 0) ok = warp_wait_bounded<false, kSpinWorkers>(smem_addr(&ctl.empty_enc[se]), (round_e - 1) & 1, abort);
             if (threadIdx.x == 64) { RNS_TOC(5, t_e); RNS_TRACE(4, st); }
-            if (ok) ok = wait_bounded<false, kSpinWorkers>(smem_addr(&ctl.full_raw[sr]), round_r & 1, abort);
+            if (ok) ok = warp_wait_bounded<false, kSpinWorkers>(smem_addr(&ctl.full_raw[sr]), round_r & 1, abort);
             if (threadIdx.x == 64) { RNS_TOC(6, t_e); RNS_TRACE(5, st); }
             if (!ok) break;
             for (int jp = 0; jp < (RNS_ABLATED(0) ? 0 : 2 * jn); ++jp) {
@@ -503,7 +527,7 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         }
 
         // ------------------------------ epilogue ----------------------------------
-        if (ok) ok = wait_bounded(smem_addr(&ctl.acc_full), 0, abort);
+        if (ok) ok = warp_wait_bounded(smem_addr(&ctl.acc_full), 0, abort);
         if (ok && !RNS_ABLATED(4)) {
             tc_fence_after();
             const int quarter = warp & 3;             // TMEM lanes 32*quarter .. +31

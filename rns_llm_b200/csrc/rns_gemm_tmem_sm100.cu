@@ -44,6 +44,8 @@ namespace rns {
 
 #ifdef RNS_ABLATION
 long long* g_timing_v2 = nullptr;
+#endif
+#if defined(RNS_ABLATION) && defined(RNS_TIMING)
 #define V2_TIC(var) long long var = clock64()
 #define V2_TOC(slot, var) do { long long now__ = clock64(); if (p.timing && blockIdx.x == 0 && blockIdx.y == 0) p.timing[slot] += now__ - var; var = now__; } while (0)
 #else

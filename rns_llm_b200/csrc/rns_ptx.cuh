@@ -216,11 +216,17 @@ __device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity, vola
     };
     // Fast path: no clock is read unless the wait keeps failing (reading the global
     // timer costs hundreds of cycles, which every blocked wait would otherwise pay).
-    for (int i = 0; i < 64; ++i)
+#ifndef RNS_SPIN_SLEEP_NS
+#define RNS_SPIN_SLEEP_NS 20   // back-off between polls of a spinning lane: frees issue slots for the encoders
+#endif
+    for (int i = 0; i < 64; ++i) {
         if (poll()) return true;
+        if (SPIN && RNS_SPIN_SLEEP_NS > 0 && i >= 4) __nanosleep(RNS_SPIN_SLEEP_NS);
+    }
     long long t0 = clock64();
     for (uint32_t spin = 1;; ++spin) {
         if (poll()) return true;
+        if (SPIN && RNS_SPIN_SLEEP_NS > 0) __nanosleep(RNS_SPIN_SLEEP_NS);
         if ((spin & 255u) == 0) {
             if (*abort) return false;
             if (clock64() - t0 > kWaitLimitCycles) {
@@ -229,6 +235,20 @@ __device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity, vola
             }
         }
     }
+}
+// The same for a whole (converged) warp, with a warp-uniform result.
+#ifndef RNS_LANE0_POLL
+#define RNS_LANE0_POLL 0   // measured: all lanes polling is faster than one lane + shuffle
+#endif
+template <bool CLUSTER = false, bool SPIN = false>
+__device__ __forceinline__ bool warp_wait_bounded(uint32_t bar, uint32_t parity, volatile int* abort) {
+#if RNS_LANE0_POLL
+    int ok = 1;
+    if ((threadIdx.x & 31) == 0) ok = wait_bounded<CLUSTER, SPIN>(bar, parity, abort) ? 1 : 0;
+    return __shfl_sync(0xffffffffu, ok, 0) != 0;
+#else
+    return __all_sync(0xffffffffu, wait_bounded<CLUSTER, SPIN>(bar, parity, abort));
+#endif
 }
 
 // Registers -> tensor memory: 16 consecutive 32-bit columns of this warp's 32 lanes.
