@@ -41,7 +41,11 @@ namespace rns {
 #define RNS_ABLATED(bit) ((p.ablate >> (bit)) & 1)
 static int g_ablate = 0;
 static long long* g_timing = nullptr;   // device buffer of per-role cycle sums (CTA 0)
-#ifdef RNS_TIMING   // clock reads cost ~100 cycles each: only in builds that want the counters
+#if defined(RNS_TIMING) && RNS_TIMING == 2   // event trace only
+#define RNS_TIC(var)
+#define RNS_TOC(slot, var)
+#define RNS_TRACE(slot, st) do { if (p.timing && blockIdx.x == 0 && blockIdx.y == 0 && (threadIdx.x & 31) == 0 && (st) < 64) p.timing[16 + (st) * 12 + (slot)] = clock64(); } while (0)
+#elif defined(RNS_TIMING)   // clock reads cost ~100 cycles each: only in builds that want the counters
 #define RNS_TIC(var) long long var = clock64()
 #define RNS_TRACE(slot, st) do { if (p.timing && (p.ablate >> 30) && blockIdx.x == 0 && blockIdx.y == 0 && (threadIdx.x & 31) == 0 && (st) < 64) p.timing[16 + (st) * 12 + (slot)] = clock64(); } while (0)
 #define RNS_TOC(slot, var) do { long long now__ = clock64(); if (p.timing && !(p.ablate >> 30) && blockIdx.x == 0 && blockIdx.y == 0 && (threadIdx.x & 31) == 0) p.timing[slot] += now__ - var; var = now__; } while (0)
@@ -223,7 +227,14 @@ struct __align__(8) SharedCtl {
     int abort;
 };
 
-template <int R, bool PAIR>
+// J_/ES_/PS_/RS_ > 0 select the "fixed" instantiation: K blocks per stage and the depths
+// of the operand, plane and raw rings are compile-time constants, and so is everything
+// that follows from the hot configuration they stand for (packed planes and packed
+// weights, 64-byte K blocks, every channel active, one-step reduced residues, two
+// encoder groups, tile_n = 128 up to four channels and 96 for five).  The roles' loops
+// are chains of dependent scalar instructions, a few cycles each: every run-time
+// parameter folded into a constant shortens a stage.  All zeros: everything run-time.
+template <int R, bool PAIR, int J_, int ES_, int PS_, int RS_>
 __global__ void __launch_bounds__(kThreads, 1)
 rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                 const __grid_constant__ GemmParams p) {
@@ -240,20 +251,37 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     // cluster are neighbours in x), y = pair of row tiles; rank 0 leads.  Each CTA of
     // a pair loads and encodes tile_n/2 rows of W starting at w_row0.
     const uint32_t pair_rank = PAIR ? cluster_cta_rank() : 0u;
+    constexpr bool FIXED = J_ > 0;
+    const int tile_k = FIXED ? 64 : p.tile_k;
+    const int tile_n = FIXED ? (R <= 4 ? 128 : 96) : p.tile_n;
     const int m_tile = PAIR ? 2 * (int)blockIdx.y + (int)pair_rank : (int)blockIdx.y;
-    const int n0 = (PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x) * p.tile_n;
-    const int w_rows = PAIR ? p.tile_n / 2 : p.tile_n;
+    const int n0 = (PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x) * tile_n;
+    const int w_rows = PAIR ? tile_n / 2 : tile_n;
     const int w_row0 = n0 + (int)pair_rank * w_rows;
     const int m0 = m_tile * kTileM;
-    const int kblocks = (p.k + p.tile_k - 1) / p.tile_k;
-    const int raw_stages = p.raw_stages, enc_stages = p.enc_stages;
-    const int J = p.sub_blocks;                       // K blocks per stage
+    const int kblocks = (p.k + tile_k - 1) / tile_k;
+    const int raw_stages = FIXED ? RS_ : p.raw_stages, enc_stages = FIXED ? ES_ : p.enc_stages;
+    const int J = FIXED ? J_ : p.sub_blocks;          // K blocks per stage
     const int nstages = (kblocks + J - 1) / J;       // stage hand-overs in the K loop
-    const bool a_planes = p.a_is_planes != 0;
-    const int groups = p.enc_groups;
+    const bool a_planes = FIXED ? true : p.a_is_planes != 0;
+    const bool a_packed = FIXED ? true : p.a_packed != 0, w_packed = FIXED ? true : p.w_packed != 0;
+    const int groups = FIXED ? 2 : p.enc_groups;
+    // Shared-memory map: the parameters' values, or the same values as constants.
+    const uint32_t tile_a_bytes = FIXED ? (uint32_t)(kTileM * 64) : p.tile_a_bytes;
+    const uint32_t tile_w_bytes = FIXED ? (uint32_t)((PAIR ? tile_n / 2 : tile_n) * 64) : p.tile_w_bytes;
+    const uint32_t raw_sub_bytes = FIXED ? ((tile_w_bytes + 1023u) & ~1023u) : p.raw_sub_bytes;
+    const uint32_t enc_sub_bytes = FIXED ? (((uint32_t)R * tile_w_bytes + 1023u) & ~1023u) : p.enc_sub_bytes;
+    const uint32_t pl_sub_bytes = FIXED ? (uint32_t)R * tile_a_bytes : p.pl_sub_bytes;
+    const uint32_t raw_stage_bytes = FIXED ? (uint32_t)J_ * raw_sub_bytes : p.raw_stage_bytes;
+    const uint32_t enc_stage_bytes = FIXED ? (uint32_t)J_ * enc_sub_bytes : p.enc_stage_bytes;
+    const uint32_t pl_stage_bytes = FIXED ? (uint32_t)J_ * pl_sub_bytes : p.pl_stage_bytes;
+    const uint32_t enc_ring_offset = FIXED ? (uint32_t)RS_ * raw_stage_bytes : p.enc_ring_offset;
+    const uint32_t pl_ring_offset = FIXED ? enc_ring_offset + (uint32_t)ES_ * enc_stage_bytes : p.pl_ring_offset;
+    const uint32_t off_raw_w = FIXED ? 0u : p.off_raw_w, off_raw_a = FIXED ? tile_w_bytes : p.off_raw_a;
+    const uint32_t off_enc_a = FIXED ? 0u : p.off_enc_a, off_enc_w = FIXED ? 0u : p.off_enc_w;
 
     int active = R;
-    if (p.active_ptr != nullptr) {
+    if (!FIXED && p.active_ptr != nullptr) {
         active = *p.active_ptr;
         active = active < 1 ? 1 : (active > R ? R : active);
     }
@@ -287,43 +315,43 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     tc_fence_after();
     const uint32_t tmem_base = ctl.tmem_base;
     volatile int* abort = &ctl.abort;
-    const uint32_t enc_base = tiles_base + p.enc_ring_offset;
-    const uint32_t pl_base = tiles_base + p.pl_ring_offset;
-    const int pl_stages = p.pl_stages;
+    const uint32_t enc_base = tiles_base + enc_ring_offset;
+    const uint32_t pl_base = tiles_base + pl_ring_offset;
+    const int pl_stages = FIXED ? PS_ : p.pl_stages;
 
     if (warp == 0) {
         // ------------------------------ raw-tile producer -------------------------
         // Source bytes (the W tile, and the A tile when activations are not planes)
         // go to the deep raw ring; a slot is free as soon as the encoders have read it.
         if (lane == 0) {
-            const uint32_t tx = (RNS_ABLATED(3) ? 0u : p.tile_w_bytes) +
-                                ((a_planes || RNS_ABLATED(2)) ? 0u : p.tile_a_bytes);
+            const uint32_t tx = (RNS_ABLATED(3) ? 0u : tile_w_bytes) +
+                                ((a_planes || RNS_ABLATED(2)) ? 0u : tile_a_bytes);
             RingPos ring(raw_stages, 0);
             for (int st = 0; st < nstages; ++st, ring.advance(1)) {
                 const int s = ring.slot;
                 const uint32_t round = ring.round;
-                const uint32_t stage = tiles_base + (uint32_t)s * p.raw_stage_bytes;
+                const uint32_t stage = tiles_base + (uint32_t)s * raw_stage_bytes;
                 const int jn = min(J, kblocks - st * J);
                 RNS_TIC(t_p);
-                if (round > 0 && !wait_bounded<false, true>(smem_addr(&ctl.empty_raw[s]), (round - 1) & 1, abort)) break;
+                if (round > 0 && !RNS_ABLATED(10) && !wait_bounded<false, true>(smem_addr(&ctl.empty_raw[s]), (round - 1) & 1, abort)) break;
                 RNS_TOC(0, t_p);
                 const uint32_t fr = smem_addr(&ctl.full_raw[s]);
                 mbar_arrive_expect_tx(fr, tx * (uint32_t)jn);
                 for (int j = 0; j < jn; ++j) {
                     const int kb = st * J + j;
-                    const uint32_t sub = stage + (uint32_t)j * p.raw_sub_bytes;
+                    const uint32_t sub = stage + (uint32_t)j * raw_sub_bytes;
                     if (RNS_ABLATED(3)) {
-                    } else if (p.w_packed)
-                        bulk_load(sub + p.off_raw_w,
-                                  p.w_ptr + ((int64_t)kb * p.w_npad + w_row0) * kPackK, p.tile_w_bytes, fr);
+                    } else if (w_packed)
+                        bulk_load(sub + off_raw_w,
+                                  p.w_ptr + ((int64_t)kb * p.w_npad + w_row0) * kPackK, tile_w_bytes, fr);
                     else
-                        tma_load_2d(sub + p.off_raw_w, &map_w, fr, kb * p.tile_k, w_row0);
+                        tma_load_2d(sub + off_raw_w, &map_w, fr, kb * tile_k, w_row0);
                     if (!a_planes && !RNS_ABLATED(2)) {
                         const int64_t a_tile = (int64_t)m_tile * kblocks + kb;   // packed tile index
-                        if (p.a_packed)
-                            bulk_load(sub + p.off_raw_a, p.a_ptr + a_tile * (kPackM * kPackK), p.tile_a_bytes, fr);
+                        if (a_packed)
+                            bulk_load(sub + off_raw_a, p.a_ptr + a_tile * (kPackM * kPackK), tile_a_bytes, fr);
                         else
-                            tma_load_2d(sub + p.off_raw_a, &map_a, fr, kb * p.tile_k, m0);
+                            tma_load_2d(sub + off_raw_a, &map_a, fr, kb * tile_k, m0);
                     }
                 }
                 RNS_TOC(1, t_p);
@@ -335,26 +363,26 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         // Activation planes are MMA operands as they arrive: they go to a ring of
         // their own, deep enough to cover the load latency, whose slots the MMAs release.
         if (lane == 0 && a_planes) {
-            const uint32_t a_bytes = (uint32_t)active * p.tile_a_bytes;
+            const uint32_t a_bytes = (uint32_t)active * tile_a_bytes;
             RingPos ring(pl_stages, 0);
             for (int st = 0; st < nstages; ++st, ring.advance(1)) {
                 const int s = ring.slot;
                 const uint32_t round = ring.round;
-                const uint32_t stage = pl_base + (uint32_t)s * p.pl_stage_bytes;
+                const uint32_t stage = pl_base + (uint32_t)s * pl_stage_bytes;
                 const int jn = min(J, kblocks - st * J);
-                if (round > 0 && !wait_bounded<false, true>(smem_addr(&ctl.empty_pl[s]), (round - 1) & 1, abort)) break;
+                if (round > 0 && !RNS_ABLATED(11) && !wait_bounded<false, true>(smem_addr(&ctl.empty_pl[s]), (round - 1) & 1, abort)) break;
                 RNS_TRACE(0, st);
                 const uint32_t fp = smem_addr(&ctl.full_pl[s]);
                 mbar_arrive_expect_tx(fp, RNS_ABLATED(2) ? 0u : a_bytes * (uint32_t)jn);
                 for (int j = 0; j < jn && !RNS_ABLATED(2); ++j) {
                     const int kb = st * J + j;
-                    const uint32_t sub = stage + (uint32_t)j * p.pl_sub_bytes;
+                    const uint32_t sub = stage + (uint32_t)j * pl_sub_bytes;
                     const int64_t a_tile = (int64_t)m_tile * kblocks + kb;
-                    if (p.a_packed) {
+                    if (a_packed) {
                         bulk_load(sub, p.a_ptr + a_tile * ((int64_t)R * kPackM * kPackK), a_bytes, fp);
                     } else {
                         for (int c = 0; c < active; ++c)
-                            tma_load_3d(sub + (uint32_t)c * p.tile_a_bytes, &map_a, fp, kb * p.tile_k, m0, c);
+                            tma_load_3d(sub + (uint32_t)c * tile_a_bytes, &map_a, fp, kb * tile_k, m0, c);
                     }
                 }
                 RNS_TRACE(1, st);
@@ -372,7 +400,7 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 const int s = ring.slot;
                 const uint32_t round = ring.round;
                 if (!wait_bounded<false, true>(smem_addr(&ctl.full_enc[s]), round & 1, abort)) break;
-                if (a_planes && !wait_bounded<false, true>(smem_addr(&ctl.full_pl[ring_pl.slot]),
+                if (a_planes && !RNS_ABLATED(11) && !wait_bounded<false, true>(smem_addr(&ctl.full_pl[ring_pl.slot]),
                                                            ring_pl.round & 1, abort)) break;
                 mbar_arrive_remote(smem_addr(&ctl.peer_ready[s]), 0);
             }
@@ -382,14 +410,14 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             // one elected lane issues the MMAs and the commits.  Issued from inside a
             // single-lane branch the same arithmetic costs ~190 cycles per MMA, three
             // times the MMA's own duration.
-            const uint32_t idesc = make_idesc(PAIR ? 256u : 128u, (uint32_t)p.tile_n);
-            const uint64_t desc0 = make_smem_desc(0, p.tile_k);        // everything but the address
-            const uint32_t a_lo0 = (a_planes ? pl_base : enc_base + p.off_enc_a) >> 4, w_lo0 = (enc_base + p.off_enc_w) >> 4;
-            const uint32_t stage_step = p.enc_stage_bytes >> 4, sub_step = p.enc_sub_bytes >> 4;
-            const uint32_t a_stage_step = (a_planes ? p.pl_stage_bytes : p.enc_stage_bytes) >> 4;
-            const uint32_t a_sub_step = (a_planes ? p.pl_sub_bytes : p.enc_sub_bytes) >> 4;
-            const uint32_t a_step = p.tile_a_bytes >> 4, w_step = p.tile_w_bytes >> 4;
-            const int nks = p.tile_k / 32;
+            const uint32_t idesc = make_idesc(PAIR ? 256u : 128u, (uint32_t)tile_n);
+            const uint64_t desc0 = make_smem_desc(0, tile_k);        // everything but the address
+            const uint32_t a_lo0 = (a_planes ? pl_base : enc_base + off_enc_a) >> 4, w_lo0 = (enc_base + off_enc_w) >> 4;
+            const uint32_t stage_step = enc_stage_bytes >> 4, sub_step = enc_sub_bytes >> 4;
+            const uint32_t a_stage_step = (a_planes ? pl_stage_bytes : enc_stage_bytes) >> 4;
+            const uint32_t a_sub_step = (a_planes ? pl_sub_bytes : enc_sub_bytes) >> 4;
+            const uint32_t a_step = tile_a_bytes >> 4, w_step = tile_w_bytes >> 4;
+            const int nks = tile_k / 32;
             const int mma_channels = RNS_ABLATED(1) ? 0 : active;
             uint32_t a_off[R], w_off[R];
 #pragma unroll
@@ -404,7 +432,7 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 const int sa = a_planes ? ring_pl.slot : s;       // slot of the A operands
                 ok = warp_wait_bounded<false, true>(smem_addr(&ctl.full_enc[s]), round & 1, abort);
                 RNS_TRACE(8, st);
-                if (ok && a_planes)
+                if (ok && a_planes && !RNS_ABLATED(11))
                     ok = warp_wait_bounded<false, true>(smem_addr(&ctl.full_pl[sa]), ring_pl.round & 1, abort);
                 RNS_TRACE(9, st);
                 if (ok && PAIR) ok = warp_wait_bounded<true>(smem_addr(&ctl.peer_ready[s]), round & 1, abort);
@@ -422,7 +450,7 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 #pragma unroll
                         for (int c = 0; c < R; ++c) {
                             if (c < mma_channels) {
-                                const uint32_t d = tmem_base + (uint32_t)(c * p.tile_n);
+                                const uint32_t d = tmem_base + (uint32_t)(c * tile_n);
 #pragma unroll
                                 for (int ks = 0; ks < 4; ++ks) {
                                     if (ks < nks) {
@@ -444,7 +472,7 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     if (RNS_ABLATED(5) && !PAIR) mbar_arrive(empty_bar);
                     else if (PAIR) umma_commit_pair(empty_bar);
                     else umma_commit(empty_bar);
-                    if (a_planes) {
+                    if (a_planes && !RNS_ABLATED(11)) {
                         if (PAIR) umma_commit_pair(empty_pl_bar);
                         else umma_commit(empty_pl_bar);
                     }
@@ -467,23 +495,23 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         const int rows_w = max(0, min(w_rows, p.n - w_row0));
         // 16-byte chunks that hold valid rows (row r occupies bytes [r*tile_k, (r+1)*tile_k)
         // of a tile in every swizzle mode).
-        const int chunks_a = a_planes ? 0 : rows_a * (p.tile_k / 16);
-        const int chunks_w = rows_w * (p.tile_k / 16);
+        const int chunks_a = a_planes ? 0 : rows_a * (tile_k / 16);
+        const int chunks_w = rows_w * (tile_k / 16);
         uint32_t enc_hi[R], enc_lo[R], enc_mk[R], enc_mfold[R];
 #pragma unroll
         for (int c = 0; c < R; ++c) {
             enc_hi[c] = p.plan.enc_hi[c]; enc_lo[c] = p.plan.enc_lo[c]; enc_mk[c] = p.plan.enc_mk[c];
             enc_mfold[c] = p.plan.enc_mfold[c];
         }
-        const bool reduced = p.exact_residues == 0;
+        const bool reduced = FIXED ? true : p.exact_residues == 0;
         const bool fast = p.plan.encode_fast != 0;
         bool ok = true;
         RingPos ring_r(raw_stages, group), ring_e(enc_stages, group);
         for (int st = group; st < nstages && ok; st += groups, ring_r.advance(groups), ring_e.advance(groups)) {
             const int sr = ring_r.slot, se = ring_e.slot;
             const uint32_t round_r = ring_r.round, round_e = ring_e.round;
-            const uint8_t* raw_stage = tiles_ptr + (size_t)sr * p.raw_stage_bytes;
-            uint8_t* enc_stage = tiles_ptr + p.enc_ring_offset + (size_t)se * p.enc_stage_bytes;
+            const uint8_t* raw_stage = tiles_ptr + (size_t)sr * raw_stage_bytes;
+            uint8_t* enc_stage = tiles_ptr + enc_ring_offset + (size_t)se * enc_stage_bytes;
             const int jn = min(J, kblocks - st * J);
             // Order matters once several groups run ahead of each other: the operand
             // slot must first be released by the MMAs of its previous round.  Because
@@ -493,15 +521,15 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             RNS_TIC(t_e);
             if (round_e > 0) ok = warp_wait_bounded<false, kSpinWorkers>(smem_addr(&ctl.empty_enc[se]), (round_e - 1) & 1, abort);
             if (threadIdx.x == 64) { RNS_TOC(5, t_e); RNS_TRACE(4, st); }
-            if (ok) ok = warp_wait_bounded<false, kSpinWorkers>(smem_addr(&ctl.full_raw[sr]), round_r & 1, abort);
+            if (ok && !RNS_ABLATED(10)) ok = warp_wait_bounded<false, kSpinWorkers>(smem_addr(&ctl.full_raw[sr]), round_r & 1, abort);
             if (threadIdx.x == 64) { RNS_TOC(6, t_e); RNS_TRACE(5, st); }
             if (!ok) break;
             for (int jp = 0; jp < (RNS_ABLATED(0) ? 0 : 2 * jn); ++jp) {
                 const int j = jp >> 1, part = jp & 1;
                 const int chunks = part == 0 ? chunks_w : chunks_a;
-                const uint8_t* raw = raw_stage + (size_t)j * p.raw_sub_bytes + (part == 0 ? p.off_raw_w : p.off_raw_a);
-                uint8_t* enc = enc_stage + (size_t)j * p.enc_sub_bytes + (part == 0 ? p.off_enc_w : p.off_enc_a);
-                const uint32_t tile_bytes = part == 0 ? p.tile_w_bytes : p.tile_a_bytes;
+                const uint8_t* raw = raw_stage + (size_t)j * raw_sub_bytes + (part == 0 ? off_raw_w : off_raw_a);
+                uint8_t* enc = enc_stage + (size_t)j * enc_sub_bytes + (part == 0 ? off_enc_w : off_enc_a);
+                const uint32_t tile_bytes = part == 0 ? tile_w_bytes : tile_a_bytes;
                 if (reduced && active == R)
                     encode_chunks_reduced<R, true>(raw, enc, tile_bytes, chunks, wt, group_threads, active, enc_mfold);
                 else if (reduced)
@@ -538,13 +566,13 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             const bool is_float = p.out_type >= RNS_OUT_F16;
             if (is_float && row < p.m) rs = p.row_scale[(int64_t)row * p.row_scale_stride];
             using XInt = typename std::conditional<(R <= 4), int, long long>::type;
-            for (int col = part * 8; col < p.tile_n; col += (kWorkerWarps / 4) * 8) {
+            for (int col = part * 8; col < tile_n; col += (kWorkerWarps / 4) * 8) {
                 __syncwarp();  // the tensor-memory loads below are warp-collective
                 int acc[R][8];
 #pragma unroll
                 for (int c = 0; c < R; ++c) {
                     if (c < active) {
-                        tmem_ld8(lane_base + (uint32_t)(c * p.tile_n + col), acc[c]);
+                        tmem_ld8(lane_base + (uint32_t)(c * tile_n + col), acc[c]);
                     } else {
 #pragma unroll
                         for (int e = 0; e < 8; ++e) acc[c][e] = 0;
@@ -688,7 +716,7 @@ static bool tc_supported(const Plan& pl, int k, int64_t lda, int64_t ldw, bool e
     return true;
 }
 
-template <int R, bool PAIR>
+template <int R, bool PAIR, int J_ = 0, int ES_ = 0, int PS_ = 0, int RS_ = 0>
 static int launch(const CUtensorMap& ma, const CUtensorMap& mw, const GemmParams& gp, dim3 grid,
                   size_t smem, cudaStream_t st) {
     // The opt-in shared-memory size is a per-device function attribute: set it on
@@ -698,7 +726,7 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& mw, const GemmParams
     RNS_CUDA_OK(cudaGetDevice(&dev));
     const uint64_t bit = 1ull << (dev & 63);
     if (!(configured.load(std::memory_order_acquire) & bit)) {
-        RNS_CUDA_OK(cudaFuncSetAttribute(rns_gemm_kernel<R, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        RNS_CUDA_OK(cudaFuncSetAttribute(rns_gemm_kernel<R, PAIR, J_, ES_, PS_, RS_>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          227 * 1024 - 1024));
         configured.fetch_or(bit, std::memory_order_release);
     }
@@ -717,10 +745,10 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& mw, const GemmParams
         cfg.attrs = attr;
         cfg.numAttrs = 1;
     }
-    const cudaError_t rc = cudaLaunchKernelEx(&cfg, rns_gemm_kernel<R, PAIR>, ma, mw, gp);
+    const cudaError_t rc = cudaLaunchKernelEx(&cfg, rns_gemm_kernel<R, PAIR, J_, ES_, PS_, RS_>, ma, mw, gp);
     if (rc != cudaSuccess) {
         int clusters = -1;
-        if (PAIR) cudaOccupancyMaxActiveClusters(&clusters, rns_gemm_kernel<R, PAIR>, &cfg);
+        if (PAIR) cudaOccupancyMaxActiveClusters(&clusters, rns_gemm_kernel<R, PAIR, J_, ES_, PS_, RS_>, &cfg);
         cudaGetLastError();
         return fail(RNS_ERR_CUDA, "launch of the RNS GEMM failed: %s (grid %u x %u, smem %zu, pair %d, "
                     "max active clusters %d)", cudaGetErrorString(rc), grid.x, grid.y, smem, (int)PAIR, clusters);
@@ -817,8 +845,14 @@ int rns_linear_fused(const rns_linear_args* a, rns_stream_t stream) {
     // tile stays at 64 rows (up to four channels; with five the tile is 96 wide and
     // single-CTA tiles measured faster).
     bool pair = a->pair_mode == 1;
-    if (a->pair_mode != 0 && a->pair_mode != 1)
+    if (a->pair_mode != 0 && a->pair_mode != 1) {
         pair = R <= 4 && m_tiles >= 2 && (int64_t)m_tiles * ((a->n + 127) / 128) >= 2 * 148;
+        // With the compile-time ring configuration (see the dispatch below) single-CTA
+        // tiles measured faster than pairs (1.69 against 1.54 channel-POPS at 4096^3).
+        if (R == 4 && planes && a_packed && w_packed && a->d_active_channels == nullptr &&
+            a->exact_residues == 0 && a->k >= 4 * 64)
+            pair = false;
+    }
     if (pair && tile_k == 128) return fail(RNS_ERR_INVALID_ARGUMENT, "pair mode uses tile_k = 64");
     if (tile_n == 0) {
         // Largest tile that still gives every SM a CTA; small problems take the
@@ -943,6 +977,15 @@ int rns_linear_fused(const rns_linear_args* a, rns_stream_t stream) {
     const dim3 grid = pair ? dim3(2 * n_tiles, m_tiles / 2, 1) : dim3(n_tiles, m_tiles, 1);
     const size_t smem = (size_t)ring_bytes(enc_stages, pl_stages, raw_stages) + 1024;
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    // The hot configurations have instantiations with compile-time ring parameters.
+    const bool fixed_ok = planes && a_packed && w_packed && tile_k == 64 && a->d_active_channels == nullptr &&
+                          a->exact_residues == 0 && gp.enc_groups == 2 && tile_n == (R <= 4 ? 128 : 96);
+    auto rings_are = [&](int j, int es, int ps, int rs) {
+        return fixed_ok && sub_blocks == j && enc_stages == es && pl_stages == ps && raw_stages == rs;
+    };
+    if (R == 4 && pair && rings_are(2, 2, 2, 4)) return launch<4, true, 2, 2, 2, 4>(map_a, map_w, gp, grid, smem, st);
+    if (R == 4 && !pair && rings_are(1, 3, 3, 4)) return launch<4, false, 1, 3, 3, 4>(map_a, map_w, gp, grid, smem, st);
+    if (R == 5 && !pair && rings_are(1, 2, 3, 7)) return launch<5, false, 1, 2, 3, 7>(map_a, map_w, gp, grid, smem, st);
     switch (R) {
         case 2: return launch_either<2>(pair, map_a, map_w, gp, grid, smem, st);
         case 3: return launch_either<3>(pair, map_a, map_w, gp, grid, smem, st);
