@@ -230,11 +230,11 @@ struct __align__(8) SharedCtl {
 // J_/ES_/PS_/RS_ > 0 select the "fixed" instantiation: K blocks per stage and the depths
 // of the operand, plane and raw rings are compile-time constants, and so is everything
 // that follows from the hot configuration they stand for (packed planes and packed
-// weights, 64-byte K blocks, every channel active, one-step reduced residues, two
+// weights, 64-byte K blocks, every channel active, one-step reduced residues, G_
 // encoder groups, tile_n = 128 up to four channels and 96 for five).  The roles' loops
 // are chains of dependent scalar instructions, a few cycles each: every run-time
 // parameter folded into a constant shortens a stage.  All zeros: everything run-time.
-template <int R, bool PAIR, int J_, int ES_, int PS_, int RS_>
+template <int R, bool PAIR, int J_, int ES_, int PS_, int RS_, int G_>
 __global__ void __launch_bounds__(kThreads, 1)
 rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                 const __grid_constant__ GemmParams p) {
@@ -252,6 +252,14 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     // a pair loads and encodes tile_n/2 rows of W starting at w_row0.
     const uint32_t pair_rank = PAIR ? cluster_cta_rank() : 0u;
     constexpr bool FIXED = J_ > 0;
+    // RS_ < 0: no raw ring at all; the encoder threads read their weight bytes from
+    // global memory into registers, two of their stages ahead (packed weights, J_ == 1).
+    constexpr bool W_DIRECT = FIXED && RS_ < 0;
+    // The operand slot and the plane slot of a stage are released by the same MMAs.
+    // When the operand ring is at least as deep as the plane ring, one commit per
+    // stage serves both: the plane producer of stage st waits on the operand ring's
+    // barrier of stage st - PS_ (one commit less on the MMA warp's path).
+    constexpr bool ONE_COMMIT = W_DIRECT && !PAIR && ES_ >= PS_;
     const int tile_k = FIXED ? 64 : p.tile_k;
     const int tile_n = FIXED ? (R <= 4 ? 128 : 96) : p.tile_n;
     const int m_tile = PAIR ? 2 * (int)blockIdx.y + (int)pair_rank : (int)blockIdx.y;
@@ -260,12 +268,12 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     const int w_row0 = n0 + (int)pair_rank * w_rows;
     const int m0 = m_tile * kTileM;
     const int kblocks = (p.k + tile_k - 1) / tile_k;
-    const int raw_stages = FIXED ? RS_ : p.raw_stages, enc_stages = FIXED ? ES_ : p.enc_stages;
+    const int raw_stages = FIXED ? (RS_ > 0 ? RS_ : 1) : p.raw_stages, enc_stages = FIXED ? ES_ : p.enc_stages;
     const int J = FIXED ? J_ : p.sub_blocks;          // K blocks per stage
     const int nstages = (kblocks + J - 1) / J;       // stage hand-overs in the K loop
     const bool a_planes = FIXED ? true : p.a_is_planes != 0;
     const bool a_packed = FIXED ? true : p.a_packed != 0, w_packed = FIXED ? true : p.w_packed != 0;
-    const int groups = FIXED ? 2 : p.enc_groups;
+    const int groups = FIXED ? G_ : p.enc_groups;
     // Shared-memory map: the parameters' values, or the same values as constants.
     const uint32_t tile_a_bytes = FIXED ? (uint32_t)(kTileM * 64) : p.tile_a_bytes;
     const uint32_t tile_w_bytes = FIXED ? (uint32_t)((PAIR ? tile_n / 2 : tile_n) * 64) : p.tile_w_bytes;
@@ -275,7 +283,7 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     const uint32_t raw_stage_bytes = FIXED ? (uint32_t)J_ * raw_sub_bytes : p.raw_stage_bytes;
     const uint32_t enc_stage_bytes = FIXED ? (uint32_t)J_ * enc_sub_bytes : p.enc_stage_bytes;
     const uint32_t pl_stage_bytes = FIXED ? (uint32_t)J_ * pl_sub_bytes : p.pl_stage_bytes;
-    const uint32_t enc_ring_offset = FIXED ? (uint32_t)RS_ * raw_stage_bytes : p.enc_ring_offset;
+    const uint32_t enc_ring_offset = FIXED ? (uint32_t)(RS_ > 0 ? RS_ : 0) * raw_stage_bytes : p.enc_ring_offset;
     const uint32_t pl_ring_offset = FIXED ? enc_ring_offset + (uint32_t)ES_ * enc_stage_bytes : p.pl_ring_offset;
     const uint32_t off_raw_w = FIXED ? 0u : p.off_raw_w, off_raw_a = FIXED ? tile_w_bytes : p.off_raw_a;
     const uint32_t off_enc_a = FIXED ? 0u : p.off_enc_a, off_enc_w = FIXED ? 0u : p.off_enc_w;
@@ -323,7 +331,7 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         // ------------------------------ raw-tile producer -------------------------
         // Source bytes (the W tile, and the A tile when activations are not planes)
         // go to the deep raw ring; a slot is free as soon as the encoders have read it.
-        if (lane == 0) {
+        if (lane == 0 && !W_DIRECT) {
             const uint32_t tx = (RNS_ABLATED(3) ? 0u : tile_w_bytes) +
                                 ((a_planes || RNS_ABLATED(2)) ? 0u : tile_a_bytes);
             RingPos ring(raw_stages, 0);
@@ -331,7 +339,7 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 const int s = ring.slot;
                 const uint32_t round = ring.round;
                 const uint32_t stage = tiles_base + (uint32_t)s * raw_stage_bytes;
-                const int jn = min(J, kblocks - st * J);
+                const int jn = (FIXED && J_ == 1) ? 1 : min(J, kblocks - st * J);
                 RNS_TIC(t_p);
                 if (round > 0 && !RNS_ABLATED(10) && !wait_bounded<false, true>(smem_addr(&ctl.empty_raw[s]), (round - 1) & 1, abort)) break;
                 RNS_TOC(0, t_p);
@@ -365,12 +373,18 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         if (lane == 0 && a_planes) {
             const uint32_t a_bytes = (uint32_t)active * tile_a_bytes;
             RingPos ring(pl_stages, 0);
+            RingPos released(enc_stages, 0);   // ONE_COMMIT: the stage whose plane slot is reused
             for (int st = 0; st < nstages; ++st, ring.advance(1)) {
                 const int s = ring.slot;
                 const uint32_t round = ring.round;
                 const uint32_t stage = pl_base + (uint32_t)s * pl_stage_bytes;
-                const int jn = min(J, kblocks - st * J);
-                if (round > 0 && !RNS_ABLATED(11) && !wait_bounded<false, true>(smem_addr(&ctl.empty_pl[s]), (round - 1) & 1, abort)) break;
+                const int jn = (FIXED && J_ == 1) ? 1 : min(J, kblocks - st * J);
+                if (ONE_COMMIT) {
+                    if (st >= pl_stages) {
+                        if (!wait_bounded<false, true>(smem_addr(&ctl.empty_enc[released.slot]), released.round & 1, abort)) break;
+                        released.advance(1);
+                    }
+                } else if (round > 0 && !RNS_ABLATED(11) && !wait_bounded<false, true>(smem_addr(&ctl.empty_pl[s]), (round - 1) & 1, abort)) break;
                 RNS_TRACE(0, st);
                 const uint32_t fp = smem_addr(&ctl.full_pl[s]);
                 mbar_arrive_expect_tx(fp, RNS_ABLATED(2) ? 0u : a_bytes * (uint32_t)jn);
@@ -427,7 +441,7 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             for (int st = 0; st < nstages && ok; ++st, ring.advance(1), ring_pl.advance(1)) {
                 const int s = ring.slot;
                 const uint32_t round = ring.round;
-                const int jn = min(J, kblocks - st * J);
+                const int jn = (FIXED && J_ == 1) ? 1 : min(J, kblocks - st * J);
                 RNS_TIC(t_m);
                 const int sa = a_planes ? ring_pl.slot : s;       // slot of the A operands
                 ok = warp_wait_bounded<false, true>(smem_addr(&ctl.full_enc[s]), round & 1, abort);
@@ -472,7 +486,7 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     if (RNS_ABLATED(5) && !PAIR) mbar_arrive(empty_bar);
                     else if (PAIR) umma_commit_pair(empty_bar);
                     else umma_commit(empty_bar);
-                    if (a_planes && !RNS_ABLATED(11)) {
+                    if (a_planes && !RNS_ABLATED(11) && !ONE_COMMIT) {
                         if (PAIR) umma_commit_pair(empty_pl_bar);
                         else umma_commit(empty_pl_bar);
                     }
@@ -506,13 +520,71 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         const bool reduced = FIXED ? true : p.exact_residues == 0;
         const bool fast = p.plan.encode_fast != 0;
         bool ok = true;
+        if constexpr (W_DIRECT) {
+            // Chunks wt, wt + group_threads, ... of the W tile of K block kb sit at
+            // w_tile(kb) + 16 * chunk in the packed weight matrix (a tile is contiguous).
+            // Two of this group's stages are kept in registers ahead of the one encoded.
+            constexpr int kGroupThreads = kWorkerThreads / (G_ > 0 ? G_ : 1);
+            constexpr int kChunks = ((R <= 4 ? 128 : 96) * 4 + kGroupThreads - 1) / kGroupThreads;   // per thread and K block
+            const int8_t* w_tile0 = p.w_ptr + (int64_t)w_row0 * kPackK + (int64_t)wt * 16;
+            const int64_t kb_stride = p.w_npad * kPackK;
+            uint4 cur[kChunks], nxt[kChunks];
+            auto load_stage = [&](int st, uint4 (&dst)[kChunks]) {
+#pragma unroll
+                for (int i = 0; i < kChunks; ++i) {
+                    const int ch = wt + i * group_threads;
+                    if (st < nstages && ch < chunks_w)
+                        dst[i] = __ldg(reinterpret_cast<const uint4*>(w_tile0 + (int64_t)st * kb_stride + (int64_t)i * group_threads * 16));
+                    else
+                        dst[i] = make_uint4(0u, 0u, 0u, 0u);
+                }
+            };
+            load_stage(group, cur);
+            load_stage(group + groups, nxt);
+            RingPos ring_e(enc_stages, group);
+            for (int st = group; st < nstages && ok; st += groups, ring_e.advance(groups)) {
+                const int se = ring_e.slot;
+                uint8_t* enc = tiles_ptr + enc_ring_offset + (size_t)se * enc_stage_bytes;
+                uint4 ahead[kChunks];
+                load_stage(st + 2 * groups, ahead);
+                if (ring_e.round > 0)
+                    ok = warp_wait_bounded<false, kSpinWorkers>(smem_addr(&ctl.empty_enc[se]), (ring_e.round - 1) & 1, abort);
+                if (!ok) break;
+#pragma unroll
+                for (int i = 0; i < kChunks; ++i) {
+                    const int ch = wt + i * group_threads;
+                    if (ch < chunks_w && !RNS_ABLATED(0)) {
+                        const uint4 x = cur[i];
+                        const uint32_t u0 = x.x ^ 0x80808080u, u1 = x.y ^ 0x80808080u;
+                        const uint32_t u2 = x.z ^ 0x80808080u, u3 = x.w ^ 0x80808080u;
+                        const uint32_t d0 = fold_pattern(x.x), d1 = fold_pattern(x.y);
+                        const uint32_t d2 = fold_pattern(x.z), d3 = fold_pattern(x.w);
+                        uint8_t* dst = enc + ch * 16;
+#pragma unroll
+                        for (int c = 0; c < R; ++c) {
+                            uint4 y;
+                            y.x = encode_word_reduced(u0, d0, enc_mfold[c]);
+                            y.y = encode_word_reduced(u1, d1, enc_mfold[c]);
+                            y.z = encode_word_reduced(u2, d2, enc_mfold[c]);
+                            y.w = encode_word_reduced(u3, d3, enc_mfold[c]);
+                            *reinterpret_cast<uint4*>(dst + (size_t)c * tile_w_bytes) = y;
+                        }
+                    }
+                }
+#pragma unroll
+                for (int i = 0; i < kChunks; ++i) { cur[i] = nxt[i]; nxt[i] = ahead[i]; }
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_addr(&ctl.full_enc[se]));
+            }
+        }
         RingPos ring_r(raw_stages, group), ring_e(enc_stages, group);
-        for (int st = group; st < nstages && ok; st += groups, ring_r.advance(groups), ring_e.advance(groups)) {
+        for (int st = group; st < nstages && ok && !W_DIRECT; st += groups, ring_r.advance(groups), ring_e.advance(groups)) {
             const int sr = ring_r.slot, se = ring_e.slot;
             const uint32_t round_r = ring_r.round, round_e = ring_e.round;
             const uint8_t* raw_stage = tiles_ptr + (size_t)sr * raw_stage_bytes;
             uint8_t* enc_stage = tiles_ptr + enc_ring_offset + (size_t)se * enc_stage_bytes;
-            const int jn = min(J, kblocks - st * J);
+            const int jn = (FIXED && J_ == 1) ? 1 : min(J, kblocks - st * J);
             // Order matters once several groups run ahead of each other: the operand
             // slot must first be released by the MMAs of its previous round.  Because
             // the raw ring is at least as deep as the operand ring, that also proves
@@ -524,8 +596,10 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             if (ok && !RNS_ABLATED(10)) ok = warp_wait_bounded<false, kSpinWorkers>(smem_addr(&ctl.full_raw[sr]), round_r & 1, abort);
             if (threadIdx.x == 64) { RNS_TOC(6, t_e); RNS_TRACE(5, st); }
             if (!ok) break;
-            for (int jp = 0; jp < (RNS_ABLATED(0) ? 0 : 2 * jn); ++jp) {
-                const int j = jp >> 1, part = jp & 1;
+            // part 0: the W tile; part 1: the A tile (nothing to do when activations are planes)
+            const int parts = (FIXED || a_planes) ? 1 : 2;
+            for (int jp = 0; jp < (RNS_ABLATED(0) ? 0 : parts * jn); ++jp) {
+                const int j = parts == 1 ? jp : jp >> 1, part = parts == 1 ? 0 : jp & 1;
                 const int chunks = part == 0 ? chunks_w : chunks_a;
                 const uint8_t* raw = raw_stage + (size_t)j * raw_sub_bytes + (part == 0 ? off_raw_w : off_raw_a);
                 uint8_t* enc = enc_stage + (size_t)j * enc_sub_bytes + (part == 0 ? off_enc_w : off_enc_a);
@@ -566,9 +640,10 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             const bool is_float = p.out_type >= RNS_OUT_F16;
             if (is_float && row < p.m) rs = p.row_scale[(int64_t)row * p.row_scale_stride];
             using XInt = typename std::conditional<(R <= 4), int, long long>::type;
-            for (int col = part * 8; col < tile_n; col += (kWorkerWarps / 4) * 8) {
-                __syncwarp();  // the tensor-memory loads below are warp-collective
-                int acc[R][8];
+            // load: R x 8 accumulator columns of this thread's row (warp-collective);
+            // finish: reconstruction, dequantisation and the store of those 8 outputs.
+            auto load = [&](int col, int (&acc)[R][8]) {
+                __syncwarp();
 #pragma unroll
                 for (int c = 0; c < R; ++c) {
                     if (c < active) {
@@ -578,9 +653,10 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                         for (int e = 0; e < 8; ++e) acc[c][e] = 0;
                     }
                 }
-                tmem_ld_wait();
+            };
+            auto finish = [&](int col, const int (&acc)[R][8]) {
                 const int gcol = n0 + col;
-                if (row >= p.m || gcol >= p.n) continue;
+                if (row >= p.m || gcol >= p.n) return;
                 XInt xs[8];
 #pragma unroll
                 for (int e = 0; e < 8; ++e) {
@@ -601,19 +677,40 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 #pragma unroll
                     for (int e = 0; e < 8; ++e) if (e < valid) out[e] = (int)xs[e];
                 } else {
+                    // column scales and bias of these 8 outputs: two 16-byte loads each when
+                    // the group is whole and aligned
+                    float cs[8], bs[8];
+                    const float* cs_ptr = p.col_scale + gcol;
+                    const float* bs_ptr = p.bias != nullptr ? p.bias + gcol : nullptr;
+                    const bool whole = valid == 8 && (reinterpret_cast<uintptr_t>(cs_ptr) & 15) == 0 &&
+                                       (reinterpret_cast<uintptr_t>(bs_ptr) & 15) == 0;
+                    if (whole) {
+                        const float4 c0 = __ldg(reinterpret_cast<const float4*>(cs_ptr));
+                        const float4 c1 = __ldg(reinterpret_cast<const float4*>(cs_ptr) + 1);
+                        cs[0] = c0.x; cs[1] = c0.y; cs[2] = c0.z; cs[3] = c0.w;
+                        cs[4] = c1.x; cs[5] = c1.y; cs[6] = c1.z; cs[7] = c1.w;
+                        if (bs_ptr != nullptr) {
+                            const float4 b0 = __ldg(reinterpret_cast<const float4*>(bs_ptr));
+                            const float4 b1 = __ldg(reinterpret_cast<const float4*>(bs_ptr) + 1);
+                            bs[0] = b0.x; bs[1] = b0.y; bs[2] = b0.z; bs[3] = b0.w;
+                            bs[4] = b1.x; bs[5] = b1.y; bs[6] = b1.z; bs[7] = b1.w;
+                        }
+                    } else {
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) {
+                            cs[e] = e < valid ? cs_ptr[e] : 0.0f;
+                            bs[e] = (e < valid && bs_ptr != nullptr) ? bs_ptr[e] : 0.0f;
+                        }
+                    }
                     float y[8];
 #pragma unroll
                     for (int e = 0; e < 8; ++e) {
-                        if (e < valid) {
-                            float xf;
-                            if constexpr (R <= 4) xf = __int2float_rn(xs[e]);
-                            else xf = __ll2float_rn(xs[e]);
-                            float v = __fmul_rn(__fmul_rn(xf, rs), p.col_scale[gcol + e]);
-                            if (p.bias != nullptr) v = __fadd_rn(v, p.bias[gcol + e]);
-                            y[e] = v;
-                        } else {
-                            y[e] = 0.0f;
-                        }
+                        float xf;
+                        if constexpr (R <= 4) xf = __int2float_rn(xs[e]);
+                        else xf = __ll2float_rn(xs[e]);
+                        float v = __fmul_rn(__fmul_rn(xf, rs), cs[e]);
+                        if (bs_ptr != nullptr) v = __fadd_rn(v, bs[e]);
+                        y[e] = v;
                     }
                     if (p.out_type == RNS_OUT_F32) {
                         float* out = static_cast<float*>(p.out) + o;
@@ -642,6 +739,33 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                             for (int e = 0; e < 8; ++e) if (e < valid) out[e] = __float2bfloat16_rn(y[e]);
                         }
                     }
+                }
+            };
+            constexpr int kColStep = (kWorkerWarps / 4) * 8;
+            if constexpr (FIXED && R <= 4) {
+                // The loads of the next column group are in flight while this one is
+                // finished (two register buffers, loop unrolled by hand).
+                constexpr int kIters = (R <= 4 ? 128 : 96) / kColStep;
+                const int col0 = part * 8;
+                int a0[R][8], a1[R][8];
+                load(col0, a0);
+#pragma unroll
+                for (int it = 0; it < kIters; it += 2) {
+                    tmem_ld_wait();
+                    if (it + 1 < kIters) load(col0 + (it + 1) * kColStep, a1);
+                    finish(col0 + it * kColStep, a0);
+                    if (it + 1 < kIters) {
+                        tmem_ld_wait();
+                        if (it + 2 < kIters) load(col0 + (it + 2) * kColStep, a0);
+                        finish(col0 + (it + 1) * kColStep, a1);
+                    }
+                }
+            } else {
+                for (int col = part * 8; col < tile_n; col += kColStep) {
+                    int acc[R][8];
+                    load(col, acc);
+                    tmem_ld_wait();
+                    finish(col, acc);
                 }
             }
         }
@@ -716,7 +840,7 @@ static bool tc_supported(const Plan& pl, int k, int64_t lda, int64_t ldw, bool e
     return true;
 }
 
-template <int R, bool PAIR, int J_ = 0, int ES_ = 0, int PS_ = 0, int RS_ = 0>
+template <int R, bool PAIR, int J_ = 0, int ES_ = 0, int PS_ = 0, int RS_ = 0, int G_ = 0>
 static int launch(const CUtensorMap& ma, const CUtensorMap& mw, const GemmParams& gp, dim3 grid,
                   size_t smem, cudaStream_t st) {
     // The opt-in shared-memory size is a per-device function attribute: set it on
@@ -726,7 +850,7 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& mw, const GemmParams
     RNS_CUDA_OK(cudaGetDevice(&dev));
     const uint64_t bit = 1ull << (dev & 63);
     if (!(configured.load(std::memory_order_acquire) & bit)) {
-        RNS_CUDA_OK(cudaFuncSetAttribute(rns_gemm_kernel<R, PAIR, J_, ES_, PS_, RS_>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        RNS_CUDA_OK(cudaFuncSetAttribute(rns_gemm_kernel<R, PAIR, J_, ES_, PS_, RS_, G_>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          227 * 1024 - 1024));
         configured.fetch_or(bit, std::memory_order_release);
     }
@@ -745,10 +869,10 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& mw, const GemmParams
         cfg.attrs = attr;
         cfg.numAttrs = 1;
     }
-    const cudaError_t rc = cudaLaunchKernelEx(&cfg, rns_gemm_kernel<R, PAIR, J_, ES_, PS_, RS_>, ma, mw, gp);
+    const cudaError_t rc = cudaLaunchKernelEx(&cfg, rns_gemm_kernel<R, PAIR, J_, ES_, PS_, RS_, G_>, ma, mw, gp);
     if (rc != cudaSuccess) {
         int clusters = -1;
-        if (PAIR) cudaOccupancyMaxActiveClusters(&clusters, rns_gemm_kernel<R, PAIR, J_, ES_, PS_, RS_>, &cfg);
+        if (PAIR) cudaOccupancyMaxActiveClusters(&clusters, rns_gemm_kernel<R, PAIR, J_, ES_, PS_, RS_, G_>, &cfg);
         cudaGetLastError();
         return fail(RNS_ERR_CUDA, "launch of the RNS GEMM failed: %s (grid %u x %u, smem %zu, pair %d, "
                     "max active clusters %d)", cudaGetErrorString(rc), grid.x, grid.y, smem, (int)PAIR, clusters);
@@ -920,6 +1044,21 @@ int rns_linear_fused(const rns_linear_args* a, rns_stream_t stream) {
     while (planes && pl_stages < pl_cap && pl_stages < 6 && ring_bytes(enc_stages, pl_stages + 1, raw_stages) <= kSmemBudget)
         ++pl_stages;
     while (raw_stages < pl_cap && ring_bytes(enc_stages, pl_stages, raw_stages + 1) <= kSmemBudget) ++raw_stages;
+    // Single-CTA tiles of the hot configuration read W straight from global memory in
+    // the encoder threads: no raw ring, and its memory deepens the operand ring.
+    const bool w_direct = !pair && planes && a_packed && w_packed && tile_k == 64 && a->d_active_channels == nullptr &&
+                          a->exact_residues == 0 && (R == 4 || R == 5) && tile_n == (R <= 4 ? 128 : 96) &&
+                          a->sub_blocks == 0 && a->enc_stages == 0 && a->enc_groups == 0 && kblocks >= 8;
+    if (w_direct) {
+        sub_blocks = 1;
+        gp.sub_blocks = 1;
+        gp.raw_stage_bytes = gp.raw_sub_bytes;
+        gp.enc_stage_bytes = gp.enc_sub_bytes;
+        gp.pl_stage_bytes = gp.pl_sub_bytes;
+        raw_stages = 0;
+        enc_stages = R == 4 ? 4 : 3;
+        pl_stages = 3;
+    }
     gp.raw_stages = raw_stages;
     gp.enc_stages = enc_stages;
     gp.pl_stages = pl_stages > 0 ? pl_stages : 1;
@@ -979,13 +1118,34 @@ int rns_linear_fused(const rns_linear_args* a, rns_stream_t stream) {
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     // The hot configurations have instantiations with compile-time ring parameters.
     const bool fixed_ok = planes && a_packed && w_packed && tile_k == 64 && a->d_active_channels == nullptr &&
-                          a->exact_residues == 0 && gp.enc_groups == 2 && tile_n == (R <= 4 ? 128 : 96);
-    auto rings_are = [&](int j, int es, int ps, int rs) {
-        return fixed_ok && sub_blocks == j && enc_stages == es && pl_stages == ps && raw_stages == rs;
+                          a->exact_residues == 0 && tile_n == (R <= 4 ? 128 : 96);
+    auto rings_are = [&](int j, int es, int ps, int rs, int g) {
+        return fixed_ok && sub_blocks == j && enc_stages == es && pl_stages == ps && raw_stages == rs &&
+               gp.enc_groups == g;
     };
-    if (R == 4 && pair && rings_are(2, 2, 2, 4)) return launch<4, true, 2, 2, 2, 4>(map_a, map_w, gp, grid, smem, st);
-    if (R == 4 && !pair && rings_are(1, 3, 3, 4)) return launch<4, false, 1, 3, 3, 4>(map_a, map_w, gp, grid, smem, st);
-    if (R == 5 && !pair && rings_are(1, 2, 3, 7)) return launch<5, false, 1, 2, 3, 7>(map_a, map_w, gp, grid, smem, st);
+#define RNS_FIXED(r, pr, j, es, ps, rs, g) \
+    if (R == r && pair == pr && rings_are(j, es, ps, rs, g)) \
+        return launch<r, pr, j, es, ps, rs, g>(map_a, map_w, gp, grid, smem, st);
+    // (one encoder group measured best with direct weight loads: 1.80 against 1.72
+    // channel-POPS at 4096^3)
+    if (w_direct) gp.enc_groups = 1;
+    if (w_direct && R == 4) return launch<4, false, 1, 4, 3, -1, 1>(map_a, map_w, gp, grid, smem, st);
+    if (w_direct && R == 5) return launch<5, false, 1, 3, 3, -1, 1>(map_a, map_w, gp, grid, smem, st);
+    RNS_FIXED(4, false, 1, 3, 3, 4, 2)
+    RNS_FIXED(5, false, 1, 2, 3, 7, 2)
+    RNS_FIXED(4, true, 2, 2, 2, 4, 2)
+#ifdef RNS_MORE_FIXED
+    RNS_FIXED(4, false, 1, 3, 3, 4, 1)
+    RNS_FIXED(4, false, 1, 2, 4, 4, 2)
+    RNS_FIXED(4, false, 1, 2, 4, 4, 1)
+    RNS_FIXED(5, false, 1, 2, 3, 7, 1)
+    RNS_FIXED(4, true, 2, 2, 2, 4, 1)
+    RNS_FIXED(4, true, 1, 4, 4, 8, 2)
+    RNS_FIXED(4, true, 1, 4, 4, 8, 4)
+    RNS_FIXED(4, true, 1, 3, 5, 4, 2)
+    RNS_FIXED(4, true, 1, 2, 6, 4, 2)
+#endif
+#undef RNS_FIXED
     switch (R) {
         case 2: return launch_either<2>(pair, map_a, map_w, gp, grid, smem, st);
         case 3: return launch_either<3>(pair, map_a, map_w, gp, grid, smem, st);

@@ -132,6 +132,22 @@ def test_tensor_memory_operand_variant(backend, mods):
         fused_int(backend, a, w, mods, variant=2)
 
 
+@pytest.mark.parametrize("mods", [C0, C4])
+def test_fixed_configuration_kernels(backend, mods):
+    """Packed planes, every channel active, default knobs and the full-width tile select
+    the instantiations with compile-time ring parameters (single-CTA tiles: weights read
+    straight from global memory by the encoder threads; pair tiles for four channels).
+    Ragged rows and columns, K from 8 blocks up."""
+    rng = np.random.default_rng(len(mods) * 31)
+    tile = 128 if len(mods) <= 4 else 96
+    for m, k, n in [(300, 1024, 260), (129, 512, 130), (256, 4096, 200), (640, 576, 96)]:
+        a, w = rand_i8(rng, (m, k), -128, 127), rand_i8(rng, (n, k), -128, 127)
+        exact = O.exact_matmul(a, w.T)
+        for pair in ([0, 1] if len(mods) <= 4 else [0]):
+            got = fused_int(backend, a, w, mods, planes=True, packed=True, pair_mode=pair, tile_n=tile)
+            assert np.array_equal(got, exact), (m, k, n, pair)
+
+
 @pytest.mark.parametrize("tuning", [dict(sub_blocks=1), dict(sub_blocks=2), dict(sub_blocks=4),
                                     dict(sub_blocks=2, enc_stages=2), dict(enc_groups=1, enc_stages=1),
                                     dict(enc_groups=2, enc_stages=3), dict(enc_groups=4, enc_stages=4),
