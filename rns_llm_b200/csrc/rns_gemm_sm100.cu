@@ -299,7 +299,9 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         for (int s = 0; s < kMaxStages; ++s) {
             mbar_init(smem_addr(&ctl.full_raw[s]), 1);
             mbar_init(smem_addr(&ctl.empty_raw[s]), kWorkerWarps / groups);
-            mbar_init(smem_addr(&ctl.full_enc[s]), kWorkerWarps / groups);
+            // ONE_COMMIT kernels: the plane load of a stage signals the operand ring's
+            // "full" barrier too (one more arrival), so the MMA warp waits once per stage.
+            mbar_init(smem_addr(&ctl.full_enc[s]), kWorkerWarps / groups + (ONE_COMMIT ? 1 : 0));
             mbar_init(smem_addr(&ctl.empty_enc[s]), 1);
             mbar_init(smem_addr(&ctl.full_pl[s]), 1);
             mbar_init(smem_addr(&ctl.empty_pl[s]), 1);
@@ -374,6 +376,7 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             const uint32_t a_bytes = (uint32_t)active * tile_a_bytes;
             RingPos ring(pl_stages, 0);
             RingPos released(enc_stages, 0);   // ONE_COMMIT: the stage whose plane slot is reused
+            RingPos filled(enc_stages, 0);     // ONE_COMMIT: operand-ring barrier of the stage being loaded
             for (int st = 0; st < nstages; ++st, ring.advance(1)) {
                 const int s = ring.slot;
                 const uint32_t round = ring.round;
@@ -386,7 +389,8 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     }
                 } else if (round > 0 && !RNS_ABLATED(11) && !wait_bounded<false, true>(smem_addr(&ctl.empty_pl[s]), (round - 1) & 1, abort)) break;
                 RNS_TRACE(0, st);
-                const uint32_t fp = smem_addr(&ctl.full_pl[s]);
+                const uint32_t fp = ONE_COMMIT ? smem_addr(&ctl.full_enc[filled.slot]) : smem_addr(&ctl.full_pl[s]);
+                if (ONE_COMMIT) filled.advance(1);
                 mbar_arrive_expect_tx(fp, RNS_ABLATED(2) ? 0u : a_bytes * (uint32_t)jn);
                 for (int j = 0; j < jn && !RNS_ABLATED(2); ++j) {
                     const int kb = st * J + j;
@@ -446,7 +450,7 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 const int sa = a_planes ? ring_pl.slot : s;       // slot of the A operands
                 ok = warp_wait_bounded<false, true>(smem_addr(&ctl.full_enc[s]), round & 1, abort);
                 RNS_TRACE(8, st);
-                if (ok && a_planes && !RNS_ABLATED(11))
+                if (ok && a_planes && !RNS_ABLATED(11) && !ONE_COMMIT)
                     ok = warp_wait_bounded<false, true>(smem_addr(&ctl.full_pl[sa]), ring_pl.round & 1, abort);
                 RNS_TRACE(9, st);
                 if (ok && PAIR) ok = warp_wait_bounded<true>(smem_addr(&ctl.peer_ready[s]), round & 1, abort);
