@@ -213,9 +213,17 @@ RNS_HD int reconstruct32(const int (&acc)[R], const Plan& pl, int active) {
     float digit[R];
     garner_digits<R>(acc, pl, active, digit);
     unsigned x = 0;
+    if (R == 4 && active == 4) {
+        // d0 + m0*d1 and d2 + m2*d3 are exact in fp32 (|.| < 2^15): two conversions and
+        // one integer multiply-add instead of four of each.
+        const float lo = fma_rn(pl.modf[0], digit[1], digit[0]);
+        const float hi = fma_rn(pl.modf[R > 2 ? 2 : 0], digit[R > 3 ? 3 : 0], digit[R > 2 ? 2 : 0]);
+        x = (unsigned)small_float_to_int(lo) + pl.place32[R > 2 ? 2 : 0] * (unsigned)small_float_to_int(hi);
+    } else {
 #pragma unroll
-    for (int i = 0; i < R; ++i)
-        if (i < active) x += pl.place32[i] * (unsigned)small_float_to_int(digit[i]);
+        for (int i = 0; i < R; ++i)
+            if (i < active) x += pl.place32[i] * (unsigned)small_float_to_int(digit[i]);
+    }
     const unsigned prod = (unsigned)pl.product[active];
     const int half = (int)(prod >> 1);
     const int low = (int)((unsigned)half - prod + 1u);

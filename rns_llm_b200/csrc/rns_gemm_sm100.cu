@@ -260,6 +260,12 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     // stage serves both: the plane producer of stage st waits on the operand ring's
     // barrier of stage st - PS_ (one commit less on the MMA warp's path).
     constexpr bool ONE_COMMIT = W_DIRECT && !PAIR && ES_ >= PS_;
+    // In those kernels warp 0 has no loads to issue and becomes a second MMA issuer:
+    // warp 1 takes the even stages, warp 0 the odd ones.  Integer accumulation does not
+    // depend on the order of the MMAs; the accumulators are zeroed beforehand, so that
+    // no MMA has to come first.  Each issuer's instruction stream per stage is longer
+    // than the MMAs it issues; two of them keep the tensor pipe fed.
+    constexpr bool TWO_ISSUERS = ONE_COMMIT;
     const int tile_k = FIXED ? 64 : p.tile_k;
     const int tile_n = FIXED ? (R <= 4 ? 128 : 96) : p.tile_n;
     const int m_tile = PAIR ? 2 * (int)blockIdx.y + (int)pair_rank : (int)blockIdx.y;
@@ -307,7 +313,7 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             mbar_init(smem_addr(&ctl.empty_pl[s]), 1);
             mbar_init(smem_addr(&ctl.peer_ready[s]), 1);
         }
-        mbar_init(smem_addr(&ctl.acc_full), 1);
+        mbar_init(smem_addr(&ctl.acc_full), TWO_ISSUERS ? 2 : 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -329,7 +335,7 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     const uint32_t pl_base = tiles_base + pl_ring_offset;
     const int pl_stages = FIXED ? PS_ : p.pl_stages;
 
-    if (warp == 0) {
+    if (warp == 0 && !TWO_ISSUERS) {
         // ------------------------------ raw-tile producer -------------------------
         // Source bytes (the W tile, and the A tile when activations are not planes)
         // go to the deep raw ring; a slot is free as soon as the encoders have read it.
@@ -407,7 +413,7 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             }
         }
         __syncwarp();
-    } else if (warp == 1) {
+    } else if (warp == 1 || (TWO_ISSUERS && warp == 0)) {
         // ------------------------------ MMA issuer --------------------------------
         // PAIR: only the leader issues MMAs; the peer's lane relays "my stage is
         // complete" to the leader's peer_ready barrier.  Completion of the MMAs is
@@ -441,8 +447,9 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 #pragma unroll
             for (int c = 0; c < R; ++c) { a_off[c] = (uint32_t)c * a_step; w_off[c] = (uint32_t)c * w_step; }
             bool ok = true;
-            RingPos ring(enc_stages, 0), ring_pl(pl_stages, 0);
-            for (int st = 0; st < nstages && ok; ++st, ring.advance(1), ring_pl.advance(1)) {
+            const int st_first = (TWO_ISSUERS && warp == 0) ? 1 : 0, st_step = TWO_ISSUERS ? 2 : 1;
+            RingPos ring(enc_stages, st_first), ring_pl(pl_stages, st_first);
+            for (int st = st_first; st < nstages && ok; st += st_step, ring.advance(st_step), ring_pl.advance(st_step)) {
                 const int s = ring.slot;
                 const uint32_t round = ring.round;
                 const int jn = (FIXED && J_ == 1) ? 1 : min(J, kblocks - st * J);
@@ -463,7 +470,7 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 const uint32_t empty_pl_bar = smem_addr(&ctl.empty_pl[sa]);
                 for (int j = 0; j < jn; ++j) {
                     const uint32_t a_j = a_st + (uint32_t)j * a_sub_step, w_j = w_st + (uint32_t)j * sub_step;
-                    const uint32_t first = (st > 0 || j > 0) ? 1u : 0u;
+                    const uint32_t first = (TWO_ISSUERS || st > 0 || j > 0) ? 1u : 0u;
                     if (elect_one()) {
 #pragma unroll
                         for (int c = 0; c < R; ++c) {
@@ -524,6 +531,18 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         const bool reduced = FIXED ? true : p.exact_residues == 0;
         const bool fast = p.plan.encode_fast != 0;
         bool ok = true;
+        if constexpr (TWO_ISSUERS) {
+            // Zero the accumulators (this warp's lane quarter, 128 of the 512 columns):
+            // with two issuers no MMA is "the first one" that would overwrite them.
+            const uint32_t zero_at = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(((warp - 2) >> 2) * 128);
+            uint32_t zeros[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) zeros[i] = 0u;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) tmem_st16(zero_at + (uint32_t)(i * 16), zeros);
+            tmem_st_wait();
+            tc_fence_before();
+        }
         if constexpr (W_DIRECT) {
             // Chunks wt, wt + group_threads, ... of the W tile of K block kb sit at
             // w_tile(kb) + 16 * chunk in the packed weight matrix (a tile is contiguous).
