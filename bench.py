@@ -58,8 +58,8 @@ def channel_ops_per_step(tokens: int, layers: int) -> float:
 
 # Mean DRAM traffic of one rns_gemm_kernel launch of this workload on one GPU
 # (dram__bytes_read.sum + dram__bytes_write.sum over the four linears of a layer:
-# 277 + 98 + 483 + 1116 MB), from an ncu capture of `bench.py --layers 2`.
-NCU_DRAM_BYTES_PER_LAUNCH = 493.2e6
+# 271 + 98 + 505 + 1114 MB), from an ncu capture of `bench.py --layers 2`.
+NCU_DRAM_BYTES_PER_LAUNCH = 496.9e6
 
 
 def algorithmic_bytes_per_launch(tokens: int) -> float:
