@@ -259,10 +259,8 @@ struct QuantOut {
 
 // Quantises columns [c, c+8) of row r, stores values and planes, returns sum |q|.
 template <typename T>
-__device__ __forceinline__ int quantize_group(const SrcView& s, const QuantOut& o, int r, int c,
-                                              float scale, int qmax) {
-    float v[8];
-    load8<T>(s, r, c, v);
+__device__ __forceinline__ int quantize_loaded(const float (&v)[8], const SrcView& s, const QuantOut& o, int r, int c,
+                                               float scale, int qmax) {
     int q[8];
     int l1 = 0;
 #pragma unroll
@@ -310,12 +308,39 @@ __device__ __forceinline__ int quantize_group(const SrcView& s, const QuantOut& 
         }
     } else {
         // ragged tail or unaligned output: plain layout only (the packed layout needs K % 8 == 0)
-        for (int i = 0; i < 8 && c + i < s.k; ++i) {
-            if (o.q) o.q[off + i] = (int8_t)q[i];
-            if (o.planes)
-                for (int ch = 0; ch < o.channels; ++ch)
-                    o.planes[(int64_t)ch * s.m * s.k + off + i] = (int8_t)centred_residue(q[i], o.mod[ch]);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            if (c + i < s.k) {
+                if (o.q) o.q[off + i] = (int8_t)q[i];
+                if (o.planes)
+                    for (int ch = 0; ch < o.channels; ++ch)
+                        o.planes[(int64_t)ch * s.m * s.k + off + i] = (int8_t)centred_residue(q[i], o.mod[ch]);
+            }
         }
+    }
+    return l1;
+}
+
+template <typename T>
+__device__ __forceinline__ int quantize_group(const SrcView& s, const QuantOut& o, int r, int c,
+                                              float scale, int qmax) {
+    float v[8];
+    load8<T>(s, r, c, v);
+    return quantize_loaded<T>(v, s, o, r, c, scale, qmax);
+}
+
+// Two groups of a row per step, both loads issued before either is processed.
+template <typename T>
+__device__ __forceinline__ int quantize_row(const SrcView& s, const QuantOut& o, int row, int lane,
+                                            int groups_per_row, float scale, int qmax) {
+    int l1 = 0;
+    for (int g = lane; g < groups_per_row; g += 64) {
+        float v0[8], v1[8];
+        const bool second = g + 32 < groups_per_row;
+        load8<T>(s, row, g * 8, v0);
+        if (second) load8<T>(s, row, (g + 32) * 8, v1);
+        l1 += quantize_loaded<T>(v0, s, o, row, g * 8, scale, qmax);
+        if (second) l1 += quantize_loaded<T>(v1, s, o, row, (g + 32) * 8, scale, qmax);
     }
     return l1;
 }
@@ -380,8 +405,7 @@ quantize_rows_kernel(const __grid_constant__ SrcView s, const __grid_constant__ 
             if (PER_ROW) o.scale[row] = scale;
             else if (row == 0) o.scale[0] = scale;
         }
-        int l1 = 0;
-        for (int g = lane; g < groups_per_row; g += 32) l1 += quantize_group<T>(s, o, row, g * 8, scale, qmax);
+        const int l1 = quantize_row<T>(s, o, row, lane, groups_per_row, scale, qmax);
         if (o.row_l1_max) worst_l1 = max(worst_l1, warp_sum(l1));
     }
     if (o.row_l1_max && lane == 0 && worst_l1 > 0) atomicMax(o.row_l1_max, worst_l1);
@@ -415,8 +439,7 @@ quantize_small_kernel(const __grid_constant__ SrcView s, const __grid_constant__
     if (threadIdx.x == 0) o.scale[0] = scale;
     int worst_l1 = 0;
     for (int row = warp; row < s.m; row += (int)(blockDim.x >> 5)) {
-        int l1 = 0;
-        for (int g = lane; g < groups_per_row; g += 32) l1 += quantize_group<T>(s, o, row, g * 8, scale, qmax);
+        const int l1 = quantize_row<T>(s, o, row, lane, groups_per_row, scale, qmax);
         if (o.row_l1_max) worst_l1 = max(worst_l1, warp_sum(l1));
     }
     if (o.row_l1_max && lane == 0 && worst_l1 > 0) atomicMax(o.row_l1_max, worst_l1);
