@@ -255,6 +255,10 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     // RS_ < 0: no raw ring at all; the encoder threads read their weight bytes from
     // global memory into registers, two of their stages ahead (packed weights, J_ == 1).
     constexpr bool W_DIRECT = FIXED && RS_ < 0;
+    // ... and with PS_ == 0 the same goes for the activations: they arrive as packed int8
+    // (one byte per value instead of R planes), the encoder threads produce the operand
+    // tiles of both sides, and the main loop has no bulk copies at all.
+    constexpr bool A_DIRECT = W_DIRECT && PS_ == 0;
     // The operand slot and the plane slot of a stage are released by the same MMAs.
     // When the operand ring is at least as deep as the plane ring, one commit per
     // stage serves both: the plane producer of stage st waits on the operand ring's
@@ -277,14 +281,14 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     const int raw_stages = FIXED ? (RS_ > 0 ? RS_ : 1) : p.raw_stages, enc_stages = FIXED ? ES_ : p.enc_stages;
     const int J = FIXED ? J_ : p.sub_blocks;          // K blocks per stage
     const int nstages = (kblocks + J - 1) / J;       // stage hand-overs in the K loop
-    const bool a_planes = FIXED ? true : p.a_is_planes != 0;
+    const bool a_planes = FIXED ? !A_DIRECT : p.a_is_planes != 0;
     const bool a_packed = FIXED ? true : p.a_packed != 0, w_packed = FIXED ? true : p.w_packed != 0;
     const int groups = FIXED ? G_ : p.enc_groups;
     // Shared-memory map: the parameters' values, or the same values as constants.
     const uint32_t tile_a_bytes = FIXED ? (uint32_t)(kTileM * 64) : p.tile_a_bytes;
     const uint32_t tile_w_bytes = FIXED ? (uint32_t)((PAIR ? tile_n / 2 : tile_n) * 64) : p.tile_w_bytes;
     const uint32_t raw_sub_bytes = FIXED ? ((tile_w_bytes + 1023u) & ~1023u) : p.raw_sub_bytes;
-    const uint32_t enc_sub_bytes = FIXED ? (((uint32_t)R * tile_w_bytes + 1023u) & ~1023u) : p.enc_sub_bytes;
+    const uint32_t enc_sub_bytes = FIXED ? (((uint32_t)R * (tile_w_bytes + (A_DIRECT ? tile_a_bytes : 0u)) + 1023u) & ~1023u) : p.enc_sub_bytes;
     const uint32_t pl_sub_bytes = FIXED ? (uint32_t)R * tile_a_bytes : p.pl_sub_bytes;
     const uint32_t raw_stage_bytes = FIXED ? (uint32_t)J_ * raw_sub_bytes : p.raw_stage_bytes;
     const uint32_t enc_stage_bytes = FIXED ? (uint32_t)J_ * enc_sub_bytes : p.enc_stage_bytes;
@@ -292,7 +296,7 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     const uint32_t enc_ring_offset = FIXED ? (uint32_t)(RS_ > 0 ? RS_ : 0) * raw_stage_bytes : p.enc_ring_offset;
     const uint32_t pl_ring_offset = FIXED ? enc_ring_offset + (uint32_t)ES_ * enc_stage_bytes : p.pl_ring_offset;
     const uint32_t off_raw_w = FIXED ? 0u : p.off_raw_w, off_raw_a = FIXED ? tile_w_bytes : p.off_raw_a;
-    const uint32_t off_enc_a = FIXED ? 0u : p.off_enc_a, off_enc_w = FIXED ? 0u : p.off_enc_w;
+    const uint32_t off_enc_a = FIXED ? 0u : p.off_enc_a, off_enc_w = FIXED ? (A_DIRECT ? (uint32_t)R * tile_a_bytes : 0u) : p.off_enc_w;
 
     int active = R;
     if (!FIXED && p.active_ptr != nullptr) {
@@ -307,7 +311,7 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             mbar_init(smem_addr(&ctl.empty_raw[s]), kWorkerWarps / groups);
             // ONE_COMMIT kernels: the plane load of a stage signals the operand ring's
             // "full" barrier too (one more arrival), so the MMA warp waits once per stage.
-            mbar_init(smem_addr(&ctl.full_enc[s]), kWorkerWarps / groups + (ONE_COMMIT ? 1 : 0));
+            mbar_init(smem_addr(&ctl.full_enc[s]), kWorkerWarps / groups + ((ONE_COMMIT && !A_DIRECT) ? 1 : 0));
             mbar_init(smem_addr(&ctl.empty_enc[s]), 1);
             mbar_init(smem_addr(&ctl.full_pl[s]), 1);
             mbar_init(smem_addr(&ctl.empty_pl[s]), 1);
@@ -333,7 +337,7 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     volatile int* abort = &ctl.abort;
     const uint32_t enc_base = tiles_base + enc_ring_offset;
     const uint32_t pl_base = tiles_base + pl_ring_offset;
-    const int pl_stages = FIXED ? PS_ : p.pl_stages;
+    const int pl_stages = FIXED ? (PS_ > 0 ? PS_ : 1) : p.pl_stages;
 
     if (warp == 0 && !TWO_ISSUERS) {
         // ------------------------------ raw-tile producer -------------------------
@@ -551,6 +555,36 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             constexpr int kChunks = ((R <= 4 ? 128 : 96) * 4 + kGroupThreads - 1) / kGroupThreads;   // per thread and K block
             const int8_t* w_tile0 = p.w_ptr + (int64_t)w_row0 * kPackK + (int64_t)wt * 16;
             const int64_t kb_stride = p.w_npad * kPackK;
+            // A_DIRECT: likewise for the activation tile (128 rows, contiguous 8 KB per K block).
+            constexpr int kChunksA = A_DIRECT ? (kTileM * 4 + kGroupThreads - 1) / kGroupThreads : 1;
+            const int8_t* a_tile0 = p.a_ptr + (int64_t)m_tile * kblocks * (kPackM * kPackK) + (int64_t)wt * 16;
+            uint4 cur_a[kChunksA], nxt_a[kChunksA];
+            auto load_stage_a = [&](int st, uint4 (&dst)[kChunksA]) {
+#pragma unroll
+                for (int i = 0; i < kChunksA; ++i) {
+                    const int ch = wt + i * group_threads;
+                    if (A_DIRECT && st < nstages && ch < chunks_a)
+                        dst[i] = __ldg(reinterpret_cast<const uint4*>(a_tile0 + (int64_t)st * (kPackM * kPackK) + (int64_t)i * group_threads * 16));
+                    else
+                        dst[i] = make_uint4(0u, 0u, 0u, 0u);
+                }
+            };
+            auto encode_chunk = [&](const uint4 x, uint8_t* dst, uint32_t tile_bytes) {
+                const uint32_t u0 = x.x ^ 0x80808080u, u1 = x.y ^ 0x80808080u;
+                const uint32_t u2 = x.z ^ 0x80808080u, u3 = x.w ^ 0x80808080u;
+                const uint32_t d0 = fold_pattern(x.x), d1 = fold_pattern(x.y);
+                const uint32_t d2 = fold_pattern(x.z), d3 = fold_pattern(x.w);
+#pragma unroll
+                for (int c = 0; c < R; ++c) {
+                    uint4 y;
+                    y.x = encode_word_reduced(u0, d0, enc_mfold[c]);
+                    y.y = encode_word_reduced(u1, d1, enc_mfold[c]);
+                    y.z = encode_word_reduced(u2, d2, enc_mfold[c]);
+                    y.w = encode_word_reduced(u3, d3, enc_mfold[c]);
+                    *reinterpret_cast<uint4*>(dst + (size_t)c * tile_bytes) = y;
+                }
+            };
+            if (A_DIRECT) { load_stage_a(group, cur_a); load_stage_a(group + groups, nxt_a); }
             uint4 cur[kChunks], nxt[kChunks];
             auto load_stage = [&](int st, uint4 (&dst)[kChunks]) {
 #pragma unroll
@@ -570,29 +604,24 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 uint8_t* enc = tiles_ptr + enc_ring_offset + (size_t)se * enc_stage_bytes;
                 uint4 ahead[kChunks];
                 load_stage(st + 2 * groups, ahead);
+                uint4 ahead_a[kChunksA];
+                if (A_DIRECT) load_stage_a(st + 2 * groups, ahead_a);
                 if (ring_e.round > 0)
                     ok = warp_wait_bounded<false, kSpinWorkers>(smem_addr(&ctl.empty_enc[se]), (ring_e.round - 1) & 1, abort);
                 if (!ok) break;
 #pragma unroll
                 for (int i = 0; i < kChunks; ++i) {
                     const int ch = wt + i * group_threads;
-                    if (ch < chunks_w && !RNS_ABLATED(0)) {
-                        const uint4 x = cur[i];
-                        const uint32_t u0 = x.x ^ 0x80808080u, u1 = x.y ^ 0x80808080u;
-                        const uint32_t u2 = x.z ^ 0x80808080u, u3 = x.w ^ 0x80808080u;
-                        const uint32_t d0 = fold_pattern(x.x), d1 = fold_pattern(x.y);
-                        const uint32_t d2 = fold_pattern(x.z), d3 = fold_pattern(x.w);
-                        uint8_t* dst = enc + ch * 16;
+                    if (ch < chunks_w && !RNS_ABLATED(0)) encode_chunk(cur[i], enc + off_enc_w + ch * 16, tile_w_bytes);
+                }
+                if (A_DIRECT) {
 #pragma unroll
-                        for (int c = 0; c < R; ++c) {
-                            uint4 y;
-                            y.x = encode_word_reduced(u0, d0, enc_mfold[c]);
-                            y.y = encode_word_reduced(u1, d1, enc_mfold[c]);
-                            y.z = encode_word_reduced(u2, d2, enc_mfold[c]);
-                            y.w = encode_word_reduced(u3, d3, enc_mfold[c]);
-                            *reinterpret_cast<uint4*>(dst + (size_t)c * tile_w_bytes) = y;
-                        }
+                    for (int i = 0; i < kChunksA; ++i) {
+                        const int ch = wt + i * group_threads;
+                        if (ch < chunks_a && !RNS_ABLATED(0)) encode_chunk(cur_a[i], enc + off_enc_a + ch * 16, tile_a_bytes);
                     }
+#pragma unroll
+                    for (int i = 0; i < kChunksA; ++i) { cur_a[i] = nxt_a[i]; nxt_a[i] = ahead_a[i]; }
                 }
 #pragma unroll
                 for (int i = 0; i < kChunks; ++i) { cur[i] = nxt[i]; nxt[i] = ahead[i]; }
@@ -1082,6 +1111,20 @@ int rns_linear_fused(const rns_linear_args* a, rns_stream_t stream) {
         enc_stages = R == 4 ? 4 : 3;
         pl_stages = 3;
     }
+    // ... and with packed int8 activations instead of planes the activation tile too.
+    const bool a_direct = !pair && !planes && a_packed && w_packed && tile_k == 64 && a->d_active_channels == nullptr &&
+                          a->exact_residues == 0 && (R == 4 || R == 5) && tile_n == (R <= 4 ? 128 : 96) &&
+                          a->sub_blocks == 0 && a->enc_stages == 0 && a->enc_groups == 0 && kblocks >= 8;
+    if (a_direct) {
+        sub_blocks = 1;
+        gp.sub_blocks = 1;
+        gp.raw_stage_bytes = gp.raw_sub_bytes;
+        gp.enc_stage_bytes = gp.enc_sub_bytes;
+        gp.pl_stage_bytes = 0;
+        raw_stages = 0;
+        enc_stages = 3;
+        pl_stages = 0;
+    }
     gp.raw_stages = raw_stages;
     gp.enc_stages = enc_stages;
     gp.pl_stages = pl_stages > 0 ? pl_stages : 1;
@@ -1151,6 +1194,9 @@ int rns_linear_fused(const rns_linear_args* a, rns_stream_t stream) {
         return launch<r, pr, j, es, ps, rs, g>(map_a, map_w, gp, grid, smem, st);
     // (one encoder group measured best with direct weight loads: 1.80 against 1.72
     // channel-POPS at 4096^3)
+    if (a_direct) gp.enc_groups = 1;
+    if (a_direct && R == 4) return launch<4, false, 1, 3, 0, -1, 1>(map_a, map_w, gp, grid, smem, st);
+    if (a_direct && R == 5) return launch<5, false, 1, 3, 0, -1, 1>(map_a, map_w, gp, grid, smem, st);
     if (w_direct) gp.enc_groups = 1;
     if (w_direct && R == 4) return launch<4, false, 1, 4, 3, -1, 1>(map_a, map_w, gp, grid, smem, st);
     if (w_direct && R == 5) return launch<5, false, 1, 3, 3, -1, 1>(map_a, map_w, gp, grid, smem, st);

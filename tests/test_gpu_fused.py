@@ -146,6 +146,9 @@ def test_fixed_configuration_kernels(backend, mods):
         for pair in ([0, 1] if len(mods) <= 4 else [0]):
             got = fused_int(backend, a, w, mods, planes=True, packed=True, pair_mode=pair, tile_n=tile)
             assert np.array_equal(got, exact), (m, k, n, pair)
+        # packed int8 activations: both operands encoded from global memory, no bulk copies
+        got = fused_int(backend, a, w, mods, packed=True, pair_mode=0, tile_n=tile)
+        assert np.array_equal(got, exact), (m, k, n, "int8 activations")
 
 
 @pytest.mark.parametrize("tuning", [dict(sub_blocks=1), dict(sub_blocks=2), dict(sub_blocks=4),
