@@ -235,6 +235,18 @@ __device__ __forceinline__ int quantize_one(float v, float scale, int qmax) {
     return (int)q;
 }
 
+// The same value with the division off the common path: t = v * (1/scale) is within
+// 2 ulp of v / scale, so the two round to different integers only when a half-integer
+// lies between them; only then (|t - round(t)| within 1e-4 of 0.5, or |t| >= 256 where
+// an ulp exceeds that margin, or NaN) the IEEE division is redone.
+__device__ __forceinline__ int quantize_one_fast(float v, float scale, float inv_scale, int qmax) {
+    const float t = __fmul_rn(v, inv_scale);
+    float q = rintf(t);
+    if (!(fabsf(t) < 256.0f) || fabsf(t - q) > 0.4999f) q = rintf(__fdiv_rn(v, scale));
+    q = fminf(fmaxf(q, (float)-qmax), (float)qmax);
+    return (int)q;
+}
+
 __device__ __forceinline__ int centred_residue(int v, int m) {
     int r = v % m;
     const int half = m / 2;
@@ -263,9 +275,10 @@ __device__ __forceinline__ int quantize_loaded(const float (&v)[8], const SrcVie
                                                float scale, int qmax) {
     int q[8];
     int l1 = 0;
+    const float inv_scale = __frcp_rn(scale);
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-        q[i] = quantize_one(v[i], scale, qmax);
+        q[i] = quantize_one_fast(v[i], scale, inv_scale, qmax);
         l1 += q[i] < 0 ? -q[i] : q[i];
     }
     const bool full = c + 8 <= s.k;
