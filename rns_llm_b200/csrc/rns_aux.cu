@@ -277,17 +277,17 @@ __device__ __forceinline__ int quantize_loaded(const float (&v)[8], const SrcVie
     int l1 = 0;
     const float inv_scale = __frcp_rn(scale);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        q[i] = quantize_one_fast(v[i], scale, inv_scale, qmax);
-        l1 += q[i] < 0 ? -q[i] : q[i];
+    for (int i = 0; i < 8; ++i) q[i] = quantize_one_fast(v[i], scale, inv_scale, qmax);
+    if (o.row_l1_max != nullptr) {   // only the adaptive path reads the row sums
+#pragma unroll
+        for (int i = 0; i < 8; ++i) l1 += q[i] < 0 ? -q[i] : q[i];
     }
     const bool full = c + 8 <= s.k;
-    uint32_t w0 = 0, w1 = 0;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        w0 |= (uint32_t)(q[i] & 0xff) << (8 * i);
-        w1 |= (uint32_t)(q[4 + i] & 0xff) << (8 * i);
-    }
+    // low bytes of four ints -> one word: (q0.b0, q1.b0) and (q2.b0, q3.b0), then both pairs
+    const uint32_t w0 = __byte_perm(__byte_perm((uint32_t)q[0], (uint32_t)q[1], 0x0040),
+                                    __byte_perm((uint32_t)q[2], (uint32_t)q[3], 0x0040), 0x5410);
+    const uint32_t w1 = __byte_perm(__byte_perm((uint32_t)q[4], (uint32_t)q[5], 0x0040),
+                                    __byte_perm((uint32_t)q[6], (uint32_t)q[7], 0x0040), 0x5410);
     // Plain: byte offset r*K + c, planes M*K apart.  Packed: tile layouts, where a
     // group of 8 columns (c % 8 == 0) is half of one 16-byte chunk.
     const int64_t off = o.packed ? packed_act_offset(r, c, 0, 1, o.kblocks) : (int64_t)r * s.k + c;
@@ -298,13 +298,19 @@ __device__ __forceinline__ int quantize_loaded(const float (&v)[8], const SrcVie
             const int64_t base = o.packed ? packed_act_offset(r, c, 0, o.channels, o.kblocks) : off;
             const uint32_t u0 = w0 ^ 0x80808080u, u1 = w1 ^ 0x80808080u;
             const uint32_t l0 = u0 & 0x7f7f7f7fu, l1w = u1 & 0x7f7f7f7fu;
+            if (o.single_fold && o.fast) {
+                // the common case (every modulus in [86, 127]) without per-channel branches
+                int8_t* dst = o.planes + base;
+#pragma unroll 4
+                for (int ch = 0; ch < o.channels; ++ch, dst += plane)
+                    *reinterpret_cast<uint2*>(dst) =
+                        make_uint2(encode_word<true>(u0, l0, o.enc_hi[ch], o.enc_lo[ch], o.enc_mk[ch]),
+                                   encode_word<true>(u1, l1w, o.enc_hi[ch], o.enc_lo[ch], o.enc_mk[ch]));
+            } else
 #pragma unroll 1
             for (int ch = 0; ch < o.channels; ++ch) {
                 uint2 e;
-                if (o.single_fold && o.fast) {
-                    e = make_uint2(encode_word<true>(u0, l0, o.enc_hi[ch], o.enc_lo[ch], o.enc_mk[ch]),
-                                   encode_word<true>(u1, l1w, o.enc_hi[ch], o.enc_lo[ch], o.enc_mk[ch]));
-                } else if (o.single_fold) {
+                if (o.single_fold) {
                     e = make_uint2(encode_word<false>(u0, l0, o.enc_hi[ch], o.enc_lo[ch], o.enc_mk[ch]),
                                    encode_word<false>(u1, l1w, o.enc_hi[ch], o.enc_lo[ch], o.enc_mk[ch]));
                 } else {
