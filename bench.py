@@ -269,6 +269,81 @@ def run_stack(stack, x):
     return h
 
 
+def run_fused_qkv_latency(args) -> None:
+    """Configuration 1 of BASELINE.json: hidden 768, three nn.Linear(768, 768) fused into
+    one RNS QKV projection, M in {1, 16, 128, 256} tokens (the shapes of the reference's
+    benchmarks/benchmark_qkv_fusion.py:60-90).  Prints one JSON line with, per M, the
+    latency of the fused module call, of three separate RNSLinear calls and of the same
+    fused call replayed from a CUDA graph (CUDA events, median of `iters` calls)."""
+    import torch
+    from torch import nn
+    from rns_llm_b200.backends import CudaRNSBackend
+    from rns_llm_b200.layers import RNSLinear, RNSQKVProjection
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; the RNS path has no CPU implementation")
+    backend = CudaRNSBackend()
+    torch.manual_seed(1001)
+    hidden = 768
+    linears = []
+    for _ in range(3):
+        layer = nn.Linear(hidden, hidden, bias=True, device="cuda", dtype=torch.float16).eval()
+        with torch.no_grad():
+            layer.weight.normal_(0, 0.02)
+            layer.bias.normal_(0, 0.02)
+        linears.append(layer)
+    fused = RNSQKVProjection.from_linears(*linears, backend=backend, mode="rns", moduli=MODULI_4).eval()
+    separate = [RNSLinear.from_linear(l, backend=backend, mode="rns", moduli=MODULI_4).eval() for l in linears]
+    iters = max(20, args.steps * 20)
+
+    def median_us(fn) -> float:
+        for _ in range(max(args.warmup, 3) * 5):
+            fn()
+        torch.cuda.synchronize()
+        times = []
+        for _ in range(iters):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(); fn(); b.record()
+            b.synchronize()
+            times.append(a.elapsed_time(b) * 1e3)
+        return statistics.median(times)
+
+    rows = []
+    with torch.no_grad():
+        for tokens in (1, 16, 128, 256):
+            x = torch.randn((1, tokens, hidden), dtype=torch.float16, device="cuda")
+            q, k, v = fused(x)
+            ref = [layer(x) for layer in separate]
+            equal = all(torch.equal(a, b) for a, b in zip((q, k, v), ref))
+            fused_us = median_us(lambda: fused(x))
+            separate_us = median_us(lambda: [layer(x) for layer in separate])
+            graph_us = None
+            try:
+                side = torch.cuda.Stream()
+                with torch.cuda.stream(side):
+                    for _ in range(3):
+                        fused(x)
+                side.synchronize()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=side):
+                    fused(x)
+                graph_us = median_us(graph.replay)
+            except Exception as exc:   # graph capture is an extra, not the measurement
+                graph_us = f"capture failed: {type(exc).__name__}"
+            ops = 2.0 * len(MODULI_4) * tokens * hidden * 3 * hidden
+            weight_bytes = 3 * hidden * hidden
+            rows.append({"tokens": tokens, "fused_us": fused_us, "three_layers_us": separate_us,
+                         "fused_graph_us": graph_us, "bit_equal_to_three_layers": bool(equal),
+                         "channel_tops": ops / (fused_us * 1e-6) / 1e12,
+                         "weight_stream_gbs": weight_bytes / (fused_us * 1e-6) / 1e9})
+    backend.check_status()
+    print(json.dumps({"metric": "fused_qkv_latency_us", "unit": "us", "n_gpus": 1, "higher_is_better": False,
+                      "data": "synthetic", "dtype": "int8",
+                      "config": {"workload": "fused_qkv_hidden768 (BASELINE.json configs[1])", "hidden": hidden,
+                                 "moduli": list(MODULI_4), "activation_scale": "per-tensor", "iters": iters},
+                      "rows": rows}), flush=True)
+
+
 def main() -> None:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -278,9 +353,14 @@ def main() -> None:
     parser.add_argument("--layers", type=int, default=32)
     parser.add_argument("--tokens", type=int, default=4096)
     parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--workload", default="c4", choices=["c4", "c1"],
+                        help="c4: the layer stack (the bench contract); c1: fused-QKV latency of configuration 1")
     args = parser.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
+        return
+    if args.workload == "c1":
+        run_fused_qkv_latency(args)
         return
 
     import torch
