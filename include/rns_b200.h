@@ -321,7 +321,7 @@ RNS_API int rns_linear_fused_supported(const int32_t* moduli, int channels, int 
  * packed_out != 0 (sizes: rns_packed_activation_bytes) -, d_scale float [1] or [M], d_row_l1_max int32 [1] = max_m
  * sum_k |q[m,k]| (NULL to skip; input of rns_select_channels).
  * d_scratch: 16 bytes of device scratch owned by the caller's stream (used
- * only by the two-launch per-tensor path, M*K > 128 Ki elements).
+ * only by the two-launch per-tensor path, M*K > 32 Ki elements).
  * quant_max must be 127 (8-bit sources).
  */
 RNS_API int rns_quantize_activations(const void* d_x, rns_float_type type,

@@ -777,7 +777,7 @@ int rns_quantize_activations(const void* d_x, rns_float_type type, int m, int k,
         return fail(RNS_ERR_INVALID_ARGUMENT, "quantize: bad shape, stride or column block");
     if (quant_max != 127)
         return fail(RNS_ERR_UNSUPPORTED, "the fused quantiser produces 8-bit values (quant_max 127)");
-    const bool small = !per_row && (int64_t)m * k <= 128 * 1024;
+    const bool small = !per_row && (int64_t)m * k <= 32 * 1024;   // one CTA: beyond this the two-launch path is faster
     if (!per_row && !small && !d_scratch)
         return fail(RNS_ERR_INVALID_ARGUMENT, "quantize: per-tensor scale needs d_scratch");
     if (packed_out && k % 8 != 0)
