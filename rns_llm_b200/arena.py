@@ -37,7 +37,7 @@ class ArenaFrame:
         count = 1
         for s in shape:
             count *= int(s)
-        nbytes = count * torch.empty((), dtype=dtype).element_size()
+        nbytes = count * dtype.itemsize
         start = self._offset
         self._offset = (start + nbytes + _ALIGN - 1) // _ALIGN * _ALIGN
         buf = self._arena._buffer(self._key, self._offset)
@@ -56,6 +56,14 @@ class StreamArena:
         index = device.index if device.index is not None else torch.cuda.current_device()
         stream = torch.cuda.current_stream(index)
         return ArenaFrame(self, (index, int(stream.cuda_stream)))
+
+    def block(self, device: torch.device, nbytes: int) -> tuple[int, int]:
+        """(device pointer, stream handle) of at least ``nbytes`` of the current
+        stream's scratch: the allocation-light form of ``frame`` for callers that
+        only need addresses (one dictionary lookup instead of tensor views)."""
+        index = device.index if device.index is not None else torch.cuda.current_device()
+        stream = int(torch.cuda.current_stream(index).cuda_stream)
+        return self._buffer((index, stream), int(nbytes)).data_ptr(), stream
 
     def _buffer(self, key: tuple[int, int], need: int) -> torch.Tensor:
         buf = self._buffers.get(key)

@@ -212,6 +212,11 @@ class CudaRNSBackend:
     # plumbing
     # ------------------------------------------------------------------
     def _mods(self, moduli: Iterable[int]) -> tuple[tuple[int, ...], C.Array]:
+        # a tuple that has been validated once is looked up, not validated again
+        if isinstance(moduli, tuple):
+            arr = self._moduli_arrays.get(moduli)
+            if arr is not None:
+                return moduli, arr
         mods = validate_moduli(moduli)
         arr = self._moduli_arrays.get(mods)
         if arr is None:
@@ -562,10 +567,14 @@ class CudaRNSBackend:
                       bias: torch.Tensor | None = None, tile_n: int = 0, tile_k: int = 0,
                       plain_weight: torch.Tensor | None = None, pair_mode: int = 2,
                       enc_groups: int = 0, exact_residues: bool = False,
-                      enc_stages: int = 0, sub_blocks: int = 0, variant: int = 0) -> None:
+                      enc_stages: int = 0, sub_blocks: int = 0, variant: int = 0,
+                      stream: int | None = None) -> None:
         """Fills ``rns_linear_args`` and launches.  ``a`` / ``a_planes`` are plain
         ([M,K] / [R,M,K]) unless ``a_packed``; the weight is the prepared packed
-        copy unless ``plain_weight`` ([N,K] int8) is given."""
+        copy unless ``plain_weight`` ([N,K] int8) is given.  Device buffers may be
+        given as tensors or as raw addresses (ints)."""
+        def ptr(t):
+            return t if isinstance(t, int) else t.data_ptr()
         mods = prepared.moduli
         args = N.LinearArgs()
         args.m, args.n, args.k = m, prepared.n, prepared.k
@@ -573,11 +582,11 @@ class CudaRNSBackend:
         for i, mod in enumerate(mods):
             args.moduli[i] = mod
         if a_planes is not None:
-            args.d_a_planes = a_planes.data_ptr()
+            args.d_a_planes = ptr(a_planes)
             args.lda = prepared.k
             args.a_plane_stride = m * prepared.k
         else:
-            args.d_a = a.data_ptr()
+            args.d_a = ptr(a)
             args.lda = prepared.k if a_packed else a.stride(0)
         args.a_packed = 1 if a_packed else 0
         if plain_weight is not None:
@@ -589,12 +598,12 @@ class CudaRNSBackend:
             args.ldw = prepared.k
             args.w_packed = 1
             device = prepared.weight_packed.device
-        args.d_active_channels = None if active is None else active.data_ptr()
+        args.d_active_channels = None if active is None else ptr(active)
         args.d_out = out.data_ptr()
         args.ldo = out.stride(0)
         args.out_type = _OUT_TYPES[out.dtype]
         if row_scale is not None:
-            args.d_row_scale = row_scale.data_ptr()
+            args.d_row_scale = ptr(row_scale)
             args.row_scale_stride = row_scale_stride
             args.d_col_scale = col_scale.data_ptr()
             args.d_bias = None if bias is None else bias.data_ptr()
@@ -606,7 +615,7 @@ class CudaRNSBackend:
         args.enc_stages = enc_stages
         args.sub_blocks = sub_blocks
         args.variant = variant
-        N.check(self._lib.rns_linear_fused(C.byref(args), self._stream(device)))
+        N.check(self._lib.rns_linear_fused(C.byref(args), self._stream(device) if stream is None else stream))
 
     def matmul_prepared_fused(self, a: torch.Tensor, prepared_weight: PreparedRNSWeight, *,
                               lut_channels: int = 0, workspace: RNSWorkspace | None = None,
@@ -844,32 +853,29 @@ class CudaRNSBackend:
         use_planes = m >= PLANES_MIN_ROWS and adaptive is None
         meta = None
         with torch.cuda.device(device):
-            frame = self.arena.frame(device)
-            scale = frame.alloc(m if per_row else 1, torch.float32)
-            scratch = frame.alloc(8, torch.int32)   # [0..3] absmax scratch, [4] row-L1 max, [5] active
-            q = None if use_planes else frame.alloc(
-                int(self._lib.rns_packed_activation_bytes(m, k, 1)), torch.int8)
-            planes = frame.alloc(int(self._lib.rns_packed_activation_bytes(m, k, channels)),
-                                 torch.int8) if use_planes else None
-            stream = self._stream(device)
+            # One block of the stream's arena, addressed by offsets (256-byte aligned):
+            # scale [M or 1] f32 | scratch 8 x i32 ([0..3] absmax, [4] row-L1 max,
+            # [5] active channels) | packed activations (int8, or R planes).
+            scale_bytes = ((m if per_row else 1) * 4 + 255) & ~255
+            act_bytes = int(self._lib.rns_packed_activation_bytes(m, k, channels if use_planes else 1))
+            base, stream = self.arena.block(device, scale_bytes + 256 + act_bytes)
+            scale, scratch, act = base, base + scale_bytes, base + scale_bytes + 256
             N.check(self._lib.rns_quantize_activations(
                 x.data_ptr(), _FLOAT_TYPES[x.dtype], m, k, ldx, col_block, col_block_stride,
                 1 if per_row else 0, 127,
-                arr, channels, None if q is None else q.data_ptr(),
-                None if planes is None else planes.data_ptr(), 1, scale.data_ptr(),
-                scratch.data_ptr() + 16 if adaptive is not None else None,
-                scratch.data_ptr(), stream))
+                arr, channels, None if use_planes else act, act if use_planes else None, 1, scale,
+                scratch + 16 if adaptive is not None else None, scratch, stream))
             active = None
             if adaptive is not None:
                 state = self._state(device)
                 if return_metadata:
                     meta = torch.empty(3, dtype=torch.int64, device=device)
                 N.check(self._lib.rns_select_channels(
-                    scratch.data_ptr() + 16, adaptive.max_abs_weight, arr, channels,
-                    adaptive.min_channels, scratch.data_ptr() + 20,
+                    scratch + 16, adaptive.max_abs_weight, arr, channels,
+                    adaptive.min_channels, scratch + 20,
                     None if meta is None else meta.data_ptr(), state.histogram.data_ptr(),
                     state.status.data_ptr(), stream))
-                active = scratch[5:6]
+                active = scratch + 20
                 self._stats["adaptive_selections"] += 1
             self._stats["encode_centered_calls"] += 1
             self._stats["encode_centered_values"] += m * k
@@ -877,9 +883,10 @@ class CudaRNSBackend:
             if adaptive is None:
                 self._stats[f"fused_gemm_channels_{channels}"] += 1
             self._launch_fused(prepared=prepared if adaptive is None else adaptive.variants[channels],
-                               m=m, a=q, a_planes=planes, a_packed=True, out=out, active=active,
+                               m=m, a=None if use_planes else act, a_planes=act if use_planes else None,
+                               a_packed=True, out=out, active=active,
                                row_scale=scale, row_scale_stride=1 if per_row else 0,
-                               col_scale=weight_scale, bias=bias)
+                               col_scale=weight_scale, bias=bias, stream=stream)
         if return_metadata:
             return out, (AdaptiveMetadata(meta) if meta is not None else None)
         return out
