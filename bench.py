@@ -269,6 +269,59 @@ def run_stack(stack, x):
     return h
 
 
+def gpu_library_baselines(tokens: int, layers: int, device) -> dict:
+    """The same four linears per layer through library kernels on this GPU, for scale (not
+    optimisation targets): fp16 F.linear, and native int8 (torch._int_mm on the same int8
+    tensors, int32 -> fp32 dequantisation and bias in eager torch).  One layer's weights,
+    CUDA events over 20 passes; returns ms per layer-pass and the tokens/s of a stack of
+    `layers` such layers."""
+    import torch
+    import torch.nn.functional as F
+
+    gen = torch.Generator(device=device)
+    gen.manual_seed(1004)
+    ws, bs, wq, ws_scale = [], [], [], []
+    for _, k, n, _, _ in LINEARS:
+        w = torch.randn((n, k), generator=gen, device=device, dtype=torch.float16) * (1.0 / k ** 0.5)
+        ws.append(w)
+        bs.append(torch.randn((n,), generator=gen, device=device, dtype=torch.float16) * 0.01)
+        scale = w.float().abs().amax(dim=1).clamp_min(1e-8) / 127.0
+        wq.append(torch.clamp(torch.round(w.float() / scale[:, None]), -127, 127).to(torch.int8).t().contiguous())
+        ws_scale.append(scale)
+    xs = [torch.randn((tokens, k), generator=gen, device=device, dtype=torch.float16) for _, k, _, _, _ in LINEARS]
+
+    def fp16_pass():
+        for x, w, b in zip(xs, ws, bs):
+            F.linear(x, w, b)
+
+    def int8_pass():
+        for x, w, s_w, b in zip(xs, wq, ws_scale, bs):
+            s_a = x.float().abs().amax().clamp_min(1e-8) / 127.0
+            xq = torch.clamp(torch.round(x.float() / s_a), -127, 127).to(torch.int8)
+            acc = torch._int_mm(xq, w)
+            (acc.float() * s_a * s_w + b.float()).half()
+
+    def time_ms(fn) -> float:
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(20):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / 20
+
+    useful = sum(2.0 * tokens * k * n for _, k, n, _, _ in LINEARS)
+    out = {}
+    for name, fn in (("fp16_f_linear", fp16_pass), ("int8_int_mm_eager_dequant", int8_pass)):
+        ms = time_ms(fn)
+        out[name] = {"ms_per_layer": ms, "useful_tops": useful / (ms * 1e-3) / 1e12,
+                     "tokens_per_s": tokens / (ms * layers * 1e-3)}
+    return out
+
+
 def run_fused_qkv_latency(args) -> None:
     """Configuration 1 of BASELINE.json: hidden 768, three nn.Linear(768, 768) fused into
     one RNS QKV projection, M in {1, 16, 128, 256} tokens (the shapes of the reference's
@@ -353,6 +406,8 @@ def main() -> None:
     parser.add_argument("--layers", type=int, default=32)
     parser.add_argument("--tokens", type=int, default=4096)
     parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--gpu-baselines", action="store_true",
+                        help="also time F.linear fp16 and torch._int_mm + eager dequantisation on the stack's shapes")
     parser.add_argument("--workload", default="c4", choices=["c4", "c1"],
                         help="c4: the layer stack (the bench contract); c1: fused-QKV latency of configuration 1")
     args = parser.parse_args()
@@ -495,6 +550,8 @@ def main() -> None:
                     "h2d_bytes_per_step": int(host_x.numel() * 2), "d2h_bytes_per_step": int(host_y.numel() * 2)},
             "gpu_launches": int(len(LINEARS) * args.layers * launches_per_linear * args.steps),
         }
+        if args.gpu_baselines and world == 1:
+            line["gpu_baselines"] = gpu_library_baselines(args.tokens, args.layers, device)
         if not args.no_cpu_baseline and world == 1:
             try:
                 line["cpu_baseline"] = {k: v for k, v in cpu_port_sample().items() if k != "seconds"}
