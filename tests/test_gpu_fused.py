@@ -140,7 +140,8 @@ def test_fixed_configuration_kernels(backend, mods):
     Ragged rows and columns, K from 8 blocks up."""
     rng = np.random.default_rng(len(mods) * 31)
     tile = 128 if len(mods) <= 4 else 96
-    for m, k, n in [(300, 1024, 260), (129, 512, 130), (256, 4096, 200), (640, 576, 96)]:
+    for m, k, n in [(300, 1024, 260), (129, 512, 130), (256, 4096, 200), (640, 576, 96),
+                    (640, 528, 728), (520, 1040, 360), (200, 2064, 256)]:   # K ending in a part block
         a, w = rand_i8(rng, (m, k), -128, 127), rand_i8(rng, (n, k), -128, 127)
         exact = O.exact_matmul(a, w.T)
         for pair in ([0, 1] if len(mods) <= 4 else [0]):
