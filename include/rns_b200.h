@@ -318,7 +318,11 @@ RNS_API int rns_linear_fused_supported(const int32_t* moduli, int channels, int 
  * Outputs: d_q int8 [M,K]
  * (may be NULL when only planes are wanted), d_planes int8 [channels,M,K]
  * (NULL to skip) - both in the packed tile layouts of rns_linear_args when
- * packed_out != 0 (sizes: rns_packed_activation_bytes) -, d_scale float [1] or [M], d_row_l1_max int32 [1] = max_m
+ * packed_out != 0 (sizes: rns_packed_activation_bytes); the plain planes hold
+ * centred residues as the reference's encode does, the packed planes, which only
+ * feed the tensor cores, one-step reduced residues (congruent, |r| <= 64 for the
+ * moduli just below 128; rns_host_encode_reduced_i8 states them) -,
+ * d_scale float [1] or [M], d_row_l1_max int32 [1] = max_m
  * sum_k |q[m,k]| (NULL to skip; input of rns_select_channels).
  * d_scratch: 16 bytes of device scratch owned by the caller's stream (used
  * only by the two-launch per-tensor path, M*K > 32 Ki elements).

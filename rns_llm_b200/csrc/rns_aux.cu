@@ -201,6 +201,7 @@ struct SrcView {
 };
 
 __device__ __forceinline__ int64_t src_offset(const SrcView& s, int r, int c) {
+    if (s.col_block == s.k) return (int64_t)r * s.ldx + c;   // plain matrix: no column blocks
     const int b = c / s.col_block;
     return (int64_t)b * s.col_block_stride + (int64_t)r * s.ldx + (c - b * s.col_block);
 }
@@ -237,14 +238,17 @@ __device__ __forceinline__ int quantize_one(float v, float scale, int qmax) {
 
 // The same value with the division off the common path: t = v * (1/scale) is within
 // 2 ulp of v / scale, so the two round to different integers only when a half-integer
-// lies between them; only then (|t - round(t)| within 1e-4 of 0.5, or |t| >= 256 where
-// an ulp exceeds that margin, or NaN) the IEEE division is redone.
-__device__ __forceinline__ int quantize_one_fast(float v, float scale, float inv_scale, int qmax) {
+// lies between them; only then (|t - round(t)| within 1e-4 of 0.5) the caller redoes
+// the IEEE division (`doubtful`).  The rounding itself is clamp, then add 1.5 * 2^23 (round to nearest
+// even in the adder): the sum's low mantissa bits are the integer, so neither a
+// rounding nor a conversion instruction is issued.  |t| >= 127.5, infinities and NaN
+// fail the same test (the clamped integer is far away, or the difference is NaN).
+__device__ __forceinline__ int quantize_one_fast(float v, float inv_scale, int qmax, bool& doubtful) {
     const float t = __fmul_rn(v, inv_scale);
-    float q = rintf(t);
-    if (!(fabsf(t) < 256.0f) || fabsf(t - q) > 0.4999f) q = rintf(__fdiv_rn(v, scale));
-    q = fminf(fmaxf(q, (float)-qmax), (float)qmax);
-    return (int)q;
+    const float magic = 12582912.0f;
+    const float r = __fadd_rn(fminf(fmaxf(t, (float)-qmax), (float)qmax), magic);
+    doubtful |= !(fabsf(t - __fsub_rn(r, magic)) <= 0.4999f);
+    return __float_as_int(r) - 0x4B400000;
 }
 
 __device__ __forceinline__ int centred_residue(int v, int m) {
@@ -262,7 +266,8 @@ struct QuantOut {
     int* row_l1_max;  // [1] or NULL
     int32_t channels;
     int32_t mod[kMaxCh];
-    uint32_t enc_hi[kMaxCh], enc_lo[kMaxCh], enc_mk[kMaxCh];
+    uint32_t enc_hi[kMaxCh], enc_lo[kMaxCh], enc_mk[kMaxCh], enc_mfold[kMaxCh];
+    int32_t reduced;    // planes hold one-step reduced residues (packed planes of the quantiser)
     int32_t single_fold;
     int32_t fast;
     int32_t packed;     // outputs in the packed tile layouts
@@ -276,8 +281,13 @@ __device__ __forceinline__ int quantize_loaded(const float (&v)[8], const SrcVie
     int q[8];
     int l1 = 0;
     const float inv_scale = __frcp_rn(scale);
+    bool redo = false;   // one branch per group: any doubtful value sends all eight through the division
 #pragma unroll
-    for (int i = 0; i < 8; ++i) q[i] = quantize_one_fast(v[i], scale, inv_scale, qmax);
+    for (int i = 0; i < 8; ++i) q[i] = quantize_one_fast(v[i], inv_scale, qmax, redo);
+    if (redo) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) q[i] = quantize_one(v[i], scale, qmax);
+    }
     if (o.row_l1_max != nullptr) {   // only the adaptive path reads the row sums
 #pragma unroll
         for (int i = 0; i < 8; ++i) l1 += q[i] < 0 ? -q[i] : q[i];
@@ -290,15 +300,26 @@ __device__ __forceinline__ int quantize_loaded(const float (&v)[8], const SrcVie
                                     __byte_perm((uint32_t)q[6], (uint32_t)q[7], 0x0040), 0x5410);
     // Plain: byte offset r*K + c, planes M*K apart.  Packed: tile layouts, where a
     // group of 8 columns (c % 8 == 0) is half of one 16-byte chunk.
-    const int64_t off = o.packed ? packed_act_offset(r, c, 0, 1, o.kblocks) : (int64_t)r * s.k + c;
+    // Packed: tile (r / 128, c / 64) of one channel (values) or of `channels` channels (planes).
+    const int64_t tile = (int64_t)(r >> 7) * o.kblocks + (c >> 6);
+    const int in_tile = packed_row_offset(r & 127, c & 63);
+    const int64_t off = o.packed ? tile * (kPackM * kPackK) + in_tile : (int64_t)r * s.k + c;
     if (full && (off & 7) == 0) {
         if (o.q) *reinterpret_cast<uint2*>(o.q + off) = make_uint2(w0, w1);
         if (o.planes) {
             const int64_t plane = o.packed ? (int64_t)kPackM * kPackK : (int64_t)s.m * s.k;
-            const int64_t base = o.packed ? packed_act_offset(r, c, 0, o.channels, o.kblocks) : off;
+            const int64_t base = o.packed ? tile * o.channels * (kPackM * kPackK) + in_tile : off;
             const uint32_t u0 = w0 ^ 0x80808080u, u1 = w1 ^ 0x80808080u;
             const uint32_t l0 = u0 & 0x7f7f7f7fu, l1w = u1 & 0x7f7f7f7fu;
-            if (o.single_fold && o.fast) {
+            if (o.reduced) {
+                // one fold pattern per word, then one multiply-add and one xor per channel
+                const uint32_t d0 = fold_pattern(w0), d1 = fold_pattern(w1);
+                int8_t* dst = o.planes + base;
+#pragma unroll 4
+                for (int ch = 0; ch < o.channels; ++ch, dst += plane)
+                    *reinterpret_cast<uint2*>(dst) = make_uint2(encode_word_reduced(u0, d0, o.enc_mfold[ch]),
+                                                                encode_word_reduced(u1, d1, o.enc_mfold[ch]));
+            } else if (o.single_fold && o.fast) {
                 // the common case (every modulus in [86, 127]) without per-channel branches
                 int8_t* dst = o.planes + base;
 #pragma unroll 4
@@ -348,18 +369,23 @@ __device__ __forceinline__ int quantize_group(const SrcView& s, const QuantOut& 
     return quantize_loaded<T>(v, s, o, r, c, scale, qmax);
 }
 
-// Two groups of a row per step, both loads issued before either is processed.
+// kQuantUnroll groups of a row per step, every load issued before the first group is processed.
+#ifndef RNS_QUNROLL
+#define RNS_QUNROLL 1
+#endif
+constexpr int kQuantUnroll = RNS_QUNROLL;
 template <typename T>
 __device__ __forceinline__ int quantize_row(const SrcView& s, const QuantOut& o, int row, int lane,
-                                            int groups_per_row, float scale, int qmax) {
+                                            int groups_per_row, float scale, int qmax, int first_group = 0) {
     int l1 = 0;
-    for (int g = lane; g < groups_per_row; g += 64) {
-        float v0[8], v1[8];
-        const bool second = g + 32 < groups_per_row;
-        load8<T>(s, row, g * 8, v0);
-        if (second) load8<T>(s, row, (g + 32) * 8, v1);
-        l1 += quantize_loaded<T>(v0, s, o, row, g * 8, scale, qmax);
-        if (second) l1 += quantize_loaded<T>(v1, s, o, row, (g + 32) * 8, scale, qmax);
+    for (int g = first_group + lane; g < groups_per_row; g += 32 * kQuantUnroll) {
+        float v[kQuantUnroll][8];
+#pragma unroll
+        for (int u = 0; u < kQuantUnroll; ++u)
+            if (g + 32 * u < groups_per_row) load8<T>(s, row, (g + 32 * u) * 8, v[u]);
+#pragma unroll
+        for (int u = 0; u < kQuantUnroll; ++u)
+            if (g + 32 * u < groups_per_row) l1 += quantize_loaded<T>(v[u], s, o, row, (g + 32 * u) * 8, scale, qmax);
     }
     return l1;
 }
@@ -400,16 +426,33 @@ absmax_kernel(const __grid_constant__ SrcView s, unsigned* __restrict__ scratch)
     }
 }
 
-// Pass 2 (one warp per row, eight rows per block): scale, int8 values, optional
-// planes, row L1.  PER_ROW: the warp first reduces its own row's absmax.
+// Pass 2 (one warp per row segment): scale, int8 values, optional planes, row L1.
+// PER_ROW: the warp first reduces its own row's absmax.  A row is one segment when
+// its absmax or its L1 sum is wanted (segments = 1); otherwise rows are cut into
+// `segments` pieces of `seg_groups` groups so that short and wide matrices both
+// spread evenly over the SMs.
+#ifndef RNS_QMINBLOCKS
+#define RNS_QMINBLOCKS 4
+#endif
 template <typename T, bool PER_ROW>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, RNS_QMINBLOCKS)
 quantize_rows_kernel(const __grid_constant__ SrcView s, const __grid_constant__ QuantOut o,
-                     int qmax, const unsigned* __restrict__ scratch) {
+                     int qmax, const unsigned* __restrict__ scratch, int segments, int seg_groups) {
     const int lane = threadIdx.x & 31;
     const int warps = (gridDim.x * blockDim.x) >> 5;
     const int groups_per_row = (s.k + 7) / 8;
     int worst_l1 = 0;
+    if (!PER_ROW && segments > 1) {
+        const float scale = fmaxf(__fdiv_rn(__uint_as_float(*scratch), (float)qmax), FLT_EPSILON);
+        if (blockIdx.x == 0 && threadIdx.x == 0) o.scale[0] = scale;
+        const int64_t units = (int64_t)s.m * segments;
+        for (int64_t u = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; u < units; u += warps) {
+            const int row = (int)(u / segments);
+            const int first = (int)(u - (int64_t)row * segments) * seg_groups;
+            quantize_row<T>(s, o, row, lane, min(groups_per_row, first + seg_groups), scale, qmax, first);
+        }
+        return;
+    }
     for (int row = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; row < s.m; row += warps) {
         float absmax;
         if (PER_ROW) {
@@ -636,7 +679,7 @@ static int fill_encoder(QuantOut& qo, const int32_t* moduli, int channels) {
     qo.fast = pl.encode_fast;
     for (int i = 0; i < kMaxCh; ++i) {
         qo.mod[i] = pl.mod[i]; qo.enc_hi[i] = pl.enc_hi[i]; qo.enc_lo[i] = pl.enc_lo[i];
-        qo.enc_mk[i] = pl.enc_mk[i];
+        qo.enc_mk[i] = pl.enc_mk[i]; qo.enc_mfold[i] = pl.enc_mfold[i];
     }
     return RNS_OK;
 }
@@ -788,6 +831,9 @@ int rns_quantize_activations(const void* d_x, rns_float_type type, int m, int k,
     qo.kblocks = (k + kPackK - 1) / kPackK;
     if (d_planes)
         if (int rc = fill_encoder(qo, moduli, channels)) return rc;
+#ifndef RNS_QUANT_CENTRED
+    qo.reduced = (d_planes && packed_out) ? 1 : 0;   // the packed planes only feed the tensor cores
+#endif
     size_t esize = 2;
     if (type == RNS_F32) esize = 4;
     else if (type != RNS_F16 && type != RNS_BF16)
@@ -804,17 +850,24 @@ int rns_quantize_activations(const void* d_x, rns_float_type type, int m, int k,
     unsigned* scratch = static_cast<unsigned*>(d_scratch);
     if (!per_row && !small) RNS_CUDA_OK(cudaMemsetAsync(scratch, 0, 16, st));
     if (d_row_l1_max && !small) RNS_CUDA_OK(cudaMemsetAsync(d_row_l1_max, 0, sizeof(int32_t), st));
-    const int row_blocks = grid_for(m, 8, 148 * 8);  // eight rows (warps) per block
+    int row_threads = 128, seg_groups = 128, segments = 1, row_cap = 148 * 16;   // 1024-column segments
+#ifdef RNS_QUANT_TUNE
+    if (const char* e = getenv("RNS_QTHREADS")) row_threads = atoi(e);
+    if (const char* e = getenv("RNS_QSEG")) seg_groups = atoi(e);
+    if (const char* e = getenv("RNS_QCAP")) row_cap = atoi(e);
+#endif
+    if (seg_groups > 0 && !per_row && !d_row_l1_max) segments = ((k + 7) / 8 + seg_groups - 1) / seg_groups;
+    const int row_blocks = grid_for((int64_t)m * segments, row_threads / 32, row_cap);  // one warp per row segment
     const int64_t groups = (int64_t)m * ((k + 7) / 8);
 #define RNS_QUANT(T)                                                                           \
     do {                                                                                       \
         if (per_row) {                                                                         \
-            quantize_rows_kernel<T, true><<<row_blocks, 256, 0, st>>>(sv, qo, quant_max, scratch); \
+            quantize_rows_kernel<T, true><<<row_blocks, row_threads, 0, st>>>(sv, qo, quant_max, scratch, 1, 0); \
         } else if (small) {                                                                    \
             quantize_small_kernel<T><<<1, 1024, 0, st>>>(sv, qo, quant_max);                   \
         } else {                                                                               \
             absmax_kernel<T><<<grid_for(groups, 256 * 4, 148 * 8), 256, 0, st>>>(sv, scratch); \
-            quantize_rows_kernel<T, false><<<row_blocks, 256, 0, st>>>(sv, qo, quant_max, scratch); \
+            quantize_rows_kernel<T, false><<<row_blocks, row_threads, 0, st>>>(sv, qo, quant_max, scratch, segments, seg_groups); \
         }                                                                                      \
     } while (0)
     switch (type) {

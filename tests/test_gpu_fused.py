@@ -309,10 +309,50 @@ def test_quantizer_outputs(backend):
         assert np.array_equal(scale.cpu().numpy(), exp_scale.reshape(-1))
         assert np.array_equal(qp.cpu().numpy()[packed_act_offsets(m, k, 1)[:, :, 0]], exp_q)
         got_planes = pp.cpu().numpy()[packed_act_offsets(m, k, 4)]            # [M,K,4]
-        assert np.array_equal(got_planes.transpose(2, 0, 1), O.encode_centered(exp_q, C0, "device"))
+        # packed planes only feed the tensor cores: one-step reduced residues (x - m for
+        # x >= 64, x + m for x < -64), the same encoder as the in-kernel one
+        reduced = np.empty((4, m * k), dtype=np.int8)
+        flat = np.ascontiguousarray(exp_q.reshape(-1))
+        N.check(lib.rns_host_encode_reduced_i8(flat.ctypes.data, flat.size, N.moduli_array(C0), 4, reduced.ctypes.data))
+        assert np.array_equal(got_planes.transpose(2, 0, 1), reduced.reshape(4, m, k))
+        for c, mod in enumerate(C0):
+            assert np.all((reduced[c].astype(int) - flat.astype(int)) % mod == 0)
     zeros = torch.zeros((4, 64), dtype=torch.float16, device="cuda")
     wq, ws, _ = backend.quantize_weight(zeros)
     assert float(ws[0]) == float(np.finfo(np.float32).eps) and int(wq.abs().max()) == 0
+
+
+def test_quantizer_ties_and_near_ties(backend):
+    """Values whose quotient by the scale sits on or within a few ulp of a half-integer:
+    the reciprocal-product shortcut may not be trusted there and the division is redone.
+    float32 input, so that the near-ties are as near as float32 allows."""
+    from rns_llm_b200 import _native as N
+    lib = N.load()
+    rng = np.random.default_rng(77)
+    m, k = 320, 512
+    for absmax in (127.0, 100.0, 3.3, 1e-3):
+        scale = np.float32(absmax) / np.float32(127)
+        halves = rng.integers(-127, 127, size=(m, k)).astype(np.float32) + np.float32(0.5)
+        x = (halves * scale).astype(np.float32)
+        nudge = rng.integers(-3, 4, size=(m, k))
+        for _ in range(3):   # up to three ulp either side, a third of the values untouched
+            step = np.sign(nudge).astype(np.float32)
+            x = np.where(nudge != 0, np.nextafter(x, x + step).astype(np.float32), x)
+            nudge = nudge - np.sign(nudge)
+        x[0, 0] = absmax; x[1, 1] = -absmax
+        xd = torch.from_numpy(x).cuda()
+        for per_row in (0, 1):
+            q = torch.empty((m, k), dtype=torch.int8, device="cuda")
+            scale_out = torch.empty(m if per_row else 1, dtype=torch.float32, device="cuda")
+            scratch = torch.empty(4, dtype=torch.int32, device="cuda")
+            N.check(lib.rns_quantize_activations(xd.data_ptr(), N.F32, m, k, k, 0, 0, per_row, 127,
+                                                 N.moduli_array(C0), 4, q.data_ptr(), None, 0,
+                                                 scale_out.data_ptr(), None, scratch.data_ptr(),
+                                                 torch.cuda.current_stream().cuda_stream))
+            torch.cuda.synchronize()
+            exp_scale = O.symmetric_scale(x, 127, axis=1 if per_row else None)
+            assert np.array_equal(scale_out.cpu().numpy(), exp_scale.reshape(-1))
+            assert np.array_equal(q.cpu().numpy(), O.quantize(x, exp_scale, 127)), (absmax, per_row)
 
 
 def test_adaptive_prefix_selected_on_device(backend):
