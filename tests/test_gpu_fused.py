@@ -322,6 +322,28 @@ def test_quantizer_outputs(backend):
     assert float(ws[0]) == float(np.finfo(np.float32).eps) and int(wq.abs().max()) == 0
 
 
+@pytest.mark.parametrize("m", [5, 200, 1100])
+@pytest.mark.parametrize("per_row", [False, True])
+def test_linear_forward_reads_gathered_column_blocks(backend, m, per_row):
+    """A [G, M, K/G] activation (what an all-gather of G column shards leaves) gives the
+    same bits as the plain [M, K] matrix it stands for: single-CTA quantiser, the
+    two-launch one, and the residue-plane path of many-token calls."""
+    torch.manual_seed(m)
+    g, k, n = 4, 1024, 264
+    blocks = torch.randn(g, m, k // g, dtype=torch.float16, device="cuda")
+    plain = blocks.permute(1, 0, 2).reshape(m, k).contiguous()
+    weight = (torch.randn(n, k, device="cuda") * 0.05).half()
+    w_q, w_scale, _ = backend.quantize_weight(weight)
+    prepared = backend.prepare_weight_nk(w_q, C0)
+    y_plain = backend.linear_forward(plain, prepared, w_scale, None, per_row=per_row).clone()
+    y_blocks = backend.linear_forward(blocks, prepared, w_scale, None, per_row=per_row)
+    torch.cuda.synchronize()
+    backend.check_status()
+    assert torch.equal(y_plain, y_blocks)
+    expect = O.rns_linear_forward(plain.cpu().numpy(), weight.cpu().numpy(), None, C0, per_row=per_row)["y"]
+    assert np.array_equal(y_blocks.cpu().numpy().view(np.uint16), expect.view(np.uint16))
+
+
 def test_quantizer_ties_and_near_ties(backend):
     """Values whose quotient by the scale sits on or within a few ulp of a half-integer:
     the reciprocal-product shortcut may not be trusted there and the division is redone.
