@@ -409,11 +409,29 @@ absmax_kernel(const __grid_constant__ SrcView s, unsigned* __restrict__ scratch)
     float best = 0.0f;
     const int groups_per_row = (s.k + 7) / 8;
     const int64_t total = (int64_t)s.m * groups_per_row;
-    for (int64_t g = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; g < total;
-         g += (int64_t)gridDim.x * blockDim.x) {
-        const int r = (int)(g / groups_per_row);
-        const int c = (int)(g - (int64_t)r * groups_per_row) * 8;
-        best = fmaxf(best, group_absmax<T>(s, r, c));
+    const unsigned stride = gridDim.x * blockDim.x;
+    if (s.vec8 && total < (1ll << 31)) {
+        // 32-bit index arithmetic and four independent 16-byte loads per thread and step
+        const unsigned count = (unsigned)total, gpr = (unsigned)groups_per_row;
+        for (unsigned g = blockIdx.x * blockDim.x + threadIdx.x; g < count; g += 4 * stride) {
+            float part4[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const unsigned gi = g + u * stride;
+                part4[u] = 0.0f;
+                if (gi < count) {
+                    const unsigned r = gi / gpr;
+                    part4[u] = group_absmax<T>(s, (int)r, (int)(gi - r * gpr) * 8);
+                }
+            }
+            best = fmaxf(fmaxf(best, fmaxf(part4[0], part4[1])), fmaxf(part4[2], part4[3]));
+        }
+    } else {
+        for (int64_t g = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; g < total; g += stride) {
+            const int r = (int)(g / groups_per_row);
+            const int c = (int)(g - (int64_t)r * groups_per_row) * 8;
+            best = fmaxf(best, group_absmax<T>(s, r, c));
+        }
     }
     best = warp_max(best);
     __shared__ float part[8];
