@@ -397,6 +397,56 @@ def run_fused_qkv_latency(args) -> None:
                       "rows": rows}), flush=True)
 
 
+def run_quantiser(args) -> None:
+    """The activation quantiser alone on the layer stack's two activation shapes: fp16
+    [tokens, K] in, packed residue planes out (both launches: absmax, then quantise +
+    planes), CUDA events over `iters` calls.  Bytes: the fp16 matrix read twice plus R
+    plane bytes per value written; the fraction is against the measured copy bandwidth."""
+    import torch
+    from rns_llm_b200 import _native as N
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; the RNS path has no CPU implementation")
+    lib = N.load()
+    peaks = load_peaks()
+    stream = torch.cuda.current_stream().cuda_stream
+    iters, rows = 50, []
+    for k, mods in ((HIDDEN, MODULI_4), (FFN, MODULI_5)):
+        m, r = args.tokens, len(mods)
+        torch.manual_seed(k)
+        x = torch.randn((m, k), dtype=torch.float16, device="cuda")
+        planes = torch.empty(int(lib.rns_packed_activation_bytes(m, k, r)), dtype=torch.int8, device="cuda")
+        scale = torch.empty(1, dtype=torch.float32, device="cuda")
+        scratch = torch.zeros(16, dtype=torch.int8, device="cuda")
+        moduli = N.moduli_array(mods)
+
+        def call():
+            N.check(lib.rns_quantize_activations(x.data_ptr(), N.F16, m, k, k, 0, 0, 0, 127, moduli, r, None,
+                                                 planes.data_ptr(), 1, scale.data_ptr(), None,
+                                                 scratch.data_ptr(), stream))
+        for _ in range(max(3, args.warmup)):
+            call()
+        torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(iters):
+            call()
+        stop.record()
+        torch.cuda.synchronize()
+        us = start.elapsed_time(stop) / iters * 1e3
+        nbytes = m * k * (2 * 2 + r)
+        gbs = nbytes / us / 1e3
+        rows.append({"rows": m, "k": k, "planes": r, "us": us, "bytes": nbytes, "gbs": gbs,
+                     "frac_of_hbm": gbs / float(peaks["hbm_gbs"])})
+    print(json.dumps({"metric": "activation_quantiser_us", "unit": "us", "n_gpus": 1, "higher_is_better": False,
+                      "data": "synthetic", "dtype": "f32 -> int8", "peak_gbs": float(peaks["hbm_gbs"]),
+                      "peak_source": peaks["source"],
+                      "config": {"workload": "activation quantiser on the layer stack's shapes", "iters": iters,
+                                 "l2_policy": "back-to-back calls: the K = 4096 case (32 MiB in, 64 MiB out) "
+                                              "fits L2, the K = 16384 case (576 MB) does not"},
+                      "rows": rows}))
+
+
 def main() -> None:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -408,14 +458,18 @@ def main() -> None:
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--gpu-baselines", action="store_true",
                         help="also time F.linear fp16 and torch._int_mm + eager dequantisation on the stack's shapes")
-    parser.add_argument("--workload", default="c4", choices=["c4", "c1"],
-                        help="c4: the layer stack (the bench contract); c1: fused-QKV latency of configuration 1")
+    parser.add_argument("--workload", default="c4", choices=["c4", "c1", "quant"],
+                        help="c4: the layer stack (the bench contract); c1: fused-QKV latency of configuration 1; "
+                             "quant: the activation quantiser alone on the stack's shapes")
     args = parser.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
         return
     if args.workload == "c1":
         run_fused_qkv_latency(args)
+        return
+    if args.workload == "quant":
+        run_quantiser(args)
         return
 
     import torch
