@@ -82,6 +82,40 @@ def load_peaks() -> dict:
     return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
 
 
+def measure_int8_peak(device, sustained_seconds: float = 3.0) -> dict:
+    """Dense int8 tensor throughput of this GPU through the library GEMM (torch._int_mm,
+    cuBLASLt int8 -> int32) at 8192^3: best of 10 single launches (burst) and the mean over
+    back-to-back launches for `sustained_seconds` (sustained, under the power cap).  It is
+    the denominator of roofline.frac: MEASURED_PEAKS.json records no int8 figure."""
+    import torch
+
+    n = 8192
+    a = torch.randint(-127, 128, (n, n), dtype=torch.int8, device=device)
+    b = torch.randint(-127, 128, (n, n), dtype=torch.int8, device=device).t()
+    ops = 2.0 * n * n * n
+    for _ in range(3):
+        torch._int_mm(a, b)
+    torch.cuda.synchronize(device)
+    best = float("inf")
+    for _ in range(10):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(); torch._int_mm(a, b); e1.record()
+        e1.synchronize()
+        best = min(best, e0.elapsed_time(e1))
+    per_launch_s = best * 1e-3
+    launches = max(20, int(sustained_seconds / per_launch_s))
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(launches):
+        torch._int_mm(a, b)
+    e1.record()
+    e1.synchronize()
+    sustained = ops * launches / (e0.elapsed_time(e1) * 1e-3) / 1e12
+    del a, b
+    return {"burst": ops / per_launch_s / 1e12, "sustained": sustained, "unit": "TOPS",
+            "how": f"torch._int_mm {n}^3: best of 10 launches; mean of {launches} back-to-back launches"}
+
+
 # --------------------------------------------------------------------------
 # clocks
 # --------------------------------------------------------------------------
@@ -205,6 +239,9 @@ def run_reference_arm(args) -> None:
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": seconds * 1e3,
+        "ms_per_step_is": "one bounded sample of the workload (rows of the QKV linear), not a full pass over "
+                          "the 128 linears; a full pass at this rate would take "
+                          f"{channel_ops_per_step(args.tokens, args.layers) / (value * 1e12):.0f} s",
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int8",
         "data": "synthetic",
         "config": workload_config(args, sharded=False),
@@ -249,7 +286,7 @@ def build_stack(backend, args, rank: int, world: int, device):
             shard_w = shard_tensor(weight, world, rank, groups)
             shard_b = shard_tensor(bias, world, rank, groups)
             layer.append(ColumnShardedRNSLinear(shard_w, shard_b, backend=backend, moduli=mods, rank=rank,
-                                                world=world, groups=groups))
+                                                world=world, groups=groups, reuse_buffer=True))
             del weight, bias, shard_w, shard_b
         stack.append(layer)
     return stack
@@ -447,31 +484,53 @@ def run_quantiser(args) -> None:
                       "rows": rows}))
 
 
-def main() -> None:
-    parser = argparse.ArgumentParser()
-    parser.add_argument("--gpus", type=int, default=1)
-    parser.add_argument("--steps", type=int, default=5)
-    parser.add_argument("--warmup", type=int, default=3)
-    parser.add_argument("--impl", default="rns_b200", choices=["rns_b200", "reference"])
-    parser.add_argument("--layers", type=int, default=32)
-    parser.add_argument("--tokens", type=int, default=4096)
-    parser.add_argument("--no-cpu-baseline", action="store_true")
-    parser.add_argument("--gpu-baselines", action="store_true",
-                        help="also time F.linear fp16 and torch._int_mm + eager dequantisation on the stack's shapes")
-    parser.add_argument("--workload", default="c4", choices=["c4", "c1", "quant"],
-                        help="c4: the layer stack (the bench contract); c1: fused-QKV latency of configuration 1; "
-                             "quant: the activation quantiser alone on the stack's shapes")
-    args = parser.parse_args()
-    if args.impl == "reference":
-        run_reference_arm(args)
-        return
-    if args.workload == "c1":
-        run_fused_qkv_latency(args)
-        return
-    if args.workload == "quant":
-        run_quantiser(args)
-        return
+# Where the run is, for the failure report: {"phase": ..., "step": ..., "layer": ..., "linear": ...}
+PROGRESS: dict = {"phase": "start"}
 
+
+def report_failure(exc: BaseException, backend=None) -> None:
+    """The last thing a failing rank writes: ONE JSON line on stderr with its rank, the
+    exception, where the run was, and the device status word with the place of an
+    expired wait (under torchrun only the launcher's table survives otherwise)."""
+    import traceback
+
+    line = {"rank": int(os.environ.get("RANK", "0")), "error": f"{type(exc).__name__}: {exc}",
+            "progress": dict(PROGRESS), "status_word": None,
+            "traceback_tail": traceback.format_exception(type(exc), exc, exc.__traceback__)[-3:]}
+    if backend is not None:
+        try:
+            for index, state in backend._device_state.items():
+                line["status_word"] = int(state.status.item())
+                line["wait_info"] = [int(v) for v in state.wait_info.cpu().tolist()]
+        except Exception as inner:      # the context may be gone; say so instead of hiding the first error
+            line["status_word"] = f"unreadable: {type(inner).__name__}: {inner}"
+    sys.stderr.write("\n" + json.dumps(line) + "\n")
+    sys.stderr.flush()
+
+
+def locate_failing_linear(backend, stack, x):
+    """After a non-zero device status: one more pass with a status check behind every
+    linear.  Returns {"layer": i, "linear": name, "error": ...} or None when the pass is clean."""
+    import torch
+    from rns_llm_b200.parallel import group_view
+
+    names = [name for name, *_ in LINEARS]
+    h = x
+    for index, layer in enumerate(stack):
+        for name, linear in zip(names, layer):
+            src = h
+            if name == "out_proj":
+                src = group_view(h, 3, 0)
+            h = linear(src)
+            torch.cuda.synchronize()
+            try:
+                backend.check_status()
+            except Exception as exc:
+                return {"layer": index, "linear": name, "error": str(exc)}
+    return None
+
+
+def run_layer_stack(args) -> None:
     import torch
     import torch.distributed as dist
 
@@ -485,12 +544,30 @@ def main() -> None:
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
     if world > 1:
+        PROGRESS["phase"] = "init_process_group"
         dist.init_process_group("nccl", device_id=device)
 
     from rns_llm_b200.backends import CudaRNSBackend
 
     backend = CudaRNSBackend()
+    try:
+        _run_layer_stack(args, backend, rank, world, local_rank, device)
+    except BaseException as exc:
+        if not isinstance(exc, SystemExit) or exc.code not in (0, None):
+            report_failure(exc, backend)
+            # Leave without running destructors: a failed rank must not wait for its peers.
+            os._exit(1)
+        raise
+
+
+def _run_layer_stack(args, backend, rank, world, local_rank, device) -> None:
+    import torch
+    import torch.distributed as dist
+
     warmup = max(args.warmup, 3)
+    PROGRESS["phase"] = "build_stack"
+    free_bytes, total_bytes = torch.cuda.mem_get_info(device)
+    PROGRESS["free_gib_at_start"] = round(free_bytes / 2**30, 1)
     stack = build_stack(backend, args, rank, world, device)
     torch.manual_seed(4321)
     host_x = torch.randn((args.tokens, HIDDEN), dtype=torch.float16).pin_memory()
@@ -524,15 +601,35 @@ def main() -> None:
         host_y.copy_(unshard(y, 1), non_blocking=True)
         return y
 
-    for _ in range(warmup):
+    def checked(phase: str):
+        """Device status after a phase, on every rank; a failure names the linear."""
+        torch.cuda.synchronize()
+        try:
+            backend.check_status()
+        except Exception as exc:
+            PROGRESS["first_failing_linear"] = locate_failing_linear(backend, stack, dev_x) or "not reproduced"
+            raise RuntimeError(f"{phase}: {exc}") from exc
+
+    PROGRESS["phase"] = "warmup"
+    for i in range(warmup):
+        PROGRESS["step"] = i
         step_device()
     barrier()
     y_check = step_device()
     if not bool(torch.isfinite(y_check).all()):
-        raise SystemExit("non-finite activations in the layer stack")
-    backend.check_status()
+        raise RuntimeError("non-finite activations in the layer stack")
+    checked("warm-up")
+    # Every rank computed the same replicated activations: compare a checksum across ranks.
+    if world > 1:
+        digest = y_check.float().sum(dtype=torch.float64).reshape(1)
+        lo, hi = digest.clone(), digest.clone()
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+        if float(lo) != float(hi):
+            raise RuntimeError(f"ranks disagree on the stack's output checksum: {float(lo)} vs {float(hi)}")
 
     # ---- timed region: device-resident inputs -------------------------------
+    PROGRESS["phase"] = "timed_device"
     backend._launch_fused = timed_launch
     sampler = ClockSampler(local_rank)
     sampler.start()
@@ -540,7 +637,8 @@ def main() -> None:
     start = torch.cuda.Event(enable_timing=True)
     stop = torch.cuda.Event(enable_timing=True)
     start.record()
-    for _ in range(args.steps):
+    for i in range(args.steps):
+        PROGRESS["step"] = i
         step_device()
     stop.record()
     barrier()
@@ -549,37 +647,46 @@ def main() -> None:
     elapsed_ms = start.elapsed_time(stop)
     gemm_ms = sum(a.elapsed_time(b) for a, b in gemm_events)
     gemm_launches = len(gemm_events)
+    checked("timed region")
 
     # ---- timed region: end to end from host buffers -------------------------
+    PROGRESS["phase"] = "timed_e2e"
     for _ in range(2):
         step_e2e()
     barrier()
     e_start = torch.cuda.Event(enable_timing=True)
     e_stop = torch.cuda.Event(enable_timing=True)
     e_start.record()
-    for _ in range(args.steps):
+    for i in range(args.steps):
+        PROGRESS["step"] = i
         step_e2e()
     e_stop.record()
     barrier()
     e2e_ms = e_start.elapsed_time(e_stop)
-    backend.check_status()
+    checked("end-to-end region")
 
+    PROGRESS["phase"] = "reduce_times"
     times = torch.tensor([elapsed_ms, e2e_ms, gemm_ms], dtype=torch.float64, device=device)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
     elapsed_ms, e2e_ms, gemm_ms = (float(v) for v in times.tolist())
 
+    PROGRESS["phase"] = "report"
     if rank == 0:
         ops = channel_ops_per_step(args.tokens, args.layers)
         ms_per_step = elapsed_ms / args.steps
         value = ops / (ms_per_step * 1e-3) / 1e12
         e2e_value = ops / (e2e_ms / args.steps * 1e-3) / 1e12
         peaks = load_peaks()
-        # Dominant kernel: rns_gemm_kernel.  Per launch it performs 2*R*M*K*(N/world)
+        # Dominant kernel: the fused RNS GEMM.  Per launch it performs 2*R*M*K*(N/world)
         # int8 tensor-core operations (the algorithmic work of one RNS linear).
         gemm_ops_per_rank = ops / world * args.steps
         achieved = gemm_ops_per_rank / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else None
-        int8_peak = 2.0 * float(peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"]))
+        two_bf16 = 2.0 * float(peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"]))
+        int8_measured = None
+        if not args.no_peak:
+            int8_measured = measure_int8_peak(device)
+        int8_peak = int8_measured["sustained"] if int8_measured else two_bf16
         launches_per_linear = 3          # absmax + quantise/encode + fused GEMM
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
@@ -591,12 +698,18 @@ def main() -> None:
             "roofline": {
                 "bound": "tensor", "kernel": "rns_gemm_kernel", "achieved": achieved, "peak": int8_peak,
                 "unit": "TOPS", "frac": None if achieved is None else achieved / int8_peak,
-                "peak_source": f"2 x bf16_tflops_sustained of MEASURED_PEAKS.json ({peaks['source']}); "
-                               "the file records no int8 figure",
+                "peak_source": ("torch._int_mm 8192^3 back to back on this GPU in this run (sustained, under the "
+                                "power cap)" if int8_measured else
+                                f"2 x bf16_tflops_sustained of MEASURED_PEAKS.json ({peaks['source']})"),
+                "peak_int8_measured": int8_measured,
+                "frac_vs_2x_bf16": None if achieved is None else achieved / two_bf16,
+                "peak_2x_bf16_sustained": two_bf16,
                 "launches": gemm_launches, "avg_launch_ms": gemm_ms / max(gemm_launches, 1),
                 "traffic": NCU_DRAM_BYTES_PER_LAUNCH if (world == 1 and args.tokens == 4096) else None,
+                "traffic_measured_in_this_run": False,
                 "traffic_unit": "bytes per launch (dram read + write, mean over the four linears)",
-                "traffic_source": "ncu capture of this command with --layers 2, profiles/rns_gemm_kernel_opt6.7b_stack.md",
+                "traffic_source": "recorded constant: ncu capture (dram__bytes_read.sum + dram__bytes_write.sum) of "
+                                  "this command with --layers 2; see the stack summary under profiles/",
                 "algorithmic_bytes": algorithmic_bytes_per_launch(args.tokens),
             },
             "clocks": clocks,
@@ -614,8 +727,47 @@ def main() -> None:
                 line["cpu_baseline"] = {"value": None, "unit": UNIT, "cores": os.cpu_count(), "kind": "port",
                                         "sample": f"failed: {exc}"}
         print(json.dumps(line), flush=True)
+    PROGRESS["phase"] = "teardown"
     if world > 1:
+        dist.barrier()
         dist.destroy_process_group()
+
+
+def main() -> None:
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=5)
+    parser.add_argument("--warmup", type=int, default=3)
+    parser.add_argument("--impl", default="rns_b200", choices=["rns_b200", "reference"])
+    parser.add_argument("--layers", type=int, default=32)
+    parser.add_argument("--tokens", type=int, default=4096)
+    parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--no-peak", action="store_true",
+                        help="skip the torch._int_mm peak measurement (roofline.frac then uses 2 x bf16 sustained)")
+    parser.add_argument("--gpu-baselines", action="store_true",
+                        help="also time F.linear fp16 and torch._int_mm + eager dequantisation on the stack's shapes")
+    parser.add_argument("--workload", default="c4", choices=["c4", "c1", "quant", "peak"],
+                        help="c4: the layer stack (the bench contract); c1: fused-QKV latency of configuration 1; "
+                             "quant: the activation quantiser alone on the stack's shapes; peak: the int8 "
+                             "library-GEMM peak of this GPU")
+    args = parser.parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+        return
+    if args.workload == "c1":
+        run_fused_qkv_latency(args)
+        return
+    if args.workload == "quant":
+        run_quantiser(args)
+        return
+    if args.workload == "peak":
+        import torch
+        if not torch.cuda.is_available():
+            raise SystemExit("bench.py needs a CUDA device")
+        print(json.dumps({"metric": "int8_library_gemm_peak", "unit": "TOPS", "n_gpus": 1,
+                          "higher_is_better": True, **measure_int8_peak(torch.device("cuda", 0), 4.0)}), flush=True)
+        return
+    run_layer_stack(args)
 
 
 if __name__ == "__main__":

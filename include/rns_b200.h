@@ -230,6 +230,9 @@ RNS_API int rns_matmul_centered_fused_out(const int8_t* d_a, const int8_t* d_b,
  * multiples of 16, 16-byte aligned bases, 2 <= channels <= 8 (and every modulus
  * >= 86 when exact_residues is set).  Anything else
  * returns RNS_ERR_UNSUPPORTED; callers then use the plane-level functions.
+ * K * 128 * 128 must not exceed INT32_MAX (K <= 131071): the per-channel sums
+ * are int32, as the reference's cuBLAS accumulators are (backends/
+ * cuda_backend.py:240); a larger K returns RNS_ERR_OVERFLOW.
  */
 typedef struct rns_linear_args {
     int32_t m, n, k;
@@ -263,6 +266,10 @@ typedef struct rns_linear_args {
                                  channels; tile_n then means tokens per tile: 32, 64 or 128) */
     int32_t exact_residues;   /* 1: in-kernel residues exactly centred (|r| <= m/2; needs every
                                  modulus >= 86); 0: one-step reduced residues (any moduli) */
+    int32_t* d_wait_info;     /* NULL, or device int32[4], zero before the launch: when a bounded
+                                 wait expires the first CTA to give up writes {wait code =
+                                 role << 20 | pipeline stage, blockIdx.x, blockIdx.y, kernel form}
+                                 here, so that the host can say where the kernel stopped */
 } rns_linear_args;
 
 RNS_API int rns_linear_fused(const rns_linear_args* args, rns_stream_t stream);

@@ -61,6 +61,7 @@ class LinearArgs(C.Structure):
         ("sub_blocks", C.c_int32),
         ("variant", C.c_int32),
         ("exact_residues", C.c_int32),
+        ("d_wait_info", C.c_void_p),
     ]
 
 

@@ -191,6 +191,7 @@ class AdaptiveMetadata(Mapping):
 @dataclass
 class _DeviceState:
     status: torch.Tensor          # int32 [1]: device-side error word
+    wait_info: torch.Tensor       # int32 [4]: which bounded wait expired (see rns_linear_args.d_wait_info)
     histogram: torch.Tensor       # int64 [MAX_CHANNELS+1]: adaptive selections per channel count
 
 
@@ -235,6 +236,7 @@ class CudaRNSBackend:
             dev = torch.device("cuda", index)
             state = _DeviceState(
                 status=torch.zeros(1, dtype=torch.int32, device=dev),
+                wait_info=torch.zeros(4, dtype=torch.int32, device=dev),
                 histogram=torch.zeros(N.MAX_CHANNELS + 1, dtype=torch.int64, device=dev),
             )
             self._device_state[index] = state
@@ -265,8 +267,14 @@ class CudaRNSBackend:
                 state.status.zero_()
                 raise OverflowError("full moduli set cannot represent the activation bound")
             if code != N.OK:
+                where = [int(v) for v in state.wait_info.cpu().tolist()]
                 state.status.zero_()
-                raise RuntimeError(f"RNS kernel reported device status {code}")
+                state.wait_info.zero_()
+                detail = ""
+                if code == N.ERR_DEVICE_TIMEOUT and where[0]:
+                    detail = (f": bounded wait expired (role {where[0] >> 20}, stage {where[0] & 0xfffff}, "
+                              f"CTA ({where[1]}, {where[2]}), kernel form {where[3]})")
+                raise RuntimeError(f"RNS kernel reported device status {code}{detail}")
 
     @staticmethod
     def _validate_matrix(matrix: torch.Tensor, name: str, ndim: int) -> None:
@@ -343,7 +351,7 @@ class CudaRNSBackend:
         tcgen05 kernel: K % 16 == 0, 2..8 channels, int32-safe channel sums."""
         mods, arr = self._mods(moduli)
         return bool(self._lib.rns_linear_fused_supported(arr, len(mods), int(k), int(k), int(k))) and (
-            int(k) * 127 * 127 <= 0x7FFFFFFF
+            int(k) * 128 * 128 <= 0x7FFFFFFF
         )
 
     def select_centered_kernel(self, *, k: int, n: int, moduli: Iterable[int],
@@ -607,7 +615,9 @@ class CudaRNSBackend:
             args.row_scale_stride = row_scale_stride
             args.d_col_scale = col_scale.data_ptr()
             args.d_bias = None if bias is None else bias.data_ptr()
-        args.d_status = self._state(device).status.data_ptr()
+        state = self._state(device)
+        args.d_status = state.status.data_ptr()
+        args.d_wait_info = state.wait_info.data_ptr()
         args.tile_n, args.tile_k = tile_n, tile_k
         args.pair_mode = pair_mode
         args.enc_groups = enc_groups

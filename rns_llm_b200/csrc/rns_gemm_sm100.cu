@@ -37,30 +37,6 @@
 
 namespace rns {
 
-#ifdef RNS_ABLATION
-#define RNS_ABLATED(bit) ((p.ablate >> (bit)) & 1)
-static int g_ablate = 0;
-static long long* g_timing = nullptr;   // device buffer of per-role cycle sums (CTA 0)
-#if defined(RNS_TIMING) && RNS_TIMING == 2   // event trace only
-#define RNS_TIC(var)
-#define RNS_TOC(slot, var)
-#define RNS_TRACE(slot, st) do { if (p.timing && blockIdx.x == 0 && blockIdx.y == 0 && (threadIdx.x & 31) == 0 && (st) < 64) p.timing[16 + (st) * 12 + (slot)] = clock64(); } while (0)
-#elif defined(RNS_TIMING)   // clock reads cost ~100 cycles each: only in builds that want the counters
-#define RNS_TIC(var) long long var = clock64()
-#define RNS_TRACE(slot, st) do { if (p.timing && (p.ablate >> 30) && blockIdx.x == 0 && blockIdx.y == 0 && (threadIdx.x & 31) == 0 && (st) < 64) p.timing[16 + (st) * 12 + (slot)] = clock64(); } while (0)
-#define RNS_TOC(slot, var) do { long long now__ = clock64(); if (p.timing && !(p.ablate >> 30) && blockIdx.x == 0 && blockIdx.y == 0 && (threadIdx.x & 31) == 0) p.timing[slot] += now__ - var; var = now__; } while (0)
-#else
-#define RNS_TIC(var)
-#define RNS_TOC(slot, var)
-#define RNS_TRACE(slot, st)
-#endif
-#else
-#define RNS_ABLATED(bit) false
-#define RNS_TIC(var)
-#define RNS_TOC(slot, var)
-#define RNS_TRACE(slot, st)
-#endif
-
 constexpr int kTileM = 128;
 #ifndef RNS_WORKER_WARPS
 #define RNS_WORKER_WARPS 16
@@ -77,9 +53,6 @@ constexpr bool kSpinWorkers = RNS_SPIN_WORKERS != 0;   // worker warps poll with
 
 struct GemmParams {
     Plan plan;
-    int32_t ablate;               // timing experiments only; always 0 unless built with RNS_ABLATION
-    long long* timing;            // likewise
-
     int32_t m, n, k;
     int32_t tile_n, tile_k;      // tile_k in {64,128}
     int32_t raw_stages;           // ring of raw (source byte) tiles: deep, covers the load latency
@@ -108,6 +81,7 @@ struct GemmParams {
     const float* col_scale;
     const float* bias;
     int32_t* status;
+    int32_t* wait_info;
     // shared-memory map (byte offsets from the 1024-aligned base)
     uint32_t raw_stage_bytes, enc_stage_bytes, enc_ring_offset;   // raw ring first, operand ring after
     uint32_t pl_stage_bytes, pl_sub_bytes, pl_ring_offset;        // plane ring last (planes only)
@@ -344,29 +318,26 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         // Source bytes (the W tile, and the A tile when activations are not planes)
         // go to the deep raw ring; a slot is free as soon as the encoders have read it.
         if (lane == 0 && !W_DIRECT) {
-            const uint32_t tx = (RNS_ABLATED(3) ? 0u : tile_w_bytes) +
-                                ((a_planes || RNS_ABLATED(2)) ? 0u : tile_a_bytes);
+            const uint32_t tx = tile_w_bytes +
+                                (a_planes ? 0u : tile_a_bytes);
             RingPos ring(raw_stages, 0);
             for (int st = 0; st < nstages; ++st, ring.advance(1)) {
                 const int s = ring.slot;
                 const uint32_t round = ring.round;
                 const uint32_t stage = tiles_base + (uint32_t)s * raw_stage_bytes;
                 const int jn = (FIXED && J_ == 1) ? 1 : min(J, kblocks - st * J);
-                RNS_TIC(t_p);
-                if (round > 0 && !RNS_ABLATED(10) && !wait_bounded<false, true>(smem_addr(&ctl.empty_raw[s]), (round - 1) & 1, abort)) break;
-                RNS_TOC(0, t_p);
+                if (round > 0 && !wait_bounded<false, true>(smem_addr(&ctl.empty_raw[s]), (round - 1) & 1, abort, wait_code(1, st))) break;
                 const uint32_t fr = smem_addr(&ctl.full_raw[s]);
                 mbar_arrive_expect_tx(fr, tx * (uint32_t)jn);
                 for (int j = 0; j < jn; ++j) {
                     const int kb = st * J + j;
                     const uint32_t sub = stage + (uint32_t)j * raw_sub_bytes;
-                    if (RNS_ABLATED(3)) {
-                    } else if (w_packed)
+                    if (w_packed)
                         bulk_load(sub + off_raw_w,
                                   p.w_ptr + ((int64_t)kb * p.w_npad + w_row0) * kPackK, tile_w_bytes, fr);
                     else
                         tma_load_2d(sub + off_raw_w, &map_w, fr, kb * tile_k, w_row0);
-                    if (!a_planes && !RNS_ABLATED(2)) {
+                    if (!a_planes) {
                         const int64_t a_tile = (int64_t)m_tile * kblocks + kb;   // packed tile index
                         if (a_packed)
                             bulk_load(sub + off_raw_a, p.a_ptr + a_tile * (kPackM * kPackK), tile_a_bytes, fr);
@@ -374,7 +345,6 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                             tma_load_2d(sub + off_raw_a, &map_a, fr, kb * tile_k, m0);
                     }
                 }
-                RNS_TOC(1, t_p);
             }
         }
         __syncwarp();
@@ -394,15 +364,14 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 const int jn = (FIXED && J_ == 1) ? 1 : min(J, kblocks - st * J);
                 if (ONE_COMMIT) {
                     if (st >= pl_stages) {
-                        if (!wait_bounded<false, true>(smem_addr(&ctl.empty_enc[released.slot]), released.round & 1, abort)) break;
+                        if (!wait_bounded<false, true>(smem_addr(&ctl.empty_enc[released.slot]), released.round & 1, abort, wait_code(2, st))) break;
                         released.advance(1);
                     }
-                } else if (round > 0 && !RNS_ABLATED(11) && !wait_bounded<false, true>(smem_addr(&ctl.empty_pl[s]), (round - 1) & 1, abort)) break;
-                RNS_TRACE(0, st);
+                } else if (round > 0 && !wait_bounded<false, true>(smem_addr(&ctl.empty_pl[s]), (round - 1) & 1, abort, wait_code(2, st))) break;
                 const uint32_t fp = ONE_COMMIT ? smem_addr(&ctl.full_enc[filled.slot]) : smem_addr(&ctl.full_pl[s]);
                 if (ONE_COMMIT) filled.advance(1);
-                mbar_arrive_expect_tx(fp, RNS_ABLATED(2) ? 0u : a_bytes * (uint32_t)jn);
-                for (int j = 0; j < jn && !RNS_ABLATED(2); ++j) {
+                mbar_arrive_expect_tx(fp, a_bytes * (uint32_t)jn);
+                for (int j = 0; j < jn; ++j) {
                     const int kb = st * J + j;
                     const uint32_t sub = stage + (uint32_t)j * pl_sub_bytes;
                     const int64_t a_tile = (int64_t)m_tile * kblocks + kb;
@@ -413,7 +382,6 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                             tma_load_3d(sub + (uint32_t)c * tile_a_bytes, &map_a, fp, kb * tile_k, m0, c);
                     }
                 }
-                RNS_TRACE(1, st);
             }
         }
         __syncwarp();
@@ -427,9 +395,9 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             for (int st = 0; st < nstages; ++st, ring.advance(1), ring_pl.advance(1)) {
                 const int s = ring.slot;
                 const uint32_t round = ring.round;
-                if (!wait_bounded<false, true>(smem_addr(&ctl.full_enc[s]), round & 1, abort)) break;
-                if (a_planes && !RNS_ABLATED(11) && !wait_bounded<false, true>(smem_addr(&ctl.full_pl[ring_pl.slot]),
-                                                           ring_pl.round & 1, abort)) break;
+                if (!wait_bounded<false, true>(smem_addr(&ctl.full_enc[s]), round & 1, abort, wait_code(3, st))) break;
+                if (a_planes && !wait_bounded<false, true>(smem_addr(&ctl.full_pl[ring_pl.slot]),
+                                                           ring_pl.round & 1, abort, wait_code(4, st))) break;
                 mbar_arrive_remote(smem_addr(&ctl.peer_ready[s]), 0);
             }
         } else if (!PAIR || pair_rank == 0) {
@@ -446,7 +414,7 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             const uint32_t a_sub_step = (a_planes ? pl_sub_bytes : enc_sub_bytes) >> 4;
             const uint32_t a_step = tile_a_bytes >> 4, w_step = tile_w_bytes >> 4;
             const int nks = tile_k / 32;
-            const int mma_channels = RNS_ABLATED(1) ? 0 : active;
+            const int mma_channels = active;
             uint32_t a_off[R], w_off[R];
 #pragma unroll
             for (int c = 0; c < R; ++c) { a_off[c] = (uint32_t)c * a_step; w_off[c] = (uint32_t)c * w_step; }
@@ -457,18 +425,13 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 const int s = ring.slot;
                 const uint32_t round = ring.round;
                 const int jn = (FIXED && J_ == 1) ? 1 : min(J, kblocks - st * J);
-                RNS_TIC(t_m);
                 const int sa = a_planes ? ring_pl.slot : s;       // slot of the A operands
-                ok = warp_wait_bounded<false, true>(smem_addr(&ctl.full_enc[s]), round & 1, abort);
-                RNS_TRACE(8, st);
-                if (ok && a_planes && !RNS_ABLATED(11) && !ONE_COMMIT)
-                    ok = warp_wait_bounded<false, true>(smem_addr(&ctl.full_pl[sa]), ring_pl.round & 1, abort);
-                RNS_TRACE(9, st);
-                if (ok && PAIR) ok = warp_wait_bounded<true>(smem_addr(&ctl.peer_ready[s]), round & 1, abort);
+                ok = warp_wait_bounded<false, true>(smem_addr(&ctl.full_enc[s]), round & 1, abort, wait_code(5, st));
+                if (ok && a_planes && !ONE_COMMIT)
+                    ok = warp_wait_bounded<false, true>(smem_addr(&ctl.full_pl[sa]), ring_pl.round & 1, abort, wait_code(6, st));
+                if (ok && PAIR) ok = warp_wait_bounded<true>(smem_addr(&ctl.peer_ready[s]), round & 1, abort, wait_code(7, st));
                 if (!ok) break;
-                if (!RNS_ABLATED(6)) tc_fence_after();
-                RNS_TOC(2, t_m);
-                RNS_TRACE(2, st);
+                tc_fence_after();
                 const uint32_t a_st = a_lo0 + (uint32_t)sa * a_stage_step, w_st = w_lo0 + (uint32_t)s * stage_step;
                 const uint32_t empty_bar = smem_addr(&ctl.empty_enc[s]);
                 const uint32_t empty_pl_bar = smem_addr(&ctl.empty_pl[sa]);
@@ -495,19 +458,15 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     }
                     __syncwarp();
                 }
-                RNS_TOC(3, t_m);
-                RNS_TRACE(3, st);
                 if (elect_one()) {
-                    if (RNS_ABLATED(5) && !PAIR) mbar_arrive(empty_bar);
-                    else if (PAIR) umma_commit_pair(empty_bar);
+                    if (PAIR) umma_commit_pair(empty_bar);
                     else umma_commit(empty_bar);
-                    if (a_planes && !RNS_ABLATED(11) && !ONE_COMMIT) {
+                    if (a_planes && !ONE_COMMIT) {
                         if (PAIR) umma_commit_pair(empty_pl_bar);
                         else umma_commit(empty_pl_bar);
                     }
                 }
                 __syncwarp();
-                RNS_TOC(4, t_m);
             }
             if (ok && elect_one()) {
                 if (PAIR) umma_commit_pair(smem_addr(&ctl.acc_full));
@@ -607,18 +566,18 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 uint4 ahead_a[kChunksA];
                 if (A_DIRECT) load_stage_a(st + 2 * groups, ahead_a);
                 if (ring_e.round > 0)
-                    ok = warp_wait_bounded<false, kSpinWorkers>(smem_addr(&ctl.empty_enc[se]), (ring_e.round - 1) & 1, abort);
+                    ok = warp_wait_bounded<false, kSpinWorkers>(smem_addr(&ctl.empty_enc[se]), (ring_e.round - 1) & 1, abort, wait_code(8, st));
                 if (!ok) break;
 #pragma unroll
                 for (int i = 0; i < kChunks; ++i) {
                     const int ch = wt + i * group_threads;
-                    if (ch < chunks_w && !RNS_ABLATED(0)) encode_chunk(cur[i], enc + off_enc_w + ch * 16, tile_w_bytes);
+                    if (ch < chunks_w) encode_chunk(cur[i], enc + off_enc_w + ch * 16, tile_w_bytes);
                 }
                 if (A_DIRECT) {
 #pragma unroll
                     for (int i = 0; i < kChunksA; ++i) {
                         const int ch = wt + i * group_threads;
-                        if (ch < chunks_a && !RNS_ABLATED(0)) encode_chunk(cur_a[i], enc + off_enc_a + ch * 16, tile_a_bytes);
+                        if (ch < chunks_a) encode_chunk(cur_a[i], enc + off_enc_a + ch * 16, tile_a_bytes);
                     }
 #pragma unroll
                     for (int i = 0; i < kChunksA; ++i) { cur_a[i] = nxt_a[i]; nxt_a[i] = ahead_a[i]; }
@@ -642,15 +601,12 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             // the raw ring is at least as deep as the operand ring, that also proves
             // that the raw slot's previous round has completed, which makes the parity
             // of the full_raw wait unambiguous.
-            RNS_TIC(t_e);
-            if (round_e > 0) ok = warp_wait_bounded<false, kSpinWorkers>(smem_addr(&ctl.empty_enc[se]), (round_e - 1) & 1, abort);
-            if (threadIdx.x == 64) { RNS_TOC(5, t_e); RNS_TRACE(4, st); }
-            if (ok && !RNS_ABLATED(10)) ok = warp_wait_bounded<false, kSpinWorkers>(smem_addr(&ctl.full_raw[sr]), round_r & 1, abort);
-            if (threadIdx.x == 64) { RNS_TOC(6, t_e); RNS_TRACE(5, st); }
+            if (round_e > 0) ok = warp_wait_bounded<false, kSpinWorkers>(smem_addr(&ctl.empty_enc[se]), (round_e - 1) & 1, abort, wait_code(9, st));
+            if (ok) ok = warp_wait_bounded<false, kSpinWorkers>(smem_addr(&ctl.full_raw[sr]), round_r & 1, abort, wait_code(10, st));
             if (!ok) break;
             // part 0: the W tile; part 1: the A tile (nothing to do when activations are planes)
             const int parts = (FIXED || a_planes) ? 1 : 2;
-            for (int jp = 0; jp < (RNS_ABLATED(0) ? 0 : parts * jn); ++jp) {
+            for (int jp = 0; jp < parts * jn; ++jp) {
                 const int j = parts == 1 ? jp : jp >> 1, part = parts == 1 ? 0 : jp & 1;
                 const int chunks = part == 0 ? chunks_w : chunks_a;
                 const uint8_t* raw = raw_stage + (size_t)j * raw_sub_bytes + (part == 0 ? off_raw_w : off_raw_a);
@@ -670,19 +626,17 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             // Every writer makes its stores visible to the async proxy, the warp
             // converges, and one lane signals for the warp (arrivals on one mbarrier
             // serialise): the operand tiles are ready, the raw slot may be refilled.
-            if (threadIdx.x == 64) { RNS_TOC(7, t_e); RNS_TRACE(6, st); }
-            if (!RNS_ABLATED(7)) fence_proxy_async_smem();
+            fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) {
                 mbar_arrive(smem_addr(&ctl.full_enc[se]));
                 mbar_arrive(smem_addr(&ctl.empty_raw[sr]));
             }
-            if (threadIdx.x == 64) { RNS_TOC(8, t_e); RNS_TRACE(7, st); }
         }
 
         // ------------------------------ epilogue ----------------------------------
-        if (ok) ok = warp_wait_bounded(smem_addr(&ctl.acc_full), 0, abort);
-        if (ok && !RNS_ABLATED(4)) {
+        if (ok) ok = warp_wait_bounded(smem_addr(&ctl.acc_full), 0, abort, wait_code(11, 0));
+        if (ok) {
             tc_fence_after();
             const int quarter = warp & 3;             // TMEM lanes 32*quarter .. +31
             const int part = (warp - 2) >> 2;         // 8-column chunks are dealt round-robin
@@ -828,8 +782,15 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     // PAIR: neither CTA may free tensor memory or leave (its shared memory feeds the
     // partner's MMAs) before both have finished.
     if (PAIR) cluster_sync_all(); else __syncthreads();
-    if (threadIdx.x == 0 && ctl.abort && p.status != nullptr)
-        atomicExch(p.status, (int)RNS_ERR_DEVICE_TIMEOUT);
+    if (threadIdx.x == 0 && ctl.abort) {
+        if (p.status != nullptr) atomicExch(p.status, (int)RNS_ERR_DEVICE_TIMEOUT);
+        // First CTA to give up records which wait expired and where in the grid.
+        if (p.wait_info != nullptr && atomicCAS(p.wait_info, 0, ctl.abort) == 0) {
+            p.wait_info[1] = (int)blockIdx.x;
+            p.wait_info[2] = (int)blockIdx.y;
+            p.wait_info[3] = R * 1000000 + (PAIR ? 100000 : 0) + (FIXED ? 10000 : 0) + tile_n;
+        }
+    }
     if (warp == 1) {
         tc_fence_after();
         if (PAIR) tmem_dealloc2(tmem_base, (uint32_t)p.tmem_cols);
@@ -948,11 +909,6 @@ using namespace rns;
 
 extern "C" {
 
-#ifdef RNS_ABLATION
-__attribute__((visibility("default"))) void rns_debug_set_ablation(int bits) { rns::g_ablate = bits; }
-__attribute__((visibility("default"))) void rns_debug_set_timing(long long* d) { rns::g_timing = d; }
-#endif
-
 int rns_linear_fused_supported(const int32_t* moduli, int channels, int k, int64_t lda, int64_t ldw) {
     Plan pl;
     if (build_plan(moduli, channels, &pl) != RNS_OK) return 0;
@@ -990,6 +946,10 @@ int rns_linear_fused(const rns_linear_args* a, rns_stream_t stream) {
     const char* why = "";
     if (!tc_supported(pl, a->k, a_packed ? 16 : a->lda, w_packed ? 16 : a->ldw, a->exact_residues != 0, &why))
         return fail(RNS_ERR_UNSUPPORTED, "tensor-core path: %s", why);
+    // The per-channel sums are int32: |sum| <= K * 128 * 128 must fit (a wrapped sum is
+    // no longer congruent to the true one modulo m).
+    if ((int64_t)a->k * 128 * 128 > (int64_t)INT32_MAX)
+        return fail(RNS_ERR_OVERFLOW, "K = %d: a channel's int32 sum could exceed 2^31 - 1 (K <= 131071)", a->k);
     if ((a_packed || w_packed) && a->tile_k == 128)
         return fail(RNS_ERR_INVALID_ARGUMENT, "packed operands use tile_k = 64");
     if (planes && !a_packed && a->a_plane_stride % 16 != 0)
@@ -1137,10 +1097,6 @@ int rns_linear_fused(const rns_linear_args* a, rns_stream_t stream) {
     while (gp.enc_groups > enc_stages) gp.enc_groups /= 2;
     gp.m = a->m; gp.n = a->n; gp.k = a->k;
     gp.tile_n = tile_n; gp.tile_k = tile_k;
-#ifdef RNS_ABLATION
-    gp.ablate = g_ablate;
-    gp.timing = g_timing;
-#endif
     gp.exact_residues = a->exact_residues ? 1 : 0;
     gp.a_is_planes = planes ? 1 : 0;
     gp.a_packed = a_packed ? 1 : 0;
@@ -1153,6 +1109,7 @@ int rns_linear_fused(const rns_linear_args* a, rns_stream_t stream) {
     gp.out = a->d_out; gp.ldo = a->ldo; gp.out_type = a->out_type;
     gp.row_scale = a->d_row_scale; gp.row_scale_stride = a->row_scale_stride;
     gp.col_scale = a->d_col_scale; gp.bias = a->d_bias; gp.status = a->d_status;
+    gp.wait_info = a->d_wait_info;
 
     // ---- tensor maps -------------------------------------------------------
     CUtensorMap map_a, map_w;

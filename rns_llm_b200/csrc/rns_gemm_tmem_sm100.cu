@@ -42,17 +42,6 @@
 
 namespace rns {
 
-#ifdef RNS_ABLATION
-long long* g_timing_v2 = nullptr;
-#endif
-#if defined(RNS_ABLATION) && defined(RNS_TIMING)
-#define V2_TIC(var) long long var = clock64()
-#define V2_TOC(slot, var) do { long long now__ = clock64(); if (p.timing && blockIdx.x == 0 && blockIdx.y == 0) p.timing[slot] += now__ - var; var = now__; } while (0)
-#else
-#define V2_TIC(var)
-#define V2_TOC(slot, var)
-#endif
-
 constexpr int kV2Threads = 576;
 constexpr int kV2Workers = 16;
 constexpr int kV2Slots = 4;            // weight-operand slots (K blocks) in tensor memory
@@ -80,7 +69,6 @@ struct TmemGemmParams {
     const float* bias;
     int32_t* status;
     uint32_t plane_sub_bytes;          // one K block: R * tile_t * 64
-    long long* timing;                 // profiling builds only
 };
 
 struct __align__(8) V2Ctl {
@@ -194,11 +182,8 @@ rns_gemm_tmem_kernel(const __grid_constant__ TmemGemmParams p) {
                 const int so = pr % kV2SlotPairs;
                 const uint32_t stage = ring_base + (uint32_t)sp * stage_bytes;
                 const int jn = min(2, kblocks - 2 * pr);
-                V2_TIC(tm);
                 ok = wait_bounded<false, true>(smem_addr(&ctl.op_full[so]), (uint32_t)(pr / kV2SlotPairs) & 1, abort);
-                V2_TOC(0, tm);
                 if (ok) ok = wait_bounded<false, true>(smem_addr(&ctl.pl_full[sp]), (uint32_t)(pr / stages) & 1, abort);
-                V2_TOC(1, tm);
                 if (!ok) break;
                 tc_fence_after();
                 for (int j = 0; j < jn; ++j) {
@@ -213,10 +198,8 @@ rns_gemm_tmem_kernel(const __grid_constant__ TmemGemmParams p) {
                                        (pr > 0 || j > 0 || ks > 0) ? 1u : 0u);
                     }
                 }
-                V2_TOC(2, tm);
                 umma_commit(smem_addr(&ctl.op_empty[so]));
                 umma_commit(smem_addr(&ctl.pl_empty[sp]));
-                V2_TOC(3, tm);
             }
             if (ok) umma_commit(smem_addr(&ctl.acc_full));
         }
@@ -264,9 +247,7 @@ rns_gemm_tmem_kernel(const __grid_constant__ TmemGemmParams p) {
                 for (int i = 0; i < 16; ++i) d[i] = fold_pattern(x[i]);
             }
             // the slot pair must have been consumed by the MMAs of its previous round
-            V2_TIC(te);
             if (round > 0) ok = wait_bounded(smem_addr(&ctl.op_empty[so]), (round - 1) & 1, abort);
-            if (threadIdx.x == 64) V2_TOC(4, te);
             if (!ok) break;
             tc_fence_after();
 #pragma unroll
@@ -278,13 +259,10 @@ rns_gemm_tmem_kernel(const __grid_constant__ TmemGemmParams p) {
                     tmem_st16(lane_base + (uint32_t)(p.opnd_col0 + (slot * R + c) * 16), v);
                 }
             }
-            if (threadIdx.x == 64) V2_TOC(5, te);
             tmem_st_wait();
-            if (threadIdx.x == 64) V2_TOC(6, te);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_addr(&ctl.op_full[so]));
-            if (threadIdx.x == 64) V2_TOC(7, te);
         }
         // A K-block count that is not a multiple of four leaves some groups one
         // hand-over short of their partners in the last pair: every pair needs all
@@ -425,9 +403,6 @@ int launch_tmem_gemm(const rns_linear_args* a, const Plan& plan, cudaStream_t st
     if (stages > npairs) stages = npairs;
     if (stages < 1) return fail(RNS_ERR_UNSUPPORTED, "token tile does not fit shared memory");
     gp.plane_stages = stages;
-#ifdef RNS_ABLATION
-    gp.timing = g_timing_v2;
-#endif
     gp.exact_residues = a->exact_residues ? 1 : 0;
     gp.active_ptr = a->d_active_channels;
     gp.planes = a->d_a_planes;
@@ -450,6 +425,3 @@ int launch_tmem_gemm(const rns_linear_args* a, const Plan& plan, cudaStream_t st
 
 }  // namespace rns
 
-#ifdef RNS_ABLATION
-extern "C" __attribute__((visibility("default"))) void rns_debug_set_timing_v2(long long* d) { rns::g_timing_v2 = d; }
-#endif

@@ -205,11 +205,13 @@ __device__ __forceinline__ uint32_t make_idesc(uint32_t m, uint32_t n) {
 }
 
 // Waits for `parity` of `bar`; false (and *abort set) when the time limit passes
-// or another thread of the CTA already gave up.
+// or another thread of the CTA already gave up.  `where` names the wait (role and
+// pipeline stage, see wait_code); the first wait of a CTA that expires leaves it in
+// *abort, and the kernel's teardown reports it to the host.
 // SPIN: poll with test_wait instead of the suspending try_wait; for the single
 // threads whose wake-up latency is on the critical path of every K block.
 template <bool CLUSTER = false, bool SPIN = false>
-__device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity, volatile int* abort) {
+__device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity, volatile int* abort, int where = 1) {
     auto poll = [&]() {
         return CLUSTER ? mbar_try_wait_cluster(bar, parity)
                        : (SPIN ? mbar_test_wait(bar, parity) : mbar_try_wait(bar, parity));
@@ -230,24 +232,30 @@ __device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity, vola
         if ((spin & 255u) == 0) {
             if (*abort) return false;
             if (clock64() - t0 > kWaitLimitCycles) {
-                *abort = 1;
+                if (*abort == 0) *abort = where;
                 return false;
             }
         }
     }
 }
+// Code of one wait: which role gave up (1 raw-tile producer, 2 plane producer, 3/4 pair
+// relay on operands/planes, 5/6/7 MMA issuer on operands/planes/peer, 8/9 encoders on a
+// released operand slot, 10 encoders on raw tiles, 11 epilogue on the accumulators) and
+// at which pipeline stage.  Never zero.
+__device__ __forceinline__ int wait_code(int role, int stage) { return (role << 20) | (stage & 0xfffff); }
+
 // The same for a whole (converged) warp, with a warp-uniform result.
 #ifndef RNS_LANE0_POLL
 #define RNS_LANE0_POLL 0   // measured: all lanes polling is faster than one lane + shuffle
 #endif
 template <bool CLUSTER = false, bool SPIN = false>
-__device__ __forceinline__ bool warp_wait_bounded(uint32_t bar, uint32_t parity, volatile int* abort) {
+__device__ __forceinline__ bool warp_wait_bounded(uint32_t bar, uint32_t parity, volatile int* abort, int where = 1) {
 #if RNS_LANE0_POLL
     int ok = 1;
-    if ((threadIdx.x & 31) == 0) ok = wait_bounded<CLUSTER, SPIN>(bar, parity, abort) ? 1 : 0;
+    if ((threadIdx.x & 31) == 0) ok = wait_bounded<CLUSTER, SPIN>(bar, parity, abort, where) ? 1 : 0;
     return __shfl_sync(0xffffffffu, ok, 0) != 0;
 #else
-    return __all_sync(0xffffffffu, wait_bounded<CLUSTER, SPIN>(bar, parity, abort));
+    return __all_sync(0xffffffffu, wait_bounded<CLUSTER, SPIN>(bar, parity, abort, where));
 #endif
 }
 

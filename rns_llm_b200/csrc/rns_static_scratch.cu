@@ -30,7 +30,9 @@ std::mutex g_setup_mutex;
 std::atomic<unsigned char*> g_device_ptr[kMaxDevices];
 
 // First call on each device (with that device current) resolves the array's
-// device address.  No allocation happens here or anywhere below.
+// device address.  No allocation happens here or anywhere below.  The address is
+// remembered per device ordinal; cudaDeviceReset invalidates it (a process that
+// resets a device must not call rns_linear_static on it again).
 int scratch_for_current_device(unsigned char** out) {
     int dev = 0;
     RNS_CUDA_OK(cudaGetDevice(&dev));
@@ -61,10 +63,22 @@ int rns_linear_static(const void* d_x, rns_float_type type, int m, int k, int64_
                       const int8_t* d_w_packed, int n, const int32_t* moduli, int channels,
                       const float* d_col_scale, const float* d_bias, void* d_out, int64_t ldo,
                       int32_t out_type, int32_t* d_status, rns_stream_t stream) {
-    if (!d_x || !d_w_packed || !d_col_scale || !d_out)
+    // Everything is checked before the first launch: a refused call queues nothing
+    // and leaves the shared array as the previous call left it.
+    if (!d_x || !d_w_packed || !d_col_scale || !d_out || !moduli)
         return rns::fail(RNS_ERR_INVALID_ARGUMENT, "rns_linear_static: NULL pointer");
     if (out_type != RNS_OUT_F16 && out_type != RNS_OUT_BF16 && out_type != RNS_OUT_F32)
         return rns::fail(RNS_ERR_INVALID_ARGUMENT, "rns_linear_static produces floating outputs only");
+    if (type != RNS_F16 && type != RNS_BF16 && type != RNS_F32)
+        return rns::fail(RNS_ERR_INVALID_ARGUMENT, "rns_linear_static: unknown float type");
+    if (m <= 0 || n <= 0 || k <= 0 || ldx < k || ldo < n)
+        return rns::fail(RNS_ERR_INVALID_ARGUMENT, "rns_linear_static: bad shape or stride");
+    if (channels < 2 || channels > RNS_TC_MAX_CHANNELS || !rns_linear_fused_supported(moduli, channels, k, 16, 16))
+        return rns::fail(RNS_ERR_UNSUPPORTED,
+                         "rns_linear_static: needs K %% 16 == 0 and 2..%d pairwise coprime moduli in [2,255]",
+                         RNS_TC_MAX_CHANNELS);
+    if ((int64_t)k * 128 * 128 > (int64_t)INT32_MAX)
+        return rns::fail(RNS_ERR_OVERFLOW, "rns_linear_static: K = %d overflows the int32 channel sums", k);
     const int64_t need = rns_packed_activation_bytes(m, k, 1);
     if (need <= 0) return rns::fail(RNS_ERR_INVALID_ARGUMENT, "rns_linear_static: bad shape");
     if ((size_t)need > kStaticBytes)

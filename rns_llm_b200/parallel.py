@@ -69,12 +69,21 @@ class ColumnShardedRNSLinear(nn.Module):
     ``forward(x)`` takes the replicated activation, either [.., K] or a gathered
     [G, M, K/G] tensor from a previous sharded layer, and returns the gathered
     output [G, M, N/G] (``gather=True``) or the local shard [M, N/G].
+
+    Ownership of the result: by default every call returns a freshly allocated
+    tensor, as the reference's ``RNSLinear`` does.  ``out=`` writes into the
+    caller's [G, M, N/G] buffer.  ``reuse_buffer=True`` (constructor) makes the
+    layer keep ONE buffer per (M, dtype, stream) and return it from every call:
+    the next forward with the same M on the same stream then overwrites the
+    tensor the previous call returned - for layer stacks that consume each
+    output before the layer runs again, not for callers that hold results.
     """
 
     def __init__(self, weight_shard: torch.Tensor, bias_shard: torch.Tensor | None, *, backend,
                  moduli: Iterable[int], rank: int, world: int, group=None, groups: int = 1,
-                 activation_scale: str = "tensor") -> None:
+                 activation_scale: str = "tensor", reuse_buffer: bool = False) -> None:
         super().__init__()
+        self.reuse_buffer = bool(reuse_buffer)
         if weight_shard.ndim != 2:
             raise ValueError("weight_shard must be [N/world, K]")
         if activation_scale not in ("tensor", "row"):
@@ -103,6 +112,8 @@ class ColumnShardedRNSLinear(nn.Module):
                    groups=groups, activation_scale=activation_scale)
 
     def _buffer(self, m: int, dtype: torch.dtype, device: torch.device) -> torch.Tensor:
+        if not self.reuse_buffer:
+            return torch.empty((self.world, m, self.local_features), dtype=dtype, device=device)
         stream = int(torch.cuda.current_stream(device).cuda_stream)
         key = (m, dtype, stream)
         buf = self._gather_buffers.get(key)
@@ -112,6 +123,8 @@ class ColumnShardedRNSLinear(nn.Module):
         return buf
 
     def forward(self, x: torch.Tensor, *, gather: bool = True, out: torch.Tensor | None = None) -> torch.Tensor:
+        """See the class docstring for who owns the returned tensor (fresh by default;
+        the layer's own buffer, overwritten by the next call, with ``reuse_buffer``)."""
         if x.ndim == 3 and x.shape[0] * x.shape[2] == self.in_features and x.shape[2] != self.in_features:
             flat, m = x, int(x.shape[1])          # gathered activation [G, M, K/G]
         else:

@@ -155,4 +155,6 @@ def main(reference_root: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: python tests/golden/make_golden.py <checkout of Nek1tt/rns-llm v0.5>")
+    main(sys.argv[1])

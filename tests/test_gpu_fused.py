@@ -549,3 +549,122 @@ def test_weight_pack_roundtrip_and_residues(backend):
         assert np.array_equal(prepared.weight_nk.cpu().numpy(), w)
         # planes are derived on request, in the reference's [R,K,N] shape
         assert np.array_equal(prepared.residues.cpu().numpy(), O.encode_centered(w.T, C0, "device"))
+
+
+def _torch_linear_reference(x_plain, w_q, w_scale, bias):
+    """Per-tensor quantisation, exact int8 GEMM through torch._int_mm and the reference's
+    fp32 dequantisation order (layers/rns_linear.py:239-241, 264, 272-275), all on the GPU."""
+    flat = x_plain.float()
+    s_a = torch.clamp(flat.abs().amax() / 127.0, min=float(np.finfo(np.float32).eps))
+    a_q = torch.clamp(torch.round(flat / s_a), -127, 127).to(torch.int8)
+    acc = torch._int_mm(a_q, w_q.t())
+    y = acc.float() * s_a * w_scale[None, :]
+    if bias is not None:
+        y = y + bias[None, :]
+    return y.to(x_plain.dtype), acc
+
+
+@pytest.mark.parametrize("world", [4, 8])
+@pytest.mark.parametrize("name,k,n,mods,groups", [("qkv", 4096, 12288, C0, 3), ("out_proj", 4096, 4096, C0, 1),
+                                                  ("fc1", 4096, 16384, C0, 1), ("fc2", 16384, 4096, C4, 1)])
+def test_rank_local_problems_of_a_sharded_stack(backend, world, name, k, n, mods, groups):
+    """What one rank of a 4- or 8-way column-sharded OPT-6.7B-shaped layer runs, on one GPU:
+    M = 4096 tokens, N / world output features, the activation read from a gathered
+    [G, M, K/G] tensor (for out_proj: a column-group view of a wider gathered tensor, as the
+    q block of a fused QKV output), the result written into slot `rank` of a [G, M, N/G]
+    buffer, for the first and the last rank.  Checked bit for bit against the same call on
+    the plain [M, K] matrix into a fresh tensor, and that against torch._int_mm + fp32
+    dequantisation (exact integers; 1e-3 relative on the fp16 outputs)."""
+    from rns_llm_b200.parallel import group_view, shard_tensor
+
+    m = 4096
+    torch.manual_seed(world * 100 + k // 1024 + n // 1024)
+    if name == "out_proj":
+        wide = torch.randn(world, m, 3 * k // world, dtype=torch.float16, device="cuda")
+        blocks = group_view(wide, 3, 0)                          # strided view, [G, M, K/G]
+    else:
+        blocks = torch.randn(world, m, k // world, dtype=torch.float16, device="cuda")
+    plain = blocks.permute(1, 0, 2).reshape(m, k).contiguous()
+    full_w = (torch.randn(n, k, device="cuda") * (1.0 / k ** 0.5)).half()
+    full_b = (torch.randn(n, device="cuda") * 0.01).float()
+    for rank in (0, world - 1):
+        weight = shard_tensor(full_w, world, rank, groups).contiguous()
+        bias = shard_tensor(full_b, world, rank, groups).contiguous()
+        w_q, w_scale, _ = backend.quantize_weight(weight)
+        prepared = backend.prepare_weight_nk(w_q, mods)
+        local_n = n // world
+        gathered = torch.full((world, m, local_n), float("nan"), dtype=torch.float16, device="cuda")
+        backend.linear_forward(blocks, prepared, w_scale, bias, out=gathered[rank])
+        fresh = backend.linear_forward(plain, prepared, w_scale, bias)
+        torch.cuda.synchronize()
+        backend.check_status()
+        assert torch.equal(gathered[rank], fresh), (name, world, rank)
+        others = [r for r in range(world) if r != rank]
+        assert bool(torch.isnan(gathered[others]).all())          # nothing written outside the slot
+        expect, _ = _torch_linear_reference(plain, w_q, w_scale, bias)
+        diff = (fresh.float() - expect.float()).abs()
+        assert float((diff / expect.float().abs().clamp_min(1e-3)).max()) <= REL_TOL
+        # the integer path on the same shard, bit-exact against the independent int8 GEMM
+        a_q = torch.randint(-127, 128, (m, k), dtype=torch.int8, device="cuda")
+        got = backend.matmul_prepared_fused(a_q, prepared)
+        assert torch.equal(got, torch._int_mm(a_q, w_q.t()).to(torch.int64)), (name, world, rank)
+    backend.check_status()
+
+
+@pytest.mark.parametrize("k", [16, 80, 144])
+def test_k_tails_inside_the_last_64_byte_block(backend, k):
+    """K is a multiple of 16 but not of 64: the packed layouts pad the last K block, the
+    quantiser does not write the pad columns of the activation side, and the result must
+    not depend on what an earlier, larger call left in the same scratch."""
+    from rns_llm_b200 import _native as N
+
+    rng = np.random.default_rng(k)
+    for m in (7, 130):
+        a, w = rand_i8(rng, (m, k), -128, 127), rand_i8(rng, (40, k), -128, 127)
+        exact = O.exact_matmul(a, w.T)
+        for mode in MODES:
+            assert np.array_equal(fused_int(backend, a, w, C0, **mode), exact), (m, mode)
+    torch.manual_seed(k)
+    n = 72
+    weight = (torch.randn(n, k, device="cuda") * 0.1).half()
+    bias = torch.randn(n, device="cuda").float()
+    w_q, w_scale, _ = backend.quantize_weight(weight)
+    prepared = backend.prepare_weight_nk(w_q, C0)
+    lib = N.load()
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+    for m in (9, 600):                       # in-kernel residues, and residue planes
+        # dirty the arena and the static array with a larger problem first
+        big = torch.randn(1024, 256, dtype=torch.float16, device="cuda") * 50
+        big_w, big_s, _ = backend.quantize_weight((torch.randn(64, 256, device="cuda")).half())
+        big_p = backend.prepare_weight_nk(big_w, C0)
+        backend.linear_forward(big, big_p, big_s, None)
+        sink = torch.empty((1024, 64), dtype=torch.float16, device="cuda")
+        N.check(lib.rns_linear_static(big.data_ptr(), N.F16, 1024, 256, 256, big_p.weight_packed.data_ptr(), 64,
+                                      N.moduli_array(C0), 4, big_s.data_ptr(), None, sink.data_ptr(), 64,
+                                      N.OUT_F16, status.data_ptr(), stream))
+        x = torch.randn(m, k, dtype=torch.float16, device="cuda")
+        expect = O.rns_linear_forward(x.cpu().numpy(), weight.cpu().numpy(), bias.cpu().numpy(), C0)["y"]
+        y = backend.linear_forward(x, prepared, w_scale, bias)
+        assert np.array_equal(y.cpu().numpy().view(np.uint16), expect.view(np.uint16)), m
+        got = torch.full((m, n), float("nan"), dtype=torch.float16, device="cuda")
+        N.check(lib.rns_linear_static(x.data_ptr(), N.F16, m, k, k, prepared.weight_packed.data_ptr(), n,
+                                      N.moduli_array(C0), 4, w_scale.data_ptr(), bias.data_ptr(), got.data_ptr(), n,
+                                      N.OUT_F16, status.data_ptr(), stream))
+        torch.cuda.synchronize()
+        assert int(status.item()) == 0
+        assert np.array_equal(got.cpu().numpy().view(np.uint16), expect.view(np.uint16)), m
+    backend.check_status()
+
+
+def test_channel_sum_overflow_is_refused(backend):
+    """K beyond 131071 could wrap an int32 channel sum: the C ABI refuses it."""
+    from rns_llm_b200 import _native as N
+    args = N.LinearArgs()
+    args.m, args.n, args.k, args.channels = 16, 16, 131072, 4
+    for i, mod in enumerate(C0):
+        args.moduli[i] = mod
+    dummy = torch.zeros(64, dtype=torch.int8, device="cuda")
+    args.d_a = dummy.data_ptr(); args.d_w = dummy.data_ptr(); args.d_out = dummy.data_ptr()
+    args.lda = args.ldw = 131072; args.ldo = 16; args.out_type = N.OUT_INT64
+    assert N.load().rns_linear_fused(args, None) == N.ERR_OVERFLOW

@@ -81,3 +81,79 @@ def test_two_rank_gloo_sharded_layers():
     results = manager.dict()
     mp.spawn(_worker, args=(world, port, results), nprocs=world, join=True)
     assert dict(results) == {0: True, 1: True}
+
+
+class _FakePrepared:
+    kernel = "tcgen05"
+
+    def __init__(self, w_q):
+        self.w_q, self.n, self.k = w_q, int(w_q.shape[0]), int(w_q.shape[1])
+
+
+class _FakeBackend:
+    """Stand-in for CudaRNSBackend with plain torch arithmetic, for this file only: it
+    lets the host logic of ColumnShardedRNSLinear (buffers, slots, gather) run on CPU."""
+
+    def quantize_weight(self, weight):
+        scale = weight.float().abs().amax(dim=1).clamp_min(1e-8) / 127.0
+        return torch.clamp(torch.round(weight.float() / scale[:, None]), -127, 127).to(torch.int32), scale, None
+
+    def prepare_weight_nk(self, w_q, moduli):
+        return _FakePrepared(w_q)
+
+    def linear_forward(self, x, prepared, weight_scale, bias, *, per_row=False, out=None):
+        if x.ndim == 3:
+            x = unshard(x.contiguous(), 1)
+        s_a = x.float().abs().amax().clamp_min(1e-8) / 127.0
+        x_q = torch.clamp(torch.round(x.float() / s_a), -127, 127).to(torch.int32)
+        y = (x_q @ prepared.w_q.t()).float() * s_a * weight_scale[None, :]
+        if bias is not None:
+            y = y + bias[None, :]
+        out.copy_(y.to(out.dtype))
+        return out
+
+
+def _layer_worker(rank: int, world: int, port: int, results):
+    import torch.cuda as cuda
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    # The layer keys its cached buffer by the current CUDA stream; there is none on CPU.
+    class _NoStream:
+        cuda_stream = 0
+    cuda.current_stream = lambda device=None: _NoStream()
+    try:
+        from rns_llm_b200.parallel import ColumnShardedRNSLinear
+        torch.manual_seed(99)
+        weight, bias = torch.randn(8, 16), torch.randn(8)
+        full = _FakeBackend()
+        ok = True
+        for reuse in (False, True):
+            layer = ColumnShardedRNSLinear(shard_tensor(weight, world, rank), shard_tensor(bias, world, rank),
+                                           backend=full, moduli=(127, 126, 125, 121), rank=rank, world=world,
+                                           reuse_buffer=reuse)
+            x1, x2 = torch.randn(5, 16), torch.randn(5, 16)
+            y1 = layer(x1)
+            kept = y1.clone()
+            y2 = layer(x2)
+            if reuse:
+                ok = ok and y1.data_ptr() == y2.data_ptr()          # documented aliasing
+            else:
+                ok = ok and torch.equal(y1, kept) and y1.data_ptr() != y2.data_ptr()
+            w_q, scale, _ = full.quantize_weight(weight)
+            expect = full.linear_forward(x2, _FakePrepared(w_q), scale, bias, out=torch.empty(5, 8))
+            ok = ok and torch.allclose(unshard(y2, 1), expect, atol=1e-5)
+        results[rank] = bool(ok)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_sharded_layer_result_ownership_two_ranks():
+    """A second forward must not change the tensor the first one returned, unless the
+    layer was built with reuse_buffer=True (then both calls return the same storage)."""
+    world = 2
+    port = _free_port()
+    manager = mp.Manager()
+    results = manager.dict()
+    mp.spawn(_layer_worker, args=(world, port, results), nprocs=world, join=True)
+    assert dict(results) == {0: True, 1: True}

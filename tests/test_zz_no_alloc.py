@@ -50,3 +50,12 @@ def test_static_scratch_entry_matches_arena_path_twice():
                                       N.moduli_array(C0), 4, w_scale.data_ptr(), bias.data_ptr(),
                                       got.data_ptr(), n, N.OUT_F16, status.data_ptr(), stream))
     assert "scratch" in str(err.value)
+
+    # bad arguments are refused before anything is queued (NULL moduli, K % 16 != 0)
+    for bad in (dict(moduli=None), dict(k=772)):
+        kk = bad.get("k", k)
+        mods = bad.get("moduli", N.moduli_array(C0))
+        code = lib.rns_linear_static(x.data_ptr(), N.F16, 16, kk, kk, prepared.weight_packed.data_ptr(), n,
+                                     mods, 4, w_scale.data_ptr(), bias.data_ptr(),
+                                     got.data_ptr(), n, N.OUT_F16, status.data_ptr(), stream)
+        assert code in (N.ERR_INVALID_ARGUMENT, N.ERR_UNSUPPORTED)
