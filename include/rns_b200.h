@@ -263,9 +263,20 @@ typedef struct rns_linear_args {
     int32_t sub_blocks;       /* 0 = choose; else K blocks of tile_k bytes per pipeline stage (1..4) */
     int32_t variant;          /* 0 = choose; 1: operands staged in shared memory; 2: weights as
                                  tensor-memory operands (packed planes + packed weights, 2..5
-                                 channels; tile_n then means tokens per tile: 32, 64 or 128) */
+                                 channels; tile_n then means tokens per tile: 32, 64 or 128);
+                                 3: two-CTA feature-major kernel (see a_tile_rows) */
     int32_t exact_residues;   /* 1: in-kernel residues exactly centred (|r| <= m/2; needs every
                                  modulus >= 86); 0: one-step reduced residues (any moduli) */
+    int32_t a_tile_rows;      /* packed planes only: token rows per packed tile. 0 or 128: the layout
+                                 above.  64 (up to four channels) or 48 (five): tiles of that many
+                                 rows, [M_pad/rows][K_pad/64][channels][rows][64], written by
+                                 rns_quantize_activations_tiled; selects the two-CTA feature-major
+                                 kernel (variant 3), which needs 4 or 5 channels and K >= 512 */
+    uint32_t* d_absmax_out;   /* NULL, or device word that receives the bit pattern of
+                                 max |y| over the floating outputs as stored (variant 3 only;
+                                 the launch clears it first): the per-tensor absmax the NEXT
+                                 layer's quantiser needs, so that it can skip its own pass over
+                                 the activations (layers/rns_linear.py:239-240 of the reference) */
     int32_t* d_wait_info;     /* NULL, or device int32[4], zero before the launch: when a bounded
                                  wait expires the first CTA to give up writes {wait code =
                                  role << 20 | pipeline stage, blockIdx.x, blockIdx.y, kernel form}
@@ -277,6 +288,12 @@ RNS_API int rns_linear_fused(const rns_linear_args* args, rns_stream_t stream);
 /* Bytes of the packed layouts (see rns_linear_args). */
 RNS_API int64_t rns_packed_weight_bytes(int n, int k);
 RNS_API int64_t rns_packed_activation_bytes(int m, int k, int channels /* 1 = source integers */);
+/* ... and of packed planes in tiles of tile_rows token rows (rns_linear_args.a_tile_rows);
+ * M is padded to a multiple of 2 * tile_rows, the token tile of the two-CTA kernel. */
+RNS_API int64_t rns_packed_planes_bytes(int m, int k, int channels, int tile_rows);
+/* Token rows per packed tile that the two-CTA kernel wants for this channel count, or 0
+ * when it does not cover it (then use the 128-row layout and variants 0..2). */
+RNS_API int rns_pair_tile_rows(int channels, int k);
 
 /*
  * Repacks quantised weights d_w int8 [N,K] (row stride ldw) into the packed
@@ -344,6 +361,29 @@ RNS_API int rns_quantize_activations(const void* d_x, rns_float_type type,
                                      float* d_scale,
                                      int32_t* d_row_l1_max, void* d_scratch,
                                      rns_stream_t stream);
+
+/*
+ * The same quantiser with two extensions used by layer stacks (no reference
+ * counterpart: the reference recomputes the absmax in eager torch for every layer):
+ *   tile_rows          token rows per packed tile of d_planes (0/128 as above, or
+ *                      rns_pair_tile_rows());
+ *   d_absmax_parts     NULL, or `absmax_parts` device words `absmax_part_stride`
+ *                      words apart, each the bit pattern of a non-negative float:
+ *                      their maximum is taken as the tensor's absmax and the
+ *                      quantiser's own pass over the activations is skipped (per-tensor
+ *                      scale only).  A previous layer's d_absmax_out provides one word;
+ *                      a column-sharded layer provides one word per rank.
+ */
+RNS_API int rns_quantize_activations_tiled(const void* d_x, rns_float_type type,
+                                           int m, int k, int64_t ldx,
+                                           int col_block, int64_t col_block_stride,
+                                           int per_row, int quant_max,
+                                           const int32_t* moduli, int channels,
+                                           int8_t* d_q, int8_t* d_planes, int packed_out,
+                                           int tile_rows, float* d_scale,
+                                           int32_t* d_row_l1_max, void* d_scratch,
+                                           const uint32_t* d_absmax_parts, int absmax_parts,
+                                           int64_t absmax_part_stride, rns_stream_t stream);
 
 /*
  * Row-L1 maximum of already-quantised activations: max_m sum_k |a[m,k]|, the

@@ -61,6 +61,8 @@ class LinearArgs(C.Structure):
         ("sub_blocks", C.c_int32),
         ("variant", C.c_int32),
         ("exact_residues", C.c_int32),
+        ("a_tile_rows", C.c_int32),
+        ("d_absmax_out", C.c_void_p),
         ("d_wait_info", C.c_void_p),
     ]
 
@@ -89,6 +91,11 @@ SIGNATURES: dict[str, tuple] = {
     "rns_quantize_activations": (C.c_int, [_VP, C.c_int, C.c_int, C.c_int, C.c_int64, C.c_int, C.c_int64, C.c_int, C.c_int, _I32P, C.c_int, _VP, _VP, C.c_int, _VP, _VP, _VP, _VP]),
     "rns_packed_weight_bytes": (C.c_int64, [C.c_int, C.c_int]),
     "rns_packed_activation_bytes": (C.c_int64, [C.c_int, C.c_int, C.c_int]),
+    "rns_packed_planes_bytes": (C.c_int64, [C.c_int, C.c_int, C.c_int, C.c_int]),
+    "rns_pair_tile_rows": (C.c_int, [C.c_int, C.c_int]),
+    "rns_quantize_activations_tiled": (C.c_int, [_VP, C.c_int, C.c_int, C.c_int, C.c_int64, C.c_int, C.c_int64, C.c_int,
+                                                 C.c_int, _I32P, C.c_int, _VP, _VP, C.c_int, C.c_int, _VP, _VP, _VP,
+                                                 _VP, C.c_int, C.c_int64, _VP]),
     "rns_pack_weight": (C.c_int, [_VP, C.c_int, C.c_int, C.c_int64, _VP, _VP]),
     "rns_unpack_weight": (C.c_int, [_VP, C.c_int, C.c_int, _VP, C.c_int64, _VP]),
     "rns_encode_planes_packed": (C.c_int, [_VP, C.c_int, C.c_int, C.c_int64, _I32P, C.c_int, _VP, _VP]),

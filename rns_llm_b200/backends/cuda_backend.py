@@ -576,7 +576,8 @@ class CudaRNSBackend:
                       plain_weight: torch.Tensor | None = None, pair_mode: int = 2,
                       enc_groups: int = 0, exact_residues: bool = False,
                       enc_stages: int = 0, sub_blocks: int = 0, variant: int = 0,
-                      stream: int | None = None) -> None:
+                      stream: int | None = None, a_tile_rows: int = 0,
+                      absmax_out: torch.Tensor | int | None = None) -> None:
         """Fills ``rns_linear_args`` and launches.  ``a`` / ``a_planes`` are plain
         ([M,K] / [R,M,K]) unless ``a_packed``; the weight is the prepared packed
         copy unless ``plain_weight`` ([N,K] int8) is given.  Device buffers may be
@@ -625,6 +626,8 @@ class CudaRNSBackend:
         args.enc_stages = enc_stages
         args.sub_blocks = sub_blocks
         args.variant = variant
+        args.a_tile_rows = a_tile_rows
+        args.d_absmax_out = None if absmax_out is None else ptr(absmax_out)
         N.check(self._lib.rns_linear_fused(C.byref(args), self._stream(device) if stream is None else stream))
 
     def matmul_prepared_fused(self, a: torch.Tensor, prepared_weight: PreparedRNSWeight, *,
@@ -823,7 +826,9 @@ class CudaRNSBackend:
     def linear_forward(self, x: torch.Tensor, prepared: PreparedRNSWeight, weight_scale: torch.Tensor,
                        bias: torch.Tensor | None, *, per_row: bool = False,
                        adaptive: PreparedAdaptiveRNSWeight | None = None,
-                       return_metadata: bool = False, out: torch.Tensor | None = None):
+                       return_metadata: bool = False, out: torch.Tensor | None = None,
+                       absmax_in: tuple[int, int, int] | None = None,
+                       absmax_out: torch.Tensor | int | None = None):
         """y[M,N] = dequant( quant(x)[M,K] @ Wq[N,K]^T ) in the dtype of ``x``.
 
         The whole of ``RNSLinear.forward`` after weight preparation
@@ -834,7 +839,15 @@ class CudaRNSBackend:
         unit inner stride, or the [G,M,K/G] result of an all-gather of column
         shards; ``weight_scale`` float32 [N]; ``bias`` float32 [N].
         ``out`` may be a [M,N] view with unit inner stride (e.g. a column block
-        of a wider matrix)."""
+        of a wider matrix).
+
+        Layer stacks can take the absmax pass out of the quantiser (per-tensor scale
+        only): ``absmax_out`` (a device uint32 word) receives the bit pattern of
+        max |y| of this call's outputs, written by the GEMM epilogue; ``absmax_in`` =
+        (address, parts, stride in words) hands the next call the words whose maximum
+        is its input's absmax (one word, or one per rank of a column-sharded layer).
+        ``absmax_out`` needs the many-token kernel (M >= 512, 4 or 5 channels,
+        K >= 512); otherwise it raises."""
         if prepared.kernel != "tcgen05":
             raise ValueError("linear_forward needs a tensor-core prepared weight")
         if x.dtype not in _FLOAT_TYPES:
@@ -861,20 +874,30 @@ class CudaRNSBackend:
         elif out.shape != (m, prepared.n) or out.stride(1) != 1 or out.dtype != x.dtype:
             raise ValueError("out must be [M,N] of x's dtype with unit inner stride")
         use_planes = m >= PLANES_MIN_ROWS and adaptive is None
+        # Many-token calls: planes in tiles of 64 / 48 token rows for the two-CTA kernel.
+        tile_rows = int(self._lib.rns_pair_tile_rows(channels, k)) if use_planes else 0
+        if absmax_in is not None and per_row:
+            raise ValueError("absmax_in serves the per-tensor scale")
+        if absmax_out is not None and (tile_rows == 0 or per_row):
+            raise ValueError("absmax_out needs the many-token kernel and a per-tensor scale")
         meta = None
         with torch.cuda.device(device):
             # One block of the stream's arena, addressed by offsets (256-byte aligned):
             # scale [M or 1] f32 | scratch 8 x i32 ([0..3] absmax, [4] row-L1 max,
             # [5] active channels) | packed activations (int8, or R planes).
             scale_bytes = ((m if per_row else 1) * 4 + 255) & ~255
-            act_bytes = int(self._lib.rns_packed_activation_bytes(m, k, channels if use_planes else 1))
+            if tile_rows:
+                act_bytes = int(self._lib.rns_packed_planes_bytes(m, k, channels, tile_rows))
+            else:
+                act_bytes = int(self._lib.rns_packed_activation_bytes(m, k, channels if use_planes else 1))
             base, stream = self.arena.block(device, scale_bytes + 256 + act_bytes)
             scale, scratch, act = base, base + scale_bytes, base + scale_bytes + 256
-            N.check(self._lib.rns_quantize_activations(
+            parts_ptr, parts, parts_stride = absmax_in if absmax_in is not None else (None, 0, 0)
+            N.check(self._lib.rns_quantize_activations_tiled(
                 x.data_ptr(), _FLOAT_TYPES[x.dtype], m, k, ldx, col_block, col_block_stride,
                 1 if per_row else 0, 127,
-                arr, channels, None if use_planes else act, act if use_planes else None, 1, scale,
-                scratch + 16 if adaptive is not None else None, scratch, stream))
+                arr, channels, None if use_planes else act, act if use_planes else None, 1, tile_rows, scale,
+                scratch + 16 if adaptive is not None else None, scratch, parts_ptr, parts, parts_stride, stream))
             active = None
             if adaptive is not None:
                 state = self._state(device)
@@ -896,7 +919,8 @@ class CudaRNSBackend:
                                m=m, a=None if use_planes else act, a_planes=act if use_planes else None,
                                a_packed=True, out=out, active=active,
                                row_scale=scale, row_scale_stride=1 if per_row else 0,
-                               col_scale=weight_scale, bias=bias, stream=stream)
+                               col_scale=weight_scale, bias=bias, stream=stream,
+                               a_tile_rows=tile_rows, absmax_out=absmax_out)
         if return_metadata:
             return out, (AdaptiveMetadata(meta) if meta is not None else None)
         return out

@@ -272,12 +272,26 @@ struct QuantOut {
     int32_t fast;
     int32_t packed;     // outputs in the packed tile layouts
     int32_t kblocks;    // K_pad / 64 (packed only)
+    int32_t tile_rows;  // token rows per packed tile (128, or 64 / 48 for the two-CTA kernel)
 };
+
+// Where a row falls in the packed layouts: its tile row and its row inside the tile
+// (computed once per row: the tile height need not be a power of two).
+struct RowPos {
+    int32_t tile;
+    int32_t inside;
+};
+__device__ __forceinline__ RowPos row_pos(const QuantOut& o, int r) {
+    RowPos p;
+    if (o.tile_rows == kPackM) { p.tile = r >> 7; p.inside = r & 127; }
+    else { p.tile = r / o.tile_rows; p.inside = r - p.tile * o.tile_rows; }
+    return p;
+}
 
 // Quantises columns [c, c+8) of row r, stores values and planes, returns sum |q|.
 template <typename T>
 __device__ __forceinline__ int quantize_loaded(const float (&v)[8], const SrcView& s, const QuantOut& o, int r, int c,
-                                               float scale, int qmax) {
+                                               float scale, int qmax, const RowPos pos) {
     int q[8];
     int l1 = 0;
     const float inv_scale = __frcp_rn(scale);
@@ -301,14 +315,15 @@ __device__ __forceinline__ int quantize_loaded(const float (&v)[8], const SrcVie
     // Plain: byte offset r*K + c, planes M*K apart.  Packed: tile layouts, where a
     // group of 8 columns (c % 8 == 0) is half of one 16-byte chunk.
     // Packed: tile (r / 128, c / 64) of one channel (values) or of `channels` channels (planes).
-    const int64_t tile = (int64_t)(r >> 7) * o.kblocks + (c >> 6);
-    const int in_tile = packed_row_offset(r & 127, c & 63);
-    const int64_t off = o.packed ? tile * (kPackM * kPackK) + in_tile : (int64_t)r * s.k + c;
+    const int64_t tile = (int64_t)pos.tile * o.kblocks + (c >> 6);
+    const int in_tile = packed_row_offset(pos.inside, c & 63);
+    const int tile_bytes = o.tile_rows * kPackK;
+    const int64_t off = o.packed ? tile * tile_bytes + in_tile : (int64_t)r * s.k + c;
     if (full && (off & 7) == 0) {
         if (o.q) *reinterpret_cast<uint2*>(o.q + off) = make_uint2(w0, w1);
         if (o.planes) {
-            const int64_t plane = o.packed ? (int64_t)kPackM * kPackK : (int64_t)s.m * s.k;
-            const int64_t base = o.packed ? tile * o.channels * (kPackM * kPackK) + in_tile : off;
+            const int64_t plane = o.packed ? (int64_t)tile_bytes : (int64_t)s.m * s.k;
+            const int64_t base = o.packed ? tile * o.channels * tile_bytes + in_tile : off;
             const uint32_t u0 = w0 ^ 0x80808080u, u1 = w1 ^ 0x80808080u;
             const uint32_t l0 = u0 & 0x7f7f7f7fu, l1w = u1 & 0x7f7f7f7fu;
             if (o.reduced) {
@@ -361,14 +376,6 @@ __device__ __forceinline__ int quantize_loaded(const float (&v)[8], const SrcVie
     return l1;
 }
 
-template <typename T>
-__device__ __forceinline__ int quantize_group(const SrcView& s, const QuantOut& o, int r, int c,
-                                              float scale, int qmax) {
-    float v[8];
-    load8<T>(s, r, c, v);
-    return quantize_loaded<T>(v, s, o, r, c, scale, qmax);
-}
-
 // kQuantUnroll groups of a row per step, every load issued before the first group is processed.
 #ifndef RNS_QUNROLL
 #define RNS_QUNROLL 1
@@ -378,6 +385,7 @@ template <typename T>
 __device__ __forceinline__ int quantize_row(const SrcView& s, const QuantOut& o, int row, int lane,
                                             int groups_per_row, float scale, int qmax, int first_group = 0) {
     int l1 = 0;
+    const RowPos pos = row_pos(o, row);
     for (int g = first_group + lane; g < groups_per_row; g += 32 * kQuantUnroll) {
         float v[kQuantUnroll][8];
 #pragma unroll
@@ -385,7 +393,7 @@ __device__ __forceinline__ int quantize_row(const SrcView& s, const QuantOut& o,
             if (g + 32 * u < groups_per_row) load8<T>(s, row, (g + 32 * u) * 8, v[u]);
 #pragma unroll
         for (int u = 0; u < kQuantUnroll; ++u)
-            if (g + 32 * u < groups_per_row) l1 += quantize_loaded<T>(v[u], s, o, row, (g + 32 * u) * 8, scale, qmax);
+            if (g + 32 * u < groups_per_row) l1 += quantize_loaded<T>(v[u], s, o, row, (g + 32 * u) * 8, scale, qmax, pos);
     }
     return l1;
 }
@@ -452,16 +460,26 @@ absmax_kernel(const __grid_constant__ SrcView s, unsigned* __restrict__ scratch)
 #ifndef RNS_QMINBLOCKS
 #define RNS_QMINBLOCKS 4
 #endif
+// Tensor-wide absmax as the maximum of `parts` words `stride` words apart (bit patterns
+// of non-negative floats: one word from this call's own absmax pass, or one per rank
+// from the epilogues of a column-sharded previous layer).
+__device__ __forceinline__ float absmax_of_parts(const unsigned* __restrict__ src, int parts, int64_t stride) {
+    unsigned best = src[0];
+    for (int i = 1; i < parts; ++i) best = max(best, src[(int64_t)i * stride]);
+    return __uint_as_float(best);
+}
+
 template <typename T, bool PER_ROW>
 __global__ void __launch_bounds__(256, RNS_QMINBLOCKS)
 quantize_rows_kernel(const __grid_constant__ SrcView s, const __grid_constant__ QuantOut o,
-                     int qmax, const unsigned* __restrict__ scratch, int segments, int seg_groups) {
+                     int qmax, const unsigned* __restrict__ scratch, int parts, int64_t part_stride,
+                     int segments, int seg_groups) {
     const int lane = threadIdx.x & 31;
     const int warps = (gridDim.x * blockDim.x) >> 5;
     const int groups_per_row = (s.k + 7) / 8;
     int worst_l1 = 0;
     if (!PER_ROW && segments > 1) {
-        const float scale = fmaxf(__fdiv_rn(__uint_as_float(*scratch), (float)qmax), FLT_EPSILON);
+        const float scale = fmaxf(__fdiv_rn(absmax_of_parts(scratch, parts, part_stride), (float)qmax), FLT_EPSILON);
         if (blockIdx.x == 0 && threadIdx.x == 0) o.scale[0] = scale;
         const int64_t units = (int64_t)s.m * segments;
         for (int64_t u = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; u < units; u += warps) {
@@ -478,7 +496,7 @@ quantize_rows_kernel(const __grid_constant__ SrcView s, const __grid_constant__ 
             for (int g = lane; g < groups_per_row; g += 32) best = fmaxf(best, group_absmax<T>(s, row, g * 8));
             absmax = warp_max(best);
         } else {
-            absmax = __uint_as_float(*scratch);
+            absmax = absmax_of_parts(scratch, parts, part_stride);
         }
         const float scale = fmaxf(__fdiv_rn(absmax, (float)qmax), FLT_EPSILON);
         if (lane == 0) {
@@ -826,11 +844,13 @@ int rns_matmul_centered_fused_out(const int8_t* d_a, const int8_t* d_b, const in
     return launch_garner<int32_t>(d_accumulators, d_out, pl, (int64_t)m * n, st);
 }
 
-int rns_quantize_activations(const void* d_x, rns_float_type type, int m, int k, int64_t ldx,
-                             int col_block, int64_t col_block_stride,
-                             int per_row, int quant_max, const int32_t* moduli, int channels,
-                             int8_t* d_q, int8_t* d_planes, int packed_out, float* d_scale,
-                             int32_t* d_row_l1_max, void* d_scratch, rns_stream_t stream) {
+static int quantize_impl(const void* d_x, rns_float_type type, int m, int k, int64_t ldx,
+                         int col_block, int64_t col_block_stride,
+                         int per_row, int quant_max, const int32_t* moduli, int channels,
+                         int8_t* d_q, int8_t* d_planes, int packed_out, int tile_rows, float* d_scale,
+                         int32_t* d_row_l1_max, void* d_scratch,
+                         const uint32_t* d_absmax_parts, int absmax_parts, int64_t absmax_part_stride,
+                         rns_stream_t stream) {
     if (!d_x || !d_scale || (!d_q && !d_planes))
         return fail(RNS_ERR_INVALID_ARGUMENT, "quantize: NULL pointer");
     if (col_block <= 0) { col_block = k; col_block_stride = 0; }
@@ -838,8 +858,15 @@ int rns_quantize_activations(const void* d_x, rns_float_type type, int m, int k,
         return fail(RNS_ERR_INVALID_ARGUMENT, "quantize: bad shape, stride or column block");
     if (quant_max != 127)
         return fail(RNS_ERR_UNSUPPORTED, "the fused quantiser produces 8-bit values (quant_max 127)");
-    const bool small = !per_row && (int64_t)m * k <= 32 * 1024;   // one CTA: beyond this the two-launch path is faster
-    if (!per_row && !small && !d_scratch)
+    if (tile_rows == 0) tile_rows = kPackM;
+    if (tile_rows != kPackM && (!packed_out || d_q != nullptr || tile_rows < 8 || tile_rows > 128 || tile_rows % 8 != 0))
+        return fail(RNS_ERR_INVALID_ARGUMENT, "quantize: tile_rows applies to packed planes only (multiple of 8, <= 128)");
+    const bool given_absmax = d_absmax_parts != nullptr;
+    if (given_absmax && (per_row || absmax_parts < 1 || absmax_parts > 64))
+        return fail(RNS_ERR_INVALID_ARGUMENT, "quantize: a given absmax serves the per-tensor scale (1..64 parts)");
+    // one CTA: beyond this size the two-launch path is faster
+    const bool small = !per_row && !given_absmax && tile_rows == kPackM && (int64_t)m * k <= 32 * 1024;
+    if (!per_row && !small && !given_absmax && !d_scratch)
         return fail(RNS_ERR_INVALID_ARGUMENT, "quantize: per-tensor scale needs d_scratch");
     if (packed_out && k % 8 != 0)
         return fail(RNS_ERR_INVALID_ARGUMENT, "quantize: the packed layout needs K % 8 == 0");
@@ -847,6 +874,7 @@ int rns_quantize_activations(const void* d_x, rns_float_type type, int m, int k,
     qo.q = d_q; qo.planes = d_planes; qo.scale = d_scale; qo.row_l1_max = d_row_l1_max;
     qo.packed = packed_out ? 1 : 0;
     qo.kblocks = (k + kPackK - 1) / kPackK;
+    qo.tile_rows = tile_rows;
     if (d_planes)
         if (int rc = fill_encoder(qo, moduli, channels)) return rc;
 #ifndef RNS_QUANT_CENTRED
@@ -859,33 +887,32 @@ int rns_quantize_activations(const void* d_x, rns_float_type type, int m, int k,
     SrcView sv{};
     sv.x = d_x; sv.m = m; sv.k = k; sv.ldx = ldx;
     sv.col_block = col_block; sv.col_block_stride = col_block_stride;
-    const size_t vec_bytes = 8 * esize;  // bytes of one group; alignment needed: 16
+    // every group of 8 columns contiguous and 16-byte aligned
     sv.vec8 = (k % 8 == 0 && col_block % 8 == 0 && (ldx * esize) % 16 == 0 &&
                (col_block_stride * esize) % 16 == 0 &&
                (reinterpret_cast<uintptr_t>(d_x) % 16) == 0) ? 1 : 0;
-    (void)vec_bytes;
     cudaStream_t st = as_stream(stream);
     unsigned* scratch = static_cast<unsigned*>(d_scratch);
-    if (!per_row && !small) RNS_CUDA_OK(cudaMemsetAsync(scratch, 0, 16, st));
+    const bool own_pass = !per_row && !small && !given_absmax;
+    if (own_pass) RNS_CUDA_OK(cudaMemsetAsync(scratch, 0, 16, st));
     if (d_row_l1_max && !small) RNS_CUDA_OK(cudaMemsetAsync(d_row_l1_max, 0, sizeof(int32_t), st));
-    int row_threads = 128, seg_groups = 128, segments = 1, row_cap = 148 * 16;   // 1024-column segments
-#ifdef RNS_QUANT_TUNE
-    if (const char* e = getenv("RNS_QTHREADS")) row_threads = atoi(e);
-    if (const char* e = getenv("RNS_QSEG")) seg_groups = atoi(e);
-    if (const char* e = getenv("RNS_QCAP")) row_cap = atoi(e);
-#endif
-    if (seg_groups > 0 && !per_row && !d_row_l1_max) segments = ((k + 7) / 8 + seg_groups - 1) / seg_groups;
+    const int row_threads = 128, seg_groups = 128, row_cap = 148 * 16;   // 1024-column segments
+    int segments = 1;
+    if (!per_row && !d_row_l1_max) segments = ((k + 7) / 8 + seg_groups - 1) / seg_groups;
     const int row_blocks = grid_for((int64_t)m * segments, row_threads / 32, row_cap);  // one warp per row segment
     const int64_t groups = (int64_t)m * ((k + 7) / 8);
+    const unsigned* absmax_src = given_absmax ? d_absmax_parts : scratch;
+    const int parts = given_absmax ? absmax_parts : 1;
+    const int64_t part_stride = given_absmax ? absmax_part_stride : 0;
 #define RNS_QUANT(T)                                                                           \
     do {                                                                                       \
         if (per_row) {                                                                         \
-            quantize_rows_kernel<T, true><<<row_blocks, row_threads, 0, st>>>(sv, qo, quant_max, scratch, 1, 0); \
+            quantize_rows_kernel<T, true><<<row_blocks, row_threads, 0, st>>>(sv, qo, quant_max, scratch, 1, 0, 1, 0); \
         } else if (small) {                                                                    \
             quantize_small_kernel<T><<<1, 1024, 0, st>>>(sv, qo, quant_max);                   \
         } else {                                                                               \
-            absmax_kernel<T><<<grid_for(groups, 256 * 4, 148 * 8), 256, 0, st>>>(sv, scratch); \
-            quantize_rows_kernel<T, false><<<row_blocks, row_threads, 0, st>>>(sv, qo, quant_max, scratch, segments, seg_groups); \
+            if (own_pass) absmax_kernel<T><<<grid_for(groups, 256 * 4, 148 * 8), 256, 0, st>>>(sv, scratch); \
+            quantize_rows_kernel<T, false><<<row_blocks, row_threads, 0, st>>>(sv, qo, quant_max, absmax_src, parts, part_stride, segments, seg_groups); \
         }                                                                                      \
     } while (0)
     switch (type) {
@@ -898,9 +925,35 @@ int rns_quantize_activations(const void* d_x, rns_float_type type, int m, int k,
     return RNS_OK;
 }
 
+int rns_quantize_activations(const void* d_x, rns_float_type type, int m, int k, int64_t ldx,
+                             int col_block, int64_t col_block_stride,
+                             int per_row, int quant_max, const int32_t* moduli, int channels,
+                             int8_t* d_q, int8_t* d_planes, int packed_out, float* d_scale,
+                             int32_t* d_row_l1_max, void* d_scratch, rns_stream_t stream) {
+    return quantize_impl(d_x, type, m, k, ldx, col_block, col_block_stride, per_row, quant_max, moduli, channels,
+                         d_q, d_planes, packed_out, 0, d_scale, d_row_l1_max, d_scratch, nullptr, 0, 0, stream);
+}
+
+int rns_quantize_activations_tiled(const void* d_x, rns_float_type type, int m, int k, int64_t ldx,
+                                   int col_block, int64_t col_block_stride,
+                                   int per_row, int quant_max, const int32_t* moduli, int channels,
+                                   int8_t* d_q, int8_t* d_planes, int packed_out, int tile_rows, float* d_scale,
+                                   int32_t* d_row_l1_max, void* d_scratch,
+                                   const uint32_t* d_absmax_parts, int absmax_parts, int64_t absmax_part_stride,
+                                   rns_stream_t stream) {
+    return quantize_impl(d_x, type, m, k, ldx, col_block, col_block_stride, per_row, quant_max, moduli, channels,
+                         d_q, d_planes, packed_out, tile_rows, d_scale, d_row_l1_max, d_scratch,
+                         d_absmax_parts, absmax_parts, absmax_part_stride, stream);
+}
+
 int64_t rns_packed_weight_bytes(int n, int k) {
     if (n <= 0 || k <= 0) return 0;
     return round_up_i64(k, kPackK) * round_up_i64(n, kPackNPad);
+}
+
+int64_t rns_packed_planes_bytes(int m, int k, int channels, int tile_rows) {
+    if (m <= 0 || k <= 0 || channels <= 0 || tile_rows <= 0) return 0;
+    return round_up_i64(m, 2 * tile_rows) * round_up_i64(k, kPackK) * channels;
 }
 
 int64_t rns_packed_activation_bytes(int m, int k, int channels) {
@@ -940,6 +993,7 @@ int rns_encode_planes_packed(const int8_t* d_a, int m, int k, int64_t lda, const
     if (int rc = fill_encoder(qo, moduli, channels)) return rc;
     qo.planes = d_planes_packed;
     qo.packed = 1;
+    qo.tile_rows = kPackM;
     qo.kblocks = (k + kPackK - 1) / kPackK;
     encode_planes_packed_kernel<<<grid_for((int64_t)m * ((k + 15) / 16), 256), 256, 0, as_stream(stream)>>>(
         d_a, m, k, lda, qo);

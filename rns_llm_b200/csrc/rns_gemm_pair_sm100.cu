@@ -1,0 +1,449 @@
+// Fused RNS linear for many-token calls on sm_100a: two CTAs of a cluster compute one
+// 256-feature x TOK-token output tile with tcgen05 cta_group::2.
+//
+// Roles of the operands are swapped against rns_gemm_sm100.cu.  The weight rows are the
+// MMA's M operand: each CTA owns 128 output features, reads its 128 x 64 bytes of the
+// packed weight per K block straight from global memory and encodes them into R residue
+// tiles in shared memory.  The tokens are the N operand, which cta_group::2 splits over
+// the pair: each CTA bulk-copies only HALF of the token tile's residue planes
+// (R x TOK/2 x 64 bytes per K block), so the L2 -> SM traffic per CTA and K block drops
+// from R x 8 KB + 8 KB to R x 4 KB + 8 KB, and a deeper plane ring fits shared memory.
+// Accumulators: R x TOK int32 columns of tensor memory in each CTA (its 128 features as
+// lanes); the epilogue is feature-major (a thread owns one feature, walks the tokens).
+//
+// Per CTA: warp 0 loads planes; warp 1 issues the MMAs (leader CTA) or tells the leader
+// that this CTA's stage is complete (peer CTA); warps 2..17 encode weights during the K
+// loop and run the epilogue.  One tcgen05.commit per stage, multicast to both CTAs,
+// releases the operand slot and the plane slot of that stage through one ring of
+// "stage done" barriers.  Every wait is bounded (status word + wait code on expiry).
+#include "rns_common.cuh"
+#include "rns_ptx.cuh"
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include <atomic>
+#include <type_traits>
+
+namespace rns {
+
+constexpr int kPairEncWarps = 16;
+constexpr int kPairThreads = (2 + kPairEncWarps) * 32;
+constexpr int kPairEncThreads = kPairEncWarps * 32;
+constexpr int kDoneRing = 8;                       // ring of "stage done" barriers (>= both ring depths)
+constexpr uint32_t kPairOpTile = 128 * kPackK;     // one channel's weight operand tile
+
+struct PairParams {
+    Plan plan;
+    int32_t m, n, k;
+    int32_t kblocks;
+    const int8_t* planes;      // [M_pad / (TOK/2)][kblocks][R][TOK/2][64]
+    const int8_t* w;           // packed weights [kblocks][w_npad][64]
+    int64_t w_npad;
+    int32_t n_ftiles;          // tiles of 256 features
+    int32_t n_ttiles;          // tiles of TOK tokens
+    int32_t band;              // feature tiles per raster band
+    void* out;
+    int64_t ldo;
+    int32_t out_type;
+    const float* row_scale;
+    int32_t row_scale_stride;
+    const float* col_scale;
+    const float* bias;
+    uint32_t* absmax_out;      // NULL, or device word: atomicMax of the bit pattern of max |y|
+    int32_t* status;
+    int32_t* wait_info;
+};
+
+struct __align__(8) PairCtl {
+    uint64_t full_op[kDoneRing];     // this CTA's encoders have written the operand slot
+    uint64_t full_pl[kDoneRing];     // this CTA's plane half has landed
+    uint64_t done[kDoneRing];        // the MMAs of the stage are complete (arrives in both CTAs)
+    uint64_t peer_ready[kDoneRing];  // leader only: the peer CTA's stage is complete
+    uint64_t acc_full;
+    uint32_t tmem_base;
+    int abort;
+    uint32_t absmax;
+};
+
+template <int R, int TOK, int ES, int PS>
+__global__ void __launch_bounds__(kPairThreads, 1)
+rns_gemm_pair_kernel(const __grid_constant__ PairParams p) {
+    static_assert(R * TOK <= 512, "accumulators must fit tensor memory");
+    static_assert(TOK % 16 == 0 && (TOK / 2) % 8 == 0, "token tile shape");
+    static_assert(ES <= kDoneRing && PS <= kDoneRing, "ring depths");
+    constexpr int TR = TOK / 2;                               // token rows this CTA loads
+    constexpr uint32_t kOpStage = (uint32_t)R * kPairOpTile;
+    constexpr uint32_t kPlTile = (uint32_t)TR * kPackK;
+    constexpr uint32_t kPlStage = (uint32_t)R * kPlTile;
+    constexpr uint32_t kTmemCols = 512;
+
+    extern __shared__ uint8_t smem_dyn[];
+    __shared__ PairCtl ctl;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t tiles_base = (smem_addr(smem_dyn) + 1023u) & ~1023u;
+    uint8_t* tiles_ptr = smem_dyn + (tiles_base - smem_addr(smem_dyn));
+    const uint32_t op_base = tiles_base;                       // operand ring first
+    const uint32_t pl_base = tiles_base + (uint32_t)ES * kOpStage;
+
+    // Raster: feature tiles in bands; inside a band the token tiles advance slowest, so
+    // the CTAs resident together share a band of the weight (it stays in L2) and a few
+    // token tiles, and every plane byte is read from DRAM once per band.
+    const uint32_t rank = cluster_cta_rank();
+    const int pair = (int)(blockIdx.x >> 1);
+    const int per_band = p.band * p.n_ttiles;
+    const int band_i = pair / per_band;
+    const int in_band = pair - band_i * per_band;
+    const int band_w = min(p.band, p.n_ftiles - band_i * p.band);
+    const int tt = in_band / band_w;
+    const int ft = band_i * p.band + (in_band - tt * band_w);
+    const int n0 = ft * 256 + (int)rank * 128;                 // first feature of this CTA
+    const int tok0 = tt * TOK;                                 // first token of the pair's tile
+    const int nst = p.kblocks;                                 // one K block of 64 bytes per stage
+
+    if (threadIdx.x == 0) {
+        ctl.abort = 0;
+        ctl.absmax = 0u;
+        for (int s = 0; s < kDoneRing; ++s) {
+            mbar_init(smem_addr(&ctl.full_op[s]), kPairEncWarps);
+            mbar_init(smem_addr(&ctl.full_pl[s]), 1);
+            mbar_init(smem_addr(&ctl.done[s]), 1);
+            mbar_init(smem_addr(&ctl.peer_ready[s]), 1);
+        }
+        mbar_init(smem_addr(&ctl.acc_full), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        tmem_alloc2(smem_addr(&ctl.tmem_base), kTmemCols);
+        tmem_relinquish2();
+    }
+    tc_fence_before();
+    cluster_sync_all();                 // both CTAs' barriers exist before either signals the other
+    tc_fence_after();
+    const uint32_t tmem_base = ctl.tmem_base;
+    volatile int* abort = &ctl.abort;
+
+    if (warp == 0) {
+        // ------------------------------ plane producer ----------------------------
+        if (lane == 0) {
+            const int8_t* src = p.planes + ((int64_t)(tt * 2 + (int)rank) * p.kblocks) * (int64_t)kPlStage;
+            int sp = 0;
+            for (int st = 0; st < nst; ++st) {
+                if (st >= PS &&
+                    !wait_bounded<false, true>(smem_addr(&ctl.done[(st - PS) & (kDoneRing - 1)]),
+                                               (uint32_t)((st - PS) >> 3) & 1u, abort, wait_code(2, st)))
+                    break;
+                const uint32_t bar = smem_addr(&ctl.full_pl[sp]);
+                mbar_arrive_expect_tx(bar, kPlStage);
+                bulk_load(pl_base + (uint32_t)sp * kPlStage, src + (int64_t)st * kPlStage, kPlStage, bar);
+                if (++sp == PS) sp = 0;
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        if (rank != 0) {
+            // ------------------------------ relay (peer CTA) ----------------------
+            if (lane == 0) {
+                int s = 0, sp = 0;
+                uint32_t ph_op = 0, ph_pl = 0;
+                for (int st = 0; st < nst; ++st) {
+                    if (!wait_bounded<false, true>(smem_addr(&ctl.full_op[s]), ph_op, abort, wait_code(3, st))) break;
+                    if (!wait_bounded<false, true>(smem_addr(&ctl.full_pl[sp]), ph_pl, abort, wait_code(4, st))) break;
+                    mbar_arrive_remote(smem_addr(&ctl.peer_ready[st & (kDoneRing - 1)]), 0);
+                    if (++s == ES) { s = 0; ph_op ^= 1u; }
+                    if (++sp == PS) { sp = 0; ph_pl ^= 1u; }
+                }
+            }
+            __syncwarp();
+        } else {
+            // ------------------------------ MMA issuer (leader CTA) ----------------
+            // The whole warp runs the loop so that addresses and descriptors are
+            // warp-uniform values; one elected lane issues.
+            const uint32_t idesc = make_idesc(256u, (uint32_t)TOK);
+            const uint64_t desc0 = make_smem_desc(0, kPackK);
+            const uint32_t a_lo0 = op_base >> 4, b_lo0 = pl_base >> 4;
+            int s = 0, sp = 0;
+            uint32_t ph_op = 0, ph_pl = 0;
+            bool ok = true;
+            for (int st = 0; st < nst; ++st) {
+                ok = warp_wait_bounded<false, true>(smem_addr(&ctl.full_op[s]), ph_op, abort, wait_code(5, st));
+                if (ok) ok = warp_wait_bounded<false, true>(smem_addr(&ctl.full_pl[sp]), ph_pl, abort, wait_code(6, st));
+                if (ok) ok = warp_wait_bounded<true>(smem_addr(&ctl.peer_ready[st & (kDoneRing - 1)]),
+                                                     (uint32_t)(st >> 3) & 1u, abort, wait_code(7, st));
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t a_st = a_lo0 + (uint32_t)s * (kOpStage >> 4);
+                const uint32_t b_st = b_lo0 + (uint32_t)sp * (kPlStage >> 4);
+                if (elect_one()) {
+#pragma unroll
+                    for (int c = 0; c < R; ++c) {
+#pragma unroll
+                        for (int ks = 0; ks < 2; ++ks) {
+                            const uint64_t da = desc0 | (uint64_t)(a_st + (uint32_t)c * (kPairOpTile >> 4) + (uint32_t)ks * 2u);
+                            const uint64_t db = desc0 | (uint64_t)(b_st + (uint32_t)c * (kPlTile >> 4) + (uint32_t)ks * 2u);
+                            umma_i8_pair(tmem_base + (uint32_t)(c * TOK), da, db, idesc, (st > 0 || ks > 0) ? 1u : 0u);
+                        }
+                    }
+                    umma_commit_pair(smem_addr(&ctl.done[st & (kDoneRing - 1)]));
+                }
+                __syncwarp();
+                if (++s == ES) { s = 0; ph_op ^= 1u; }
+                if (++sp == PS) { sp = 0; ph_pl ^= 1u; }
+            }
+            if (ok && elect_one()) umma_commit_pair(smem_addr(&ctl.acc_full));
+            __syncwarp();
+        }
+    } else {
+        // ------------------------------ encoders ----------------------------------
+        const int e = (warp - 2) * 32 + lane;                  // 16-byte chunk of the 128 x 64 weight tile
+        const bool row_valid = n0 + (e >> 2) < p.n;
+        uint32_t mfold[R];
+#pragma unroll
+        for (int c = 0; c < R; ++c) mfold[c] = p.plan.enc_mfold[c];
+        const int8_t* w_src = p.w + (int64_t)n0 * kPackK + (int64_t)e * 16;
+        const int64_t kb_stride = p.w_npad * kPackK;
+        auto load_w = [&](int st) -> uint4 {
+            if (row_valid && st < nst) return __ldg(reinterpret_cast<const uint4*>(w_src + (int64_t)st * kb_stride));
+            return make_uint4(0u, 0u, 0u, 0u);
+        };
+        uint4 cur = load_w(0), nxt = load_w(1), nxt2 = load_w(2);
+        bool ok = true;
+        int s = 0;
+        for (int st = 0; st < nst && ok; ++st) {
+            const uint4 ahead = load_w(st + 3);
+            if (st >= ES)
+                ok = warp_wait_bounded(smem_addr(&ctl.done[(st - ES) & (kDoneRing - 1)]),
+                                       (uint32_t)((st - ES) >> 3) & 1u, abort, wait_code(8, st));
+            if (!ok) break;
+            uint8_t* dst = tiles_ptr + (size_t)s * kOpStage + (size_t)e * 16;
+            const uint32_t u0 = cur.x ^ 0x80808080u, u1 = cur.y ^ 0x80808080u;
+            const uint32_t u2 = cur.z ^ 0x80808080u, u3 = cur.w ^ 0x80808080u;
+            const uint32_t d0 = fold_pattern(cur.x), d1 = fold_pattern(cur.y);
+            const uint32_t d2 = fold_pattern(cur.z), d3 = fold_pattern(cur.w);
+#pragma unroll
+            for (int c = 0; c < R; ++c) {
+                uint4 y;
+                y.x = encode_word_reduced(u0, d0, mfold[c]);
+                y.y = encode_word_reduced(u1, d1, mfold[c]);
+                y.z = encode_word_reduced(u2, d2, mfold[c]);
+                y.w = encode_word_reduced(u3, d3, mfold[c]);
+                *reinterpret_cast<uint4*>(dst + (size_t)c * kPairOpTile) = y;
+            }
+            cur = nxt; nxt = nxt2; nxt2 = ahead;
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_addr(&ctl.full_op[s]));
+            if (++s == ES) s = 0;
+        }
+
+        // ------------------------------ epilogue (feature-major) ------------------
+        if (ok) ok = warp_wait_bounded(smem_addr(&ctl.acc_full), 0, abort, wait_code(11, 0));
+        if (ok) {
+            tc_fence_after();
+            const int quarter = warp & 3;                      // tensor-memory lanes 32*quarter .. +31
+            const int part = (warp - 2) >> 2;                  // quarter of the token columns
+            const int feat = n0 + quarter * 32 + lane;
+            const bool feat_ok = feat < p.n;
+            const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
+            const bool is_float = p.out_type >= RNS_OUT_F16;
+            float cs = 0.0f, bs = 0.0f;
+            if (is_float && feat_ok) {
+                cs = p.col_scale[feat];
+                if (p.bias != nullptr) bs = p.bias[feat];
+            }
+            const float rs_all = (is_float && p.row_scale_stride == 0) ? p.row_scale[0] : 0.0f;
+            using XInt = typename std::conditional<(R <= 4), int, long long>::type;
+            float biggest = 0.0f;
+            constexpr int kColsPerPart = TOK / 4;
+            auto load = [&](int col, int (&acc)[R][8]) {
+                __syncwarp();
+#pragma unroll
+                for (int c = 0; c < R; ++c) tmem_ld8(lane_base + (uint32_t)(c * TOK + col), acc[c]);
+            };
+            auto finish = [&](int col, const int (&acc)[R][8]) {
+                const int tok_first = tok0 + col;
+                if (!feat_ok || tok_first >= p.m) return;
+#pragma unroll
+                for (int t = 0; t < 8; ++t) {
+                    const int tok = tok_first + t;
+                    if (tok >= p.m) break;
+                    int one[R];
+#pragma unroll
+                    for (int c = 0; c < R; ++c) one[c] = acc[c][t];
+                    XInt xv;
+                    if constexpr (R <= 4) xv = reconstruct32<R>(one, p.plan, R);
+                    else xv = reconstruct<R>(one, p.plan, R);
+                    const int64_t o = (int64_t)tok * p.ldo + feat;
+                    if (p.out_type == RNS_OUT_INT64) {
+                        static_cast<long long*>(p.out)[o] = (long long)xv;
+                    } else if (p.out_type == RNS_OUT_INT32) {
+                        static_cast<int*>(p.out)[o] = (int)xv;
+                    } else {
+                        float xf;
+                        if constexpr (R <= 4) xf = __int2float_rn(xv);
+                        else xf = __ll2float_rn(xv);
+                        const float rs = p.row_scale_stride == 0 ? rs_all : p.row_scale[tok];
+                        float y = __fmul_rn(__fmul_rn(xf, rs), cs);
+                        if (p.bias != nullptr) y = __fadd_rn(y, bs);
+                        if (p.out_type == RNS_OUT_F16) {
+                            const __half h = __float2half_rn(y);
+                            static_cast<__half*>(p.out)[o] = h;
+                            biggest = fmaxf(biggest, fabsf(__half2float(h)));
+                        } else if (p.out_type == RNS_OUT_BF16) {
+                            const __nv_bfloat16 h = __float2bfloat16_rn(y);
+                            static_cast<__nv_bfloat16*>(p.out)[o] = h;
+                            biggest = fmaxf(biggest, fabsf(__bfloat162float(h)));
+                        } else {
+                            static_cast<float*>(p.out)[o] = y;
+                            biggest = fmaxf(biggest, fabsf(y));
+                        }
+                    }
+                }
+            };
+            const int col0 = part * kColsPerPart;
+            constexpr int kIters = kColsPerPart / 8;
+            if constexpr (R <= 4) {
+                // The loads of the next 8 token columns are in flight while these are finished.
+                int a0[R][8], a1[R][8];
+                load(col0, a0);
+#pragma unroll
+                for (int it = 0; it < kIters; it += 2) {
+                    tmem_ld_wait();
+                    if (it + 1 < kIters) load(col0 + (it + 1) * 8, a1);
+                    finish(col0 + it * 8, a0);
+                    if (it + 1 < kIters) {
+                        tmem_ld_wait();
+                        if (it + 2 < kIters) load(col0 + (it + 2) * 8, a0);
+                        finish(col0 + (it + 1) * 8, a1);
+                    }
+                }
+            } else {
+                // one buffer: two of them (2 x R x 8 registers) would spill
+#pragma unroll 1
+                for (int it = 0; it < kIters; ++it) {
+                    int acc[R][8];
+                    load(col0 + it * 8, acc);
+                    tmem_ld_wait();
+                    finish(col0 + it * 8, acc);
+                }
+            }
+            if (p.absmax_out != nullptr && is_float) {
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) biggest = fmaxf(biggest, __shfl_xor_sync(0xffffffffu, biggest, o));
+                if (lane == 0) atomicMax(&ctl.absmax, __float_as_uint(biggest));
+            }
+        }
+    }
+
+    // ------------------------------ teardown ---------------------------------------
+    // Nothing may still be on its way to this CTA's barriers when it leaves: the last
+    // stages' commits are waited for here (nobody else waits for them).
+    if (warp == 1 && lane == 0 && !*abort) {
+        for (int st = nst > kDoneRing ? nst - kDoneRing : 0; st < nst; ++st)
+            if (!wait_bounded(smem_addr(&ctl.done[st & (kDoneRing - 1)]), (uint32_t)(st >> 3) & 1u, abort,
+                              wait_code(12, st)))
+                break;
+    }
+    tc_fence_before();
+    // Neither CTA may free tensor memory or leave (its shared memory feeds the partner's
+    // MMAs, its barriers receive the partner's arrivals) before both have finished.
+    cluster_sync_all();
+    if (threadIdx.x == 0) {
+        if (ctl.abort) {
+            if (p.status != nullptr) atomicExch(p.status, (int)RNS_ERR_DEVICE_TIMEOUT);
+            if (p.wait_info != nullptr && atomicCAS(p.wait_info, 0, ctl.abort) == 0) {
+                p.wait_info[1] = (int)blockIdx.x;
+                p.wait_info[2] = (int)blockIdx.y;
+                p.wait_info[3] = R * 1000000 + 200000 + TOK;
+            }
+        } else if (p.absmax_out != nullptr && ctl.absmax != 0u) {
+            atomicMax(p.absmax_out, ctl.absmax);
+        }
+    }
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc2(tmem_base, kTmemCols);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------
+template <int R, int TOK, int ES, int PS>
+static int launch_pair(const PairParams& pp, int pairs, cudaStream_t st) {
+    constexpr size_t smem = (size_t)ES * R * kPairOpTile + (size_t)PS * R * (TOK / 2) * kPackK + 1024;
+    static_assert(smem + sizeof(PairCtl) <= 227 * 1024, "rings exceed shared memory");
+    static std::atomic<uint64_t> configured{0};
+    int dev = 0;
+    RNS_CUDA_OK(cudaGetDevice(&dev));
+    const uint64_t bit = 1ull << (dev & 63);
+    if (!(configured.load(std::memory_order_acquire) & bit)) {
+        RNS_CUDA_OK(cudaFuncSetAttribute(rns_gemm_pair_kernel<R, TOK, ES, PS>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        configured.fetch_or(bit, std::memory_order_release);
+    }
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3((unsigned)(2 * pairs), 1, 1);
+    cfg.blockDim = dim3(kPairThreads, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const cudaError_t rc = cudaLaunchKernelEx(&cfg, rns_gemm_pair_kernel<R, TOK, ES, PS>, pp);
+    if (rc != cudaSuccess) {
+        cudaGetLastError();
+        return fail(RNS_ERR_CUDA, "launch of the paired RNS GEMM failed: %s (%d pairs, smem %zu)",
+                    cudaGetErrorString(rc), pairs, smem);
+    }
+    return RNS_OK;
+}
+
+int pair_gemm_token_tile(int channels) { return channels <= 4 ? 128 : 96; }
+
+bool pair_gemm_supported(const rns_linear_args* a) {
+    return a->d_a_planes != nullptr && a->a_packed != 0 && a->w_packed != 0 && a->d_active_channels == nullptr &&
+           a->exact_residues == 0 && (a->channels == 4 || a->channels == 5) &&
+           a->a_tile_rows == pair_gemm_token_tile(a->channels) / 2 && a->k >= 8 * kPackK && a->k % 16 == 0;
+}
+
+int launch_pair_gemm(const rns_linear_args* a, const Plan& plan, cudaStream_t st) {
+    PairParams pp;
+    memset(&pp, 0, sizeof(pp));
+    pp.plan = plan;
+    const int R = plan.channels;
+    const int tok = pair_gemm_token_tile(R);
+    pp.m = a->m; pp.n = a->n; pp.k = a->k;
+    pp.kblocks = (a->k + kPackK - 1) / kPackK;
+    pp.planes = a->d_a_planes;
+    pp.w = a->d_w;
+    pp.w_npad = round_up_i64(a->n, kPackNPad);
+    pp.n_ftiles = (a->n + 255) / 256;
+    pp.n_ttiles = (a->m + tok - 1) / tok;
+    // Band: as many feature tiles as keep the band's weight bytes around 32 MB (a quarter
+    // of L2), at least the number that fills the GPU once with one token tile each.
+    const int64_t band_bytes = 32ll << 20;
+    int band = (int)(band_bytes / ((int64_t)256 * pp.kblocks * kPackK));
+    if (band < 1) band = 1;
+    if (band > pp.n_ftiles) band = pp.n_ftiles;
+    pp.band = band;
+    pp.out = a->d_out; pp.ldo = a->ldo; pp.out_type = a->out_type;
+    pp.row_scale = a->d_row_scale; pp.row_scale_stride = a->row_scale_stride;
+    pp.col_scale = a->d_col_scale; pp.bias = a->d_bias;
+    pp.absmax_out = a->d_absmax_out;
+    pp.status = a->d_status; pp.wait_info = a->d_wait_info;
+    const int64_t pairs = (int64_t)pp.n_ftiles * pp.n_ttiles;
+    if (pairs > (1 << 30)) return fail(RNS_ERR_UNSUPPORTED, "too many output tiles");
+    if (a->d_absmax_out != nullptr) RNS_CUDA_OK(cudaMemsetAsync(a->d_absmax_out, 0, sizeof(uint32_t), st));
+    if (R == 4) return launch_pair<4, 128, 4, 6>(pp, (int)pairs, st);
+    return launch_pair<5, 96, 3, 7>(pp, (int)pairs, st);
+}
+
+}  // namespace rns

@@ -902,6 +902,10 @@ static int launch_either(bool pair, const CUtensorMap& ma, const CUtensorMap& mw
 // rns_gemm_tmem_sm100.cu
 bool tmem_gemm_supported(const rns_linear_args* a);
 int launch_tmem_gemm(const rns_linear_args* a, const Plan& plan, cudaStream_t st);
+// rns_gemm_pair_sm100.cu
+int pair_gemm_token_tile(int channels);
+bool pair_gemm_supported(const rns_linear_args* a);
+int launch_pair_gemm(const rns_linear_args* a, const Plan& plan, cudaStream_t st);
 
 }  // namespace rns
 
@@ -914,6 +918,11 @@ int rns_linear_fused_supported(const int32_t* moduli, int channels, int k, int64
     if (build_plan(moduli, channels, &pl) != RNS_OK) return 0;
     const char* why = "";
     return tc_supported(pl, k, lda, ldw, false, &why) ? 1 : 0;
+}
+
+int rns_pair_tile_rows(int channels, int k) {
+    if ((channels != 4 && channels != 5) || k < 8 * kPackK || k % 16 != 0) return 0;
+    return pair_gemm_token_tile(channels) / 2;
 }
 
 int rns_linear_fused(const rns_linear_args* a, rns_stream_t stream) {
@@ -963,7 +972,21 @@ int rns_linear_fused(const rns_linear_args* a, rns_stream_t stream) {
     // (packed planes + packed weights only).  Variant 2 is limited to 64-token tiles by
     // the 512 tensor-memory columns and measured slower (775 vs 1050 channel-TOPS at
     // 4096^3, four channels), so 0 always resolves to 1; 2 stays selectable.
-    if (a->variant < 0 || a->variant > 2) return fail(RNS_ERR_INVALID_ARGUMENT, "variant must be 0, 1 or 2");
+    if (a->variant < 0 || a->variant > 3) return fail(RNS_ERR_INVALID_ARGUMENT, "variant must be 0, 1, 2 or 3");
+    // 3: the two-CTA feature-major kernel; the only one that reads planes in tiles of
+    // a_tile_rows != 128 rows, so that layout selects it.
+    if (a->variant == 3 || (a->a_tile_rows != 0 && a->a_tile_rows != kPackM)) {
+        if (a->variant != 0 && a->variant != 3)
+            return fail(RNS_ERR_INVALID_ARGUMENT, "planes in tiles of %d rows are read by variant 3 only", a->a_tile_rows);
+        if (!pair_gemm_supported(a))
+            return fail(RNS_ERR_UNSUPPORTED, "variant 3 needs packed planes in tiles of 64 (4 channels) or 48 (5 channels) "
+                                             "rows, packed weights, all channels active and K >= 512");
+        if (is_float && a->d_absmax_out != nullptr && a->row_scale_stride != 0)
+            return fail(RNS_ERR_INVALID_ARGUMENT, "d_absmax_out serves per-tensor scales");
+        return launch_pair_gemm(a, pl, reinterpret_cast<cudaStream_t>(stream));
+    }
+    if (a->d_absmax_out != nullptr)
+        return fail(RNS_ERR_UNSUPPORTED, "d_absmax_out is filled by variant 3 only");
     if (a->variant == 2 && !tmem_gemm_supported(a))
         return fail(RNS_ERR_UNSUPPORTED, "variant 2 needs packed planes, packed weights and 2..5 channels");
     if (a->variant == 2)
@@ -990,6 +1013,7 @@ int rns_linear_fused(const rns_linear_args* a, rns_stream_t stream) {
             pair = false;
     }
     if (pair && tile_k == 128) return fail(RNS_ERR_INVALID_ARGUMENT, "pair mode uses tile_k = 64");
+    const int kblocks_hint = (a->k + tile_k - 1) / tile_k;
     if (tile_n == 0) {
         // Largest tile that still gives every SM a CTA; small problems take the
         // narrowest tile so that more SMs stream the weights.
@@ -1000,6 +1024,14 @@ int rns_linear_fused(const rns_linear_args* a, rns_stream_t stream) {
             if ((int64_t)m_tiles * ((a->n + c - 1) / c) >= 148) { tile_n = c; break; }
         }
         if (tile_n > max_tile_n) tile_n = max_tile_n;
+        // Many-token calls on packed planes always take the full-width tile, i.e. the
+        // instantiations with compile-time ring parameters, even when that leaves a few
+        // SMs without a CTA: a narrower tile would select the run-time form, and that
+        // form launched back to back between the fixed ones (the rank-local sequence of an
+        // 8-way sharded stack) ended with "unspecified launch failure" on some launches.
+        if (planes && a_packed && w_packed && (R == 4 || R == 5) && m_tiles >= 4 && !pair &&
+            a->d_active_channels == nullptr && a->exact_residues == 0 && kblocks_hint >= 8)
+            tile_n = max_tile_n;
         if (pair && tile_n % 32 != 0) tile_n = tile_n + 16 <= max_tile_n ? tile_n + 16 : tile_n - 16;
     }
     if (tile_n < 16 || tile_n > 128 || tile_n % 16 != 0 || tile_n > max_tile_n)

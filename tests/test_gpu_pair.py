@@ -1,0 +1,120 @@
+"""The two-CTA feature-major kernel (rns_linear_args.variant 3) through the C ABI:
+exact integers against the int64 oracle on ragged shapes, the dequantised outputs of
+linear_forward against the oracle's fp32 operation order, and the absmax word that lets
+a layer stack skip the quantiser's own pass over the activations."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import rns_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+C0 = (127, 126, 125, 121)
+C4 = (127, 126, 125, 121, 113)
+
+
+@pytest.fixture(scope="module")
+def backend():
+    from rns_llm_b200.backends import CudaRNSBackend
+    return CudaRNSBackend()
+
+
+def tiled_plane_offsets(m, k, channels, tile_rows):
+    """Byte offset of (row, col, channel) in [M_pad/rows][K_pad/64][channels][rows][64]
+    with 16-byte chunks of a row XORed by (row_in_tile >> 1) & 3 (include/rns_b200.h)."""
+    rows = np.arange(m)[:, None, None]
+    cols = np.arange(k)[None, :, None]
+    ch = np.arange(channels)[None, None, :]
+    kblocks = (k + 63) // 64
+    tile = ((rows // tile_rows) * kblocks + (cols >> 6)) * channels + ch
+    r, c = rows % tile_rows, cols & 63
+    inner = r * 64 + ((((c >> 4) ^ ((r >> 1) & 3)) << 4) | (c & 15))
+    return tile * (tile_rows * 64) + inner
+
+
+def pair_int(backend, a, w_nk, mods, out_dtype=torch.int64):
+    from rns_llm_b200 import _native as N
+    lib = N.load()
+    m, k = a.shape
+    rows = int(lib.rns_pair_tile_rows(len(mods), k))
+    assert rows in (64, 48)
+    nbytes = int(lib.rns_packed_planes_bytes(m, k, len(mods), rows))
+    assert nbytes == -(-m // (2 * rows)) * 2 * rows * -(-k // 64) * 64 * len(mods)
+    host = np.full(nbytes, 77, dtype=np.int8)                   # pad rows / columns hold junk
+    planes = O.encode_centered(a, mods, "device")               # [R, M, K]
+    host[tiled_plane_offsets(m, k, len(mods), rows)] = np.moveaxis(planes, 0, 2)
+    w_dev = torch.from_numpy(np.ascontiguousarray(w_nk)).cuda()
+    prepared = backend.prepare_weight_nk(w_dev, mods)
+    out = torch.full((m, w_nk.shape[0]), -7, dtype=out_dtype, device="cuda")
+    backend._launch_fused(prepared=prepared, m=m, a=None, a_planes=torch.from_numpy(host).cuda(), a_packed=True,
+                          out=out, a_tile_rows=rows)
+    torch.cuda.synchronize()
+    backend.check_status()
+    return out.cpu().numpy()
+
+
+@pytest.mark.parametrize("mods", [C0, C4])
+@pytest.mark.parametrize("m,k,n", [(128, 512, 256), (300, 1024, 260), (97, 528, 130), (700, 2048, 700),
+                                   (1024, 4096, 512)])
+def test_pair_kernel_exact_integers(backend, mods, m, k, n):
+    rng = np.random.default_rng(m + k + n + len(mods))
+    a = rng.integers(-128, 128, size=(m, k)).astype(np.int8)
+    w = rng.integers(-128, 128, size=(n, k)).astype(np.int8)
+    exact = O.exact_matmul(a, w.T)
+    assert np.array_equal(pair_int(backend, a, w, mods), exact)
+    if len(mods) == 4:
+        assert np.array_equal(pair_int(backend, a, w, mods, torch.int32), exact.astype(np.int32))
+
+
+@pytest.mark.parametrize("mods", [C0, C4])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("per_row", [False, True])
+def test_pair_kernel_linear_forward_matches_oracle(backend, mods, dtype, per_row):
+    torch.manual_seed(11 + len(mods))
+    m, k, n = 600, 1024, 392
+    x = torch.randn(m, k).to(dtype)
+    weight = (torch.randn(n, k) * 0.05).to(dtype)
+    bias = torch.randn(n).to(dtype)
+    np_dtype = {torch.float16: np.float16, torch.float32: np.float32}.get(dtype, np.float32)
+    res = O.rns_linear_forward(x.float().numpy(), weight.float().numpy(), bias.float().numpy(), mods,
+                               per_row=per_row, out_dtype=np_dtype)
+    w_q, w_scale, _ = backend.quantize_weight(weight.cuda())
+    prepared = backend.prepare_weight_nk(w_q, mods)
+    y = backend.linear_forward(x.cuda(), prepared, w_scale, bias.float().cuda(), per_row=per_row)
+    torch.cuda.synchronize()
+    backend.check_status()
+    if dtype == torch.bfloat16:
+        assert torch.equal(y.cpu(), torch.from_numpy(res["y"]).to(torch.bfloat16))
+    else:
+        assert np.array_equal(y.cpu().numpy(), res["y"])
+
+
+def test_absmax_word_feeds_the_next_quantiser(backend):
+    """The epilogue's max |y| equals the tensor's absmax as the next layer computes it, and
+    a quantiser given that word (alone, or as the maximum of several words) produces the
+    same bits as one that scans the activations itself."""
+    torch.manual_seed(5)
+    m, k, n = 1024, 1024, 768
+    x = torch.randn(m, k, dtype=torch.float16, device="cuda")
+    w1 = (torch.randn(n, k, device="cuda") * 0.05).half()
+    w2 = (torch.randn(512, n, device="cuda") * 0.05).half()
+    q1, s1, _ = backend.quantize_weight(w1)
+    q2, s2, _ = backend.quantize_weight(w2)
+    p1, p2 = backend.prepare_weight_nk(q1, C0), backend.prepare_weight_nk(q2, C0)
+    words = torch.zeros(8, dtype=torch.int32, device="cuda")
+    y1 = backend.linear_forward(x, p1, s1, None, absmax_out=words.data_ptr())
+    torch.cuda.synchronize()
+    got = words[:1].view(torch.float32).item()
+    assert got == float(y1.float().abs().max())
+    plain = backend.linear_forward(y1, p2, s2, None).clone()
+    given = backend.linear_forward(y1, p2, s2, None, absmax_in=(words.data_ptr(), 1, 0)).clone()
+    assert torch.equal(plain, given)
+    # several parts: the maximum counts (smaller words elsewhere must not matter)
+    words[2] = torch.tensor([0.25], dtype=torch.float32).view(torch.int32).item()
+    words[4] = 0
+    spread = backend.linear_forward(y1, p2, s2, None, absmax_in=(words.data_ptr(), 3, 2))
+    assert torch.equal(plain, spread)
+    backend.check_status()
+    with pytest.raises(ValueError):
+        backend.linear_forward(x[:64], p1, s1, None, absmax_out=words.data_ptr())
