@@ -28,10 +28,23 @@
 namespace rns {
 
 constexpr int kPairEncWarps = 16;
-constexpr int kPairThreads = (2 + kPairEncWarps) * 32;
-constexpr int kPairEncThreads = kPairEncWarps * 32;
+constexpr int kPairGroups = 2;                     // encoder groups; group g encodes the stages st = g (mod 2)
+constexpr int kPairGroupWarps = kPairEncWarps / kPairGroups;
+constexpr int kPairGroupThreads = kPairGroupWarps * 32;
+constexpr int kPairPlaneWarp = 2 + kPairEncWarps;  // the warp that loads planes
+constexpr int kPairThreads = (3 + kPairEncWarps) * 32;
 constexpr int kDoneRing = 8;                       // ring of "stage done" barriers (>= both ring depths)
 constexpr uint32_t kPairOpTile = 128 * kPackK;     // one channel's weight operand tile
+constexpr int kPairChunks = 128 * 4 / kPairGroupThreads;   // 16-byte chunks of a weight tile per encoder thread
+
+#ifdef RNS_PAIR_TIMING
+__device__ long long g_pair_dbg[32];
+#define PT_NOW() clock64()
+#define PT_ADD(slot, t0) do { if (blockIdx.x < 2) atomicAdd((unsigned long long*)&g_pair_dbg[(slot) + 16 * (blockIdx.x & 1)], (unsigned long long)(clock64() - (t0))); } while (0)
+#else
+#define PT_NOW() 0ll
+#define PT_ADD(slot, t0) do { (void)(t0); } while (0)
+#endif
 
 struct PairParams {
     Plan plan;
@@ -56,10 +69,9 @@ struct PairParams {
 };
 
 struct __align__(8) PairCtl {
-    uint64_t full_op[kDoneRing];     // this CTA's encoders have written the operand slot
-    uint64_t full_pl[kDoneRing];     // this CTA's plane half has landed
+    uint64_t full_op[kDoneRing];     // leader: the encoder groups of BOTH CTAs have written the operand slot
+    uint64_t full_pl[kDoneRing];     // this CTA's plane half has landed (leader: and the peer's)
     uint64_t done[kDoneRing];        // the MMAs of the stage are complete (arrives in both CTAs)
-    uint64_t peer_ready[kDoneRing];  // leader only: the peer CTA's stage is complete
     uint64_t acc_full;
     uint32_t tmem_base;
     int abort;
@@ -71,7 +83,12 @@ __global__ void __launch_bounds__(kPairThreads, 1)
 rns_gemm_pair_kernel(const __grid_constant__ PairParams p) {
     static_assert(R * TOK <= 512, "accumulators must fit tensor memory");
     static_assert(TOK % 16 == 0 && (TOK / 2) % 8 == 0, "token tile shape");
-    static_assert(ES <= kDoneRing && PS <= kDoneRing, "ring depths");
+    static_assert(ES <= kDoneRing && PS <= kDoneRing && ES >= kPairGroups, "ring depths");
+    // An issuer warp takes every other stage.  With even ring depths a slot is always
+    // handled by the same warp, which therefore sees every phase of the slot's barrier; with
+    // an odd depth it would skip alternate phases and could mistake "the phase before last
+    // has completed" for the one it waits for (a parity wait cannot tell them apart).
+    static_assert(ES % 2 == 0 && PS % 2 == 0 && kDoneRing % 2 == 0, "ring depths must be even");
     constexpr int TR = TOK / 2;                               // token rows this CTA loads
     constexpr uint32_t kOpStage = (uint32_t)R * kPairOpTile;
     constexpr uint32_t kPlTile = (uint32_t)TR * kPackK;
@@ -107,12 +124,13 @@ rns_gemm_pair_kernel(const __grid_constant__ PairParams p) {
         ctl.abort = 0;
         ctl.absmax = 0u;
         for (int s = 0; s < kDoneRing; ++s) {
-            mbar_init(smem_addr(&ctl.full_op[s]), kPairEncWarps);
-            mbar_init(smem_addr(&ctl.full_pl[s]), 1);
+            // The leader's barriers collect the peer CTA's arrivals too: its encoder warps
+            // arrive on the leader's full_op directly, its plane load through a relay lane.
+            mbar_init(smem_addr(&ctl.full_op[s]), 2 * kPairGroupWarps);
+            mbar_init(smem_addr(&ctl.full_pl[s]), rank == 0 ? 2 : 1);
             mbar_init(smem_addr(&ctl.done[s]), 1);
-            mbar_init(smem_addr(&ctl.peer_ready[s]), 1);
         }
-        mbar_init(smem_addr(&ctl.acc_full), 1);
+        mbar_init(smem_addr(&ctl.acc_full), 2);                // one commit from each issuer warp
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -125,7 +143,7 @@ rns_gemm_pair_kernel(const __grid_constant__ PairParams p) {
     const uint32_t tmem_base = ctl.tmem_base;
     volatile int* abort = &ctl.abort;
 
-    if (warp == 0) {
+    if (warp == kPairPlaneWarp) {
         // ------------------------------ plane producer ----------------------------
         if (lane == 0) {
             const int8_t* src = p.planes + ((int64_t)(tt * 2 + (int)rank) * p.kblocks) * (int64_t)kPlStage;
@@ -142,36 +160,40 @@ rns_gemm_pair_kernel(const __grid_constant__ PairParams p) {
             }
         }
         __syncwarp();
-    } else if (warp == 1) {
+    } else if (warp <= 1) {
         if (rank != 0) {
-            // ------------------------------ relay (peer CTA) ----------------------
-            if (lane == 0) {
-                int s = 0, sp = 0;
-                uint32_t ph_op = 0, ph_pl = 0;
+            // ------------------------------ plane relay (peer CTA) ----------------
+            // Tells the leader that this CTA's plane half of a stage has landed.  Planes
+            // run several stages ahead of the MMAs, so this hop is off the critical path.
+            if (warp == 1 && lane == 0) {
                 for (int st = 0; st < nst; ++st) {
-                    if (!wait_bounded<false, true>(smem_addr(&ctl.full_op[s]), ph_op, abort, wait_code(3, st))) break;
-                    if (!wait_bounded<false, true>(smem_addr(&ctl.full_pl[sp]), ph_pl, abort, wait_code(4, st))) break;
-                    mbar_arrive_remote(smem_addr(&ctl.peer_ready[st & (kDoneRing - 1)]), 0);
-                    if (++s == ES) { s = 0; ph_op ^= 1u; }
-                    if (++sp == PS) { sp = 0; ph_pl ^= 1u; }
+                    if (!wait_bounded<false, true>(smem_addr(&ctl.full_pl[st % PS]), (uint32_t)(st / PS) & 1u, abort,
+                                                   wait_code(4, st))) break;
+                    mbar_arrive_remote_relaxed(smem_addr(&ctl.full_pl[st % PS]), 0);
                 }
             }
             __syncwarp();
         } else {
-            // ------------------------------ MMA issuer (leader CTA) ----------------
-            // The whole warp runs the loop so that addresses and descriptors are
-            // warp-uniform values; one elected lane issues.
+            // ------------------------------ MMA issuers (leader CTA) ---------------
+            // Two warps take alternate stages: an issuer's instruction stream per stage
+            // (two barrier tests, eight MMAs, a commit) is longer than the MMAs run, so
+            // one of them cannot keep the tensor pipe fed.  Integer accumulation does not
+            // depend on the order of the MMAs; the accumulators are zeroed beforehand, so
+            // that no MMA has to come first.  Each whole warp runs the loop (addresses and
+            // descriptors are then warp-uniform values); one elected lane issues.
             const uint32_t idesc = make_idesc(256u, (uint32_t)TOK);
             const uint64_t desc0 = make_smem_desc(0, kPackK);
             const uint32_t a_lo0 = op_base >> 4, b_lo0 = pl_base >> 4;
-            int s = 0, sp = 0;
-            uint32_t ph_op = 0, ph_pl = 0;
             bool ok = true;
-            for (int st = 0; st < nst; ++st) {
-                ok = warp_wait_bounded<false, true>(smem_addr(&ctl.full_op[s]), ph_op, abort, wait_code(5, st));
-                if (ok) ok = warp_wait_bounded<false, true>(smem_addr(&ctl.full_pl[sp]), ph_pl, abort, wait_code(6, st));
-                if (ok) ok = warp_wait_bounded<true>(smem_addr(&ctl.peer_ready[st & (kDoneRing - 1)]),
-                                                     (uint32_t)(st >> 3) & 1u, abort, wait_code(7, st));
+            for (int st = warp; st < nst; st += 2) {
+                const int s = st % ES, sp = st % PS;
+                long long pt = PT_NOW();
+                ok = warp_wait_bounded<false, true>(smem_addr(&ctl.full_op[s]), (uint32_t)(st / ES) & 1u, abort, wait_code(5, st));
+                if (lane == 0) PT_ADD(0 + 4 * warp, pt);
+                pt = PT_NOW();
+                if (ok) ok = warp_wait_bounded<false, true>(smem_addr(&ctl.full_pl[sp]), (uint32_t)(st / PS) & 1u, abort, wait_code(6, st));
+                if (lane == 0) PT_ADD(1 + 4 * warp, pt);
+                pt = PT_NOW();
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t a_st = a_lo0 + (uint32_t)s * (kOpStage >> 4);
@@ -183,63 +205,104 @@ rns_gemm_pair_kernel(const __grid_constant__ PairParams p) {
                         for (int ks = 0; ks < 2; ++ks) {
                             const uint64_t da = desc0 | (uint64_t)(a_st + (uint32_t)c * (kPairOpTile >> 4) + (uint32_t)ks * 2u);
                             const uint64_t db = desc0 | (uint64_t)(b_st + (uint32_t)c * (kPlTile >> 4) + (uint32_t)ks * 2u);
-                            umma_i8_pair(tmem_base + (uint32_t)(c * TOK), da, db, idesc, (st > 0 || ks > 0) ? 1u : 0u);
+                            umma_i8_pair(tmem_base + (uint32_t)(c * TOK), da, db, idesc, 1u);
                         }
                     }
                     umma_commit_pair(smem_addr(&ctl.done[st & (kDoneRing - 1)]));
                 }
                 __syncwarp();
-                if (++s == ES) { s = 0; ph_op ^= 1u; }
-                if (++sp == PS) { sp = 0; ph_pl ^= 1u; }
+                if (lane == 0) PT_ADD(2 + 4 * warp, pt);
             }
             if (ok && elect_one()) umma_commit_pair(smem_addr(&ctl.acc_full));
             __syncwarp();
         }
     } else {
         // ------------------------------ encoders ----------------------------------
-        const int e = (warp - 2) * 32 + lane;                  // 16-byte chunk of the 128 x 64 weight tile
-        const bool row_valid = n0 + (e >> 2) < p.n;
+        // Zero this warp's share of the accumulators first (its lane quarter, 128 of the
+        // 512 columns): the arrival on the first stage's barrier publishes it.
+        {
+            const uint32_t zero_at = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(((warp - 2) >> 2) * 128);
+            uint32_t zeros[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) zeros[i] = 0u;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) tmem_st16(zero_at + (uint32_t)(i * 16), zeros);
+            tmem_st_wait();
+            tc_fence_before();
+        }
+        const int group = (warp - 2) & (kPairGroups - 1);
+        const int e0 = ((warp - 2) / kPairGroups) * 32 + lane;  // first 16-byte chunk of this thread
         uint32_t mfold[R];
 #pragma unroll
         for (int c = 0; c < R; ++c) mfold[c] = p.plan.enc_mfold[c];
-        const int8_t* w_src = p.w + (int64_t)n0 * kPackK + (int64_t)e * 16;
+        const int8_t* w_src = p.w + (int64_t)n0 * kPackK + (int64_t)e0 * 16;
         const int64_t kb_stride = p.w_npad * kPackK;
-        auto load_w = [&](int st) -> uint4 {
-            if (row_valid && st < nst) return __ldg(reinterpret_cast<const uint4*>(w_src + (int64_t)st * kb_stride));
-            return make_uint4(0u, 0u, 0u, 0u);
+        bool valid[kPairChunks];
+#pragma unroll
+        for (int i = 0; i < kPairChunks; ++i) valid[i] = n0 + ((e0 + i * kPairGroupThreads) >> 2) < p.n;
+        auto load_w = [&](int st, uint4 (&dst)[kPairChunks]) {
+#pragma unroll
+            for (int i = 0; i < kPairChunks; ++i) {
+                if (valid[i] && st < nst)
+                    dst[i] = __ldg(reinterpret_cast<const uint4*>(w_src + (int64_t)st * kb_stride + (int64_t)i * kPairGroupThreads * 16));
+                else
+                    dst[i] = make_uint4(0u, 0u, 0u, 0u);
+            }
         };
-        uint4 cur = load_w(0), nxt = load_w(1), nxt2 = load_w(2);
+        uint4 cur[kPairChunks], nxt[kPairChunks];
+        load_w(group, cur);
+        load_w(group + kPairGroups, nxt);
         bool ok = true;
-        int s = 0;
-        for (int st = 0; st < nst && ok; ++st) {
-            const uint4 ahead = load_w(st + 3);
+        // In the very first stages every group must have zeroed its accumulator share
+        // before any MMA runs: both groups' first arrivals come after their zeroing, and
+        // the issuers of stage 0 and 1 each wait for one of them - but an MMA of stage 0
+        // writes columns that the other group zeroes.  So the groups meet once here.
+        asm volatile("bar.sync 1, %0;" ::"n"(kPairEncWarps * 32) : "memory");
+        for (int st = group; st < nst && ok; st += kPairGroups) {
+            const int s = st % ES;
+            uint4 ahead[kPairChunks];
+            load_w(st + 2 * kPairGroups, ahead);
+            long long pt = PT_NOW();
             if (st >= ES)
                 ok = warp_wait_bounded(smem_addr(&ctl.done[(st - ES) & (kDoneRing - 1)]),
                                        (uint32_t)((st - ES) >> 3) & 1u, abort, wait_code(8, st));
+            if (threadIdx.x == 64) PT_ADD(8, pt);
+            pt = PT_NOW();
             if (!ok) break;
-            uint8_t* dst = tiles_ptr + (size_t)s * kOpStage + (size_t)e * 16;
-            const uint32_t u0 = cur.x ^ 0x80808080u, u1 = cur.y ^ 0x80808080u;
-            const uint32_t u2 = cur.z ^ 0x80808080u, u3 = cur.w ^ 0x80808080u;
-            const uint32_t d0 = fold_pattern(cur.x), d1 = fold_pattern(cur.y);
-            const uint32_t d2 = fold_pattern(cur.z), d3 = fold_pattern(cur.w);
+            uint8_t* dst = tiles_ptr + (size_t)s * kOpStage + (size_t)e0 * 16;
 #pragma unroll
-            for (int c = 0; c < R; ++c) {
-                uint4 y;
-                y.x = encode_word_reduced(u0, d0, mfold[c]);
-                y.y = encode_word_reduced(u1, d1, mfold[c]);
-                y.z = encode_word_reduced(u2, d2, mfold[c]);
-                y.w = encode_word_reduced(u3, d3, mfold[c]);
-                *reinterpret_cast<uint4*>(dst + (size_t)c * kPairOpTile) = y;
+            for (int i = 0; i < kPairChunks; ++i) {
+                const uint4 x = cur[i];
+                const uint32_t u0 = x.x ^ 0x80808080u, u1 = x.y ^ 0x80808080u;
+                const uint32_t u2 = x.z ^ 0x80808080u, u3 = x.w ^ 0x80808080u;
+                const uint32_t d0 = fold_pattern(x.x), d1 = fold_pattern(x.y);
+                const uint32_t d2 = fold_pattern(x.z), d3 = fold_pattern(x.w);
+#pragma unroll
+                for (int c = 0; c < R; ++c) {
+                    uint4 y;
+                    y.x = encode_word_reduced(u0, d0, mfold[c]);
+                    y.y = encode_word_reduced(u1, d1, mfold[c]);
+                    y.z = encode_word_reduced(u2, d2, mfold[c]);
+                    y.w = encode_word_reduced(u3, d3, mfold[c]);
+                    *reinterpret_cast<uint4*>(dst + (size_t)i * kPairGroupThreads * 16 + (size_t)c * kPairOpTile) = y;
+                }
             }
-            cur = nxt; nxt = nxt2; nxt2 = ahead;
+#pragma unroll
+            for (int i = 0; i < kPairChunks; ++i) { cur[i] = nxt[i]; nxt[i] = ahead[i]; }
             fence_proxy_async_smem();
             __syncwarp();
-            if (lane == 0) mbar_arrive(smem_addr(&ctl.full_op[s]));
-            if (++s == ES) s = 0;
+            if (lane == 0) {
+                if (rank == 0) mbar_arrive(smem_addr(&ctl.full_op[s]));
+                else mbar_arrive_remote_relaxed(smem_addr(&ctl.full_op[s]), 0);
+            }
+            if (threadIdx.x == 64) PT_ADD(9, pt);
         }
 
         // ------------------------------ epilogue (feature-major) ------------------
+        long long pt_epi = PT_NOW();
         if (ok) ok = warp_wait_bounded(smem_addr(&ctl.acc_full), 0, abort, wait_code(11, 0));
+        if (threadIdx.x == 64) PT_ADD(10, pt_epi);
+        pt_epi = PT_NOW();
         if (ok) {
             tc_fence_after();
             const int quarter = warp & 3;                      // tensor-memory lanes 32*quarter .. +31
@@ -257,6 +320,11 @@ rns_gemm_pair_kernel(const __grid_constant__ PairParams p) {
             using XInt = typename std::conditional<(R <= 4), int, long long>::type;
             float biggest = 0.0f;
             constexpr int kColsPerPart = TOK / 4;
+            // Two-byte outputs leave in pairs: lanes 2j and 2j+1 hold neighbouring features,
+            // the even lane stores both features of the even tokens, the odd lane those of the
+            // odd tokens (one 4-byte store instead of two 2-byte ones).
+            const bool pair_store = (p.out_type == RNS_OUT_F16 || p.out_type == RNS_OUT_BF16) && (p.ldo & 1) == 0 &&
+                                    (reinterpret_cast<uintptr_t>(p.out) & 3) == 0 && n0 + quarter * 32 + 32 <= p.n;
             auto load = [&](int col, int (&acc)[R][8]) {
                 __syncwarp();
 #pragma unroll
@@ -264,42 +332,85 @@ rns_gemm_pair_kernel(const __grid_constant__ PairParams p) {
             };
             auto finish = [&](int col, const int (&acc)[R][8]) {
                 const int tok_first = tok0 + col;
-                if (!feat_ok || tok_first >= p.m) return;
+                if (tok_first >= p.m) return;                  // warp-uniform
+                XInt xv[8];
 #pragma unroll
                 for (int t = 0; t < 8; ++t) {
-                    const int tok = tok_first + t;
-                    if (tok >= p.m) break;
                     int one[R];
 #pragma unroll
                     for (int c = 0; c < R; ++c) one[c] = acc[c][t];
-                    XInt xv;
-                    if constexpr (R <= 4) xv = reconstruct32<R>(one, p.plan, R);
-                    else xv = reconstruct<R>(one, p.plan, R);
-                    const int64_t o = (int64_t)tok * p.ldo + feat;
-                    if (p.out_type == RNS_OUT_INT64) {
-                        static_cast<long long*>(p.out)[o] = (long long)xv;
-                    } else if (p.out_type == RNS_OUT_INT32) {
-                        static_cast<int*>(p.out)[o] = (int)xv;
-                    } else {
-                        float xf;
-                        if constexpr (R <= 4) xf = __int2float_rn(xv);
-                        else xf = __ll2float_rn(xv);
-                        const float rs = p.row_scale_stride == 0 ? rs_all : p.row_scale[tok];
-                        float y = __fmul_rn(__fmul_rn(xf, rs), cs);
-                        if (p.bias != nullptr) y = __fadd_rn(y, bs);
-                        if (p.out_type == RNS_OUT_F16) {
-                            const __half h = __float2half_rn(y);
-                            static_cast<__half*>(p.out)[o] = h;
-                            biggest = fmaxf(biggest, fabsf(__half2float(h)));
-                        } else if (p.out_type == RNS_OUT_BF16) {
-                            const __nv_bfloat16 h = __float2bfloat16_rn(y);
-                            static_cast<__nv_bfloat16*>(p.out)[o] = h;
-                            biggest = fmaxf(biggest, fabsf(__bfloat162float(h)));
-                        } else {
-                            static_cast<float*>(p.out)[o] = y;
-                            biggest = fmaxf(biggest, fabsf(y));
+                    if constexpr (R <= 4) xv[t] = reconstruct32<R>(one, p.plan, R);
+                    else xv[t] = reconstruct<R>(one, p.plan, R);
+                }
+                const int valid_t = min(8, p.m - tok_first);   // warp-uniform
+                if (!is_float) {
+                    if (!feat_ok) return;
+#pragma unroll
+                    for (int t = 0; t < 8; ++t) {
+                        if (t < valid_t) {
+                            const int64_t o = (int64_t)(tok_first + t) * p.ldo + feat;
+                            if (p.out_type == RNS_OUT_INT64) static_cast<long long*>(p.out)[o] = (long long)xv[t];
+                            else static_cast<int*>(p.out)[o] = (int)xv[t];
                         }
                     }
+                    return;
+                }
+                float y[8];
+#pragma unroll
+                for (int t = 0; t < 8; ++t) {
+                    float xf;
+                    if constexpr (R <= 4) xf = __int2float_rn(xv[t]);
+                    else xf = __ll2float_rn(xv[t]);
+                    const float rs = p.row_scale_stride == 0 ? rs_all : (t < valid_t ? p.row_scale[tok_first + t] : 0.0f);
+                    float v = __fmul_rn(__fmul_rn(xf, rs), cs);
+                    if (p.bias != nullptr) v = __fadd_rn(v, bs);
+                    y[t] = v;
+                }
+                if (p.out_type == RNS_OUT_F32) {
+                    if (!feat_ok) return;
+#pragma unroll
+                    for (int t = 0; t < 8; ++t) {
+                        if (t < valid_t) {
+                            static_cast<float*>(p.out)[(int64_t)(tok_first + t) * p.ldo + feat] = y[t];
+                            biggest = fmaxf(biggest, fabsf(y[t]));
+                        }
+                    }
+                    return;
+                }
+                // fp16 / bf16: the stored bit patterns, and their magnitudes for the absmax word
+                unsigned short h[8];
+#pragma unroll
+                for (int t = 0; t < 8; ++t) {
+                    if (p.out_type == RNS_OUT_F16) {
+                        const __half v = __float2half_rn(y[t]);
+                        h[t] = __half_as_ushort(v);
+                        if (t < valid_t && feat_ok) biggest = fmaxf(biggest, fabsf(__half2float(v)));
+                    } else {
+                        const __nv_bfloat16 v = __float2bfloat16_rn(y[t]);
+                        h[t] = __bfloat16_as_ushort(v);
+                        if (t < valid_t && feat_ok) biggest = fmaxf(biggest, fabsf(__bfloat162float(v)));
+                    }
+                }
+                unsigned short* out16 = static_cast<unsigned short*>(p.out);
+                if (pair_store) {
+                    const bool odd = (lane & 1) != 0;
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        // even lane keeps token 2i and sends token 2i+1; odd lane the other way round
+                        const unsigned mine = odd ? h[2 * i + 1] : h[2 * i];
+                        const unsigned send = odd ? h[2 * i] : h[2 * i + 1];
+                        const unsigned got = __shfl_xor_sync(0xffffffffu, send, 1);
+                        const int t = 2 * i + (odd ? 1 : 0);
+                        if (t < valid_t) {
+                            const unsigned word = odd ? (got | (mine << 16)) : (mine | (got << 16));
+                            const int64_t o = (int64_t)(tok_first + t) * p.ldo + (feat & ~1);
+                            *reinterpret_cast<unsigned*>(out16 + o) = word;
+                        }
+                    }
+                } else if (feat_ok) {
+#pragma unroll
+                    for (int t = 0; t < 8; ++t)
+                        if (t < valid_t) out16[(int64_t)(tok_first + t) * p.ldo + feat] = h[t];
                 }
             };
             const int col0 = part * kColsPerPart;
@@ -334,6 +445,7 @@ rns_gemm_pair_kernel(const __grid_constant__ PairParams p) {
                 for (int o = 16; o > 0; o >>= 1) biggest = fmaxf(biggest, __shfl_xor_sync(0xffffffffu, biggest, o));
                 if (lane == 0) atomicMax(&ctl.absmax, __float_as_uint(biggest));
             }
+            if (threadIdx.x == 64) PT_ADD(11, pt_epi);
         }
     }
 
@@ -443,7 +555,15 @@ int launch_pair_gemm(const rns_linear_args* a, const Plan& plan, cudaStream_t st
     if (pairs > (1 << 30)) return fail(RNS_ERR_UNSUPPORTED, "too many output tiles");
     if (a->d_absmax_out != nullptr) RNS_CUDA_OK(cudaMemsetAsync(a->d_absmax_out, 0, sizeof(uint32_t), st));
     if (R == 4) return launch_pair<4, 128, 4, 6>(pp, (int)pairs, st);
-    return launch_pair<5, 96, 3, 7>(pp, (int)pairs, st);
+    return launch_pair<5, 96, 4, 4>(pp, (int)pairs, st);
 }
+
+#ifdef RNS_PAIR_TIMING
+extern "C" __attribute__((visibility("default"))) int rns_debug_pair_timing(long long* host32, int reset) {
+    if (host32 && cudaMemcpyFromSymbol(host32, g_pair_dbg, sizeof(long long) * 32) != cudaSuccess) return 1;
+    if (reset) { long long z[32] = {0}; if (cudaMemcpyToSymbol(g_pair_dbg, z, sizeof(z)) != cudaSuccess) return 1; }
+    return 0;
+}
+#endif
 
 }  // namespace rns

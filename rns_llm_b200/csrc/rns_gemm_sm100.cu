@@ -243,7 +243,12 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     // depend on the order of the MMAs; the accumulators are zeroed beforehand, so that
     // no MMA has to come first.  Each issuer's instruction stream per stage is longer
     // than the MMAs it issues; two of them keep the tensor pipe fed.
-    constexpr bool TWO_ISSUERS = ONE_COMMIT;
+    // Only with an even operand-ring depth: a warp that takes every other stage then always
+    // meets the same slots and sees every phase of their barriers.  With an odd depth it
+    // would skip alternate phases of a slot, and a parity wait cannot tell "the phase before
+    // last has completed" from the awaited one: when the planes of stage s landed after
+    // those of stage s + 1, the issuer of stage s + 3 could pass its wait early.
+    constexpr bool TWO_ISSUERS = ONE_COMMIT && (ES_ % 2 == 0);
     const int tile_k = FIXED ? 64 : p.tile_k;
     const int tile_n = FIXED ? (R <= 4 ? 128 : 96) : p.tile_n;
     const int m_tile = PAIR ? 2 * (int)blockIdx.y + (int)pair_rank : (int)blockIdx.y;
