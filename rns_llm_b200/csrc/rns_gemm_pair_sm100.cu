@@ -37,15 +37,6 @@ constexpr int kDoneRing = 8;                       // ring of "stage done" barri
 constexpr uint32_t kPairOpTile = 128 * kPackK;     // one channel's weight operand tile
 constexpr int kPairChunks = 128 * 4 / kPairGroupThreads;   // 16-byte chunks of a weight tile per encoder thread
 
-#ifdef RNS_PAIR_TIMING
-__device__ long long g_pair_dbg[32];
-#define PT_NOW() clock64()
-#define PT_ADD(slot, t0) do { if (blockIdx.x < 2) atomicAdd((unsigned long long*)&g_pair_dbg[(slot) + 16 * (blockIdx.x & 1)], (unsigned long long)(clock64() - (t0))); } while (0)
-#else
-#define PT_NOW() 0ll
-#define PT_ADD(slot, t0) do { (void)(t0); } while (0)
-#endif
-
 struct PairParams {
     Plan plan;
     int32_t m, n, k;
@@ -72,12 +63,41 @@ struct __align__(8) PairCtl {
     uint64_t full_op[kDoneRing];     // leader: the encoder groups of BOTH CTAs have written the operand slot
     uint64_t full_pl[kDoneRing];     // this CTA's plane half has landed (leader: and the peer's)
     uint64_t done[kDoneRing];        // the MMAs of the stage are complete (arrives in both CTAs)
-    uint64_t acc_full;
+    uint64_t acc_full;               // the tile's MMAs are complete (arrives in both CTAs)
+    uint64_t tmem_free;              // leader: both CTAs' accumulators are drained and zeroed
     uint32_t tmem_base;
     int abort;
     uint32_t absmax;
 };
 
+// Output tile of a cluster: its position in the raster and the CTA's share of it.
+struct PairTile {
+    int n0;      // first feature of this CTA
+    int tok0;    // first token of the pair's tile
+    int tt;      // token tile index
+};
+
+template <int TOK>
+__device__ __forceinline__ PairTile pair_tile(const PairParams& p, int tile, uint32_t rank) {
+    // Raster: feature tiles in bands; inside a band the token tiles advance slowest, so
+    // the clusters working at the same time share a band of the weight (it stays in L2)
+    // and a few token tiles, and every plane byte is read from DRAM once per band.
+    const int per_band = p.band * p.n_ttiles;
+    const int band_i = tile / per_band;
+    const int in_band = tile - band_i * per_band;
+    const int band_w = min(p.band, p.n_ftiles - band_i * p.band);
+    PairTile t;
+    t.tt = in_band / band_w;
+    const int ft = band_i * p.band + (in_band - t.tt * band_w);
+    t.n0 = ft * 256 + (int)rank * 128;
+    t.tok0 = t.tt * TOK;
+    return t;
+}
+
+// Persistent: a cluster walks the tiles cluster, cluster + clusters, ...  All rings run on
+// one stage counter g that keeps counting across tiles (slot = g mod depth), so the loads
+// and the weight encoding of the next tile start while this tile's last MMAs and its
+// epilogue are still running; only the MMAs wait for the accumulators to be drained.
 template <int R, int TOK, int ES, int PS>
 __global__ void __launch_bounds__(kPairThreads, 1)
 rns_gemm_pair_kernel(const __grid_constant__ PairParams p) {
@@ -105,19 +125,9 @@ rns_gemm_pair_kernel(const __grid_constant__ PairParams p) {
     const uint32_t op_base = tiles_base;                       // operand ring first
     const uint32_t pl_base = tiles_base + (uint32_t)ES * kOpStage;
 
-    // Raster: feature tiles in bands; inside a band the token tiles advance slowest, so
-    // the CTAs resident together share a band of the weight (it stays in L2) and a few
-    // token tiles, and every plane byte is read from DRAM once per band.
     const uint32_t rank = cluster_cta_rank();
-    const int pair = (int)(blockIdx.x >> 1);
-    const int per_band = p.band * p.n_ttiles;
-    const int band_i = pair / per_band;
-    const int in_band = pair - band_i * per_band;
-    const int band_w = min(p.band, p.n_ftiles - band_i * p.band);
-    const int tt = in_band / band_w;
-    const int ft = band_i * p.band + (in_band - tt * band_w);
-    const int n0 = ft * 256 + (int)rank * 128;                 // first feature of this CTA
-    const int tok0 = tt * TOK;                                 // first token of the pair's tile
+    const int cluster = (int)(blockIdx.x >> 1), clusters = (int)(gridDim.x >> 1);
+    const int tiles = p.n_ftiles * p.n_ttiles;
     const int nst = p.kblocks;                                 // one K block of 64 bytes per stage
 
     if (threadIdx.x == 0) {
@@ -131,6 +141,7 @@ rns_gemm_pair_kernel(const __grid_constant__ PairParams p) {
             mbar_init(smem_addr(&ctl.done[s]), 1);
         }
         mbar_init(smem_addr(&ctl.acc_full), 2);                // one commit from each issuer warp
+        mbar_init(smem_addr(&ctl.tmem_free), 2 * kPairEncWarps);   // leader: both CTAs' epilogue warps
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -146,30 +157,38 @@ rns_gemm_pair_kernel(const __grid_constant__ PairParams p) {
     if (warp == kPairPlaneWarp) {
         // ------------------------------ plane producer ----------------------------
         if (lane == 0) {
-            const int8_t* src = p.planes + ((int64_t)(tt * 2 + (int)rank) * p.kblocks) * (int64_t)kPlStage;
-            int sp = 0;
-            for (int st = 0; st < nst; ++st) {
-                if (st >= PS &&
-                    !wait_bounded<false, true>(smem_addr(&ctl.done[(st - PS) & (kDoneRing - 1)]),
-                                               (uint32_t)((st - PS) >> 3) & 1u, abort, wait_code(2, st)))
-                    break;
-                const uint32_t bar = smem_addr(&ctl.full_pl[sp]);
-                mbar_arrive_expect_tx(bar, kPlStage);
-                bulk_load(pl_base + (uint32_t)sp * kPlStage, src + (int64_t)st * kPlStage, kPlStage, bar);
-                if (++sp == PS) sp = 0;
+            int g = 0;
+            bool ok = true;
+            for (int tile = cluster; tile < tiles && ok; tile += clusters) {
+                const PairTile t = pair_tile<TOK>(p, tile, rank);
+                const int8_t* src = p.planes + ((int64_t)(t.tt * 2 + (int)rank) * p.kblocks) * (int64_t)kPlStage;
+                for (int st = 0; st < nst; ++st, ++g) {
+                    if (g >= PS &&
+                        !wait_bounded<false, true>(smem_addr(&ctl.done[(g - PS) & (kDoneRing - 1)]),
+                                                   (uint32_t)((g - PS) >> 3) & 1u, abort, wait_code(2, st))) {
+                        ok = false;
+                        break;
+                    }
+                    const int sp = g % PS;
+                    const uint32_t bar = smem_addr(&ctl.full_pl[sp]);
+                    mbar_arrive_expect_tx(bar, kPlStage);
+                    bulk_load(pl_base + (uint32_t)sp * kPlStage, src + (int64_t)st * kPlStage, kPlStage, bar);
+                }
             }
         }
         __syncwarp();
     } else if (warp <= 1) {
+        const int my_tiles = (tiles - cluster + clusters - 1) / clusters;
+        const int total = my_tiles * nst;                      // stages this cluster runs
         if (rank != 0) {
             // ------------------------------ plane relay (peer CTA) ----------------
             // Tells the leader that this CTA's plane half of a stage has landed.  Planes
             // run several stages ahead of the MMAs, so this hop is off the critical path.
             if (warp == 1 && lane == 0) {
-                for (int st = 0; st < nst; ++st) {
-                    if (!wait_bounded<false, true>(smem_addr(&ctl.full_pl[st % PS]), (uint32_t)(st / PS) & 1u, abort,
-                                                   wait_code(4, st))) break;
-                    mbar_arrive_remote_relaxed(smem_addr(&ctl.full_pl[st % PS]), 0);
+                for (int g = 0; g < total; ++g) {
+                    if (!wait_bounded<false, true>(smem_addr(&ctl.full_pl[g % PS]), (uint32_t)(g / PS) & 1u, abort,
+                                                   wait_code(4, g))) break;
+                    mbar_arrive_remote_relaxed(smem_addr(&ctl.full_pl[g % PS]), 0);
                 }
             }
             __syncwarp();
@@ -178,147 +197,150 @@ rns_gemm_pair_kernel(const __grid_constant__ PairParams p) {
             // Two warps take alternate stages: an issuer's instruction stream per stage
             // (two barrier tests, eight MMAs, a commit) is longer than the MMAs run, so
             // one of them cannot keep the tensor pipe fed.  Integer accumulation does not
-            // depend on the order of the MMAs; the accumulators are zeroed beforehand, so
-            // that no MMA has to come first.  Each whole warp runs the loop (addresses and
-            // descriptors are then warp-uniform values); one elected lane issues.
+            // depend on the order of the MMAs; the epilogue warps leave the accumulators
+            // zeroed, so that no MMA has to come first.  Each whole warp runs the loop
+            // (addresses and descriptors are then warp-uniform values); one elected lane
+            // issues.
             const uint32_t idesc = make_idesc(256u, (uint32_t)TOK);
             const uint64_t desc0 = make_smem_desc(0, kPackK);
             const uint32_t a_lo0 = op_base >> 4, b_lo0 = pl_base >> 4;
             bool ok = true;
-            for (int st = warp; st < nst; st += 2) {
-                const int s = st % ES, sp = st % PS;
-                long long pt = PT_NOW();
-                ok = warp_wait_bounded<false, true>(smem_addr(&ctl.full_op[s]), (uint32_t)(st / ES) & 1u, abort, wait_code(5, st));
-                if (lane == 0) PT_ADD(0 + 4 * warp, pt);
-                pt = PT_NOW();
-                if (ok) ok = warp_wait_bounded<false, true>(smem_addr(&ctl.full_pl[sp]), (uint32_t)(st / PS) & 1u, abort, wait_code(6, st));
-                if (lane == 0) PT_ADD(1 + 4 * warp, pt);
-                pt = PT_NOW();
+            int g0 = 0;                                        // first stage of the current tile
+            for (int ti = 0; ti < my_tiles && ok; ++ti, g0 += nst) {
+                // accumulators drained and zeroed (by both CTAs) since the previous tile
+                ok = warp_wait_bounded<false, true>(smem_addr(&ctl.tmem_free), (uint32_t)ti & 1u, abort, wait_code(9, ti));
                 if (!ok) break;
-                tc_fence_after();
-                const uint32_t a_st = a_lo0 + (uint32_t)s * (kOpStage >> 4);
-                const uint32_t b_st = b_lo0 + (uint32_t)sp * (kPlStage >> 4);
-                if (elect_one()) {
+                for (int g = g0 + ((g0 + warp) & 1); g < g0 + nst; g += 2) {
+                    const int s = g % ES, sp = g % PS;
+                    ok = warp_wait_bounded<false, true>(smem_addr(&ctl.full_op[s]), (uint32_t)(g / ES) & 1u, abort, wait_code(5, g));
+                    if (ok) ok = warp_wait_bounded<false, true>(smem_addr(&ctl.full_pl[sp]), (uint32_t)(g / PS) & 1u, abort, wait_code(6, g));
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t a_st = a_lo0 + (uint32_t)s * (kOpStage >> 4);
+                    const uint32_t b_st = b_lo0 + (uint32_t)sp * (kPlStage >> 4);
+                    if (elect_one()) {
 #pragma unroll
-                    for (int c = 0; c < R; ++c) {
+                        for (int c = 0; c < R; ++c) {
 #pragma unroll
-                        for (int ks = 0; ks < 2; ++ks) {
-                            const uint64_t da = desc0 | (uint64_t)(a_st + (uint32_t)c * (kPairOpTile >> 4) + (uint32_t)ks * 2u);
-                            const uint64_t db = desc0 | (uint64_t)(b_st + (uint32_t)c * (kPlTile >> 4) + (uint32_t)ks * 2u);
-                            umma_i8_pair(tmem_base + (uint32_t)(c * TOK), da, db, idesc, 1u);
+                            for (int ks = 0; ks < 2; ++ks) {
+                                const uint64_t da = desc0 | (uint64_t)(a_st + (uint32_t)c * (kPairOpTile >> 4) + (uint32_t)ks * 2u);
+                                const uint64_t db = desc0 | (uint64_t)(b_st + (uint32_t)c * (kPlTile >> 4) + (uint32_t)ks * 2u);
+                                umma_i8_pair(tmem_base + (uint32_t)(c * TOK), da, db, idesc, 1u);
+                            }
                         }
+                        umma_commit_pair(smem_addr(&ctl.done[g & (kDoneRing - 1)]));
                     }
-                    umma_commit_pair(smem_addr(&ctl.done[st & (kDoneRing - 1)]));
+                    __syncwarp();
                 }
+                // this warp's MMAs of the tile are in the pipe: the accumulators are complete
+                // when both warps' commits have arrived
+                if (ok && elect_one()) umma_commit_pair(smem_addr(&ctl.acc_full));
                 __syncwarp();
-                if (lane == 0) PT_ADD(2 + 4 * warp, pt);
             }
-            if (ok && elect_one()) umma_commit_pair(smem_addr(&ctl.acc_full));
-            __syncwarp();
         }
     } else {
-        // ------------------------------ encoders ----------------------------------
-        // Zero this warp's share of the accumulators first (its lane quarter, 128 of the
-        // 512 columns): the arrival on the first stage's barrier publishes it.
-        {
-            const uint32_t zero_at = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(((warp - 2) >> 2) * 128);
+        // ------------------------------ encoders / epilogue ------------------------
+        const int quarter = warp & 3;                          // tensor-memory lanes 32*quarter .. +31
+        const int part = (warp - 2) >> 2;                      // quarter of the token columns
+        const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
+        // Zeroes this warp's share of the accumulators (its lane quarter, 128 of the 512
+        // columns) and tells the leader's issuers.
+        auto zero_and_release = [&]() {
             uint32_t zeros[16];
 #pragma unroll
             for (int i = 0; i < 16; ++i) zeros[i] = 0u;
 #pragma unroll
-            for (int i = 0; i < 8; ++i) tmem_st16(zero_at + (uint32_t)(i * 16), zeros);
+            for (int i = 0; i < 8; ++i) tmem_st16(lane_base + (uint32_t)(part * 128 + i * 16), zeros);
             tmem_st_wait();
             tc_fence_before();
-        }
+            __syncwarp();
+            if (lane == 0) {
+                if (rank == 0) mbar_arrive(smem_addr(&ctl.tmem_free));
+                else mbar_arrive_remote_relaxed(smem_addr(&ctl.tmem_free), 0);
+            }
+        };
+        zero_and_release();
         const int group = (warp - 2) & (kPairGroups - 1);
         const int e0 = ((warp - 2) / kPairGroups) * 32 + lane;  // first 16-byte chunk of this thread
         uint32_t mfold[R];
 #pragma unroll
         for (int c = 0; c < R; ++c) mfold[c] = p.plan.enc_mfold[c];
-        const int8_t* w_src = p.w + (int64_t)n0 * kPackK + (int64_t)e0 * 16;
         const int64_t kb_stride = p.w_npad * kPackK;
-        bool valid[kPairChunks];
-#pragma unroll
-        for (int i = 0; i < kPairChunks; ++i) valid[i] = n0 + ((e0 + i * kPairGroupThreads) >> 2) < p.n;
-        auto load_w = [&](int st, uint4 (&dst)[kPairChunks]) {
-#pragma unroll
-            for (int i = 0; i < kPairChunks; ++i) {
-                if (valid[i] && st < nst)
-                    dst[i] = __ldg(reinterpret_cast<const uint4*>(w_src + (int64_t)st * kb_stride + (int64_t)i * kPairGroupThreads * 16));
-                else
-                    dst[i] = make_uint4(0u, 0u, 0u, 0u);
-            }
-        };
-        uint4 cur[kPairChunks], nxt[kPairChunks];
-        load_w(group, cur);
-        load_w(group + kPairGroups, nxt);
+        const bool is_float = p.out_type >= RNS_OUT_F16;
+        const float rs_all = (is_float && p.row_scale_stride == 0) ? p.row_scale[0] : 0.0f;
+        float biggest = 0.0f;
         bool ok = true;
-        // In the very first stages every group must have zeroed its accumulator share
-        // before any MMA runs: both groups' first arrivals come after their zeroing, and
-        // the issuers of stage 0 and 1 each wait for one of them - but an MMA of stage 0
-        // writes columns that the other group zeroes.  So the groups meet once here.
-        asm volatile("bar.sync 1, %0;" ::"n"(kPairEncWarps * 32) : "memory");
-        for (int st = group; st < nst && ok; st += kPairGroups) {
-            const int s = st % ES;
-            uint4 ahead[kPairChunks];
-            load_w(st + 2 * kPairGroups, ahead);
-            long long pt = PT_NOW();
-            if (st >= ES)
-                ok = warp_wait_bounded(smem_addr(&ctl.done[(st - ES) & (kDoneRing - 1)]),
-                                       (uint32_t)((st - ES) >> 3) & 1u, abort, wait_code(8, st));
-            if (threadIdx.x == 64) PT_ADD(8, pt);
-            pt = PT_NOW();
-            if (!ok) break;
-            uint8_t* dst = tiles_ptr + (size_t)s * kOpStage + (size_t)e0 * 16;
+        int g0 = 0, ti = 0;
+        for (int tile = cluster; tile < tiles && ok; tile += clusters, ++ti, g0 += nst) {
+            const PairTile t = pair_tile<TOK>(p, tile, rank);
+            const int n0 = t.n0, tok0 = t.tok0;
+            // -------- weight encoding: this group's stages of the tile --------
+            const int8_t* w_src = p.w + (int64_t)n0 * kPackK + (int64_t)e0 * 16;
+            bool valid[kPairChunks];
 #pragma unroll
-            for (int i = 0; i < kPairChunks; ++i) {
-                const uint4 x = cur[i];
-                const uint32_t u0 = x.x ^ 0x80808080u, u1 = x.y ^ 0x80808080u;
-                const uint32_t u2 = x.z ^ 0x80808080u, u3 = x.w ^ 0x80808080u;
-                const uint32_t d0 = fold_pattern(x.x), d1 = fold_pattern(x.y);
-                const uint32_t d2 = fold_pattern(x.z), d3 = fold_pattern(x.w);
+            for (int i = 0; i < kPairChunks; ++i) valid[i] = n0 + ((e0 + i * kPairGroupThreads) >> 2) < p.n;
+            auto load_w = [&](int st, uint4 (&dst)[kPairChunks]) {
 #pragma unroll
-                for (int c = 0; c < R; ++c) {
-                    uint4 y;
-                    y.x = encode_word_reduced(u0, d0, mfold[c]);
-                    y.y = encode_word_reduced(u1, d1, mfold[c]);
-                    y.z = encode_word_reduced(u2, d2, mfold[c]);
-                    y.w = encode_word_reduced(u3, d3, mfold[c]);
-                    *reinterpret_cast<uint4*>(dst + (size_t)i * kPairGroupThreads * 16 + (size_t)c * kPairOpTile) = y;
+                for (int i = 0; i < kPairChunks; ++i) {
+                    if (valid[i] && st < nst)
+                        dst[i] = __ldg(reinterpret_cast<const uint4*>(w_src + (int64_t)st * kb_stride + (int64_t)i * kPairGroupThreads * 16));
+                    else
+                        dst[i] = make_uint4(0u, 0u, 0u, 0u);
+                }
+            };
+            const int st_first = (g0 + group) & 1;             // stages with g = group (mod 2)
+            uint4 cur[kPairChunks], nxt[kPairChunks];
+            load_w(st_first, cur);
+            load_w(st_first + kPairGroups, nxt);
+            for (int st = st_first; st < nst && ok; st += kPairGroups) {
+                const int g = g0 + st;
+                const int s = g % ES;
+                uint4 ahead[kPairChunks];
+                load_w(st + 2 * kPairGroups, ahead);
+                if (g >= ES)
+                    ok = warp_wait_bounded(smem_addr(&ctl.done[(g - ES) & (kDoneRing - 1)]),
+                                           (uint32_t)((g - ES) >> 3) & 1u, abort, wait_code(8, g));
+                if (!ok) break;
+                uint8_t* dst = tiles_ptr + (size_t)s * kOpStage + (size_t)e0 * 16;
+#pragma unroll
+                for (int i = 0; i < kPairChunks; ++i) {
+                    const uint4 x = cur[i];
+                    const uint32_t u0 = x.x ^ 0x80808080u, u1 = x.y ^ 0x80808080u;
+                    const uint32_t u2 = x.z ^ 0x80808080u, u3 = x.w ^ 0x80808080u;
+                    const uint32_t d0 = fold_pattern(x.x), d1 = fold_pattern(x.y);
+                    const uint32_t d2 = fold_pattern(x.z), d3 = fold_pattern(x.w);
+#pragma unroll
+                    for (int c = 0; c < R; ++c) {
+                        uint4 y;
+                        y.x = encode_word_reduced(u0, d0, mfold[c]);
+                        y.y = encode_word_reduced(u1, d1, mfold[c]);
+                        y.z = encode_word_reduced(u2, d2, mfold[c]);
+                        y.w = encode_word_reduced(u3, d3, mfold[c]);
+                        *reinterpret_cast<uint4*>(dst + (size_t)i * kPairGroupThreads * 16 + (size_t)c * kPairOpTile) = y;
+                    }
+                }
+#pragma unroll
+                for (int i = 0; i < kPairChunks; ++i) { cur[i] = nxt[i]; nxt[i] = ahead[i]; }
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                    if (rank == 0) mbar_arrive(smem_addr(&ctl.full_op[s]));
+                    else mbar_arrive_remote_relaxed(smem_addr(&ctl.full_op[s]), 0);
                 }
             }
-#pragma unroll
-            for (int i = 0; i < kPairChunks; ++i) { cur[i] = nxt[i]; nxt[i] = ahead[i]; }
-            fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0) {
-                if (rank == 0) mbar_arrive(smem_addr(&ctl.full_op[s]));
-                else mbar_arrive_remote_relaxed(smem_addr(&ctl.full_op[s]), 0);
-            }
-            if (threadIdx.x == 64) PT_ADD(9, pt);
-        }
 
-        // ------------------------------ epilogue (feature-major) ------------------
-        long long pt_epi = PT_NOW();
-        if (ok) ok = warp_wait_bounded(smem_addr(&ctl.acc_full), 0, abort, wait_code(11, 0));
-        if (threadIdx.x == 64) PT_ADD(10, pt_epi);
-        pt_epi = PT_NOW();
-        if (ok) {
+            // -------- epilogue of the tile (feature-major) --------
+            if (ok) ok = warp_wait_bounded(smem_addr(&ctl.acc_full), (uint32_t)ti & 1u, abort, wait_code(11, ti));
+            if (!ok) break;
             tc_fence_after();
-            const int quarter = warp & 3;                      // tensor-memory lanes 32*quarter .. +31
-            const int part = (warp - 2) >> 2;                  // quarter of the token columns
             const int feat = n0 + quarter * 32 + lane;
             const bool feat_ok = feat < p.n;
-            const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
-            const bool is_float = p.out_type >= RNS_OUT_F16;
             float cs = 0.0f, bs = 0.0f;
             if (is_float && feat_ok) {
                 cs = p.col_scale[feat];
                 if (p.bias != nullptr) bs = p.bias[feat];
             }
-            const float rs_all = (is_float && p.row_scale_stride == 0) ? p.row_scale[0] : 0.0f;
             using XInt = typename std::conditional<(R <= 4), int, long long>::type;
-            float biggest = 0.0f;
             constexpr int kColsPerPart = TOK / 4;
             // Two-byte outputs leave in pairs: lanes 2j and 2j+1 hold neighbouring features,
             // the even lane stores both features of the even tokens, the odd lane those of the
@@ -335,44 +357,44 @@ rns_gemm_pair_kernel(const __grid_constant__ PairParams p) {
                 if (tok_first >= p.m) return;                  // warp-uniform
                 XInt xv[8];
 #pragma unroll
-                for (int t = 0; t < 8; ++t) {
+                for (int t8 = 0; t8 < 8; ++t8) {
                     int one[R];
 #pragma unroll
-                    for (int c = 0; c < R; ++c) one[c] = acc[c][t];
-                    if constexpr (R <= 4) xv[t] = reconstruct32<R>(one, p.plan, R);
-                    else xv[t] = reconstruct<R>(one, p.plan, R);
+                    for (int c = 0; c < R; ++c) one[c] = acc[c][t8];
+                    if constexpr (R <= 4) xv[t8] = reconstruct32<R>(one, p.plan, R);
+                    else xv[t8] = reconstruct<R>(one, p.plan, R);
                 }
                 const int valid_t = min(8, p.m - tok_first);   // warp-uniform
                 if (!is_float) {
                     if (!feat_ok) return;
 #pragma unroll
-                    for (int t = 0; t < 8; ++t) {
-                        if (t < valid_t) {
-                            const int64_t o = (int64_t)(tok_first + t) * p.ldo + feat;
-                            if (p.out_type == RNS_OUT_INT64) static_cast<long long*>(p.out)[o] = (long long)xv[t];
-                            else static_cast<int*>(p.out)[o] = (int)xv[t];
+                    for (int t8 = 0; t8 < 8; ++t8) {
+                        if (t8 < valid_t) {
+                            const int64_t o = (int64_t)(tok_first + t8) * p.ldo + feat;
+                            if (p.out_type == RNS_OUT_INT64) static_cast<long long*>(p.out)[o] = (long long)xv[t8];
+                            else static_cast<int*>(p.out)[o] = (int)xv[t8];
                         }
                     }
                     return;
                 }
                 float y[8];
 #pragma unroll
-                for (int t = 0; t < 8; ++t) {
+                for (int t8 = 0; t8 < 8; ++t8) {
                     float xf;
-                    if constexpr (R <= 4) xf = __int2float_rn(xv[t]);
-                    else xf = __ll2float_rn(xv[t]);
-                    const float rs = p.row_scale_stride == 0 ? rs_all : (t < valid_t ? p.row_scale[tok_first + t] : 0.0f);
+                    if constexpr (R <= 4) xf = __int2float_rn(xv[t8]);
+                    else xf = __ll2float_rn(xv[t8]);
+                    const float rs = p.row_scale_stride == 0 ? rs_all : (t8 < valid_t ? p.row_scale[tok_first + t8] : 0.0f);
                     float v = __fmul_rn(__fmul_rn(xf, rs), cs);
                     if (p.bias != nullptr) v = __fadd_rn(v, bs);
-                    y[t] = v;
+                    y[t8] = v;
                 }
                 if (p.out_type == RNS_OUT_F32) {
                     if (!feat_ok) return;
 #pragma unroll
-                    for (int t = 0; t < 8; ++t) {
-                        if (t < valid_t) {
-                            static_cast<float*>(p.out)[(int64_t)(tok_first + t) * p.ldo + feat] = y[t];
-                            biggest = fmaxf(biggest, fabsf(y[t]));
+                    for (int t8 = 0; t8 < 8; ++t8) {
+                        if (t8 < valid_t) {
+                            static_cast<float*>(p.out)[(int64_t)(tok_first + t8) * p.ldo + feat] = y[t8];
+                            biggest = fmaxf(biggest, fabsf(y[t8]));
                         }
                     }
                     return;
@@ -380,15 +402,15 @@ rns_gemm_pair_kernel(const __grid_constant__ PairParams p) {
                 // fp16 / bf16: the stored bit patterns, and their magnitudes for the absmax word
                 unsigned short h[8];
 #pragma unroll
-                for (int t = 0; t < 8; ++t) {
+                for (int t8 = 0; t8 < 8; ++t8) {
                     if (p.out_type == RNS_OUT_F16) {
-                        const __half v = __float2half_rn(y[t]);
-                        h[t] = __half_as_ushort(v);
-                        if (t < valid_t && feat_ok) biggest = fmaxf(biggest, fabsf(__half2float(v)));
+                        const __half v = __float2half_rn(y[t8]);
+                        h[t8] = __half_as_ushort(v);
+                        if (t8 < valid_t && feat_ok) biggest = fmaxf(biggest, fabsf(__half2float(v)));
                     } else {
-                        const __nv_bfloat16 v = __float2bfloat16_rn(y[t]);
-                        h[t] = __bfloat16_as_ushort(v);
-                        if (t < valid_t && feat_ok) biggest = fmaxf(biggest, fabsf(__bfloat162float(v)));
+                        const __nv_bfloat16 v = __float2bfloat16_rn(y[t8]);
+                        h[t8] = __bfloat16_as_ushort(v);
+                        if (t8 < valid_t && feat_ok) biggest = fmaxf(biggest, fabsf(__bfloat162float(v)));
                     }
                 }
                 unsigned short* out16 = static_cast<unsigned short*>(p.out);
@@ -400,17 +422,17 @@ rns_gemm_pair_kernel(const __grid_constant__ PairParams p) {
                         const unsigned mine = odd ? h[2 * i + 1] : h[2 * i];
                         const unsigned send = odd ? h[2 * i] : h[2 * i + 1];
                         const unsigned got = __shfl_xor_sync(0xffffffffu, send, 1);
-                        const int t = 2 * i + (odd ? 1 : 0);
-                        if (t < valid_t) {
+                        const int t8 = 2 * i + (odd ? 1 : 0);
+                        if (t8 < valid_t) {
                             const unsigned word = odd ? (got | (mine << 16)) : (mine | (got << 16));
-                            const int64_t o = (int64_t)(tok_first + t) * p.ldo + (feat & ~1);
+                            const int64_t o = (int64_t)(tok_first + t8) * p.ldo + (feat & ~1);
                             *reinterpret_cast<unsigned*>(out16 + o) = word;
                         }
                     }
                 } else if (feat_ok) {
 #pragma unroll
-                    for (int t = 0; t < 8; ++t)
-                        if (t < valid_t) out16[(int64_t)(tok_first + t) * p.ldo + feat] = h[t];
+                    for (int t8 = 0; t8 < 8; ++t8)
+                        if (t8 < valid_t) out16[(int64_t)(tok_first + t8) * p.ldo + feat] = h[t8];
                 }
             };
             const int col0 = part * kColsPerPart;
@@ -440,12 +462,16 @@ rns_gemm_pair_kernel(const __grid_constant__ PairParams p) {
                     finish(col0 + it * 8, acc);
                 }
             }
-            if (p.absmax_out != nullptr && is_float) {
+            // Every column this warp read belongs to channel blocks c*TOK + [col0, col0 + TOK/4);
+            // the columns it ZEROES are its 128-column block.  All sixteen warps have to be
+            // done reading before anyone's zeroes may land on columns another warp still reads.
+            asm volatile("bar.sync 1, %0;" ::"n"(kPairEncWarps * 32) : "memory");
+            zero_and_release();
+        }
+        if (p.absmax_out != nullptr && is_float) {
 #pragma unroll
-                for (int o = 16; o > 0; o >>= 1) biggest = fmaxf(biggest, __shfl_xor_sync(0xffffffffu, biggest, o));
-                if (lane == 0) atomicMax(&ctl.absmax, __float_as_uint(biggest));
-            }
-            if (threadIdx.x == 64) PT_ADD(11, pt_epi);
+            for (int o = 16; o > 0; o >>= 1) biggest = fmaxf(biggest, __shfl_xor_sync(0xffffffffu, biggest, o));
+            if (lane == 0) atomicMax(&ctl.absmax, __float_as_uint(biggest));
         }
     }
 
@@ -453,9 +479,10 @@ rns_gemm_pair_kernel(const __grid_constant__ PairParams p) {
     // Nothing may still be on its way to this CTA's barriers when it leaves: the last
     // stages' commits are waited for here (nobody else waits for them).
     if (warp == 1 && lane == 0 && !*abort) {
-        for (int st = nst > kDoneRing ? nst - kDoneRing : 0; st < nst; ++st)
-            if (!wait_bounded(smem_addr(&ctl.done[st & (kDoneRing - 1)]), (uint32_t)(st >> 3) & 1u, abort,
-                              wait_code(12, st)))
+        const int total = ((tiles - cluster + clusters - 1) / clusters) * nst;
+        for (int g = total > kDoneRing ? total - kDoneRing : 0; g < total; ++g)
+            if (!wait_bounded(smem_addr(&ctl.done[g & (kDoneRing - 1)]), (uint32_t)(g >> 3) & 1u, abort,
+                              wait_code(12, g)))
                 break;
     }
     tc_fence_before();
@@ -487,18 +514,13 @@ template <int R, int TOK, int ES, int PS>
 static int launch_pair(const PairParams& pp, int pairs, cudaStream_t st) {
     constexpr size_t smem = (size_t)ES * R * kPairOpTile + (size_t)PS * R * (TOK / 2) * kPackK + 1024;
     static_assert(smem + sizeof(PairCtl) <= 227 * 1024, "rings exceed shared memory");
-    static std::atomic<uint64_t> configured{0};
+    // Per device: the opt-in shared-memory size, and how many clusters of two CTAs the GPU
+    // holds at once (one CTA per SM; a GPC with an odd number of SMs leaves one unpaired).
+    static std::atomic<int> resident[64];
     int dev = 0;
     RNS_CUDA_OK(cudaGetDevice(&dev));
-    const uint64_t bit = 1ull << (dev & 63);
-    if (!(configured.load(std::memory_order_acquire) & bit)) {
-        RNS_CUDA_OK(cudaFuncSetAttribute(rns_gemm_pair_kernel<R, TOK, ES, PS>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        configured.fetch_or(bit, std::memory_order_release);
-    }
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
-    cfg.gridDim = dim3((unsigned)(2 * pairs), 1, 1);
     cfg.blockDim = dim3(kPairThreads, 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
@@ -509,11 +531,27 @@ static int launch_pair(const PairParams& pp, int pairs, cudaStream_t st) {
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
+    int clusters = resident[dev & 63].load(std::memory_order_acquire);
+    if (clusters == 0) {
+        RNS_CUDA_OK(cudaFuncSetAttribute(rns_gemm_pair_kernel<R, TOK, ES, PS>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        int sms = 0;
+        RNS_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+        cfg.gridDim = dim3((unsigned)(sms & ~1), 1, 1);
+        if (cudaOccupancyMaxActiveClusters(&clusters, rns_gemm_pair_kernel<R, TOK, ES, PS>, &cfg) != cudaSuccess ||
+            clusters < 1) {
+            cudaGetLastError();
+            clusters = sms / 2 > 8 ? sms / 2 - 4 : 1;          // a safe guess: a few SMs short of all
+        }
+        resident[dev & 63].store(clusters, std::memory_order_release);
+    }
+    if (clusters > pairs) clusters = pairs;
+    cfg.gridDim = dim3((unsigned)(2 * clusters), 1, 1);
     const cudaError_t rc = cudaLaunchKernelEx(&cfg, rns_gemm_pair_kernel<R, TOK, ES, PS>, pp);
     if (rc != cudaSuccess) {
         cudaGetLastError();
-        return fail(RNS_ERR_CUDA, "launch of the paired RNS GEMM failed: %s (%d pairs, smem %zu)",
-                    cudaGetErrorString(rc), pairs, smem);
+        return fail(RNS_ERR_CUDA, "launch of the paired RNS GEMM failed: %s (%d clusters for %d tiles, smem %zu)",
+                    cudaGetErrorString(rc), clusters, pairs, smem);
     }
     return RNS_OK;
 }
@@ -557,13 +595,5 @@ int launch_pair_gemm(const rns_linear_args* a, const Plan& plan, cudaStream_t st
     if (R == 4) return launch_pair<4, 128, 4, 6>(pp, (int)pairs, st);
     return launch_pair<5, 96, 4, 4>(pp, (int)pairs, st);
 }
-
-#ifdef RNS_PAIR_TIMING
-extern "C" __attribute__((visibility("default"))) int rns_debug_pair_timing(long long* host32, int reset) {
-    if (host32 && cudaMemcpyFromSymbol(host32, g_pair_dbg, sizeof(long long) * 32) != cudaSuccess) return 1;
-    if (reset) { long long z[32] = {0}; if (cudaMemcpyToSymbol(g_pair_dbg, z, sizeof(z)) != cudaSuccess) return 1; }
-    return 0;
-}
-#endif
 
 }  // namespace rns
