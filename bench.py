@@ -58,8 +58,8 @@ def channel_ops_per_step(tokens: int, layers: int) -> float:
 
 # Mean DRAM traffic of one rns_gemm_kernel launch of this workload on one GPU
 # (dram__bytes_read.sum + dram__bytes_write.sum over the four linears of a layer:
-# 271 + 98 + 505 + 1114 MB), from an ncu capture of `bench.py --layers 2`.
-NCU_DRAM_BYTES_PER_LAUNCH = 496.9e6
+# 286 + 99 + 362 + 1153 MB), from an ncu capture of `bench.py --layers 2`.
+NCU_DRAM_BYTES_PER_LAUNCH = 475.1e6
 
 
 def algorithmic_bytes_per_launch(tokens: int) -> float:
@@ -687,7 +687,10 @@ def _run_layer_stack(args, backend, rank, world, local_rank, device) -> None:
         if not args.no_peak:
             int8_measured = measure_int8_peak(device)
         int8_peak = int8_measured["sustained"] if int8_measured else two_bf16
-        launches_per_linear = 3          # absmax + quantise/encode + fused GEMM
+        # Kernels of this library per step: per linear one quantise/encode launch and one fused
+        # GEMM; an absmax pass only where the input does not carry the previous layer's
+        # absmax word (the q view that feeds out_proj, and the step's very first input).
+        launches_per_step = args.layers * (2 * len(LINEARS) + 1) + 1
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
@@ -696,7 +699,7 @@ def _run_layer_stack(args, backend, rank, world, local_rank, device) -> None:
             "useful_tops": useful_ops_per_step(args.tokens, args.layers) / (ms_per_step * 1e-3) / 1e12,
             "tokens_per_s": args.tokens / (ms_per_step * 1e-3),
             "roofline": {
-                "bound": "tensor", "kernel": "rns_gemm_kernel", "achieved": achieved, "peak": int8_peak,
+                "bound": "tensor", "kernel": "rns_gemm_pair_kernel", "achieved": achieved, "peak": int8_peak,
                 "unit": "TOPS", "frac": None if achieved is None else achieved / int8_peak,
                 "peak_source": ("torch._int_mm 8192^3 back to back on this GPU in this run (sustained, under the "
                                 "power cap)" if int8_measured else
@@ -715,7 +718,7 @@ def _run_layer_stack(args, backend, rank, world, local_rank, device) -> None:
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms / args.steps,
                     "h2d_bytes_per_step": int(host_x.numel() * 2), "d2h_bytes_per_step": int(host_y.numel() * 2)},
-            "gpu_launches": int(len(LINEARS) * args.layers * launches_per_linear * args.steps),
+            "gpu_launches": int(launches_per_step * args.steps),
         }
         if args.gpu_baselines and world == 1:
             line["gpu_baselines"] = gpu_library_baselines(args.tokens, args.layers, device)

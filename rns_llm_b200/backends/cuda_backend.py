@@ -925,6 +925,11 @@ class CudaRNSBackend:
             return out, (AdaptiveMetadata(meta) if meta is not None else None)
         return out
 
+    def supports_absmax_out(self, *, m: int, k: int, channels: int) -> bool:
+        """True when ``linear_forward`` runs the many-token kernel for this problem, the one
+        whose epilogue can report max |y| (``absmax_out``)."""
+        return m >= PLANES_MIN_ROWS and int(self._lib.rns_pair_tile_rows(int(channels), int(k))) > 0
+
     def quantize_weight(self, weight: torch.Tensor, quant_max: int = 127
                         ) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
         """Per-output-channel symmetric int8 of an nn.Linear weight [N,K]

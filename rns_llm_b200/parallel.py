@@ -13,6 +13,14 @@ as a [G, M, N/G] tensor.  The next sharded layer reads that layout directly
 column c % (N/G)), so a layer stack never pays a transposing copy; ``unshard``
 produces the ordinary [M, N] matrix when a caller needs it.
 
+A layer also passes on the absmax of what it produced: every rank's GEMM epilogue
+leaves max |y| of its shard in a word that travels at the end of the rank's block of
+the gathered buffer, and the next sharded layer hands those G words to its quantiser,
+which then skips its own pass over the activations (the reference recomputes the
+per-tensor absmax in eager torch, src/rns_llm/layers/rns_linear.py:239-240).  Only a
+tensor returned by ``forward`` itself carries the words; a view of part of it (one of
+q, k, v) does not, because its absmax is another number.
+
 Fused QKV is sharded inside each of q, k and v (rank g owns rows
 [q_g; k_g; v_g]), so that the three projections of the gathered result are
 again plain column blocks.
@@ -54,6 +62,24 @@ def unshard(gathered: torch.Tensor, groups: int = 1) -> torch.Tensor:
     per = local // groups
     # gathered[g, m, j*per + c] is column  j*(world*per) + g*per + c  of the full output
     return gathered.view(world, m, groups, per).permute(1, 2, 0, 3).reshape(m, groups * world * per)
+
+
+ABSMAX_PAD = 8      # elements kept free behind each rank's block of a gathered buffer (>= 4 bytes, 16-byte multiple)
+
+
+class GatheredActivation(torch.Tensor):
+    """A gathered [G, M, N/G] output that knows where the G absmax words of its blocks
+    are: ``absmax_words`` = (device address of rank 0's word, G, distance in 4-byte
+    words).  Views and results of other operations are plain tensors again."""
+
+    absmax_words: tuple[int, int, int] | None = None
+
+    @classmethod
+    def __torch_function__(cls, func, types, args=(), kwargs=None):
+        # Anything computed from it (views included) is a plain tensor without the words.
+        with torch._C.DisableTorchFunctionSubclass():
+            result = func(*args, **(kwargs or {}))
+        return result
 
 
 def group_view(gathered: torch.Tensor, groups: int, index: int) -> torch.Tensor:
@@ -112,13 +138,17 @@ class ColumnShardedRNSLinear(nn.Module):
                    groups=groups, activation_scale=activation_scale)
 
     def _buffer(self, m: int, dtype: torch.dtype, device: torch.device) -> torch.Tensor:
+        """Flat [G, M*N/G + ABSMAX_PAD] buffer: each rank's block is its [M, N/G] shard
+        followed by a few spare elements, the first four bytes of which hold the shard's
+        absmax word."""
+        block = m * self.local_features + ABSMAX_PAD
         if not self.reuse_buffer:
-            return torch.empty((self.world, m, self.local_features), dtype=dtype, device=device)
+            return torch.empty((self.world, block), dtype=dtype, device=device)
         stream = int(torch.cuda.current_stream(device).cuda_stream)
         key = (m, dtype, stream)
         buf = self._gather_buffers.get(key)
         if buf is None:
-            buf = torch.empty((self.world, m, self.local_features), dtype=dtype, device=device)
+            buf = torch.empty((self.world, block), dtype=dtype, device=device)
             self._gather_buffers[key] = buf
         return buf
 
@@ -130,17 +160,37 @@ class ColumnShardedRNSLinear(nn.Module):
         else:
             flat = x.reshape(-1, self.in_features)
             m = int(flat.shape[0])
-        gathered = out if out is not None else self._buffer(m, flat.dtype, flat.device)
+        absmax_in = getattr(x, "absmax_words", None) if isinstance(x, GatheredActivation) else None
+        if absmax_in is not None and self.per_row:
+            absmax_in = None
+        if out is not None:
+            # Caller-owned [G, M, N/G] memory: no room for the absmax words.
+            local = out[self.rank]
+            self.backend.linear_forward(flat, self.prepared, self.weight_scale, self.bias,
+                                        per_row=self.per_row, out=local, absmax_in=absmax_in)
+            if gather and self.world > 1:
+                dist.all_gather_into_tensor(out.view(self.world * m, self.local_features), local, group=self.group)
+            return out if gather else local
+        buf = self._buffer(m, flat.dtype, flat.device)
+        count = m * self.local_features
+        gathered = buf[:, :count].view(self.world, m, self.local_features)      # stride(0) = count + pad
         local = gathered[self.rank]
+        report = (not self.per_row) and self.backend.supports_absmax_out(m=m, k=self.in_features,
+                                                                         channels=len(self.moduli))
+        word = buf[self.rank, count:].data_ptr() if report else None
         self.backend.linear_forward(flat, self.prepared, self.weight_scale, self.bias,
-                                    per_row=self.per_row, out=local)
+                                    per_row=self.per_row, out=local, absmax_in=absmax_in, absmax_out=word)
         if not gather:
             return local
         if self.world > 1:
-            # In place: this rank's shard already sits at its slot of the output.
-            dist.all_gather_into_tensor(gathered.view(self.world * m, self.local_features), local,
-                                        group=self.group)
-        return gathered
+            # In place: this rank's block (shard + absmax word) already sits at its slot.
+            dist.all_gather_into_tensor(buf.view(-1), buf[self.rank], group=self.group)
+        if not report:
+            return gathered
+        result = gathered.as_subclass(GatheredActivation)
+        result.absmax_words = (buf[0, count:].data_ptr(), self.world,
+                               (count + ABSMAX_PAD) * buf.element_size() // 4)
+        return result
 
 
 def sharded_qkv_from_linears(q_proj: nn.Linear, k_proj: nn.Linear, v_proj: nn.Linear, *, backend, moduli,

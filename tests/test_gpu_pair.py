@@ -118,3 +118,34 @@ def test_absmax_word_feeds_the_next_quantiser(backend):
     backend.check_status()
     with pytest.raises(ValueError):
         backend.linear_forward(x[:64], p1, s1, None, absmax_out=words.data_ptr())
+
+
+def test_sharded_layers_pass_the_absmax_on(backend):
+    """A chain of column-sharded layers (one rank, so no process group is needed) gives the
+    same bits whether the second layer scans its input for the absmax or takes the word the
+    first layer's epilogue left behind; a column-group view does not carry the word."""
+    from rns_llm_b200.parallel import ColumnShardedRNSLinear, GatheredActivation, group_view
+
+    torch.manual_seed(21)
+    m, k = 1024, 1024
+    x = torch.randn(m, k, dtype=torch.float16, device="cuda")
+    w1 = (torch.randn(1536, k, device="cuda") * 0.04).half()
+    w2 = (torch.randn(768, 1536, device="cuda") * 0.04).half()
+    w3 = (torch.randn(640, 512, device="cuda") * 0.04).half()
+    l1 = ColumnShardedRNSLinear(w1, None, backend=backend, moduli=C0, rank=0, world=1, groups=3)
+    l2 = ColumnShardedRNSLinear(w2, None, backend=backend, moduli=C0, rank=0, world=1)
+    l3 = ColumnShardedRNSLinear(w3, None, backend=backend, moduli=C0, rank=0, world=1)
+    y1 = l1(x)
+    assert isinstance(y1, GatheredActivation) and y1.absmax_words is not None and y1.absmax_words[1] == 1
+    y2 = l2(y1)                                   # takes the word
+    y2_plain = l2(y1.as_subclass(torch.Tensor))   # scans the activations itself
+    torch.cuda.synchronize()
+    assert torch.equal(y2.as_subclass(torch.Tensor), y2_plain.as_subclass(torch.Tensor))
+    q = group_view(y1, 3, 0)
+    assert not isinstance(q, GatheredActivation)
+    y3 = l3(q)
+    expect = O.rns_linear_forward(q.permute(1, 0, 2).reshape(m, 512).cpu().numpy(), w3.cpu().numpy(), None, C0)["y"]
+    assert np.array_equal(y3[0].cpu().numpy().view(np.uint16), expect.view(np.uint16))
+    expect2 = O.rns_linear_forward(y1[0].cpu().numpy(), w2.cpu().numpy(), None, C0)["y"]
+    assert np.array_equal(y2[0].cpu().numpy().view(np.uint16), expect2.view(np.uint16))
+    backend.check_status()

@@ -101,7 +101,11 @@ class _FakeBackend:
     def prepare_weight_nk(self, w_q, moduli):
         return _FakePrepared(w_q)
 
-    def linear_forward(self, x, prepared, weight_scale, bias, *, per_row=False, out=None):
+    def supports_absmax_out(self, *, m, k, channels):
+        return False
+
+    def linear_forward(self, x, prepared, weight_scale, bias, *, per_row=False, out=None, absmax_in=None,
+                       absmax_out=None):
         if x.ndim == 3:
             x = unshard(x.contiguous(), 1)
         s_a = x.float().abs().amax().clamp_min(1e-8) / 127.0
