@@ -359,13 +359,87 @@ def gpu_library_baselines(tokens: int, layers: int, device) -> dict:
     return out
 
 
+def _reference_package():
+    """The unmodified reference (its Python package and its CUDA extension built for this
+    GPU) when it is installed under baseline/_ref, else None with the reason."""
+    root = ROOT / "baseline" / "_ref"
+    if not (root / "rns_llm").is_dir():
+        return None, "the reference is not installed under baseline/_ref"
+    if str(root) not in sys.path:
+        sys.path.insert(0, str(root))
+    try:
+        import rns_llm  # noqa: F401
+        from rns_llm.backends import cuda_backend as module
+        if not module.cuda_extension_available():
+            return None, "the reference's CUDA extension is not built"
+        return module, ""
+    except Exception as exc:       # an import problem must not lose the other columns
+        return None, f"{type(exc).__name__}: {exc}"
+
+
+def _median_us(fn, iters: int, warm: int) -> float:
+    import torch
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(iters):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(); fn(); b.record()
+        b.synchronize()
+        times.append(a.elapsed_time(b) * 1e3)
+    return statistics.median(times)
+
+
+def _graph_us(fn, iters: int, warm: int):
+    """The same call replayed from a CUDA graph (device time without the host's share)."""
+    import torch
+    try:
+        side = torch.cuda.Stream()
+        with torch.cuda.stream(side):
+            for _ in range(3):
+                fn()
+        side.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            fn()
+        return _median_us(graph.replay, iters, warm)
+    except Exception as exc:   # graph capture is an extra, not the measurement
+        return f"capture failed: {type(exc).__name__}"
+
+
+def _int8_library_linear(weights, biases):
+    """Native int8 baseline on the same tensors: per-tensor activation quantisation in eager
+    torch, torch._int_mm on the concatenated int8 weight (rows padded to 32: the library GEMM
+    refuses fewer than 17), fp32 dequantisation with the same scales, bias, cast."""
+    import torch
+    w = torch.cat(weights, dim=0).float()
+    scale = w.abs().amax(dim=1).clamp_min(1e-8) / 127.0
+    wq = torch.clamp(torch.round(w / scale[:, None]), -127, 127).to(torch.int8).t().contiguous()
+    bias = torch.cat(biases).float()
+
+    def run(x):
+        flat = x.reshape(-1, x.shape[-1]).float()
+        s_a = flat.abs().amax().clamp_min(1e-8) / 127.0
+        xq = torch.clamp(torch.round(flat / s_a), -127, 127).to(torch.int8)
+        rows = xq.shape[0]
+        if rows < 32:
+            xq = torch.nn.functional.pad(xq, (0, 0, 0, 32 - rows))
+        acc = torch._int_mm(xq, wq)[:rows]
+        return (acc.float() * s_a * scale + bias).to(x.dtype)
+    return run
+
+
 def run_fused_qkv_latency(args) -> None:
     """Configuration 1 of BASELINE.json: hidden 768, three nn.Linear(768, 768) fused into
-    one RNS QKV projection, M in {1, 16, 128, 256} tokens (the shapes of the reference's
-    benchmarks/benchmark_qkv_fusion.py:60-90).  Prints one JSON line with, per M, the
-    latency of the fused module call, of three separate RNSLinear calls and of the same
-    fused call replayed from a CUDA graph (CUDA events, median of `iters` calls)."""
+    one RNS QKV projection, M in {1, 16, 128, 256} tokens (the shapes and the protocol of the
+    reference's benchmarks/benchmark_qkv_fusion.py:60-90).  One JSON line with, per M, the
+    median latency (CUDA events) of: the fused module call, three separate RNSLinear calls,
+    the fused call replayed from a CUDA graph, and as baselines on the same GPU and tensors:
+    fp16 F.linear on the concatenated weight, native int8 (torch._int_mm + eager quantise /
+    dequantise) and the unmodified reference's fused-QKV module on its own CUDA path."""
     import torch
+    import torch.nn.functional as F
     from torch import nn
     from rns_llm_b200.backends import CudaRNSBackend
     from rns_llm_b200.layers import RNSLinear, RNSQKVProjection
@@ -384,19 +458,16 @@ def run_fused_qkv_latency(args) -> None:
         linears.append(layer)
     fused = RNSQKVProjection.from_linears(*linears, backend=backend, mode="rns", moduli=MODULI_4).eval()
     separate = [RNSLinear.from_linear(l, backend=backend, mode="rns", moduli=MODULI_4).eval() for l in linears]
-    iters = max(20, args.steps * 20)
-
-    def median_us(fn) -> float:
-        for _ in range(max(args.warmup, 3) * 5):
-            fn()
-        torch.cuda.synchronize()
-        times = []
-        for _ in range(iters):
-            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            a.record(); fn(); b.record()
-            b.synchronize()
-            times.append(a.elapsed_time(b) * 1e3)
-        return statistics.median(times)
+    w_cat = torch.cat([l.weight.detach() for l in linears], dim=0)
+    b_cat = torch.cat([l.bias.detach() for l in linears], dim=0)
+    int8_linear = _int8_library_linear([l.weight.detach() for l in linears], [l.bias.detach() for l in linears])
+    ref_module, ref_why = _reference_package()
+    ref_fused = None
+    if ref_module is not None:
+        from rns_llm.layers import RNSQKVProjection as RefQKV
+        ref_backend = ref_module.CudaRNSBackend()
+        ref_fused = RefQKV.from_linears(*linears, backend=ref_backend, mode="rns", moduli=MODULI_4).eval()
+    iters, warm = max(20, args.steps * 20), max(args.warmup, 3) * 5
 
     rows = []
     with torch.no_grad():
@@ -405,33 +476,258 @@ def run_fused_qkv_latency(args) -> None:
             q, k, v = fused(x)
             ref = [layer(x) for layer in separate]
             equal = all(torch.equal(a, b) for a, b in zip((q, k, v), ref))
-            fused_us = median_us(lambda: fused(x))
-            separate_us = median_us(lambda: [layer(x) for layer in separate])
-            graph_us = None
-            try:
-                side = torch.cuda.Stream()
-                with torch.cuda.stream(side):
-                    for _ in range(3):
-                        fused(x)
-                side.synchronize()
-                graph = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(graph, stream=side):
-                    fused(x)
-                graph_us = median_us(graph.replay)
-            except Exception as exc:   # graph capture is an extra, not the measurement
-                graph_us = f"capture failed: {type(exc).__name__}"
+            row = {"tokens": tokens, "bit_equal_to_three_layers": bool(equal),
+                   "fused_us": _median_us(lambda: fused(x), iters, warm),
+                   "three_layers_us": _median_us(lambda: [layer(x) for layer in separate], iters, warm),
+                   "fused_graph_us": _graph_us(lambda: fused(x), iters, warm),
+                   "fp16_us": _median_us(lambda: F.linear(x, w_cat, b_cat), iters, warm),
+                   "fp16_graph_us": _graph_us(lambda: F.linear(x, w_cat, b_cat), iters, warm),
+                   "int_mm_us": _median_us(lambda: int8_linear(x), iters, warm),
+                   "int_mm_graph_us": _graph_us(lambda: int8_linear(x), iters, warm)}
+            if ref_fused is not None:
+                rq, rk, rv = ref_fused(x)
+                row["reference_cuda_us"] = _median_us(lambda: ref_fused(x), iters, warm)
+                row["equal_to_reference_cuda"] = bool(torch.equal(rq, q) and torch.equal(rk, k) and torch.equal(rv, v))
+            else:
+                row["reference_cuda_us"] = None
             ops = 2.0 * len(MODULI_4) * tokens * hidden * 3 * hidden
-            weight_bytes = 3 * hidden * hidden
-            rows.append({"tokens": tokens, "fused_us": fused_us, "three_layers_us": separate_us,
-                         "fused_graph_us": graph_us, "bit_equal_to_three_layers": bool(equal),
-                         "channel_tops": ops / (fused_us * 1e-6) / 1e12,
-                         "weight_stream_gbs": weight_bytes / (fused_us * 1e-6) / 1e9})
+            row["channel_tops"] = ops / (row["fused_us"] * 1e-6) / 1e12
+            row["weight_stream_gbs_graph"] = (3 * hidden * hidden / (row["fused_graph_us"] * 1e-6) / 1e9
+                                              if isinstance(row["fused_graph_us"], float) else None)
+            rows.append(row)
     backend.check_status()
     print(json.dumps({"metric": "fused_qkv_latency_us", "unit": "us", "n_gpus": 1, "higher_is_better": False,
                       "data": "synthetic", "dtype": "int8",
                       "config": {"workload": "fused_qkv_hidden768 (BASELINE.json configs[1])", "hidden": hidden,
-                                 "moduli": list(MODULI_4), "activation_scale": "per-tensor", "iters": iters},
+                                 "moduli": list(MODULI_4), "activation_scale": "per-tensor", "iters": iters,
+                                 "reference_cuda": "measured" if ref_fused is not None else f"unavailable: {ref_why}"},
                       "rows": rows}), flush=True)
+
+
+def run_concurrency(args) -> None:
+    """Configuration 2 of BASELINE.json, the protocol of the reference's
+    benchmarks/benchmark_concurrency.py:94-118 and benchmark_adaptive_channels.py: (i) 1, 2
+    and 4 requests of one token each (K = N = 768, int8) merged along M into one RNS GEMM,
+    against the same requests as independent calls on their own CUDA streams; (ii) M = 128
+    with activations in [-15, 15]: adaptive channel prefix chosen on the device (3 of 4
+    channels) against the fixed 4-channel call.  Exactness is asserted before timing."""
+    import numpy as np
+    import torch
+    from rns_llm_b200.backends import CudaRNSBackend
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; the RNS path has no CPU implementation")
+    backend = CudaRNSBackend()
+    ref_module, ref_why = _reference_package()
+    ref_backend = ref_module.CudaRNSBackend() if ref_module is not None else None
+    torch.manual_seed(1002)
+    k = n = 768
+    w = torch.randint(-127, 128, (k, n), dtype=torch.int8, device="cuda")
+    iters, warm = max(20, args.steps * 20), max(args.warmup, 3) * 5
+
+    def exact(a):
+        return torch.from_numpy(a.cpu().numpy().astype(np.int64) @ w.cpu().numpy().astype(np.int64)).cuda()
+
+    def batching_rows(be, label):
+        prepared = be.prepare_weight(w, MODULI_4)
+        rows = []
+        for count in (1, 2, 4):
+            requests = [torch.randint(-127, 128, (1, k), dtype=torch.int8, device="cuda") for _ in range(count)]
+            workspace = be.create_request_batch_workspace(device=w.device, dtype=torch.int8,
+                                                          rows_per_request=[1] * count, k=k,
+                                                          channels=len(MODULI_4), n=n)
+            merged = be.matmul_prepared_fused_requests(requests, prepared, workspace=workspace, clone_outputs=True)
+            assert all(torch.equal(o, exact(r)) for o, r in zip(merged, requests)), "merged batch is not exact"
+            streams = [torch.cuda.Stream() for _ in range(count)]
+            spaces = [be.create_workspace(device=w.device, channels=len(MODULI_4), m=1, n=n) for _ in range(count)]
+
+            def independent():
+                current = torch.cuda.current_stream()
+                for stream, req, space in zip(streams, requests, spaces):
+                    stream.wait_stream(current)
+                    with torch.cuda.stream(stream):
+                        be.matmul_prepared_fused(req, prepared, workspace=space)
+                for stream in streams:
+                    current.wait_stream(stream)
+            independent()
+            torch.cuda.synchronize()
+            merged_us = _median_us(lambda: be.matmul_prepared_fused_requests(requests, prepared, workspace=workspace),
+                                   iters, warm)
+            streams_us = _median_us(independent, iters, warm)
+            rows.append({"impl": label, "requests": count, "merged_us": merged_us, "independent_streams_us": streams_us,
+                         "merged_requests_per_s": count / (merged_us * 1e-6)})
+        return rows
+
+    def adaptive_rows(be, label):
+        prepared_full = be.prepare_weight(w, MODULI_4)
+        prepared_adaptive = be.prepare_weight_adaptive(w, MODULI_4, min_channels=3)
+        a = torch.randint(-15, 16, (128, k), dtype=torch.int8, device="cuda")
+        out, meta = be.matmul_prepared_adaptive_fused(a, prepared_adaptive, return_metadata=True)
+        assert torch.equal(out, exact(a)) and int(meta["channels"]) == 3, "adaptive prefix is wrong"
+        full = torch.randint(-127, 128, (128, k), dtype=torch.int8, device="cuda")
+        out_full, meta_full = be.matmul_prepared_adaptive_fused(full, prepared_adaptive, return_metadata=True)
+        assert torch.equal(out_full, exact(full)) and int(meta_full["channels"]) == 4
+        return {"impl": label, "tokens": 128, "selected_channels": int(meta["channels"]),
+                "adaptive_us": _median_us(lambda: be.matmul_prepared_adaptive_fused(a, prepared_adaptive), iters, warm),
+                "fixed_4_channels_us": _median_us(lambda: be.matmul_prepared_fused(a, prepared_full), iters, warm)}
+
+    batching = batching_rows(backend, "rns_b200")
+    adaptive = [adaptive_rows(backend, "rns_b200")]
+    if ref_backend is not None:
+        batching += batching_rows(ref_backend, "reference_cuda")
+        adaptive.append(adaptive_rows(ref_backend, "reference_cuda"))
+    backend.check_status()
+    print(json.dumps({"metric": "continuous_batching_and_adaptive_latency_us", "unit": "us", "n_gpus": 1,
+                      "higher_is_better": False, "data": "synthetic", "dtype": "int8",
+                      "config": {"workload": "continuous batching + adaptive channels (BASELINE.json configs[2])",
+                                 "k": k, "n": n, "moduli": list(MODULI_4), "iters": iters,
+                                 "reference_cuda": "measured" if ref_backend is not None else f"unavailable: {ref_why}"},
+                      "continuous_batching": batching, "adaptive_channels": adaptive}), flush=True)
+
+
+def run_opt_decoder(args) -> None:
+    """Configuration 3 of BASELINE.json: an OPT-125m-architecture decoder with random weights
+    (12 layers, hidden 768, 12 heads, FFN 3072, vocabulary 50272, learned positions, fp16,
+    seed 1003); fused q|k|v and out_proj of all 12 attention blocks replaced by RNS linears as
+    the reference's scripts/evaluate_ppl.py:53-94 does, softmax and FFN in fp16.  Synthetic
+    token ids uniform over the vocabulary, batch 8 x 512 tokens of prefill, then 128 greedy
+    decode steps with the key/value cache.  Three variants on the same weights: fp16, native
+    int8 (torch._int_mm on the same int8 tensors and scales in the same four linears per
+    block) and RNS.  Reports tokens/s of each and the logits error of the RNS model against
+    both; refuses to report when the RNS path did not run (stats counters, as
+    scripts/evaluate_ppl.py:212-217)."""
+    import copy
+
+    import torch
+    from torch import nn
+    from transformers import OPTConfig, OPTForCausalLM
+
+    from rns_llm_b200.backends import CudaRNSBackend
+    from rns_llm_b200.integration import replace_opt_attention_blocks, replace_selected_linears
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; the RNS path has no CPU implementation")
+    batch, prompt, new_tokens = 8, 512, 128
+    config = OPTConfig(vocab_size=50272, hidden_size=768, num_hidden_layers=12, num_attention_heads=12, ffn_dim=3072,
+                       max_position_embeddings=2048, word_embed_proj_dim=768, do_layer_norm_before=True)
+    torch.manual_seed(1003)
+    base = OPTForCausalLM(config).half().cuda().eval()
+    parameters = sum(p.numel() for p in base.parameters())
+
+    class Int8Linear(nn.Module):
+        """nn.Linear through the library int8 GEMM: per-output-channel int8 weights, per-tensor
+        int8 activations, torch._int_mm, fp32 dequantisation in the reference's order."""
+
+        def __init__(self, layer: nn.Linear) -> None:
+            super().__init__()
+            w = layer.weight.detach().float()
+            scale = w.abs().amax(dim=1).clamp_min(torch.finfo(torch.float32).eps) / 127.0
+            self.register_buffer("wq_t", torch.clamp(torch.round(w / scale[:, None]), -127, 127).to(torch.int8).t().contiguous())
+            self.register_buffer("scale", scale)
+            self.register_buffer("bias", None if layer.bias is None else layer.bias.detach().float())
+
+        def forward(self, x):
+            flat = x.reshape(-1, x.shape[-1]).float()
+            s_a = flat.abs().amax().clamp_min(torch.finfo(torch.float32).eps) / 127.0
+            xq = torch.clamp(torch.round(flat / s_a), -127, 127).to(torch.int8)
+            rows = xq.shape[0]
+            if rows < 32:
+                xq = nn.functional.pad(xq, (0, 0, 0, 32 - rows))
+            y = torch._int_mm(xq, self.wq_t)[:rows].float() * s_a * self.scale
+            if self.bias is not None:
+                y = y + self.bias
+            return y.reshape(*x.shape[:-1], -1).to(x.dtype)
+
+    def int8_variant():
+        model = copy.deepcopy(base)
+        for layer in model.model.decoder.layers:
+            attn = layer.self_attn
+            for name in ("q_proj", "k_proj", "v_proj", "out_proj"):
+                setattr(attn, name, Int8Linear(getattr(attn, name)))
+        return model.eval()
+
+    backend = CudaRNSBackend()
+
+    def rns_variant(with_ffn: bool):
+        model = copy.deepcopy(base)
+        replaced, coordinators = replace_opt_attention_blocks(model, backend=backend, blocks=None, moduli=MODULI_4,
+                                                              include_out_proj=True)
+        if with_ffn:
+            replaced += replace_selected_linears(model, backend=backend, patterns=("fc1", "fc2"), moduli=MODULI_4)
+        return model.eval(), replaced, coordinators
+
+    torch.manual_seed(2003)
+    ids = torch.randint(0, config.vocab_size, (batch, prompt), device="cuda")
+
+    def generate(model):
+        """Prefill + greedy decode with the key/value cache; returns (prefill logits of the
+        last position as fp32, seconds of prefill, seconds of decode)."""
+        with torch.no_grad():
+            e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+            e0.record()
+            out = model(input_ids=ids, use_cache=True)
+            logits = out.logits[:, -1, :].float()
+            e1.record()
+            cache = out.past_key_values
+            token = logits.argmax(dim=-1, keepdim=True)
+            for _ in range(new_tokens):
+                out = model(input_ids=token, past_key_values=cache, use_cache=True)
+                cache = out.past_key_values
+                token = out.logits[:, -1, :].argmax(dim=-1, keepdim=True)
+            e2.record()
+            torch.cuda.synchronize()
+        return logits, e0.elapsed_time(e1) * 1e-3, e1.elapsed_time(e2) * 1e-3
+
+    def measure(model):
+        generate(model)                       # warm-up: weight preparation, arenas, autotuning
+        best = None
+        for _ in range(max(1, min(args.steps, 3))):
+            logits, prefill_s, decode_s = generate(model)
+            if best is None or prefill_s + decode_s < best[1] + best[2]:
+                best = (logits, prefill_s, decode_s)
+        logits, prefill_s, decode_s = best
+        return logits, {"prefill_s": prefill_s, "decode_s": decode_s,
+                        "prefill_tokens_per_s": batch * prompt / prefill_s,
+                        "decode_tokens_per_s": batch * new_tokens / decode_s,
+                        "tokens_per_s": batch * (prompt + new_tokens) / (prefill_s + decode_s)}
+
+    results = {}
+    fp16_logits, results["fp16"] = measure(base)
+    int8_model = int8_variant()
+    int8_logits, results["int8_int_mm"] = measure(int8_model)
+    del int8_model
+    backend.reset_stats()
+    rns_model, replaced, coordinators = rns_variant(with_ffn=False)
+    rns_logits, results["rns"] = measure(rns_model)
+    stats = backend.stats_snapshot()
+    if stats.get("fused_gemm_calls", 0) <= 0 or any(c.projection.compute_count <= 0 for c in coordinators):
+        raise SystemExit("the RNS path did not run (fused_gemm_calls / compute_count are zero): nothing to report")
+    backend.check_status()
+    del rns_model
+    ffn_model, replaced_ffn, _ = rns_variant(with_ffn=True)
+    ffn_logits, results["rns_attention_and_ffn"] = measure(ffn_model)
+    backend.check_status()
+
+    def errors(got, ref):
+        diff = (got - ref).abs()
+        return {"max_abs": float(diff.max()), "relative_l2": float(diff.norm() / ref.norm().clamp_min(1e-12)),
+                "argmax_agreement": float((got.argmax(-1) == ref.argmax(-1)).float().mean())}
+
+    print(json.dumps({
+        "metric": "opt125m_shaped_decoder_tokens_per_s", "unit": "tokens/s", "n_gpus": 1, "higher_is_better": True,
+        "data": "synthetic", "dtype": "int8 (RNS linears), fp16 elsewhere",
+        "value": results["rns"]["tokens_per_s"],
+        "config": {"workload": "opt125m_shaped_decoder (BASELINE.json configs[3])", "parameters": parameters,
+                   "batch": batch, "prompt_tokens": prompt, "new_tokens": new_tokens, "moduli": list(MODULI_4),
+                   "replaced_modules": len(replaced), "replaced_with_ffn": len(replaced_ffn),
+                   "decode": "eager module calls with the key/value cache (no CUDA graph)"},
+        "variants": results,
+        "logits_error_last_prefill_position": {
+            "rns_vs_fp16": errors(rns_logits, fp16_logits), "rns_vs_int8": errors(rns_logits, int8_logits),
+            "int8_vs_fp16": errors(int8_logits, fp16_logits),
+            "rns_attention_and_ffn_vs_fp16": errors(ffn_logits, fp16_logits)},
+        "rns_stats": {k: v for k, v in stats.items() if k.startswith("fused_gemm")},
+    }), flush=True)
 
 
 def run_quantiser(args) -> None:
@@ -749,16 +1045,23 @@ def main() -> None:
                         help="skip the torch._int_mm peak measurement (roofline.frac then uses 2 x bf16 sustained)")
     parser.add_argument("--gpu-baselines", action="store_true",
                         help="also time F.linear fp16 and torch._int_mm + eager dequantisation on the stack's shapes")
-    parser.add_argument("--workload", default="c4", choices=["c4", "c1", "quant", "peak"],
+    parser.add_argument("--workload", default="c4", choices=["c4", "c1", "c2", "c3", "quant", "peak"],
                         help="c4: the layer stack (the bench contract); c1: fused-QKV latency of configuration 1; "
-                             "quant: the activation quantiser alone on the stack's shapes; peak: the int8 "
-                             "library-GEMM peak of this GPU")
+                             "c2: continuous batching and adaptive channels of configuration 2; c3: the "
+                             "OPT-125m-shaped decoder of configuration 3; quant: the activation quantiser alone "
+                             "on the stack's shapes; peak: the int8 library-GEMM peak of this GPU")
     args = parser.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
         return
     if args.workload == "c1":
         run_fused_qkv_latency(args)
+        return
+    if args.workload == "c2":
+        run_concurrency(args)
+        return
+    if args.workload == "c3":
+        run_opt_decoder(args)
         return
     if args.workload == "quant":
         run_quantiser(args)

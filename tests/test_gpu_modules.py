@@ -168,3 +168,80 @@ def test_opt_decoder_layer_with_rns_attention(backend):
     rel = float((logits - base).abs().max() / base.abs().max())
     assert rel < 0.05, rel
     backend.check_status()
+
+
+class _ExactInt8Linear(torch.nn.Module):
+    """Test twin of an RNS linear in plain torch: the reference's quantisation
+    (layers/rns_linear.py:154-166, 183-184, 239-241), an exact int64 matrix product in
+    place of the RNS GEMM, and its fp32 dequantisation order (:264, 272-275)."""
+
+    def __init__(self, weight, bias):
+        super().__init__()
+        w = weight.detach().float()
+        eps = torch.finfo(torch.float32).eps
+        self.scale = torch.clamp(w.abs().amax(dim=1, keepdim=True) / 127.0, min=eps)
+        self.wq = torch.clamp(torch.round(w / self.scale), -127, 127).to(torch.int64)
+        self.bias = None if bias is None else bias.detach().float()
+
+    def forward(self, x):
+        flat = x.reshape(-1, x.shape[-1]).float()
+        s_a = torch.clamp(flat.abs().amax() / 127.0, min=torch.finfo(torch.float32).eps)
+        xq = torch.clamp(torch.round(flat / s_a), -127, 127).to(torch.int64)
+        acc = (xq.cpu() @ self.wq.cpu().t()).to(x.device)         # exact: int64 on the host
+        y = acc.float() * s_a * self.scale.reshape(1, -1)
+        if self.bias is not None:
+            y = y + self.bias
+        return y.reshape(*x.shape[:-1], -1).to(x.dtype)
+
+
+@pytest.mark.parametrize("tokens", [24, 520])
+def test_opt125m_shaped_model_with_rns_attention_and_ffn(backend, tokens):
+    """The 12-layer OPT-125m-shaped model of configuration 3 (smaller vocabulary to keep the
+    test light) with every attention block (fused q|k|v + out_proj) and every FFN linear
+    (fc1, fc2) replaced through the library's model-level helpers.  Its logits equal, bit
+    for bit, those of a twin whose linears are exact int8 products in plain torch, and stay
+    within a bound of the fp16 model's."""
+    transformers = pytest.importorskip("transformers")
+    import copy
+    from rns_llm_b200.integration import find_parent, replace_opt_attention_blocks, replace_selected_linears
+
+    config = transformers.OPTConfig(vocab_size=2048, hidden_size=768, num_hidden_layers=12, num_attention_heads=12,
+                                    ffn_dim=3072, max_position_embeddings=1024, word_embed_proj_dim=768)
+    torch.manual_seed(1003)
+    base = transformers.OPTForCausalLM(config).half().cuda().eval()
+    ids = torch.randint(0, 2048, (2, tokens // 2), device="cuda")
+    rns = copy.deepcopy(base)
+    replaced, coordinators = replace_opt_attention_blocks(rns, backend=backend, moduli=C0)
+    replaced += replace_selected_linears(rns, backend=backend, patterns=("fc1", "fc2"), moduli=C0)
+    assert len(replaced) == 12 * 4 and len(coordinators) == 12
+    twin = copy.deepcopy(base)
+    for layer in twin.model.decoder.layers:
+        attn = layer.self_attn
+        w = torch.cat([attn.q_proj.weight, attn.k_proj.weight, attn.v_proj.weight], dim=0)
+        b = torch.cat([attn.q_proj.bias, attn.k_proj.bias, attn.v_proj.bias], dim=0)
+        fused = _ExactInt8Linear(w, b)
+        for index, name in enumerate(("q_proj", "k_proj", "v_proj")):
+            # the fused projection quantises the activation once; each slice is a column block
+            setattr(attn, name, _Slice(fused, index, 768))
+        attn.out_proj = _ExactInt8Linear(attn.out_proj.weight, attn.out_proj.bias)
+        layer.fc1 = _ExactInt8Linear(layer.fc1.weight, layer.fc1.bias)
+        layer.fc2 = _ExactInt8Linear(layer.fc2.weight, layer.fc2.bias)
+    backend.reset_stats()
+    with torch.no_grad():
+        want = base(ids).logits.float()
+        got = rns(ids).logits.float()
+        exact = twin(ids).logits.float()
+    backend.check_status()
+    assert backend.stats_snapshot()["fused_gemm_calls"] == 12 * 4
+    assert all(c.projection.compute_count == 1 for c in coordinators)
+    assert torch.equal(got, exact)
+    assert float((got - want).norm() / want.norm()) < 0.05
+
+
+class _Slice(torch.nn.Module):
+    def __init__(self, fused, index, width):
+        super().__init__()
+        self.fused, self.index, self.width = fused, index, width
+
+    def forward(self, x):
+        return self.fused(x)[..., self.index * self.width:(self.index + 1) * self.width]
