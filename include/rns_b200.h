@@ -421,6 +421,27 @@ RNS_API int rns_quantize_weight(const void* d_w, rns_float_type type, int n, int
                                 int32_t* d_max_abs, rns_stream_t stream);
 
 /*
+ * Few-token linear in ONE launch (decode steps, merged single-token requests): the
+ * whole of RNSLinear.forward (layers/rns_linear.py:237-275: absmax, quantise, encode,
+ * per-channel products, reconstruction, dequantise, bias) for M <= 32 tokens, where
+ * the reference pays about 17 launches and this library's two-step path two.  Needs no
+ * scratch memory at all.
+ *   d_x      activations [M,K], row stride ldx: floating (x_type = rns_float_type;
+ *            quantised per tensor, or per row when per_row != 0) or already-quantised
+ *            int8 (x_type = -1; the merged activations of
+ *            matmul_prepared_fused_requests, backends/cuda_backend.py:647-703)
+ *   d_out    [M,N] of out_type: exact int64 / int32, or F16 / BF16 / F32 =
+ *            type(f32(x) * s_a * col_scale[n] + bias[n]) (s_a = 1 for int8 activations)
+ * rns_linear_small_supported: M <= 32, K % 16 == 0, 2..6 channels, channels * K <=
+ * 196608; anything else returns RNS_ERR_UNSUPPORTED (use rns_linear_fused).
+ */
+RNS_API int rns_linear_small_supported(int m, int k, int channels);
+RNS_API int rns_linear_small(const void* d_x, int x_type, int m, int k, int64_t ldx, int per_row,
+                             const int8_t* d_w_packed, int n, const int32_t* moduli, int channels,
+                             const float* d_col_scale, const float* d_bias, void* d_out, int64_t ldo,
+                             int32_t out_type, rns_stream_t stream);
+
+/*
  * The floating-point linear for hosts that cannot allocate device memory.  It
  * has no counterpart in the reference, whose workspaces are torch tensors.
  *

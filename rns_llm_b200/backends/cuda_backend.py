@@ -656,7 +656,15 @@ class CudaRNSBackend:
         self._stats["fused_gemm_calls"] += 1
         self._stats[f"fused_gemm_channels_{channels}"] += 1
         with torch.cuda.device(a.device):
-            if m >= PLANES_MIN_ROWS:
+            if (_active is None and a.stride(1) == 1 and
+                    self._lib.rns_linear_small_supported(m, prepared_weight.k, channels)):
+                # Few tokens (merged single-token requests): one launch, no scratch.
+                _, arr = self._mods(mods)
+                N.check(self._lib.rns_linear_small(
+                    a.data_ptr(), -1, m, prepared_weight.k, a.stride(0), 0, prepared_weight.weight_packed.data_ptr(),
+                    prepared_weight.n, arr, channels, None, None, workspace.output.data_ptr(),
+                    workspace.output.stride(0), N.OUT_INT64, self._stream(a.device)))
+            elif m >= PLANES_MIN_ROWS:
                 frame = self.arena.frame(a.device)
                 planes = frame.alloc(int(self._lib.rns_packed_activation_bytes(m, prepared_weight.k, channels)),
                                      torch.int8)
@@ -873,6 +881,20 @@ class CudaRNSBackend:
             out = torch.empty((m, prepared.n), dtype=x.dtype, device=device)
         elif out.shape != (m, prepared.n) or out.stride(1) != 1 or out.dtype != x.dtype:
             raise ValueError("out must be [M,N] of x's dtype with unit inner stride")
+        if (adaptive is None and absmax_in is None and absmax_out is None and x.ndim == 2 and
+                self._lib.rns_linear_small_supported(m, k, channels)):
+            # Few tokens: the whole layer in one launch, no scratch.
+            with torch.cuda.device(device):
+                N.check(self._lib.rns_linear_small(
+                    x.data_ptr(), _FLOAT_TYPES[x.dtype], m, k, ldx, 1 if per_row else 0,
+                    prepared.weight_packed.data_ptr(), prepared.n, arr, channels, weight_scale.data_ptr(),
+                    None if bias is None else bias.data_ptr(), out.data_ptr(), out.stride(0),
+                    _OUT_TYPES[out.dtype], self._stream(device)))
+            self._stats["encode_centered_calls"] += 1
+            self._stats["encode_centered_values"] += m * k
+            self._stats["fused_gemm_calls"] += 1
+            self._stats[f"fused_gemm_channels_{channels}"] += 1
+            return (out, None) if return_metadata else out
         use_planes = m >= PLANES_MIN_ROWS and adaptive is None
         # Many-token calls: planes in tiles of 64 / 48 token rows for the two-CTA kernel.
         tile_rows = int(self._lib.rns_pair_tile_rows(channels, k)) if use_planes else 0
