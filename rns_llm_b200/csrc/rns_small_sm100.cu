@@ -54,6 +54,28 @@ template <> __device__ __forceinline__ float small_load<__half>(const __half* p,
 template <> __device__ __forceinline__ float small_load<__nv_bfloat16>(const __nv_bfloat16* p, int64_t i) { return __bfloat162float(p[i]); }
 template <> __device__ __forceinline__ float small_load<float>(const float* p, int64_t i) { return p[i]; }
 
+// Eight consecutive activations starting at element `i` (a multiple of 8) of a row with
+// `valid` elements left; one 16-byte load when the address allows it.
+template <typename T>
+__device__ __forceinline__ void small_load8(const T* row, int i, int valid, bool vec, float (&v)[8]) {
+    if (vec && valid >= 8) {
+        if constexpr (sizeof(T) == 2) {
+            const uint4 raw = *reinterpret_cast<const uint4*>(row + i);
+            const T* h = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = small_load<T>(h, j);
+        } else {
+            const float4 lo = *reinterpret_cast<const float4*>(row + i);
+            const float4 hi = *reinterpret_cast<const float4*>(row + i + 4);
+            v[0] = (float)lo.x; v[1] = (float)lo.y; v[2] = (float)lo.z; v[3] = (float)lo.w;
+            v[4] = (float)hi.x; v[5] = (float)hi.y; v[6] = (float)hi.z; v[7] = (float)hi.w;
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = j < valid ? small_load<T>(row, i + j) : 0.0f;
+    }
+}
+
 __device__ __forceinline__ void mma_s8(int (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
     asm volatile(
         "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -84,13 +106,22 @@ rns_linear_small_kernel(const __grid_constant__ SmallParams p) {
     constexpr bool kIntegers = std::is_same<T, int8_t>::value;
 
     // ---------------- activation scale(s) ----------------
+    const int groups_per_row = (p.k + 7) / 8;                    // groups of 8 consecutive columns
+    bool vec = false;
     if constexpr (!kIntegers) {
         const T* x = static_cast<const T*>(p.x);
+        vec = (p.k % 8 == 0) && ((p.ldx * sizeof(T)) % 16 == 0) && (reinterpret_cast<uintptr_t>(p.x) % 16 == 0);
         if (p.per_row) {
             // one warp per row of this CTA's token block
             for (int r = warp; r < rows; r += kSmallWarps) {
                 float best = 0.0f;
-                for (int c = lane; c < p.k; c += 32) best = fmaxf(best, fabsf(small_load<T>(x, (int64_t)(m0 + r) * p.ldx + c)));
+                const T* row = x + (int64_t)(m0 + r) * p.ldx;
+                for (int gi = lane; gi < groups_per_row; gi += 32) {
+                    float v[8];
+                    small_load8<T>(row, gi * 8, p.k - gi * 8, vec, v);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) best = fmaxf(best, fabsf(v[j]));
+                }
 #pragma unroll
                 for (int o = 16; o > 0; o >>= 1) best = fmaxf(best, __shfl_xor_sync(0xffffffffu, best, o));
                 if (lane == 0) s_row_scale[r] = fmaxf(__fdiv_rn(best, 127.0f), FLT_EPSILON);
@@ -98,9 +129,14 @@ rns_linear_small_kernel(const __grid_constant__ SmallParams p) {
         } else {
             // the tensor's absmax: every CTA scans all M rows (M is small)
             float best = 0.0f;
-            for (int r = 0; r < p.m; ++r)
-                for (int c = threadIdx.x; c < p.k; c += kSmallThreads)
-                    best = fmaxf(best, fabsf(small_load<T>(x, (int64_t)r * p.ldx + c)));
+            const int total = p.m * groups_per_row;
+            for (int i = threadIdx.x; i < total; i += kSmallThreads) {
+                const int r = i / groups_per_row, gi = i - r * groups_per_row;
+                float v[8];
+                small_load8<T>(x + (int64_t)r * p.ldx, gi * 8, p.k - gi * 8, vec, v);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) best = fmaxf(best, fabsf(v[j]));
+            }
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) best = fmaxf(best, __shfl_xor_sync(0xffffffffu, best, o));
             if (lane == 0) s_part[warp] = best;
@@ -114,38 +150,42 @@ rns_linear_small_kernel(const __grid_constant__ SmallParams p) {
     }
 
     // ---------------- quantise + encode the token block into shared memory ----------------
-    // One thread per group of four consecutive K bytes of one row.
+    // One thread per group of eight consecutive K bytes of one row (two words of residues
+    // per channel, 8 bytes apart from nothing: they are neighbours inside a 16-byte half).
     {
-        const int words_per_row = ksteps * 8;                    // 4-byte words per padded row
-        for (int idx = threadIdx.x; idx < kSmallTokens * words_per_row; idx += kSmallThreads) {
-            const int r = idx / words_per_row;
-            const int wcol = idx - r * words_per_row;
-            const int c0 = wcol * 4;
-            uint32_t word = 0;
-            if (r < rows) {
+        const int groups_padded = ksteps * 4;                     // groups per padded row
+        for (int idx = threadIdx.x; idx < kSmallTokens * groups_padded; idx += kSmallThreads) {
+            const int r = idx / groups_padded;
+            const int gi = idx - r * groups_padded;
+            const int c0 = gi * 8;
+            uint32_t word[2] = {0u, 0u};
+            if (r < rows && c0 < p.k) {
+                int q[8];
+                if constexpr (kIntegers) {
+                    const int8_t* row = static_cast<const int8_t*>(p.x) + (int64_t)(m0 + r) * p.ldx;
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const int c = c0 + j;
-                    int q = 0;
-                    if (c < p.k) {
-                        if constexpr (kIntegers) {
-                            q = (int)static_cast<const int8_t*>(p.x)[(int64_t)(m0 + r) * p.ldx + c];
-                        } else {
-                            const float v = small_load<T>(static_cast<const T*>(p.x), (int64_t)(m0 + r) * p.ldx + c);
-                            float t = rintf(__fdiv_rn(v, s_row_scale[r]));
-                            t = fminf(fmaxf(t, -127.0f), 127.0f);
-                            q = (int)t;
-                        }
+                    for (int j = 0; j < 8; ++j) q[j] = c0 + j < p.k ? (int)row[c0 + j] : 0;
+                } else {
+                    float v[8];
+                    small_load8<T>(static_cast<const T*>(p.x) + (int64_t)(m0 + r) * p.ldx, c0, p.k - c0, vec, v);
+                    const float scale = s_row_scale[r];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        float t = rintf(__fdiv_rn(v[j], scale));
+                        q[j] = (int)fminf(fmaxf(t, -127.0f), 127.0f);
                     }
-                    word |= (uint32_t)(q & 0xff) << (8 * j);
                 }
+#pragma unroll
+                for (int j = 0; j < 8; ++j) word[j >> 2] |= (uint32_t)(q[j] & 0xff) << (8 * (j & 3));
             }
-            const uint32_t u = word ^ 0x80808080u, d = fold_pattern(word);
             const int kstep = c0 >> 5, byte_in_step = c0 & 31;
 #pragma unroll
-            for (int c = 0; c < R; ++c)
-                *reinterpret_cast<uint32_t*>(smem + small_a_offset(c, kstep, ksteps, r, byte_in_step)) =
-                    encode_word_reduced(u, d, p.plan.enc_mfold[c]);
+            for (int c = 0; c < R; ++c) {
+                uint2 e;
+                e.x = encode_word_reduced(word[0] ^ 0x80808080u, fold_pattern(word[0]), p.plan.enc_mfold[c]);
+                e.y = encode_word_reduced(word[1] ^ 0x80808080u, fold_pattern(word[1]), p.plan.enc_mfold[c]);
+                *reinterpret_cast<uint2*>(smem + small_a_offset(c, kstep, ksteps, r, byte_in_step)) = e;
+            }
         }
     }
     __syncthreads();
@@ -231,7 +271,8 @@ static int launch_small(const SmallParams& sp, size_t smem_bytes, cudaStream_t s
     int dev = 0;
     RNS_CUDA_OK(cudaGetDevice(&dev));
     const uint64_t bit = 1ull << (dev & 63);
-    if (smem_bytes > 48 * 1024 && !(configured.load(std::memory_order_acquire) & bit)) {
+    // static + dynamic shared memory can pass the 48 KB default: opt in once per device
+    if (!(configured.load(std::memory_order_acquire) & bit)) {
         RNS_CUDA_OK(cudaFuncSetAttribute(rns_linear_small_kernel<R, T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          96 * 1024));
         configured.fetch_or(bit, std::memory_order_release);

@@ -555,7 +555,8 @@ def _torch_linear_reference(x_plain, w_q, w_scale, bias):
     """Per-tensor quantisation, exact int8 GEMM through torch._int_mm and the reference's
     fp32 dequantisation order (layers/rns_linear.py:239-241, 264, 272-275), all on the GPU."""
     flat = x_plain.float()
-    s_a = torch.clamp(flat.abs().amax() / 127.0, min=float(np.finfo(np.float32).eps))
+    amax = flat.abs().amax()
+    s_a = torch.clamp(amax / torch.full_like(amax, 127.0), min=float(np.finfo(np.float32).eps))
     a_q = torch.clamp(torch.round(flat / s_a), -127, 127).to(torch.int8)
     acc = torch._int_mm(a_q, w_q.t())
     y = acc.float() * s_a * w_scale[None, :]

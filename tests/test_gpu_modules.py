@@ -179,13 +179,19 @@ class _ExactInt8Linear(torch.nn.Module):
         super().__init__()
         w = weight.detach().float()
         eps = torch.finfo(torch.float32).eps
-        self.scale = torch.clamp(w.abs().amax(dim=1, keepdim=True) / 127.0, min=eps)
+        # Division by a TENSOR: on CUDA torch turns a division by a Python scalar into a
+        # multiplication by its reciprocal, which rounds differently in the last place for
+        # some values; the kernels (and torch on the CPU, where the golden vectors come
+        # from) divide.
+        amax = w.abs().amax(dim=1, keepdim=True)
+        self.scale = torch.clamp(amax / torch.full_like(amax, 127.0), min=eps)
         self.wq = torch.clamp(torch.round(w / self.scale), -127, 127).to(torch.int64)
         self.bias = None if bias is None else bias.detach().float()
 
     def forward(self, x):
         flat = x.reshape(-1, x.shape[-1]).float()
-        s_a = torch.clamp(flat.abs().amax() / 127.0, min=torch.finfo(torch.float32).eps)
+        amax = flat.abs().amax()
+        s_a = torch.clamp(amax / torch.full_like(amax, 127.0), min=torch.finfo(torch.float32).eps)
         xq = torch.clamp(torch.round(flat / s_a), -127, 127).to(torch.int64)
         acc = (xq.cpu() @ self.wq.cpu().t()).to(x.device)         # exact: int64 on the host
         y = acc.float() * s_a * self.scale.reshape(1, -1)

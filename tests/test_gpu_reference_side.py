@@ -150,5 +150,7 @@ def test_dequantised_outputs_match_the_reference_rnslinear(tokens):
         denom = r.float().abs().clamp_min(1e-3)
         assert float(((m.float() - r.float()).abs() / denom).max()) <= REL_TOL
         assert torch.equal(m, f)
-        # in practice the two agree bit for bit: same integers, same fp32 operation order
-        assert torch.equal(m, r)
+        # Not bit for bit: on CUDA the reference's eager `absmax / 127` is a multiplication by
+        # the reciprocal (torch's scalar-divisor shortcut), which moves a few scales by one
+        # unit in the last place against the division its CPU path - and this package - use.
+        assert float((m != r).float().mean()) < 0.05
