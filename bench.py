@@ -260,7 +260,7 @@ def workload_config(args, sharded: bool) -> dict:
         "linears_per_layer": [f"{name}:{k}->{n}:R{len(mods)}" for name, k, n, mods, _ in LINEARS],
         "moduli_k4096": list(MODULI_4), "moduli_k16384": list(MODULI_5),
         "activation_scale": "per-tensor", "out_dtype": "float16",
-        "parallelism": f"column-sharded N x{args.gpus} + NCCL all-gather" if sharded else "single GPU",
+        "parallelism": f"column-sharded N x{args.gpus}" if sharded else "single GPU",
         "l2_policy": "inputs larger than L2 (about 6.4 GB of int8 weights streamed per step)",
     }
 
@@ -268,7 +268,32 @@ def workload_config(args, sharded: bool) -> dict:
 # --------------------------------------------------------------------------
 # GPU arm
 # --------------------------------------------------------------------------
-def build_stack(backend, args, rank: int, world: int, device):
+def make_peer_arena(args, world: int, device):
+    """Symmetric memory for the sharded stack's outputs (the exchange then runs inside the
+    GEMM epilogues as peer stores); None, with the reason, when the platform does not offer
+    it or `--exchange nccl` asks for the all-gather.  All ranks take the same decision."""
+    import torch
+    import torch.distributed as dist
+    from rns_llm_b200.parallel import ABSMAX_PAD, PeerArena
+
+    if world == 1:
+        return None, "single GPU"
+    if args.exchange == "nccl":
+        return None, "--exchange nccl"
+    nbytes = args.layers * sum(world * ((args.tokens * (n // world) + ABSMAX_PAD) * 2 + 256) for _, _, n, _, _ in LINEARS)
+    arena, why = None, ""
+    try:
+        arena = PeerArena(nbytes, device)
+    except Exception as exc:            # not available here: every rank must fall back together
+        why = f"{type(exc).__name__}: {exc}"
+    flag = torch.tensor([1 if arena is not None else 0], dtype=torch.int32, device=device)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    if int(flag.item()) == 0:
+        return None, why or "symmetric memory failed on another rank"
+    return arena, ""
+
+
+def build_stack(backend, args, rank: int, world: int, device, peer_arena=None):
     """Random-init weights, quantised and prepared layer by layer (the fp16
     weights are not kept).  Returns a list of layers, each a list of sharded
     linears in LINEARS order."""
@@ -286,7 +311,8 @@ def build_stack(backend, args, rank: int, world: int, device):
             shard_w = shard_tensor(weight, world, rank, groups)
             shard_b = shard_tensor(bias, world, rank, groups)
             layer.append(ColumnShardedRNSLinear(shard_w, shard_b, backend=backend, moduli=mods, rank=rank,
-                                                world=world, groups=groups, reuse_buffer=True))
+                                                world=world, groups=groups, reuse_buffer=True,
+                                                peer_arena=peer_arena))
             del weight, bias, shard_w, shard_b
         stack.append(layer)
     return stack
@@ -864,7 +890,12 @@ def _run_layer_stack(args, backend, rank, world, local_rank, device) -> None:
     PROGRESS["phase"] = "build_stack"
     free_bytes, total_bytes = torch.cuda.mem_get_info(device)
     PROGRESS["free_gib_at_start"] = round(free_bytes / 2**30, 1)
-    stack = build_stack(backend, args, rank, world, device)
+    PROGRESS["phase"] = "peer_arena"
+    peer_arena, arena_why = make_peer_arena(args, world, device)
+    PROGRESS["phase"] = "build_stack"
+    stack = build_stack(backend, args, rank, world, device, peer_arena)
+    exchange = ("peer stores from the GEMM epilogue into symmetric memory + a barrier per layer"
+                if peer_arena is not None else f"NCCL all-gather per layer ({arena_why})")
     torch.manual_seed(4321)
     host_x = torch.randn((args.tokens, HIDDEN), dtype=torch.float16).pin_memory()
     host_y = torch.empty((args.tokens, HIDDEN), dtype=torch.float16).pin_memory()
@@ -991,7 +1022,7 @@ def _run_layer_stack(args, backend, rank, world, local_rank, device) -> None:
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
-            "config": workload_config(args, sharded=world > 1),
+            "config": dict(workload_config(args, sharded=world > 1), exchange=exchange),
             "useful_tops": useful_ops_per_step(args.tokens, args.layers) / (ms_per_step * 1e-3) / 1e12,
             "tokens_per_s": args.tokens / (ms_per_step * 1e-3),
             "roofline": {
@@ -1041,6 +1072,9 @@ def main() -> None:
     parser.add_argument("--layers", type=int, default=32)
     parser.add_argument("--tokens", type=int, default=4096)
     parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--exchange", default="auto", choices=["auto", "peer", "nccl"],
+                        help="multi-GPU output exchange: peer stores over symmetric memory when available (auto, "
+                             "peer), or the NCCL all-gather")
     parser.add_argument("--no-peak", action="store_true",
                         help="skip the torch._int_mm peak measurement (roofline.frac then uses 2 x bf16 sustained)")
     parser.add_argument("--gpu-baselines", action="store_true",

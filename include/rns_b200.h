@@ -36,6 +36,7 @@ typedef void* rns_stream_t;
 
 #define RNS_MAX_CHANNELS 10   /* reference: csrc/rns_cuda.cu:963-975 accepts 2..10 */
 #define RNS_TC_MAX_CHANNELS 8 /* channel count the tcgen05 kernel is instantiated for */
+#define RNS_MAX_PEERS 7       /* other ranks of one NVLink domain that a launch can store to */
 
 typedef enum rns_status {
     RNS_OK = 0,
@@ -274,9 +275,19 @@ typedef struct rns_linear_args {
                                  kernel (variant 3), which needs 4 or 5 channels and K >= 512 */
     uint32_t* d_absmax_out;   /* NULL, or device word that receives the bit pattern of
                                  max |y| over the floating outputs as stored (variant 3 only;
-                                 the launch clears it first): the per-tensor absmax the NEXT
+                                 two words: the launch clears both and uses [1] as a counter): the per-tensor absmax the NEXT
                                  layer's quantiser needs, so that it can skip its own pass over
                                  the activations (layers/rns_linear.py:239-240 of the reference) */
+    int32_t n_out_copies;     /* variant 3, floating outputs: the tile is ALSO stored, at the same
+                                 offsets (same ldo), into these buffers - the same output slot in
+                                 the memory of the other ranks of a column-sharded layer, mapped
+                                 into this process (peer memory over NVLink; plain stores only).
+                                 The exchange then runs under the GEMM instead of in an all-gather
+                                 after it; the ranks still have to meet (a barrier) before anyone
+                                 reads.  With d_absmax_out, d_absmax_copies[g] receives the finished
+                                 word too (d_absmax_out then needs two words: [1] counts CTAs). */
+    void* d_out_copies[RNS_MAX_PEERS];
+    uint32_t* d_absmax_copies[RNS_MAX_PEERS];
     int32_t* d_wait_info;     /* NULL, or device int32[4], zero before the launch: when a bounded
                                  wait expires the first CTA to give up writes {wait code =
                                  role << 20 | pipeline stage, blockIdx.x, blockIdx.y, kernel form}

@@ -20,6 +20,7 @@ _lib: C.CDLL | None = None
 
 MAX_CHANNELS = 10
 TC_MAX_CHANNELS = 8
+MAX_PEERS = 7
 
 # rns_status
 OK, ERR_INVALID_ARGUMENT, ERR_BAD_MODULI, ERR_UNSUPPORTED, ERR_OVERFLOW, ERR_CUDA, ERR_DEVICE_TIMEOUT = range(7)
@@ -63,6 +64,9 @@ class LinearArgs(C.Structure):
         ("exact_residues", C.c_int32),
         ("a_tile_rows", C.c_int32),
         ("d_absmax_out", C.c_void_p),
+        ("n_out_copies", C.c_int32),
+        ("d_out_copies", C.c_void_p * MAX_PEERS),
+        ("d_absmax_copies", C.c_void_p * MAX_PEERS),
         ("d_wait_info", C.c_void_p),
     ]
 

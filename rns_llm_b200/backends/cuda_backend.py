@@ -577,7 +577,8 @@ class CudaRNSBackend:
                       enc_groups: int = 0, exact_residues: bool = False,
                       enc_stages: int = 0, sub_blocks: int = 0, variant: int = 0,
                       stream: int | None = None, a_tile_rows: int = 0,
-                      absmax_out: torch.Tensor | int | None = None) -> None:
+                      absmax_out: torch.Tensor | int | None = None,
+                      out_copies: Sequence[int] = (), absmax_copies: Sequence[int] = ()) -> None:
         """Fills ``rns_linear_args`` and launches.  ``a`` / ``a_planes`` are plain
         ([M,K] / [R,M,K]) unless ``a_packed``; the weight is the prepared packed
         copy unless ``plain_weight`` ([N,K] int8) is given.  Device buffers may be
@@ -628,6 +629,11 @@ class CudaRNSBackend:
         args.variant = variant
         args.a_tile_rows = a_tile_rows
         args.d_absmax_out = None if absmax_out is None else ptr(absmax_out)
+        args.n_out_copies = len(out_copies)
+        for index, address in enumerate(out_copies):
+            args.d_out_copies[index] = address
+        for index, address in enumerate(absmax_copies):
+            args.d_absmax_copies[index] = address
         N.check(self._lib.rns_linear_fused(C.byref(args), self._stream(device) if stream is None else stream))
 
     def matmul_prepared_fused(self, a: torch.Tensor, prepared_weight: PreparedRNSWeight, *,
@@ -836,7 +842,8 @@ class CudaRNSBackend:
                        adaptive: PreparedAdaptiveRNSWeight | None = None,
                        return_metadata: bool = False, out: torch.Tensor | None = None,
                        absmax_in: tuple[int, int, int] | None = None,
-                       absmax_out: torch.Tensor | int | None = None):
+                       absmax_out: torch.Tensor | int | None = None,
+                       out_copies: Sequence[int] = (), absmax_copies: Sequence[int] = ()):
         """y[M,N] = dequant( quant(x)[M,K] @ Wq[N,K]^T ) in the dtype of ``x``.
 
         The whole of ``RNSLinear.forward`` after weight preparation
@@ -855,7 +862,9 @@ class CudaRNSBackend:
         (address, parts, stride in words) hands the next call the words whose maximum
         is its input's absmax (one word, or one per rank of a column-sharded layer).
         ``absmax_out`` needs the many-token kernel (M >= 512, 4 or 5 channels,
-        K >= 512); otherwise it raises."""
+        K >= 512); otherwise it raises.  ``out_copies`` (device addresses, e.g. the
+        same output slot in other ranks' memory) receive the same stores as ``out``
+        from that kernel's epilogue, ``absmax_copies`` the finished absmax word."""
         if prepared.kernel != "tcgen05":
             raise ValueError("linear_forward needs a tensor-core prepared weight")
         if x.dtype not in _FLOAT_TYPES:
@@ -881,7 +890,7 @@ class CudaRNSBackend:
             out = torch.empty((m, prepared.n), dtype=x.dtype, device=device)
         elif out.shape != (m, prepared.n) or out.stride(1) != 1 or out.dtype != x.dtype:
             raise ValueError("out must be [M,N] of x's dtype with unit inner stride")
-        if (adaptive is None and absmax_in is None and absmax_out is None and x.ndim == 2 and
+        if (adaptive is None and absmax_in is None and absmax_out is None and not out_copies and x.ndim == 2 and
                 self._lib.rns_linear_small_supported(m, k, channels)):
             # Few tokens: the whole layer in one launch, no scratch.
             with torch.cuda.device(device):
@@ -902,6 +911,8 @@ class CudaRNSBackend:
             raise ValueError("absmax_in serves the per-tensor scale")
         if absmax_out is not None and (tile_rows == 0 or per_row):
             raise ValueError("absmax_out needs the many-token kernel and a per-tensor scale")
+        if out_copies and tile_rows == 0:
+            raise ValueError("out_copies need the many-token kernel")
         meta = None
         with torch.cuda.device(device):
             # One block of the stream's arena, addressed by offsets (256-byte aligned):
@@ -942,7 +953,8 @@ class CudaRNSBackend:
                                a_packed=True, out=out, active=active,
                                row_scale=scale, row_scale_stride=1 if per_row else 0,
                                col_scale=weight_scale, bias=bias, stream=stream,
-                               a_tile_rows=tile_rows, absmax_out=absmax_out)
+                               a_tile_rows=tile_rows, absmax_out=absmax_out,
+                               out_copies=out_copies, absmax_copies=absmax_copies)
         if return_metadata:
             return out, (AdaptiveMetadata(meta) if meta is not None else None)
         return out

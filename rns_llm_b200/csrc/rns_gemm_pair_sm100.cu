@@ -54,7 +54,14 @@ struct PairParams {
     int32_t row_scale_stride;
     const float* col_scale;
     const float* bias;
-    uint32_t* absmax_out;      // NULL, or device word: atomicMax of the bit pattern of max |y|
+    uint32_t* absmax_out;      // NULL, or device words: [0] atomicMax of the bit pattern of max |y|,
+                               // [1] count of CTAs that have contributed (both cleared by the launch)
+    // Column-sharded layers: the tile is also stored, at the same offsets, into the output
+    // buffers of the other ranks (peer memory, plain stores), and the finished absmax word
+    // into theirs.  n_copies = 0: p.out only.
+    int32_t n_copies;
+    void* out_copies[RNS_MAX_PEERS];
+    uint32_t* absmax_copies[RNS_MAX_PEERS];
     int32_t* status;
     int32_t* wait_info;
 };
@@ -69,6 +76,109 @@ struct __align__(8) PairCtl {
     int abort;
     uint32_t absmax;
 };
+
+
+// ---------------------------------------------------------------------------
+// The epilogue's reconstruction for two outputs at a time with packed fp32
+// instructions (fma / mul / add .f32x2: two IEEE single-precision results per
+// instruction on sm_100).  Same operations, same rounding and same order per lane as
+// garner_digits / reconstruct32 / reconstruct in rns_common.cuh (which the host tests
+// evaluate); only the instruction count halves.
+// ---------------------------------------------------------------------------
+struct F2 { float x, y; };
+__device__ __forceinline__ unsigned long long f2_bits(F2 v) {
+    return ((unsigned long long)__float_as_uint(v.y) << 32) | (unsigned long long)__float_as_uint(v.x);
+}
+__device__ __forceinline__ F2 f2_from(unsigned long long b) {
+    F2 v; v.x = __uint_as_float((unsigned)b); v.y = __uint_as_float((unsigned)(b >> 32)); return v;
+}
+__device__ __forceinline__ F2 f2_splat(float s) { F2 v; v.x = s; v.y = s; return v; }
+__device__ __forceinline__ F2 fma2(F2 a, F2 b, F2 c) {
+    unsigned long long d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(f2_bits(a)), "l"(f2_bits(b)), "l"(f2_bits(c)));
+    return f2_from(d);
+}
+__device__ __forceinline__ F2 mul2(F2 a, F2 b) {
+    unsigned long long d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(f2_bits(a)), "l"(f2_bits(b)));
+    return f2_from(d);
+}
+__device__ __forceinline__ F2 add2(F2 a, F2 b) {
+    unsigned long long d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(f2_bits(a)), "l"(f2_bits(b)));
+    return f2_from(d);
+}
+
+// Centred mixed-radix digits of two outputs (all R channels active).
+template <int R>
+__device__ __forceinline__ void garner_digits_x2(const int (&a0)[R], const int (&a1)[R], const Plan& pl, F2 (&digit)[R]) {
+    const F2 magic = f2_splat(kMagic), neg_magic = f2_splat(-kMagic);
+#pragma unroll
+    for (int i = 0; i < R; ++i) {
+        F2 r;
+        r.x = bits_to_float(loose_residue(a0[i], pl.mod[i], pl.recip[i]) + kMagicBits);
+        r.y = bits_to_float(loose_residue(a1[i], pl.mod[i], pl.recip[i]) + kMagicBits);
+        r = add2(r, neg_magic);                                   // small_int_to_float
+        F2 t = (i == 0) ? r : mul2(r, f2_splat(pl.gscale[i]));
+#pragma unroll
+        for (int j = 0; j < i; ++j) t = fma2(f2_splat(pl.gneg[i][j]), digit[j], t);
+        // centre_mod: q = (t * rcp + magic) - magic;  digit = -q * m + t
+        const F2 q = add2(fma2(t, f2_splat(pl.rcpf[i]), magic), neg_magic);
+        digit[i] = fma2(q, f2_splat(-pl.modf[i]), t);
+    }
+}
+
+// reconstruct32 for two outputs (R <= 4, all channels active).
+template <int R>
+__device__ __forceinline__ void reconstruct32_x2(const int (&a0)[R], const int (&a1)[R], const Plan& pl, int& x0, int& x1) {
+    static_assert(R <= 4, "32-bit reconstruction covers at most four channels");
+    F2 digit[R];
+    garner_digits_x2<R>(a0, a1, pl, digit);
+    const F2 magic = f2_splat(kMagic);
+    unsigned u0 = 0, u1 = 0;
+    if constexpr (R == 4) {
+        const F2 lo = add2(fma2(f2_splat(pl.modf[0]), digit[1], digit[0]), magic);
+        const F2 hi = add2(fma2(f2_splat(pl.modf[2]), digit[3], digit[2]), magic);
+        u0 = (unsigned)(float_to_bits(lo.x) - kMagicBits) + pl.place32[2] * (unsigned)(float_to_bits(hi.x) - kMagicBits);
+        u1 = (unsigned)(float_to_bits(lo.y) - kMagicBits) + pl.place32[2] * (unsigned)(float_to_bits(hi.y) - kMagicBits);
+    } else {
+#pragma unroll
+        for (int i = 0; i < R; ++i) {
+            const F2 d = add2(digit[i], magic);
+            u0 += pl.place32[i] * (unsigned)(float_to_bits(d.x) - kMagicBits);
+            u1 += pl.place32[i] * (unsigned)(float_to_bits(d.y) - kMagicBits);
+        }
+    }
+    const unsigned prod = (unsigned)pl.product[R];
+    const int half = (int)(prod >> 1);
+    const int low = (int)((unsigned)half - prod + 1u);
+    int s0 = (int)u0, s1 = (int)u1;
+    if (s0 > half) s0 = (int)(u0 - prod); else if (s0 < low) s0 = (int)(u0 + prod);
+    if (s1 > half) s1 = (int)(u1 - prod); else if (s1 < low) s1 = (int)(u1 + prod);
+    x0 = s0; x1 = s1;
+}
+
+// reconstruct for two outputs (any R up to 8, all channels active).
+template <int R>
+__device__ __forceinline__ void reconstruct64_x2(const int (&a0)[R], const int (&a1)[R], const Plan& pl, long long& x0, long long& x1) {
+    F2 digit[R];
+    garner_digits_x2<R>(a0, a1, pl, digit);
+    const F2 magic = f2_splat(kMagic);
+    int lo0 = 0, lo1 = 0;
+    long long v0 = 0, v1 = 0;
+#pragma unroll
+    for (int i = 0; i < R; ++i) {
+        const F2 d = add2(digit[i], magic);
+        const int d0 = float_to_bits(d.x) - kMagicBits, d1 = float_to_bits(d.y) - kMagicBits;
+        if (i < 4) { lo0 += (int)pl.place32[i] * d0; lo1 += (int)pl.place32[i] * d1; }
+        else { v0 += pl.place64[i] * (long long)d0; v1 += pl.place64[i] * (long long)d1; }
+    }
+    v0 += lo0; v1 += lo1;
+    const long long prod = pl.product[R], half = prod >> 1;
+    if (v0 > half) v0 -= prod; else if (v0 < half - prod + 1) v0 += prod;
+    if (v1 > half) v1 -= prod; else if (v1 < half - prod + 1) v1 += prod;
+    x0 = v0; x1 = v1;
+}
 
 // Output tile of a cluster: its position in the raster and the CTA's share of it.
 struct PairTile {
@@ -345,8 +455,9 @@ rns_gemm_pair_kernel(const __grid_constant__ PairParams p) {
             // Two-byte outputs leave in pairs: lanes 2j and 2j+1 hold neighbouring features,
             // the even lane stores both features of the even tokens, the odd lane those of the
             // odd tokens (one 4-byte store instead of two 2-byte ones).
-            const bool pair_store = (p.out_type == RNS_OUT_F16 || p.out_type == RNS_OUT_BF16) && (p.ldo & 1) == 0 &&
-                                    (reinterpret_cast<uintptr_t>(p.out) & 3) == 0 && n0 + quarter * 32 + 32 <= p.n;
+            bool pair_store = (p.out_type == RNS_OUT_F16 || p.out_type == RNS_OUT_BF16) && (p.ldo & 1) == 0 &&
+                              (reinterpret_cast<uintptr_t>(p.out) & 3) == 0 && n0 + quarter * 32 + 32 <= p.n;
+            for (int g = 0; g < p.n_copies; ++g) pair_store = pair_store && (reinterpret_cast<uintptr_t>(p.out_copies[g]) & 3) == 0;
             auto load = [&](int col, int (&acc)[R][8]) {
                 __syncwarp();
 #pragma unroll
@@ -357,12 +468,12 @@ rns_gemm_pair_kernel(const __grid_constant__ PairParams p) {
                 if (tok_first >= p.m) return;                  // warp-uniform
                 XInt xv[8];
 #pragma unroll
-                for (int t8 = 0; t8 < 8; ++t8) {
-                    int one[R];
+                for (int t8 = 0; t8 < 8; t8 += 2) {
+                    int one0[R], one1[R];
 #pragma unroll
-                    for (int c = 0; c < R; ++c) one[c] = acc[c][t8];
-                    if constexpr (R <= 4) xv[t8] = reconstruct32<R>(one, p.plan, R);
-                    else xv[t8] = reconstruct<R>(one, p.plan, R);
+                    for (int c = 0; c < R; ++c) { one0[c] = acc[c][t8]; one1[c] = acc[c][t8 + 1]; }
+                    if constexpr (R <= 4) reconstruct32_x2<R>(one0, one1, p.plan, xv[t8], xv[t8 + 1]);
+                    else reconstruct64_x2<R>(one0, one1, p.plan, xv[t8], xv[t8 + 1]);
                 }
                 const int valid_t = min(8, p.m - tok_first);   // warp-uniform
                 if (!is_float) {
@@ -379,21 +490,24 @@ rns_gemm_pair_kernel(const __grid_constant__ PairParams p) {
                 }
                 float y[8];
 #pragma unroll
-                for (int t8 = 0; t8 < 8; ++t8) {
-                    float xf;
-                    if constexpr (R <= 4) xf = __int2float_rn(xv[t8]);
-                    else xf = __ll2float_rn(xv[t8]);
-                    const float rs = p.row_scale_stride == 0 ? rs_all : (t8 < valid_t ? p.row_scale[tok_first + t8] : 0.0f);
-                    float v = __fmul_rn(__fmul_rn(xf, rs), cs);
-                    if (p.bias != nullptr) v = __fadd_rn(v, bs);
-                    y[t8] = v;
+                for (int t8 = 0; t8 < 8; t8 += 2) {
+                    F2 xf, rs;
+                    if constexpr (R <= 4) { xf.x = __int2float_rn(xv[t8]); xf.y = __int2float_rn(xv[t8 + 1]); }
+                    else { xf.x = __ll2float_rn(xv[t8]); xf.y = __ll2float_rn(xv[t8 + 1]); }
+                    rs.x = p.row_scale_stride == 0 ? rs_all : (t8 < valid_t ? p.row_scale[tok_first + t8] : 0.0f);
+                    rs.y = p.row_scale_stride == 0 ? rs_all : (t8 + 1 < valid_t ? p.row_scale[tok_first + t8 + 1] : 0.0f);
+                    F2 v = mul2(mul2(xf, rs), f2_splat(cs));       // separately rounded, in the reference's order
+                    if (p.bias != nullptr) v = add2(v, f2_splat(bs));
+                    y[t8] = v.x; y[t8 + 1] = v.y;
                 }
                 if (p.out_type == RNS_OUT_F32) {
                     if (!feat_ok) return;
 #pragma unroll
                     for (int t8 = 0; t8 < 8; ++t8) {
                         if (t8 < valid_t) {
-                            static_cast<float*>(p.out)[(int64_t)(tok_first + t8) * p.ldo + feat] = y[t8];
+                            const int64_t o = (int64_t)(tok_first + t8) * p.ldo + feat;
+                            static_cast<float*>(p.out)[o] = y[t8];
+                            for (int g = 0; g < p.n_copies; ++g) static_cast<float*>(p.out_copies[g])[o] = y[t8];
                             biggest = fmaxf(biggest, fabsf(y[t8]));
                         }
                     }
@@ -427,12 +541,19 @@ rns_gemm_pair_kernel(const __grid_constant__ PairParams p) {
                             const unsigned word = odd ? (got | (mine << 16)) : (mine | (got << 16));
                             const int64_t o = (int64_t)(tok_first + t8) * p.ldo + (feat & ~1);
                             *reinterpret_cast<unsigned*>(out16 + o) = word;
+                            for (int g = 0; g < p.n_copies; ++g)
+                                *reinterpret_cast<unsigned*>(static_cast<unsigned short*>(p.out_copies[g]) + o) = word;
                         }
                     }
                 } else if (feat_ok) {
 #pragma unroll
-                    for (int t8 = 0; t8 < 8; ++t8)
-                        if (t8 < valid_t) out16[(int64_t)(tok_first + t8) * p.ldo + feat] = h[t8];
+                    for (int t8 = 0; t8 < 8; ++t8) {
+                        if (t8 < valid_t) {
+                            const int64_t o = (int64_t)(tok_first + t8) * p.ldo + feat;
+                            out16[o] = h[t8];
+                            for (int g = 0; g < p.n_copies; ++g) static_cast<unsigned short*>(p.out_copies[g])[o] = h[t8];
+                        }
+                    }
                 }
             };
             const int col0 = part * kColsPerPart;
@@ -497,8 +618,16 @@ rns_gemm_pair_kernel(const __grid_constant__ PairParams p) {
                 p.wait_info[2] = (int)blockIdx.y;
                 p.wait_info[3] = R * 1000000 + 200000 + TOK;
             }
-        } else if (p.absmax_out != nullptr && ctl.absmax != 0u) {
-            atomicMax(p.absmax_out, ctl.absmax);
+        } else if (p.absmax_out != nullptr) {
+            if (ctl.absmax != 0u) atomicMax(p.absmax_out, ctl.absmax);
+            if (p.n_copies > 0) {
+                // The last CTA to contribute hands the finished word to the other ranks.
+                __threadfence();
+                if (atomicAdd(p.absmax_out + 1, 1u) == gridDim.x - 1) {
+                    const uint32_t final_word = atomicMax(p.absmax_out, 0u);
+                    for (int g = 0; g < p.n_copies; ++g) *p.absmax_copies[g] = final_word;
+                }
+            }
         }
     }
     if (warp == 1) {
@@ -588,10 +717,15 @@ int launch_pair_gemm(const rns_linear_args* a, const Plan& plan, cudaStream_t st
     pp.row_scale = a->d_row_scale; pp.row_scale_stride = a->row_scale_stride;
     pp.col_scale = a->d_col_scale; pp.bias = a->d_bias;
     pp.absmax_out = a->d_absmax_out;
+    pp.n_copies = a->n_out_copies;
+    for (int g = 0; g < a->n_out_copies && g < RNS_MAX_PEERS; ++g) {
+        pp.out_copies[g] = a->d_out_copies[g];
+        pp.absmax_copies[g] = a->d_absmax_copies[g];
+    }
     pp.status = a->d_status; pp.wait_info = a->d_wait_info;
     const int64_t pairs = (int64_t)pp.n_ftiles * pp.n_ttiles;
     if (pairs > (1 << 30)) return fail(RNS_ERR_UNSUPPORTED, "too many output tiles");
-    if (a->d_absmax_out != nullptr) RNS_CUDA_OK(cudaMemsetAsync(a->d_absmax_out, 0, sizeof(uint32_t), st));
+    if (a->d_absmax_out != nullptr) RNS_CUDA_OK(cudaMemsetAsync(a->d_absmax_out, 0, 2 * sizeof(uint32_t), st));
     if (R == 4) return launch_pair<4, 128, 4, 6>(pp, (int)pairs, st);
     return launch_pair<5, 96, 4, 4>(pp, (int)pairs, st);
 }

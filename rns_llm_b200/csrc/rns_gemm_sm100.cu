@@ -988,10 +988,17 @@ int rns_linear_fused(const rns_linear_args* a, rns_stream_t stream) {
                                              "rows, packed weights, all channels active and K >= 512");
         if (is_float && a->d_absmax_out != nullptr && a->row_scale_stride != 0)
             return fail(RNS_ERR_INVALID_ARGUMENT, "d_absmax_out serves per-tensor scales");
+        if (a->n_out_copies < 0 || a->n_out_copies > RNS_MAX_PEERS)
+            return fail(RNS_ERR_INVALID_ARGUMENT, "n_out_copies must be in [0, %d]", RNS_MAX_PEERS);
+        if (a->n_out_copies > 0 && !is_float)
+            return fail(RNS_ERR_INVALID_ARGUMENT, "output copies serve floating outputs");
+        for (int g = 0; g < a->n_out_copies; ++g)
+            if (!a->d_out_copies[g] || (a->d_absmax_out != nullptr && !a->d_absmax_copies[g]))
+                return fail(RNS_ERR_INVALID_ARGUMENT, "d_out_copies / d_absmax_copies hold a NULL pointer");
         return launch_pair_gemm(a, pl, reinterpret_cast<cudaStream_t>(stream));
     }
-    if (a->d_absmax_out != nullptr)
-        return fail(RNS_ERR_UNSUPPORTED, "d_absmax_out is filled by variant 3 only");
+    if (a->d_absmax_out != nullptr || a->n_out_copies != 0)
+        return fail(RNS_ERR_UNSUPPORTED, "d_absmax_out and output copies are served by variant 3 only");
     if (a->variant == 2 && !tmem_gemm_supported(a))
         return fail(RNS_ERR_UNSUPPORTED, "variant 2 needs packed planes, packed weights and 2..5 channels");
     if (a->variant == 2)

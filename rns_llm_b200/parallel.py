@@ -64,7 +64,55 @@ def unshard(gathered: torch.Tensor, groups: int = 1) -> torch.Tensor:
     return gathered.view(world, m, groups, per).permute(1, 2, 0, 3).reshape(m, groups * world * per)
 
 
-ABSMAX_PAD = 8      # elements kept free behind each rank's block of a gathered buffer (>= 4 bytes, 16-byte multiple)
+ABSMAX_PAD = 8      # elements kept free behind each rank's block of a gathered buffer (>= 8 bytes, 16-byte multiple)
+
+
+class PeerArena:
+    """Symmetric memory for the gathered outputs of column-sharded layers: one buffer of the
+    same size on every rank of the group, each rank's buffer mapped into every other rank
+    (torch.distributed._symmetric_memory over CUDA peer access / NVLink).
+
+    With it a sharded layer needs no all-gather: the GEMM epilogue stores every output tile
+    into its slot of ALL ranks' buffers (plain peer stores, issued tile by tile while the
+    GEMM runs), and after the launch the ranks only meet at a barrier.  Blocks are handed out
+    in allocation order, which is the same on every rank, so a block sits at the same offset
+    everywhere.  Construction is collective; when symmetric memory is not available here
+    (no peer access, unsupported platform) it raises, and callers keep the NCCL all-gather.
+    """
+
+    def __init__(self, nbytes: int, device: torch.device, group=None) -> None:
+        import torch.distributed._symmetric_memory as symm_mem
+
+        self.group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        if self.world - 1 > 7:
+            raise ValueError("a peer arena serves at most 8 ranks")
+        self.nbytes = (int(nbytes) + 255) // 256 * 256
+        self.buffer = symm_mem.empty(self.nbytes, dtype=torch.uint8, device=device)
+        self.handle = symm_mem.rendezvous(self.buffer, self.group)
+        self.peer_bases = [int(p) for p in self.handle.buffer_ptrs]
+        if len(self.peer_bases) != self.world or self.peer_bases[self.rank] != self.buffer.data_ptr():
+            raise RuntimeError("symmetric memory returned an unexpected set of peer pointers")
+        self._offset = 0
+
+    def alloc(self, nbytes: int) -> tuple[torch.Tensor, int]:
+        """(local uint8 view, byte offset) of the next block; identical offsets on all ranks."""
+        start = self._offset
+        end = start + (int(nbytes) + 255) // 256 * 256
+        if end > self.nbytes:
+            raise RuntimeError(f"peer arena of {self.nbytes} bytes is full ({end} needed)")
+        self._offset = end
+        return self.buffer[start:start + int(nbytes)], start
+
+    def peer_addresses(self, offset: int) -> list[int]:
+        """Device address of byte ``offset`` in every OTHER rank's buffer, in rank order."""
+        return [base + offset for r, base in enumerate(self.peer_bases) if r != self.rank]
+
+    def barrier(self) -> None:
+        """All ranks' stores issued before it (on the current stream) are visible to every
+        rank after it; queued on the current stream, no host synchronisation."""
+        self.handle.barrier(channel=0)
 
 
 class GatheredActivation(torch.Tensor):
@@ -96,6 +144,11 @@ class ColumnShardedRNSLinear(nn.Module):
     [G, M, K/G] tensor from a previous sharded layer, and returns the gathered
     output [G, M, N/G] (``gather=True``) or the local shard [M, N/G].
 
+    Exchange: one NCCL all-gather after the GEMM, or - with ``peer_arena`` - none: the GEMM
+    epilogue stores each tile into every rank's buffer while it runs and the ranks meet at
+    a barrier (many-token calls with a per-tensor scale; other calls fall back to the
+    all-gather).  A layer with a peer arena owns its output buffer (as ``reuse_buffer``).
+
     Ownership of the result: by default every call returns a freshly allocated
     tensor, as the reference's ``RNSLinear`` does.  ``out=`` writes into the
     caller's [G, M, N/G] buffer.  ``reuse_buffer=True`` (constructor) makes the
@@ -107,9 +160,12 @@ class ColumnShardedRNSLinear(nn.Module):
 
     def __init__(self, weight_shard: torch.Tensor, bias_shard: torch.Tensor | None, *, backend,
                  moduli: Iterable[int], rank: int, world: int, group=None, groups: int = 1,
-                 activation_scale: str = "tensor", reuse_buffer: bool = False) -> None:
+                 activation_scale: str = "tensor", reuse_buffer: bool = False,
+                 peer_arena: "PeerArena | None" = None) -> None:
         super().__init__()
-        self.reuse_buffer = bool(reuse_buffer)
+        self.reuse_buffer = bool(reuse_buffer) or peer_arena is not None
+        self.peer_arena = peer_arena
+        self._peer_blocks: dict[tuple[int, torch.dtype], tuple[torch.Tensor, int]] = {}
         if weight_shard.ndim != 2:
             raise ValueError("weight_shard must be [N/world, K]")
         if activation_scale not in ("tensor", "row"):
@@ -171,18 +227,33 @@ class ColumnShardedRNSLinear(nn.Module):
             if gather and self.world > 1:
                 dist.all_gather_into_tensor(out.view(self.world * m, self.local_features), local, group=self.group)
             return out if gather else local
-        buf = self._buffer(m, flat.dtype, flat.device)
         count = m * self.local_features
-        gathered = buf[:, :count].view(self.world, m, self.local_features)      # stride(0) = count + pad
-        local = gathered[self.rank]
         report = (not self.per_row) and self.backend.supports_absmax_out(m=m, k=self.in_features,
                                                                          channels=len(self.moduli))
+        use_peers = self.peer_arena is not None and report and self.world > 1 and gather
+        if self.peer_arena is not None:
+            buf, offset = self._peer_block(m, flat.dtype)
+        else:
+            buf, offset = self._buffer(m, flat.dtype, flat.device), 0
+        gathered = buf[:, :count].view(self.world, m, self.local_features)      # stride(0) = count + pad
+        local = gathered[self.rank]
         word = buf[self.rank, count:].data_ptr() if report else None
+        out_copies: list[int] = []
+        absmax_copies: list[int] = []
+        if use_peers:
+            size = buf.element_size()
+            block = (count + ABSMAX_PAD) * size
+            mine = offset + self.rank * block                      # my slot, at the same offset on every rank
+            out_copies = self.peer_arena.peer_addresses(mine)
+            absmax_copies = self.peer_arena.peer_addresses(mine + count * size)
         self.backend.linear_forward(flat, self.prepared, self.weight_scale, self.bias,
-                                    per_row=self.per_row, out=local, absmax_in=absmax_in, absmax_out=word)
+                                    per_row=self.per_row, out=local, absmax_in=absmax_in, absmax_out=word,
+                                    out_copies=out_copies, absmax_copies=absmax_copies)
         if not gather:
             return local
-        if self.world > 1:
+        if use_peers:
+            self.peer_arena.barrier()
+        elif self.world > 1:
             # In place: this rank's block (shard + absmax word) already sits at its slot.
             dist.all_gather_into_tensor(buf.view(-1), buf[self.rank], group=self.group)
         if not report:
@@ -191,6 +262,18 @@ class ColumnShardedRNSLinear(nn.Module):
         result.absmax_words = (buf[0, count:].data_ptr(), self.world,
                                (count + ABSMAX_PAD) * buf.element_size() // 4)
         return result
+
+    def _peer_block(self, m: int, dtype: torch.dtype) -> tuple[torch.Tensor, int]:
+        """This layer's [G, M*N/G + pad] buffer inside the peer arena (allocated on first use,
+        in the same order on every rank) and its byte offset."""
+        key = (m, dtype)
+        hit = self._peer_blocks.get(key)
+        if hit is None:
+            block = m * self.local_features + ABSMAX_PAD
+            raw, offset = self.peer_arena.alloc(self.world * block * dtype.itemsize)
+            hit = (raw.view(dtype).view(self.world, block), offset)
+            self._peer_blocks[key] = hit
+        return hit
 
 
 def sharded_qkv_from_linears(q_proj: nn.Linear, k_proj: nn.Linear, v_proj: nn.Linear, *, backend, moduli,

@@ -149,3 +149,38 @@ def test_sharded_layers_pass_the_absmax_on(backend):
     expect2 = O.rns_linear_forward(y1[0].cpu().numpy(), w2.cpu().numpy(), None, C0)["y"]
     assert np.array_equal(y2[0].cpu().numpy().view(np.uint16), expect2.view(np.uint16))
     backend.check_status()
+
+
+def test_output_copies_and_absmax_hand_over(backend):
+    """The epilogue's fan-out, on one GPU: buffers of this process stand in for the other
+    ranks' memory.  Every copy receives exactly what `out` receives, and the finished
+    absmax word (written by the last CTA to contribute) equals max |y|."""
+    torch.manual_seed(31)
+    m, k, n = 640, 1024, 520
+    x = torch.randn(m, k, dtype=torch.float16, device="cuda")
+    weight = (torch.randn(n, k, device="cuda") * 0.05).half()
+    bias = torch.randn(n, device="cuda").float()
+    w_q, w_scale, _ = backend.quantize_weight(weight)
+    prepared = backend.prepare_weight_nk(w_q, C0)
+    plain = backend.linear_forward(x, prepared, w_scale, bias).clone()
+    for copies in (1, 3, 7):
+        out = torch.full((m, n), float("nan"), dtype=torch.float16, device="cuda")
+        peers = [torch.full((m, n), float("nan"), dtype=torch.float16, device="cuda") for _ in range(copies)]
+        words = torch.zeros(2, dtype=torch.int32, device="cuda")
+        peer_words = torch.full((copies, 4), -1, dtype=torch.int32, device="cuda")
+        backend.linear_forward(x, prepared, w_scale, bias, out=out, absmax_out=words.data_ptr(),
+                               out_copies=[p.data_ptr() for p in peers],
+                               absmax_copies=[peer_words[i].data_ptr() for i in range(copies)])
+        torch.cuda.synchronize()
+        assert torch.equal(out, plain)
+        for p in peers:
+            assert torch.equal(p, plain)
+        expect = float(plain.float().abs().max())
+        assert words[:1].view(torch.float32).item() == expect
+        assert int(words[1]) == 148 or int(words[1]) > 0            # every CTA counted itself
+        for i in range(copies):
+            assert peer_words[i, :1].view(torch.float32).item() == expect
+            assert int(peer_words[i, 1]) == -1                       # only the word itself is handed over
+    backend.check_status()
+    with pytest.raises(ValueError):
+        backend.linear_forward(x[:64], prepared, w_scale, bias, out_copies=[plain.data_ptr()])

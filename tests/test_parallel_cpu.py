@@ -105,7 +105,7 @@ class _FakeBackend:
         return False
 
     def linear_forward(self, x, prepared, weight_scale, bias, *, per_row=False, out=None, absmax_in=None,
-                       absmax_out=None):
+                       absmax_out=None, out_copies=(), absmax_copies=()):
         if x.ndim == 3:
             x = unshard(x.contiguous(), 1)
         s_a = x.float().abs().amax().clamp_min(1e-8) / 127.0
