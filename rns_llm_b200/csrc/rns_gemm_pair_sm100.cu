@@ -208,7 +208,9 @@ __device__ __forceinline__ PairTile pair_tile(const PairParams& p, int tile, uin
 // one stage counter g that keeps counting across tiles (slot = g mod depth), so the loads
 // and the weight encoding of the next tile start while this tile's last MMAs and its
 // epilogue are still running; only the MMAs wait for the accumulators to be drained.
-template <int R, int TOK, int ES, int PS>
+// COPIES: the instantiation that also stores into the other ranks' buffers; the plain one
+// carries none of that code.
+template <int R, int TOK, int ES, int PS, bool COPIES>
 __global__ void __launch_bounds__(kPairThreads, 1)
 rns_gemm_pair_kernel(const __grid_constant__ PairParams p) {
     static_assert(R * TOK <= 512, "accumulators must fit tensor memory");
@@ -457,7 +459,7 @@ rns_gemm_pair_kernel(const __grid_constant__ PairParams p) {
             // odd tokens (one 4-byte store instead of two 2-byte ones).
             bool pair_store = (p.out_type == RNS_OUT_F16 || p.out_type == RNS_OUT_BF16) && (p.ldo & 1) == 0 &&
                               (reinterpret_cast<uintptr_t>(p.out) & 3) == 0 && n0 + quarter * 32 + 32 <= p.n;
-            for (int g = 0; g < p.n_copies; ++g) pair_store = pair_store && (reinterpret_cast<uintptr_t>(p.out_copies[g]) & 3) == 0;
+            for (int g = 0; COPIES && g < p.n_copies; ++g) pair_store = pair_store && (reinterpret_cast<uintptr_t>(p.out_copies[g]) & 3) == 0;
             auto load = [&](int col, int (&acc)[R][8]) {
                 __syncwarp();
 #pragma unroll
@@ -507,7 +509,7 @@ rns_gemm_pair_kernel(const __grid_constant__ PairParams p) {
                         if (t8 < valid_t) {
                             const int64_t o = (int64_t)(tok_first + t8) * p.ldo + feat;
                             static_cast<float*>(p.out)[o] = y[t8];
-                            for (int g = 0; g < p.n_copies; ++g) static_cast<float*>(p.out_copies[g])[o] = y[t8];
+                            for (int g = 0; COPIES && g < p.n_copies; ++g) static_cast<float*>(p.out_copies[g])[o] = y[t8];
                             biggest = fmaxf(biggest, fabsf(y[t8]));
                         }
                     }
@@ -541,7 +543,7 @@ rns_gemm_pair_kernel(const __grid_constant__ PairParams p) {
                             const unsigned word = odd ? (got | (mine << 16)) : (mine | (got << 16));
                             const int64_t o = (int64_t)(tok_first + t8) * p.ldo + (feat & ~1);
                             *reinterpret_cast<unsigned*>(out16 + o) = word;
-                            for (int g = 0; g < p.n_copies; ++g)
+                            for (int g = 0; COPIES && g < p.n_copies; ++g)
                                 *reinterpret_cast<unsigned*>(static_cast<unsigned short*>(p.out_copies[g]) + o) = word;
                         }
                     }
@@ -551,7 +553,7 @@ rns_gemm_pair_kernel(const __grid_constant__ PairParams p) {
                         if (t8 < valid_t) {
                             const int64_t o = (int64_t)(tok_first + t8) * p.ldo + feat;
                             out16[o] = h[t8];
-                            for (int g = 0; g < p.n_copies; ++g) static_cast<unsigned short*>(p.out_copies[g])[o] = h[t8];
+                            for (int g = 0; COPIES && g < p.n_copies; ++g) static_cast<unsigned short*>(p.out_copies[g])[o] = h[t8];
                         }
                     }
                 }
@@ -620,12 +622,12 @@ rns_gemm_pair_kernel(const __grid_constant__ PairParams p) {
             }
         } else if (p.absmax_out != nullptr) {
             if (ctl.absmax != 0u) atomicMax(p.absmax_out, ctl.absmax);
-            if (p.n_copies > 0) {
+            if (COPIES && p.n_copies > 0) {
                 // The last CTA to contribute hands the finished word to the other ranks.
                 __threadfence();
                 if (atomicAdd(p.absmax_out + 1, 1u) == gridDim.x - 1) {
                     const uint32_t final_word = atomicMax(p.absmax_out, 0u);
-                    for (int g = 0; g < p.n_copies; ++g) *p.absmax_copies[g] = final_word;
+                    for (int g = 0; COPIES && g < p.n_copies; ++g) *p.absmax_copies[g] = final_word;
                 }
             }
         }
@@ -639,7 +641,7 @@ rns_gemm_pair_kernel(const __grid_constant__ PairParams p) {
 // ---------------------------------------------------------------------------
 // Host side
 // ---------------------------------------------------------------------------
-template <int R, int TOK, int ES, int PS>
+template <int R, int TOK, int ES, int PS, bool COPIES>
 static int launch_pair(const PairParams& pp, int pairs, cudaStream_t st) {
     constexpr size_t smem = (size_t)ES * R * kPairOpTile + (size_t)PS * R * (TOK / 2) * kPackK + 1024;
     static_assert(smem + sizeof(PairCtl) <= 227 * 1024, "rings exceed shared memory");
@@ -662,12 +664,12 @@ static int launch_pair(const PairParams& pp, int pairs, cudaStream_t st) {
     cfg.numAttrs = 1;
     int clusters = resident[dev & 63].load(std::memory_order_acquire);
     if (clusters == 0) {
-        RNS_CUDA_OK(cudaFuncSetAttribute(rns_gemm_pair_kernel<R, TOK, ES, PS>,
+        RNS_CUDA_OK(cudaFuncSetAttribute(rns_gemm_pair_kernel<R, TOK, ES, PS, COPIES>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         int sms = 0;
         RNS_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
         cfg.gridDim = dim3((unsigned)(sms & ~1), 1, 1);
-        if (cudaOccupancyMaxActiveClusters(&clusters, rns_gemm_pair_kernel<R, TOK, ES, PS>, &cfg) != cudaSuccess ||
+        if (cudaOccupancyMaxActiveClusters(&clusters, rns_gemm_pair_kernel<R, TOK, ES, PS, COPIES>, &cfg) != cudaSuccess ||
             clusters < 1) {
             cudaGetLastError();
             clusters = sms / 2 > 8 ? sms / 2 - 4 : 1;          // a safe guess: a few SMs short of all
@@ -676,7 +678,7 @@ static int launch_pair(const PairParams& pp, int pairs, cudaStream_t st) {
     }
     if (clusters > pairs) clusters = pairs;
     cfg.gridDim = dim3((unsigned)(2 * clusters), 1, 1);
-    const cudaError_t rc = cudaLaunchKernelEx(&cfg, rns_gemm_pair_kernel<R, TOK, ES, PS>, pp);
+    const cudaError_t rc = cudaLaunchKernelEx(&cfg, rns_gemm_pair_kernel<R, TOK, ES, PS, COPIES>, pp);
     if (rc != cudaSuccess) {
         cudaGetLastError();
         return fail(RNS_ERR_CUDA, "launch of the paired RNS GEMM failed: %s (%d clusters for %d tiles, smem %zu)",
@@ -726,8 +728,12 @@ int launch_pair_gemm(const rns_linear_args* a, const Plan& plan, cudaStream_t st
     const int64_t pairs = (int64_t)pp.n_ftiles * pp.n_ttiles;
     if (pairs > (1 << 30)) return fail(RNS_ERR_UNSUPPORTED, "too many output tiles");
     if (a->d_absmax_out != nullptr) RNS_CUDA_OK(cudaMemsetAsync(a->d_absmax_out, 0, 2 * sizeof(uint32_t), st));
-    if (R == 4) return launch_pair<4, 128, 4, 6>(pp, (int)pairs, st);
-    return launch_pair<5, 96, 4, 4>(pp, (int)pairs, st);
+    if (pp.n_copies > 0) {
+        if (R == 4) return launch_pair<4, 128, 4, 6, true>(pp, (int)pairs, st);
+        return launch_pair<5, 96, 4, 4, true>(pp, (int)pairs, st);
+    }
+    if (R == 4) return launch_pair<4, 128, 4, 6, false>(pp, (int)pairs, st);
+    return launch_pair<5, 96, 4, 4, false>(pp, (int)pairs, st);
 }
 
 }  // namespace rns

@@ -40,24 +40,25 @@ def _worker(rank: int, world: int, port: int, results):
         w2 = (torch.randn(1024, 1536, device=device) * 0.04).half()
 
         def chain(arena):
-            l1 = ColumnShardedRNSLinear(shard_tensor(w1, world, rank, 3), shard_tensor(b1, world, rank, 3),
-                                        backend=backend, moduli=C0, rank=rank, world=world, groups=3, peer_arena=arena)
+            l1 = ColumnShardedRNSLinear(shard_tensor(w1, world, rank), shard_tensor(b1, world, rank),
+                                        backend=backend, moduli=C0, rank=rank, world=world, peer_arena=arena)
             l2 = ColumnShardedRNSLinear(shard_tensor(w2, world, rank), None, backend=backend, moduli=C0, rank=rank,
                                         world=world, peer_arena=arena)
             y1 = l1(x)
             carried = isinstance(y1, GatheredActivation) and y1.absmax_words is not None
             y2 = l2(y1)
             torch.cuda.synchronize()
-            return unshard(y1, 3).clone(), unshard(y2, 1).clone(), carried
+            return unshard(y1, 1).clone(), unshard(y2, 1).clone(), carried
 
         # unsharded, on this rank alone
-        f1 = ColumnShardedRNSLinear(w1, b1, backend=backend, moduli=C0, rank=0, world=1, groups=3)
+        f1 = ColumnShardedRNSLinear(w1, b1, backend=backend, moduli=C0, rank=0, world=1)
         f2 = ColumnShardedRNSLinear(w2, None, backend=backend, moduli=C0, rank=0, world=1)
         full1 = f1(x)
         full2 = unshard(f2(full1), 1)
-        full1 = unshard(full1, 3)
+        full1 = unshard(full1, 1)
         n1, n2, carried_nccl = chain(None)
-        ok = torch.equal(n1, full1) and torch.equal(n2, full2) and carried_nccl
+        checks = {"nccl layer 1": torch.equal(n1, full1), "nccl layer 2": torch.equal(n2, full2),
+                  "nccl absmax words": bool(carried_nccl)}
         peer_note = ""
         try:
             arena = PeerArena(64 << 20, device)
@@ -68,9 +69,12 @@ def _worker(rank: int, world: int, port: int, results):
         if int(flag.item()):
             for _ in range(3):                                    # buffers are reused: several rounds
                 p1, p2, carried_peer = chain(arena)
-                ok = ok and torch.equal(p1, full1) and torch.equal(p2, full2) and carried_peer
+                checks["peer layer 1"] = checks.get("peer layer 1", True) and torch.equal(p1, full1)
+                checks["peer layer 2"] = checks.get("peer layer 2", True) and torch.equal(p2, full2)
+                checks["peer absmax words"] = checks.get("peer absmax words", True) and bool(carried_peer)
         backend.check_status()
-        results[rank] = (bool(ok), peer_note)
+        failed = [name for name, good in checks.items() if not good]
+        results[rank] = (not failed, f"failed: {failed}; {peer_note}")
     finally:
         dist.destroy_process_group()
 
