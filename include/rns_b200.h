@@ -265,20 +265,25 @@ typedef struct rns_linear_args {
     int32_t variant;          /* 0 = choose; 1: operands staged in shared memory; 2: weights as
                                  tensor-memory operands (packed planes + packed weights, 2..5
                                  channels; tile_n then means tokens per tile: 32, 64 or 128);
-                                 3: two-CTA feature-major kernel (see a_tile_rows) */
+                                 3 and 4: two-CTA feature-major kernels (see a_tile_rows); 4, the
+                                 one 0 resolves to for that layout, gives every residue channel
+                                 the int8 weight itself as its weight operand (a representative
+                                 of the same residue class: the sums differ by multiples of the
+                                 modulus, the reconstructed integers not at all), 3 encodes the
+                                 canonical weight residues per channel inside the kernel */
     int32_t exact_residues;   /* 1: in-kernel residues exactly centred (|r| <= m/2; needs every
                                  modulus >= 86); 0: one-step reduced residues (any moduli) */
     int32_t a_tile_rows;      /* packed planes only: token rows per packed tile. 0 or 128: the layout
                                  above.  64 (up to four channels) or 48 (five): tiles of that many
                                  rows, [M_pad/rows][K_pad/64][channels][rows][64], written by
                                  rns_quantize_activations_tiled; selects the two-CTA feature-major
-                                 kernel (variant 3), which needs 4 or 5 channels and K >= 512 */
+                                 kernels (variants 3 and 4), which need 4 or 5 channels and K >= 512 */
     uint32_t* d_absmax_out;   /* NULL, or device word that receives the bit pattern of
-                                 max |y| over the floating outputs as stored (variant 3 only;
+                                 max |y| over the floating outputs as stored (variants 3 and 4 only;
                                  two words: the launch clears both and uses [1] as a counter): the per-tensor absmax the NEXT
                                  layer's quantiser needs, so that it can skip its own pass over
                                  the activations (layers/rns_linear.py:239-240 of the reference) */
-    int32_t n_out_copies;     /* variant 3, floating outputs: the tile is ALSO stored, at the same
+    int32_t n_out_copies;     /* variants 3 and 4, floating outputs: the tile is ALSO stored, at the same
                                  offsets (same ldo), into these buffers - the same output slot in
                                  the memory of the other ranks of a column-sharded layer, mapped
                                  into this process (peer memory over NVLink; plain stores only).

@@ -977,14 +977,15 @@ int rns_linear_fused(const rns_linear_args* a, rns_stream_t stream) {
     // (packed planes + packed weights only).  Variant 2 is limited to 64-token tiles by
     // the 512 tensor-memory columns and measured slower (775 vs 1050 channel-TOPS at
     // 4096^3, four channels), so 0 always resolves to 1; 2 stays selectable.
-    if (a->variant < 0 || a->variant > 3) return fail(RNS_ERR_INVALID_ARGUMENT, "variant must be 0, 1, 2 or 3");
-    // 3: the two-CTA feature-major kernel; the only one that reads planes in tiles of
-    // a_tile_rows != 128 rows, so that layout selects it.
-    if (a->variant == 3 || (a->a_tile_rows != 0 && a->a_tile_rows != kPackM)) {
-        if (a->variant != 0 && a->variant != 3)
-            return fail(RNS_ERR_INVALID_ARGUMENT, "planes in tiles of %d rows are read by variant 3 only", a->a_tile_rows);
+    if (a->variant < 0 || a->variant > 4) return fail(RNS_ERR_INVALID_ARGUMENT, "variant must be 0, 1, 2, 3 or 4");
+    // 3 and 4: the two-CTA feature-major kernels, the only ones that read planes in tiles
+    // of a_tile_rows != 128 rows, so that layout selects them (4 unless 3 is asked for).
+    // 4 feeds every channel the int8 weight itself, 3 encodes canonical weight residues.
+    if (a->variant >= 3 || (a->a_tile_rows != 0 && a->a_tile_rows != kPackM)) {
+        if (a->variant != 0 && a->variant < 3)
+            return fail(RNS_ERR_INVALID_ARGUMENT, "planes in tiles of %d rows are read by variants 3 and 4 only", a->a_tile_rows);
         if (!pair_gemm_supported(a))
-            return fail(RNS_ERR_UNSUPPORTED, "variant 3 needs packed planes in tiles of 64 (4 channels) or 48 (5 channels) "
+            return fail(RNS_ERR_UNSUPPORTED, "variants 3 and 4 need packed planes in tiles of 64 (4 channels) or 48 (5 channels) "
                                              "rows, packed weights, all channels active and K >= 512");
         if (is_float && a->d_absmax_out != nullptr && a->row_scale_stride != 0)
             return fail(RNS_ERR_INVALID_ARGUMENT, "d_absmax_out serves per-tensor scales");
@@ -998,7 +999,7 @@ int rns_linear_fused(const rns_linear_args* a, rns_stream_t stream) {
         return launch_pair_gemm(a, pl, reinterpret_cast<cudaStream_t>(stream));
     }
     if (a->d_absmax_out != nullptr || a->n_out_copies != 0)
-        return fail(RNS_ERR_UNSUPPORTED, "d_absmax_out and output copies are served by variant 3 only");
+        return fail(RNS_ERR_UNSUPPORTED, "d_absmax_out and output copies are served by variants 3 and 4 only");
     if (a->variant == 2 && !tmem_gemm_supported(a))
         return fail(RNS_ERR_UNSUPPORTED, "variant 2 needs packed planes, packed weights and 2..5 channels");
     if (a->variant == 2)

@@ -33,7 +33,7 @@ def tiled_plane_offsets(m, k, channels, tile_rows):
     return tile * (tile_rows * 64) + inner
 
 
-def pair_int(backend, a, w_nk, mods, out_dtype=torch.int64):
+def pair_int(backend, a, w_nk, mods, out_dtype=torch.int64, variant=0):
     from rns_llm_b200 import _native as N
     lib = N.load()
     m, k = a.shape
@@ -48,23 +48,40 @@ def pair_int(backend, a, w_nk, mods, out_dtype=torch.int64):
     prepared = backend.prepare_weight_nk(w_dev, mods)
     out = torch.full((m, w_nk.shape[0]), -7, dtype=out_dtype, device="cuda")
     backend._launch_fused(prepared=prepared, m=m, a=None, a_planes=torch.from_numpy(host).cuda(), a_packed=True,
-                          out=out, a_tile_rows=rows)
+                          out=out, a_tile_rows=rows, variant=variant)
     torch.cuda.synchronize()
     backend.check_status()
     return out.cpu().numpy()
 
 
+@pytest.mark.parametrize("variant", [0, 3, 4])   # 0 resolves to 4 (int8 weights as every channel's operand); 3 encodes
 @pytest.mark.parametrize("mods", [C0, C4])
 @pytest.mark.parametrize("m,k,n", [(128, 512, 256), (300, 1024, 260), (97, 528, 130), (700, 2048, 700),
-                                   (1024, 4096, 512)])
-def test_pair_kernel_exact_integers(backend, mods, m, k, n):
+                                   (1024, 4096, 512), (260, 576, 1000), (1300, 576, 2000)])
+def test_pair_kernel_exact_integers(backend, mods, m, k, n, variant):
     rng = np.random.default_rng(m + k + n + len(mods))
     a = rng.integers(-128, 128, size=(m, k)).astype(np.int8)
     w = rng.integers(-128, 128, size=(n, k)).astype(np.int8)
     exact = O.exact_matmul(a, w.T)
-    assert np.array_equal(pair_int(backend, a, w, mods), exact)
+    assert np.array_equal(pair_int(backend, a, w, mods, variant=variant), exact)
     if len(mods) == 4:
-        assert np.array_equal(pair_int(backend, a, w, mods, torch.int32), exact.astype(np.int32))
+        assert np.array_equal(pair_int(backend, a, w, mods, torch.int32, variant=variant), exact.astype(np.int32))
+
+
+@pytest.mark.parametrize("mods,k", [(C0, 4096), (C4, 16384)])
+def test_pair_kernel_extreme_magnitudes(backend, mods, k):
+    """Every product at its largest magnitude and one sign: the channel sums of the kernel that
+    feeds raw int8 weights reach K * 64 * 128 (K * 128 * 128 could not occur: the activation
+    side is always a reduced residue), far inside int32; the integers stay exact."""
+    m, n = 256, 256
+    for a_val, w_val in ((-128, -128), (127, -128), (64, -128), (-65, 127), (63, 127)):
+        a = np.full((m, k), a_val, dtype=np.int8)
+        w = np.full((n, k), w_val, dtype=np.int8)
+        a[::7, ::5] = -a_val if a_val != -128 else 127           # a few sign changes so that rows differ
+        exact = O.exact_matmul(a, w.T)
+        if np.abs(exact).max() > (int(np.prod([int(v) for v in mods], dtype=object)) - 1) // 2:
+            continue                                             # beyond the moduli set's capacity
+        assert np.array_equal(pair_int(backend, a, w, mods), exact)
 
 
 @pytest.mark.parametrize("mods", [C0, C4])
