@@ -40,6 +40,9 @@ struct Plan {
     // floor(2^32/m) clipped to INT32_MAX: q = mulhi(v, recip) is within one of
     // floor(v/m) for any int32 v, so v - q*m lies in [-m, 2m).
     int32_t recip[kMaxCh];
+    // m * floor(2^31 / m): added to an int32 sum it gives a non-negative uint32 of the same
+    // residue class (needs |sum| <= 2^31 - m, which the K bound of the callers guarantees).
+    uint32_t ubias[kMaxCh];
     float modf[kMaxCh];
     float rcpf[kMaxCh];            // 1.0f / m
     // Flattened Garner: digit_i = centred( r_i*gscale[i] + sum_{j<i} gneg[i][j]*digit_j  mod m_i )
@@ -148,6 +151,13 @@ RNS_HD int mul_hi(int a, int b) {
     return (int)(((long long)a * (long long)b) >> 32);
 #endif
 }
+RNS_HD uint32_t mul_hi_u32(uint32_t a, uint32_t b) {
+#ifdef __CUDA_ARCH__
+    return __umulhi(a, b);
+#else
+    return (uint32_t)(((unsigned long long)a * (unsigned long long)b) >> 32);
+#endif
+}
 
 // Exact int -> float for |v| < 2^22 without the conversion unit.
 RNS_HD float small_int_to_float(int v) { return add_rn(bits_to_float(v + kMagicBits), -kMagic); }
@@ -156,6 +166,16 @@ RNS_HD int small_float_to_int(float v) { return float_to_bits(add_rn(v, kMagic))
 
 // Loose residue of an int32 accumulator: congruent to v mod m, in [-m, 2m).
 RNS_HD int loose_residue(int v, int m, int recip) { return v - mul_hi(v, recip) * m; }
+
+// Canonical residue in [0, m) of an int32 accumulator with |v| <= 2^31 - m: bias to a
+// non-negative uint32, unsigned Barrett step (quotient at most one short), one conditional
+// subtraction.  Fits a byte for every modulus up to 255.
+RNS_HD uint32_t canonical_residue(int v, int m, int recip, uint32_t ubias) {
+    const uint32_t u = (uint32_t)v + ubias;
+    uint32_t r = u - mul_hi_u32(u, (uint32_t)recip) * (uint32_t)m;      // [0, 2m)
+    const uint32_t r2 = r - (uint32_t)m;
+    return r2 < r ? r2 : r;                                             // r >= m: r - m, else r
+}
 
 // t -> representative of t mod m with |result| <= m/2 (t integral, |t| < 2^22).
 RNS_HD float centre_mod(float t, float m, float rcp) {
@@ -233,13 +253,6 @@ RNS_HD int reconstruct32(const int (&acc)[R], const Plan& pl, int active) {
     return sx;
 }
 
-RNS_HD uint32_t mul_hi_u32(uint32_t a, uint32_t b) {
-#ifdef __CUDA_ARCH__
-    return __umulhi(a, b);
-#else
-    return (uint32_t)(((unsigned long long)a * (unsigned long long)b) >> 32);
-#endif
-}
 
 // Centred residues of four packed int8 values for one modulus (single fold;
 // requires m >= 86).  u = bytes biased by 128, ul = u with the top bit of each

@@ -28,6 +28,9 @@
 
 namespace rns {
 
+#ifndef RNS_PAIR_SPLIT_EPILOGUE
+#define RNS_PAIR_SPLIT_EPILOGUE 1   // 0: single-phase epilogue, for comparison builds
+#endif
 constexpr int kRawStages = 8;      // ring depth (even: an issuer warp keeps its slots; <= kDoneRing)
 
 template <int R, int TOK, bool COPIES>
@@ -198,8 +201,8 @@ rns_gemm_pair_raw_kernel(const __grid_constant__ PairParams p) {
             const PairTile t = pair_tile<TOK>(p, tile, rank);
             if (!warp_wait_bounded(smem_addr(&ctl.acc_full), (uint32_t)ti & 1u, abort, wait_code(11, ti))) break;
             tc_fence_after();
-            pair_epilogue<R, TOK, COPIES>(p, t.n0, t.tok0, quarter, part, lane, lane_base, is_float, rs_all, biggest);
-            release();
+            pair_epilogue<R, TOK, COPIES, (R <= 4 && RNS_PAIR_SPLIT_EPILOGUE != 0)>(p, t.n0, t.tok0, quarter, part, lane, lane_base, is_float, rs_all,
+                                                    biggest, release);
         }
         if (p.absmax_out != nullptr && is_float) {
 #pragma unroll

@@ -262,7 +262,7 @@ rns_gemm_pair_kernel(const __grid_constant__ PairParams p) {
             if (ok) ok = warp_wait_bounded(smem_addr(&ctl.acc_full), (uint32_t)ti & 1u, abort, wait_code(11, ti));
             if (!ok) break;
             tc_fence_after();
-            pair_epilogue<R, TOK, COPIES>(p, n0, tok0, quarter, part, lane, lane_base, is_float, rs_all, biggest);
+            pair_epilogue<R, TOK, COPIES, false>(p, n0, tok0, quarter, part, lane, lane_base, is_float, rs_all, biggest, [] {});
             // Every column this warp read belongs to channel blocks c*TOK + [col0, col0 + TOK/4);
             // the columns it ZEROES are its 128-column block.  All sixteen warps have to be
             // done reading before anyone's zeroes may land on columns another warp still reads.

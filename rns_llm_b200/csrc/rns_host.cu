@@ -69,6 +69,7 @@ int build_plan(const int32_t* moduli, int channels, Plan* out) {
         p.mod[i] = m;
         const uint64_t recip = (1ull << 32) / (uint64_t)m;
         p.recip[i] = recip > (uint64_t)INT_MAX ? INT_MAX : (int32_t)recip;
+        p.ubias[i] = (uint32_t)m * (uint32_t)((1u << 31) / (uint32_t)m);
         p.modf[i] = (float)m;
         p.rcpf[i] = 1.0f / (float)m;
         const int half = m / 2;
@@ -158,6 +159,24 @@ int rns_host_reconstruct(const int32_t* sums, int64_t count, const int32_t* modu
                 return rns::fail(RNS_ERR_INVALID_ARGUMENT,
                                  "32- and 64-bit reconstructions disagree at %lld: %d vs %lld",
                                  (long long)i, narrow, wide);
+        }
+        // The two-phase epilogue first replaces each sum by its canonical residue (packed
+        // into a byte), then reconstructs from those: same integer.
+        {
+            int res[rns::kMaxCh] = {0};
+            bool in_range = true;
+            for (int c = 0; c < channels; ++c) {
+                if (acc[c] > INT32_MAX - plan.mod[c] || acc[c] < -(INT32_MAX - plan.mod[c])) in_range = false;
+                const uint32_t r = rns::canonical_residue(acc[c], plan.mod[c], plan.recip[c], plan.ubias[c]);
+                const long long expect = (((long long)acc[c] % plan.mod[c]) + plan.mod[c]) % plan.mod[c];
+                if (in_range && (long long)r != expect)
+                    return rns::fail(RNS_ERR_INVALID_ARGUMENT, "canonical residue of %d mod %d is %u, expected %lld",
+                                     acc[c], plan.mod[c], r, expect);
+                res[c] = (int)r;
+            }
+            if (in_range && rns::reconstruct<rns::kMaxCh>(res, plan, active) != wide)
+                return rns::fail(RNS_ERR_INVALID_ARGUMENT, "reconstruction from canonical residues disagrees at %lld",
+                                 (long long)i);
         }
         out[i] = wide;
     }

@@ -98,15 +98,16 @@ __device__ __forceinline__ F2 add2(F2 a, F2 b) {
     return f2_from(d);
 }
 
-// Centred mixed-radix digits of two outputs (all R channels active).
-template <int R>
+// Centred mixed-radix digits of two outputs (all R channels active).  RES: a0 / a1 hold
+// residues in [0, m) already (canonical_residue) instead of int32 channel sums.
+template <int R, bool RES = false>
 __device__ __forceinline__ void garner_digits_x2(const int (&a0)[R], const int (&a1)[R], const Plan& pl, F2 (&digit)[R]) {
     const F2 magic = f2_splat(kMagic), neg_magic = f2_splat(-kMagic);
 #pragma unroll
     for (int i = 0; i < R; ++i) {
         F2 r;
-        r.x = bits_to_float(loose_residue(a0[i], pl.mod[i], pl.recip[i]) + kMagicBits);
-        r.y = bits_to_float(loose_residue(a1[i], pl.mod[i], pl.recip[i]) + kMagicBits);
+        r.x = bits_to_float((RES ? a0[i] : loose_residue(a0[i], pl.mod[i], pl.recip[i])) + kMagicBits);
+        r.y = bits_to_float((RES ? a1[i] : loose_residue(a1[i], pl.mod[i], pl.recip[i])) + kMagicBits);
         r = add2(r, neg_magic);                                   // small_int_to_float
         F2 t = (i == 0) ? r : mul2(r, f2_splat(pl.gscale[i]));
 #pragma unroll
@@ -118,11 +119,11 @@ __device__ __forceinline__ void garner_digits_x2(const int (&a0)[R], const int (
 }
 
 // reconstruct32 for two outputs (R <= 4, all channels active).
-template <int R>
+template <int R, bool RES = false>
 __device__ __forceinline__ void reconstruct32_x2(const int (&a0)[R], const int (&a1)[R], const Plan& pl, int& x0, int& x1) {
     static_assert(R <= 4, "32-bit reconstruction covers at most four channels");
     F2 digit[R];
-    garner_digits_x2<R>(a0, a1, pl, digit);
+    garner_digits_x2<R, RES>(a0, a1, pl, digit);
     const F2 magic = f2_splat(kMagic);
     unsigned u0 = 0, u1 = 0;
     if constexpr (R == 4) {
@@ -198,9 +199,17 @@ __device__ __forceinline__ PairTile pair_tile(const PairParams& p, int tile, uin
 // part*TOK/4 .. +TOK/4 of every channel block.  Reads the R int32 sums of each output,
 // reconstructs the integer, scales, converts and stores (also into the other ranks'
 // buffers when COPIES); `biggest` collects max |y| of the stored values.
-template <int R, int TOK, bool COPIES>
+//
+// SPLIT (up to four channels): two phases.  The first only empties tensor memory: every
+// sum becomes its canonical residue, the R residues of an output share one register
+// (a byte each), and `release()` runs as soon as the last column is read - the next
+// tile's MMAs start then.  The second phase reconstructs, scales and stores from those
+// registers while the tensor pipe is busy again.  Without SPLIT, release() runs last.
+template <int R, int TOK, bool COPIES, bool SPLIT, typename Release>
 __device__ __forceinline__ void pair_epilogue(const PairParams& p, int n0, int tok0, int quarter, int part, int lane,
-                                              uint32_t lane_base, bool is_float, float rs_all, float& biggest) {
+                                              uint32_t lane_base, bool is_float, float rs_all, float& biggest,
+                                              Release&& release) {
+    static_assert(!SPLIT || R <= 4, "one register holds the residues of at most four channels");
     const int feat = n0 + quarter * 32 + lane;
     const bool feat_ok = feat < p.n;
     float cs = 0.0f, bs = 0.0f;
@@ -221,7 +230,8 @@ __device__ __forceinline__ void pair_epilogue(const PairParams& p, int n0, int t
 #pragma unroll
         for (int c = 0; c < R; ++c) tmem_ld8(lane_base + (uint32_t)(c * TOK + col), acc[c]);
     };
-    auto finish = [&](int col, const int (&acc)[R][8]) {
+    auto finish = [&](int col, const int (&acc)[R][8], auto from_residues) {
+        [[maybe_unused]] constexpr bool RES = decltype(from_residues)::value;
         const int tok_first = tok0 + col;
         if (tok_first >= p.m) return;                  // warp-uniform
         XInt xv[8];
@@ -230,7 +240,7 @@ __device__ __forceinline__ void pair_epilogue(const PairParams& p, int n0, int t
             int one0[R], one1[R];
 #pragma unroll
             for (int c = 0; c < R; ++c) { one0[c] = acc[c][t8]; one1[c] = acc[c][t8 + 1]; }
-            if constexpr (R <= 4) reconstruct32_x2<R>(one0, one1, p.plan, xv[t8], xv[t8 + 1]);
+            if constexpr (R <= 4) reconstruct32_x2<R, RES>(one0, one1, p.plan, xv[t8], xv[t8 + 1]);
             else reconstruct64_x2<R>(one0, one1, p.plan, xv[t8], xv[t8 + 1]);
         }
         const int valid_t = min(8, p.m - tok_first);   // warp-uniform
@@ -316,7 +326,37 @@ __device__ __forceinline__ void pair_epilogue(const PairParams& p, int n0, int t
     };
     const int col0 = part * kColsPerPart;
     constexpr int kIters = kColsPerPart / 8;
-    if constexpr (R <= 4) {
+    const std::false_type sums;
+    if constexpr (SPLIT) {
+        // Phase 1.  One buffer: the other warps of the scheduler cover the load latency.
+        uint32_t packed[kIters][8];
+#pragma unroll
+        for (int it = 0; it < kIters; ++it) {
+            int acc[R][8];
+            load(col0 + it * 8, acc);
+            tmem_ld_wait();
+#pragma unroll
+            for (int t8 = 0; t8 < 8; ++t8) {
+                uint32_t word = 0;
+#pragma unroll
+                for (int c = 0; c < R; ++c)
+                    word |= canonical_residue(acc[c][t8], p.plan.mod[c], p.plan.recip[c], p.plan.ubias[c]) << (8 * c);
+                packed[it][t8] = word;
+            }
+        }
+        release();
+        // Phase 2.
+        const std::true_type residues;
+#pragma unroll
+        for (int it = 0; it < kIters; ++it) {
+            int acc[R][8];
+#pragma unroll
+            for (int t8 = 0; t8 < 8; ++t8)
+#pragma unroll
+                for (int c = 0; c < R; ++c) acc[c][t8] = (int)((packed[it][t8] >> (8 * c)) & 0xffu);
+            finish(col0 + it * 8, acc, residues);
+        }
+    } else if constexpr (R <= 4) {
         // The loads of the next 8 token columns are in flight while these are finished.
         int a0[R][8], a1[R][8];
         load(col0, a0);
@@ -324,13 +364,14 @@ __device__ __forceinline__ void pair_epilogue(const PairParams& p, int n0, int t
         for (int it = 0; it < kIters; it += 2) {
             tmem_ld_wait();
             if (it + 1 < kIters) load(col0 + (it + 1) * 8, a1);
-            finish(col0 + it * 8, a0);
+            finish(col0 + it * 8, a0, sums);
             if (it + 1 < kIters) {
                 tmem_ld_wait();
                 if (it + 2 < kIters) load(col0 + (it + 2) * 8, a0);
-                finish(col0 + (it + 1) * 8, a1);
+                finish(col0 + (it + 1) * 8, a1, sums);
             }
         }
+        release();
     } else {
         // one buffer: two of them (2 x R x 8 registers) would spill
 #pragma unroll 1
@@ -338,8 +379,9 @@ __device__ __forceinline__ void pair_epilogue(const PairParams& p, int n0, int t
             int acc[R][8];
             load(col0 + it * 8, acc);
             tmem_ld_wait();
-            finish(col0 + it * 8, acc);
+            finish(col0 + it * 8, acc, sums);
         }
+        release();
     }
 }
 
