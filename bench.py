@@ -59,7 +59,7 @@ def channel_ops_per_step(tokens: int, layers: int) -> float:
 # Mean DRAM traffic of one rns_gemm_kernel launch of this workload on one GPU
 # (dram__bytes_read.sum + dram__bytes_write.sum over the four linears of a layer:
 # 286 + 99 + 362 + 1153 MB), from an ncu capture of `bench.py --layers 2`.
-NCU_DRAM_BYTES_PER_LAUNCH = 475.1e6
+NCU_DRAM_BYTES_PER_LAUNCH = 476.3e6
 
 
 def algorithmic_bytes_per_launch(tokens: int) -> float:
@@ -1026,7 +1026,7 @@ def _run_layer_stack(args, backend, rank, world, local_rank, device) -> None:
             "useful_tops": useful_ops_per_step(args.tokens, args.layers) / (ms_per_step * 1e-3) / 1e12,
             "tokens_per_s": args.tokens / (ms_per_step * 1e-3),
             "roofline": {
-                "bound": "tensor", "kernel": "rns_gemm_pair_kernel", "achieved": achieved, "peak": int8_peak,
+                "bound": "tensor", "kernel": "rns_gemm_pair_raw_kernel", "achieved": achieved, "peak": int8_peak,
                 "unit": "TOPS", "frac": None if achieved is None else achieved / int8_peak,
                 "peak_source": ("torch._int_mm 8192^3 back to back on this GPU in this run (sustained, under the "
                                 "power cap)" if int8_measured else
