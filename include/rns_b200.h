@@ -274,10 +274,10 @@ typedef struct rns_linear_args {
     int32_t exact_residues;   /* 1: in-kernel residues exactly centred (|r| <= m/2; needs every
                                  modulus >= 86); 0: one-step reduced residues (any moduli) */
     int32_t a_tile_rows;      /* packed planes only: token rows per packed tile. 0 or 128: the layout
-                                 above.  64 (up to four channels) or 48 (five): tiles of that many
+                                 above.  64 (up to four channels), 48 (five) or 32 (six): tiles of that many
                                  rows, [M_pad/rows][K_pad/64][channels][rows][64], written by
                                  rns_quantize_activations_tiled; selects the two-CTA feature-major
-                                 kernels (variants 3 and 4), which need 4 or 5 channels and K >= 512 */
+                                 kernels (variants 3 and 4), which need 4 to 6 channels (variant 3: 4 or 5) and K >= 512 */
     uint32_t* d_absmax_out;   /* NULL, or device word that receives the bit pattern of
                                  max |y| over the floating outputs as stored (variants 3 and 4 only;
                                  two words: the launch clears both and uses [1] as a counter): the per-tensor absmax the NEXT
@@ -297,6 +297,13 @@ typedef struct rns_linear_args {
                                  wait expires the first CTA to give up writes {wait code =
                                  role << 20 | pipeline stage, blockIdx.x, blockIdx.y, kernel form}
                                  here, so that the host can say where the kernel stopped */
+    int64_t w_channel_stride; /* 0: d_w is ONE quantised int8 matrix, the source of every channel's weight
+                                 operand.  Else (variant 0 / 4, tiled planes, 4..6 channels): d_w holds
+                                 `channels` packed int8 matrices this many bytes apart (a multiple of 16;
+                                 at least rns_packed_weight_bytes(n, k)), matrix c = the centred residues
+                                 mod moduli[c] of a weight whose source integers are wider than int8
+                                 (quant_bits 12 / 16 of layers/rns_linear.py:45-46, 96-98 of the reference;
+                                 its backend caches the same planes, 4 bytes per value) */
 } rns_linear_args;
 
 RNS_API int rns_linear_fused(const rns_linear_args* args, rns_stream_t stream);
@@ -307,8 +314,9 @@ RNS_API int64_t rns_packed_activation_bytes(int m, int k, int channels /* 1 = so
 /* ... and of packed planes in tiles of tile_rows token rows (rns_linear_args.a_tile_rows);
  * M is padded to a multiple of 2 * tile_rows, the token tile of the two-CTA kernel. */
 RNS_API int64_t rns_packed_planes_bytes(int m, int k, int channels, int tile_rows);
-/* Token rows per packed tile that the two-CTA kernel wants for this channel count, or 0
- * when it does not cover it (then use the 128-row layout and variants 0..2). */
+/* Token rows per packed tile that the two-CTA kernel wants for this channel count (64 up to
+ * four channels, 48 for five, 32 for six), or 0 when it does
+ * not cover it (then use the 128-row layout and variants 0..2). */
 RNS_API int rns_pair_tile_rows(int channels, int k);
 
 /*

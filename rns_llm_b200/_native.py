@@ -68,6 +68,7 @@ class LinearArgs(C.Structure):
         ("d_out_copies", C.c_void_p * MAX_PEERS),
         ("d_absmax_copies", C.c_void_p * MAX_PEERS),
         ("d_wait_info", C.c_void_p),
+        ("w_channel_stride", C.c_int64),
     ]
 
 

@@ -45,6 +45,7 @@ CenteredKernelName = Literal["auto", "scalar", "dp4a", "dp4a_safe", "cublas", "t
 # Activations with at least this many rows are encoded to planes once by a
 # separate kernel; below it every CTA encodes its own A tile inside the GEMM.
 PLANES_MIN_ROWS = 512
+WIDE_MIN_ROWS = 128          # wide sources: fewer rows stay on the plane-level pipeline
 
 _INT_TYPES = {torch.int8: N.INT8, torch.int16: N.INT16, torch.int32: N.INT32}
 _FLOAT_TYPES = {torch.float16: N.F16, torch.bfloat16: N.BF16, torch.float32: N.F32}
@@ -77,12 +78,17 @@ class PreparedRNSWeight:
     and ``residues`` rebuild the plain [N,K] matrix / the [R,K,N] planes on
     access for callers that read those attributes.  Sources wider than int8, or
     moduli the packed encoder cannot fold in one step, use the plane-level
-    kernels and keep real planes as the reference does.
+    kernels and keep real planes as the reference does; where the two-CTA
+    tensor-core kernel covers the shape (4..6 channels, K >= 512, K % 16 == 0)
+    ``weight_planes_packed`` also holds those planes in the packed tile layout,
+    one [N,K] matrix per channel ``weight_plane_stride`` bytes apart, for
+    ``CudaRNSBackend.linear_forward_wide``.
     """
 
     def __init__(self, *, backend: "CudaRNSBackend", moduli: tuple[int, ...], k: int, n: int,
                  kernel: str, weight_packed: torch.Tensor | None = None,
-                 residues: torch.Tensor | None = None) -> None:
+                 residues: torch.Tensor | None = None,
+                 weight_planes_packed: torch.Tensor | None = None, weight_plane_stride: int = 0) -> None:
         self._backend = backend
         self.moduli = moduli
         self.k = int(k)
@@ -90,6 +96,8 @@ class PreparedRNSWeight:
         self.kernel = kernel
         self.weight_packed = weight_packed
         self._residues = residues
+        self.weight_planes_packed = weight_planes_packed
+        self.weight_plane_stride = int(weight_plane_stride)
 
     @property
     def weight_nk(self) -> torch.Tensor | None:
@@ -115,6 +123,7 @@ class PreparedRNSWeight:
             backend=self._backend, moduli=self.moduli[:channels], k=self.k, n=self.n, kernel=kernel,
             weight_packed=self.weight_packed,
             residues=None if self._residues is None else self._residues[:channels],
+            weight_planes_packed=self.weight_planes_packed, weight_plane_stride=self.weight_plane_stride,
         )
 
 
@@ -512,7 +521,19 @@ class CudaRNSBackend:
             return self.prepare_weight_nk(b.t(), mods)
         residues = self.encode_centered(b.contiguous(), mods)
         kernel = self.select_centered_kernel(k=k, n=n, moduli=mods, requested="auto", device=b.device)
-        return PreparedRNSWeight(backend=self, moduli=mods, k=k, n=n, kernel=kernel, residues=residues)
+        planes_packed, stride = None, 0
+        if (b.dtype != torch.int8 and int(self._lib.rns_pair_tile_rows(len(mods), k)) > 0
+                and self.tensor_core_compatible(k=k, moduli=mods)):
+            # Wide sources on the tensor cores: the same centred planes once more, each as a
+            # packed [N,K] matrix (R bytes per value; the reference caches 4 R bytes per value).
+            nbytes = int(self._lib.rns_packed_weight_bytes(n, k))
+            stride = (nbytes + 255) & ~255
+            planes_packed = torch.zeros(len(mods) * stride, dtype=torch.int8, device=b.device)
+            for channel in range(len(mods)):
+                planes_packed[channel * stride: channel * stride + nbytes].copy_(
+                    self._pack_weight(residues[channel].t()))
+        return PreparedRNSWeight(backend=self, moduli=mods, k=k, n=n, kernel=kernel, residues=residues,
+                                 weight_planes_packed=planes_packed, weight_plane_stride=stride)
 
     def _pack_weight(self, w: torch.Tensor) -> torch.Tensor:
         n, k = int(w.shape[0]), int(w.shape[1])
@@ -578,7 +599,8 @@ class CudaRNSBackend:
                       enc_stages: int = 0, sub_blocks: int = 0, variant: int = 0,
                       stream: int | None = None, a_tile_rows: int = 0,
                       absmax_out: torch.Tensor | int | None = None,
-                      out_copies: Sequence[int] = (), absmax_copies: Sequence[int] = ()) -> None:
+                      out_copies: Sequence[int] = (), absmax_copies: Sequence[int] = (),
+                      weight_planes: bool = False) -> None:
         """Fills ``rns_linear_args`` and launches.  ``a`` / ``a_planes`` are plain
         ([M,K] / [R,M,K]) unless ``a_packed``; the weight is the prepared packed
         copy unless ``plain_weight`` ([N,K] int8) is given.  Device buffers may be
@@ -599,7 +621,13 @@ class CudaRNSBackend:
             args.d_a = ptr(a)
             args.lda = prepared.k if a_packed else a.stride(0)
         args.a_packed = 1 if a_packed else 0
-        if plain_weight is not None:
+        if weight_planes:
+            args.d_w = prepared.weight_planes_packed.data_ptr()
+            args.ldw = prepared.k
+            args.w_packed = 1
+            args.w_channel_stride = prepared.weight_plane_stride
+            device = prepared.weight_planes_packed.device
+        elif plain_weight is not None:
             args.d_w = plain_weight.data_ptr()
             args.ldw = plain_weight.stride(0)
             device = plain_weight.device
@@ -861,7 +889,7 @@ class CudaRNSBackend:
         max |y| of this call's outputs, written by the GEMM epilogue; ``absmax_in`` =
         (address, parts, stride in words) hands the next call the words whose maximum
         is its input's absmax (one word, or one per rank of a column-sharded layer).
-        ``absmax_out`` needs the many-token kernel (M >= 512, 4 or 5 channels,
+        ``absmax_out`` needs the many-token kernel (M >= 512, 4 to 6 channels,
         K >= 512); otherwise it raises.  ``out_copies`` (device addresses, e.g. the
         same output slot in other ranks' memory) receive the same stores as ``out``
         from that kernel's epilogue, ``absmax_copies`` the finished absmax word."""
@@ -957,6 +985,57 @@ class CudaRNSBackend:
                                out_copies=out_copies, absmax_copies=absmax_copies)
         if return_metadata:
             return out, (AdaptiveMetadata(meta) if meta is not None else None)
+        return out
+
+    def supports_wide_forward(self, prepared: PreparedRNSWeight, m: int) -> bool:
+        """True when ``linear_forward_wide`` serves this call: the prepared weight carries
+        packed residue planes and there are enough rows to fill tensor-core tiles."""
+        return prepared.weight_planes_packed is not None and int(m) >= WIDE_MIN_ROWS
+
+    def linear_forward_wide(self, x: torch.Tensor, prepared: PreparedRNSWeight, weight_scale: torch.Tensor,
+                            bias: torch.Tensor | None, *, quant_max: int, per_row: bool = False,
+                            out: torch.Tensor | None = None) -> torch.Tensor:
+        """``RNSLinear.forward`` for sources wider than 8 bits (quant_bits 12 / 16,
+        layers/rns_linear.py:45-46, 96-98, 237-275 of the reference) on the tensor cores:
+        the quantiser writes the centred residues of the 12/16-bit integers as tiled planes
+        (the integers themselves are never stored), the two-CTA kernel multiplies them
+        with the cached residue planes of the weight, one int8 MMA per channel, and its
+        epilogue reconstructs the (up to 48-bit) integer, converts it to fp32 as
+        ``integer_result.float()`` does and applies ``* s_a * s_w + bias``."""
+        if prepared.weight_planes_packed is None:
+            raise ValueError("linear_forward_wide needs a prepared weight with packed residue planes")
+        if x.dtype not in _FLOAT_TYPES or x.ndim != 2 or x.stride(1) != 1:
+            raise ValueError("x must be [M,K] float16, bfloat16 or float32 with unit inner stride")
+        if not 127 < int(quant_max) <= 32767:
+            raise ValueError("quant_max of a wide source lies in (127, 32767]")
+        m, k = int(x.shape[0]), int(x.shape[1])
+        if k != prepared.k:
+            raise ValueError("K dimension does not match prepared weight")
+        device = x.device
+        mods, arr = self._mods(prepared.moduli)
+        channels = len(mods)
+        tile_rows = int(self._lib.rns_pair_tile_rows(channels, k))
+        if tile_rows == 0:
+            raise ValueError("the two-CTA kernel does not cover this channel count / K")
+        if out is None:
+            out = torch.empty((m, prepared.n), dtype=x.dtype, device=device)
+        elif out.shape != (m, prepared.n) or out.stride(1) != 1 or out.dtype != x.dtype:
+            raise ValueError("out must be [M,N] of x's dtype with unit inner stride")
+        with torch.cuda.device(device):
+            scale_bytes = ((m if per_row else 1) * 4 + 255) & ~255
+            act_bytes = int(self._lib.rns_packed_planes_bytes(m, k, channels, tile_rows))
+            base, stream = self.arena.block(device, scale_bytes + 256 + act_bytes)
+            scale, scratch, act = base, base + scale_bytes, base + scale_bytes + 256
+            N.check(self._lib.rns_quantize_activations_tiled(
+                x.data_ptr(), _FLOAT_TYPES[x.dtype], m, k, int(x.stride(0)), 0, 0, 1 if per_row else 0,
+                int(quant_max), arr, channels, None, act, 1, tile_rows, scale, None, scratch, None, 0, 0, stream))
+            self._stats["encode_centered_calls"] += 1
+            self._stats["encode_centered_values"] += m * k
+            self._stats["fused_gemm_calls"] += 1
+            self._stats[f"fused_gemm_channels_{channels}"] += 1
+            self._launch_fused(prepared=prepared, m=m, a=None, a_planes=act, a_packed=True, out=out,
+                               row_scale=scale, row_scale_stride=1 if per_row else 0, col_scale=weight_scale,
+                               bias=bias, stream=stream, a_tile_rows=tile_rows, weight_planes=True)
         return out
 
     def supports_absmax_out(self, *, m: int, k: int, channels: int) -> bool:

@@ -243,11 +243,12 @@ __device__ __forceinline__ int quantize_one(float v, float scale, int qmax) {
 // even in the adder): the sum's low mantissa bits are the integer, so neither a
 // rounding nor a conversion instruction is issued.  |t| >= 127.5, infinities and NaN
 // fail the same test (the clamped integer is far away, or the difference is NaN).
+// Wider targets (qmax up to 32767): 2 ulp of t reach 0.002, so the margin widens to 0.01.
 __device__ __forceinline__ int quantize_one_fast(float v, float inv_scale, int qmax, bool& doubtful) {
     const float t = __fmul_rn(v, inv_scale);
     const float magic = 12582912.0f;
     const float r = __fadd_rn(fminf(fmaxf(t, (float)-qmax), (float)qmax), magic);
-    doubtful |= !(fabsf(t - __fsub_rn(r, magic)) <= 0.4999f);
+    doubtful |= !(fabsf(t - __fsub_rn(r, magic)) <= (qmax <= 127 ? 0.4999f : 0.49f));
     return __float_as_int(r) - 0x4B400000;
 }
 
@@ -856,8 +857,12 @@ static int quantize_impl(const void* d_x, rns_float_type type, int m, int k, int
     if (col_block <= 0) { col_block = k; col_block_stride = 0; }
     if (m <= 0 || k <= 0 || ldx < col_block || k % col_block != 0)
         return fail(RNS_ERR_INVALID_ARGUMENT, "quantize: bad shape, stride or column block");
-    if (quant_max != 127)
-        return fail(RNS_ERR_UNSUPPORTED, "the fused quantiser produces 8-bit values (quant_max 127)");
+    // 127: int8 values (d_q) and / or their residue planes.  128..32767 (quant_bits 12 / 16 of the
+    // reference's RNSLinear): residue planes only - the values themselves do not fit d_q.
+    const bool wide = quant_max > 127;
+    if (quant_max < 127 || quant_max > 32767 || (wide && (d_q != nullptr || d_planes == nullptr || d_row_l1_max != nullptr)))
+        return fail(RNS_ERR_UNSUPPORTED, "the fused quantiser produces 8-bit values (quant_max 127), or residue planes "
+                                         "only for quant_max up to 32767");
     if (tile_rows == 0) tile_rows = kPackM;
     if (tile_rows != kPackM && (!packed_out || d_q != nullptr || tile_rows < 8 || tile_rows > 128 || tile_rows % 8 != 0))
         return fail(RNS_ERR_INVALID_ARGUMENT, "quantize: tile_rows applies to packed planes only (multiple of 8, <= 128)");
@@ -880,6 +885,7 @@ static int quantize_impl(const void* d_x, rns_float_type type, int m, int k, int
 #ifndef RNS_QUANT_CENTRED
     qo.reduced = (d_planes && packed_out) ? 1 : 0;   // the packed planes only feed the tensor cores
 #endif
+    if (wide) { qo.reduced = 0; qo.single_fold = 0; qo.fast = 0; }   // true centred residues of 16-bit integers
     size_t esize = 2;
     if (type == RNS_F32) esize = 4;
     else if (type != RNS_F16 && type != RNS_BF16)

@@ -31,18 +31,21 @@ namespace rns {
 #ifndef RNS_PAIR_SPLIT_EPILOGUE
 #define RNS_PAIR_SPLIT_EPILOGUE 1   // 0: single-phase epilogue, for comparison builds
 #endif
-constexpr int kRawStages = 8;      // ring depth (even: an issuer warp keeps its slots; <= kDoneRing)
-
-template <int R, int TOK, bool COPIES>
+// WCH: the weight operand is given per channel (R packed matrices, p.w_channel_stride
+// bytes apart): sources wider than int8, whose residues do not fit the trick above, with
+// the residue planes of the weight cached at prepare time.  S: ring depth (<= kDoneRing).
+// ISSUERS: 2 = warps 0 and 1 take alternate stages (needs an even S, so that a slot keeps
+// its warp and the warp sees every phase of the slot's barrier); 1 = warp 0 issues all.
+template <int R, int TOK, int S, int ISSUERS, bool WCH, bool COPIES>
 __global__ void __launch_bounds__(kPairThreads, 1)
 rns_gemm_pair_raw_kernel(const __grid_constant__ PairParams p) {
     static_assert(R * TOK <= 512, "accumulators must fit tensor memory");
-    static_assert(TOK % 16 == 0 && (TOK / 2) % 8 == 0, "token tile shape");
-    static_assert(kRawStages <= kDoneRing && kRawStages % 2 == 0, "ring depth");
-    constexpr int S = kRawStages;
+    static_assert(TOK % 32 == 0 && (TOK / 2) % 8 == 0, "token tile shape");
+    static_assert(S <= kDoneRing && (ISSUERS == 1 || (ISSUERS == 2 && S % 2 == 0)), "ring depth");
     constexpr int TR = TOK / 2;                               // token rows this CTA loads
     constexpr uint32_t kPlTile = (uint32_t)TR * kPackK;
     constexpr uint32_t kPlStage = (uint32_t)R * kPlTile;
+    constexpr uint32_t kWStage = (WCH ? (uint32_t)R : 1u) * kPairOpTile;
     constexpr uint32_t kTmemCols = 512;
 
     extern __shared__ uint8_t smem_dyn[];
@@ -52,7 +55,7 @@ rns_gemm_pair_raw_kernel(const __grid_constant__ PairParams p) {
     const int lane = threadIdx.x & 31;
     const uint32_t tiles_base = (smem_addr(smem_dyn) + 1023u) & ~1023u;
     const uint32_t w_base = tiles_base;                        // weight ring first
-    const uint32_t pl_base = tiles_base + (uint32_t)S * kPairOpTile;
+    const uint32_t pl_base = tiles_base + (uint32_t)S * kWStage;
 
     const uint32_t rank = cluster_cta_rank();
     const int cluster = (int)(blockIdx.x >> 1), clusters = (int)(gridDim.x >> 1);
@@ -69,7 +72,7 @@ rns_gemm_pair_raw_kernel(const __grid_constant__ PairParams p) {
             mbar_init(smem_addr(&ctl.full_pl[s]), rank == 0 ? 2 : 1);
             mbar_init(smem_addr(&ctl.done[s]), 1);
         }
-        mbar_init(smem_addr(&ctl.acc_full), 2);                // one commit from each issuer warp
+        mbar_init(smem_addr(&ctl.acc_full), ISSUERS);          // one commit from each issuer warp
         mbar_init(smem_addr(&ctl.tmem_free), 2 * kPairEncWarps);   // leader: both CTAs' epilogue warps
         mbar_init(smem_addr(&ctl.first_issued), 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -97,7 +100,7 @@ rns_gemm_pair_raw_kernel(const __grid_constant__ PairParams p) {
                 const bool w_rows = t.n0 < p.w_npad;
                 const int8_t* w_src = p.w + (int64_t)t.n0 * kPackK;
                 const int64_t kb_stride = p.w_npad * kPackK;
-                const uint32_t bytes = kPlStage + (w_rows ? kPairOpTile : 0u);
+                const uint32_t bytes = kPlStage + (w_rows ? kWStage : 0u);
                 for (int st = 0; st < nst; ++st, ++g) {
                     if (g >= S &&
                         !wait_bounded<false, true>(smem_addr(&ctl.done[(g - S) & (kDoneRing - 1)]),
@@ -108,7 +111,12 @@ rns_gemm_pair_raw_kernel(const __grid_constant__ PairParams p) {
                     const int s = g % S;
                     const uint32_t bar = smem_addr(&ctl.full_pl[s]);
                     mbar_arrive_expect_tx(bar, bytes);
-                    if (w_rows) bulk_load(w_base + (uint32_t)s * kPairOpTile, w_src + (int64_t)st * kb_stride, kPairOpTile, bar);
+                    if (w_rows) {
+#pragma unroll
+                        for (int c = 0; c < (WCH ? R : 1); ++c)
+                            bulk_load(w_base + (uint32_t)s * kWStage + (uint32_t)c * kPairOpTile,
+                                      w_src + (int64_t)c * p.w_channel_stride + (int64_t)st * kb_stride, kPairOpTile, bar);
+                    }
                     bulk_load(pl_base + (uint32_t)s * kPlStage, pl_src + (int64_t)st * kPlStage, kPlStage, bar);
                 }
             }
@@ -116,7 +124,9 @@ rns_gemm_pair_raw_kernel(const __grid_constant__ PairParams p) {
         __syncwarp();
     } else if (warp <= 1) {
         const int total = my_tiles * nst;                      // stages this cluster runs
-        if (rank != 0) {
+        if (rank == 0 && warp >= ISSUERS) {
+            // the second warp has nothing to issue in the one-issuer form
+        } else if (rank != 0) {
             // ------------------------------ relay (peer CTA) -----------------------
             // Tells the leader that this CTA's half of a stage has landed.  Loads run
             // several stages ahead of the MMAs, so this hop is off the critical path.
@@ -140,19 +150,19 @@ rns_gemm_pair_raw_kernel(const __grid_constant__ PairParams p) {
             bool ok = true;
             int g0 = 0;                                        // first stage of the current tile
             for (int ti = 0; ti < my_tiles && ok; ++ti, g0 += nst) {
-                const bool owner = ((g0 & 1) == warp);         // issues the tile's first stage
+                const bool owner = ISSUERS == 1 || ((g0 & 1) == warp);   // issues the tile's first stage
                 // accumulators drained (by both CTAs) since the previous tile
                 ok = warp_wait_bounded<false, true>(smem_addr(&ctl.tmem_free), (uint32_t)ti & 1u, abort, wait_code(9, ti));
                 if (ok && !owner)
                     ok = warp_wait_bounded<false, true>(smem_addr(&ctl.first_issued), (uint32_t)ti & 1u, abort, wait_code(7, ti));
                 if (!ok) break;
                 tc_fence_after();
-                for (int g = g0 + ((g0 + warp) & 1); g < g0 + nst; g += 2) {
+                for (int g = g0 + (ISSUERS == 2 ? ((g0 + warp) & 1) : 0); g < g0 + nst; g += ISSUERS) {
                     const int s = g % S;
                     ok = warp_wait_bounded<false, true>(smem_addr(&ctl.full_pl[s]), (uint32_t)(g / S) & 1u, abort, wait_code(6, g));
                     if (!ok) break;
                     tc_fence_after();
-                    const uint32_t a_st = a_lo0 + (uint32_t)s * (kPairOpTile >> 4);
+                    const uint32_t a_st = a_lo0 + (uint32_t)s * (kWStage >> 4);
                     const uint32_t b_st = b_lo0 + (uint32_t)s * (kPlStage >> 4);
                     const bool first = g == g0;
                     if (elect_one()) {
@@ -160,13 +170,13 @@ rns_gemm_pair_raw_kernel(const __grid_constant__ PairParams p) {
                         for (int c = 0; c < R; ++c) {
 #pragma unroll
                             for (int ks = 0; ks < 2; ++ks) {
-                                const uint64_t da = desc0 | (uint64_t)(a_st + (uint32_t)ks * 2u);
+                                const uint64_t da = desc0 | (uint64_t)(a_st + (WCH ? (uint32_t)c * (kPairOpTile >> 4) : 0u) + (uint32_t)ks * 2u);
                                 const uint64_t db = desc0 | (uint64_t)(b_st + (uint32_t)c * (kPlTile >> 4) + (uint32_t)ks * 2u);
                                 umma_i8_pair(tmem_base + (uint32_t)(c * TOK), da, db, idesc, (first && ks == 0) ? 0u : 1u);
                             }
                         }
                         umma_commit_pair(smem_addr(&ctl.done[g & (kDoneRing - 1)]));
-                        if (first) {
+                        if (first && ISSUERS == 2) {
                             tc_fence_before();
                             mbar_arrive(smem_addr(&ctl.first_issued));
                         }
@@ -199,10 +209,23 @@ rns_gemm_pair_raw_kernel(const __grid_constant__ PairParams p) {
         int ti = 0;
         for (int tile = cluster; tile < tiles; tile += clusters, ++ti) {
             const PairTile t = pair_tile<TOK>(p, tile, rank);
-            if (!warp_wait_bounded(smem_addr(&ctl.acc_full), (uint32_t)ti & 1u, abort, wait_code(11, ti))) break;
+            bool ok = warp_wait_bounded(smem_addr(&ctl.acc_full), (uint32_t)ti & 1u, abort, wait_code(11, ti));
+            if constexpr (COPIES) {
+                // The four warps of a token-column block meet at a barrier inside the epilogue
+                // (row-wide stores): they enter it together or not at all, even when a wait
+                // expires for one of them while the phase completes for another.
+                int all;
+                asm volatile("{\n\t.reg .pred pin, pout;\n\tsetp.ne.b32 pin, %1, 0;\n\t"
+                             "bar.red.and.pred pout, %2, 128, pin;\n\tselp.b32 %0, 1, 0, pout;\n\t}"
+                             : "=r"(all) : "r"(ok ? 1 : 0), "r"(2 + part) : "memory");
+                ok = all != 0;
+            }
+            if (!ok) break;
             tc_fence_after();
-            pair_epilogue<R, TOK, COPIES, (R <= 4 && RNS_PAIR_SPLIT_EPILOGUE != 0)>(p, t.n0, t.tok0, quarter, part, lane, lane_base, is_float, rs_all,
-                                                    biggest, release);
+            pair_epilogue<R, TOK, COPIES, (R <= 4 && RNS_PAIR_SPLIT_EPILOGUE != 0)>(
+                p, t.n0, t.tok0, quarter, part, lane, lane_base, is_float, rs_all, biggest, release,
+                COPIES ? reinterpret_cast<unsigned short*>(smem_dyn + (tiles_base - smem_addr(smem_dyn)) +
+                                                           (size_t)S * (kWStage + kPlStage)) : nullptr);
         }
         if (p.absmax_out != nullptr && is_float) {
 #pragma unroll
@@ -231,7 +254,7 @@ rns_gemm_pair_raw_kernel(const __grid_constant__ PairParams p) {
             if (p.wait_info != nullptr && atomicCAS(p.wait_info, 0, ctl.abort) == 0) {
                 p.wait_info[1] = (int)blockIdx.x;
                 p.wait_info[2] = (int)blockIdx.y;
-                p.wait_info[3] = R * 1000000 + 300000 + TOK;
+                p.wait_info[3] = R * 1000000 + (WCH ? 400000 : 300000) + TOK;
             }
         } else if (p.absmax_out != nullptr) {
             if (ctl.absmax != 0u) atomicMax(p.absmax_out, ctl.absmax);
@@ -254,21 +277,36 @@ rns_gemm_pair_raw_kernel(const __grid_constant__ PairParams p) {
 // ---------------------------------------------------------------------------
 // Host side
 // ---------------------------------------------------------------------------
-template <int R, int TOK, bool COPIES>
+template <int R, int TOK, int S, int ISSUERS, bool WCH, bool COPIES>
 static int launch_pair_raw(const PairParams& pp, int pairs, cudaStream_t st) {
-    constexpr size_t smem = (size_t)kRawStages * (kPairOpTile + (size_t)R * (TOK / 2) * kPackK) + 1024;
+    // COPIES: 16 KB behind the rings stage the row-wide stores (4 blocks x 2 buffers x 8 x 128 x 2 bytes)
+    constexpr size_t smem = (size_t)S * ((WCH ? R : 1) * kPairOpTile + (size_t)R * (TOK / 2) * kPackK) + 1024 +
+                            (COPIES ? kPairStageBytes : 0);
     static_assert(smem + sizeof(PairCtl) <= 227 * 1024, "ring exceeds shared memory");
-    return launch_pair_clusters<rns_gemm_pair_raw_kernel<R, TOK, COPIES>>(smem, pp, pairs, st);
+    return launch_pair_clusters<rns_gemm_pair_raw_kernel<R, TOK, S, ISSUERS, WCH, COPIES>>(smem, pp, pairs, st);
 }
+
+int pair_raw_token_tile(int channels) { return channels <= 4 ? 128 : (channels == 5 ? 96 : 64); }
 
 int launch_pair_raw_gemm(const PairParams& pp, int pairs, cudaStream_t st) {
     const int R = pp.plan.channels;
-    if (pp.n_copies > 0) {
-        if (R == 4) return launch_pair_raw<4, 128, true>(pp, pairs, st);
-        return launch_pair_raw<5, 96, true>(pp, pairs, st);
+    if (pp.w_channel_stride != 0) {
+        // residue planes of a wide weight: deeper stages, shallower rings; no output copies
+        if (pp.n_copies > 0) return fail(RNS_ERR_UNSUPPORTED, "output copies are not built for per-channel weights");
+        if (R == 4) return launch_pair_raw<4, 128, 4, 2, true, false>(pp, pairs, st);
+        if (R == 5) return launch_pair_raw<5, 96, 4, 2, true, false>(pp, pairs, st);
+        if (R == 6) return launch_pair_raw<6, 64, 3, 1, true, false>(pp, pairs, st);
+        return fail(RNS_ERR_UNSUPPORTED, "per-channel weights: 4, 5 or 6 channels");
     }
-    if (R == 4) return launch_pair_raw<4, 128, false>(pp, pairs, st);
-    return launch_pair_raw<5, 96, false>(pp, pairs, st);
+    if (pp.n_copies > 0) {
+        if (R == 4) return launch_pair_raw<4, 128, 8, 2, false, true>(pp, pairs, st);
+        if (R == 5) return launch_pair_raw<5, 96, 8, 2, false, true>(pp, pairs, st);
+        return fail(RNS_ERR_UNSUPPORTED, "output copies: 4 or 5 channels");
+    }
+    if (R == 4) return launch_pair_raw<4, 128, 8, 2, false, false>(pp, pairs, st);
+    if (R == 5) return launch_pair_raw<5, 96, 8, 2, false, false>(pp, pairs, st);
+    if (R == 6) return launch_pair_raw<6, 64, 8, 2, false, false>(pp, pairs, st);
+    return fail(RNS_ERR_UNSUPPORTED, "the two-CTA kernel covers 4, 5 or 6 channels");
 }
 
 }  // namespace rns

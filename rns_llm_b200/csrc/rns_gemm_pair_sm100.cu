@@ -326,11 +326,15 @@ static int launch_pair(const PairParams& pp, int pairs, cudaStream_t st) {
     return launch_pair_clusters<rns_gemm_pair_kernel<R, TOK, ES, PS, COPIES>>(smem, pp, pairs, st);
 }
 
-int pair_gemm_token_tile(int channels) { return channels <= 4 ? 128 : 96; }
+int pair_gemm_token_tile(int channels) { return pair_raw_token_tile(channels); }
 
+// 4, 5 or 6 channels (the weight-encoding kernel, variant 3, and output copies: 4 or 5).
 bool pair_gemm_supported(const rns_linear_args* a) {
+    const bool channels_ok = a->channels == 4 || a->channels == 5 ||
+                             (a->channels == 6 && a->variant != 3 && a->n_out_copies == 0);
     return a->d_a_planes != nullptr && a->a_packed != 0 && a->w_packed != 0 && a->d_active_channels == nullptr &&
-           a->exact_residues == 0 && (a->channels == 4 || a->channels == 5) &&
+           a->exact_residues == 0 && channels_ok && (a->w_channel_stride == 0 || a->variant != 3) &&
+           a->w_channel_stride >= 0 && a->w_channel_stride % 16 == 0 &&
            a->a_tile_rows == pair_gemm_token_tile(a->channels) / 2 && a->k >= 8 * kPackK && a->k % 16 == 0;
 }
 
@@ -345,6 +349,7 @@ int launch_pair_gemm(const rns_linear_args* a, const Plan& plan, cudaStream_t st
     pp.planes = a->d_a_planes;
     pp.w = a->d_w;
     pp.w_npad = round_up_i64(a->n, kPackNPad);
+    pp.w_channel_stride = a->w_channel_stride;
     pp.n_ftiles = (a->n + 255) / 256;
     pp.n_ttiles = (a->m + tok - 1) / tok;
     // Band: as many feature tiles as keep the band's weight bytes around 32 MB (a quarter

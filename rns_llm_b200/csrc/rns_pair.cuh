@@ -23,6 +23,7 @@ constexpr int kPairPlaneWarp = 2 + kPairEncWarps;  // the warp that loads planes
 constexpr int kPairThreads = (3 + kPairEncWarps) * 32;
 constexpr int kDoneRing = 8;                       // ring of "stage done" barriers (>= both ring depths)
 constexpr uint32_t kPairOpTile = 128 * kPackK;     // one channel's weight operand tile
+constexpr size_t kPairStageBytes = 4 * 2 * 8 * 128 * 2;   // staging of the row-wide stores (output copies)
 constexpr int kPairChunks = 128 * 4 / kPairGroupThreads;   // 16-byte chunks of a weight tile per encoder thread
 
 struct PairParams {
@@ -32,6 +33,8 @@ struct PairParams {
     const int8_t* planes;      // [M_pad / (TOK/2)][kblocks][R][TOK/2][64]
     const int8_t* w;           // packed weights [kblocks][w_npad][64]
     int64_t w_npad;
+    int64_t w_channel_stride;  // 0: one matrix (the int8 weight) for every channel; else bytes between the
+                               // packed residue planes of the weight, one per channel
     int32_t n_ftiles;          // tiles of 256 features
     int32_t n_ttiles;          // tiles of TOK tokens
     int32_t band;              // feature tiles per raster band
@@ -208,7 +211,7 @@ __device__ __forceinline__ PairTile pair_tile(const PairParams& p, int tile, uin
 template <int R, int TOK, bool COPIES, bool SPLIT, typename Release>
 __device__ __forceinline__ void pair_epilogue(const PairParams& p, int n0, int tok0, int quarter, int part, int lane,
                                               uint32_t lane_base, bool is_float, float rs_all, float& biggest,
-                                              Release&& release) {
+                                              Release&& release, unsigned short* stage = nullptr) {
     static_assert(!SPLIT || R <= 4, "one register holds the residues of at most four channels");
     const int feat = n0 + quarter * 32 + lane;
     const bool feat_ok = feat < p.n;
@@ -225,6 +228,17 @@ __device__ __forceinline__ void pair_epilogue(const PairParams& p, int n0, int t
     bool pair_store = (p.out_type == RNS_OUT_F16 || p.out_type == RNS_OUT_BF16) && (p.ldo & 1) == 0 &&
                       (reinterpret_cast<uintptr_t>(p.out) & 3) == 0 && n0 + quarter * 32 + 32 <= p.n;
     for (int g = 0; COPIES && g < p.n_copies; ++g) pair_store = pair_store && (reinterpret_cast<uintptr_t>(p.out_copies[g]) & 3) == 0;
+    // Row-wide stores (COPIES with a staging buffer): the four warps that share a block of
+    // token columns (one per lane quarter, 4 x 32 features) meet in shared memory, 8 tokens at
+    // a time, and each lane then stores 16 bytes, a warp two token rows of 256 contiguous
+    // bytes - instead of 64-byte pieces, which NVLink carries at a fraction of its rate.
+    bool wide_store = false;
+    if constexpr (COPIES) {
+        wide_store = stage != nullptr && (p.out_type == RNS_OUT_F16 || p.out_type == RNS_OUT_BF16) &&
+                     n0 + 128 <= p.n && (p.ldo & 7) == 0 && (reinterpret_cast<uintptr_t>(p.out) & 15) == 0;
+        for (int g = 0; g < p.n_copies; ++g)
+            wide_store = wide_store && (reinterpret_cast<uintptr_t>(p.out_copies[g]) & 15) == 0;
+    }
     auto load = [&](int col, int (&acc)[R][8]) {
         __syncwarp();
 #pragma unroll
@@ -296,6 +310,24 @@ __device__ __forceinline__ void pair_epilogue(const PairParams& p, int n0, int t
             }
         }
         unsigned short* out16 = static_cast<unsigned short*>(p.out);
+        if (COPIES && wide_store) {
+            // two buffers per token-column block: a buffer is rewritten two chunks later, after
+            // every one of the four warps has passed the barrier of the chunk in between
+            const int chunk = (col - part * kColsPerPart) >> 3;
+            unsigned short* sb = stage + ((part * 2 + (chunk & 1)) * 8) * 128;
+#pragma unroll
+            for (int t8 = 0; t8 < 8; ++t8) sb[t8 * 128 + quarter * 32 + lane] = h[t8];
+            asm volatile("bar.sync %0, 128;" ::"r"(2 + part) : "memory");
+            const int t = quarter * 2 + (lane >> 4);
+            const uint4 v = *reinterpret_cast<const uint4*>(sb + t * 128 + (lane & 15) * 8);
+            if (t < valid_t) {
+                const int64_t o = (int64_t)(tok_first + t) * p.ldo + n0 + (lane & 15) * 8;
+                *reinterpret_cast<uint4*>(out16 + o) = v;
+                for (int g = 0; g < p.n_copies; ++g)
+                    *reinterpret_cast<uint4*>(static_cast<unsigned short*>(p.out_copies[g]) + o) = v;
+            }
+            return;
+        }
         if (pair_store) {
             const bool odd = (lane & 1) != 0;
 #pragma unroll
@@ -430,6 +462,7 @@ static int launch_pair_clusters(size_t smem, const PairParams& pp, int pairs, cu
 }
 
 // rns_gemm_pair_raw_sm100.cu
+int pair_raw_token_tile(int channels);
 int launch_pair_raw_gemm(const PairParams& pp, int pairs, cudaStream_t st);
 
 }  // namespace rns

@@ -6,13 +6,15 @@
 // pipeline set-up) costs more in fixed latency than the arithmetic.  This kernel does
 // the whole of RNSLinear.forward for such calls (src/rns_llm/layers/rns_linear.py:
 // 237-275 of the reference): per-tensor or per-row absmax and quantisation of the
-// activations, residue encoding of both operands, one int8 dot product per residue
-// channel, mixed-radix reconstruction, dequantisation, bias, store.
+// activations, their residues per channel (the int8 weight serves every channel as the
+// representative of its residue class), one int8 dot product per residue channel,
+// mixed-radix reconstruction, dequantisation, bias, store.
 //
 // One CTA (4 warps) owns 8 output features and up to 16 tokens.  Every CTA quantises the
 // (small) activation block itself and keeps its residues in shared memory in the
-// fragment order of mma.sync.m16n8k32; the four warps split K, each encodes the weight
-// bytes it needs straight from global memory (packed layout), issues one
+// fragment order of mma.sync.m16n8k32; the four warps split K, each requests the weight
+// words of its first K steps before anything else (packed layout, straight from global
+// memory, so that they arrive during the quantisation), issues one
 // mma.sync.m16n8k32.s8 per channel and K step, and the partial sums meet in shared
 // memory, where one thread per output reconstructs and stores.  No scratch in global
 // memory, no second launch, nothing to allocate.
@@ -28,6 +30,7 @@
 namespace rns {
 
 constexpr int kSmallWarps = 4;
+constexpr int kSmallAhead = 8;         // K steps per warp whose weight words are requested before the quantisation
 constexpr int kSmallThreads = kSmallWarps * 32;
 constexpr int kSmallFeatures = 8;      // output features per CTA (the n of m16n8k32)
 constexpr int kSmallTokens = 16;       // tokens per CTA (the m of m16n8k32)
@@ -104,6 +107,33 @@ rns_linear_small_kernel(const __grid_constant__ SmallParams p) {
     const int m0 = blockIdx.y * kSmallTokens;
     const int rows = min(kSmallTokens, p.m - m0);
     constexpr bool kIntegers = std::is_same<T, int8_t>::value;
+
+    // ---------------- weight words of this lane's first K steps, requested now ----------------
+    // The kernel is a chain of latencies (activations, their absmax, the weights, the
+    // reduction); the weight bytes do not depend on the activations, so their loads go out
+    // first and land while the token block is quantised.
+    const int wg = lane >> 2, wt = lane & 3;
+    const int wrow = n0 + wg;                                     // weight row (output feature) of this lane
+    const bool wrow_ok = wrow < p.n;
+    const int wswz = (wrow >> 1) & 3;
+    auto load_weight_words = [&](int s, uint32_t& w0, uint32_t& w1) {
+        // bytes s*32 + 4t .. +3 and s*32 + 16 + 4t .. +3 of weight row wrow
+        w0 = 0u; w1 = 0u;
+        if (wrow_ok) {
+            const int kb = s >> 1, base = (s & 1) * 32;
+            const int8_t* rowp = p.w + ((int64_t)kb * p.w_npad + wrow) * kPackK;
+            const int b0 = base + 4 * wt, b1 = base + 16 + 4 * wt;
+            w0 = __ldg(reinterpret_cast<const uint32_t*>(rowp + ((((b0 >> 4) ^ wswz) << 4) | (b0 & 15))));
+            w1 = __ldg(reinterpret_cast<const uint32_t*>(rowp + ((((b1 >> 4) ^ wswz) << 4) | (b1 & 15))));
+        }
+    };
+    uint32_t ahead0[kSmallAhead], ahead1[kSmallAhead];
+#pragma unroll
+    for (int i = 0; i < kSmallAhead; ++i) {
+        const int s = warp + i * kSmallWarps;
+        ahead0[i] = 0u; ahead1[i] = 0u;
+        if (s < ksteps) load_weight_words(s, ahead0[i], ahead1[i]);
+    }
 
     // ---------------- activation scale(s) ----------------
     const int groups_per_row = (p.k + 7) / 8;                    // groups of 8 consecutive columns
@@ -195,35 +225,34 @@ rns_linear_small_kernel(const __grid_constant__ SmallParams p) {
 #pragma unroll
     for (int c = 0; c < R; ++c) { acc[c][0] = acc[c][1] = acc[c][2] = acc[c][3] = 0; }
     {
-        const int g = lane >> 2, t = lane & 3;
-        const int wrow = n0 + g;                                  // weight row (output feature) of this lane
-        const bool row_ok = wrow < p.n;
-        const int swz = (wrow >> 1) & 3;
-        for (int s = warp; s < ksteps; s += kSmallWarps) {
-            // bytes s*32 + 4t .. +3 and s*32 + 16 + 4t .. +3 of weight row wrow
-            uint32_t w0 = 0, w1 = 0;
-            if (row_ok) {
-                const int kb = s >> 1, base = (s & 1) * 32;
-                const int8_t* rowp = p.w + ((int64_t)kb * p.w_npad + wrow) * kPackK;
-                const int b0 = base + 4 * t, b1 = base + 16 + 4 * t;
-                w0 = __ldg(reinterpret_cast<const uint32_t*>(rowp + ((((b0 >> 4) ^ swz) << 4) | (b0 & 15))));
-                w1 = __ldg(reinterpret_cast<const uint32_t*>(rowp + ((((b1 >> 4) ^ swz) << 4) | (b1 & 15))));
-            }
-            const uint32_t u0 = w0 ^ 0x80808080u, u1 = w1 ^ 0x80808080u;
-            const uint32_t d0 = fold_pattern(w0), d1 = fold_pattern(w1);
+        // One K step of one channel set.  The weight operand of EVERY channel is the int8
+        // weight itself: a representative of its residue class for any modulus, so the sums
+        // differ from those of canonical residues by multiples of the modulus only, and
+        // |a_c| <= 128, |w| <= 128 keep them far inside int32 at the K this kernel takes.
+        auto step = [&](int s, uint32_t w0, uint32_t w1) {
+            const uint32_t b[2] = {w0, w1};
 #pragma unroll
             for (int c = 0; c < R; ++c) {
-                uint32_t b[2], a[4];
-                b[0] = encode_word_reduced(u0, d0, p.plan.enc_mfold[c]);
-                b[1] = encode_word_reduced(u1, d1, p.plan.enc_mfold[c]);
+                uint32_t a[4];
                 const uint8_t* ap = smem + small_a_offset(c, s, ksteps, 0, 0);
-                a[0] = *reinterpret_cast<const uint32_t*>(ap + g * 16 + 4 * t);
-                a[1] = *reinterpret_cast<const uint32_t*>(ap + (g + 8) * 16 + 4 * t);
-                a[2] = *reinterpret_cast<const uint32_t*>(ap + 256 + g * 16 + 4 * t);
-                a[3] = *reinterpret_cast<const uint32_t*>(ap + 256 + (g + 8) * 16 + 4 * t);
+                a[0] = *reinterpret_cast<const uint32_t*>(ap + wg * 16 + 4 * wt);
+                a[1] = *reinterpret_cast<const uint32_t*>(ap + (wg + 8) * 16 + 4 * wt);
+                a[2] = *reinterpret_cast<const uint32_t*>(ap + 256 + wg * 16 + 4 * wt);
+                a[3] = *reinterpret_cast<const uint32_t*>(ap + 256 + (wg + 8) * 16 + 4 * wt);
                 mma_s8(acc[c], a, b);
             }
+        };
+#pragma unroll
+        for (int i = 0; i < kSmallAhead; ++i) {
+            const int s = warp + i * kSmallWarps;
+            if (s < ksteps) step(s, ahead0[i], ahead1[i]);
         }
+        for (int s = warp + kSmallAhead * kSmallWarps; s < ksteps; s += kSmallWarps) {
+            uint32_t w0, w1;
+            load_weight_words(s, w0, w1);
+            step(s, w0, w1);
+        }
+        const int g = wg, t = wt;
         // fragment -> [token][feature]: c0,c1 = row g, features 2t, 2t+1; c2,c3 = row g + 8
 #pragma unroll
         for (int c = 0; c < R; ++c) {

@@ -135,7 +135,11 @@ class RNSLinear(nn.Module):
     # sources wider than 8 bits, which take the plane-level pipeline.
     def _symmetric_scale(self, values: torch.Tensor, dim=None) -> torch.Tensor:
         max_abs = values.detach().abs().amax(dim=dim, keepdim=True)
-        return torch.clamp(max_abs / float(self.quant_max), min=torch.finfo(torch.float32).eps)
+        # Tensor divisor: with a Python scalar torch's CUDA kernel multiplies by the rounded
+        # reciprocal, which differs from the IEEE quotient (what the reference computes on the
+        # CPU and the quantiser kernels compute) in the last bit for some inputs.
+        return torch.clamp(max_abs / torch.full_like(max_abs, float(self.quant_max)),
+                           min=torch.finfo(torch.float32).eps)
 
     def _quantize(self, values: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
         return torch.clamp(torch.round(values / scale), -self.quant_max, self.quant_max).to(self.quant_dtype)
@@ -237,7 +241,19 @@ class RNSLinear(nn.Module):
                 result, self.last_adaptive_metadata = result
             return result.reshape(*lead, self.out_features).to(inputs.dtype)
 
-        # Wide sources (12/16-bit) or shapes outside the tensor-core kernel:
+        if (self.quant_bits != 8 and self.fused and not self.adaptive_channels
+                and self.backend.supports_wide_forward(prepared, flat.shape[0])):
+            # 12/16-bit sources with enough rows: quantiser -> residue planes -> the two-CTA
+            # tensor-core kernel with the weight's cached residue planes.
+            if flat.stride(-1) != 1 or flat.dtype not in (torch.float16, torch.bfloat16, torch.float32):
+                flat = flat.contiguous() if flat.dtype in (torch.float16, torch.bfloat16, torch.float32) \
+                    else flat.float().contiguous()
+            result = self.backend.linear_forward_wide(
+                flat, prepared, self._weight_scale, self._bias_float(), quant_max=self.quant_max,
+                per_row=self.activation_scale == "row")
+            return result.reshape(*lead, self.out_features).to(inputs.dtype)
+
+        # Wide sources (12/16-bit) with few rows, or shapes outside the tensor-core kernel:
         # the reference's plane-level pipeline, op for op (rns_linear.py:239-275).
         flat = flat.float().contiguous()
         scale_dim = 1 if self.activation_scale == "row" else None

@@ -168,17 +168,20 @@ def test_sharded_layers_pass_the_absmax_on(backend):
     backend.check_status()
 
 
-def test_output_copies_and_absmax_hand_over(backend):
+@pytest.mark.parametrize("m,k,n,mods", [(640, 1024, 520, C0), (600, 1024, 384, C4), (645, 512, 260, C0),
+                                        (1027, 768, 1024, C0)])
+def test_output_copies_and_absmax_hand_over(backend, m, k, n, mods):
     """The epilogue's fan-out, on one GPU: buffers of this process stand in for the other
     ranks' memory.  Every copy receives exactly what `out` receives, and the finished
-    absmax word (written by the last CTA to contribute) equals max |y|."""
+    absmax word (written by the last CTA to contribute) equals max |y|.  The shapes take
+    the row-wide staged stores (full 128-feature blocks, row stride a multiple of 8), the
+    lane-pair stores (ragged last block; stride 260) and ragged token tiles."""
     torch.manual_seed(31)
-    m, k, n = 640, 1024, 520
     x = torch.randn(m, k, dtype=torch.float16, device="cuda")
     weight = (torch.randn(n, k, device="cuda") * 0.05).half()
     bias = torch.randn(n, device="cuda").float()
     w_q, w_scale, _ = backend.quantize_weight(weight)
-    prepared = backend.prepare_weight_nk(w_q, C0)
+    prepared = backend.prepare_weight_nk(w_q, mods)
     plain = backend.linear_forward(x, prepared, w_scale, bias).clone()
     for copies in (1, 3, 7):
         out = torch.full((m, n), float("nan"), dtype=torch.float16, device="cuda")
