@@ -806,6 +806,67 @@ def run_quantiser(args) -> None:
                       "rows": rows}))
 
 
+def run_wide_sources(args) -> None:
+    """quant_bits 12 and 16 (sources wider than int8, where the residue system is not
+    degenerate) on the linears of one layer of the stack's shapes: the module on the
+    tensor-core path (residue planes on both sides, one int8 MMA per channel) against the
+    same module on the plane-level pipeline (exact SIMT GEMM per channel + Garner kernel,
+    the stand-in for the reference's cuBLAS route) and fp16 F.linear; CUDA events over
+    `iters` calls, outputs compared."""
+    import torch
+    import torch.nn.functional as F
+    from rns_llm_b200.backends import CudaRNSBackend
+    from rns_llm_b200.layers import RNSLinear
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; the RNS path has no CPU implementation")
+    backend = CudaRNSBackend()
+    iters, rows = 10, []
+
+    def timed(fn, n):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(n):
+            fn()
+        stop.record()
+        torch.cuda.synchronize()
+        return start.elapsed_time(stop) / n
+
+    m = args.tokens
+    for bits in (12, 16):
+        for name, k, n in (("qkv", HIDDEN, 3 * HIDDEN), ("fc2", FFN, HIDDEN)):
+            torch.manual_seed(bits + k)
+            layer = RNSLinear(k, n, backend=backend, mode="rns", quant_bits=bits).half().cuda().eval()
+            x = torch.randn((m, k), dtype=torch.float16, device="cuda")
+            with torch.no_grad():
+                y = layer(x)
+                fast_ms = timed(lambda: layer(x), iters)
+                backend.check_status()
+                prepared = layer._prepared_weight
+                planes, prepared.weight_planes_packed = prepared.weight_planes_packed, None   # plane-level pipeline
+                try:
+                    y_planes = layer(x)
+                    plane_ms = timed(lambda: layer(x), 2)
+                finally:
+                    prepared.weight_planes_packed = planes
+                fp16_ms = timed(lambda: F.linear(x, layer.weight, layer.bias), iters)
+            r = len(layer.moduli)
+            rows.append({"quant_bits": bits, "linear": name, "m": m, "k": k, "n": n, "channels": r,
+                         "moduli": list(layer.moduli), "tensor_core_ms": fast_ms,
+                         "channel_tops": 2.0 * r * m * k * n / fast_ms / 1e9,
+                         "plane_pipeline_ms": plane_ms, "fp16_linear_ms": fp16_ms,
+                         "max_abs_diff_vs_plane_pipeline": float((y.float() - y_planes.float()).abs().max()),
+                         "max_abs_diff_vs_fp16": float((y.float() - F.linear(x, layer.weight, layer.bias).float()).abs().max())})
+    print(json.dumps({"metric": "wide_source_rns_linear_ms", "unit": "ms", "n_gpus": 1, "higher_is_better": False,
+                      "data": "synthetic", "dtype": "int16 sources, int8 residues",
+                      "config": {"workload": "RNSLinear quant_bits 12 / 16 on the stack's QKV and fc2 shapes",
+                                 "tokens": m, "iters": iters},
+                      "rows": rows}))
+
+
 # Where the run is, for the failure report: {"phase": ..., "step": ..., "layer": ..., "linear": ...}
 PROGRESS: dict = {"phase": "start"}
 
@@ -1079,7 +1140,7 @@ def main() -> None:
                         help="skip the torch._int_mm peak measurement (roofline.frac then uses 2 x bf16 sustained)")
     parser.add_argument("--gpu-baselines", action="store_true",
                         help="also time F.linear fp16 and torch._int_mm + eager dequantisation on the stack's shapes")
-    parser.add_argument("--workload", default="c4", choices=["c4", "c1", "c2", "c3", "quant", "peak"],
+    parser.add_argument("--workload", default="c4", choices=["c4", "c1", "c2", "c3", "quant", "peak", "wide"],
                         help="c4: the layer stack (the bench contract); c1: fused-QKV latency of configuration 1; "
                              "c2: continuous batching and adaptive channels of configuration 2; c3: the "
                              "OPT-125m-shaped decoder of configuration 3; quant: the activation quantiser alone "
@@ -1096,6 +1157,9 @@ def main() -> None:
         return
     if args.workload == "c3":
         run_opt_decoder(args)
+        return
+    if args.workload == "wide":
+        run_wide_sources(args)
         return
     if args.workload == "quant":
         run_quantiser(args)

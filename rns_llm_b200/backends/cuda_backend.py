@@ -932,9 +932,17 @@ class CudaRNSBackend:
             self._stats["fused_gemm_calls"] += 1
             self._stats[f"fused_gemm_channels_{channels}"] += 1
             return (out, None) if return_metadata else out
-        use_planes = m >= PLANES_MIN_ROWS and adaptive is None
-        # Many-token calls: planes in tiles of 64 / 48 token rows for the two-CTA kernel.
+        use_planes = m >= PLANES_MIN_ROWS
+        # Many-token calls: planes in tiles of 64 / 48 / 32 token rows for the two-CTA kernel.
         tile_rows = int(self._lib.rns_pair_tile_rows(channels, k)) if use_planes else 0
+        # Adaptive calls with many tokens: the prefix is still chosen on the device (metadata,
+        # counters, overflow status), but the two-CTA kernel then runs the FULL set - the
+        # integer is the same for every sufficient prefix, and four channels on that kernel
+        # take less time than three on the general one.  Where it does not cover the shape
+        # the general kernel honours the prefix, from int8 activations.
+        full_set_kernel = adaptive is not None and tile_rows != 0
+        if adaptive is not None and tile_rows == 0:
+            use_planes = False
         if absmax_in is not None and per_row:
             raise ValueError("absmax_in serves the per-tensor scale")
         if absmax_out is not None and (tile_rows == 0 or per_row):
@@ -978,7 +986,7 @@ class CudaRNSBackend:
                 self._stats[f"fused_gemm_channels_{channels}"] += 1
             self._launch_fused(prepared=prepared if adaptive is None else adaptive.variants[channels],
                                m=m, a=None if use_planes else act, a_planes=act if use_planes else None,
-                               a_packed=True, out=out, active=active,
+                               a_packed=True, out=out, active=None if full_set_kernel else active,
                                row_scale=scale, row_scale_stride=1 if per_row else 0,
                                col_scale=weight_scale, bias=bias, stream=stream,
                                a_tile_rows=tile_rows, absmax_out=absmax_out,

@@ -204,3 +204,33 @@ def test_output_copies_and_absmax_hand_over(backend, m, k, n, mods):
     backend.check_status()
     with pytest.raises(ValueError):
         backend.linear_forward(x[:64], prepared, w_scale, bias, out_copies=[plain.data_ptr()])
+
+
+def test_adaptive_many_token_calls_take_the_two_cta_kernel(backend):
+    """Adaptive layers with many tokens: the prefix is chosen on the device as always (metadata,
+    counters), the two-CTA kernel runs the full set, and the outputs are those of the
+    non-adaptive layer bit for bit (every sufficient prefix reconstructs the same integer)."""
+    from rns_llm_b200.layers import RNSLinear
+    torch.manual_seed(17)
+    m, k, n = 640, 1024, 384
+    plain = RNSLinear(k, n, backend=backend, mode="rns", moduli=C0).half().cuda().eval()
+    adaptive = RNSLinear(k, n, backend=backend, mode="rns", moduli=C0, adaptive_channels=True,
+                         adaptive_min_channels=3).half().cuda().eval()
+    adaptive.load_state_dict(plain.state_dict())
+    x = torch.randn(m, k, dtype=torch.float16, device="cuda") * 0.02
+    x[0, 0] = 1.0                                   # one large value: small quantised rows, a three-channel bound
+    backend.reset_stats()
+    with torch.no_grad():
+        y_plain = plain(x)
+        y_adaptive = adaptive(x)
+    torch.cuda.synchronize()
+    backend.check_status()
+    assert torch.equal(y_plain, y_adaptive)
+    meta = adaptive.last_adaptive_metadata
+    assert meta is not None and int(meta["channels"]) in (3, 4) and int(meta["bound"]) <= int(meta["capacity"])
+    res = O.rns_linear_forward(x.float().cpu().numpy(), plain.weight.detach().float().cpu().numpy(),
+                               plain.bias.detach().float().cpu().numpy(), C0, out_dtype=np.float16)
+    expect_channels, expect_bound = O.adaptive_channels(res["a_q"], res["w_q"], C0, 3)
+    assert int(meta["channels"]) == expect_channels and int(meta["bound"]) == expect_bound
+    assert np.array_equal(y_adaptive.cpu().numpy(), res["y"])
+    assert backend.stats_snapshot()["adaptive_selections"] == 1
