@@ -215,7 +215,9 @@ RNS_API int rns_matmul_centered_fused_out(const int8_t* d_a, const int8_t* d_b,
  *
  * d_active_channels, when non-NULL, points to a device int c (2..channels):
  * only the first c moduli are used (adaptive prefix, backends/cuda_backend.py:
- * 573-622, decided on the device by rns_select_channels).
+ * 573-622, decided on the device by rns_select_channels).  Honoured by the
+ * general kernel and, with tiled planes (a_tile_rows), by variant 4 for 4 or 5
+ * channels without w_channel_stride and output copies.
  *
  * Integer output types store x = sum_k a[m,k]*w[n,k] reconstructed and
  * recentred exactly as csrc/rns_cuda.cu:380-414.  Floating output types store
@@ -340,6 +342,12 @@ RNS_API int rns_unpack_weight(const int8_t* d_packed, int n, int k, int8_t* d_w,
 RNS_API int rns_encode_planes_packed(const int8_t* d_a, int m, int k, int64_t lda,
                                      const int32_t* moduli, int channels, int8_t* d_planes_packed,
                                      rns_stream_t stream);
+/* The same in tiles of tile_rows token rows ([M_pad/rows][K_pad/64][channels][rows][64],
+ * rns_linear_args.a_tile_rows; rns_packed_planes_bytes gives the size): the integer entry
+ * of the two-CTA kernels. */
+RNS_API int rns_encode_planes_tiled(const int8_t* d_a, int m, int k, int64_t lda,
+                                    const int32_t* moduli, int channels, int tile_rows,
+                                    int8_t* d_planes_packed, rns_stream_t stream);
 
 /* 1 when rns_linear_fused accepts this problem, 0 when it would return
  * RNS_ERR_UNSUPPORTED (the role of CudaRNSBackend.cublas_compatible,

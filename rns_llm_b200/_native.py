@@ -104,6 +104,7 @@ SIGNATURES: dict[str, tuple] = {
     "rns_pack_weight": (C.c_int, [_VP, C.c_int, C.c_int, C.c_int64, _VP, _VP]),
     "rns_unpack_weight": (C.c_int, [_VP, C.c_int, C.c_int, _VP, C.c_int64, _VP]),
     "rns_encode_planes_packed": (C.c_int, [_VP, C.c_int, C.c_int, C.c_int64, _I32P, C.c_int, _VP, _VP]),
+    "rns_encode_planes_tiled": (C.c_int, [_VP, C.c_int, C.c_int, C.c_int64, _I32P, C.c_int, C.c_int, _VP, _VP]),
     "rns_row_l1_max_i8": (C.c_int, [_VP, C.c_int, C.c_int, C.c_int64, _VP, _VP]),
     "rns_select_channels": (C.c_int, [_VP, C.c_int32, _I32P, C.c_int, C.c_int, _VP, _VP, _VP, _VP, _VP]),
     "rns_linear_small_supported": (C.c_int, [C.c_int, C.c_int, C.c_int]),

@@ -700,14 +700,26 @@ class CudaRNSBackend:
                     workspace.output.stride(0), N.OUT_INT64, self._stream(a.device)))
             elif m >= PLANES_MIN_ROWS:
                 frame = self.arena.frame(a.device)
-                planes = frame.alloc(int(self._lib.rns_packed_activation_bytes(m, prepared_weight.k, channels)),
-                                     torch.int8)
                 _, arr = self._mods(mods)
-                N.check(self._lib.rns_encode_planes_packed(a.data_ptr(), m, prepared_weight.k, a.stride(0),
-                                                           arr, channels, planes.data_ptr(),
-                                                           self._stream(a.device)))
+                # tiles of 64 / 48 / 32 rows for the two-CTA kernel where it covers the call
+                # (an adaptive prefix: 4 or 5 channels), else the 128-row layout
+                tile_rows = int(self._lib.rns_pair_tile_rows(channels, prepared_weight.k))
+                if _active is not None and channels > 5:
+                    tile_rows = 0
+                if tile_rows:
+                    planes = frame.alloc(int(self._lib.rns_packed_planes_bytes(m, prepared_weight.k, channels,
+                                                                               tile_rows)), torch.int8)
+                    N.check(self._lib.rns_encode_planes_tiled(a.data_ptr(), m, prepared_weight.k, a.stride(0),
+                                                              arr, channels, tile_rows, planes.data_ptr(),
+                                                              self._stream(a.device)))
+                else:
+                    planes = frame.alloc(int(self._lib.rns_packed_activation_bytes(m, prepared_weight.k,
+                                                                                   channels)), torch.int8)
+                    N.check(self._lib.rns_encode_planes_packed(a.data_ptr(), m, prepared_weight.k, a.stride(0),
+                                                               arr, channels, planes.data_ptr(),
+                                                               self._stream(a.device)))
                 self._launch_fused(prepared=prepared_weight, m=m, a=None, a_planes=planes, a_packed=True,
-                                   out=workspace.output, active=_active)
+                                   out=workspace.output, active=_active, a_tile_rows=tile_rows)
             else:
                 self._launch_fused(prepared=prepared_weight, m=m, a=a, a_planes=None,
                                    out=workspace.output, active=_active)
@@ -799,7 +811,19 @@ class CudaRNSBackend:
             self._stats["encode_centered_calls"] += 1
             self._stats["encode_centered_values"] += int(a.numel())
             self._stats["fused_gemm_calls"] += 1
-            self._launch_fused(prepared=full, m=m, a=a, a_planes=None, out=out, active=active)
+            tile_rows = 0
+            if m >= PLANES_MIN_ROWS and channels <= 5 and a.stride(1) == 1:
+                tile_rows = int(self._lib.rns_pair_tile_rows(channels, full.k))
+            if tile_rows:
+                # many tokens: tiled planes, and the two-CTA kernel computes the chosen prefix
+                planes = frame.alloc(int(self._lib.rns_packed_planes_bytes(m, full.k, channels, tile_rows)),
+                                     torch.int8)
+                N.check(self._lib.rns_encode_planes_tiled(a.data_ptr(), m, full.k, a.stride(0), arr, channels,
+                                                          tile_rows, planes.data_ptr(), stream))
+                self._launch_fused(prepared=full, m=m, a=None, a_planes=planes, a_packed=True, out=out,
+                                   active=active, a_tile_rows=tile_rows)
+            else:
+                self._launch_fused(prepared=full, m=m, a=a, a_planes=None, out=out, active=active)
         if return_metadata:
             return out, AdaptiveMetadata(meta)
         return out
@@ -935,14 +959,12 @@ class CudaRNSBackend:
         use_planes = m >= PLANES_MIN_ROWS
         # Many-token calls: planes in tiles of 64 / 48 / 32 token rows for the two-CTA kernel.
         tile_rows = int(self._lib.rns_pair_tile_rows(channels, k)) if use_planes else 0
-        # Adaptive calls with many tokens: the prefix is still chosen on the device (metadata,
-        # counters, overflow status), but the two-CTA kernel then runs the FULL set - the
-        # integer is the same for every sufficient prefix, and four channels on that kernel
-        # take less time than three on the general one.  Where it does not cover the shape
-        # the general kernel honours the prefix, from int8 activations.
-        full_set_kernel = adaptive is not None and tile_rows != 0
-        if adaptive is not None and tile_rows == 0:
-            use_planes = False
+        # Adaptive calls: the two-CTA kernel reads the prefix chosen on the device and skips
+        # the other channels' planes, MMAs and residues (4 or 5 channels in the full set);
+        # where it does not cover the shape the general kernel does the same from int8
+        # activations.
+        if adaptive is not None and (tile_rows == 0 or channels > 5):
+            use_planes, tile_rows = False, 0
         if absmax_in is not None and per_row:
             raise ValueError("absmax_in serves the per-tensor scale")
         if absmax_out is not None and (tile_rows == 0 or per_row):
@@ -986,7 +1008,7 @@ class CudaRNSBackend:
                 self._stats[f"fused_gemm_channels_{channels}"] += 1
             self._launch_fused(prepared=prepared if adaptive is None else adaptive.variants[channels],
                                m=m, a=None if use_planes else act, a_planes=act if use_planes else None,
-                               a_packed=True, out=out, active=None if full_set_kernel else active,
+                               a_packed=True, out=out, active=active,
                                row_scale=scale, row_scale_stride=1 if per_row else 0,
                                col_scale=weight_scale, bias=bias, stream=stream,
                                a_tile_rows=tile_rows, absmax_out=absmax_out,

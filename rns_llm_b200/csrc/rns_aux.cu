@@ -687,7 +687,11 @@ encode_planes_packed_kernel(const int8_t* __restrict__ a, int m, int k, int64_t 
             x = *reinterpret_cast<const uint4*>(tmp);
         }
         const uint32_t w[4] = {x.x, x.y, x.z, x.w};
-        const int64_t base = packed_act_offset(row, col, 0, o.channels, o.kblocks);
+        // tile (row / tile_rows, col / 64) of `channels` channels, tile_rows x 64 bytes each
+        const RowPos pos = row_pos(o, row);
+        const int tile_bytes = o.tile_rows * kPackK;
+        const int64_t base = ((int64_t)pos.tile * o.kblocks + (col >> 6)) * o.channels * tile_bytes +
+                             packed_row_offset(pos.inside, col & 63);
 #pragma unroll 1
         for (int ch = 0; ch < o.channels; ++ch) {
             uint32_t e[4];
@@ -702,7 +706,7 @@ encode_planes_packed_kernel(const int8_t* __restrict__ a, int m, int k, int64_t 
                         e[j] |= (uint32_t)(centred_residue((int)(int8_t)(w[j] >> (8 * b)), o.mod[ch]) & 0xff) << (8 * b);
                 }
             }
-            *reinterpret_cast<uint4*>(o.planes + base + (int64_t)ch * kPackM * kPackK) =
+            *reinterpret_cast<uint4*>(o.planes + base + (int64_t)ch * tile_bytes) =
                 make_uint4(e[0], e[1], e[2], e[3]);
         }
     }
@@ -992,14 +996,21 @@ int rns_unpack_weight(const int8_t* d_packed, int n, int k, int8_t* d_w, int64_t
 
 int rns_encode_planes_packed(const int8_t* d_a, int m, int k, int64_t lda, const int32_t* moduli,
                              int channels, int8_t* d_planes_packed, rns_stream_t stream) {
-    if (!d_a || !d_planes_packed) return fail(RNS_ERR_INVALID_ARGUMENT, "encode_planes_packed: NULL pointer");
+    return rns_encode_planes_tiled(d_a, m, k, lda, moduli, channels, kPackM, d_planes_packed, stream);
+}
+
+int rns_encode_planes_tiled(const int8_t* d_a, int m, int k, int64_t lda, const int32_t* moduli,
+                            int channels, int tile_rows, int8_t* d_planes_packed, rns_stream_t stream) {
+    if (!d_a || !d_planes_packed) return fail(RNS_ERR_INVALID_ARGUMENT, "encode_planes: NULL pointer");
     if (m <= 0 || k <= 0 || lda < k)
-        return fail(RNS_ERR_INVALID_ARGUMENT, "encode_planes_packed: bad shape or stride");
+        return fail(RNS_ERR_INVALID_ARGUMENT, "encode_planes: bad shape or stride");
+    if (tile_rows < 8 || tile_rows > 128 || tile_rows % 8 != 0)
+        return fail(RNS_ERR_INVALID_ARGUMENT, "encode_planes: tile_rows must be a multiple of 8, at most 128");
     QuantOut qo{};
     if (int rc = fill_encoder(qo, moduli, channels)) return rc;
     qo.planes = d_planes_packed;
     qo.packed = 1;
-    qo.tile_rows = kPackM;
+    qo.tile_rows = tile_rows;
     qo.kblocks = (k + kPackK - 1) / kPackK;
     encode_planes_packed_kernel<<<grid_for((int64_t)m * ((k + 15) / 16), 256), 256, 0, as_stream(stream)>>>(
         d_a, m, k, lda, qo);

@@ -36,9 +36,13 @@ namespace rns {
 // the residue planes of the weight cached at prepare time.  S: ring depth (<= kDoneRing).
 // ISSUERS: 2 = warps 0 and 1 take alternate stages (needs an even S, so that a slot keeps
 // its warp and the warp sees every phase of the slot's barrier); 1 = warp 0 issues all.
-template <int R, int TOK, int S, int ISSUERS, bool WCH, bool COPIES>
+// PREFIX: p.active points at the number of leading channels to compute (the adaptive
+// prefix a preceding kernel chose on the device): the planes, MMAs and residues of the
+// others are skipped, and the reconstruction uses the prefix's product.
+template <int R, int TOK, int S, int ISSUERS, bool WCH, bool COPIES, bool PREFIX = false>
 __global__ void __launch_bounds__(kPairThreads, 1)
 rns_gemm_pair_raw_kernel(const __grid_constant__ PairParams p) {
+    static_assert(!PREFIX || (!WCH && !COPIES), "the prefix form exists for one int8 weight matrix, no copies");
     static_assert(R * TOK <= 512, "accumulators must fit tensor memory");
     static_assert(TOK % 32 == 0 && (TOK / 2) % 8 == 0, "token tile shape");
     static_assert(S <= kDoneRing && (ISSUERS == 1 || (ISSUERS == 2 && S % 2 == 0)), "ring depth");
@@ -86,6 +90,8 @@ rns_gemm_pair_raw_kernel(const __grid_constant__ PairParams p) {
     tc_fence_after();
     const uint32_t tmem_base = ctl.tmem_base;
     volatile int* abort = &ctl.abort;
+    int act = R;                                               // every thread reads the same word
+    if constexpr (PREFIX) act = min(max(*reinterpret_cast<const volatile int32_t*>(p.active), 1), R);
 
     if (warp == kPairPlaneWarp) {
         // ------------------------------ producer ----------------------------------
@@ -100,7 +106,8 @@ rns_gemm_pair_raw_kernel(const __grid_constant__ PairParams p) {
                 const bool w_rows = t.n0 < p.w_npad;
                 const int8_t* w_src = p.w + (int64_t)t.n0 * kPackK;
                 const int64_t kb_stride = p.w_npad * kPackK;
-                const uint32_t bytes = kPlStage + (w_rows ? kWStage : 0u);
+                const uint32_t pl_bytes = PREFIX ? (uint32_t)act * kPlTile : kPlStage;   // leading channels only
+                const uint32_t bytes = pl_bytes + (w_rows ? kWStage : 0u);
                 for (int st = 0; st < nst; ++st, ++g) {
                     if (g >= S &&
                         !wait_bounded<false, true>(smem_addr(&ctl.done[(g - S) & (kDoneRing - 1)]),
@@ -117,7 +124,7 @@ rns_gemm_pair_raw_kernel(const __grid_constant__ PairParams p) {
                             bulk_load(w_base + (uint32_t)s * kWStage + (uint32_t)c * kPairOpTile,
                                       w_src + (int64_t)c * p.w_channel_stride + (int64_t)st * kb_stride, kPairOpTile, bar);
                     }
-                    bulk_load(pl_base + (uint32_t)s * kPlStage, pl_src + (int64_t)st * kPlStage, kPlStage, bar);
+                    bulk_load(pl_base + (uint32_t)s * kPlStage, pl_src + (int64_t)st * kPlStage, pl_bytes, bar);
                 }
             }
         }
@@ -168,6 +175,7 @@ rns_gemm_pair_raw_kernel(const __grid_constant__ PairParams p) {
                     if (elect_one()) {
 #pragma unroll
                         for (int c = 0; c < R; ++c) {
+                            if (PREFIX && c >= act) continue;
 #pragma unroll
                             for (int ks = 0; ks < 2; ++ks) {
                                 const uint64_t da = desc0 | (uint64_t)(a_st + (WCH ? (uint32_t)c * (kPairOpTile >> 4) : 0u) + (uint32_t)ks * 2u);
@@ -222,10 +230,10 @@ rns_gemm_pair_raw_kernel(const __grid_constant__ PairParams p) {
             }
             if (!ok) break;
             tc_fence_after();
-            pair_epilogue<R, TOK, COPIES, (R <= 4 && RNS_PAIR_SPLIT_EPILOGUE != 0)>(
+            pair_epilogue<R, TOK, COPIES, (R <= 4 && RNS_PAIR_SPLIT_EPILOGUE != 0), PREFIX>(
                 p, t.n0, t.tok0, quarter, part, lane, lane_base, is_float, rs_all, biggest, release,
                 COPIES ? reinterpret_cast<unsigned short*>(smem_dyn + (tiles_base - smem_addr(smem_dyn)) +
-                                                           (size_t)S * (kWStage + kPlStage)) : nullptr);
+                                                           (size_t)S * (kWStage + kPlStage)) : nullptr, act);
         }
         if (p.absmax_out != nullptr && is_float) {
 #pragma unroll
@@ -277,13 +285,13 @@ rns_gemm_pair_raw_kernel(const __grid_constant__ PairParams p) {
 // ---------------------------------------------------------------------------
 // Host side
 // ---------------------------------------------------------------------------
-template <int R, int TOK, int S, int ISSUERS, bool WCH, bool COPIES>
+template <int R, int TOK, int S, int ISSUERS, bool WCH, bool COPIES, bool PREFIX = false>
 static int launch_pair_raw(const PairParams& pp, int pairs, cudaStream_t st) {
     // COPIES: 16 KB behind the rings stage the row-wide stores (4 blocks x 2 buffers x 8 x 128 x 2 bytes)
     constexpr size_t smem = (size_t)S * ((WCH ? R : 1) * kPairOpTile + (size_t)R * (TOK / 2) * kPackK) + 1024 +
                             (COPIES ? kPairStageBytes : 0);
     static_assert(smem + sizeof(PairCtl) <= 227 * 1024, "ring exceeds shared memory");
-    return launch_pair_clusters<rns_gemm_pair_raw_kernel<R, TOK, S, ISSUERS, WCH, COPIES>>(smem, pp, pairs, st);
+    return launch_pair_clusters<rns_gemm_pair_raw_kernel<R, TOK, S, ISSUERS, WCH, COPIES, PREFIX>>(smem, pp, pairs, st);
 }
 
 int pair_raw_token_tile(int channels) { return channels <= 4 ? 128 : (channels == 5 ? 96 : 64); }
@@ -297,6 +305,12 @@ int launch_pair_raw_gemm(const PairParams& pp, int pairs, cudaStream_t st) {
         if (R == 5) return launch_pair_raw<5, 96, 4, 2, true, false>(pp, pairs, st);
         if (R == 6) return launch_pair_raw<6, 64, 3, 1, true, false>(pp, pairs, st);
         return fail(RNS_ERR_UNSUPPORTED, "per-channel weights: 4, 5 or 6 channels");
+    }
+    if (pp.active != nullptr) {
+        if (pp.n_copies > 0) return fail(RNS_ERR_UNSUPPORTED, "an adaptive prefix and output copies are not built together");
+        if (R == 4) return launch_pair_raw<4, 128, 8, 2, false, false, true>(pp, pairs, st);
+        if (R == 5) return launch_pair_raw<5, 96, 8, 2, false, false, true>(pp, pairs, st);
+        return fail(RNS_ERR_UNSUPPORTED, "adaptive prefix: 4 or 5 channels");
     }
     if (pp.n_copies > 0) {
         if (R == 4) return launch_pair_raw<4, 128, 8, 2, false, true>(pp, pairs, st);

@@ -262,7 +262,7 @@ rns_gemm_pair_kernel(const __grid_constant__ PairParams p) {
             if (ok) ok = warp_wait_bounded(smem_addr(&ctl.acc_full), (uint32_t)ti & 1u, abort, wait_code(11, ti));
             if (!ok) break;
             tc_fence_after();
-            pair_epilogue<R, TOK, COPIES, false>(p, n0, tok0, quarter, part, lane, lane_base, is_float, rs_all, biggest, [] {});
+            pair_epilogue<R, TOK, COPIES, false, false>(p, n0, tok0, quarter, part, lane, lane_base, is_float, rs_all, biggest, [] {});
             // Every column this warp read belongs to channel blocks c*TOK + [col0, col0 + TOK/4);
             // the columns it ZEROES are its 128-column block.  All sixteen warps have to be
             // done reading before anyone's zeroes may land on columns another warp still reads.
@@ -332,7 +332,10 @@ int pair_gemm_token_tile(int channels) { return pair_raw_token_tile(channels); }
 bool pair_gemm_supported(const rns_linear_args* a) {
     const bool channels_ok = a->channels == 4 || a->channels == 5 ||
                              (a->channels == 6 && a->variant != 3 && a->n_out_copies == 0);
-    return a->d_a_planes != nullptr && a->a_packed != 0 && a->w_packed != 0 && a->d_active_channels == nullptr &&
+    // an adaptive prefix (d_active_channels) is honoured by the raw-weight kernel with one weight matrix
+    const bool prefix_ok = a->d_active_channels == nullptr ||
+                           (a->variant != 3 && a->w_channel_stride == 0 && a->n_out_copies == 0 && a->channels <= 5);
+    return a->d_a_planes != nullptr && a->a_packed != 0 && a->w_packed != 0 && prefix_ok &&
            a->exact_residues == 0 && channels_ok && (a->w_channel_stride == 0 || a->variant != 3) &&
            a->w_channel_stride >= 0 && a->w_channel_stride % 16 == 0 &&
            a->a_tile_rows == pair_gemm_token_tile(a->channels) / 2 && a->k >= 8 * kPackK && a->k % 16 == 0;
@@ -368,6 +371,7 @@ int launch_pair_gemm(const rns_linear_args* a, const Plan& plan, cudaStream_t st
         pp.out_copies[g] = a->d_out_copies[g];
         pp.absmax_copies[g] = a->d_absmax_copies[g];
     }
+    pp.active = a->d_active_channels;
     pp.status = a->d_status; pp.wait_info = a->d_wait_info;
     const int64_t pairs = (int64_t)pp.n_ftiles * pp.n_ttiles;
     if (pairs > (1 << 30)) return fail(RNS_ERR_UNSUPPORTED, "too many output tiles");

@@ -53,6 +53,7 @@ struct PairParams {
     int32_t n_copies;
     void* out_copies[RNS_MAX_PEERS];
     uint32_t* absmax_copies[RNS_MAX_PEERS];
+    const int32_t* active;     // NULL, or device int: only the first *active channels are computed (adaptive prefix)
     int32_t* status;
     int32_t* wait_info;
 };
@@ -103,8 +104,11 @@ __device__ __forceinline__ F2 add2(F2 a, F2 b) {
 
 // Centred mixed-radix digits of two outputs (all R channels active).  RES: a0 / a1 hold
 // residues in [0, m) already (canonical_residue) instead of int32 channel sums.
-template <int R, bool RES = false>
-__device__ __forceinline__ void garner_digits_x2(const int (&a0)[R], const int (&a1)[R], const Plan& pl, F2 (&digit)[R]) {
+// PREFIX: only the first `act` channels carry the value (adaptive prefix); the digits of the
+// others are zero.  Without PREFIX `act` is ignored and all R channels are used.
+template <int R, bool RES = false, bool PREFIX = false>
+__device__ __forceinline__ void garner_digits_x2(const int (&a0)[R], const int (&a1)[R], const Plan& pl, F2 (&digit)[R],
+                                                 int act = R) {
     const F2 magic = f2_splat(kMagic), neg_magic = f2_splat(-kMagic);
 #pragma unroll
     for (int i = 0; i < R; ++i) {
@@ -118,15 +122,17 @@ __device__ __forceinline__ void garner_digits_x2(const int (&a0)[R], const int (
         // centre_mod: q = (t * rcp + magic) - magic;  digit = -q * m + t
         const F2 q = add2(fma2(t, f2_splat(pl.rcpf[i]), magic), neg_magic);
         digit[i] = fma2(q, f2_splat(-pl.modf[i]), t);
+        if (PREFIX && i >= act) digit[i] = f2_splat(0.0f);
     }
 }
 
 // reconstruct32 for two outputs (R <= 4, all channels active).
-template <int R, bool RES = false>
-__device__ __forceinline__ void reconstruct32_x2(const int (&a0)[R], const int (&a1)[R], const Plan& pl, int& x0, int& x1) {
+template <int R, bool RES = false, bool PREFIX = false>
+__device__ __forceinline__ void reconstruct32_x2(const int (&a0)[R], const int (&a1)[R], const Plan& pl, int& x0, int& x1,
+                                                 int act = R) {
     static_assert(R <= 4, "32-bit reconstruction covers at most four channels");
     F2 digit[R];
-    garner_digits_x2<R, RES>(a0, a1, pl, digit);
+    garner_digits_x2<R, RES, PREFIX>(a0, a1, pl, digit, act);
     const F2 magic = f2_splat(kMagic);
     unsigned u0 = 0, u1 = 0;
     if constexpr (R == 4) {
@@ -142,7 +148,7 @@ __device__ __forceinline__ void reconstruct32_x2(const int (&a0)[R], const int (
             u1 += pl.place32[i] * (unsigned)(float_to_bits(d.y) - kMagicBits);
         }
     }
-    const unsigned prod = (unsigned)pl.product[R];
+    const unsigned prod = (unsigned)pl.product[PREFIX ? act : R];
     const int half = (int)(prod >> 1);
     const int low = (int)((unsigned)half - prod + 1u);
     int s0 = (int)u0, s1 = (int)u1;
@@ -152,10 +158,11 @@ __device__ __forceinline__ void reconstruct32_x2(const int (&a0)[R], const int (
 }
 
 // reconstruct for two outputs (any R up to 8, all channels active).
-template <int R>
-__device__ __forceinline__ void reconstruct64_x2(const int (&a0)[R], const int (&a1)[R], const Plan& pl, long long& x0, long long& x1) {
+template <int R, bool PREFIX = false>
+__device__ __forceinline__ void reconstruct64_x2(const int (&a0)[R], const int (&a1)[R], const Plan& pl, long long& x0, long long& x1,
+                                                 int act = R) {
     F2 digit[R];
-    garner_digits_x2<R>(a0, a1, pl, digit);
+    garner_digits_x2<R, false, PREFIX>(a0, a1, pl, digit, act);
     const F2 magic = f2_splat(kMagic);
     int lo0 = 0, lo1 = 0;
     long long v0 = 0, v1 = 0;
@@ -167,7 +174,7 @@ __device__ __forceinline__ void reconstruct64_x2(const int (&a0)[R], const int (
         else { v0 += pl.place64[i] * (long long)d0; v1 += pl.place64[i] * (long long)d1; }
     }
     v0 += lo0; v1 += lo1;
-    const long long prod = pl.product[R], half = prod >> 1;
+    const long long prod = pl.product[PREFIX ? act : R], half = prod >> 1;
     if (v0 > half) v0 -= prod; else if (v0 < half - prod + 1) v0 += prod;
     if (v1 > half) v1 -= prod; else if (v1 < half - prod + 1) v1 += prod;
     x0 = v0; x1 = v1;
@@ -208,10 +215,11 @@ __device__ __forceinline__ PairTile pair_tile(const PairParams& p, int tile, uin
 // (a byte each), and `release()` runs as soon as the last column is read - the next
 // tile's MMAs start then.  The second phase reconstructs, scales and stores from those
 // registers while the tensor pipe is busy again.  Without SPLIT, release() runs last.
-template <int R, int TOK, bool COPIES, bool SPLIT, typename Release>
+// PREFIX: `act` <= R channels carry the value (the adaptive prefix chosen on the device).
+template <int R, int TOK, bool COPIES, bool SPLIT, bool PREFIX = false, typename Release>
 __device__ __forceinline__ void pair_epilogue(const PairParams& p, int n0, int tok0, int quarter, int part, int lane,
                                               uint32_t lane_base, bool is_float, float rs_all, float& biggest,
-                                              Release&& release, unsigned short* stage = nullptr) {
+                                              Release&& release, unsigned short* stage = nullptr, int act = R) {
     static_assert(!SPLIT || R <= 4, "one register holds the residues of at most four channels");
     const int feat = n0 + quarter * 32 + lane;
     const bool feat_ok = feat < p.n;
@@ -254,8 +262,8 @@ __device__ __forceinline__ void pair_epilogue(const PairParams& p, int n0, int t
             int one0[R], one1[R];
 #pragma unroll
             for (int c = 0; c < R; ++c) { one0[c] = acc[c][t8]; one1[c] = acc[c][t8 + 1]; }
-            if constexpr (R <= 4) reconstruct32_x2<R, RES>(one0, one1, p.plan, xv[t8], xv[t8 + 1]);
-            else reconstruct64_x2<R>(one0, one1, p.plan, xv[t8], xv[t8 + 1]);
+            if constexpr (R <= 4) reconstruct32_x2<R, RES, PREFIX>(one0, one1, p.plan, xv[t8], xv[t8 + 1], act);
+            else reconstruct64_x2<R, PREFIX>(one0, one1, p.plan, xv[t8], xv[t8 + 1], act);
         }
         const int valid_t = min(8, p.m - tok_first);   // warp-uniform
         if (!is_float) {
@@ -372,7 +380,8 @@ __device__ __forceinline__ void pair_epilogue(const PairParams& p, int n0, int t
                 uint32_t word = 0;
 #pragma unroll
                 for (int c = 0; c < R; ++c)
-                    word |= canonical_residue(acc[c][t8], p.plan.mod[c], p.plan.recip[c], p.plan.ubias[c]) << (8 * c);
+                    if (!PREFIX || c < act)      // columns of unused channels hold stale sums
+                        word |= canonical_residue(acc[c][t8], p.plan.mod[c], p.plan.recip[c], p.plan.ubias[c]) << (8 * c);
                 packed[it][t8] = word;
             }
         }

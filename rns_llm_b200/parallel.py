@@ -106,8 +106,12 @@ class PeerArena:
         return self.buffer[start:start + int(nbytes)], start
 
     def peer_addresses(self, offset: int) -> list[int]:
-        """Device address of byte ``offset`` in every OTHER rank's buffer, in rank order."""
-        return [base + offset for r, base in enumerate(self.peer_bases) if r != self.rank]
+        """Device address of byte ``offset`` in every OTHER rank's buffer, starting with the
+        next rank and wrapping round: a kernel that stores to the copies in list order then
+        aims at a different GPU on every rank at any moment, instead of all ranks writing
+        into rank 0 first."""
+        world = len(self.peer_bases)
+        return [self.peer_bases[(self.rank + step) % world] + offset for step in range(1, world)]
 
     def barrier(self) -> None:
         """All ranks' stores issued before it (on the current stream) are visible to every

@@ -33,7 +33,7 @@ def tiled_plane_offsets(m, k, channels, tile_rows):
     return tile * (tile_rows * 64) + inner
 
 
-def pair_int(backend, a, w_nk, mods, out_dtype=torch.int64, variant=0):
+def pair_int(backend, a, w_nk, mods, out_dtype=torch.int64, variant=0, active=None):
     from rns_llm_b200 import _native as N
     lib = N.load()
     m, k = a.shape
@@ -43,12 +43,15 @@ def pair_int(backend, a, w_nk, mods, out_dtype=torch.int64, variant=0):
     assert nbytes == -(-m // (2 * rows)) * 2 * rows * -(-k // 64) * 64 * len(mods)
     host = np.full(nbytes, 77, dtype=np.int8)                   # pad rows / columns hold junk
     planes = O.encode_centered(a, mods, "device")               # [R, M, K]
+    if active is not None:
+        planes[active:] = 99                                     # channels beyond the prefix: never read
     host[tiled_plane_offsets(m, k, len(mods), rows)] = np.moveaxis(planes, 0, 2)
     w_dev = torch.from_numpy(np.ascontiguousarray(w_nk)).cuda()
     prepared = backend.prepare_weight_nk(w_dev, mods)
     out = torch.full((m, w_nk.shape[0]), -7, dtype=out_dtype, device="cuda")
     backend._launch_fused(prepared=prepared, m=m, a=None, a_planes=torch.from_numpy(host).cuda(), a_packed=True,
-                          out=out, a_tile_rows=rows, variant=variant)
+                          out=out, a_tile_rows=rows, variant=variant,
+                          active=None if active is None else torch.tensor([active], dtype=torch.int32, device="cuda"))
     torch.cuda.synchronize()
     backend.check_status()
     return out.cpu().numpy()
@@ -66,6 +69,25 @@ def test_pair_kernel_exact_integers(backend, mods, m, k, n, variant):
     assert np.array_equal(pair_int(backend, a, w, mods, variant=variant), exact)
     if len(mods) == 4:
         assert np.array_equal(pair_int(backend, a, w, mods, torch.int32, variant=variant), exact.astype(np.int32))
+
+
+@pytest.mark.parametrize("mods", [C0, C4])
+@pytest.mark.parametrize("m,k,n", [(300, 512, 260), (1300, 576, 2000)])
+def test_pair_kernel_channel_prefix(backend, mods, m, k, n):
+    """d_active_channels: only the leading channels are loaded, multiplied and reconstructed.
+    Operand ranges are chosen so that the products fit the prefix's capacity; the planes of
+    the unused channels hold junk, to show that nothing reads them."""
+    rng = np.random.default_rng(m + k + len(mods))
+    for active in range(2, len(mods) + 1):
+        capacity = (int(np.prod([int(v) for v in mods[:active]], dtype=object)) - 1) // 2
+        a_max = 1 if active == 2 else (15 if active == 3 else 127)
+        w_max = min(127, capacity // (k * a_max))
+        assert w_max >= 1
+        a = rng.integers(-a_max, a_max + 1, size=(m, k)).astype(np.int8)
+        w = rng.integers(-w_max, w_max + 1, size=(n, k)).astype(np.int8)
+        exact = O.exact_matmul(a, w.T)
+        assert np.abs(exact).max() <= capacity
+        assert np.array_equal(pair_int(backend, a, w, mods, active=active), exact), active
 
 
 @pytest.mark.parametrize("mods,k", [(C0, 4096), (C4, 16384)])
@@ -208,7 +230,7 @@ def test_output_copies_and_absmax_hand_over(backend, m, k, n, mods):
 
 def test_adaptive_many_token_calls_take_the_two_cta_kernel(backend):
     """Adaptive layers with many tokens: the prefix is chosen on the device as always (metadata,
-    counters), the two-CTA kernel runs the full set, and the outputs are those of the
+    counters), the two-CTA kernel computes only that prefix, and the outputs are those of the
     non-adaptive layer bit for bit (every sufficient prefix reconstructs the same integer)."""
     from rns_llm_b200.layers import RNSLinear
     torch.manual_seed(17)
@@ -234,3 +256,29 @@ def test_adaptive_many_token_calls_take_the_two_cta_kernel(backend):
     assert int(meta["channels"]) == expect_channels and int(meta["bound"]) == expect_bound
     assert np.array_equal(y_adaptive.cpu().numpy(), res["y"])
     assert backend.stats_snapshot()["adaptive_selections"] == 1
+
+
+@pytest.mark.parametrize("mods,min_channels", [(C0, 3), (C4, 3)])
+def test_adaptive_integer_entry_with_many_tokens(backend, mods, min_channels):
+    """matmul_prepared_adaptive_fused at M >= 512: tiled planes from int8 activations, the
+    prefix chosen on the device, the two-CTA kernel computing only that prefix."""
+    rng = np.random.default_rng(77 + len(mods))
+    m, k, n = 700, 768, 520
+    w_kn = rng.integers(-127, 128, size=(k, n)).astype(np.int8)
+    adaptive = backend.prepare_weight_adaptive(torch.from_numpy(w_kn).cuda(), mods, min_channels=min_channels)
+    backend.reset_stats()
+    seen = set()
+    for a_max in (3, 40, 127):
+        a = rng.integers(-a_max, a_max + 1, size=(m, k)).astype(np.int8)
+        out, meta = backend.matmul_prepared_adaptive_fused(torch.from_numpy(a).cuda(), adaptive, return_metadata=True)
+        assert np.array_equal(out.cpu().numpy(), O.exact_matmul(a, w_kn)), a_max
+        expect = O.adaptive_channels(a, w_kn.T, mods, min_channels)
+        assert (meta["channels"], meta["bound"]) == expect
+        seen.add(expect[0])
+    assert len(seen) >= 2                                        # more than one prefix length was exercised
+    backend.check_status()
+    # the non-adaptive integer entry takes the same kernel
+    full = backend.prepare_weight(torch.from_numpy(w_kn).cuda(), mods)
+    a = rng.integers(-127, 128, size=(m, k)).astype(np.int8)
+    assert np.array_equal(backend.matmul_prepared_fused(torch.from_numpy(a).cuda(), full).cpu().numpy(),
+                          O.exact_matmul(a, w_kn))
