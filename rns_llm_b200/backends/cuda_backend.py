@@ -45,6 +45,11 @@ CenteredKernelName = Literal["auto", "scalar", "dp4a", "dp4a_safe", "cublas", "t
 # Activations with at least this many rows are encoded to planes once by a
 # separate kernel; below it every CTA encodes its own A tile inside the GEMM.
 PLANES_MIN_ROWS = 512
+# Where the two-CTA kernel covers the shape it also wins below that: from 320 rows on, and
+# from 33 rows on when the weight is large (K*N >= 2^23; measured on 768 x 2304 and
+# 4096 x 4096 / 12288 weights under graph replay).  At most 32 rows go to the one-launch kernel.
+PAIR_MIN_ROWS = 320
+PAIR_LARGE_WEIGHT = 1 << 23
 WIDE_MIN_ROWS = 128          # wide sources: fewer rows stay on the plane-level pipeline
 
 _INT_TYPES = {torch.int8: N.INT8, torch.int16: N.INT16, torch.int32: N.INT32}
@@ -698,12 +703,12 @@ class CudaRNSBackend:
                     a.data_ptr(), -1, m, prepared_weight.k, a.stride(0), 0, prepared_weight.weight_packed.data_ptr(),
                     prepared_weight.n, arr, channels, None, None, workspace.output.data_ptr(),
                     workspace.output.stride(0), N.OUT_INT64, self._stream(a.device)))
-            elif m >= PLANES_MIN_ROWS:
+            elif m >= PLANES_MIN_ROWS or self._pair_tile_rows(m, prepared_weight.k, prepared_weight.n, channels):
                 frame = self.arena.frame(a.device)
                 _, arr = self._mods(mods)
                 # tiles of 64 / 48 / 32 rows for the two-CTA kernel where it covers the call
                 # (an adaptive prefix: 4 or 5 channels), else the 128-row layout
-                tile_rows = int(self._lib.rns_pair_tile_rows(channels, prepared_weight.k))
+                tile_rows = self._pair_tile_rows(m, prepared_weight.k, prepared_weight.n, channels)
                 if _active is not None and channels > 5:
                     tile_rows = 0
                 if tile_rows:
@@ -812,8 +817,8 @@ class CudaRNSBackend:
             self._stats["encode_centered_values"] += int(a.numel())
             self._stats["fused_gemm_calls"] += 1
             tile_rows = 0
-            if m >= PLANES_MIN_ROWS and channels <= 5 and a.stride(1) == 1:
-                tile_rows = int(self._lib.rns_pair_tile_rows(channels, full.k))
+            if channels <= 5 and a.stride(1) == 1:
+                tile_rows = self._pair_tile_rows(m, full.k, full.n, channels)
             if tile_rows:
                 # many tokens: tiled planes, and the two-CTA kernel computes the chosen prefix
                 planes = frame.alloc(int(self._lib.rns_packed_planes_bytes(m, full.k, channels, tile_rows)),
@@ -956,9 +961,10 @@ class CudaRNSBackend:
             self._stats["fused_gemm_calls"] += 1
             self._stats[f"fused_gemm_channels_{channels}"] += 1
             return (out, None) if return_metadata else out
-        use_planes = m >= PLANES_MIN_ROWS
-        # Many-token calls: planes in tiles of 64 / 48 / 32 token rows for the two-CTA kernel.
-        tile_rows = int(self._lib.rns_pair_tile_rows(channels, k)) if use_planes else 0
+        # Planes in tiles of 64 / 48 / 32 token rows for the two-CTA kernel where it is the
+        # faster one; otherwise 128-row planes from 512 rows on, int8 activations below.
+        tile_rows = self._pair_tile_rows(m, k, prepared.n, channels)
+        use_planes = tile_rows != 0 or m >= PLANES_MIN_ROWS
         # Adaptive calls: the two-CTA kernel reads the prefix chosen on the device and skips
         # the other channels' planes, MMAs and residues (4 or 5 channels in the full set);
         # where it does not cover the shape the general kernel does the same from int8
@@ -1068,10 +1074,19 @@ class CudaRNSBackend:
                                bias=bias, stream=stream, a_tile_rows=tile_rows, weight_planes=True)
         return out
 
+    def _pair_tile_rows(self, m: int, k: int, n: int, channels: int) -> int:
+        """Token rows per packed tile when this call should take the two-CTA kernel, else 0."""
+        rows = int(self._lib.rns_pair_tile_rows(int(channels), int(k)))
+        if rows == 0 or m <= 32:
+            return 0
+        if m >= PAIR_MIN_ROWS or int(k) * int(n) >= PAIR_LARGE_WEIGHT:
+            return rows
+        return 0
+
     def supports_absmax_out(self, *, m: int, k: int, channels: int) -> bool:
         """True when ``linear_forward`` runs the many-token kernel for this problem, the one
         whose epilogue can report max |y| (``absmax_out``)."""
-        return m >= PLANES_MIN_ROWS and int(self._lib.rns_pair_tile_rows(int(channels), int(k))) > 0
+        return m >= PAIR_MIN_ROWS and int(self._lib.rns_pair_tile_rows(int(channels), int(k))) > 0
 
     def quantize_weight(self, weight: torch.Tensor, quant_max: int = 127
                         ) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
