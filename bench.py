@@ -312,7 +312,8 @@ def build_stack(backend, args, rank: int, world: int, device, peer_arena=None):
             shard_b = shard_tensor(bias, world, rank, groups)
             layer.append(ColumnShardedRNSLinear(shard_w, shard_b, backend=backend, moduli=mods, rank=rank,
                                                 world=world, groups=groups, reuse_buffer=True,
-                                                peer_arena=peer_arena))
+                                                peer_arena=peer_arena,
+                                                multicast=args.exchange == "multicast"))
             del weight, bias, shard_w, shard_b
         stack.append(layer)
     return stack
@@ -957,6 +958,11 @@ def _run_layer_stack(args, backend, rank, world, local_rank, device) -> None:
     stack = build_stack(backend, args, rank, world, device, peer_arena)
     exchange = ("peer stores from the GEMM epilogue into symmetric memory + a barrier per layer"
                 if peer_arena is not None else f"NCCL all-gather per layer ({arena_why})")
+    if peer_arena is not None and args.exchange == "multicast":
+        used = sum(1 for layer in stack for lin in layer if lin.multicast)
+        exchange = (f"multicast stores (multimem.st through NVSwitch) from the GEMM epilogue in {used} of "
+                    f"{sum(len(layer) for layer in stack)} linears + a barrier per layer"
+                    if used else exchange + " (no multicast mapping on this platform)")
     torch.manual_seed(4321)
     host_x = torch.randn((args.tokens, HIDDEN), dtype=torch.float16).pin_memory()
     host_y = torch.empty((args.tokens, HIDDEN), dtype=torch.float16).pin_memory()
@@ -1133,9 +1139,9 @@ def main() -> None:
     parser.add_argument("--layers", type=int, default=32)
     parser.add_argument("--tokens", type=int, default=4096)
     parser.add_argument("--no-cpu-baseline", action="store_true")
-    parser.add_argument("--exchange", default="auto", choices=["auto", "peer", "nccl"],
+    parser.add_argument("--exchange", default="auto", choices=["auto", "peer", "multicast", "nccl"],
                         help="multi-GPU output exchange: peer stores over symmetric memory when available (auto, "
-                             "peer), or the NCCL all-gather")
+                             "peer), the same as NVLink multicast stores (multicast), or the NCCL all-gather")
     parser.add_argument("--no-peak", action="store_true",
                         help="skip the torch._int_mm peak measurement (roofline.frac then uses 2 x bf16 sustained)")
     parser.add_argument("--gpu-baselines", action="store_true",

@@ -306,6 +306,12 @@ typedef struct rns_linear_args {
                                  mod moduli[c] of a weight whose source integers are wider than int8
                                  (quant_bits 12 / 16 of layers/rns_linear.py:45-46, 96-98 of the reference;
                                  its backend caches the same planes, 4 bytes per value) */
+    int32_t out_copies_multicast; /* 1: d_out_copies[0] and d_absmax_copies[0] (n_out_copies = 1) are NVLink
+                                 multicast addresses (NVLS: one mapping that covers the same slot on every
+                                 rank, this one included); the epilogue then issues ONE multimem.st per
+                                 16 bytes instead of a store per peer, and the switch replicates it.  Needs
+                                 two-byte outputs, N a multiple of 128, ldo a multiple of 8 and 16-byte
+                                 aligned bases (only the row-wide store path has a multicast form) */
 } rns_linear_args;
 
 RNS_API int rns_linear_fused(const rns_linear_args* args, rns_stream_t stream);

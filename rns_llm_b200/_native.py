@@ -69,6 +69,7 @@ class LinearArgs(C.Structure):
         ("d_absmax_copies", C.c_void_p * MAX_PEERS),
         ("d_wait_info", C.c_void_p),
         ("w_channel_stride", C.c_int64),
+        ("out_copies_multicast", C.c_int32),
     ]
 
 

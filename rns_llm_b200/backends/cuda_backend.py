@@ -47,7 +47,8 @@ CenteredKernelName = Literal["auto", "scalar", "dp4a", "dp4a_safe", "cublas", "t
 PLANES_MIN_ROWS = 512
 # Where the two-CTA kernel covers the shape it also wins below that: from 320 rows on, and
 # from 33 rows on when the weight is large (K*N >= 2^23; measured on 768 x 2304 and
-# 4096 x 4096 / 12288 weights under graph replay).  At most 32 rows go to the one-launch kernel.
+# 4096 x 4096 / 12288 weights under graph replay).  At most 32 rows go to the one-launch kernel
+# where it holds the residues of a token block in shared memory (K up to 1536 at four channels).
 PAIR_MIN_ROWS = 320
 PAIR_LARGE_WEIGHT = 1 << 23
 WIDE_MIN_ROWS = 128          # wide sources: fewer rows stay on the plane-level pipeline
@@ -605,7 +606,7 @@ class CudaRNSBackend:
                       stream: int | None = None, a_tile_rows: int = 0,
                       absmax_out: torch.Tensor | int | None = None,
                       out_copies: Sequence[int] = (), absmax_copies: Sequence[int] = (),
-                      weight_planes: bool = False) -> None:
+                      weight_planes: bool = False, copies_multicast: bool = False) -> None:
         """Fills ``rns_linear_args`` and launches.  ``a`` / ``a_planes`` are plain
         ([M,K] / [R,M,K]) unless ``a_packed``; the weight is the prepared packed
         copy unless ``plain_weight`` ([N,K] int8) is given.  Device buffers may be
@@ -663,6 +664,7 @@ class CudaRNSBackend:
         args.a_tile_rows = a_tile_rows
         args.d_absmax_out = None if absmax_out is None else ptr(absmax_out)
         args.n_out_copies = len(out_copies)
+        args.out_copies_multicast = 1 if copies_multicast else 0
         for index, address in enumerate(out_copies):
             args.d_out_copies[index] = address
         for index, address in enumerate(absmax_copies):
@@ -900,7 +902,8 @@ class CudaRNSBackend:
                        return_metadata: bool = False, out: torch.Tensor | None = None,
                        absmax_in: tuple[int, int, int] | None = None,
                        absmax_out: torch.Tensor | int | None = None,
-                       out_copies: Sequence[int] = (), absmax_copies: Sequence[int] = ()):
+                       out_copies: Sequence[int] = (), absmax_copies: Sequence[int] = (),
+                       copies_multicast: bool = False):
         """y[M,N] = dequant( quant(x)[M,K] @ Wq[N,K]^T ) in the dtype of ``x``.
 
         The whole of ``RNSLinear.forward`` after weight preparation
@@ -921,7 +924,10 @@ class CudaRNSBackend:
         ``absmax_out`` needs the many-token kernel (M >= 512, 4 to 6 channels,
         K >= 512); otherwise it raises.  ``out_copies`` (device addresses, e.g. the
         same output slot in other ranks' memory) receive the same stores as ``out``
-        from that kernel's epilogue, ``absmax_copies`` the finished absmax word."""
+        from that kernel's epilogue, ``absmax_copies`` the finished absmax word.  With
+        ``copies_multicast`` the single address in each list is an NVLink multicast address
+        that maps the slot on every rank: one ``multimem.st`` per 16 bytes, replicated by the
+        switch (two-byte outputs, N % 128 == 0, row stride % 8 == 0)."""
         if prepared.kernel != "tcgen05":
             raise ValueError("linear_forward needs a tensor-core prepared weight")
         if x.dtype not in _FLOAT_TYPES:
@@ -1018,7 +1024,8 @@ class CudaRNSBackend:
                                row_scale=scale, row_scale_stride=1 if per_row else 0,
                                col_scale=weight_scale, bias=bias, stream=stream,
                                a_tile_rows=tile_rows, absmax_out=absmax_out,
-                               out_copies=out_copies, absmax_copies=absmax_copies)
+                               out_copies=out_copies, absmax_copies=absmax_copies,
+                               copies_multicast=copies_multicast)
         if return_metadata:
             return out, (AdaptiveMetadata(meta) if meta is not None else None)
         return out
@@ -1077,8 +1084,8 @@ class CudaRNSBackend:
     def _pair_tile_rows(self, m: int, k: int, n: int, channels: int) -> int:
         """Token rows per packed tile when this call should take the two-CTA kernel, else 0."""
         rows = int(self._lib.rns_pair_tile_rows(int(channels), int(k)))
-        if rows == 0 or m <= 32:
-            return 0
+        if rows == 0 or self._lib.rns_linear_small_supported(int(m), int(k), int(channels)):
+            return 0          # not covered, or few tokens that the one-launch kernel takes
         if m >= PAIR_MIN_ROWS or int(k) * int(n) >= PAIR_LARGE_WEIGHT:
             return rows
         return 0

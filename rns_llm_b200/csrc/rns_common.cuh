@@ -177,6 +177,13 @@ RNS_HD uint32_t canonical_residue(int v, int m, int recip, uint32_t ubias) {
     return r2 < r ? r2 : r;                                             // r >= m: r - m, else r
 }
 
+// The same without the conditional subtraction: a residue in [0, 2m), which still fits a byte
+// when m <= 127.
+RNS_HD uint32_t nonneg_residue(int v, int m, int recip, uint32_t ubias) {
+    const uint32_t u = (uint32_t)v + ubias;
+    return u - mul_hi_u32(u, (uint32_t)recip) * (uint32_t)m;
+}
+
 // t -> representative of t mod m with |result| <= m/2 (t integral, |t| < 2^22).
 RNS_HD float centre_mod(float t, float m, float rcp) {
     const float q = add_rn(fma_rn(t, rcp, kMagic), -kMagic);

@@ -271,7 +271,10 @@ rns_gemm_pair_raw_kernel(const __grid_constant__ PairParams p) {
                 __threadfence();
                 if (atomicAdd(p.absmax_out + 1, 1u) == gridDim.x - 1) {
                     const uint32_t final_word = atomicMax(p.absmax_out, 0u);
-                    for (int g = 0; COPIES && g < p.n_copies; ++g) *p.absmax_copies[g] = final_word;
+                    for (int g = 0; COPIES && g < p.n_copies; ++g) {
+                        if (p.copies_mc) multimem_store_u32(p.absmax_copies[g], final_word);
+                        else *p.absmax_copies[g] = final_word;
+                    }
                 }
             }
         }

@@ -367,6 +367,15 @@ int launch_pair_gemm(const rns_linear_args* a, const Plan& plan, cudaStream_t st
     pp.col_scale = a->d_col_scale; pp.bias = a->d_bias;
     pp.absmax_out = a->d_absmax_out;
     pp.n_copies = a->n_out_copies;
+    pp.copies_mc = a->out_copies_multicast != 0 ? 1 : 0;
+    if (pp.copies_mc) {
+        // only the row-wide store path has a multicast form: every tile must take it
+        const bool two_byte = a->out_type == RNS_OUT_F16 || a->out_type == RNS_OUT_BF16;
+        if (a->variant == 3 || a->n_out_copies != 1 || !two_byte || a->n % 128 != 0 || a->ldo % 8 != 0 ||
+            (reinterpret_cast<uintptr_t>(a->d_out) & 15) || (reinterpret_cast<uintptr_t>(a->d_out_copies[0]) & 15))
+            return fail(RNS_ERR_INVALID_ARGUMENT, "multicast output copies need variant 0/4, one copy address, two-byte "
+                                                  "outputs, N %% 128 == 0, ldo %% 8 == 0 and 16-byte aligned bases");
+    }
     for (int g = 0; g < a->n_out_copies && g < RNS_MAX_PEERS; ++g) {
         pp.out_copies[g] = a->d_out_copies[g];
         pp.absmax_copies[g] = a->d_absmax_copies[g];

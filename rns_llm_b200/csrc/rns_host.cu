@@ -173,6 +173,12 @@ int rns_host_reconstruct(const int32_t* sums, int64_t count, const int32_t* modu
                     return rns::fail(RNS_ERR_INVALID_ARGUMENT, "canonical residue of %d mod %d is %u, expected %lld",
                                      acc[c], plan.mod[c], r, expect);
                 res[c] = (int)r;
+                // the lighter form the epilogue uses when every modulus is below 128
+                const uint32_t loose = rns::nonneg_residue(acc[c], plan.mod[c], plan.recip[c], plan.ubias[c]);
+                if (in_range && (loose >= 2u * (uint32_t)plan.mod[c] || (long long)(loose % (uint32_t)plan.mod[c]) != expect))
+                    return rns::fail(RNS_ERR_INVALID_ARGUMENT, "non-negative residue of %d mod %d is %u", acc[c],
+                                     plan.mod[c], loose);
+                if (plan.encode_fast) res[c] = (int)loose;
             }
             if (in_range && rns::reconstruct<rns::kMaxCh>(res, plan, active) != wide)
                 return rns::fail(RNS_ERR_INVALID_ARGUMENT, "reconstruction from canonical residues disagrees at %lld",

@@ -51,6 +51,7 @@ struct PairParams {
     // buffers of the other ranks (peer memory, plain stores), and the finished absmax word
     // into theirs.  n_copies = 0: p.out only.
     int32_t n_copies;
+    int32_t copies_mc;         // the copy addresses are multicast addresses: multimem.st instead of plain stores
     void* out_copies[RNS_MAX_PEERS];
     uint32_t* absmax_copies[RNS_MAX_PEERS];
     const int32_t* active;     // NULL, or device int: only the first *active channels are computed (adaptive prefix)
@@ -103,7 +104,7 @@ __device__ __forceinline__ F2 add2(F2 a, F2 b) {
 }
 
 // Centred mixed-radix digits of two outputs (all R channels active).  RES: a0 / a1 hold
-// residues in [0, m) already (canonical_residue) instead of int32 channel sums.
+// residues in [0, 2m) already (canonical_residue / nonneg_residue) instead of int32 channel sums.
 // PREFIX: only the first `act` channels carry the value (adaptive prefix); the digits of the
 // others are zero.  Without PREFIX `act` is ignored and all R channels are used.
 template <int R, bool RES = false, bool PREFIX = false>
@@ -331,8 +332,11 @@ __device__ __forceinline__ void pair_epilogue(const PairParams& p, int n0, int t
             if (t < valid_t) {
                 const int64_t o = (int64_t)(tok_first + t) * p.ldo + n0 + (lane & 15) * 8;
                 *reinterpret_cast<uint4*>(out16 + o) = v;
-                for (int g = 0; g < p.n_copies; ++g)
-                    *reinterpret_cast<uint4*>(static_cast<unsigned short*>(p.out_copies[g]) + o) = v;
+                for (int g = 0; g < p.n_copies; ++g) {
+                    unsigned short* dst = static_cast<unsigned short*>(p.out_copies[g]) + o;
+                    if (p.copies_mc) multimem_store16(dst, v);      // one store, every rank of the multicast group
+                    else *reinterpret_cast<uint4*>(dst) = v;
+                }
             }
             return;
         }
@@ -370,19 +374,34 @@ __device__ __forceinline__ void pair_epilogue(const PairParams& p, int n0, int t
     if constexpr (SPLIT) {
         // Phase 1.  One buffer: the other warps of the scheduler cover the load latency.
         uint32_t packed[kIters][8];
+        // Every modulus below 128 (the int8 configurations): the Barrett step's result in
+        // [0, 2m) already fits its byte, and the recurrence of phase 2 takes it as it is.
+        const bool byte_fits = p.plan.encode_fast != 0;
 #pragma unroll
         for (int it = 0; it < kIters; ++it) {
             int acc[R][8];
             load(col0 + it * 8, acc);
             tmem_ld_wait();
+            if (byte_fits) {
 #pragma unroll
-            for (int t8 = 0; t8 < 8; ++t8) {
-                uint32_t word = 0;
+                for (int t8 = 0; t8 < 8; ++t8) {
+                    uint32_t word = 0;
 #pragma unroll
-                for (int c = 0; c < R; ++c)
-                    if (!PREFIX || c < act)      // columns of unused channels hold stale sums
-                        word |= canonical_residue(acc[c][t8], p.plan.mod[c], p.plan.recip[c], p.plan.ubias[c]) << (8 * c);
-                packed[it][t8] = word;
+                    for (int c = 0; c < R; ++c)
+                        if (!PREFIX || c < act)      // columns of unused channels hold stale sums
+                            word |= nonneg_residue(acc[c][t8], p.plan.mod[c], p.plan.recip[c], p.plan.ubias[c]) << (8 * c);
+                    packed[it][t8] = word;
+                }
+            } else {
+#pragma unroll
+                for (int t8 = 0; t8 < 8; ++t8) {
+                    uint32_t word = 0;
+#pragma unroll
+                    for (int c = 0; c < R; ++c)
+                        if (!PREFIX || c < act)
+                            word |= canonical_residue(acc[c][t8], p.plan.mod[c], p.plan.recip[c], p.plan.ubias[c]) << (8 * c);
+                    packed[it][t8] = word;
+                }
             }
         }
         release();

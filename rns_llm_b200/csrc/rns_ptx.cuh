@@ -294,4 +294,16 @@ __device__ __forceinline__ void umma_i8_ts(uint32_t d_tmem, uint32_t a_tmem, uin
         : "memory");
 }
 
+// Stores through an NVLink multicast address (NVLS): the switch delivers the bytes to the same
+// offset of every GPU bound to the multicast object.  16 bytes, and one 32-bit word.
+__device__ __forceinline__ void multimem_store16(void* mc_addr, uint4 v) {
+    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};"
+                 ::"l"(mc_addr), "f"(__uint_as_float(v.x)), "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)),
+                   "f"(__uint_as_float(v.w))
+                 : "memory");
+}
+__device__ __forceinline__ void multimem_store_u32(void* mc_addr, uint32_t v) {
+    asm volatile("multimem.st.relaxed.sys.global.u32 [%0], %1;" ::"l"(mc_addr), "r"(v) : "memory");
+}
+
 }  // namespace rns

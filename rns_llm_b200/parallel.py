@@ -94,6 +94,9 @@ class PeerArena:
         self.peer_bases = [int(p) for p in self.handle.buffer_ptrs]
         if len(self.peer_bases) != self.world or self.peer_bases[self.rank] != self.buffer.data_ptr():
             raise RuntimeError("symmetric memory returned an unexpected set of peer pointers")
+        # NVLink multicast mapping of the same buffer (NVLS), 0 where the platform has none: a
+        # store to it lands at the same offset on every rank.
+        self.multicast_base = int(getattr(self.handle, "multicast_ptr", 0) or 0)
         self._offset = 0
 
     def alloc(self, nbytes: int) -> tuple[torch.Tensor, int]:
@@ -151,7 +154,10 @@ class ColumnShardedRNSLinear(nn.Module):
     Exchange: one NCCL all-gather after the GEMM, or - with ``peer_arena`` - none: the GEMM
     epilogue stores each tile into every rank's buffer while it runs and the ranks meet at
     a barrier (many-token calls with a per-tensor scale; other calls fall back to the
-    all-gather).  A layer with a peer arena owns its output buffer (as ``reuse_buffer``).
+    all-gather).  ``multicast=True`` makes those stores multicast stores through NVSwitch
+    (one per 16 bytes instead of one per peer) where the arena has a multicast mapping, the
+    outputs are two bytes wide and N/G is a multiple of 128.  A layer with a peer arena owns
+    its output buffer (as ``reuse_buffer``).
 
     Ownership of the result: by default every call returns a freshly allocated
     tensor, as the reference's ``RNSLinear`` does.  ``out=`` writes into the
@@ -165,10 +171,13 @@ class ColumnShardedRNSLinear(nn.Module):
     def __init__(self, weight_shard: torch.Tensor, bias_shard: torch.Tensor | None, *, backend,
                  moduli: Iterable[int], rank: int, world: int, group=None, groups: int = 1,
                  activation_scale: str = "tensor", reuse_buffer: bool = False,
-                 peer_arena: "PeerArena | None" = None) -> None:
+                 peer_arena: "PeerArena | None" = None, multicast: bool = False) -> None:
         super().__init__()
         self.reuse_buffer = bool(reuse_buffer) or peer_arena is not None
         self.peer_arena = peer_arena
+        # One multimem.st through the arena's NVLink multicast mapping instead of a store per
+        # peer (where the platform offers the mapping and the shard's shape allows it).
+        self.multicast = bool(multicast) and peer_arena is not None and peer_arena.multicast_base != 0
         self._peer_blocks: dict[tuple[int, torch.dtype], tuple[torch.Tensor, int]] = {}
         if weight_shard.ndim != 2:
             raise ValueError("weight_shard must be [N/world, K]")
@@ -244,15 +253,22 @@ class ColumnShardedRNSLinear(nn.Module):
         word = buf[self.rank, count:].data_ptr() if report else None
         out_copies: list[int] = []
         absmax_copies: list[int] = []
+        use_mc = False
         if use_peers:
             size = buf.element_size()
             block = (count + ABSMAX_PAD) * size
             mine = offset + self.rank * block                      # my slot, at the same offset on every rank
-            out_copies = self.peer_arena.peer_addresses(mine)
-            absmax_copies = self.peer_arena.peer_addresses(mine + count * size)
+            use_mc = (self.multicast and size == 2 and self.local_features % 128 == 0 and mine % 16 == 0)
+            if use_mc:
+                out_copies = [self.peer_arena.multicast_base + mine]
+                absmax_copies = [self.peer_arena.multicast_base + mine + count * size]
+            else:
+                out_copies = self.peer_arena.peer_addresses(mine)
+                absmax_copies = self.peer_arena.peer_addresses(mine + count * size)
         self.backend.linear_forward(flat, self.prepared, self.weight_scale, self.bias,
                                     per_row=self.per_row, out=local, absmax_in=absmax_in, absmax_out=word,
-                                    out_copies=out_copies, absmax_copies=absmax_copies)
+                                    out_copies=out_copies, absmax_copies=absmax_copies,
+                                    **({"copies_multicast": True} if use_mc else {}))
         if not gather:
             return local
         if use_peers:

@@ -1,6 +1,7 @@
 """Two ranks on two GPUs (skipped with fewer): a chain of column-sharded RNS layers whose
-outputs are exchanged (a) by the NCCL all-gather and (b) by peer stores from the GEMM
-epilogue into symmetric memory plus a barrier.  Both must reproduce, bit for bit, the
+outputs are exchanged (a) by the NCCL all-gather, (b) by peer stores from the GEMM
+epilogue into symmetric memory plus a barrier and (c) by the same stores as NVLink multicast
+stores, where the platform maps a multicast address.  All must reproduce, bit for bit, the
 unsharded layers run on one GPU, including the absmax words that travel with the blocks."""
 import os
 import socket
@@ -39,11 +40,14 @@ def _worker(rank: int, world: int, port: int, results):
         b1 = (torch.randn(1536, device=device) * 0.1).half()
         w2 = (torch.randn(1024, 1536, device=device) * 0.04).half()
 
-        def chain(arena):
+        def chain(arena, multicast=False):
             l1 = ColumnShardedRNSLinear(shard_tensor(w1, world, rank), shard_tensor(b1, world, rank),
-                                        backend=backend, moduli=C0, rank=rank, world=world, peer_arena=arena)
+                                        backend=backend, moduli=C0, rank=rank, world=world, peer_arena=arena,
+                                        multicast=multicast)
             l2 = ColumnShardedRNSLinear(shard_tensor(w2, world, rank), None, backend=backend, moduli=C0, rank=rank,
-                                        world=world, peer_arena=arena)
+                                        world=world, peer_arena=arena, multicast=multicast)
+            if multicast and not (l1.multicast and l2.multicast):
+                return None
             y1 = l1(x)
             carried = isinstance(y1, GatheredActivation) and y1.absmax_words is not None
             y2 = l2(y1)
@@ -72,9 +76,22 @@ def _worker(rank: int, world: int, port: int, results):
                 checks["peer layer 1"] = checks.get("peer layer 1", True) and torch.equal(p1, full1)
                 checks["peer layer 2"] = checks.get("peer layer 2", True) and torch.equal(p2, full2)
                 checks["peer absmax words"] = checks.get("peer absmax words", True) and bool(carried_peer)
+            # the same exchange as multicast stores through NVSwitch, where the platform maps one
+            mc = torch.tensor([1 if arena.multicast_base else 0], device=device)
+            dist.all_reduce(mc, op=dist.ReduceOp.MIN)
+            if int(mc.item()):
+                for _ in range(3):
+                    got = chain(arena, multicast=True)
+                    checks["multicast layer 1"] = checks.get("multicast layer 1", True) and torch.equal(got[0], full1)
+                    checks["multicast layer 2"] = checks.get("multicast layer 2", True) and torch.equal(got[1], full2)
+                    checks["multicast absmax words"] = checks.get("multicast absmax words", True) and bool(got[2])
+                peer_note += " multicast exchange checked"
+            else:
+                peer_note += " no multicast mapping: multicast exchange not run"
         backend.check_status()
         failed = [name for name, good in checks.items() if not good]
         results[rank] = (not failed, f"failed: {failed}; {peer_note}")
+        print(f"rank {rank}: {sorted(checks)}; {peer_note}", flush=True)
     finally:
         dist.destroy_process_group()
 
