@@ -286,10 +286,14 @@ def make_peer_arena(args, world: int, device):
         arena = PeerArena(nbytes, device)
     except Exception as exc:            # not available here: every rank must fall back together
         why = f"{type(exc).__name__}: {exc}"
-    flag = torch.tensor([1 if arena is not None else 0], dtype=torch.int32, device=device)
+    # [arena exists, it has an NVLink multicast mapping]: the minimum over ranks decides for all
+    flag = torch.tensor([1 if arena is not None else 0,
+                         1 if arena is not None and arena.multicast_base != 0 else 0],
+                        dtype=torch.int32, device=device)
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
-    if int(flag.item()) == 0:
+    if int(flag[0].item()) == 0:
         return None, why or "symmetric memory failed on another rank"
+    arena.multicast_everywhere = bool(int(flag[1].item()))
     return arena, ""
 
 
@@ -313,7 +317,8 @@ def build_stack(backend, args, rank: int, world: int, device, peer_arena=None):
             layer.append(ColumnShardedRNSLinear(shard_w, shard_b, backend=backend, moduli=mods, rank=rank,
                                                 world=world, groups=groups, reuse_buffer=True,
                                                 peer_arena=peer_arena,
-                                                multicast=args.exchange == "multicast"))
+                                                multicast=(args.exchange in ("auto", "multicast") and
+                                                           getattr(peer_arena, "multicast_everywhere", False))))
             del weight, bias, shard_w, shard_b
         stack.append(layer)
     return stack
@@ -958,7 +963,7 @@ def _run_layer_stack(args, backend, rank, world, local_rank, device) -> None:
     stack = build_stack(backend, args, rank, world, device, peer_arena)
     exchange = ("peer stores from the GEMM epilogue into symmetric memory + a barrier per layer"
                 if peer_arena is not None else f"NCCL all-gather per layer ({arena_why})")
-    if peer_arena is not None and args.exchange == "multicast":
+    if peer_arena is not None and args.exchange in ("auto", "multicast"):
         used = sum(1 for layer in stack for lin in layer if lin.multicast)
         exchange = (f"multicast stores (multimem.st through NVSwitch) from the GEMM epilogue in {used} of "
                     f"{sum(len(layer) for layer in stack)} linears + a barrier per layer"
@@ -1140,8 +1145,9 @@ def main() -> None:
     parser.add_argument("--tokens", type=int, default=4096)
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--exchange", default="auto", choices=["auto", "peer", "multicast", "nccl"],
-                        help="multi-GPU output exchange: peer stores over symmetric memory when available (auto, "
-                             "peer), the same as NVLink multicast stores (multicast), or the NCCL all-gather")
+                        help="multi-GPU output exchange from the GEMM epilogue over symmetric memory: NVLink "
+                             "multicast stores where every rank has the mapping, else a store per peer (auto, "
+                             "multicast); a store per peer (peer); or the NCCL all-gather after the GEMM (nccl)")
     parser.add_argument("--no-peak", action="store_true",
                         help="skip the torch._int_mm peak measurement (roofline.frac then uses 2 x bf16 sustained)")
     parser.add_argument("--gpu-baselines", action="store_true",
