@@ -312,6 +312,15 @@ typedef struct rns_linear_args {
                                  16 bytes instead of a store per peer, and the switch replicates it.  Needs
                                  two-byte outputs, N a multiple of 128, ldo a multiple of 8 and 16-byte
                                  aligned bases (only the row-wide store path has a multicast form) */
+    int32_t groups;           /* 0: an ordinary call.  >= 1 (variant 0 / 4, tiled planes, one weight matrix, no
+                                 prefix, no copies): that many independent m x k x n problems in one launch -
+                                 the grouped multi-head QK^T / AV products the reference lists as open work
+                                 (docs/OPTIMIZATIONS_V04.md:49; benchmarks/benchmark_attention.py:107-113
+                                 times one head).  d_a_planes: the tiled planes of the [groups * m, k] matrix
+                                 (m a multiple of 2 * a_tile_rows); d_w: the packed [groups * n, k] matrix
+                                 (n a multiple of 8; problem g multiplies rows g * n .. g * n + n - 1);
+                                 d_out: [groups][m][ldo]; scales and bias are shared by the problems.
+                                 K may be as small as 64 here */
 } rns_linear_args;
 
 RNS_API int rns_linear_fused(const rns_linear_args* args, rns_stream_t stream);

@@ -70,6 +70,7 @@ class LinearArgs(C.Structure):
         ("d_wait_info", C.c_void_p),
         ("w_channel_stride", C.c_int64),
         ("out_copies_multicast", C.c_int32),
+        ("groups", C.c_int32),
     ]
 
 

@@ -606,7 +606,8 @@ class CudaRNSBackend:
                       stream: int | None = None, a_tile_rows: int = 0,
                       absmax_out: torch.Tensor | int | None = None,
                       out_copies: Sequence[int] = (), absmax_copies: Sequence[int] = (),
-                      weight_planes: bool = False, copies_multicast: bool = False) -> None:
+                      weight_planes: bool = False, copies_multicast: bool = False, groups: int = 0,
+                      packed_weight: torch.Tensor | None = None) -> None:
         """Fills ``rns_linear_args`` and launches.  ``a`` / ``a_planes`` are plain
         ([M,K] / [R,M,K]) unless ``a_packed``; the weight is the prepared packed
         copy unless ``plain_weight`` ([N,K] int8) is given.  Device buffers may be
@@ -627,7 +628,13 @@ class CudaRNSBackend:
             args.d_a = ptr(a)
             args.lda = prepared.k if a_packed else a.stride(0)
         args.a_packed = 1 if a_packed else 0
-        if weight_planes:
+        args.groups = int(groups)
+        if packed_weight is not None:
+            args.d_w = packed_weight.data_ptr()
+            args.ldw = prepared.k
+            args.w_packed = 1
+            device = packed_weight.device
+        elif weight_planes:
             args.d_w = prepared.weight_planes_packed.data_ptr()
             args.ldw = prepared.k
             args.w_packed = 1
@@ -1029,6 +1036,60 @@ class CudaRNSBackend:
         if return_metadata:
             return out, (AdaptiveMetadata(meta) if meta is not None else None)
         return out
+
+    def matmul_grouped(self, a: torch.Tensor, b_nk: torch.Tensor, moduli: Iterable[int], *,
+                       out_dtype: torch.dtype = torch.int64) -> torch.Tensor:
+        """Exact integer products of ``G`` independent problems in ONE launch:
+        ``out[g] = a[g] @ b_nk[g].T`` for int8 ``a`` [G,M,K] and ``b_nk`` [G,N,K] (both
+        operands are activations: nothing is cached).  The grouped multi-head products of
+        attention - scores ``Q K^T`` (``a`` = Q [B*H,T,d], ``b_nk`` = K [B*H,T,d]) and
+        ``P V`` (``a`` = P [B*H,T,T], ``b_nk`` = V^T [B*H,d,T]) - which the reference lists as
+        open work (docs/OPTIMIZATIONS_V04.md:49) and times for one head through the plane
+        pipeline (benchmarks/benchmark_attention.py:107-113).  One launch encodes the tiled
+        residue planes of all G*M rows, one packs all G*N weight rows, one runs the two-CTA
+        kernel over every (problem, tile).  4 to 6 moduli, K % 16 == 0, N % 8 == 0."""
+        if a.ndim != 3 or b_nk.ndim != 3 or a.dtype != torch.int8 or b_nk.dtype != torch.int8:
+            raise ValueError("matmul_grouped takes int8 a [G,M,K] and b_nk [G,N,K]")
+        if not a.is_cuda or a.device != b_nk.device:
+            raise ValueError("a and b_nk must be CUDA tensors on one device")
+        groups, m, k = (int(v) for v in a.shape)
+        if int(b_nk.shape[0]) != groups or int(b_nk.shape[2]) != k:
+            raise ValueError("group counts or K dimensions do not match")
+        n = int(b_nk.shape[1])
+        mods, arr = self._mods(moduli)
+        channels = len(mods)
+        if channels not in (4, 5, 6) or k % 16 != 0 or k < 64 or n % 8 != 0:
+            raise ValueError("matmul_grouped needs 4 to 6 moduli, K % 16 == 0, K >= 64 and N % 8 == 0")
+        if not self.tensor_core_compatible(k=k, moduli=mods):
+            raise ValueError("moduli / K are outside the tensor-core kernel's range")
+        if out_dtype not in (torch.int64, torch.int32):
+            raise ValueError("out_dtype must be torch.int64 or torch.int32")
+        token_tile = {4: 128, 5: 96, 6: 64}[channels]
+        m_pad = -(-m // token_tile) * token_tile
+        a = a.contiguous()
+        if m_pad != m:
+            a = torch.nn.functional.pad(a, (0, 0, 0, m_pad - m))            # whole token tiles per problem
+        b_nk = b_nk.contiguous()
+        device = a.device
+        out = torch.empty((groups, m_pad, n), dtype=out_dtype, device=device)
+        prepared = PreparedRNSWeight(backend=self, moduli=mods, k=k, n=n, kernel="tcgen05")
+        with torch.cuda.device(device):
+            stream = self._stream(device)
+            frame = self.arena.frame(device)
+            tile_rows = token_tile // 2
+            planes = frame.alloc(int(self._lib.rns_packed_planes_bytes(groups * m_pad, k, channels, tile_rows)),
+                                 torch.int8)
+            N.check(self._lib.rns_encode_planes_tiled(a.data_ptr(), groups * m_pad, k, k, arr, channels,
+                                                      tile_rows, planes.data_ptr(), stream))
+            packed = frame.alloc(int(self._lib.rns_packed_weight_bytes(groups * n, k)), torch.int8)
+            N.check(self._lib.rns_pack_weight(b_nk.data_ptr(), groups * n, k, k, packed.data_ptr(), stream))
+            self._stats["encode_centered_calls"] += 1
+            self._stats["encode_centered_values"] += int(a.numel())
+            self._stats["fused_gemm_calls"] += 1
+            self._stats[f"fused_gemm_channels_{channels}"] += 1
+            self._launch_fused(prepared=prepared, m=m_pad, a=None, a_planes=planes, a_packed=True, out=out[0],
+                               a_tile_rows=tile_rows, groups=groups, packed_weight=packed, stream=stream)
+        return out[:, :m] if m_pad != m else out
 
     def supports_wide_forward(self, prepared: PreparedRNSWeight, m: int) -> bool:
         """True when ``linear_forward_wide`` serves this call: the prepared weight carries

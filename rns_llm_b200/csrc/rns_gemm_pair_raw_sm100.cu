@@ -63,7 +63,7 @@ rns_gemm_pair_raw_kernel(const __grid_constant__ PairParams p) {
 
     const uint32_t rank = cluster_cta_rank();
     const int cluster = (int)(blockIdx.x >> 1), clusters = (int)(gridDim.x >> 1);
-    const int tiles = p.n_ftiles * p.n_ttiles;
+    const int tiles = p.n_ftiles * p.n_ttiles * (p.groups > 1 ? p.groups : 1);
     const int nst = p.kblocks;                                 // one K block of 64 bytes per stage
     const int my_tiles = (tiles - cluster + clusters - 1) / clusters;
 
@@ -100,11 +100,12 @@ rns_gemm_pair_raw_kernel(const __grid_constant__ PairParams p) {
             bool ok = true;
             for (int tile = cluster; tile < tiles && ok; tile += clusters) {
                 const PairTile t = pair_tile<TOK>(p, tile, rank);
-                const int8_t* pl_src = p.planes + ((int64_t)(t.tt * 2 + (int)rank) * p.kblocks) * (int64_t)kPlStage;
+                const int8_t* pl_src = p.planes + ((int64_t)((t.grp * p.n_ttiles + t.tt) * 2 + (int)rank) * p.kblocks) * (int64_t)kPlStage;
                 // Feature rows past the padded weight (possible only in the last tile's
                 // second half) are not loaded; their outputs are never stored.
-                const bool w_rows = t.n0 < p.w_npad;
-                const int8_t* w_src = p.w + (int64_t)t.n0 * kPackK;
+                const int64_t w_row0 = (int64_t)t.grp * p.w_group_rows + t.n0;    // first weight row of this CTA
+                const bool w_rows = w_row0 < p.w_npad;
+                const int8_t* w_src = p.w + w_row0 * kPackK;
                 const int64_t kb_stride = p.w_npad * kPackK;
                 const uint32_t pl_bytes = PREFIX ? (uint32_t)act * kPlTile : kPlStage;   // leading channels only
                 const uint32_t bytes = pl_bytes + (w_rows ? kWStage : 0u);
@@ -233,7 +234,8 @@ rns_gemm_pair_raw_kernel(const __grid_constant__ PairParams p) {
             pair_epilogue<R, TOK, COPIES, (R <= 4 && RNS_PAIR_SPLIT_EPILOGUE != 0), PREFIX>(
                 p, t.n0, t.tok0, quarter, part, lane, lane_base, is_float, rs_all, biggest, release,
                 COPIES ? reinterpret_cast<unsigned short*>(smem_dyn + (tiles_base - smem_addr(smem_dyn)) +
-                                                           (size_t)S * (kWStage + kPlStage)) : nullptr, act);
+                                                           (size_t)S * (kWStage + kPlStage)) : nullptr, act,
+                (int64_t)t.grp * p.out_group_stride);
         }
         if (p.absmax_out != nullptr && is_float) {
 #pragma unroll

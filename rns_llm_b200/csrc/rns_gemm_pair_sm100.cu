@@ -328,6 +328,14 @@ static int launch_pair(const PairParams& pp, int pairs, cudaStream_t st) {
 
 int pair_gemm_token_tile(int channels) { return pair_raw_token_tile(channels); }
 
+// Grouped calls: the plain raw-weight form only, whole token tiles, weight rows in eights.
+static bool pair_groups_ok(const rns_linear_args* a) {
+    if (a->groups <= 0) return a->groups == 0;
+    return a->variant != 3 && a->w_channel_stride == 0 && a->n_out_copies == 0 && a->d_active_channels == nullptr &&
+           a->d_absmax_out == nullptr && a->m % pair_gemm_token_tile(a->channels) == 0 && a->n % 8 == 0 &&
+           (int64_t)a->groups * a->m <= INT32_MAX && (int64_t)a->groups * a->n <= INT32_MAX;
+}
+
 // 4, 5 or 6 channels (the weight-encoding kernel, variant 3, and output copies: 4 or 5).
 bool pair_gemm_supported(const rns_linear_args* a) {
     const bool channels_ok = a->channels == 4 || a->channels == 5 ||
@@ -338,7 +346,8 @@ bool pair_gemm_supported(const rns_linear_args* a) {
     return a->d_a_planes != nullptr && a->a_packed != 0 && a->w_packed != 0 && prefix_ok &&
            a->exact_residues == 0 && channels_ok && (a->w_channel_stride == 0 || a->variant != 3) &&
            a->w_channel_stride >= 0 && a->w_channel_stride % 16 == 0 &&
-           a->a_tile_rows == pair_gemm_token_tile(a->channels) / 2 && a->k >= 8 * kPackK && a->k % 16 == 0;
+           a->a_tile_rows == pair_gemm_token_tile(a->channels) / 2 && a->k % 16 == 0 &&
+           a->k >= (a->groups >= 1 ? kPackK : 8 * kPackK) && pair_groups_ok(a);
 }
 
 int launch_pair_gemm(const rns_linear_args* a, const Plan& plan, cudaStream_t st) {
@@ -351,8 +360,12 @@ int launch_pair_gemm(const rns_linear_args* a, const Plan& plan, cudaStream_t st
     pp.kblocks = (a->k + kPackK - 1) / kPackK;
     pp.planes = a->d_a_planes;
     pp.w = a->d_w;
-    pp.w_npad = round_up_i64(a->n, kPackNPad);
+    const int groups = a->groups > 1 ? a->groups : 1;
+    pp.w_npad = round_up_i64((int64_t)groups * a->n, kPackNPad);
     pp.w_channel_stride = a->w_channel_stride;
+    pp.groups = groups;
+    pp.w_group_rows = a->n;
+    pp.out_group_stride = (int64_t)a->m * a->ldo;
     pp.n_ftiles = (a->n + 255) / 256;
     pp.n_ttiles = (a->m + tok - 1) / tok;
     // Band: as many feature tiles as keep the band's weight bytes around 32 MB (a quarter
@@ -382,7 +395,7 @@ int launch_pair_gemm(const rns_linear_args* a, const Plan& plan, cudaStream_t st
     }
     pp.active = a->d_active_channels;
     pp.status = a->d_status; pp.wait_info = a->d_wait_info;
-    const int64_t pairs = (int64_t)pp.n_ftiles * pp.n_ttiles;
+    const int64_t pairs = (int64_t)pp.n_ftiles * pp.n_ttiles * groups;
     if (pairs > (1 << 30)) return fail(RNS_ERR_UNSUPPORTED, "too many output tiles");
     if (a->d_absmax_out != nullptr) RNS_CUDA_OK(cudaMemsetAsync(a->d_absmax_out, 0, 2 * sizeof(uint32_t), st));
     // Variant 3 asks for the kernel that encodes canonical weight residues per channel;

@@ -987,7 +987,8 @@ int rns_linear_fused(const rns_linear_args* a, rns_stream_t stream) {
         if (!pair_gemm_supported(a))
             return fail(RNS_ERR_UNSUPPORTED, "variants 3 and 4 need packed planes in tiles of 64 (4 channels), 48 (5) or 32 "
                                              "(6, variant 4 without output copies) rows, packed weights, all channels active "
-                                             "and K >= 512; per-channel weights (w_channel_stride) are read by variant 4 only");
+                                             "and K >= 512 (grouped calls: K >= 64, whole token tiles, N %% 8 == 0); "
+                                             "per-channel weights (w_channel_stride) are read by variant 4 only");
         if (is_float && a->d_absmax_out != nullptr && a->row_scale_stride != 0)
             return fail(RNS_ERR_INVALID_ARGUMENT, "d_absmax_out serves per-tensor scales");
         if (a->n_out_copies < 0 || a->n_out_copies > RNS_MAX_PEERS)
@@ -999,9 +1000,9 @@ int rns_linear_fused(const rns_linear_args* a, rns_stream_t stream) {
                 return fail(RNS_ERR_INVALID_ARGUMENT, "d_out_copies / d_absmax_copies hold a NULL pointer");
         return launch_pair_gemm(a, pl, reinterpret_cast<cudaStream_t>(stream));
     }
-    if (a->d_absmax_out != nullptr || a->n_out_copies != 0 || a->w_channel_stride != 0)
-        return fail(RNS_ERR_UNSUPPORTED, "d_absmax_out, output copies and per-channel weights are served by the "
-                                         "two-CTA kernels (tiled planes) only");
+    if (a->d_absmax_out != nullptr || a->n_out_copies != 0 || a->w_channel_stride != 0 || a->groups != 0)
+        return fail(RNS_ERR_UNSUPPORTED, "d_absmax_out, output copies, per-channel weights and grouped calls are served by "
+                                         "the two-CTA kernels (tiled planes) only");
     if (a->variant == 2 && !tmem_gemm_supported(a))
         return fail(RNS_ERR_UNSUPPORTED, "variant 2 needs packed planes, packed weights and 2..5 channels");
     if (a->variant == 2)

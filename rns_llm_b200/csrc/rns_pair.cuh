@@ -35,8 +35,15 @@ struct PairParams {
     int64_t w_npad;
     int64_t w_channel_stride;  // 0: one matrix (the int8 weight) for every channel; else bytes between the
                                // packed residue planes of the weight, one per channel
-    int32_t n_ftiles;          // tiles of 256 features
-    int32_t n_ttiles;          // tiles of TOK tokens
+    int32_t n_ftiles;          // tiles of 256 features (per problem of a grouped call)
+    int32_t n_ttiles;          // tiles of TOK tokens (per problem)
+    // Grouped calls (groups > 1; the raw-weight kernel's plain form): `groups` independent
+    // problems of the same m x k x n.  The planes are those of the [groups * m, k] matrix (m a
+    // multiple of the token tile), the weight is the packed [groups * n, k] matrix (problem g
+    // owns rows g * w_group_rows ..), the outputs lie out_group_stride elements apart.
+    int32_t groups;
+    int32_t w_group_rows;
+    int64_t out_group_stride;
     int32_t band;              // feature tiles per raster band
     void* out;
     int64_t ldo;
@@ -183,9 +190,10 @@ __device__ __forceinline__ void reconstruct64_x2(const int (&a0)[R], const int (
 
 // Output tile of a cluster: its position in the raster and the CTA's share of it.
 struct PairTile {
-    int n0;      // first feature of this CTA
-    int tok0;    // first token of the pair's tile
-    int tt;      // token tile index
+    int n0;      // first feature of this CTA (inside its group)
+    int tok0;    // first token of the pair's tile (inside its group)
+    int tt;      // token tile index (inside its group)
+    int grp;     // problem of a grouped call (0 otherwise)
 };
 
 template <int TOK>
@@ -193,11 +201,17 @@ __device__ __forceinline__ PairTile pair_tile(const PairParams& p, int tile, uin
     // Raster: feature tiles in bands; inside a band the token tiles advance slowest, so
     // the clusters working at the same time share a band of the weight (it stays in L2)
     // and a few token tiles, and every plane byte is read from DRAM once per band.
+    PairTile t;
+    t.grp = 0;
+    if (p.groups > 1) {              // grouped call: the problems one after the other, each with its own raster
+        const int per_group = p.n_ftiles * p.n_ttiles;
+        t.grp = tile / per_group;
+        tile -= t.grp * per_group;
+    }
     const int per_band = p.band * p.n_ttiles;
     const int band_i = tile / per_band;
     const int in_band = tile - band_i * per_band;
     const int band_w = min(p.band, p.n_ftiles - band_i * p.band);
-    PairTile t;
     t.tt = in_band / band_w;
     const int ft = band_i * p.band + (in_band - t.tt * band_w);
     t.n0 = ft * 256 + (int)rank * 128;
@@ -220,7 +234,8 @@ __device__ __forceinline__ PairTile pair_tile(const PairParams& p, int tile, uin
 template <int R, int TOK, bool COPIES, bool SPLIT, bool PREFIX = false, typename Release>
 __device__ __forceinline__ void pair_epilogue(const PairParams& p, int n0, int tok0, int quarter, int part, int lane,
                                               uint32_t lane_base, bool is_float, float rs_all, float& biggest,
-                                              Release&& release, unsigned short* stage = nullptr, int act = R) {
+                                              Release&& release, unsigned short* stage = nullptr, int act = R,
+                                              int64_t out_off = 0) {
     static_assert(!SPLIT || R <= 4, "one register holds the residues of at most four channels");
     const int feat = n0 + quarter * 32 + lane;
     const bool feat_ok = feat < p.n;
@@ -272,7 +287,7 @@ __device__ __forceinline__ void pair_epilogue(const PairParams& p, int n0, int t
 #pragma unroll
             for (int t8 = 0; t8 < 8; ++t8) {
                 if (t8 < valid_t) {
-                    const int64_t o = (int64_t)(tok_first + t8) * p.ldo + feat;
+                    const int64_t o = out_off + (int64_t)(tok_first + t8) * p.ldo + feat;
                     if (p.out_type == RNS_OUT_INT64) static_cast<long long*>(p.out)[o] = (long long)xv[t8];
                     else static_cast<int*>(p.out)[o] = (int)xv[t8];
                 }
@@ -296,7 +311,7 @@ __device__ __forceinline__ void pair_epilogue(const PairParams& p, int n0, int t
 #pragma unroll
             for (int t8 = 0; t8 < 8; ++t8) {
                 if (t8 < valid_t) {
-                    const int64_t o = (int64_t)(tok_first + t8) * p.ldo + feat;
+                    const int64_t o = out_off + (int64_t)(tok_first + t8) * p.ldo + feat;
                     static_cast<float*>(p.out)[o] = y[t8];
                     for (int g = 0; COPIES && g < p.n_copies; ++g) static_cast<float*>(p.out_copies[g])[o] = y[t8];
                     biggest = fmaxf(biggest, fabsf(y[t8]));
@@ -330,7 +345,7 @@ __device__ __forceinline__ void pair_epilogue(const PairParams& p, int n0, int t
             const int t = quarter * 2 + (lane >> 4);
             const uint4 v = *reinterpret_cast<const uint4*>(sb + t * 128 + (lane & 15) * 8);
             if (t < valid_t) {
-                const int64_t o = (int64_t)(tok_first + t) * p.ldo + n0 + (lane & 15) * 8;
+                const int64_t o = out_off + (int64_t)(tok_first + t) * p.ldo + n0 + (lane & 15) * 8;
                 *reinterpret_cast<uint4*>(out16 + o) = v;
                 for (int g = 0; g < p.n_copies; ++g) {
                     unsigned short* dst = static_cast<unsigned short*>(p.out_copies[g]) + o;
@@ -351,7 +366,7 @@ __device__ __forceinline__ void pair_epilogue(const PairParams& p, int n0, int t
                 const int t8 = 2 * i + (odd ? 1 : 0);
                 if (t8 < valid_t) {
                     const unsigned word = odd ? (got | (mine << 16)) : (mine | (got << 16));
-                    const int64_t o = (int64_t)(tok_first + t8) * p.ldo + (feat & ~1);
+                    const int64_t o = out_off + (int64_t)(tok_first + t8) * p.ldo + (feat & ~1);
                     *reinterpret_cast<unsigned*>(out16 + o) = word;
                     for (int g = 0; COPIES && g < p.n_copies; ++g)
                         *reinterpret_cast<unsigned*>(static_cast<unsigned short*>(p.out_copies[g]) + o) = word;
@@ -361,7 +376,7 @@ __device__ __forceinline__ void pair_epilogue(const PairParams& p, int n0, int t
 #pragma unroll
             for (int t8 = 0; t8 < 8; ++t8) {
                 if (t8 < valid_t) {
-                    const int64_t o = (int64_t)(tok_first + t8) * p.ldo + feat;
+                    const int64_t o = out_off + (int64_t)(tok_first + t8) * p.ldo + feat;
                     out16[o] = h[t8];
                     for (int g = 0; COPIES && g < p.n_copies; ++g) static_cast<unsigned short*>(p.out_copies[g])[o] = h[t8];
                 }
