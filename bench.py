@@ -873,6 +873,69 @@ def run_wide_sources(args) -> None:
                       "rows": rows}))
 
 
+def run_grouped_attention(args) -> None:
+    """Grouped multi-head integer products, scores Q K^T and context P V of all heads of a
+    batch in one launch each (`matmul_grouped`), against (a) the same products one head at a
+    time through the single-problem integer entry (how the reference's attention benchmark
+    shapes them: one head, benchmarks/benchmark_attention.py:107-113), (b) fp16 torch.bmm.
+    CUDA events over `iters` calls; results compared with the per-head path."""
+    import torch
+    from rns_llm_b200.backends import CudaRNSBackend
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; the RNS path has no CPU implementation")
+    backend = CudaRNSBackend()
+    iters, rows = 20, []
+
+    def timed(fn, n):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(n):
+            fn()
+        stop.record()
+        torch.cuda.synchronize()
+        return start.elapsed_time(stop) / n
+
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(2024)
+    for label, heads_total, tokens, head_dim in (("opt125m batch 8 x 512", 96, 512, 64),
+                                                 ("opt6.7b batch 1 x 2048", 32, 2048, 128)):
+        q = torch.randint(-127, 128, (heads_total, tokens, head_dim), generator=gen, device="cuda", dtype=torch.int8)
+        k = torch.randint(-127, 128, (heads_total, tokens, head_dim), generator=gen, device="cuda", dtype=torch.int8)
+        p = torch.randint(0, 128, (heads_total, tokens, tokens), generator=gen, device="cuda", dtype=torch.int8)
+        v_t = torch.randint(-127, 128, (heads_total, head_dim, tokens), generator=gen, device="cuda", dtype=torch.int8)
+        for name, a, b in (("scores Q K^T", q, k), ("context P V", p, v_t)):
+            groups, m, kk = a.shape
+            n = b.shape[1]
+            grouped = backend.matmul_grouped(a, b, MODULI_4)
+            grouped_ms = timed(lambda: backend.matmul_grouped(a, b, MODULI_4), iters)
+            backend.check_status()
+            prepared = [backend.prepare_weight_nk(b[g], MODULI_4) for g in range(min(groups, 8))]
+
+            def per_head():
+                return [backend.matmul_prepared_fused(a[g], prepared[g]) for g in range(len(prepared))]
+            same = all(torch.equal(x, grouped[g]) for g, x in enumerate(per_head()))
+            per_head_ms = timed(per_head, 5) * groups / len(prepared)        # weights prepared outside the timing
+            a16, b16 = a.half(), b.half()
+            fp16_ms = timed(lambda: torch.bmm(a16, b16.transpose(1, 2)), iters)
+            r = len(MODULI_4)
+            rows.append({"shape": label, "product": name, "groups": groups, "m": m, "k": kk, "n": n, "channels": r,
+                         "grouped_ms": grouped_ms, "channel_tops": 2.0 * r * groups * m * kk * n / grouped_ms / 1e9,
+                         "one_head_at_a_time_ms": per_head_ms, "fp16_bmm_ms": fp16_ms,
+                         "equal_to_one_head_at_a_time": bool(same)})
+    print(json.dumps({"metric": "grouped_attention_products_ms", "unit": "ms", "n_gpus": 1, "higher_is_better": False,
+                      "data": "synthetic", "dtype": "int8",
+                      "config": {"workload": "grouped multi-head Q K^T and P V (exact int64 outputs)",
+                                 "moduli": list(MODULI_4), "iters": iters,
+                                 "note": "grouped = plane encode + weight pack + one GEMM launch for all heads; "
+                                         "one head at a time = plane encode + GEMM per head with the packed "
+                                         "operand prepared outside the timed region"},
+                      "rows": rows}))
+
+
 # Where the run is, for the failure report: {"phase": ..., "step": ..., "layer": ..., "linear": ...}
 PROGRESS: dict = {"phase": "start"}
 
@@ -1152,7 +1215,7 @@ def main() -> None:
                         help="skip the torch._int_mm peak measurement (roofline.frac then uses 2 x bf16 sustained)")
     parser.add_argument("--gpu-baselines", action="store_true",
                         help="also time F.linear fp16 and torch._int_mm + eager dequantisation on the stack's shapes")
-    parser.add_argument("--workload", default="c4", choices=["c4", "c1", "c2", "c3", "quant", "peak", "wide"],
+    parser.add_argument("--workload", default="c4", choices=["c4", "c1", "c2", "c3", "quant", "peak", "wide", "attn"],
                         help="c4: the layer stack (the bench contract); c1: fused-QKV latency of configuration 1; "
                              "c2: continuous batching and adaptive channels of configuration 2; c3: the "
                              "OPT-125m-shaped decoder of configuration 3; quant: the activation quantiser alone "
@@ -1172,6 +1235,9 @@ def main() -> None:
         return
     if args.workload == "wide":
         run_wide_sources(args)
+        return
+    if args.workload == "attn":
+        run_grouped_attention(args)
         return
     if args.workload == "quant":
         run_quantiser(args)
