@@ -919,11 +919,14 @@ def run_grouped_attention(args) -> None:
                 return [backend.matmul_prepared_fused(a[g], prepared[g]) for g in range(len(prepared))]
             same = all(torch.equal(x, grouped[g]) for g, x in enumerate(per_head()))
             per_head_ms = timed(per_head, 5) * groups / len(prepared)        # weights prepared outside the timing
+            scaled_ms = timed(lambda: backend.matmul_grouped(a, b, MODULI_4, out_dtype=torch.float16, scale=1e-4),
+                              iters)
             a16, b16 = a.half(), b.half()
             fp16_ms = timed(lambda: torch.bmm(a16, b16.transpose(1, 2)), iters)
             r = len(MODULI_4)
             rows.append({"shape": label, "product": name, "groups": groups, "m": m, "k": kk, "n": n, "channels": r,
                          "grouped_ms": grouped_ms, "channel_tops": 2.0 * r * groups * m * kk * n / grouped_ms / 1e9,
+                         "grouped_fp16_scaled_ms": scaled_ms,
                          "one_head_at_a_time_ms": per_head_ms, "fp16_bmm_ms": fp16_ms,
                          "equal_to_one_head_at_a_time": bool(same)})
     print(json.dumps({"metric": "grouped_attention_products_ms", "unit": "ms", "n_gpus": 1, "higher_is_better": False,

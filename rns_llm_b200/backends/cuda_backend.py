@@ -1038,7 +1038,7 @@ class CudaRNSBackend:
         return out
 
     def matmul_grouped(self, a: torch.Tensor, b_nk: torch.Tensor, moduli: Iterable[int], *,
-                       out_dtype: torch.dtype = torch.int64) -> torch.Tensor:
+                       out_dtype: torch.dtype = torch.int64, scale: float | None = None) -> torch.Tensor:
         """Exact integer products of ``G`` independent problems in ONE launch:
         ``out[g] = a[g] @ b_nk[g].T`` for int8 ``a`` [G,M,K] and ``b_nk`` [G,N,K] (both
         operands are activations: nothing is cached).  The grouped multi-head products of
@@ -1047,7 +1047,10 @@ class CudaRNSBackend:
         open work (docs/OPTIMIZATIONS_V04.md:49) and times for one head through the plane
         pipeline (benchmarks/benchmark_attention.py:107-113).  One launch encodes the tiled
         residue planes of all G*M rows, one packs all G*N weight rows, one runs the two-CTA
-        kernel over every (problem, tile).  4 to 6 moduli, K % 16 == 0, N % 8 == 0."""
+        kernel over every (problem, tile).  4 to 6 moduli, K % 16 == 0, N % 8 == 0.
+        ``out_dtype`` int64 / int32 returns the integers; float16 / bfloat16 / float32 with
+        ``scale`` returns ``type(f32(x) * f32(scale))`` from the epilogue (a quarter of the
+        output bytes of int64: e.g. scores scaled by s_q * s_k / sqrt(d))."""
         if a.ndim != 3 or b_nk.ndim != 3 or a.dtype != torch.int8 or b_nk.dtype != torch.int8:
             raise ValueError("matmul_grouped takes int8 a [G,M,K] and b_nk [G,N,K]")
         if not a.is_cuda or a.device != b_nk.device:
@@ -1062,8 +1065,9 @@ class CudaRNSBackend:
             raise ValueError("matmul_grouped needs 4 to 6 moduli, K % 16 == 0, K >= 64 and N % 8 == 0")
         if not self.tensor_core_compatible(k=k, moduli=mods):
             raise ValueError("moduli / K are outside the tensor-core kernel's range")
-        if out_dtype not in (torch.int64, torch.int32):
-            raise ValueError("out_dtype must be torch.int64 or torch.int32")
+        floating = out_dtype in _FLOAT_TYPES
+        if floating != (scale is not None) or (not floating and out_dtype not in (torch.int64, torch.int32)):
+            raise ValueError("out_dtype int64 / int32 without scale, or float16 / bfloat16 / float32 with scale")
         token_tile = {4: 128, 5: 96, 6: 64}[channels]
         m_pad = -(-m // token_tile) * token_tile
         a = a.contiguous()
@@ -1087,8 +1091,12 @@ class CudaRNSBackend:
             self._stats["encode_centered_values"] += int(a.numel())
             self._stats["fused_gemm_calls"] += 1
             self._stats[f"fused_gemm_channels_{channels}"] += 1
+            scales = {}
+            if floating:
+                scales = dict(row_scale=torch.full((1,), float(scale), dtype=torch.float32, device=device),
+                              row_scale_stride=0, col_scale=torch.ones(n, dtype=torch.float32, device=device))
             self._launch_fused(prepared=prepared, m=m_pad, a=None, a_planes=planes, a_packed=True, out=out[0],
-                               a_tile_rows=tile_rows, groups=groups, packed_weight=packed, stream=stream)
+                               a_tile_rows=tile_rows, groups=groups, packed_weight=packed, stream=stream, **scales)
         return out[:, :m] if m_pad != m else out
 
     def supports_wide_forward(self, prepared: PreparedRNSWeight, m: int) -> bool:

@@ -73,6 +73,21 @@ def test_attention_scores_and_values_of_all_heads(backend):
     backend.check_status()
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
+def test_grouped_scaled_floating_outputs(backend, dtype):
+    rng = np.random.default_rng(5)
+    groups, m, k, n = 12, 256, 64, 264
+    a = rng.integers(-127, 128, size=(groups, m, k)).astype(np.int8)
+    b = rng.integers(-127, 128, size=(groups, n, k)).astype(np.int8)
+    scale = np.float32(0.0123 * 0.0456 / 8.0)
+    got = backend.matmul_grouped(torch.from_numpy(a).cuda(), torch.from_numpy(b).cuda(), C0, out_dtype=dtype,
+                                 scale=float(scale))
+    expect = (grouped_exact(a, b).astype(np.float32) * scale).astype(np.float32)
+    expect = expect.astype(np.float16) if dtype == torch.float16 else expect
+    assert np.array_equal(got.cpu().numpy(), expect)
+    backend.check_status()
+
+
 def test_grouped_arguments_are_checked(backend):
     a = torch.zeros((2, 128, 64), dtype=torch.int8, device="cuda")
     with pytest.raises(ValueError):
@@ -83,3 +98,6 @@ def test_grouped_arguments_are_checked(backend):
         backend.matmul_grouped(a, torch.zeros((2, 128, 64), dtype=torch.int8, device="cuda"), (127, 126, 125))
     with pytest.raises(ValueError):
         backend.matmul_grouped(a.float(), torch.zeros((2, 128, 64), dtype=torch.int8, device="cuda"), C0)
+    with pytest.raises(ValueError):      # a floating output needs its scale
+        backend.matmul_grouped(a, torch.zeros((2, 128, 64), dtype=torch.int8, device="cuda"), C0,
+                               out_dtype=torch.float16)
