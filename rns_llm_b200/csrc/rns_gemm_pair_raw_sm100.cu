@@ -29,7 +29,7 @@
 namespace rns {
 
 #ifndef RNS_PAIR_SPLIT_EPILOGUE
-#define RNS_PAIR_SPLIT_EPILOGUE 1   // 0: single-phase epilogue, for comparison builds
+#define RNS_PAIR_SPLIT_EPILOGUE 6   // two-phase epilogue up to this many channels (0: never), for comparison builds
 #endif
 // WCH: the weight operand is given per channel (R packed matrices, p.w_channel_stride
 // bytes apart): sources wider than int8, whose residues do not fit the trick above, with
@@ -231,7 +231,7 @@ rns_gemm_pair_raw_kernel(const __grid_constant__ PairParams p) {
             }
             if (!ok) break;
             tc_fence_after();
-            pair_epilogue<R, TOK, COPIES, (R <= 4 && RNS_PAIR_SPLIT_EPILOGUE != 0), PREFIX>(
+            pair_epilogue<R, TOK, COPIES, (R <= 6 && R <= RNS_PAIR_SPLIT_EPILOGUE), PREFIX>(
                 p, t.n0, t.tok0, quarter, part, lane, lane_base, is_float, rs_all, biggest, release,
                 COPIES ? reinterpret_cast<unsigned short*>(smem_dyn + (tiles_base - smem_addr(smem_dyn)) +
                                                            (size_t)S * (kWStage + kPlStage)) : nullptr, act,

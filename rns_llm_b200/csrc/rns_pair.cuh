@@ -166,11 +166,11 @@ __device__ __forceinline__ void reconstruct32_x2(const int (&a0)[R], const int (
 }
 
 // reconstruct for two outputs (any R up to 8, all channels active).
-template <int R, bool PREFIX = false>
+template <int R, bool RES = false, bool PREFIX = false>
 __device__ __forceinline__ void reconstruct64_x2(const int (&a0)[R], const int (&a1)[R], const Plan& pl, long long& x0, long long& x1,
                                                  int act = R) {
     F2 digit[R];
-    garner_digits_x2<R, false, PREFIX>(a0, a1, pl, digit, act);
+    garner_digits_x2<R, RES, PREFIX>(a0, a1, pl, digit, act);
     const F2 magic = f2_splat(kMagic);
     int lo0 = 0, lo1 = 0;
     long long v0 = 0, v1 = 0;
@@ -236,7 +236,7 @@ __device__ __forceinline__ void pair_epilogue(const PairParams& p, int n0, int t
                                               uint32_t lane_base, bool is_float, float rs_all, float& biggest,
                                               Release&& release, unsigned short* stage = nullptr, int act = R,
                                               int64_t out_off = 0) {
-    static_assert(!SPLIT || R <= 4, "one register holds the residues of at most four channels");
+    static_assert(!SPLIT || R <= 6, "the packed form covers up to six channels");
     const int feat = n0 + quarter * 32 + lane;
     const bool feat_ok = feat < p.n;
     float cs = 0.0f, bs = 0.0f;
@@ -279,7 +279,7 @@ __device__ __forceinline__ void pair_epilogue(const PairParams& p, int n0, int t
 #pragma unroll
             for (int c = 0; c < R; ++c) { one0[c] = acc[c][t8]; one1[c] = acc[c][t8 + 1]; }
             if constexpr (R <= 4) reconstruct32_x2<R, RES, PREFIX>(one0, one1, p.plan, xv[t8], xv[t8 + 1], act);
-            else reconstruct64_x2<R, PREFIX>(one0, one1, p.plan, xv[t8], xv[t8 + 1], act);
+            else reconstruct64_x2<R, RES, PREFIX>(one0, one1, p.plan, xv[t8], xv[t8 + 1], act);
         }
         const int valid_t = min(8, p.m - tok_first);   // warp-uniform
         if (!is_float) {
@@ -388,34 +388,40 @@ __device__ __forceinline__ void pair_epilogue(const PairParams& p, int n0, int t
     const std::false_type sums;
     if constexpr (SPLIT) {
         // Phase 1.  One buffer: the other warps of the scheduler cover the load latency.
+        // Channels 0..3 of an output share one register, a byte each; channels 4 and 5 are
+        // packed densely, kExtra bytes per output, 8 * kExtra bytes per step of 8 columns.
+        constexpr int kLow = R < 4 ? R : 4;
+        constexpr int kExtra = R - kLow;
+        constexpr int kHighWords = kExtra == 0 ? 1 : 2 * kExtra;
         uint32_t packed[kIters][8];
+        [[maybe_unused]] uint32_t packed_high[kIters][kHighWords];
         // Every modulus below 128 (the int8 configurations): the Barrett step's result in
         // [0, 2m) already fits its byte, and the recurrence of phase 2 takes it as it is.
         const bool byte_fits = p.plan.encode_fast != 0;
+        auto residue = [&](int v, int c) -> uint32_t {
+            return byte_fits ? nonneg_residue(v, p.plan.mod[c], p.plan.recip[c], p.plan.ubias[c])
+                             : canonical_residue(v, p.plan.mod[c], p.plan.recip[c], p.plan.ubias[c]);
+        };
 #pragma unroll
         for (int it = 0; it < kIters; ++it) {
             int acc[R][8];
             load(col0 + it * 8, acc);
             tmem_ld_wait();
-            if (byte_fits) {
 #pragma unroll
-                for (int t8 = 0; t8 < 8; ++t8) {
-                    uint32_t word = 0;
+            for (int w = 0; w < kHighWords; ++w) packed_high[it][w] = 0u;
 #pragma unroll
-                    for (int c = 0; c < R; ++c)
-                        if (!PREFIX || c < act)      // columns of unused channels hold stale sums
-                            word |= nonneg_residue(acc[c][t8], p.plan.mod[c], p.plan.recip[c], p.plan.ubias[c]) << (8 * c);
-                    packed[it][t8] = word;
-                }
-            } else {
+            for (int t8 = 0; t8 < 8; ++t8) {
+                uint32_t word = 0;
 #pragma unroll
-                for (int t8 = 0; t8 < 8; ++t8) {
-                    uint32_t word = 0;
+                for (int c = 0; c < kLow; ++c)
+                    if (!PREFIX || c < act)      // columns of unused channels hold stale sums
+                        word |= residue(acc[c][t8], c) << (8 * c);
+                packed[it][t8] = word;
 #pragma unroll
-                    for (int c = 0; c < R; ++c)
-                        if (!PREFIX || c < act)
-                            word |= canonical_residue(acc[c][t8], p.plan.mod[c], p.plan.recip[c], p.plan.ubias[c]) << (8 * c);
-                    packed[it][t8] = word;
+                for (int e = 0; e < kExtra; ++e) {
+                    const int byte = t8 * kExtra + e;                // position in this step's high bytes
+                    if (!PREFIX || kLow + e < act)
+                        packed_high[it][byte >> 2] |= residue(acc[kLow + e][t8], kLow + e) << (8 * (byte & 3));
                 }
             }
         }
@@ -426,9 +432,15 @@ __device__ __forceinline__ void pair_epilogue(const PairParams& p, int n0, int t
         for (int it = 0; it < kIters; ++it) {
             int acc[R][8];
 #pragma unroll
-            for (int t8 = 0; t8 < 8; ++t8)
+            for (int t8 = 0; t8 < 8; ++t8) {
 #pragma unroll
-                for (int c = 0; c < R; ++c) acc[c][t8] = (int)((packed[it][t8] >> (8 * c)) & 0xffu);
+                for (int c = 0; c < kLow; ++c) acc[c][t8] = (int)((packed[it][t8] >> (8 * c)) & 0xffu);
+#pragma unroll
+                for (int e = 0; e < kExtra; ++e) {
+                    const int byte = t8 * kExtra + e;
+                    acc[kLow + e][t8] = (int)((packed_high[it][byte >> 2] >> (8 * (byte & 3))) & 0xffu);
+                }
+            }
             finish(col0 + it * 8, acc, residues);
         }
     } else if constexpr (R <= 4) {
