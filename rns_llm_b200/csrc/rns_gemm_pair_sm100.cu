@@ -370,8 +370,14 @@ int launch_pair_gemm(const rns_linear_args* a, const Plan& plan, cudaStream_t st
     pp.n_ttiles = (a->m + tok - 1) / tok;
     // Band: as many feature tiles as keep the band's weight bytes around 32 MB (a quarter
     // of L2), at least the number that fills the GPU once with one token tile each.
-    const int64_t band_bytes = 32ll << 20;
-    int band = (int)(band_bytes / ((int64_t)256 * pp.kblocks * kPackK));
+    // (Per-channel weight planes count R times: with one byte per value assumed, the bands of
+    // a five-channel wide layer held 160 MB and the launch read 4.5 GB from DRAM, 13 times
+    // its operands.)
+    // Measured on the wide QKV / fc2 shapes: 32 MB suits K = 4096, 96 MB K = 16384, where every
+    // band re-reads 335 MB of planes.
+    const int64_t band_bytes = (a->w_channel_stride != 0 && a->k >= 8192 ? 96ll : 32ll) << 20;
+    const int64_t weight_copies = a->w_channel_stride != 0 ? R : 1;
+    int band = (int)(band_bytes / ((int64_t)256 * pp.kblocks * kPackK * weight_copies));
     if (band < 1) band = 1;
     if (band > pp.n_ftiles) band = pp.n_ftiles;
     pp.band = band;
