@@ -602,9 +602,9 @@ rns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             uint8_t* enc_stage = tiles_ptr + enc_ring_offset + (size_t)se * enc_stage_bytes;
             const int jn = (FIXED && J_ == 1) ? 1 : min(J, kblocks - st * J);
             // Order matters once several groups run ahead of each other: the operand
-            // slot must first be released by the MMAs of its previous round.  Because
+            // slot must first be released by the MMAs of its previous revolution of the ring.  Because
             // the raw ring is at least as deep as the operand ring, that also proves
-            // that the raw slot's previous round has completed, which makes the parity
+            // that the raw slot's previous revolution has completed, which makes the parity
             // of the full_raw wait unambiguous.
             if (round_e > 0) ok = warp_wait_bounded<false, kSpinWorkers>(smem_addr(&ctl.empty_enc[se]), (round_e - 1) & 1, abort, wait_code(9, st));
             if (ok) ok = warp_wait_bounded<false, kSpinWorkers>(smem_addr(&ctl.full_raw[sr]), round_r & 1, abort, wait_code(10, st));

@@ -246,7 +246,7 @@ rns_gemm_tmem_kernel(const __grid_constant__ TmemGemmParams p) {
 #pragma unroll
                 for (int i = 0; i < 16; ++i) d[i] = fold_pattern(x[i]);
             }
-            // the slot pair must have been consumed by the MMAs of its previous round
+            // the slot pair must have been consumed by the MMAs of its previous revolution of the ring
             if (round > 0) ok = wait_bounded(smem_addr(&ctl.op_empty[so]), (round - 1) & 1, abort);
             if (!ok) break;
             tc_fence_after();
