@@ -489,6 +489,23 @@ RNS_API int rns_linear_small(const void* d_x, int x_type, int m, int k, int64_t 
                              int32_t out_type, rns_stream_t stream);
 
 /*
+ * Few tokens on LARGE weights (decode steps of a big model: M <= 64, any K % 16 == 0, 2..5
+ * channels): the same result as rns_linear_fused from ONE launch that streams the packed
+ * weight once, from activations that are already quantised - d_q int8 [M,K] (row stride ldq,
+ * a multiple of 8; 8-byte aligned) with their scale(s) on the device, as
+ * rns_quantize_activations leaves them (plain layout).  Floating outputs:
+ * type(f32(x) * d_row_scale[m * row_scale_stride] * d_col_scale[n] (+ d_bias[n])); integer
+ * outputs (d_row_scale NULL): the exact products.  No scratch.  No counterpart in the
+ * reference, whose path is the same for every M (layers/rns_linear.py:237-275).
+ */
+RNS_API int rns_linear_stream_supported(int m, int k, int channels);
+RNS_API int rns_linear_stream(const int8_t* d_q, int m, int k, int64_t ldq, const float* d_row_scale,
+                              int row_scale_stride, const int8_t* d_w_packed, int n,
+                              const int32_t* moduli, int channels, const float* d_col_scale,
+                              const float* d_bias, void* d_out, int64_t ldo, int32_t out_type,
+                              rns_stream_t stream);
+
+/*
  * The floating-point linear for hosts that cannot allocate device memory.  It
  * has no counterpart in the reference, whose workspaces are torch tensors.
  *

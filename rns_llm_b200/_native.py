@@ -110,6 +110,9 @@ SIGNATURES: dict[str, tuple] = {
     "rns_row_l1_max_i8": (C.c_int, [_VP, C.c_int, C.c_int, C.c_int64, _VP, _VP]),
     "rns_select_channels": (C.c_int, [_VP, C.c_int32, _I32P, C.c_int, C.c_int, _VP, _VP, _VP, _VP, _VP]),
     "rns_linear_small_supported": (C.c_int, [C.c_int, C.c_int, C.c_int]),
+    "rns_linear_stream_supported": (C.c_int, [C.c_int, C.c_int, C.c_int]),
+    "rns_linear_stream": (C.c_int, [_VP, C.c_int, C.c_int, C.c_int64, _VP, C.c_int, _VP, C.c_int, _I32P, C.c_int,
+                                    _VP, _VP, _VP, C.c_int64, C.c_int32, _VP]),
     "rns_linear_small": (C.c_int, [_VP, C.c_int, C.c_int, C.c_int, C.c_int64, C.c_int, _VP, C.c_int, _I32P, C.c_int,
                                    _VP, _VP, _VP, C.c_int64, C.c_int32, _VP]),
     "rns_static_scratch_bytes": (C.c_int64, []),

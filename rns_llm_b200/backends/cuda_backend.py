@@ -50,6 +50,7 @@ PLANES_MIN_ROWS = 512
 # 4096 x 4096 / 12288 weights under graph replay).  At most 32 rows go to the one-launch kernel
 # where it holds the residues of a token block in shared memory (K up to 1536 at four channels).
 PAIR_MIN_ROWS = 320
+STREAM_MAX_ROWS = 32         # few tokens beyond the one-launch kernel's K: the weight-streaming kernel
 PAIR_LARGE_WEIGHT = 1 << 23
 WIDE_MIN_ROWS = 128          # wide sources: fewer rows stay on the plane-level pipeline
 
@@ -969,6 +970,29 @@ class CudaRNSBackend:
                     prepared.weight_packed.data_ptr(), prepared.n, arr, channels, weight_scale.data_ptr(),
                     None if bias is None else bias.data_ptr(), out.data_ptr(), out.stride(0),
                     _OUT_TYPES[out.dtype], self._stream(device)))
+            self._stats["encode_centered_calls"] += 1
+            self._stats["encode_centered_values"] += m * k
+            self._stats["fused_gemm_calls"] += 1
+            self._stats[f"fused_gemm_channels_{channels}"] += 1
+            return (out, None) if return_metadata else out
+        if (adaptive is None and absmax_out is None and not out_copies and m <= STREAM_MAX_ROWS and k % 8 == 0 and
+                k * prepared.n < PAIR_LARGE_WEIGHT and self._lib.rns_linear_stream_supported(m, k, channels)):
+            # Few tokens on a weight whose K the one-launch kernel cannot hold (and which is not
+            # large: from K*N = 2^23 the two-CTA kernel measured faster): quantise to plain int8
+            # (one or two small launches), then ONE launch that streams the weight once.
+            with torch.cuda.device(device):
+                scale_bytes = ((m if per_row else 1) * 4 + 255) & ~255
+                base, stream = self.arena.block(device, scale_bytes + 256 + m * k)
+                scale, scratch, act = base, base + scale_bytes, base + scale_bytes + 256
+                parts_ptr, parts, parts_stride = absmax_in if absmax_in is not None else (None, 0, 0)
+                N.check(self._lib.rns_quantize_activations_tiled(
+                    x.data_ptr(), _FLOAT_TYPES[x.dtype], m, k, ldx, col_block, col_block_stride,
+                    1 if per_row else 0, 127, arr, channels, act, None, 0, 0, scale, None, scratch,
+                    parts_ptr, parts, parts_stride, stream))
+                N.check(self._lib.rns_linear_stream(
+                    act, m, k, k, scale, 1 if per_row else 0, prepared.weight_packed.data_ptr(), prepared.n, arr,
+                    channels, weight_scale.data_ptr(), None if bias is None else bias.data_ptr(), out.data_ptr(),
+                    out.stride(0), _OUT_TYPES[out.dtype], stream))
             self._stats["encode_centered_calls"] += 1
             self._stats["encode_centered_values"] += m * k
             self._stats["fused_gemm_calls"] += 1

@@ -16,8 +16,8 @@ from pathlib import Path
 HERE = Path(__file__).resolve().parent
 REPO = HERE.parent.parent
 SOURCES = ("rns_host.cu", "rns_aux.cu", "rns_gemm_sm100.cu", "rns_gemm_tmem_sm100.cu",
-           "rns_gemm_pair_sm100.cu", "rns_gemm_pair_raw_sm100.cu", "rns_small_sm100.cu", "rns_static_scratch.cu")
-HEADERS = (HERE / "rns_common.cuh", HERE / "rns_ptx.cuh", HERE / "rns_pair.cuh", REPO / "include" / "rns_b200.h")
+           "rns_gemm_pair_sm100.cu", "rns_gemm_pair_raw_sm100.cu", "rns_small_sm100.cu", "rns_stream_sm100.cu", "rns_static_scratch.cu")
+HEADERS = (HERE / "rns_common.cuh", HERE / "rns_ptx.cuh", HERE / "rns_pair.cuh", HERE / "rns_mma_sync.cuh", REPO / "include" / "rns_b200.h")
 LIBRARY = HERE / "librns_b200.so"
 
 NVCC_FLAGS = [
