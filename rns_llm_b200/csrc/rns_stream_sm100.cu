@@ -10,10 +10,10 @@
 //   - 4 warps; the CTA owns 16 tokens x 32 output features, warp w the 8 features
 //     n0 + 8w .. + 7 (one n-tile of mma.sync.m16n8k32), for ALL of K: no partial sums meet;
 //   - per chunk all threads form the residues of the 16 x 512 int8 activations (one fold
-//     pattern per word, a multiply-add and an xor per channel) in shared memory, in fragment
-//     order; then every warp runs the chunk's 16 K steps: one mma per channel and step, the
-//     A fragments from shared memory, the B fragment = the int8 weight words themselves
-//     (every channel's operand, as in the other kernels);
+//     pattern per word, a multiply-add and an xor per channel) in shared memory, fragment-major
+//     (a lane's four A words side by side: one 128-bit load per fragment); then every warp runs
+//     the chunk's 16 K steps: one mma per channel and step, the B fragment = the int8 weight
+//     words themselves (every channel's operand, as in the other kernels);
 //   - a lane keeps the weight words of 16 K steps in registers, requested one chunk ahead
 //     (2 words per step): 4 KB per warp in flight, about 40 KB per SM with three CTAs
 //     resident - the latency-bandwidth product of HBM.
@@ -56,7 +56,7 @@ struct StreamParams {
 template <int R>
 __global__ void __launch_bounds__(kStreamThreads)
 rns_linear_stream_kernel(const __grid_constant__ StreamParams p) {
-    // residues of one chunk: [channel][K step][half][token row][16 bytes]
+    // residues of one chunk: [channel][K step][lane of the mma][its four A words]
     __shared__ __align__(16) uint8_t s_a[R * kStreamSteps * 512];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
@@ -97,13 +97,19 @@ rns_linear_stream_kernel(const __grid_constant__ StreamParams p) {
                 const uint2 raw = *reinterpret_cast<const uint2*>(p.q + (int64_t)(m0 + r) * p.ldq + c0 + col);
                 word[0] = raw.x; word[1] = raw.y;
             }
-            const int kstep = col >> 5, byte_in_step = col & 31;
+            // Fragment-major layout: per channel and K step, lane (g, t) of the mma owns 16
+            // contiguous bytes = its four A words {row g half 0, row g+8 half 0, row g half 1,
+            // row g+8 half 1}, so a fragment is ONE 128-bit shared-memory load.  The 8 columns of
+            // this thread are words t0 and t0 + 1 of row r in one half of the step.
+            const int kstep = col >> 5, half = (col >> 4) & 1, t0 = (col & 15) >> 2;
+            const int slot = half * 2 + (r >> 3);
 #pragma unroll
             for (int c = 0; c < R; ++c) {
-                uint2 e;
-                e.x = encode_word_reduced(word[0] ^ 0x80808080u, fold_pattern(word[0]), p.plan.enc_mfold[c]);
-                e.y = encode_word_reduced(word[1] ^ 0x80808080u, fold_pattern(word[1]), p.plan.enc_mfold[c]);
-                *reinterpret_cast<uint2*>(s_a + small_a_offset(c, kstep, kStreamSteps, r, byte_in_step)) = e;
+                const uint32_t e0 = encode_word_reduced(word[0] ^ 0x80808080u, fold_pattern(word[0]), p.plan.enc_mfold[c]);
+                const uint32_t e1 = encode_word_reduced(word[1] ^ 0x80808080u, fold_pattern(word[1]), p.plan.enc_mfold[c]);
+                uint8_t* base = s_a + (size_t)(c * kStreamSteps + kstep) * 512 + slot * 4;
+                *reinterpret_cast<uint32_t*>(base + ((r & 7) * 4 + t0) * 16) = e0;
+                *reinterpret_cast<uint32_t*>(base + ((r & 7) * 4 + t0 + 1) * 16) = e1;
             }
         }
         __syncthreads();
@@ -114,12 +120,8 @@ rns_linear_stream_kernel(const __grid_constant__ StreamParams p) {
             load_weight((chunk + 1) * kStreamSteps + i, w0[i], w1[i]);
 #pragma unroll
             for (int c = 0; c < R; ++c) {
-                uint32_t a[4];
-                const uint8_t* ap = s_a + small_a_offset(c, i, kStreamSteps, 0, 0);
-                a[0] = *reinterpret_cast<const uint32_t*>(ap + g * 16 + 4 * t);
-                a[1] = *reinterpret_cast<const uint32_t*>(ap + (g + 8) * 16 + 4 * t);
-                a[2] = *reinterpret_cast<const uint32_t*>(ap + 256 + g * 16 + 4 * t);
-                a[3] = *reinterpret_cast<const uint32_t*>(ap + 256 + (g + 8) * 16 + 4 * t);
+                const uint4 f = *reinterpret_cast<const uint4*>(s_a + (size_t)(c * kStreamSteps + i) * 512 + lane * 16);
+                const uint32_t a[4] = {f.x, f.y, f.z, f.w};
                 mma_s8(acc[c], a, b);
             }
         }
