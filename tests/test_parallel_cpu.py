@@ -161,3 +161,73 @@ def test_sharded_layer_result_ownership_two_ranks():
     results = manager.dict()
     mp.spawn(_layer_worker, args=(world, port, results), nprocs=world, join=True)
     assert dict(results) == {0: True, 1: True}
+
+
+class _RecordingBackend(_FakeBackend):
+    """Reports the many-token kernel as available and records what the layer asks of it."""
+
+    def __init__(self):
+        self.calls = []
+
+    def supports_absmax_out(self, *, m, k, channels):
+        return True
+
+    def linear_forward(self, x, prepared, weight_scale, bias, *, per_row=False, out=None, absmax_in=None,
+                       absmax_out=None, out_copies=(), absmax_copies=(), copies_multicast=False):
+        self.calls.append({"out_copies": list(out_copies), "absmax_copies": list(absmax_copies),
+                           "multicast": bool(copies_multicast), "absmax_out": absmax_out})
+        return super().linear_forward(x, prepared, weight_scale, bias, per_row=per_row, out=out)
+
+
+class _FakeArena:
+    """The addressing of PeerArena without symmetric memory: four 'ranks' with made-up bases."""
+
+    def __init__(self, rank: int, world: int, multicast_base: int):
+        from rns_llm_b200.parallel import PeerArena
+        self.rank, self.world = rank, world
+        self.buffer = torch.zeros(1 << 20, dtype=torch.uint8)
+        self.peer_bases = [0x10_0000_0000 * (r + 1) for r in range(world)]
+        self.multicast_base = multicast_base
+        self.nbytes, self._offset, self.barriers = int(self.buffer.numel()), 0, 0
+        self.alloc = PeerArena.alloc.__get__(self)
+        self.peer_addresses = PeerArena.peer_addresses.__get__(self)
+
+    def barrier(self):
+        self.barriers += 1
+
+
+def test_exchange_addresses_of_a_sharded_layer(monkeypatch):
+    """Per-peer stores go to every OTHER rank's slot, starting with the right-hand neighbour;
+    the multicast form hands the kernel ONE address inside the multicast mapping, and only for
+    shards whose shape the row-wide multicast store covers."""
+    import torch.cuda as cuda
+    from rns_llm_b200.parallel import ABSMAX_PAD, ColumnShardedRNSLinear
+
+    class _NoStream:
+        cuda_stream = 0
+    monkeypatch.setattr(cuda, "current_stream", lambda device=None: _NoStream())
+    rank, world, m, k = 1, 4, 8, 32
+    mc_base = 0x7f_0000_0000
+    for local, multicast, expect_mc in ((128, True, True), (128, False, False), (64, True, False)):
+        backend, arena = _RecordingBackend(), _FakeArena(rank, world, mc_base)
+        layer = ColumnShardedRNSLinear(torch.randn(local, k).half(), None, backend=backend, moduli=(127, 126, 125, 121),
+                                       rank=rank, world=world, peer_arena=arena, multicast=multicast)
+        assert layer.multicast == multicast
+        y = layer(torch.randn(m, k).half())
+        assert y.shape == (world, m, local) and arena.barriers == 1
+        call = backend.calls[-1]
+        block = (m * local + ABSMAX_PAD) * 2                      # bytes of one rank's block (fp16)
+        mine = rank * block                                       # first layer of the arena: offset 0
+        assert call["multicast"] == expect_mc
+        if expect_mc:
+            assert call["out_copies"] == [mc_base + mine]
+            assert call["absmax_copies"] == [mc_base + mine + m * local * 2]
+        else:
+            order = [2, 3, 0]                                     # neighbours of rank 1, wrapping round
+            assert call["out_copies"] == [arena.peer_bases[r] + mine for r in order]
+            assert call["absmax_copies"] == [arena.peer_bases[r] + mine + m * local * 2 for r in order]
+    # an arena without a multicast mapping: the flag is dropped at construction
+    plain = ColumnShardedRNSLinear(torch.randn(128, k).half(), None, backend=_RecordingBackend(),
+                                   moduli=(127, 126, 125, 121), rank=rank, world=world,
+                                   peer_arena=_FakeArena(rank, world, 0), multicast=True)
+    assert plain.multicast is False
